@@ -1,0 +1,196 @@
+/* neoml_b200.h -- C ABI of the B200 (sm_100a) kernel library behind a NeoML IMathEngine.
+ *
+ * Every entry point is the device-side body of one IMathEngine virtual (NeoMathEngine/include/NeoMathEngine/
+ * NeoMathEngine.h, cited per function as NME.h:line).  Conventions:
+ *   - all pointers are DEVICE pointers to fp32 / int32 data of the calling process, 4-byte aligned or better
+ *     (NeoML handles may sit at any 4-byte offset; aligned fast paths are selected at run time);
+ *   - sizes are element counts, exactly the ints the IMathEngine method receives;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, nothing synchronises;
+ *   - the return value is 0 (NB200_OK) or a negative NB200_E* code; nothing throws, nothing allocates;
+ *     the engine turns a non-zero code into IMathEngineExceptionHandler::OnAssert;
+ *   - optional operands (free terms, residual) are NULL when absent, like the `const CConstFloatHandle*`
+ *     arguments of the reference.
+ * There is no CPU fallback: on a machine without a usable sm_100 device every compute call returns
+ * NB200_ENODEVICE.
+ */
+#ifndef NEOML_B200_H
+#define NEOML_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB200_API __attribute__((visibility("default")))
+
+enum {
+	NB200_OK = 0,
+	NB200_EINVAL = -1,     /* bad argument (negative size, null required pointer, unsupported combination) */
+	NB200_ENODEVICE = -2,  /* no sm_100 device / CUDA runtime error at launch */
+	NB200_ELAUNCH = -3,    /* cudaGetLastError() after the launch was not cudaSuccess */
+	NB200_EDEVICE = -4,    /* a kernel reported a bounded-wait timeout in the status word */
+	NB200_ETOOBIG = -5     /* request exceeds a documented fixed capacity */
+};
+
+/* Arithmetic of the dense contractions.  The reference selects cuBLAS math modes with the engine flags
+ * GpuMathEngineCublasUseTensorCores{Half,TF32}Flag (NME.h:1271-1274, CudaMathEngine.cu:56-65). */
+enum {
+	NB200_PREC_3XTF32 = 0, /* default: hi/lo TF32 split, 3 tcgen05 MMAs, fp32 accumulate; fp32-level accuracy */
+	NB200_PREC_TF32 = 1,   /* opt-in single TF32 MMA (1e-2 tolerance class) */
+	NB200_PREC_FP32_SIMT = 2 /* exact fp32 FMA on CUDA cores; diagnostic cross-check, slow */
+};
+
+/* Epilogue activations (TActivationFunction subset used by the rowwise descs, ActivationDesc.h:27-47). */
+enum {
+	NB200_ACT_NONE = 0,
+	NB200_ACT_RELU = 1,   /* param > 0: min(max(x,0),param); else max(x,0)  (VectorReLU, NME.h:143-145) */
+	NB200_ACT_HSWISH = 2  /* x * relu6(x+3) / 6 */
+};
+
+/* Optional fused tail of a contraction: y = act(acc + bias[n] (+ residual[m,n])).
+ * The plain IMathEngine calls use bias only; the engine's fusion queue fills the rest. */
+typedef struct nb200_epilogue {
+	const float* bias;       /* [N] or NULL */
+	const float* residual;   /* [M x N] with row stride ld_residual, or NULL; may alias the output */
+	int ld_residual;
+	int act;                 /* NB200_ACT_* */
+	float act_param;         /* ReLU upper threshold (<=0: none) */
+	int accumulate;          /* 1: y += result (the ...AndAdd variants); 0: overwrite */
+} nb200_epilogue;
+
+/* ---- library ------------------------------------------------------------------------------------------- */
+NB200_API int nb200_version(void);
+/* Number of sm_100 devices visible; 0 when none (then every compute call fails with NB200_ENODEVICE). */
+NB200_API int nb200_device_count(void);
+NB200_API const char* nb200_error_string(int code);
+/* Device-side status word of the calling thread's current device: 0 = clean, else the code of the first bounded
+ * wait that gave up (kernel id << 8 | site).  Reading synchronises `stream`.  `reset` != 0 clears it. */
+NB200_API int nb200_device_status(void* stream, int reset);
+/* Kernels launched by this library in this process since load (for launch accounting in benchmarks). */
+NB200_API uint64_t nb200_launch_count(void);
+
+/* ---- dense contractions (tcgen05 / TMEM) ----------------------------------------------------------------- */
+/* IBlasEngine::MultiplyMatrixByTransposedMatrix (NME.h:529-532):
+ * C[M x N] (row stride ldc) = A[M x K] (row stride lda) * B[N x K]^T (row stride ldb). */
+NB200_API int nb200_multiply_matrix_by_transposed_matrix(void* stream, const float* a, int m, int k, int lda,
+	const float* b, int n, int ldb, float* c, int ldc, const nb200_epilogue* epi, int precision);
+/* Batched overload (NME.h:533-535): `batch` contiguous problems of identical shape, dense strides. */
+NB200_API int nb200_batch_multiply_matrix_by_transposed_matrix(void* stream, int batch, const float* a, int m,
+	int k, const float* b, int n, float* c, const nb200_epilogue* epi, int precision);
+/* IBlasEngine::MultiplyMatrixByMatrix (NME.h:580-582): C_b[M x N] = A_b[M x K] * B_b[K x N], dense row-major. */
+NB200_API int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int m, int k,
+	const float* b, int n, float* c, const nb200_epilogue* epi, int precision);
+/* IDnnEngine::InitBlobConvolution + BlobConvolution (NME.h:751-756; CPU CpuMathEngineDnnConv.cpp:43-73,391-431).
+ * Channels-last blobs: x [batch,h,w,c], filter [k,r,s,c], y [batch,ho,wo,k];
+ * ho = 1 + (h - (r-1)*dil_h - 1 + 2*pad_h) / stride_h (same for wo) must equal the values passed. */
+typedef struct nb200_conv_desc {
+	int batch, h, w, c;          /* source */
+	int k, r, s;                 /* filter count, height, width */
+	int pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
+	int ho, wo;                  /* result */
+} nb200_conv_desc;
+NB200_API int nb200_blob_convolution(void* stream, const nb200_conv_desc* desc, const float* x,
+	const float* filter, float* y, const nb200_epilogue* epi, int precision);
+
+/* ---- depthwise / fused blocks ----------------------------------------------------------------------------- */
+/* IDnnEngine::BlobChannelwiseConvolution (NME.h:766-771): x [batch,h,w,c], filter [r,s,c], y [batch,ho,wo,c]. */
+typedef struct nb200_chconv_desc {
+	int batch, h, w, c, r, s, pad_h, pad_w, stride_h, stride_w, ho, wo;
+} nb200_chconv_desc;
+NB200_API int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* desc, const float* x,
+	const float* filter, const float* free_term, float* y, int act, float act_param);
+
+/* IDnnEngine::InitRowwiseMobileNetV2 + MobileNetV2Block (NME.h:1095-1101,1069-1071;
+ * CPU CpuRowwiseMobileNetV2.h:151-295):
+ * y = [x +] W_down * act2( dw3x3( act1( W_exp * x + b_exp ) ) + b_dw ) + b_down.
+ * x [batch,h,w,c_in]; w_exp [c_exp,c_in]; w_dw [3,3,c_exp]; w_down [c_out,c_exp]; y [batch,ho,wo,c_out].
+ * `scratch` must hold nb200_mobilenetv2_scratch_floats(desc) floats (the engine takes it from StackAlloc). */
+typedef struct nb200_mbv2_desc {
+	int batch, h, w, c_in, c_exp, c_out, stride;
+	int residual;               /* 1: add x (needs c_in == c_out, stride == 1); y may alias x */
+	int act_exp, act_dw;        /* NB200_ACT_* */
+	float act_exp_param, act_dw_param;
+} nb200_mbv2_desc;
+NB200_API size_t nb200_mobilenetv2_scratch_floats(const nb200_mbv2_desc* desc);
+NB200_API int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* desc, const float* x,
+	const float* w_exp, const float* b_exp, const float* w_dw, const float* b_dw,
+	const float* w_down, const float* b_down, float* y, float* scratch, int precision);
+
+/* ---- memory-bound vector / matrix ops ---------------------------------------------------------------------- */
+/* Elementwise family (IVectorMathEngine, NME.h:69-384).  `op` selects the method; operands unused by an op
+ * are NULL.  Scalars that NeoML keeps on the device arrive as device pointers (`scalar`), true scalars in `value`. */
+enum {
+	NB200_VEC_COPY = 0,          /* VectorCopy           y = a                         NME.h:73  */
+	NB200_VEC_FILL = 1,          /* VectorFill(value)    y = value                     NME.h:86  */
+	NB200_VEC_FILL_HANDLE = 2,   /* VectorFill(handle)   y = *scalar                   NME.h:90  */
+	NB200_VEC_ADD = 3,           /* VectorAdd            y = a + b                     NME.h:236 */
+	NB200_VEC_SUB = 4,           /* VectorSub            y = a - b                     NME.h:249 */
+	NB200_VEC_ELTWISE_MUL = 5,   /* VectorEltwiseMultiply y = a * b                    NME.h:279 */
+	NB200_VEC_MULTIPLY = 6,      /* VectorMultiply       y = a * *scalar               NME.h:268 */
+	NB200_VEC_NEG_MULTIPLY = 7,  /* VectorNegMultiply    y = -a * *scalar              NME.h:273 */
+	NB200_VEC_ADD_VALUE = 8,     /* VectorAddValue       y = a + *scalar               NME.h:240 */
+	NB200_VEC_RELU = 9,          /* VectorReLU           thr=*scalar; thr>0 ? min(max(a,0),thr) : max(a,0)  NME.h:144 */
+	NB200_VEC_SIGMOID = 10,      /* VectorSigmoid        y = 1/(1+exp(-a))             NME.h:311 */
+	NB200_VEC_SQRT = 11,         /* VectorSqrt                                         NME.h:299 */
+	NB200_VEC_INV = 12,          /* VectorInv            y = 1/a                       NME.h:302 */
+	NB200_VEC_TANH = 13,         /* VectorTanh                                         NME.h:319 */
+	NB200_VEC_EXP = 14,          /* VectorExp                                          NME.h:215 */
+	NB200_VEC_HSWISH = 15,       /* VectorHSwish                                       NME.h:162 */
+	NB200_VEC_ELTWISE_MAX = 16,  /* VectorEltwiseMax                                   NME.h:169 */
+	NB200_VEC_ELTWISE_DIV = 17,  /* VectorEltwiseDivide  y = a / b                     NME.h:291 */
+	NB200_VEC_MUL_ADD = 18,      /* VectorMultiplyAndAdd y = a + b * *scalar           NME.h:259 */
+	NB200_VEC_OP_COUNT
+};
+NB200_API int nb200_vector_op(void* stream, int op, const float* a, const float* b, const float* scalar,
+	float value, float* y, int count);
+/* Int32 VectorCopy / VectorFill (NME.h:74,87). */
+NB200_API int nb200_vector_copy_int(void* stream, const int* a, int* y, int count);
+NB200_API int nb200_vector_fill_int(void* stream, int value, int* y, int count);
+
+/* AddVectorToMatrixRows (NME.h:419-420): y[b][h][w] = x[b][h][w] + v[b][w]. */
+NB200_API int nb200_add_vector_to_matrix_rows(void* stream, int batch, const float* x, float* y, int height,
+	int width, const float* v);
+/* AddVectorToMatrixColumns (NME.h:423-424): y[h][w] = x[h][w] + v[h]. */
+NB200_API int nb200_add_vector_to_matrix_columns(void* stream, const float* x, float* y, int height, int width,
+	const float* v);
+/* SumMatrixRows / SumMatrixRowsAdd (NME.h:433-436): y[b][w] (+)= sum_h x[b][h][w]. */
+NB200_API int nb200_sum_matrix_rows(void* stream, int batch, float* y, const float* x, int height, int width,
+	int add);
+/* SumMatrixColumns (NME.h:439-440): y[h] = sum_w x[h][w]. */
+NB200_API int nb200_sum_matrix_columns(void* stream, float* y, const float* x, int height, int width);
+/* MultiplyDiagMatrixByMatrix (NME.h:570-572): y[i][j] = d[i] * x[i][j]. */
+NB200_API int nb200_multiply_diag_matrix_by_matrix(void* stream, const float* d, int height, const float* x,
+	int width, float* y);
+/* BatchMultiplyMatrixByDiagMatrix / MultiplyMatrixByDiagMatrix (NME.h:588-596): y[b][i][j] = x[b][i][j] * d[b?][j];
+ * diag_stride is `width` when each batch has its own diagonal, 0 when one diagonal serves all. */
+NB200_API int nb200_multiply_matrix_by_diag_matrix(void* stream, int batch, const float* x, int height, int width,
+	const float* d, int diag_stride, float* y);
+/* MatrixSoftmaxByRows (NME.h:450): row-wise softmax, may run in place. */
+NB200_API int nb200_matrix_softmax_by_rows(void* stream, const float* x, int height, int width, float* y);
+/* TransposeMatrix (NME.h:599-603): x [batch][height][medium][width][channels] -> y [batch][width][medium][height][channels]. */
+NB200_API int nb200_transpose_matrix(void* stream, int batch, const void* x, int height, int medium, int width,
+	int channels, void* y);
+/* FindMaxValueInRows (NME.h:466-469): per row max and (optional) first arg-max column index. */
+NB200_API int nb200_find_max_value_in_rows(void* stream, const float* x, int height, int width, float* max_values,
+	int* max_indices);
+/* FindMaxValueInColumns (NME.h:472-474): per batch and column, max over rows and its first row index. */
+NB200_API int nb200_find_max_value_in_columns(void* stream, int batch, const float* x, int height, int width,
+	float* max_values, int* row_indices);
+/* InitMaxPooling + BlobMaxPooling (NME.h:817-822): x [batch,h,w,c] -> y [batch,ho,wo,c], no padding;
+ * max_indices (optional) receives the flat in-image index of each maximum. */
+NB200_API int nb200_blob_max_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w,
+	int stride_h, int stride_w, const float* x, float* y, int* max_indices);
+/* InitMeanPooling + BlobMeanPooling (NME.h:837-841). */
+NB200_API int nb200_blob_mean_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w,
+	int stride_h, int stride_w, const float* x, float* y);
+/* BlobResizeImage (NME.h:705-710): positive deltas pad, negative crop; padding 0 = constant(default_value),
+ * 1 = edge, 2 = reflect (TBlobResizePadding, NME.h:61-66).  x [batch,h,w,c] -> y [batch,h+dt+db,w+dl+dr,c]. */
+NB200_API int nb200_blob_resize_image(void* stream, int batch, int h, int w, int c, int delta_left, int delta_right,
+	int delta_top, int delta_bottom, int padding, float default_value, const float* x, float* y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEOML_B200_H */

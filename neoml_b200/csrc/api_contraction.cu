@@ -1,0 +1,145 @@
+// C-ABI entry points for the dense contractions: argument checks, then one description for the shared kernels.
+#include "contraction.cuh"
+
+using namespace nb200;
+
+namespace {
+
+void fill_epilogue(ContractionParams& p, const nb200_epilogue* epi)
+{
+	p.bias = nullptr;
+	p.residual = nullptr;
+	p.ldr = 0;
+	p.act = NB200_ACT_NONE;
+	p.act_param = 0.f;
+	p.accumulate = 0;
+	if(epi != nullptr) {
+		p.bias = epi->bias;
+		p.residual = epi->residual;
+		p.ldr = epi->ld_residual;
+		p.act = epi->act;
+		p.act_param = epi->act_param;
+		p.accumulate = epi->accumulate;
+	}
+}
+
+bool vec_ok(const void* base, long long ld, long long batchStride)
+{
+	return aligned16(base) && (ld % 4) == 0 && (batchStride % 4) == 0;
+}
+
+int run(ContractionParams& p, int batch, void* stream, int precision)
+{
+	if(precision != NB200_PREC_3XTF32 && precision != NB200_PREC_TF32 && precision != NB200_PREC_FP32_SIMT) {
+		return NB200_EINVAL;
+	}
+	if(p.M == 0 || p.N == 0 || batch == 0) return NB200_OK;
+	if(p.A == nullptr || p.B == nullptr || p.C == nullptr) return NB200_EINVAL;
+	p.precision = precision;
+	p.stages = 0;
+	p.status = device_status_word();
+	if(p.status == nullptr) return NB200_ENODEVICE;
+	p.c_vec = vec_ok(p.C, p.ldc, p.strideC) && (p.bias == nullptr || aligned16(p.bias))
+		&& (p.residual == nullptr || vec_ok(p.residual, p.ldr, p.strideC)) ? 1 : 0;
+	if(precision == NB200_PREC_FP32_SIMT) return launch_contraction_simt(p, batch, as_stream(stream));
+	return launch_contraction_tc(p, batch, as_stream(stream));
+}
+
+} // namespace
+
+extern "C" {
+
+int nb200_multiply_matrix_by_transposed_matrix(void* stream, const float* a, int m, int k, int lda,
+	const float* b, int n, int ldb, float* c, int ldc, const nb200_epilogue* epi, int precision)
+{
+	if(m < 0 || n < 0 || k <= 0 || lda < k || ldb < k || ldc < n) return NB200_EINVAL;
+	ContractionParams p = {};
+	p.A = a; p.B = b; p.C = c;
+	p.M = m; p.N = n; p.K = k;
+	p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+	p.a_mode = A_ROWS; p.b_mode = B_ROWS;
+	fill_epilogue(p, epi);
+	if(p.residual == nullptr) p.ldr = ldc;
+	p.a_vec = vec_ok(a, lda, 0); p.b_vec = vec_ok(b, ldb, 0);
+	return run(p, 1, stream, precision);
+}
+
+int nb200_batch_multiply_matrix_by_transposed_matrix(void* stream, int batch, const float* a, int m,
+	int k, const float* b, int n, float* c, const nb200_epilogue* epi, int precision)
+{
+	if(batch < 0 || m < 0 || n < 0 || k <= 0) return NB200_EINVAL;
+	ContractionParams p = {};
+	p.A = a; p.B = b; p.C = c;
+	p.M = m; p.N = n; p.K = k;
+	p.lda = k; p.ldb = k; p.ldc = n;
+	p.strideA = static_cast<long long>(m) * k; p.strideB = static_cast<long long>(n) * k;
+	p.strideC = static_cast<long long>(m) * n;
+	p.a_mode = A_ROWS; p.b_mode = B_ROWS;
+	fill_epilogue(p, epi);
+	if(p.residual == nullptr) p.ldr = n;
+	p.a_vec = vec_ok(a, k, p.strideA); p.b_vec = vec_ok(b, k, p.strideB);
+	return run(p, batch, stream, precision);
+}
+
+int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int m, int k,
+	const float* b, int n, float* c, const nb200_epilogue* epi, int precision)
+{
+	if(batch < 0 || m < 0 || n < 0 || k <= 0) return NB200_EINVAL;
+	ContractionParams p = {};
+	p.A = a; p.B = b; p.C = c;
+	p.M = m; p.N = n; p.K = k;
+	p.lda = k; p.ldb = n; p.ldc = n;
+	p.strideA = static_cast<long long>(m) * k; p.strideB = static_cast<long long>(k) * n;
+	p.strideC = static_cast<long long>(m) * n;
+	p.a_mode = A_ROWS; p.b_mode = B_COLS;
+	fill_epilogue(p, epi);
+	if(p.residual == nullptr) p.ldr = n;
+	p.a_vec = vec_ok(a, k, p.strideA); p.b_vec = 0;
+	return run(p, batch, stream, precision);
+}
+
+int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
+	const nb200_epilogue* epi, int precision)
+{
+	if(d == nullptr) return NB200_EINVAL;
+	if(d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0
+		|| d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
+		return NB200_EINVAL;
+	}
+	// output size rule of the reference (CpuMathEngineDnnConv.cpp:59-62)
+	const int ho = 1 + (d->h - (d->r - 1) * d->dil_h - 1 + 2 * d->pad_h) / d->stride_h;
+	const int wo = 1 + (d->w - (d->s - 1) * d->dil_w - 1 + 2 * d->pad_w) / d->stride_w;
+	if(ho != d->ho || wo != d->wo || ho <= 0 || wo <= 0) return NB200_EINVAL;
+	const long long inElems = static_cast<long long>(d->batch) * d->h * d->w * d->c;
+	const long long outRows = static_cast<long long>(d->batch) * ho * wo;
+	const long long kk = static_cast<long long>(d->r) * d->s * d->c;
+	if(inElems > 0x7fffffffLL || outRows * d->k > 0x7fffffffLL || kk > 0x7fffffffLL) return NB200_ETOOBIG;
+
+	ContractionParams p = {};
+	p.A = x; p.B = filter; p.C = y;
+	p.M = static_cast<int>(outRows); p.N = d->k; p.K = static_cast<int>(kk);
+	p.lda = 0; p.ldb = p.K; p.ldc = d->k;
+	p.H = d->h; p.W = d->w; p.Cin = d->c; p.Ho = ho; p.Wo = wo; p.S = d->s;
+	p.padH = d->pad_h; p.padW = d->pad_w; p.strH = d->stride_h; p.strW = d->stride_w;
+	p.dilH = d->dil_h; p.dilW = d->dil_w;
+	p.b_mode = B_ROWS;
+	fill_epilogue(p, epi);
+	if(p.residual == nullptr) p.ldr = d->k;
+	p.b_vec = vec_ok(filter, p.K, 0);
+	const bool pointwise = d->r == 1 && d->s == 1 && d->pad_h == 0 && d->pad_w == 0 && d->stride_h == 1 && d->stride_w == 1;
+	if(pointwise) {
+		// a 1x1/stride-1 convolution is the plain product  y[M x K] = x[M x C] * filter[K x C]^T
+		p.a_mode = A_ROWS;
+		p.lda = d->c;
+		p.a_vec = vec_ok(x, d->c, 0);
+	} else if(d->c % 32 == 0 && aligned16(x)) {
+		p.a_mode = A_CONV_TAP;
+		p.a_vec = 1;
+	} else {
+		p.a_mode = A_CONV_ANY;
+		p.a_vec = 0;
+	}
+	return run(p, 1, stream, precision);
+}
+
+} // extern "C"

@@ -1,0 +1,216 @@
+// Shared device/host helpers for the sm_100a kernel library: launch bookkeeping, the per-device status
+// word used by bounded waits, and thin wrappers over the PTX this library issues by hand
+// (mbarrier, tcgen05 alloc/mma/commit/ld, proxy fences).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/neoml_b200.h"
+
+namespace nb200 {
+
+// ---- host side ---------------------------------------------------------------------------------------------
+// Status word (device memory, one per device) that kernels write when a bounded wait gives up.
+int* device_status_word();              // nullptr when no device is usable
+void count_launch(int n = 1);
+int check_launch();                     // maps cudaGetLastError() to NB200_* codes
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Grid size for grid-stride kernels: a whole number of waves over the SMs of the current device.
+int sm_count();
+inline int grid_for(long long work_items, int per_block, int waves_cap = 8)
+{
+	long long blocks = (work_items + per_block - 1) / per_block;
+	long long cap = static_cast<long long>(sm_count()) * waves_cap;
+	if(blocks > cap) blocks = cap;
+	if(blocks < 1) blocks = 1;
+	return static_cast<int>(blocks);
+}
+
+// ---- device side -------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+	return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ bool elect_one()
+{
+	uint32_t pred = 0;
+	asm volatile(
+		"{\n\t.reg .pred P;\n\t"
+		"elect.sync _|P, 0xffffffff;\n\t"
+		"selp.b32 %0, 1, 0, P;\n\t}"
+		: "=r"(pred));
+	return pred != 0;
+}
+
+// -- mbarrier -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence()
+{
+	asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+	uint32_t done;
+	asm volatile(
+		"{\n\t.reg .pred P;\n\t"
+		"mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+		"selp.b32 %0, 1, 0, P;\n\t}"
+		: "=r"(done)
+		: "r"(smem_u32(bar)), "r"(parity)
+		: "memory");
+	return done != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+	uint64_t t;
+	asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+	return t;
+}
+
+// Bounded wait: polls until the phase with the given parity completes, the CTA-wide abort flag is raised, or two
+// seconds of wall time have passed.  On timeout it raises the abort flag, records `site` in the global status word
+// and returns false; the caller must then leave its role loop and go to the common teardown.
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+	int* status, int site)
+{
+	if(mbar_try_wait(bar, parity)) return true;
+	const uint64_t t0 = global_timer_ns();
+	for(uint32_t it = 1;; ++it) {
+		if(mbar_try_wait(bar, parity)) return true;
+		if((it & 63u) == 0u) {
+			if(*abort_flag != 0) return false;
+			if(global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+		}
+	}
+	*abort_flag = 1;
+	if(status != nullptr) atomicCAS(status, 0, site);
+	return false;
+}
+
+// -- proxy / tcgen05 fences --------------------------------------------------------------------------------------
+// Makes this thread's generic-proxy shared-memory writes visible to the async proxy (tcgen05.mma operand reads).
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+	asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync()
+{
+	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync()
+{
+	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// -- tensor memory ---------------------------------------------------------------------------------------------
+// Whole-warp calls (.sync.aligned).  `columns` is a power of two >= 32.
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t columns)
+{
+	asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+		::"r"(smem_u32(dst_smem)), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns)
+{
+	asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+
+// 32 lanes x 32 bit, 16 consecutive columns: thread i of warp w reads TMEM lane 32*(w%4)+i.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v)
+{
+	uint32_t r[16];
+	asm volatile(
+		"tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+		  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+		: "r"(taddr));
+	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+	for(int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// -- UMMA descriptors --------------------------------------------------------------------------------------------
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes (32 fp32) with the
+// 128-byte swizzle: 16-byte chunk c of row r lives at r*128 + ((c ^ (r & 7)) << 4); 8-row groups are 1024 B apart.
+// Field layout (PTX ISA, tcgen05 matrix descriptor): [0,14) start>>4, [16,30) leading byte offset>>4 (unused for
+// swizzled K-major, set to 1), [32,46) stride byte offset>>4 (1024 B between 8-row groups), [46,48) version = 1,
+// [61,64) layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr)
+{
+	uint64_t d = 0;
+	d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+	d |= static_cast<uint64_t>(1) << 16;
+	d |= static_cast<uint64_t>(1024 >> 4) << 32;
+	d |= static_cast<uint64_t>(1) << 46;
+	d |= static_cast<uint64_t>(2) << 61;
+	return d;
+}
+
+// Instruction descriptor for kind::tf32, fp32 accumulate, both operands K-major, tile M x N.
+// [4,6) D format 1 = F32; [7,10) A format 2 = TF32; [10,13) B format 2 = TF32; [15] A major 0; [16] B major 0;
+// [17,23) N>>3; [24,29) M>>4.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n)
+{
+	return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+		(static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; one thread issues for the CTA.
+__device__ __forceinline__ void umma_tf32_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+	uint32_t accumulate)
+{
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+		::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+		::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ float to_tf32(float x)
+{
+	uint32_t r;
+	asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+	return __uint_as_float(r);
+}
+
+__device__ __forceinline__ float apply_act(float v, int act, float param)
+{
+	if(act == NB200_ACT_RELU) {
+		v = fmaxf(v, 0.f);
+		if(param > 0.f) v = fminf(v, param);
+	} else if(act == NB200_ACT_HSWISH) {
+		v = v * fminf(fmaxf(v + 3.f, 0.f), 6.f) * (1.f / 6.f);
+	}
+	return v;
+}
+
+#endif // __CUDACC__
+
+} // namespace nb200

@@ -1,0 +1,95 @@
+// Parameter block shared by the tensor-core (tcgen05) and the CUDA-core contraction kernels.
+// One description covers MultiplyMatrixByTransposedMatrix, MultiplyMatrixByMatrix, their batched forms and
+// BlobConvolution viewed as an implicit GEMM:  C[M x N] = gatherA[M x K] * gatherB[N x K]^T  (+ epilogue).
+#pragma once
+#include "common.cuh"
+
+namespace nb200 {
+
+enum { A_ROWS = 0, A_CONV_TAP = 1, A_CONV_ANY = 2 };
+enum { B_ROWS = 0, B_COLS = 1 };
+
+struct ContractionParams {
+	const float* A;
+	const float* B;
+	float* C;
+	const float* bias;
+	const float* residual;
+	int M, N, K;
+	int lda, ldb, ldc, ldr;
+	long long strideA, strideB, strideC; // per batch entry (gridDim.y)
+	int a_mode; // A_ROWS: element (m,k) at A[m*lda + k]
+	            // A_CONV_TAP: channels-last image gather, C % 32 == 0 (a 32-wide K block lies inside one filter tap)
+	            // A_CONV_ANY: channels-last image gather, any C (per-element tap arithmetic)
+	int b_mode; // B_ROWS: element (n,k) at B[n*ldb + k];  B_COLS: element (n,k) at B[k*ldb + n]
+	int a_vec;  // 16-byte loads are legal for A (base and all row starts 16-byte aligned)
+	int b_vec;
+	int c_vec;  // 16-byte stores legal for C (and loads for residual)
+	// convolution geometry (a_mode != A_ROWS)
+	int H, W, Cin, Ho, Wo, S, padH, padW, strH, strW, dilH, dilW;
+	// epilogue
+	int act;
+	float act_param;
+	int accumulate;
+	int precision;
+	int stages;
+	int* status;
+};
+
+// Decodes output row m of a convolution into the image base offset and the top-left input coordinate.
+struct ConvRow {
+	int base; // n * H * W * Cin, or -1 when the row is out of range
+	int iy0, ix0;
+};
+
+__device__ __forceinline__ ConvRow conv_row(const ContractionParams& p, int m)
+{
+	ConvRow r;
+	if(m >= p.M) {
+		r.base = -1;
+		r.iy0 = r.ix0 = 0;
+		return r;
+	}
+	const int hw = p.Ho * p.Wo;
+	const int n = m / hw;
+	const int rem = m - n * hw;
+	const int oy = rem / p.Wo;
+	const int ox = rem - oy * p.Wo;
+	r.base = n * p.H * p.W * p.Cin;
+	r.iy0 = oy * p.strH - p.padH;
+	r.ix0 = ox * p.strW - p.padW;
+	return r;
+}
+
+// One element of the gathered A operand (generic, slow path; also used by the CUDA-core kernel).
+__device__ __forceinline__ float gather_a(const ContractionParams& p, const float* A, const ConvRow& row, int m, int k)
+{
+	if(k >= p.K) return 0.f;
+	if(p.a_mode == A_ROWS) {
+		return m < p.M ? __ldg(A + static_cast<size_t>(m) * p.lda + k) : 0.f;
+	}
+	if(row.base < 0) return 0.f;
+	const int sc = p.S * p.Cin;
+	const int r = k / sc;
+	const int j = k - r * sc;
+	const int s = j / p.Cin;
+	const int c = j - s * p.Cin;
+	const int iy = row.iy0 + r * p.dilH;
+	const int ix = row.ix0 + s * p.dilW;
+	if(static_cast<unsigned>(iy) >= static_cast<unsigned>(p.H) || static_cast<unsigned>(ix) >= static_cast<unsigned>(p.W)) {
+		return 0.f;
+	}
+	return __ldg(A + row.base + (iy * p.W + ix) * p.Cin + c);
+}
+
+__device__ __forceinline__ float gather_b(const ContractionParams& p, const float* B, int n, int k)
+{
+	if(k >= p.K || n >= p.N) return 0.f;
+	return p.b_mode == B_ROWS ? __ldg(B + static_cast<size_t>(n) * p.ldb + k)
+		: __ldg(B + static_cast<size_t>(k) * p.ldb + n);
+}
+
+int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
+int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
+
+} // namespace nb200

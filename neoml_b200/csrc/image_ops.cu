@@ -1,0 +1,251 @@
+// Channels-last image ops that are pure data movement or small stencils: 2-D max/mean pooling, image
+// resize (pad/crop) and depthwise (channelwise) convolution.  One thread handles 4 consecutive channels of one
+// output pixel when channels % 4 == 0 and the buffers are 16-byte aligned, so every access is a coalesced 16-byte
+// load/store along the channel dimension; the stencil re-reads hit L1/L2.
+#include "common.cuh"
+#include <float.h>
+
+namespace nb200 {
+
+namespace {
+
+struct Pool2d {
+	int batch, h, w, c, fh, fw, sh, sw, ho, wo;
+};
+
+template<bool MAX, int V>
+__global__ void __launch_bounds__(256) pool_kernel(const Pool2d p, const float* __restrict__ x, float* __restrict__ y,
+	int* __restrict__ maxIndices, long long total)
+{
+	const int cv = p.c / V;
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
+		long long r = t;
+		const int c = static_cast<int>(r % cv) * V; r /= cv;
+		const int ox = static_cast<int>(r % p.wo); r /= p.wo;
+		const int oy = static_cast<int>(r % p.ho); r /= p.ho;
+		const long long n = r;
+		const float* img = x + n * p.h * p.w * p.c;
+		float acc[V];
+		int idx[V];
+#pragma unroll
+		for(int e = 0; e < V; ++e) { acc[e] = MAX ? -FLT_MAX : 0.f; idx[e] = 0; }
+		for(int fy = 0; fy < p.fh; ++fy) {
+			const int iy = oy * p.sh + fy;
+			for(int fx = 0; fx < p.fw; ++fx) {
+				const int ix = ox * p.sw + fx;
+				const int pix = iy * p.w + ix;
+				const float* src = img + static_cast<size_t>(pix) * p.c + c;
+				float v[V];
+				if(V == 4) {
+					const float4 q = __ldg(reinterpret_cast<const float4*>(src));
+					v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+				} else {
+					v[0] = __ldg(src);
+				}
+#pragma unroll
+				for(int e = 0; e < V; ++e) {
+					if(MAX) {
+						if(v[e] > acc[e] || (fy == 0 && fx == 0)) { acc[e] = v[e]; idx[e] = pix * p.c + c + e; }
+					} else {
+						acc[e] += v[e];
+					}
+				}
+			}
+		}
+		const size_t o = ((static_cast<size_t>(n) * p.ho + oy) * p.wo + ox) * p.c + c;
+		if(!MAX) {
+			const float inv = 1.f / static_cast<float>(p.fh * p.fw);
+#pragma unroll
+			for(int e = 0; e < V; ++e) acc[e] *= inv;
+		}
+		if(V == 4) {
+			*reinterpret_cast<float4*>(y + o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+		} else {
+			y[o] = acc[0];
+		}
+		if(MAX && maxIndices != nullptr) {
+#pragma unroll
+			for(int e = 0; e < V; ++e) maxIndices[o + e] = idx[e];
+		}
+	}
+}
+
+struct Resize {
+	int batch, h, w, c, dl, dt, ho, wo, padding;
+	float value;
+};
+
+template<int V>
+__global__ void __launch_bounds__(256) resize_kernel(const Resize p, const float* __restrict__ x, float* __restrict__ y,
+	long long total)
+{
+	const int cv = p.c / V;
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
+		long long r = t;
+		const int c = static_cast<int>(r % cv) * V; r /= cv;
+		const int ox = static_cast<int>(r % p.wo); r /= p.wo;
+		const int oy = static_cast<int>(r % p.ho); r /= p.ho;
+		const long long n = r;
+		int iy = oy - p.dt, ix = ox - p.dl;
+		bool inside = iy >= 0 && iy < p.h && ix >= 0 && ix < p.w;
+		if(!inside && p.padding != 0) {
+			if(p.padding == 1) { // edge
+				iy = min(max(iy, 0), p.h - 1);
+				ix = min(max(ix, 0), p.w - 1);
+			} else { // reflect
+				if(iy < 0) iy = -iy; else if(iy >= p.h) iy = 2 * (p.h - 1) - iy;
+				if(ix < 0) ix = -ix; else if(ix >= p.w) ix = 2 * (p.w - 1) - ix;
+				iy = min(max(iy, 0), p.h - 1);
+				ix = min(max(ix, 0), p.w - 1);
+			}
+			inside = true;
+		}
+		float* dst = y + t * V;
+		if(V == 4) {
+			float4 v = make_float4(p.value, p.value, p.value, p.value);
+			if(inside) v = __ldg(reinterpret_cast<const float4*>(x + ((n * p.h + iy) * p.w + ix) * p.c + c));
+			*reinterpret_cast<float4*>(dst) = v;
+		} else {
+			*dst = inside ? __ldg(x + ((n * p.h + iy) * p.w + ix) * p.c + c) : p.value;
+		}
+	}
+}
+
+template<int V>
+__global__ void __launch_bounds__(256) chconv_kernel(const nb200_chconv_desc p, const float* __restrict__ x,
+	const float* __restrict__ filter, const float* __restrict__ freeTerm, float* __restrict__ y, int act,
+	float actParam, long long total)
+{
+	const int cv = p.c / V;
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride) {
+		long long r = t;
+		const int c = static_cast<int>(r % cv) * V; r /= cv;
+		const int ox = static_cast<int>(r % p.wo); r /= p.wo;
+		const int oy = static_cast<int>(r % p.ho); r /= p.ho;
+		const long long n = r;
+		const float* img = x + n * p.h * p.w * p.c;
+		float acc[V];
+#pragma unroll
+		for(int e = 0; e < V; ++e) acc[e] = freeTerm != nullptr ? __ldg(freeTerm + c + e) : 0.f;
+		for(int fy = 0; fy < p.r; ++fy) {
+			const int iy = oy * p.stride_h - p.pad_h + fy;
+			if(static_cast<unsigned>(iy) >= static_cast<unsigned>(p.h)) continue;
+			for(int fx = 0; fx < p.s; ++fx) {
+				const int ix = ox * p.stride_w - p.pad_w + fx;
+				if(static_cast<unsigned>(ix) >= static_cast<unsigned>(p.w)) continue;
+				const float* src = img + (static_cast<size_t>(iy) * p.w + ix) * p.c + c;
+				const float* wgt = filter + (fy * p.s + fx) * p.c + c;
+				if(V == 4) {
+					const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+					const float4 f = __ldg(reinterpret_cast<const float4*>(wgt));
+					acc[0] = fmaf(a.x, f.x, acc[0]); acc[1] = fmaf(a.y, f.y, acc[1]);
+					acc[2] = fmaf(a.z, f.z, acc[2]); acc[3] = fmaf(a.w, f.w, acc[3]);
+				} else {
+					acc[0] = fmaf(__ldg(src), __ldg(wgt), acc[0]);
+				}
+			}
+		}
+#pragma unroll
+		for(int e = 0; e < V; ++e) acc[e] = apply_act(acc[e], act, actParam);
+		float* dst = y + t * V;
+		if(V == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+		else *dst = acc[0];
+	}
+}
+
+int pool_common(void* stream, bool isMax, int batch, int h, int w, int c, int fh, int fw, int sh, int sw,
+	const float* x, float* y, int* maxIndices)
+{
+	if(batch < 0 || h <= 0 || w <= 0 || c <= 0 || fh <= 0 || fw <= 0 || sh <= 0 || sw <= 0 || fh > h || fw > w) {
+		return NB200_EINVAL;
+	}
+	Pool2d p = { batch, h, w, c, fh, fw, sh, sw, (h - fh) / sh + 1, (w - fw) / sw + 1 };
+	const long long outElems = static_cast<long long>(batch) * p.ho * p.wo * c;
+	if(outElems == 0) return NB200_OK;
+	if(x == nullptr || y == nullptr) return NB200_EINVAL;
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	const bool vec = c % 4 == 0 && aligned16(x) && aligned16(y);
+	cudaStream_t s = as_stream(stream);
+	if(vec) {
+		const long long total = outElems / 4;
+		if(isMax) pool_kernel<true, 4><<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, maxIndices, total);
+		else pool_kernel<false, 4><<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, nullptr, total);
+	} else {
+		if(isMax) pool_kernel<true, 1><<<grid_for(outElems, 256, 16), 256, 0, s>>>(p, x, y, maxIndices, outElems);
+		else pool_kernel<false, 1><<<grid_for(outElems, 256, 16), 256, 0, s>>>(p, x, y, nullptr, outElems);
+	}
+	count_launch();
+	return check_launch();
+}
+
+} // namespace
+} // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nb200_blob_max_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w, int stride_h,
+	int stride_w, const float* x, float* y, int* max_indices)
+{
+	return pool_common(stream, true, batch, h, w, c, filter_h, filter_w, stride_h, stride_w, x, y, max_indices);
+}
+
+int nb200_blob_mean_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w, int stride_h,
+	int stride_w, const float* x, float* y)
+{
+	return pool_common(stream, false, batch, h, w, c, filter_h, filter_w, stride_h, stride_w, x, y, nullptr);
+}
+
+int nb200_blob_resize_image(void* stream, int batch, int h, int w, int c, int delta_left, int delta_right,
+	int delta_top, int delta_bottom, int padding, float default_value, const float* x, float* y)
+{
+	if(batch < 0 || h <= 0 || w <= 0 || c <= 0 || padding < 0 || padding > 2) return NB200_EINVAL;
+	const int ho = h + delta_top + delta_bottom, wo = w + delta_left + delta_right;
+	if(ho <= 0 || wo <= 0) return NB200_EINVAL;
+	const long long outElems = static_cast<long long>(batch) * ho * wo * c;
+	if(outElems == 0) return NB200_OK;
+	if(x == nullptr || y == nullptr) return NB200_EINVAL;
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	Resize p = { batch, h, w, c, delta_left, delta_top, ho, wo, padding, default_value };
+	cudaStream_t s = as_stream(stream);
+	if(c % 4 == 0 && aligned16(x) && aligned16(y)) {
+		resize_kernel<4><<<grid_for(outElems / 4, 256, 16), 256, 0, s>>>(p, x, y, outElems / 4);
+	} else {
+		resize_kernel<1><<<grid_for(outElems, 256, 16), 256, 0, s>>>(p, x, y, outElems);
+	}
+	count_launch();
+	return check_launch();
+}
+
+int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* d, const float* x, const float* filter,
+	const float* free_term, float* y, int act, float act_param)
+{
+	if(d == nullptr) return NB200_EINVAL;
+	if(d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->r <= 0 || d->s <= 0 || d->stride_h <= 0
+		|| d->stride_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
+		return NB200_EINVAL;
+	}
+	const int ho = 1 + (d->h - d->r + 2 * d->pad_h) / d->stride_h;
+	const int wo = 1 + (d->w - d->s + 2 * d->pad_w) / d->stride_w;
+	if(ho != d->ho || wo != d->wo || ho <= 0 || wo <= 0) return NB200_EINVAL;
+	const long long outElems = static_cast<long long>(d->batch) * ho * wo * d->c;
+	if(outElems == 0) return NB200_OK;
+	if(x == nullptr || filter == nullptr || y == nullptr) return NB200_EINVAL;
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	cudaStream_t s = as_stream(stream);
+	const bool vec = d->c % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(filter)
+		&& (free_term == nullptr || aligned16(free_term));
+	if(vec) {
+		chconv_kernel<4><<<grid_for(outElems / 4, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, outElems / 4);
+	} else {
+		chconv_kernel<1><<<grid_for(outElems, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, outElems);
+	}
+	count_launch();
+	return check_launch();
+}
+
+} // extern "C"

@@ -1,0 +1,92 @@
+// MobileNetV2 inverted-residual block:  y = [x +] W_down * act2(dw3x3(act1(W_exp * x + b_exp)) + b_dw) + b_down.
+//
+// The block is run over groups of images small enough that the expanded (c_exp-channel) intermediates of one group
+// stay resident in the 126 MB L2: expand (tensor-core 1x1 + bias + activation in the epilogue) -> depthwise 3x3
+// (+ bias + activation) -> project (tensor-core 1x1 + bias + residual in the epilogue).  The scratch buffer is reused
+// by every group, so its lines are overwritten while still in L2 and the intermediates do not stream through HBM.
+#include "contraction.cuh"
+
+extern "C" int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* desc, const float* x,
+	const float* filter, const float* free_term, float* y, int act, float act_param);
+
+using namespace nb200;
+
+namespace {
+
+constexpr long long L2_GROUP_BYTES = 40ll << 20; // both intermediates of one group
+
+struct Mbv2Plan {
+	int ho, wo;
+	int groupImages;
+	long long expandFloatsPerImage, dwFloatsPerImage;
+};
+
+bool plan(const nb200_mbv2_desc* d, Mbv2Plan& pl)
+{
+	if(d == nullptr || d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c_in <= 0 || d->c_exp <= 0 || d->c_out <= 0) return false;
+	if(d->stride != 1 && d->stride != 2) return false;
+	if(d->residual && (d->c_in != d->c_out || d->stride != 1)) return false;
+	pl.ho = 1 + (d->h - 3 + 2) / d->stride;
+	pl.wo = 1 + (d->w - 3 + 2) / d->stride;
+	pl.expandFloatsPerImage = static_cast<long long>(d->h) * d->w * d->c_exp;
+	pl.dwFloatsPerImage = static_cast<long long>(pl.ho) * pl.wo * d->c_exp;
+	const long long perImageBytes = (pl.expandFloatsPerImage + pl.dwFloatsPerImage) * 4;
+	long long g = L2_GROUP_BYTES / perImageBytes;
+	if(g < 1) g = 1;
+	if(g > d->batch) g = d->batch > 0 ? d->batch : 1;
+	pl.groupImages = static_cast<int>(g);
+	return true;
+}
+
+} // namespace
+
+extern "C" {
+
+size_t nb200_mobilenetv2_scratch_floats(const nb200_mbv2_desc* d)
+{
+	Mbv2Plan pl;
+	if(!plan(d, pl)) return 0;
+	return static_cast<size_t>(pl.groupImages) * static_cast<size_t>(pl.expandFloatsPerImage + pl.dwFloatsPerImage);
+}
+
+int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* d, const float* x, const float* w_exp,
+	const float* b_exp, const float* w_dw, const float* b_dw, const float* w_down, const float* b_down, float* y,
+	float* scratch, int precision)
+{
+	Mbv2Plan pl;
+	if(!plan(d, pl)) return NB200_EINVAL;
+	if(d->batch == 0) return NB200_OK;
+	if(x == nullptr || w_exp == nullptr || w_dw == nullptr || w_down == nullptr || y == nullptr || scratch == nullptr) {
+		return NB200_EINVAL;
+	}
+	float* expanded = scratch;
+	float* dwOut = scratch + static_cast<size_t>(pl.groupImages) * pl.expandFloatsPerImage;
+	const long long inPerImage = static_cast<long long>(d->h) * d->w * d->c_in;
+	const long long outPerImage = static_cast<long long>(pl.ho) * pl.wo * d->c_out;
+
+	for(int n0 = 0; n0 < d->batch; n0 += pl.groupImages) {
+		const int imgs = d->batch - n0 < pl.groupImages ? d->batch - n0 : pl.groupImages;
+		const float* xg = x + n0 * inPerImage;
+		float* yg = y + n0 * outPerImage;
+
+		nb200_epilogue e1 = {};
+		e1.bias = b_exp; e1.act = d->act_exp; e1.act_param = d->act_exp_param;
+		int rc = nb200_multiply_matrix_by_transposed_matrix(stream, xg, imgs * d->h * d->w, d->c_in, d->c_in,
+			w_exp, d->c_exp, d->c_in, expanded, d->c_exp, &e1, precision);
+		if(rc != NB200_OK) return rc;
+
+		nb200_chconv_desc cd = { imgs, d->h, d->w, d->c_exp, 3, 3, 1, 1, d->stride, d->stride, pl.ho, pl.wo };
+		rc = nb200_blob_channelwise_convolution(stream, &cd, expanded, w_dw, b_dw, dwOut, d->act_dw, d->act_dw_param);
+		if(rc != NB200_OK) return rc;
+
+		nb200_epilogue e2 = {};
+		e2.bias = b_down;
+		if(d->residual) { e2.residual = xg; e2.ld_residual = d->c_in; }
+		rc = nb200_multiply_matrix_by_transposed_matrix(stream, dwOut, imgs * pl.ho * pl.wo, d->c_exp, d->c_exp,
+			w_down, d->c_out, d->c_exp, yg, d->c_out, &e2, precision);
+		if(rc != NB200_OK) return rc;
+	}
+	return NB200_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,343 @@
+"""Test-side access to the checkers under oracle/: the plain-C oracle (always) and, where it has been built, the
+reference's own CPU math engine behind oracle/_ref/libref_shim.so.  numpy in, numpy out."""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+ORACLE_DIR = ROOT / "oracle"
+
+_fp = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_ip = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+_i, _f, _vp = C.c_int, C.c_float, C.c_void_p
+
+
+def _opt(a):
+    """ctypes argument for an optional float array."""
+    return None if a is None else a.ctypes.data_as(_vp)
+
+
+def out_size(size, filt, pad, stride, dil=1):
+    return 1 + (size - (filt - 1) * dil - 1 + 2 * pad) // stride
+
+
+class Oracle:
+    """Plain-C restatement (oracle/neoml_oracle.c)."""
+
+    def __init__(self):
+        so = ORACLE_DIR / "liboracle.so"
+        src = ORACLE_DIR / "neoml_oracle.c"
+        if not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
+            subprocess.run(["make", "-C", str(ORACLE_DIR), "liboracle.so"], check=True, capture_output=True)
+        self.lib = C.CDLL(str(so))
+
+    def multiply_matrix_by_transposed_matrix(self, a, b, lda=None, ldb=None, m=None, k=None, n=None):
+        m = a.shape[0] if m is None else m
+        k = a.shape[1] if k is None else k
+        n = b.shape[0] if n is None else n
+        lda = a.shape[1] if lda is None else lda
+        ldb = b.shape[1] if ldb is None else ldb
+        c = np.zeros((m, n), np.float32)
+        self.lib.oracle_multiply_matrix_by_transposed_matrix(_opt(a), m, k, lda, _opt(b), n, ldb, _opt(c), n)
+        return c
+
+    def multiply_matrix_by_matrix(self, a, b):
+        batch, m, k = a.shape
+        n = b.shape[2]
+        c = np.zeros((batch, m, n), np.float32)
+        self.lib.oracle_multiply_matrix_by_matrix(batch, _opt(a), m, k, _opt(b), n, _opt(c))
+        return c
+
+    def blob_convolution(self, x, flt, free_term=None, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+        n, h, w, c = x.shape
+        k, r, s, _ = flt.shape
+        ho, wo = out_size(h, r, padding[0], stride[0], dilation[0]), out_size(w, s, padding[1], stride[1], dilation[1])
+        y = np.zeros((n, ho, wo, k), np.float32)
+        self.lib.oracle_blob_convolution(n, h, w, c, k, r, s, padding[0], padding[1], stride[0], stride[1],
+                                         dilation[0], dilation[1], _opt(x), _opt(flt), _opt(free_term), _opt(y))
+        return y
+
+    def blob_channelwise_convolution(self, x, flt, free_term=None, padding=(0, 0), stride=(1, 1)):
+        n, h, w, c = x.shape
+        r, s, _ = flt.shape
+        ho, wo = out_size(h, r, padding[0], stride[0]), out_size(w, s, padding[1], stride[1])
+        y = np.zeros((n, ho, wo, c), np.float32)
+        self.lib.oracle_blob_channelwise_convolution(n, h, w, c, r, s, padding[0], padding[1], stride[0], stride[1],
+                                                     _opt(x), _opt(flt), _opt(free_term), _opt(y))
+        return y
+
+    def mobilenetv2_block(self, x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, stride=1, residual=False,
+                          act_exp=1, act_exp_param=6.0, act_dw=1, act_dw_param=6.0):
+        n, h, w, c_in = x.shape
+        c_exp, c_out = w_exp.shape[0], w_down.shape[0]
+        ho, wo = out_size(h, 3, 1, stride), out_size(w, 3, 1, stride)
+        y = np.zeros((n, ho, wo, c_out), np.float32)
+        self.lib.oracle_mobilenetv2_block(n, h, w, c_in, c_exp, c_out, stride, int(residual), act_exp,
+                                          _f(act_exp_param), act_dw, _f(act_dw_param), _opt(x), _opt(w_exp),
+                                          _opt(b_exp), _opt(w_dw), _opt(b_dw), _opt(w_down), _opt(b_down), _opt(y))
+        return y
+
+    def vector_op(self, op, a=None, b=None, scalar=0.0, count=None):
+        ref = a if a is not None else b
+        n = count if count is not None else ref.size
+        y = np.zeros(n, np.float32)
+        self.lib.oracle_vector_op(op, _opt(a), _opt(b), _f(scalar), _opt(y), n)
+        return y
+
+    def add_vector_to_matrix_rows(self, batch, x, height, width, v):
+        y = np.zeros_like(x)
+        self.lib.oracle_add_vector_to_matrix_rows(batch, _opt(x), _opt(y), height, width, _opt(v))
+        return y
+
+    def add_vector_to_matrix_columns(self, x, height, width, v):
+        y = np.zeros_like(x)
+        self.lib.oracle_add_vector_to_matrix_columns(_opt(x), _opt(y), height, width, _opt(v))
+        return y
+
+    def sum_matrix_rows(self, batch, x, height, width, init=None):
+        y = np.zeros((batch, width), np.float32) if init is None else init.copy()
+        self.lib.oracle_sum_matrix_rows(batch, _opt(y), _opt(x), height, width, int(init is not None))
+        return y
+
+    def sum_matrix_columns(self, x, height, width):
+        y = np.zeros(height, np.float32)
+        self.lib.oracle_sum_matrix_columns(_opt(y), _opt(x), height, width)
+        return y
+
+    def multiply_diag_matrix_by_matrix(self, d, height, x, width):
+        y = np.zeros_like(x)
+        self.lib.oracle_multiply_diag_matrix_by_matrix(_opt(d), height, _opt(x), width, _opt(y))
+        return y
+
+    def multiply_matrix_by_diag_matrix(self, batch, x, height, width, d, diag_stride):
+        y = np.zeros_like(x)
+        self.lib.oracle_multiply_matrix_by_diag_matrix(batch, _opt(x), height, width, _opt(d), diag_stride, _opt(y))
+        return y
+
+    def matrix_softmax_by_rows(self, x, height, width):
+        y = np.zeros_like(x)
+        self.lib.oracle_matrix_softmax_by_rows(_opt(x), height, width, _opt(y))
+        return y
+
+    def transpose_matrix(self, batch, x, height, medium, width, channels):
+        y = np.zeros_like(x)
+        self.lib.oracle_transpose_matrix(batch, _opt(x), height, medium, width, channels, _opt(y))
+        return y
+
+    def find_max_value_in_rows(self, x, height, width):
+        v, i = np.zeros(height, np.float32), np.zeros(height, np.int32)
+        self.lib.oracle_find_max_value_in_rows(_opt(x), height, width, _opt(v), i.ctypes.data_as(_vp))
+        return v, i
+
+    def find_max_value_in_columns(self, batch, x, height, width):
+        v, i = np.zeros((batch, width), np.float32), np.zeros((batch, width), np.int32)
+        self.lib.oracle_find_max_value_in_columns(batch, _opt(x), height, width, _opt(v), i.ctypes.data_as(_vp))
+        return v, i
+
+    def blob_max_pooling(self, x, fsize, stride):
+        n, h, w, c = x.shape
+        ho, wo = (h - fsize[0]) // stride[0] + 1, (w - fsize[1]) // stride[1] + 1
+        y, idx = np.zeros((n, ho, wo, c), np.float32), np.zeros((n, ho, wo, c), np.int32)
+        self.lib.oracle_blob_max_pooling(n, h, w, c, fsize[0], fsize[1], stride[0], stride[1], _opt(x), _opt(y),
+                                         idx.ctypes.data_as(_vp))
+        return y, idx
+
+    def blob_mean_pooling(self, x, fsize, stride):
+        n, h, w, c = x.shape
+        ho, wo = (h - fsize[0]) // stride[0] + 1, (w - fsize[1]) // stride[1] + 1
+        y = np.zeros((n, ho, wo, c), np.float32)
+        self.lib.oracle_blob_mean_pooling(n, h, w, c, fsize[0], fsize[1], stride[0], stride[1], _opt(x), _opt(y))
+        return y
+
+    def blob_resize_image(self, x, dl, dr, dt, db, padding=0, default_value=0.0):
+        n, h, w, c = x.shape
+        y = np.zeros((n, h + dt + db, w + dl + dr, c), np.float32)
+        self.lib.oracle_blob_resize_image(n, h, w, c, dl, dr, dt, db, padding, _f(default_value), _opt(x), _opt(y))
+        return y
+
+
+class Reference:
+    """The reference's own CPU math engine (oracle/_ref, built by `make -C oracle ref`).  Same method names and
+    argument order as Oracle.  `available()` is False where the reference build does not exist."""
+
+    SO = ORACLE_DIR / "_ref" / "libref_shim.so"
+
+    @classmethod
+    def available(cls) -> bool:
+        return cls.SO.exists()
+
+    def __init__(self):
+        self.lib = C.CDLL(str(self.SO))
+        self.lib.ref_engine_create.restype = _vp
+        self.lib.ref_engine_destroy.argtypes = [_vp]
+        self.engine = _vp(self.lib.ref_engine_create())
+        assert self.engine.value, "reference CPU engine could not be created"
+        self.last_seconds = 0.0
+
+    def close(self):
+        if self.engine is not None and self.engine.value:
+            self.lib.ref_engine_destroy(self.engine)
+            self.engine = None
+
+    def _chk(self, rc):
+        assert rc == 0, f"reference engine call failed ({rc})"
+
+    def multiply_matrix_by_transposed_matrix(self, a, b, lda=None, ldb=None, m=None, k=None, n=None):
+        m = a.shape[0] if m is None else m
+        k = a.shape[1] if k is None else k
+        n = b.shape[0] if n is None else n
+        lda = a.shape[1] if lda is None else lda
+        ldb = b.shape[1] if ldb is None else ldb
+        c = np.zeros((m, n), np.float32)
+        sec = C.c_double(0)
+        self._chk(self.lib.ref_multiply_matrix_by_transposed_matrix(self.engine, _opt(a), m, k, lda, _opt(b), n, ldb,
+                                                                    _opt(c), n, C.byref(sec)))
+        self.last_seconds = sec.value
+        return c
+
+    def multiply_matrix_by_matrix(self, a, b):
+        batch, m, k = a.shape
+        n = b.shape[2]
+        c = np.zeros((batch, m, n), np.float32)
+        sec = C.c_double(0)
+        self._chk(self.lib.ref_multiply_matrix_by_matrix(self.engine, batch, _opt(a), m, k, _opt(b), n, _opt(c),
+                                                         C.byref(sec)))
+        self.last_seconds = sec.value
+        return c
+
+    def blob_convolution(self, x, flt, free_term=None, padding=(0, 0), stride=(1, 1), dilation=(1, 1), out=None):
+        n, h, w, c = x.shape
+        k, r, s, _ = flt.shape
+        ho, wo = out_size(h, r, padding[0], stride[0], dilation[0]), out_size(w, s, padding[1], stride[1], dilation[1])
+        y = np.zeros((n, ho, wo, k), np.float32) if out is None else out
+        sec = C.c_double(0)
+        self._chk(self.lib.ref_blob_convolution(self.engine, n, h, w, c, k, r, s, padding[0], padding[1], stride[0],
+                                                stride[1], dilation[0], dilation[1], _opt(x), _opt(flt),
+                                                _opt(free_term), _opt(y), C.byref(sec)))
+        self.last_seconds = sec.value
+        return y
+
+    def blob_channelwise_convolution(self, x, flt, free_term=None, padding=(0, 0), stride=(1, 1)):
+        n, h, w, c = x.shape
+        r, s, _ = flt.shape
+        ho, wo = out_size(h, r, padding[0], stride[0]), out_size(w, s, padding[1], stride[1])
+        y = np.zeros((n, ho, wo, c), np.float32)
+        sec = C.c_double(0)
+        self._chk(self.lib.ref_blob_channelwise_convolution(self.engine, n, h, w, c, r, s, padding[0], padding[1],
+                                                            stride[0], stride[1], _opt(x), _opt(flt), _opt(free_term),
+                                                            _opt(y), C.byref(sec)))
+        self.last_seconds = sec.value
+        return y
+
+    def mobilenetv2_block(self, x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, stride=1, residual=False,
+                          act_exp=1, act_exp_param=6.0, act_dw=1, act_dw_param=6.0):
+        n, h, w, c_in = x.shape
+        c_exp, c_out = w_exp.shape[0], w_down.shape[0]
+        ho, wo = out_size(h, 3, 1, stride), out_size(w, 3, 1, stride)
+        y = np.zeros((n, ho, wo, c_out), np.float32)
+        sec = C.c_double(0)
+        self._chk(self.lib.ref_mobilenetv2_block(self.engine, n, h, w, c_in, c_exp, c_out, stride, int(residual),
+                                                 act_exp, _f(act_exp_param), act_dw, _f(act_dw_param), _opt(x),
+                                                 _opt(w_exp), _opt(b_exp), _opt(w_dw), _opt(b_dw), _opt(w_down),
+                                                 _opt(b_down), _opt(y), C.byref(sec)))
+        self.last_seconds = sec.value
+        return y
+
+    def vector_op(self, op, a=None, b=None, scalar=0.0, count=None):
+        ref = a if a is not None else b
+        n = count if count is not None else ref.size
+        y = np.zeros(n, np.float32)
+        sc = np.array([scalar], np.float32)
+        self._chk(self.lib.ref_vector_op(self.engine, op, _opt(a), _opt(b), _opt(sc), _f(scalar), _opt(y), n))
+        return y
+
+    def add_vector_to_matrix_rows(self, batch, x, height, width, v):
+        y = np.zeros_like(x)
+        self._chk(self.lib.ref_add_vector_to_matrix_rows(self.engine, batch, _opt(x), _opt(y), height, width, _opt(v)))
+        return y
+
+    def add_vector_to_matrix_columns(self, x, height, width, v):
+        y = np.zeros_like(x)
+        self._chk(self.lib.ref_add_vector_to_matrix_columns(self.engine, _opt(x), _opt(y), height, width, _opt(v)))
+        return y
+
+    def sum_matrix_rows(self, batch, x, height, width, init=None):
+        y = np.zeros((batch, width), np.float32) if init is None else init.copy()
+        self._chk(self.lib.ref_sum_matrix_rows(self.engine, batch, _opt(y), _opt(x), height, width, int(init is not None)))
+        return y
+
+    def sum_matrix_columns(self, x, height, width):
+        y = np.zeros(height, np.float32)
+        self._chk(self.lib.ref_sum_matrix_columns(self.engine, _opt(y), _opt(x), height, width))
+        return y
+
+    def multiply_diag_matrix_by_matrix(self, d, height, x, width):
+        y = np.zeros_like(x)
+        self._chk(self.lib.ref_multiply_diag_matrix_by_matrix(self.engine, _opt(d), height, _opt(x), width, _opt(y)))
+        return y
+
+    def multiply_matrix_by_diag_matrix(self, batch, x, height, width, d, diag_stride):
+        y = np.zeros_like(x)
+        self._chk(self.lib.ref_multiply_matrix_by_diag_matrix(self.engine, batch, _opt(x), height, width, _opt(d),
+                                                              diag_stride, _opt(y)))
+        return y
+
+    def matrix_softmax_by_rows(self, x, height, width):
+        y = np.zeros_like(x)
+        self._chk(self.lib.ref_matrix_softmax_by_rows(self.engine, _opt(x), height, width, _opt(y)))
+        return y
+
+    def transpose_matrix(self, batch, x, height, medium, width, channels):
+        y = np.zeros_like(x)
+        self._chk(self.lib.ref_transpose_matrix(self.engine, batch, _opt(x), height, medium, width, channels, _opt(y)))
+        return y
+
+    def find_max_value_in_rows(self, x, height, width):
+        v, i = np.zeros(height, np.float32), np.zeros(height, np.int32)
+        self._chk(self.lib.ref_find_max_value_in_rows(self.engine, _opt(x), height, width, _opt(v), i.ctypes.data_as(_vp)))
+        return v, i
+
+    def find_max_value_in_columns(self, batch, x, height, width):
+        v, i = np.zeros((batch, width), np.float32), np.zeros((batch, width), np.int32)
+        self._chk(self.lib.ref_find_max_value_in_columns(self.engine, batch, _opt(x), height, width, _opt(v),
+                                                         i.ctypes.data_as(_vp)))
+        return v, i
+
+    def blob_max_pooling(self, x, fsize, stride):
+        n, h, w, c = x.shape
+        ho, wo = (h - fsize[0]) // stride[0] + 1, (w - fsize[1]) // stride[1] + 1
+        y, idx = np.zeros((n, ho, wo, c), np.float32), np.zeros((n, ho, wo, c), np.int32)
+        self._chk(self.lib.ref_blob_max_pooling(self.engine, n, h, w, c, fsize[0], fsize[1], stride[0], stride[1],
+                                                _opt(x), _opt(y), idx.ctypes.data_as(_vp)))
+        return y, idx
+
+    def blob_mean_pooling(self, x, fsize, stride):
+        n, h, w, c = x.shape
+        ho, wo = (h - fsize[0]) // stride[0] + 1, (w - fsize[1]) // stride[1] + 1
+        y = np.zeros((n, ho, wo, c), np.float32)
+        self._chk(self.lib.ref_blob_mean_pooling(self.engine, n, h, w, c, fsize[0], fsize[1], stride[0], stride[1],
+                                                 _opt(x), _opt(y)))
+        return y
+
+    def blob_resize_image(self, x, dl, dr, dt, db, padding=0, default_value=0.0):
+        n, h, w, c = x.shape
+        y = np.zeros((n, h + dt + db, w + dl + dr, c), np.float32)
+        self._chk(self.lib.ref_blob_resize_image(self.engine, n, h, w, c, dl, dr, dt, db, padding, _f(default_value),
+                                                 _opt(x), _opt(y)))
+        return y
+
+
+def rel_err(got: np.ndarray, want: np.ndarray) -> float:
+    """Parity metric for floating-point results: max_i |g_i - w_i| / max(|w_i|, tau), tau = 1e-3 * RMS(want).
+    The floor tau keeps the ratio meaningful for outputs that cancel to ~0 (sums of +-1-range products), where the
+    reference CPU engine itself differs from an fp64 evaluation by several 1e-5 of the element's own magnitude."""
+    got = np.asarray(got, np.float64).ravel()
+    want = np.asarray(want, np.float64).ravel()
+    if want.size == 0:
+        return 0.0
+    tau = 1e-3 * float(np.sqrt(np.mean(want * want))) + 1e-30
+    return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), tau)))

@@ -1,0 +1,70 @@
+"""Host-side checks of the C-ABI library that need no GPU: it loads, exports every symbol the public header
+declares, validates arguments, and refuses to compute without a device (there is no CPU fallback)."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from neoml_b200 import _capi as capi
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared():
+    text = (ROOT / "include" / "neoml_b200.h").read_text()
+    return sorted(set(re.findall(r"NB200_API\s+[\w\s\*]+?\b(nb200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = capi.load()
+    names = _declared()
+    assert len(names) >= 25
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/neoml_b200.h but not exported"
+    assert sorted(capi.SIGNATURES) == names, "python prototypes and the header disagree"
+
+
+def test_every_declaration_cites_the_reference_interface():
+    text = (ROOT / "include" / "neoml_b200.h").read_text()
+    # each compute entry point is preceded by a comment naming the IMathEngine method and its line
+    for name in _declared():
+        if name in ("nb200_version", "nb200_device_count", "nb200_error_string", "nb200_device_status",
+                    "nb200_launch_count", "nb200_mobilenetv2_scratch_floats", "nb200_vector_copy_int",
+                    "nb200_vector_fill_int"):
+            continue
+        head = text[:text.index(name + "(")]
+        # the citing comment sits directly above the declaration (a desc struct may lie between them)
+        assert "NME.h:" in head[-1400:], name
+
+
+def test_error_strings():
+    lib = capi.load()
+    assert lib.nb200_error_string(0) == b"ok"
+    assert b"device" in lib.nb200_error_string(capi.ENODEVICE)
+    assert lib.nb200_version() >= 100
+
+
+def test_argument_validation_needs_no_device():
+    lib = capi.load()
+    assert lib.nb200_vector_op(None, 999, None, None, None, 0.0, None, 4) == capi.EINVAL
+    assert lib.nb200_vector_op(None, 0, None, None, None, 0.0, None, -1) == capi.EINVAL
+    assert lib.nb200_vector_op(None, 0, None, None, None, 0.0, None, 0) == capi.OK  # empty input is a no-op
+    assert lib.nb200_multiply_matrix_by_transposed_matrix(None, None, 4, 0, 4, None, 4, 4, None, 4, None, 0) == capi.EINVAL
+    assert lib.nb200_multiply_matrix_by_transposed_matrix(None, None, 0, 8, 8, None, 4, 8, None, 4, None, 0) == capi.OK
+    d = capi.ConvDesc(1, 8, 8, 4, 4, 3, 3, 1, 1, 1, 1, 1, 1, 7, 8)  # wrong output height
+    assert lib.nb200_blob_convolution(None, C.byref(d), None, None, None, None, 0) == capi.EINVAL
+    assert lib.nb200_matrix_softmax_by_rows(None, None, 0, 16, None) == capi.OK
+    assert lib.nb200_transpose_matrix(None, 1, None, -1, 1, 1, 1, None) == capi.EINVAL
+
+
+def test_no_cpu_fallback_without_a_device():
+    lib = capi.load()
+    if lib.nb200_device_count() > 0:
+        pytest.skip("a B200 is present")
+    buf = (C.c_float * 16)()
+    rc = lib.nb200_vector_op(None, capi.VEC["COPY"], C.addressof(buf), None, None, 0.0, C.addressof(buf), 16)
+    assert rc == capi.ENODEVICE
+    rc = lib.nb200_multiply_matrix_by_transposed_matrix(None, C.addressof(buf), 4, 4, 4, C.addressof(buf), 4, 4,
+                                                        C.addressof(buf), 4, None, 0)
+    assert rc == capi.ENODEVICE
