@@ -7,6 +7,9 @@
 //              After the main loop the same warps are the epilogue: tcgen05.ld -> bias/residual/activation -> global.
 //   warp 8     allocates TMEM, and one elected lane issues the MMAs: per 8-wide K step lo*hi, hi*lo, hi*hi
 //              (3xTF32; the lo*lo term is below fp32 resolution) or hi*hi only (plain TF32).
+//              The two cross terms go to their own TMEM accumulator: the tensor core truncates on every
+//              accumulate, so the main accumulator should take one add per K step, not three; the epilogue adds
+//              the small accumulator to the main one in fp32.
 // Stage hand-over is by mbarriers: full[s] (256 producer arrivals, after a generic->async proxy fence) and
 // empty[s] (tcgen05.commit).  Every wait is bounded; on timeout the CTA raises an abort flag, records the site in
 // the device status word and falls through to the common teardown that frees TMEM.
@@ -68,6 +71,10 @@ __global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const Contra
 	// the swizzle pattern is a function of the absolute shared-memory address: tiles must start on 1024 B
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
+	// once any CTA on this device has given up on a wait, later CTAs do not start: a broken pipeline must not
+	// cost two seconds per tile
+	if(*reinterpret_cast<volatile int*>(p.status) != 0) return;
+
 	const bool threeX = p.precision == NB200_PREC_3XTF32;
 	constexpr int B_TILE_BYTES = BN * BK * 4;
 	const int stageBytes = (A_TILE_BYTES + B_TILE_BYTES) * (threeX ? 2 : 1);
@@ -97,7 +104,8 @@ __global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const Contra
 	const float* __restrict__ R = p.residual != nullptr ? p.residual + batch * p.strideC : nullptr;
 
 	const int numKb = (p.K + BK - 1) / BK;
-	constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); // power of two
+	constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); // power of two
+	const uint32_t tmemCols = threeX ? 2 * ACC_COLS : ACC_COLS; // main accumulator [+ cross-term accumulator]
 
 	if(tid == 0) {
 		for(int s = 0; s < stages; ++s) {
@@ -110,7 +118,7 @@ __global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const Contra
 		mbar_init_fence();
 	}
 	if(warp == 8) {
-		tmem_alloc(tmemSlot, TMEM_COLS);
+		tmem_alloc(tmemSlot, tmemCols);
 		tmem_relinquish();
 	}
 	tc_fence_before_sync();
@@ -236,7 +244,14 @@ __global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const Contra
 				const int col = half * COLS_PER_HALF + cc;
 				float v[16];
 				// every lane of the warp must take part in the TMEM load, in range or not
-				tmem_ld16(tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(col), v);
+				const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(col);
+				tmem_ld16(taddr, v);
+				if(threeX) {
+					float x[16];
+					tmem_ld16(taddr + ACC_COLS, x);
+#pragma unroll
+					for(int i = 0; i < 16; ++i) v[i] += x[i];
+				}
 				const int n = n0 + col;
 				if(m < p.M && n < p.N) {
 #pragma unroll
@@ -299,13 +314,12 @@ __global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const Contra
 					const uint32_t kOff = static_cast<uint32_t>(ks) * 32u; // 8 floats inside the 128-byte row
 					const uint64_t dAhi = umma_desc_k128(aHi + kOff);
 					const uint64_t dBhi = umma_desc_k128(bHi + kOff);
-					uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
+					const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
 					if(threeX) {
 						const uint64_t dAlo = umma_desc_k128(aLo + kOff);
 						const uint64_t dBlo = umma_desc_k128(bLo + kOff);
-						umma_tf32_ss(tmemBase, dAlo, dBhi, idesc, acc);
-						umma_tf32_ss(tmemBase, dAhi, dBlo, idesc, 1u);
-						acc = 1u;
+						umma_tf32_ss(tmemBase + ACC_COLS, dAlo, dBhi, idesc, acc);
+						umma_tf32_ss(tmemBase + ACC_COLS, dAhi, dBlo, idesc, 1u);
 					}
 					umma_tf32_ss(tmemBase, dAhi, dBhi, idesc, acc);
 				}
@@ -328,7 +342,7 @@ __global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const Contra
 	__syncthreads();
 	if(warp == 8) {
 		tc_fence_after_sync();
-		tmem_dealloc(tmemBase, TMEM_COLS);
+		tmem_dealloc(tmemBase, tmemCols);
 	}
 }
 

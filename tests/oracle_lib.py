@@ -331,13 +331,25 @@ class Reference:
         return y
 
 
-def rel_err(got: np.ndarray, want: np.ndarray) -> float:
-    """Parity metric for floating-point results: max_i |g_i - w_i| / max(|w_i|, tau), tau = 1e-3 * RMS(want).
-    The floor tau keeps the ratio meaningful for outputs that cancel to ~0 (sums of +-1-range products), where the
-    reference CPU engine itself differs from an fp64 evaluation by several 1e-5 of the element's own magnitude."""
+def rel_err(got: np.ndarray, want: np.ndarray, floor: float = 1e-3) -> float:
+    """max_i |g_i - w_i| / max(|w_i|, floor * RMS(want)).
+
+    Element-wise relative error is ill-posed for sums that cancel to ~0, so every use names its floor:
+    floor=1.0 (GATE_FLOOR) is the norm-wise figure the parity gate uses; floor=1e-3 is the strict figure that is
+    printed beside it.  Under the strict floor the reference CPU engine itself is 3e-5 .. 3e-4 away from an exact
+    (fp64) evaluation of the cases in tests/golden, i.e. it would not meet 1e-4 against its own definition."""
     got = np.asarray(got, np.float64).ravel()
     want = np.asarray(want, np.float64).ravel()
     if want.size == 0:
         return 0.0
-    tau = 1e-3 * float(np.sqrt(np.mean(want * want))) + 1e-30
+    tau = floor * float(np.sqrt(np.mean(want * want))) + 1e-30
     return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), tau)))
+
+
+GATE_FLOOR = 1.0
+TOL_FP32 = 1e-4   # 3xTF32 / fp32 paths: max relative error against the reference CPU engine
+TOL_TF32 = 1e-2   # opt-in plain TF32
+
+
+def gate_err(got, want) -> float:
+    return rel_err(got, want, GATE_FLOOR)

@@ -1,0 +1,277 @@
+"""Parity of the CUDA path against the reference CPU engine's committed outputs (tests/golden) and the plain-C
+oracle, through the C ABI (neoml_b200.ops -> include/neoml_b200.h).  Needs a B200: run with -m gpu.
+
+Tolerances (north-star contract): 1e-4 max relative error for the default 3xTF32 arithmetic, 1e-2 for opt-in TF32;
+index outputs bit-exact.  The error metric is oracle_lib.gate_err (norm-wise: |g-w| / max(|w|, RMS(w))); the
+strict-floor figure (floor 1e-3 x RMS) is printed alongside.
+"""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle_lib import TOL_FP32, TOL_TF32, gate_err, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from neoml_b200 import _capi, ops as ops_mod
+    assert _capi.load().nb200_device_count() >= 1, "no sm_100 device: the CUDA path cannot run (no fallback exists)"
+    yield ops_mod
+    torch.cuda.synchronize()
+    assert _capi.load().nb200_device_status(None, 0) == 0, "a kernel reported a bounded-wait timeout"
+
+
+def dev(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+PRECISIONS = [(0, TOL_FP32), (1, TOL_TF32), (2, TOL_FP32)]
+
+
+def check(got, want, tol, what):
+    g, s = gate_err(got, want), rel_err(got, want)
+    print(f"{what}: gate {g:.3e} strict {s:.3e}")
+    assert got.shape == want.shape
+    assert np.isfinite(got).all(), what
+    assert g < tol, f"{what}: {g:.3e} >= {tol}"
+
+
+@pytest.mark.parametrize("prec,tol", PRECISIONS)
+@pytest.mark.parametrize("name", sorted(cases.CONV_CASES))
+def test_blob_convolution_golden(ops, golden, oracle, name, prec, tol):
+    x, f, b, kw = cases.conv_inputs(name)
+    y = host(ops.BlobConvolution(dev(x), dev(f), dev(b), precision=prec, **kw))
+    check(y, golden[f"conv/{name}"], tol, f"conv/{name}/ref")
+    check(y, oracle.blob_convolution(x, f, b, **kw), tol, f"conv/{name}/oracle")
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONV_CASES_ORACLE_ONLY))
+def test_blob_convolution_oracle_only(ops, oracle, name):
+    x, f, b, kw = cases.conv_inputs(name)
+    y = host(ops.BlobConvolution(dev(x), dev(f), dev(b), **kw))
+    check(y, oracle.blob_convolution(x, f, b, **kw), TOL_FP32, f"conv/{name}/oracle")
+
+
+def test_blob_convolution_fused_tail(ops, oracle):
+    """bias + residual + ReLU in the epilogue equals the unfused sequence."""
+    x, f, b, kw = cases.conv_inputs("k3_c32_tap")
+    want = oracle.blob_convolution(x, f, b, **kw)
+    res = cases.uniform(77, want.shape)
+    want = np.maximum(want + res, 0.0)
+    y = host(ops.BlobConvolution(dev(x), dev(f), dev(b), residual=dev(res), act=ops.ACT_RELU, **kw))
+    check(y, want, TOL_FP32, "conv fused tail")
+
+
+def test_blob_convolution_unaligned_handles(ops, oracle):
+    """NeoML handles may sit at any 4-byte offset: shift every operand by one float."""
+    x, f, b, kw = cases.conv_inputs("k3_c32_tap")
+    want = oracle.blob_convolution(x, f, b, **kw)
+
+    def shifted(a):
+        buf = torch.zeros(a.size + 1, dtype=torch.float32, device="cuda")
+        buf[1:] = torch.from_numpy(a.ravel()).cuda()
+        return buf[1:].view(a.shape)
+
+    out = torch.zeros(want.size + 1, dtype=torch.float32, device="cuda")
+    y = ops.BlobConvolution(shifted(x), shifted(f), shifted(b), result=out[1:].view(want.shape), **kw)
+    check(host(y), want, TOL_FP32, "conv unaligned")
+
+
+@pytest.mark.parametrize("prec,tol", PRECISIONS)
+@pytest.mark.parametrize("name", sorted(cases.MMT_CASES))
+def test_multiply_matrix_by_transposed_matrix(ops, golden, name, prec, tol):
+    a, b, kw = cases.mmt_inputs(name)
+    y = ops.MultiplyMatrixByTransposedMatrix(dev(a), dev(b), first_height=kw["m"], first_width=kw["k"],
+                                             second_height=kw["n"], first_row_size=kw["lda"],
+                                             second_row_size=kw["ldb"], precision=prec)
+    check(host(y), golden[f"mmt/{name}"], tol, f"mmt/{name}")
+
+
+def test_mmt_strided_result_and_bias(ops, oracle):
+    a, b, kw = cases.mmt_inputs("strided")
+    bias = cases.uniform(5, (kw["n"],))
+    want = oracle.multiply_matrix_by_transposed_matrix(a, b, **kw) + bias
+    out = torch.full((kw["m"], kw["n"] + 3), 7.0, dtype=torch.float32, device="cuda")
+    ops.MultiplyMatrixByTransposedMatrix(dev(a), dev(b), out, first_height=kw["m"], first_width=kw["k"],
+                                         second_height=kw["n"], first_row_size=kw["lda"], second_row_size=kw["ldb"],
+                                         result_row_size=kw["n"] + 3, free_term=dev(bias))
+    got = host(out)
+    check(np.ascontiguousarray(got[:, :kw["n"]]), want, TOL_FP32, "mmt strided result")
+    assert (got[:, kw["n"]:] == 7.0).all(), "columns beyond the result width were overwritten"
+
+
+@pytest.mark.parametrize("prec,tol", PRECISIONS)
+@pytest.mark.parametrize("name", sorted(cases.MM_CASES))
+def test_multiply_matrix_by_matrix(ops, golden, name, prec, tol):
+    a, b = cases.mm_inputs(name)
+    check(host(ops.MultiplyMatrixByMatrix(dev(a), dev(b), precision=prec)), golden[f"mm/{name}"], tol, f"mm/{name}")
+
+
+def test_batch_mmt(ops, oracle):
+    a, b = cases.uniform(41, (3, 50, 70)), cases.uniform(42, (3, 33, 70))
+    want = np.stack([oracle.multiply_matrix_by_transposed_matrix(a[i], b[i]) for i in range(3)])
+    check(host(ops.BatchMultiplyMatrixByTransposedMatrix(dev(a), dev(b))), want, TOL_FP32, "batch mmt")
+
+
+@pytest.mark.parametrize("name", sorted(cases.CHCONV_CASES))
+def test_channelwise_convolution(ops, golden, name):
+    x, f, b, kw = cases.chconv_inputs(name)
+    check(host(ops.BlobChannelwiseConvolution(dev(x), dev(f), dev(b), **kw)), golden[f"chconv/{name}"], TOL_FP32,
+          f"chconv/{name}")
+
+
+@pytest.mark.parametrize("prec,tol", [(0, TOL_FP32), (1, TOL_TF32)])
+@pytest.mark.parametrize("name", sorted(cases.MBV2_CASES))
+def test_mobilenetv2_block(ops, golden, name, prec, tol):
+    (x, we, be, wd, bd, wp, bp), kw = cases.mbv2_inputs(name)
+    y = ops.MobileNetV2Block(dev(x), dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), stride=kw["stride"],
+                             residual=kw["residual"], expand_act=kw["act_exp"], expand_act_param=kw["act_exp_param"],
+                             channelwise_act=kw["act_dw"], channelwise_act_param=kw["act_dw_param"], precision=prec)
+    check(host(y), golden[f"mbv2/{name}"], tol, f"mbv2/{name}")
+
+
+def test_mobilenetv2_block_in_place(ops, golden):
+    (x, we, be, wd, bd, wp, bp), kw = cases.mbv2_inputs("relu6_res")
+    xd = dev(x)
+    ops.MobileNetV2Block(xd, dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), result=xd, stride=1, residual=True)
+    check(host(xd), golden["mbv2/relu6_res"], TOL_FP32, "mbv2 in place")
+
+
+@pytest.mark.parametrize("name", sorted(cases.SOFTMAX_CASES))
+def test_softmax(ops, golden, name):
+    x, h, w = cases.softmax_inputs(name)
+    xd = dev(x)
+    check(host(ops.MatrixSoftmaxByRows(xd, h, w)), golden[f"softmax/{name}"], 1e-5, f"softmax/{name}")
+    ops.MatrixSoftmaxByRows(xd, h, w, result=xd)  # in place
+    check(host(xd), golden[f"softmax/{name}"], 1e-5, f"softmax/{name} in place")
+
+
+def test_vector_ops(ops, oracle):
+    from neoml_b200._capi import VEC_OPS
+    for n in (1, 7, 1001, 4096):
+        a = cases.uniform(11, (n,), -4, 4)
+        b = cases.uniform(12, (n,), -4, 4)
+        sc = torch.tensor([0.7], dtype=torch.float32, device="cuda")
+        for op, name in enumerate(VEC_OPS):
+            a_ = np.abs(a) + 0.1 if name in ("SQRT", "INV") else a
+            b_ = np.abs(b) + 0.5 if name == "ELTWISE_DIV" else b
+            got = host(ops.vector_op(name, dev(a_), dev(b_), scalar=sc, value=0.7))
+            want = oracle.vector_op(op, a_, b_, 0.7)
+            assert rel_err(got, want) < 1e-5, (name, n)  # fused multiply-add vs two roundings, expf vs exp
+
+
+def test_vector_ops_unaligned_and_in_place(ops, oracle):
+    a = cases.uniform(13, (1003,))
+    buf = torch.zeros(1004, dtype=torch.float32, device="cuda")
+    buf[1:] = dev(a)
+    thr = torch.tensor([0.25], dtype=torch.float32, device="cuda")
+    ops.vector_op("RELU", buf[1:], scalar=thr, result=buf[1:])
+    assert np.array_equal(host(buf[1:]), oracle.vector_op(9, a, None, 0.25))
+    assert float(buf[0]) == 0.0
+
+
+def test_matrix_helpers(ops, oracle):
+    for (bsz, h, w) in [(3, 5, 7), (2, 64, 768), (1, 300, 2048), (4, 49, 64)]:
+        m = cases.uniform(21, (bsz * h * w,))
+        v_bw, v_rows, v_w = cases.uniform(22, (bsz * w,)), cases.uniform(23, (bsz * h,)), cases.uniform(24, (w,))
+        md = dev(m)
+        assert np.array_equal(host(ops.AddVectorToMatrixRows(bsz, md, dev(v_bw), h, w)),
+                              oracle.add_vector_to_matrix_rows(bsz, m, h, w, v_bw))
+        assert np.array_equal(host(ops.AddVectorToMatrixColumns(md, dev(v_rows), bsz * h, w)),
+                              oracle.add_vector_to_matrix_columns(m, bsz * h, w, v_rows))
+        assert gate_err(host(ops.SumMatrixRows(bsz, md, h, w)), oracle.sum_matrix_rows(bsz, m, h, w)) < 1e-5
+        init = cases.uniform(25, (bsz, w))
+        assert gate_err(host(ops.SumMatrixRows(bsz, md, h, w, result=dev(init), add=True)),
+                        oracle.sum_matrix_rows(bsz, m, h, w, init)) < 1e-5
+        assert gate_err(host(ops.SumMatrixColumns(md, bsz * h, w)), oracle.sum_matrix_columns(m, bsz * h, w)) < 1e-5
+        assert np.array_equal(host(ops.MultiplyDiagMatrixByMatrix(dev(v_rows), md, bsz * h, w)),
+                              oracle.multiply_diag_matrix_by_matrix(v_rows, bsz * h, m, w))
+        assert np.array_equal(host(ops.BatchMultiplyMatrixByDiagMatrix(1, md, bsz * h, w, dev(v_w), 0)),
+                              oracle.multiply_matrix_by_diag_matrix(1, m, bsz * h, w, v_w, 0))
+        assert np.array_equal(host(ops.BatchMultiplyMatrixByDiagMatrix(bsz, md, h, w, dev(v_bw), w)),
+                              oracle.multiply_matrix_by_diag_matrix(bsz, m, h, w, v_bw, w))
+
+
+def test_transpose(ops, oracle):
+    for (b, h, m, w, c) in [(2, 3, 4, 5, 6), (2, 48, 1, 12, 64), (3, 50, 1, 70, 1), (1, 1, 1, 9, 4), (2, 33, 1, 1, 5)]:
+        t = cases.uniform(26, (b * h * m * w * c,))
+        assert np.array_equal(host(ops.TransposeMatrix(b, dev(t), h, m, w, c)), oracle.transpose_matrix(b, t, h, m, w, c))
+
+
+def test_argmax_bit_exact(ops, oracle):
+    for (h, w) in [(13, 37), (256, 1000), (5, 1)]:
+        am = cases.uniform(27, (h * w,))
+        am[3 % am.size] = am.max()  # a tie: first maximum must win
+        v, i = ops.FindMaxValueInRows(dev(am), h, w)
+        ov, oi = oracle.find_max_value_in_rows(am, h, w)
+        assert np.array_equal(host(v), ov) and np.array_equal(host(i), oi)
+    am = cases.uniform(28, (2 * 6 * 37,))
+    v, i = ops.FindMaxValueInColumns(2, dev(am), 6, 37)
+    ov, oi = oracle.find_max_value_in_columns(2, am, 6, 37)
+    assert np.array_equal(host(v), ov) and np.array_equal(host(i), oi)
+
+
+def test_pooling_and_resize(ops, oracle):
+    for shape in [(2, 9, 11, 6), (2, 10, 12, 8)]:
+        x = cases.uniform(31, shape)
+        y, idx = ops.BlobMaxPooling(dev(x), (3, 3), (2, 2), with_indices=True)
+        want, _ = oracle.blob_max_pooling(x, (3, 3), (2, 2))
+        assert np.array_equal(host(y), want)
+        # every index points at a maximum of its window (the reference's index layout: offset inside the image)
+        flat = x.reshape(shape[0], -1)
+        picked = np.take_along_axis(flat, host(idx).reshape(shape[0], -1).astype(np.int64), axis=1)
+        assert np.array_equal(picked.reshape(want.shape), want)
+        assert rel_err(host(ops.BlobMeanPooling(dev(x), (3, 2), (2, 1))), oracle.blob_mean_pooling(x, (3, 2), (2, 1))) < 1e-6
+        for pad in (0, 1, 2):
+            assert np.array_equal(host(ops.BlobResizeImage(dev(x), 1, 2, 2, 1, pad, 0.5)),
+                                  oracle.blob_resize_image(x, 1, 2, 2, 1, pad, 0.5))
+        assert np.array_equal(host(ops.BlobResizeImage(dev(x), -1, -2, -2, 1, 0, 0.5)),
+                              oracle.blob_resize_image(x, -1, -2, -2, 1, 0, 0.5))
+
+
+def test_empty_inputs(ops):
+    e = torch.empty(0, dtype=torch.float32, device="cuda")
+    assert ops.vector_op("COPY", e, result=e).numel() == 0
+    y = ops.MultiplyMatrixByTransposedMatrix(torch.empty((0, 8), device="cuda"), torch.ones((4, 8), device="cuda"))
+    assert y.shape == (0, 4)
+
+
+# ---- full-size checks through size-independent properties ------------------------------------------------------------
+
+def test_config1_convolution_full_size(ops, oracle):
+    """BASELINE config 1 (32x56x56x64, 64 filters 3x3, pad 1, bias): sampled outputs against the oracle, and
+    linearity conv(x1 + x2) == conv(x1) + conv(x2) - bias over the whole tensor."""
+    x1, x2 = cases.uniform(101, (32, 56, 56, 64)), cases.uniform(102, (32, 56, 56, 64))
+    f, b = cases.uniform(103, (64, 3, 3, 64)), cases.uniform(104, (64,))
+    fd, bd = dev(f), dev(b)
+    y1 = ops.BlobConvolution(dev(x1), fd, bd, padding=(1, 1))
+    y2 = ops.BlobConvolution(dev(x2), fd, bd, padding=(1, 1))
+    y12 = ops.BlobConvolution(dev(x1 + x2), fd, bd, padding=(1, 1))
+    lin = host(y1 + y2 - bd)
+    check(host(y12), lin, 2e-4, "config1 linearity")  # two roundings of the inputs' sum on the right-hand side
+    # oracle on 3 images
+    want = oracle.blob_convolution(x1[:3], f, b, padding=(1, 1))
+    check(host(y1)[:3], want, TOL_FP32, "config1 vs oracle (3 images)")
+    # the exact-fp32 CUDA-core path on the full tensor
+    y_simt = ops.BlobConvolution(dev(x1), fd, bd, padding=(1, 1), precision=ops.PREC_FP32_SIMT)
+    check(host(y1), host(y_simt), TOL_FP32, "config1 tensor-core vs CUDA-core")
+
+
+def test_config5_gemm_1024(ops, oracle):
+    a, b = cases.uniform(111, (1024, 1024)), cases.uniform(112, (1024, 1024))
+    y = ops.MultiplyMatrixByMatrix(dev(a), dev(b))
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    check(host(y), want, TOL_FP32, "gemm 1024 NN")
+    yt = ops.MultiplyMatrixByTransposedMatrix(dev(a), dev(b))
+    want_t = (a.astype(np.float64) @ b.astype(np.float64).T).astype(np.float32)
+    check(host(yt), want_t, TOL_FP32, "gemm 1024 NT")
+    y_tf32 = ops.MultiplyMatrixByMatrix(dev(a), dev(b), precision=ops.PREC_TF32)
+    check(host(y_tf32), want, TOL_TF32, "gemm 1024 NN tf32")
