@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: ResNet-50 v1.5 fp32-accurate inference (images/s) through the B200 math-engine kernels.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by torch.distributed.run (one rank per GPU); inference is batch-sharded with no data-path
+collective (weak scaling: every rank runs the full per-GPU batch).  Rank 0 prints ONE JSON line.
+
+A step is one forward pass over one synthetic batch (256 x 224 x 224 x 3, uniform[0,1], seeded; He-normal weights with
+the BatchNorm folded into the free terms).  `value` is timed with the batch already resident in HBM; `e2e` runs the
+same call with the batch in pinned host memory, host->device copy and device->host read of the result inside the
+timed region.  `roofline` describes the dominant kernel (the tcgen05 contraction) from CUDA-event timings of every
+contraction launch in one extra, instrumented step.  `cpu_baseline` times the reference's own CPU math engine
+(oracle/_ref) on a bounded sample of the same workload on this host's cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "resnet50_fp32_infer_images_per_s"
+UNIT = "images/s"
+IMAGE = (224, 224, 3)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=256, help="per-GPU batch")
+    ap.add_argument("--precision", type=int, default=0, help="0 = 3xTF32 (default), 1 = TF32 opt-in")
+    ap.add_argument("--unfused", action="store_true", help="issue conv / add / ReLU as separate engine calls")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", action="store_true", help="print the per-contraction timing table to stderr")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------------- CPU legs
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_reference_run(per_thread_batch: int, rounds_budget_s: float, min_rounds: int, max_rounds: int, warm: int):
+    """Times the reference CPU math engine (or, where it was not built, the plain-C oracle port) on ResNet-50:
+    one engine per host thread, each thread a replica on its own slice of the batch -- the reference's own
+    multi-core model (CDistributedInference).  Returns (images/s, ms per round, cores, kind, sample text)."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import numpy as np
+    from neoml_b200 import resnet50
+    import ref_backend
+    from oracle_lib import Reference
+
+    kind = "reference" if Reference.available() else "port"
+    cores = host_cores() if kind == "reference" else 1
+    weights = resnet50.make_weights()
+    rng = np.random.default_rng(7)
+    inputs = [rng.uniform(0, 1, (per_thread_batch, *IMAGE)).astype(np.float32) for _ in range(cores)]
+    backends = [None] * cores
+    barrier = threading.Barrier(cores + 1)
+    stop = {"flag": False}
+
+    def worker(i):
+        backends[i] = ref_backend.RefBackend() if kind == "reference" else ref_backend.OracleBackend()
+        while True:
+            barrier.wait()
+            if stop["flag"]:
+                break
+            resnet50.forward(backends[i], weights, inputs[i], fuse=False)
+            barrier.wait()
+
+    threads = [threading.Thread(target=worker, args=(i,), daemon=True) for i in range(cores)]
+    for t in threads:
+        t.start()
+    times = []
+    t_start = time.perf_counter()
+    rounds = 0
+    while True:
+        barrier.wait()
+        t0 = time.perf_counter()
+        barrier.wait()
+        dt = time.perf_counter() - t0
+        rounds += 1
+        if rounds > warm:
+            times.append(dt)
+        timed = len(times)
+        if timed >= max_rounds or (timed >= min_rounds and time.perf_counter() - t_start > rounds_budget_s):
+            break
+    stop["flag"] = True
+    barrier.wait()
+    for t in threads:
+        t.join()
+    images = per_thread_batch * cores
+    total = sum(times)
+    ips = images * len(times) / total
+    sample = (f"ResNet-50 forward, {cores} engine(s) x batch {per_thread_batch} per round, {len(times)} timed rounds "
+              f"after {warm} warm-up; sgemm = MLAS (no MKL on this host)" if kind == "reference" else
+              f"plain-C oracle port, 1 thread x batch {per_thread_batch}, {len(times)} rounds")
+    return ips, 1e3 * total / len(times), cores, kind, sample
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ips, ms, cores, kind, sample = cpu_reference_run(per_thread_batch=1, rounds_budget_s=0.0, min_rounds=args.steps,
+                                                     max_rounds=args.steps, warm=args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(ips, 3), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": "resnet50_v1.5_infer_b256_224x224x3", "per_gpu_batch": 256,
+                   "step": f"bounded sample of the workload: {cores} host threads x 1 image per step",
+                   "engine": "reference CPU math engine (MLAS sgemm)"},
+        "cpu_baseline": {"value": round(ips, 3), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": round(ips, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of this rank's GPU, sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the busiest half of the samples is "under load"
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class ContractionTimer:
+    """CUDA events around every contraction launch of one instrumented step."""
+
+    def __init__(self, torch):
+        self.torch, self.records, self._start = torch, [], None
+
+    def begin(self):
+        self._start = self.torch.cuda.Event(enable_timing=True)
+        self._start.record()
+
+    def end(self, kind, flops):
+        e = self.torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.records.append((kind, flops, self._start, e))
+
+    def totals(self):
+        self.torch.cuda.synchronize()
+        ms = [(k, f, s.elapsed_time(e)) for k, f, s, e in self.records]
+        return sum(f for _, f, _ in ms), sum(t for _, _, t in ms), len(ms), ms
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from neoml_b200 import _capi, resnet50
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl ours needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _capi.load()
+    if lib.nb200_device_count() < 1:
+        raise SystemExit("libneoml_b200.so sees no sm_100 device")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    batch = args.batch
+    be = resnet50.EngineBackend(precision=args.precision)
+    weights = be.upload(resnet50.make_weights())
+    rng = np.random.default_rng(1234 + rank)
+    host_x = torch.from_numpy(rng.uniform(0, 1, (batch, *IMAGE)).astype(np.float32)).pin_memory()
+    dev_x = host_x.cuda()
+    fuse = not args.unfused
+
+    def step(x):
+        return resnet50.forward(be, weights, x, fuse=fuse)
+
+    # ---- device-resident timing -------------------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step(dev_x)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = lib.nb200_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        probs, idx = step(dev_x)
+    stop.record()
+    barrier()
+    launches = lib.nb200_launch_count() - launches0
+    ms_total = start.elapsed_time(stop)
+    clocks = sampler.stop()
+
+    # ---- end to end: pinned host batch -> device -> forward -> result back, double-buffered ---------------------------
+    copy_stream = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    bufs = [torch.empty_like(dev_x) for _ in range(2)]
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    host_idx = torch.empty(batch, dtype=torch.int32).pin_memory()
+    host_probs = torch.empty((batch, resnet50.CLASSES), dtype=torch.float32).pin_memory()
+
+    def e2e_loop(n):
+        for i in range(n):
+            b = i % 2
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[b])  # the forward two steps ago has finished reading this buffer
+                bufs[b].copy_(host_x, non_blocking=True)
+                copied[b].record(copy_stream)
+            main.wait_event(copied[b])
+            p, ix = step(bufs[b])
+            consumed[b].record(main)
+            host_idx.copy_(ix, non_blocking=True)
+            host_probs.copy_(p, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for b in range(2):
+        consumed[b].record(main)
+    e2e_loop(2)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_loop(args.steps)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    # max over ranks
+    times = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = float(times[0]), float(times[1])
+
+    status = lib.nb200_device_status(None, 0)
+    if status != 0:
+        raise SystemExit(f"a kernel reported a bounded-wait timeout (status {status:#x}); no number is reported")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (rank 0, one instrumented step) -----------------------------------------------
+    timer = ContractionTimer(torch)
+    be_t = resnet50.EngineBackend(precision=args.precision, timer=timer)
+    resnet50.forward(be_t, weights, dev_x, fuse=fuse)
+    flops, tc_ms, tc_launches, per_layer = timer.totals()
+    if args.layers:
+        names = [sp.name for sp in resnet50.conv_specs()]
+        order = ["stem"]
+        for si, (_, _, blocks, _) in enumerate(resnet50.STAGES):
+            for bi in range(blocks):
+                p = f"s{si + 1}b{bi + 1}"
+                order += ([p + "_down"] if bi == 0 else []) + [p + "_c1", p + "_c2", p + "_c3"]
+        order.append("fc")
+        assert len(order) == len(per_layer) and set(order) == set(names) | {"fc"}
+        for name, (_, f, t) in zip(order, per_layer):
+            print(f"{name:10s} {f / 1e9:9.2f} GFLOP {t:8.3f} ms {f / t / 1e9:8.1f} TFLOP/s", file=sys.stderr)
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        pk = json.loads(peaks_path.read_text())
+        peak_tf, peak_src = float(pk["bf16_tflops_sustained"]), "MEASURED_PEAKS.json bf16_tflops_sustained"
+    else:
+        peak_tf, peak_src = 1390.7, "fallback (MEASURED_PEAKS.json absent): sustained cuBLAS bf16 measured on this pool"
+    achieved_tf = flops / (tc_ms * 1e-3) / 1e12
+    mma_per_product = 3 if args.precision == 0 else 1
+    eff_peak = peak_tf / 2 / mma_per_product  # TF32 runs at half the bf16 rate; 3xTF32 issues three MMAs per product
+    roofline = {
+        "bound": "tensor", "kernel": "contraction_tc_kernel (tcgen05 kind::tf32, implicit-GEMM conv + FC)",
+        "achieved": round(achieved_tf, 2), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved_tf / peak_tf, 4),
+        "peak_source": peak_src, "traffic": None,
+        "launches_per_step": tc_launches, "ms_per_step_in_kernel": round(tc_ms, 3),
+        "algorithmic_gflop_per_step": round(flops / 1e9, 2),
+        "effective_peak_for_this_arithmetic": round(eff_peak, 1),
+        "frac_of_effective_peak": round(achieved_tf / eff_peak, 4),
+        "note": "peak is dense bf16; TF32 = 1/2 of it, 3xTF32 = 1/6 (algorithmic flops counted once)",
+    }
+
+    images = batch * world * args.steps
+    line = {
+        "metric": METRIC, "value": round(images / (ms_total * 1e-3), 2), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_total / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32 (3xTF32 split on tcgen05, fp32 accumulate)" if args.precision == 0 else "tf32",
+        "data": "synthetic",
+        "config": {"workload": "resnet50_v1.5_infer_b256_224x224x3" if batch == 256 else f"resnet50_v1.5_infer_b{batch}",
+                   "per_gpu_batch": batch, "global_batch": batch * world, "parallelism": f"batch-sharded x{world}",
+                   "fused_epilogues": fuse, "l2": "inputs and activations larger than L2 (154 MB batch, 822 MB stem output)"},
+        "clocks": clocks,
+        "e2e": {"value": round(images / (e2e_ms * 1e-3), 2), "unit": UNIT,
+                "h2d_bytes_per_step": host_x.numel() * 4, "d2h_bytes_per_step": host_idx.numel() * 4 + host_probs.numel() * 4,
+                "ms_per_step": round(e2e_ms / args.steps, 3)},
+        "gpu_launches": int(launches),
+        "roofline": roofline,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            ips, ms, cores, kind, sample = cpu_reference_run(per_thread_batch=1, rounds_budget_s=args.cpu_seconds,
+                                                             min_rounds=2, max_rounds=50, warm=1)
+            line["cpu_baseline"] = {"value": round(ips, 3), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
+        except Exception as exc:  # the baseline is reported, never required
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -68,6 +68,13 @@ NB200_API const char* nb200_error_string(int code);
 /* Device-side status word of the calling thread's current device: 0 = clean, else the code of the first bounded
  * wait that gave up (kernel id << 8 | site).  Reading synchronises `stream`.  `reset` != 0 clears it. */
 NB200_API int nb200_device_status(void* stream, int reset);
+/* Text of the CUDA runtime error behind the calling thread's last NB200_ELAUNCH / NB200_ENODEVICE. */
+NB200_API const char* nb200_last_cuda_error(void);
+/* Debug aid: when device_buffer is non-NULL, CTA 0 of every later contraction launch stores clock64() stamps of its
+ * pipeline roles for the first `steps` K-block steps at device_buffer[role * steps + step] (11 stamp kinds, 8-byte words; kinds 0-6 are per K-block step, 7-10 per tile).
+ * skip_mask switches pipeline stages off to time the others in isolation (results are then wrong): bit 0 no MMA,
+ * bit 1 converters move no data, bit 2 the epilogue stores nothing.  0 for normal operation. */
+NB200_API void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int skip_mask);
 /* Kernels launched by this library in this process since load (for launch accounting in benchmarks). */
 NB200_API uint64_t nb200_launch_count(void);
 
@@ -91,8 +98,13 @@ typedef struct nb200_conv_desc {
 	int pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
 	int ho, wo;                  /* result */
 } nb200_conv_desc;
+/* `scratch` is optional (NULL = none): nb200_blob_convolution_scratch_floats(desc) floats of device memory (0 for most
+ * shapes) that let a convolution whose channel count is not a multiple of four (the 3-channel network stem) run on
+ * 16-byte pieces: the image and the filter are widened to 4-channel pixels there first.  The engine takes it from
+ * its stack allocator; without it the same result is computed by a slower element-wise gather. */
+NB200_API size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* desc);
 NB200_API int nb200_blob_convolution(void* stream, const nb200_conv_desc* desc, const float* x,
-	const float* filter, float* y, const nb200_epilogue* epi, int precision);
+	const float* filter, float* y, float* scratch, const nb200_epilogue* epi, int precision);
 
 /* ---- depthwise / fused blocks ----------------------------------------------------------------------------- */
 /* IDnnEngine::BlobChannelwiseConvolution (NME.h:766-771): x [batch,h,w,c], filter [r,s,c], y [batch,ho,wo,c]. */

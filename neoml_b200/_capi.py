@@ -49,11 +49,14 @@ SIGNATURES = {
     "nb200_device_count": (_i, []),
     "nb200_error_string": (C.c_char_p, [_i]),
     "nb200_device_status": (_i, [_vp, _i]),
+    "nb200_last_cuda_error": (C.c_char_p, []),
+    "nb200_debug_set_contraction_trace": (None, [_vp, _i, _i]),
     "nb200_launch_count": (C.c_uint64, []),
     "nb200_multiply_matrix_by_transposed_matrix": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _EP, _i]),
     "nb200_batch_multiply_matrix_by_transposed_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
     "nb200_multiply_matrix_by_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
-    "nb200_blob_convolution": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _EP, _i]),
+    "nb200_blob_convolution_scratch_floats": (C.c_size_t, [C.POINTER(ConvDesc)]),
+    "nb200_blob_convolution": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _vp, _EP, _i]),
     "nb200_blob_channelwise_convolution": (_i, [_vp, C.POINTER(ChConvDesc), _vp, _vp, _vp, _vp, _i, _f]),
     "nb200_mobilenetv2_scratch_floats": (C.c_size_t, [C.POINTER(Mbv2Desc)]),
     "nb200_mobilenetv2_block": (_i, [_vp, C.POINTER(Mbv2Desc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
@@ -82,6 +85,8 @@ class Nb200Error(RuntimeError):
     def __init__(self, fn: str, code: int):
         self.code = code
         msg = load().nb200_error_string(code).decode() if _lib is not None else str(code)
+        if code in (ELAUNCH, ENODEVICE) and _lib is not None:
+            msg += ": " + _lib.nb200_last_cuda_error().decode()
         super().__init__(f"{fn} failed: {msg} ({code})")
 
 

@@ -35,6 +35,11 @@ int run(ContractionParams& p, int batch, void* stream, int precision)
 	}
 	if(p.M == 0 || p.N == 0 || batch == 0) return NB200_OK;
 	if(p.A == nullptr || p.B == nullptr || p.C == nullptr) return NB200_EINVAL;
+	// the kernels index each operand of one batch entry with 32-bit element offsets (NeoML blobs are < 2^31 elements)
+	if(static_cast<long long>(p.M) * (p.a_mode == A_ROWS ? p.lda : 1) > 0x7fffffffLL
+		|| static_cast<long long>(p.M) * p.ldc > 0x7fffffffLL) {
+		return NB200_ETOOBIG;
+	}
 	p.precision = precision;
 	p.stages = 0;
 	p.status = device_status_word();
@@ -47,7 +52,39 @@ int run(ContractionParams& p, int batch, void* stream, int precision)
 
 } // namespace
 
+// y[pixel][0..cOut) = x[pixel][0..cIn), zero beyond: widens a channels-last blob (or filter) to a multiple of four
+// channels so that every filter tap is one aligned 16-byte piece
+__global__ void __launch_bounds__(256) pad_channels_kernel(const float* __restrict__ x, float* __restrict__ y,
+	long long pixels, int cIn, int cOut)
+{
+	const long long total = pixels * cOut;
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+		const long long px = i / cOut;
+		const int c = static_cast<int>(i - px * cOut);
+		y[i] = c < cIn ? __ldg(x + px * cIn + c) : 0.f;
+	}
+}
+
+bool wants_channel_padding(const nb200_conv_desc* d)
+{
+	const bool pointwise = d->r == 1 && d->s == 1 && d->pad_h == 0 && d->pad_w == 0 && d->stride_h == 1 && d->stride_w == 1;
+	return !pointwise && d->c % 4 != 0;
+}
+
 extern "C" {
+
+size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* d)
+{
+	if(d == nullptr || d->c <= 0 || !wants_channel_padding(d)) return 0;
+	const size_t c4 = static_cast<size_t>((d->c + 3) / 4 * 4);
+	return (static_cast<size_t>(d->batch) * d->h * d->w + static_cast<size_t>(d->k) * d->r * d->s) * c4 + 8;
+}
+
+void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int skip_mask)
+{
+	set_contraction_trace(static_cast<unsigned long long*>(device_buffer), steps, skip_mask);
+}
 
 int nb200_multiply_matrix_by_transposed_matrix(void* stream, const float* a, int m, int k, int lda,
 	const float* b, int n, int ldb, float* c, int ldc, const nb200_epilogue* epi, int precision)
@@ -99,9 +136,30 @@ int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int
 }
 
 int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
-	const nb200_epilogue* epi, int precision)
+	float* scratch, const nb200_epilogue* epi, int precision)
 {
 	if(d == nullptr) return NB200_EINVAL;
+	if(scratch != nullptr && d->c > 0 && d->batch > 0 && wants_channel_padding(d) && precision != NB200_PREC_FP32_SIMT) {
+		// channel counts that are not a multiple of four (the 3-channel stem) would be gathered element by element;
+		// with scratch the image and the filter are first widened to 4-channel pixels (zeros in the new channels add
+		// nothing to any sum) and the convolution runs on 16-byte pieces
+		if(x == nullptr || filter == nullptr) return NB200_EINVAL;
+		if(device_status_word() == nullptr) return NB200_ENODEVICE;
+		const int c4 = (d->c + 3) / 4 * 4;
+		const long long pixels = static_cast<long long>(d->batch) * d->h * d->w;
+		const long long taps = static_cast<long long>(d->k) * d->r * d->s;
+		if(pixels * c4 > 0x7fffffffLL) return NB200_ETOOBIG;
+		float* xs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
+		float* fs = xs + pixels * c4;
+		pad_channels_kernel<<<grid_for(pixels * c4, 256, 16), 256, 0, as_stream(stream)>>>(x, xs, pixels, d->c, c4);
+		pad_channels_kernel<<<grid_for(taps * c4, 256, 16), 256, 0, as_stream(stream)>>>(filter, fs, taps, d->c, c4);
+		count_launch(2);
+		const int rc = check_launch();
+		if(rc != NB200_OK) return rc;
+		nb200_conv_desc padded = *d;
+		padded.c = c4;
+		return nb200_blob_convolution(stream, &padded, xs, fs, y, nullptr, epi, precision);
+	}
 	if(d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0
 		|| d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
 		return NB200_EINVAL;
@@ -132,12 +190,10 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 		p.a_mode = A_ROWS;
 		p.lda = d->c;
 		p.a_vec = vec_ok(x, d->c, 0);
-	} else if(d->c % 32 == 0 && aligned16(x)) {
-		p.a_mode = A_CONV_TAP;
-		p.a_vec = 1;
 	} else {
-		p.a_mode = A_CONV_ANY;
-		p.a_vec = 0;
+		// gathered rows; 16-byte copies when a chunk of four K indices never straddles a filter tap
+		p.a_mode = A_CONV_TAP;
+		p.a_vec = d->c % 4 == 0 && aligned16(x) ? 1 : 0;
 	}
 	return run(p, 1, stream, precision);
 }

@@ -103,6 +103,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 	return false;
 }
 
+// Warp-wide form: lane 0 polls, the result is shared by shuffle.  Keeps 31 of 32 lanes off the shared-memory
+// pipeline while a whole warp waits for the same phase (the __shfl_sync also orders the warp's later reads).
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+	int* status, int site)
+{
+	int done = 0;
+	if((threadIdx.x & 31) == 0) done = mbar_wait_bounded(bar, parity, abort_flag, status, site) ? 1 : 0;
+	done = __shfl_sync(0xffffffffu, done, 0);
+	return done != 0;
+}
+
 // -- proxy / tcgen05 fences --------------------------------------------------------------------------------------
 // Makes this thread's generic-proxy shared-memory writes visible to the async proxy (tcgen05.mma operand reads).
 __device__ __forceinline__ void fence_proxy_async_smem()
@@ -148,6 +159,31 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v)
 	for(int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Same access pattern, issue only: 16 / 32 columns into r[]; tmem_ld_wait() must precede the first use of r[].
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t* r)
+{
+	asm volatile(
+		"tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+		  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+		: "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r)
+{
+	asm volatile(
+		"tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+		"%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+		  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+		  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+		  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+		: "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait()
+{
+	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // -- UMMA descriptors --------------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes (32 fp32) with the
 // 128-byte swizzle: 16-byte chunk c of row r lives at r*128 + ((c ^ (r & 7)) << 4); 8-row groups are 1024 B apart.
@@ -191,6 +227,67 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
 	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
 		::"r"(smem_u32(bar)) : "memory");
+}
+
+// -- TMA (bulk tensor copies driven by a CUtensorMap in kernel parameter space) ------------------------------------------
+// Arrive + announce `bytes` of pending TMA traffic on the barrier (one thread per phase).
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Tiled load of one box at element coordinates (x, y, z); x * 4 bytes must be a multiple of 16.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, uint64_t* bar, int x, int y, int z)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+		::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// im2col load from a channels-last image map (C, W, H, N): `pixelsPerColumn` output positions starting at the window
+// origin (w, h) of image n, channels [c, c + channelsPerPixel), filter tap offset (off_w, off_h) in input pixels.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst_smem, const void* tmap, uint64_t* bar, int c, int w,
+	int h, int n, uint16_t off_w, uint16_t off_h)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+		" [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+		::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+		  "h"(off_w), "h"(off_h) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_descriptor(const void* tmap)
+{
+	asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+
+// -- Ampere-style asynchronous copies (global -> shared, no registers held while in flight) ------------------------
+// 16-byte copy through L2 only; bytes beyond src_bytes (0..16) are written as zero.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, uint32_t src_bytes)
+{
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+// 4-byte copy; src_bytes is 4 or 0 (zero fill).
+__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src, uint32_t src_bytes)
+{
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+	asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// Arrives on the mbarrier once every cp.async issued so far by this thread has landed; the thread does not wait.
+// The arrival is one of the barrier's expected arrivals (.noinc).
+__device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar)
+{
+	asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Named barrier among `threads` threads of the CTA (id 1..15; id 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int threads)
+{
+	asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+template<int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+	asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 __device__ __forceinline__ float to_tf32(float x)

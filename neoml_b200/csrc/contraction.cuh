@@ -6,7 +6,7 @@
 
 namespace nb200 {
 
-enum { A_ROWS = 0, A_CONV_TAP = 1, A_CONV_ANY = 2 };
+enum { A_ROWS = 0, A_CONV_TAP = 1 };
 enum { B_ROWS = 0, B_COLS = 1 };
 
 struct ContractionParams {
@@ -19,12 +19,14 @@ struct ContractionParams {
 	int lda, ldb, ldc, ldr;
 	long long strideA, strideB, strideC; // per batch entry (gridDim.y)
 	int a_mode; // A_ROWS: element (m,k) at A[m*lda + k]
-	            // A_CONV_TAP: channels-last image gather, C % 32 == 0 (a 32-wide K block lies inside one filter tap)
-	            // A_CONV_ANY: channels-last image gather, any C (per-element tap arithmetic)
+	            // A_CONV_TAP: channels-last image gather, k = (r*S + s)*Cin + c; a_vec says whether Cin % 4 == 0 and the
+	            //             image is 16-byte aligned (then four consecutive k share a filter tap and move as 16 bytes)
 	int b_mode; // B_ROWS: element (n,k) at B[n*ldb + k];  B_COLS: element (n,k) at B[k*ldb + n]
 	int a_vec;  // 16-byte loads are legal for A (base and all row starts 16-byte aligned)
 	int b_vec;
 	int c_vec;  // 16-byte stores legal for C (and loads for residual)
+	int a_tma;  // A arrives by TMA (1: tiled rows, 2: im2col); the launcher decides, 0 = cp.async gather
+	int b_tma;  // B arrives by TMA (tiled rows)
 	// convolution geometry (a_mode != A_ROWS)
 	int H, W, Cin, Ho, Wo, S, padH, padW, strH, strW, dilH, dilW;
 	// epilogue
@@ -34,6 +36,10 @@ struct ContractionParams {
 	int precision;
 	int stages;
 	int* status;
+	// optional pipeline trace (debug aid): CTA 0 stores clock64() at [role * traceSteps + step]; nullptr = off
+	unsigned long long* trace;
+	int traceSteps;
+	int debugSkip; // debug aid, bit 0: issue no MMA, bit 1: converters move no data, bit 2: epilogue stores nothing
 };
 
 // Decodes output row m of a convolution into the image base offset and the top-left input coordinate.
@@ -89,6 +95,7 @@ __device__ __forceinline__ float gather_b(const ContractionParams& p, const floa
 		: __ldg(B + static_cast<size_t>(k) * p.ldb + n);
 }
 
+void set_contraction_trace(unsigned long long* buffer, int steps, int debugSkip);
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
 int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
 

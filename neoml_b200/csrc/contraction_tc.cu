@@ -1,19 +1,36 @@
 // Implicit-GEMM contraction on the 5th-generation tensor cores (tcgen05.mma kind::tf32, accumulators in TMEM).
 //
-// One CTA computes a 128 x BN tile of C.  Nine warps:
-//   warps 0-7  producers: gather 32-wide K blocks of A (128 rows) and B (BN rows) straight from global memory
-//              (no im2col matrix exists anywhere), split every value into a TF32 "hi" and a TF32 "lo" part,
-//              and store both into the 128-byte-swizzled K-major shared-memory layout the MMA reads.
-//              After the main loop the same warps are the epilogue: tcgen05.ld -> bias/residual/activation -> global.
-//   warp 8     allocates TMEM, and one elected lane issues the MMAs: per 8-wide K step lo*hi, hi*lo, hi*hi
-//              (3xTF32; the lo*lo term is below fp32 resolution) or hi*hi only (plain TF32).
-//              The two cross terms go to their own TMEM accumulator: the tensor core truncates on every
-//              accumulate, so the main accumulator should take one add per K step, not three; the epilogue adds
-//              the small accumulator to the main one in fp32.
-// Stage hand-over is by mbarriers: full[s] (256 producer arrivals, after a generic->async proxy fence) and
-// empty[s] (tcgen05.commit).  Every wait is bounded; on timeout the CTA raises an abort flag, records the site in
-// the device status word and falls through to the common teardown that frees TMEM.
+// Persistent kernel: one CTA per SM walks the 128 x BN output tiles (tile = blockIdx.x + i * gridDim.x, the N tile
+// index fastest so that CTAs running together share the same rows of A in L2).  Sixteen warps (four per SM sub-partition, so every thread may hold 128 registers), four roles:
+//   warps 0-1   copy.  Every 32-wide K block of A (128 rows) and B (BN rows) is gathered straight from global memory
+//               (no im2col matrix exists anywhere) by asynchronous copies (cp.async, zero-fill for padding and
+//               tails) into a ring of "raw" shared-memory slots laid out in the 128-byte-swizzled K-major format
+//               the MMA reads.  The copy warps never wait for data: a slot's completion is signalled by
+//               cp.async.mbarrier.arrive, and they run as many slots ahead as the ring holds, which is what keeps
+//               ~100 KB per SM in flight without holding registers.  Operands that are a plain box of a tensor
+//               (row-major A and B with 16-byte-aligned rows) or an im2col column block of a channels-last image
+//               with C % 32 == 0 are loaded by TMA instead: thread 0 issues one cp.async.bulk.tensor per operand
+//               tile and announces the bytes on the same barrier.  The cp.async gather remains for everything TMA
+//               cannot describe (4-byte-aligned handles, column-major B, odd channel counts).
+//   warps 4-7   convert.  3xTF32: the tensor core reads an fp32 word as TF32 by ignoring the low 13 mantissa bits,
+//               so a raw slot *is* the "hi" operand; these warps form lo = x - trunc_tf32(x) (exact in fp32) into a
+//               2-deep ring of "lo" slots.  Plain TF32: they round the raw slot to nearest TF32 in place.
+//   warp 2      allocates TMEM; one lane issues the MMAs: per 8-wide K step lo*hi, hi*lo (into a "cross"
+//               accumulator) and hi*hi (into the main accumulator) for 3xTF32, hi*hi only for plain TF32.
+//               The tensor core truncates on every accumulate, so the main accumulator takes one add per K step,
+//               not three; the lo*lo term is below fp32 resolution and is dropped.
+//   warps 8-15  epilogue: each warp owns 32 rows x BN/2 columns.  It prefetches its residual block into L2 before it
+//               waits for the accumulators, then per 16 columns: tcgen05.ld (main + cross) -> shared-memory
+//               transpose -> bias / residual (loaded one chunk ahead) / activation -> coalesced 16-byte stores.  With two
+//               accumulator sets in TMEM (when 4 x BN columns fit in 512) the epilogue of tile i overlaps the main
+//               loop of tile i+1.
+// Hand-over is by mbarriers: rawFull[r] (64 cp.async arrivals + the TMA issuer's expect_tx), cvtFull[.] (128 converter arrivals after a
+// generic->async proxy fence), rawEmpty[r] / loEmpty[l] / accFull[b] (tcgen05.commit), accEmpty[b] (256 epilogue
+// arrivals).  Every wait is bounded; on timeout the CTA raises an abort flag, records the site in the device status
+// word and every role falls through to the common teardown that frees TMEM.
 #include "contraction.cuh"
+#include <cuda.h>
+#include <string.h>
 
 namespace nb200 {
 
@@ -21,16 +38,24 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 32;                 // floats per K block = one 128-byte swizzle row
-constexpr int PRODUCER_THREADS = 256;
-constexpr int THREADS = PRODUCER_THREADS + 32;
+constexpr int COPY_WARPS = 2;
+constexpr int COPY_THREADS = COPY_WARPS * 32;
+constexpr int MMA_WARP = 2;            // warp 3 is a spare that goes straight to the final barrier
+constexpr int CVT_WARP0 = 4;
+constexpr int CVT_WARPS = 4;
+constexpr int CVT_THREADS = CVT_WARPS * 32;
+constexpr int EPI_WARP0 = CVT_WARP0 + CVT_WARPS;
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int THREADS = (EPI_WARP0 + EPI_WARPS) * 32;
 constexpr int A_TILE_BYTES = BM * BK * 4; // 16 KB
+constexpr int STAGING_BYTES_PER_WARP = 32 * 64; // 32 rows x 16 floats
+constexpr int LO_SLOTS = 2;
+constexpr int MAX_RAW_SLOTS = 8;
 
-enum { SITE_EMPTY = 0x101, SITE_FULL = 0x102, SITE_ACCUM = 0x103, SITE_DRAIN = 0x104 };
-
-template<int BN>
-struct Frag {
-	float4 a[BM / 32];
-	float4 b[BN / 32];
+enum {
+	SITE_RAW_EMPTY = 0x101, SITE_RAW_FULL = 0x102, SITE_CVT_FULL = 0x103, SITE_LO_EMPTY = 0x104,
+	SITE_ACC_FULL = 0x105, SITE_ACC_EMPTY = 0x106
 };
 
 __device__ __forceinline__ float4 ldg4(const float* p)
@@ -38,335 +63,608 @@ __device__ __forceinline__ float4 ldg4(const float* p)
 	return __ldg(reinterpret_cast<const float4*>(p));
 }
 
-// Loads 4 consecutive K elements [k, k+4) of a row-addressed operand (element (row,k) at base + k).
-__device__ __forceinline__ float4 load_row4(const float* rowPtr, int k, int K, bool vec)
+// byte offset of 16-byte chunk `chunk` of row `row` inside a 128-byte-swizzled K-major tile
+__device__ __forceinline__ uint32_t swz(int row, int chunk)
 {
-	float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-	if(rowPtr == nullptr || k >= K) return v;
-	if(vec && k + 4 <= K) return ldg4(rowPtr + k);
-	v.x = __ldg(rowPtr + k);
-	if(k + 1 < K) v.y = __ldg(rowPtr + k + 1);
-	if(k + 2 < K) v.z = __ldg(rowPtr + k + 2);
-	if(k + 3 < K) v.w = __ldg(rowPtr + k + 3);
-	return v;
+	return static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
 }
 
-__device__ __forceinline__ void split_store(uint8_t* hiTile, uint8_t* loTile, int row, int chunk, float4 v, bool threeX)
+// debug aid: per-role time stamps of the first traceSteps K-block steps of CTA 0
+enum { TR_COPY_ISSUED = 0, TR_RAW_FULL = 1, TR_CVT_DONE = 2, TR_MMA_ISSUED = 3, TR_COPY_SLOT_FREE = 4, TR_COPY_A_DONE = 5, TR_COPY_B_DONE = 6,
+	TR_EPI_ACC_FULL = 7, TR_EPI_TMEM_READ = 8, TR_EPI_TILE_DONE = 9, TR_MMA_TILE_COMMITTED = 10, TR_ROLES = 11 }; // 7..10 are per tile
+__device__ __forceinline__ void trace(const ContractionParams& p, int role, int step)
 {
-	const uint32_t off = static_cast<uint32_t>(row) * 128u + (static_cast<uint32_t>(chunk ^ (row & 7)) << 4);
-	float4 hi;
-	hi.x = to_tf32(v.x); hi.y = to_tf32(v.y); hi.z = to_tf32(v.z); hi.w = to_tf32(v.w);
-	*reinterpret_cast<float4*>(hiTile + off) = hi;
-	if(threeX) {
-		float4 lo;
-		lo.x = to_tf32(v.x - hi.x); lo.y = to_tf32(v.y - hi.y); lo.z = to_tf32(v.z - hi.z); lo.w = to_tf32(v.w - hi.w);
-		*reinterpret_cast<float4*>(loTile + off) = lo;
-	}
+	if(p.trace != nullptr && blockIdx.x == 0 && step < p.traceSteps) p.trace[role * p.traceSteps + step] = clock64();
+}
+
+struct TileCoord {
+	int m0, n0, batch;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int nTiles, int tilesPerBatch, int bn)
+{
+	TileCoord t;
+	t.batch = tile / tilesPerBatch;
+	const int r = tile - t.batch * tilesPerBatch;
+	const int mTile = r / nTiles;
+	t.m0 = mTile * BM;
+	t.n0 = (r - mTile * nTiles) * bn;
+	return t;
 }
 
 template<int BN>
-__global__ void __launch_bounds__(THREADS, 1) contraction_tc_kernel(const ContractionParams p)
+__global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p, int numTiles, int nTiles,
+	int tilesPerBatch, int rawSlots, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB)
 {
 	extern __shared__ uint8_t smem_raw[];
-	// the swizzle pattern is a function of the absolute shared-memory address: tiles must start on 1024 B
-	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-
 	// once any CTA on this device has given up on a wait, later CTAs do not start: a broken pipeline must not
 	// cost two seconds per tile
 	if(*reinterpret_cast<volatile int*>(p.status) != 0) return;
 
+	// the swizzle pattern is a function of the absolute shared-memory address: tiles must start on 1024 B
+	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+
 	const bool threeX = p.precision == NB200_PREC_3XTF32;
 	constexpr int B_TILE_BYTES = BN * BK * 4;
-	const int stageBytes = (A_TILE_BYTES + B_TILE_BYTES) * (threeX ? 2 : 1);
-	const int stages = p.stages;
+	constexpr int SLOT_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 
-	uint64_t* fullBar = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * stageBytes);
-	uint64_t* emptyBar = fullBar + stages;
-	uint64_t* accumBar = emptyBar + stages;
-	uint64_t* drainBar = accumBar + 1;
-	uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(drainBar + 1);
+	constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); // power of two
+	const uint32_t accStride = threeX ? 2 * ACC_COLS : ACC_COLS;  // main [+ cross] accumulator of one set
+	const int accSets = 2 * accStride <= 512 ? 2 : 1;
+	const uint32_t tmemCols = accStride * accSets;                   // 32 .. 512, a power of two
+
+	uint8_t* rawRing = smem;
+	uint8_t* loRing = rawRing + static_cast<size_t>(rawSlots) * SLOT_BYTES;
+	uint8_t* staging = loRing + (threeX ? LO_SLOTS * SLOT_BYTES : 0);
+	uint64_t* rawFullBar = reinterpret_cast<uint64_t*>(staging + EPI_WARPS * STAGING_BYTES_PER_WARP + EPI_WARPS * 256);
+	uint64_t* rawEmptyBar = rawFullBar + MAX_RAW_SLOTS;
+	uint64_t* cvtFullBar = rawEmptyBar + MAX_RAW_SLOTS;
+	uint64_t* loEmptyBar = cvtFullBar + MAX_RAW_SLOTS;
+	uint64_t* accFullBar = loEmptyBar + LO_SLOTS;
+	uint64_t* accEmptyBar = accFullBar + 2;
+	uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmptyBar + 2);
 	volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
 	const int tid = threadIdx.x;
 	const int warp = tid >> 5;
 	const int lane = tid & 31;
-
-	const int nTiles = (p.N + BN - 1) / BN;
-	const int tileId = blockIdx.x;
-	const int nTile = tileId % nTiles;
-	const int mTile = tileId / nTiles;
-	const int m0 = mTile * BM;
-	const int n0 = nTile * BN;
-	const int batch = blockIdx.y;
-	const float* __restrict__ A = p.A + batch * p.strideA;
-	const float* __restrict__ B = p.B + batch * p.strideB;
-	float* __restrict__ C = p.C + batch * p.strideC;
-	const float* __restrict__ R = p.residual != nullptr ? p.residual + batch * p.strideC : nullptr;
-
 	const int numKb = (p.K + BK - 1) / BK;
-	constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); // power of two
-	const uint32_t tmemCols = threeX ? 2 * ACC_COLS : ACC_COLS; // main accumulator [+ cross-term accumulator]
+	const int myTiles = blockIdx.x < numTiles ? (numTiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+	const int totalSteps = myTiles * numKb;
 
 	if(tid == 0) {
-		for(int s = 0; s < stages; ++s) {
-			mbar_init(&fullBar[s], PRODUCER_THREADS);
-			mbar_init(&emptyBar[s], 1);
+		for(int s = 0; s < MAX_RAW_SLOTS; ++s) {
+			mbar_init(&rawFullBar[s], COPY_THREADS + 1); // every copy thread's cp.async arrival + the TMA issuer's expect_tx
+			mbar_init(&rawEmptyBar[s], 1);
+			mbar_init(&cvtFullBar[s], CVT_THREADS);
 		}
-		mbar_init(accumBar, 1);
-		mbar_init(drainBar, 1);
+		for(int s = 0; s < LO_SLOTS; ++s) mbar_init(&loEmptyBar[s], 1);
+		for(int b = 0; b < 2; ++b) {
+			mbar_init(&accFullBar[b], 1);
+			mbar_init(&accEmptyBar[b], EPI_THREADS);
+		}
 		*abortFlag = 0;
 		mbar_init_fence();
 	}
-	if(warp == 8) {
+	if(warp == MMA_WARP) {
 		tmem_alloc(tmemSlot, tmemCols);
 		tmem_relinquish();
+	}
+	if(tid == 0) {
+		if(p.a_tma) tma_prefetch_descriptor(&mapA);
+		if(p.b_tma) tma_prefetch_descriptor(&mapB);
 	}
 	tc_fence_before_sync();
 	__syncthreads();
 	tc_fence_after_sync();
 	const uint32_t tmemBase = *tmemSlot;
 
-	if(warp < 8) {
-		// ------------------------------------------------------------------ producers
-		// (row, chunk) ownership: a thread always handles 16-byte chunk `chunk` of rows row0, row0+32, ...
-		int aRow0, aChunk, bRow0, bChunk;
-		aRow0 = tid >> 3; aChunk = tid & 7;
-		if(p.b_mode == B_ROWS) { bRow0 = tid >> 3; bChunk = tid & 7; } else { bRow0 = tid & 31; bChunk = tid >> 5; }
-
-		const float* aPtr[BM / 32];
-		ConvRow aConv[BM / 32];
-#pragma unroll
-		for(int i = 0; i < BM / 32; ++i) {
-			const int m = m0 + aRow0 + 32 * i;
-			aPtr[i] = nullptr;
-			aConv[i].base = -1; aConv[i].iy0 = 0; aConv[i].ix0 = 0;
-			if(p.a_mode == A_ROWS) {
-				if(m < p.M) aPtr[i] = A + static_cast<size_t>(m) * p.lda;
-			} else {
-				aConv[i] = conv_row(p, m);
-			}
-		}
-		const float* bPtr[BN / 32];
-#pragma unroll
-		for(int j = 0; j < BN / 32; ++j) {
-			const int n = n0 + bRow0 + 32 * j;
-			bPtr[j] = nullptr;
-			if(n < p.N) bPtr[j] = p.b_mode == B_ROWS ? B + static_cast<size_t>(n) * p.ldb : B + n;
-		}
-
-		auto load = [&](int kb, Frag<BN>& f) {
-			const int kA = kb * BK + aChunk * 4;
-			if(p.a_mode == A_ROWS) {
-#pragma unroll
-				for(int i = 0; i < BM / 32; ++i) f.a[i] = load_row4(aPtr[i], kA, p.K, p.a_vec != 0);
-			} else if(p.a_mode == A_CONV_TAP) {
-				const int k0 = kb * BK;
-				const int tap = k0 / p.Cin;
-				const int c0 = k0 - tap * p.Cin + aChunk * 4;
-				const int r = tap / p.S;
-				const int s = tap - r * p.S;
-				const int dy = r * p.dilH, dx = s * p.dilW;
-#pragma unroll
-				for(int i = 0; i < BM / 32; ++i) {
-					const int iy = aConv[i].iy0 + dy, ix = aConv[i].ix0 + dx;
-					const bool ok = aConv[i].base >= 0 && static_cast<unsigned>(iy) < static_cast<unsigned>(p.H)
-						&& static_cast<unsigned>(ix) < static_cast<unsigned>(p.W);
-					f.a[i] = ok ? ldg4(A + aConv[i].base + (iy * p.W + ix) * p.Cin + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
-				}
-			} else {
-#pragma unroll
-				for(int i = 0; i < BM / 32; ++i) {
-					const int m = m0 + aRow0 + 32 * i;
-					f.a[i].x = gather_a(p, A, aConv[i], m, kA);
-					f.a[i].y = gather_a(p, A, aConv[i], m, kA + 1);
-					f.a[i].z = gather_a(p, A, aConv[i], m, kA + 2);
-					f.a[i].w = gather_a(p, A, aConv[i], m, kA + 3);
-				}
-			}
-			const int kB = kb * BK + bChunk * 4;
-			if(p.b_mode == B_ROWS) {
-#pragma unroll
-				for(int j = 0; j < BN / 32; ++j) f.b[j] = load_row4(bPtr[j], kB, p.K, p.b_vec != 0);
-			} else {
-#pragma unroll
-				for(int j = 0; j < BN / 32; ++j) {
-					float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-					if(bPtr[j] != nullptr) {
-						const float* q = bPtr[j] + static_cast<size_t>(kB) * p.ldb;
-						if(kB < p.K) v.x = __ldg(q);
-						if(kB + 1 < p.K) v.y = __ldg(q + p.ldb);
-						if(kB + 2 < p.K) v.z = __ldg(q + 2 * static_cast<size_t>(p.ldb));
-						if(kB + 3 < p.K) v.w = __ldg(q + 3 * static_cast<size_t>(p.ldb));
-					}
-					f.b[j] = v;
-				}
-			}
-		};
-
-		auto store = [&](int stage, const Frag<BN>& f) {
-			uint8_t* base = smem + static_cast<size_t>(stage) * stageBytes;
-			uint8_t* aHi = base;
-			uint8_t* aLo = base + A_TILE_BYTES;
-			uint8_t* bHi = base + (threeX ? 2 : 1) * A_TILE_BYTES;
-			uint8_t* bLo = bHi + B_TILE_BYTES;
-#pragma unroll
-			for(int i = 0; i < BM / 32; ++i) split_store(aHi, aLo, aRow0 + 32 * i, aChunk, f.a[i], threeX);
-#pragma unroll
-			for(int j = 0; j < BN / 32; ++j) split_store(bHi, bLo, bRow0 + 32 * j, bChunk, f.b[j], threeX);
-		};
-
-		Frag<BN> cur, nxt;
+	if(warp < COPY_WARPS) {
+		// ------------------------------------------------------------------ copy
+		// piece ownership: chunk tid%8 of rows tid/8 + 8*q.  Column-major B ([k][n]): consecutive lanes take
+		// consecutive n so that each 4-byte copy is coalesced: rows tid%32 + 32*(q/4), chunks tid/32 + 2*(q%4).
+		constexpr int A_PIECES = BM / 8, B_PIECES = BN / 8;
+		const int row0 = tid >> 3, chunk0 = tid & 7;
+		const bool bCols = p.b_mode != B_ROWS;
+		const bool aVec = p.a_vec != 0, bVec = p.b_vec != 0;
+		const bool conv = p.a_mode != A_ROWS;
+		int tile = blockIdx.x;
+		int step = 0;
 		bool ok = true;
-		load(0, cur);
-		for(int kb = 0; kb < numKb; ++kb) {
-			if(kb + 1 < numKb) load(kb + 1, nxt);
-			const int stage = kb % stages;
-			const uint32_t parity = ((kb / stages) & 1) ^ 1;
-			if(!mbar_wait_bounded(&emptyBar[stage], parity, abortFlag, p.status, SITE_EMPTY)) { ok = false; break; }
-			store(stage, cur);
-			fence_proxy_async_smem();
-			mbar_arrive(&fullBar[stage]);
-			cur = nxt;
-		}
-
-		// ------------------------------------------------------------------ epilogue
-		if(ok) ok = mbar_wait_bounded(accumBar, 0, abortFlag, p.status, SITE_ACCUM);
-		if(ok) {
-			tc_fence_after_sync();
-			const int quad = warp & 3;
-			const int half = warp >> 2;
-			const int m = m0 + quad * 32 + lane;
-			constexpr int COLS_PER_HALF = BN / 2;
-			float* cRow = C + static_cast<size_t>(m) * p.ldc;
-			const float* rRow = R != nullptr ? R + static_cast<size_t>(m) * p.ldr : nullptr;
-#pragma unroll 1
-			for(int cc = 0; cc < COLS_PER_HALF; cc += 16) {
-				const int col = half * COLS_PER_HALF + cc;
-				float v[16];
-				// every lane of the warp must take part in the TMEM load, in range or not
-				const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(col);
-				tmem_ld16(taddr, v);
-				if(threeX) {
-					float x[16];
-					tmem_ld16(taddr + ACC_COLS, x);
+		for(int local = 0; local < myTiles && ok; ++local, tile += gridDim.x) {
+			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
+			const float* A = p.A + tc.batch * p.strideA;
+			const float* B = p.B + tc.batch * p.strideB;
+			// where this thread's rows start: an element offset into A (row-major) or the image origin (convolution)
+			ConvRow aRow[A_PIECES];
 #pragma unroll
-					for(int i = 0; i < 16; ++i) v[i] += x[i];
+			for(int i = 0; i < (p.a_tma ? 0 : A_PIECES); ++i) {
+				const int m = tc.m0 + row0 + 8 * i;
+				if(conv) {
+					aRow[i] = conv_row(p, m);
+				} else {
+					aRow[i].base = m < p.M ? m * p.lda : -1;
+					aRow[i].iy0 = aRow[i].ix0 = 0;
 				}
-				const int n = n0 + col;
-				if(m < p.M && n < p.N) {
+			}
+			for(int kb = 0; kb < numKb; ++kb, ++step) {
+				const int slot = step % rawSlots;
+				const uint32_t parity = ((step / rawSlots) & 1) ^ 1;
+				if(!mbar_wait_bounded_warp(&rawEmptyBar[slot], parity, abortFlag, p.status, SITE_RAW_EMPTY)) { ok = false; break; }
+				if(tid == 0) trace(p, TR_COPY_SLOT_FREE, step);
+				const uint32_t aTile = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES);
+				const uint32_t bTile = aTile + A_TILE_BYTES;
+				if(tid == 0) {
+					// operands that are plain boxes of a tensor (or im2col columns of an image) come by TMA: one
+					// instruction per tile, zero fill outside the tensor, completion counted in bytes on rawFull
+					const uint32_t bytes = (p.a_tma ? A_TILE_BYTES : 0) + (p.b_tma ? B_TILE_BYTES : 0);
+					mbar_arrive_expect_tx(&rawFullBar[slot], bytes);
+					if(p.a_tma == 1) {
+						tma_load_3d(aTile, &mapA, &rawFullBar[slot], kb * BK, tc.m0, tc.batch);
+					} else if(p.a_tma == 2) {
+						const int k0 = kb * BK;
+						const int tap = k0 / p.Cin;
+						const int r = tap / p.S;
+						const int s = tap - r * p.S;
+						const int hw = p.Ho * p.Wo;
+						const int n = tc.m0 / hw;
+						const int rem = tc.m0 - n * hw;
+						const int oy = rem / p.Wo;
+						const int ox = rem - oy * p.Wo;
+						tma_load_im2col_4d(aTile, &mapA, &rawFullBar[slot], k0 - tap * p.Cin, ox * p.strW - p.padW,
+							oy * p.strH - p.padH, n, static_cast<uint16_t>(s * p.dilW), static_cast<uint16_t>(r * p.dilH));
+					}
+					if(p.b_tma) tma_load_3d(bTile, &mapB, &rawFullBar[slot], kb * BK, tc.n0, tc.batch);
+				}
+				const int kA = kb * BK + chunk0 * 4;
+				const int kLeftA = p.K - kA; // elements of this chunk inside K: >= 4 full, 1..3 partial, <= 0 none
+				if(p.a_tma) {
+					// nothing to gather
+				} else if(!conv) {
 #pragma unroll
-					for(int q = 0; q < 4; ++q) {
-						const int nq = n + q * 4;
-						if(nq >= p.N) break;
-						float o[4] = { v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3] };
-						const bool full = nq + 4 <= p.N;
-						if(full && p.c_vec) {
-							if(p.bias != nullptr) {
-								const float4 bv = ldg4(p.bias + nq);
-								o[0] += bv.x; o[1] += bv.y; o[2] += bv.z; o[3] += bv.w;
-							}
-							if(rRow != nullptr) {
-								const float4 rv = *reinterpret_cast<const float4*>(rRow + nq);
-								o[0] += rv.x; o[1] += rv.y; o[2] += rv.z; o[3] += rv.w;
-							}
-#pragma unroll
-							for(int e = 0; e < 4; ++e) o[e] = apply_act(o[e], p.act, p.act_param);
-							if(p.accumulate) {
-								const float4 cv = *reinterpret_cast<const float4*>(cRow + nq);
-								o[0] += cv.x; o[1] += cv.y; o[2] += cv.z; o[3] += cv.w;
-							}
-							*reinterpret_cast<float4*>(cRow + nq) = make_float4(o[0], o[1], o[2], o[3]);
+					for(int i = 0; i < A_PIECES; ++i) {
+						const uint32_t dst = aTile + swz(row0 + 8 * i, chunk0);
+						const bool rowOk = aRow[i].base >= 0 && kLeftA > 0;
+						const float* src = rowOk ? A + aRow[i].base + kA : p.A;
+						if(aVec) {
+							cp_async16(dst, src, rowOk ? static_cast<uint32_t>(min(kLeftA, 4)) * 4u : 0u);
 						} else {
 #pragma unroll
 							for(int e = 0; e < 4; ++e) {
-								if(nq + e < p.N) {
-									float x = o[e];
-									if(p.bias != nullptr) x += __ldg(p.bias + nq + e);
-									if(rRow != nullptr) x += rRow[nq + e];
-									x = apply_act(x, p.act, p.act_param);
-									if(p.accumulate) x += cRow[nq + e];
-									cRow[nq + e] = x;
-								}
+								const bool eOk = rowOk && e < kLeftA;
+								cp_async4(dst + 4 * e, eOk ? src + e : p.A, eOk ? 4u : 0u);
 							}
 						}
 					}
+				} else if(aVec) {
+					// channels-last image, Cin % 4 == 0: the four K indices of a chunk share one filter tap
+					const int tap = kA / p.Cin;
+					const int c = kA - tap * p.Cin;
+					const int r = tap / p.S;
+					const int s = tap - r * p.S;
+					const int dy = r * p.dilH, dx = s * p.dilW;
+#pragma unroll
+					for(int i = 0; i < A_PIECES; ++i) {
+						const int iy = aRow[i].iy0 + dy, ix = aRow[i].ix0 + dx;
+						const bool pOk = kLeftA > 0 && aRow[i].base >= 0 && static_cast<unsigned>(iy) < static_cast<unsigned>(p.H)
+							&& static_cast<unsigned>(ix) < static_cast<unsigned>(p.W);
+						const float* src = pOk ? A + aRow[i].base + (iy * p.W + ix) * p.Cin + c : p.A;
+						cp_async16(aTile + swz(row0 + 8 * i, chunk0), src, pOk ? 16u : 0u);
+					}
+				} else {
+					// any channel count / alignment: the filter position (r, s, c) of the four K indices depends on k only,
+					// so it is decoded once per chunk and stepped; the rows differ in their image origin alone
+					int r[4], s[4], c[4];
+					{
+						const int sc = p.S * p.Cin;
+						int rr = kA / sc;
+						const int j = kA - rr * sc;
+						int ss = j / p.Cin;
+						int cc = j - ss * p.Cin;
+#pragma unroll
+						for(int e = 0; e < 4; ++e) {
+							r[e] = rr; s[e] = ss; c[e] = cc;
+							if(++cc == p.Cin) { cc = 0; if(++ss == p.S) { ss = 0; ++rr; } }
+						}
+					}
+#pragma unroll
+					for(int i = 0; i < A_PIECES; ++i) {
+						const uint32_t dst = aTile + swz(row0 + 8 * i, chunk0);
+#pragma unroll
+						for(int e = 0; e < 4; ++e) {
+							const int iy = aRow[i].iy0 + r[e] * p.dilH, ix = aRow[i].ix0 + s[e] * p.dilW;
+							const bool eOk = e < kLeftA && aRow[i].base >= 0 && static_cast<unsigned>(iy) < static_cast<unsigned>(p.H)
+								&& static_cast<unsigned>(ix) < static_cast<unsigned>(p.W);
+							cp_async4(dst + 4 * e, eOk ? A + aRow[i].base + (iy * p.W + ix) * p.Cin + c[e] : p.A, eOk ? 4u : 0u);
+						}
+					}
 				}
+				if(tid == 0) trace(p, TR_COPY_A_DONE, step);
+#pragma unroll
+				for(int j = 0; j < (p.b_tma ? 0 : B_PIECES); ++j) {
+					const int row = bCols ? (tid & 31) + 32 * (j >> 2) : row0 + 8 * j;
+					const int bChunk = bCols ? (tid >> 5) + 2 * (j & 3) : chunk0;
+					const int kB = kb * BK + bChunk * 4;
+					const int kLeftB = p.K - kB;
+					const uint32_t dst = bTile + swz(row, bChunk);
+					const bool rowOk = tc.n0 + row < p.N && kLeftB > 0;
+					if(!bCols) {
+						const float* src = rowOk ? B + static_cast<size_t>(tc.n0 + row) * p.ldb + kB : p.B;
+						if(bVec) {
+							cp_async16(dst, src, rowOk ? static_cast<uint32_t>(min(kLeftB, 4)) * 4u : 0u);
+						} else {
+#pragma unroll
+							for(int e = 0; e < 4; ++e) {
+								const bool eOk = rowOk && e < kLeftB;
+								cp_async4(dst + 4 * e, eOk ? src + e : p.B, eOk ? 4u : 0u);
+							}
+						}
+					} else {
+						// B stored [k][n]: four K-consecutive elements of column n are ldb apart
+						const float* src = B + static_cast<size_t>(kB) * p.ldb + tc.n0 + row;
+#pragma unroll
+						for(int e = 0; e < 4; ++e) {
+							const bool eOk = rowOk && e < kLeftB;
+							cp_async4(dst + 4 * e, eOk ? src + static_cast<size_t>(e) * p.ldb : p.B, eOk ? 4u : 0u);
+						}
+					}
+				}
+				if(tid == 0) trace(p, TR_COPY_B_DONE, step);
+				cp_async_arrive_on(&rawFullBar[slot]);
+				if(tid == 0) trace(p, TR_COPY_ISSUED, step);
 			}
 		}
-	} else {
-		// ------------------------------------------------------------------ MMA issuer (warp 8)
+		cp_async_wait<0>();
+	} else if(warp >= CVT_WARP0 && warp < EPI_WARP0) {
+		// ------------------------------------------------------------------ convert
+		constexpr int A_PIECES = BM / 16, B_PIECES = BN / 16;
+		const int ct = tid - CVT_WARP0 * 32;
+		const int row0 = ct >> 3, chunk0 = ct & 7;
+		bool ok = true;
+		for(int i = 0; i < totalSteps && ok; ++i) {
+			const int slot = i % rawSlots;
+			if(!mbar_wait_bounded_warp(&rawFullBar[slot], (i / rawSlots) & 1, abortFlag, p.status, SITE_RAW_FULL)) { ok = false; break; }
+			uint8_t* raw = rawRing + static_cast<size_t>(slot) * SLOT_BYTES;
+			if(ct == 0) trace(p, TR_RAW_FULL, i);
+			if(threeX) {
+				const int ls = i % LO_SLOTS;
+				if(!mbar_wait_bounded_warp(&loEmptyBar[ls], ((i / LO_SLOTS) & 1) ^ 1, abortFlag, p.status, SITE_LO_EMPTY)) { ok = false; break; }
+				uint8_t* lo = loRing + static_cast<size_t>(ls) * SLOT_BYTES;
+#pragma unroll
+				for(int q = 0; q < A_PIECES + B_PIECES && !(p.debugSkip & 2); ++q) {
+					const uint32_t off = q < A_PIECES ? swz(row0 + 16 * q, chunk0)
+						: static_cast<uint32_t>(A_TILE_BYTES) + swz(row0 + 16 * (q - A_PIECES), chunk0);
+					const float4 v = *reinterpret_cast<const float4*>(raw + off);
+					float4 l;
+					l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+					l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+					l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+					l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+					*reinterpret_cast<float4*>(lo + off) = l;
+				}
+				if(!(p.debugSkip & 8)) fence_proxy_async_smem();
+				mbar_arrive(&cvtFullBar[ls]);
+				if(ct == 0) trace(p, TR_CVT_DONE, i);
+			} else {
+				// plain TF32: round to nearest in place (the tensor core alone would truncate)
+#pragma unroll
+				for(int q = 0; q < A_PIECES + B_PIECES; ++q) {
+					const uint32_t off = q < A_PIECES ? swz(row0 + 16 * q, chunk0)
+						: static_cast<uint32_t>(A_TILE_BYTES) + swz(row0 + 16 * (q - A_PIECES), chunk0);
+					float4 v = *reinterpret_cast<const float4*>(raw + off);
+					v.x = to_tf32(v.x); v.y = to_tf32(v.y); v.z = to_tf32(v.z); v.w = to_tf32(v.w);
+					*reinterpret_cast<float4*>(raw + off) = v;
+				}
+				fence_proxy_async_smem();
+				mbar_arrive(&cvtFullBar[slot]);
+			}
+		}
+	} else if(warp == MMA_WARP) {
+		// ------------------------------------------------------------------ MMA issuer
 		if(lane == 0) {
 			const uint32_t idesc = umma_idesc_tf32(BM, BN);
 			bool ok = true;
-			for(int kb = 0; kb < numKb && ok; ++kb) {
-				const int stage = kb % stages;
-				const uint32_t parity = (kb / stages) & 1;
-				if(!mbar_wait_bounded(&fullBar[stage], parity, abortFlag, p.status, SITE_FULL)) { ok = false; break; }
+			int it = 0;
+			for(int local = 0; local < myTiles && ok; ++local) {
+				const int set = local % accSets;
+				const uint32_t accParity = ((local / accSets) & 1) ^ 1;
+				if(!mbar_wait_bounded(&accEmptyBar[set], accParity, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
 				tc_fence_after_sync();
-				const uint32_t base = smem_u32(smem + static_cast<size_t>(stage) * stageBytes);
-				const uint32_t aHi = base;
-				const uint32_t aLo = base + A_TILE_BYTES;
-				const uint32_t bHi = base + (threeX ? 2 : 1) * A_TILE_BYTES;
-				const uint32_t bLo = bHi + B_TILE_BYTES;
-				const int kLeft = p.K - kb * BK;
-				const int kSteps = kLeft >= BK ? BK / 8 : (kLeft + 7) / 8;
-				for(int ks = 0; ks < kSteps; ++ks) {
-					const uint32_t kOff = static_cast<uint32_t>(ks) * 32u; // 8 floats inside the 128-byte row
-					const uint64_t dAhi = umma_desc_k128(aHi + kOff);
-					const uint64_t dBhi = umma_desc_k128(bHi + kOff);
-					const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
-					if(threeX) {
-						const uint64_t dAlo = umma_desc_k128(aLo + kOff);
-						const uint64_t dBlo = umma_desc_k128(bLo + kOff);
-						umma_tf32_ss(tmemBase + ACC_COLS, dAlo, dBhi, idesc, acc);
-						umma_tf32_ss(tmemBase + ACC_COLS, dAhi, dBlo, idesc, 1u);
+				const uint32_t accMain = tmemBase + set * accStride;
+				const uint32_t accCross = accMain + ACC_COLS;
+				for(int kb = 0; kb < numKb; ++kb, ++it) {
+					const int slot = it % rawSlots;
+					const int ls = it % LO_SLOTS;
+					uint64_t* ready = threeX ? &cvtFullBar[ls] : &cvtFullBar[slot];
+					const uint32_t parity = threeX ? (it / LO_SLOTS) & 1 : (it / rawSlots) & 1;
+					if(!mbar_wait_bounded(ready, parity, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
+					tc_fence_after_sync();
+					const uint32_t aHi = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES);
+					const uint32_t bHi = aHi + A_TILE_BYTES;
+					const uint32_t aLo = smem_u32(loRing + static_cast<size_t>(ls) * SLOT_BYTES);
+					const uint32_t bLo = aLo + A_TILE_BYTES;
+					const int kLeft = p.K - kb * BK;
+					const int kSteps = kLeft >= BK ? BK / 8 : (kLeft + 7) / 8;
+					for(int ks = 0; ks < kSteps && !(p.debugSkip & 1); ++ks) {
+						const uint32_t kOff = static_cast<uint32_t>(ks) * 32u; // 8 floats inside the 128-byte row
+						const uint64_t dAhi = umma_desc_k128(aHi + kOff);
+						const uint64_t dBhi = umma_desc_k128(bHi + kOff);
+						const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
+						if(threeX) {
+							const uint64_t dAlo = umma_desc_k128(aLo + kOff);
+							const uint64_t dBlo = umma_desc_k128(bLo + kOff);
+							umma_tf32_ss(accCross, dAlo, dBhi, idesc, acc);
+							umma_tf32_ss(accCross, dAhi, dBlo, idesc, 1u);
+						}
+						umma_tf32_ss(accMain, dAhi, dBhi, idesc, acc);
 					}
-					umma_tf32_ss(tmemBase, dAhi, dBhi, idesc, acc);
+					umma_commit(&rawEmptyBar[slot]);
+					if(threeX) umma_commit(&loEmptyBar[ls]);
+					trace(p, TR_MMA_ISSUED, it);
 				}
-				umma_commit(&emptyBar[stage]);
+				if(ok) umma_commit(&accFullBar[set]);
+				trace(p, TR_MMA_TILE_COMMITTED, local);
 			}
-			if(ok) {
-				umma_commit(accumBar);
-			} else {
-				// something timed out: let whatever was issued finish before TMEM is freed
-				umma_commit(drainBar);
+			if(!ok) {
+				// something timed out: give whatever was issued time to finish before TMEM is freed
 				const uint64_t t0 = global_timer_ns();
-				while(!mbar_try_wait(drainBar, 0) && global_timer_ns() - t0 < WAIT_LIMIT_NS) {
+				while(global_timer_ns() - t0 < 1000000ull) {
 				}
 			}
 		}
 		__syncwarp();
+	} else if(warp >= EPI_WARP0) {
+		// ------------------------------------------------------------------ epilogue
+		constexpr int HALF_COLS = BN / 2;
+		constexpr int CHUNKS = HALF_COLS / 16;
+		const int ew = warp - EPI_WARP0;
+		const int quad = warp & 3;  // the TMEM lane quarter this warp may read
+		const int half = ew >> 2;   // which half of the tile's columns
+		uint8_t* stg = staging + ew * STAGING_BYTES_PER_WARP;
+		const int rowInGroup = lane >> 2;  // 0..7: which of the 8 rows a warp-wide 16-byte access covers
+		const int c4 = lane & 3;           // which 16-byte piece of the 64-byte row slice
+		const bool vec = p.c_vec != 0;
+		float* biasStrip = reinterpret_cast<float*>(staging + EPI_WARPS * STAGING_BYTES_PER_WARP) + ew * 64;
+		int biasCol = -1;
+		bool ok = true;
+		for(int local = 0; local < myTiles && ok; ++local) {
+			const int tile = blockIdx.x + local * gridDim.x;
+			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
+			float* __restrict__ C = p.C + tc.batch * p.strideC;
+			const float* __restrict__ R = p.residual != nullptr ? p.residual + tc.batch * p.strideC : nullptr;
+			const int set = local % accSets;
+			const uint32_t accParity = (local / accSets) & 1;
+			const int rowBase = tc.m0 + quad * 32;
+			const int colBase = tc.n0 + half * HALF_COLS;
+			const bool useRes = vec && R != nullptr;
+
+			auto load_res = [&](int ch, float4* dst) {
+				const int n = colBase + ch * 16 + c4 * 4;
+#pragma unroll
+				for(int i = 0; i < 4; ++i) {
+					const int m = rowBase + 8 * i + rowInGroup;
+					dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+					if(m < p.M && n + 4 <= p.N) dst[i] = *reinterpret_cast<const float4*>(R + static_cast<size_t>(m) * p.ldr + n);
+				}
+			};
+
+			// the bias values of this warp's columns sit in a per-warp shared-memory strip; it is reloaded only when the
+			// column range changes (a persistent CTA usually keeps its N tile), before the accumulators are awaited
+			if(colBase != biasCol) {
+				__syncwarp();
+				for(int j = lane; j < HALF_COLS; j += 32) {
+					const int n = colBase + j;
+					biasStrip[j] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.f;
+				}
+				biasCol = colBase;
+				__syncwarp();
+			}
+			float4 res[4], resNext[4];
+			if(useRes) {
+				// pull this warp's residual rows (HALF_COLS * 4 bytes each) towards L2 while the main loop of the tile runs
+				const int m = rowBase + lane;
+				if(m < p.M && colBase < p.N) {
+					const char* line = reinterpret_cast<const char*>(R + static_cast<size_t>(m) * p.ldr + colBase);
+					const int bytes = min(HALF_COLS, p.N - colBase) * 4;
+					for(int off = 0; off < bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(line + off));
+				}
+			}
+
+			if(!mbar_wait_bounded_warp(&accFullBar[set], accParity, abortFlag, p.status, SITE_ACC_FULL)) { ok = false; break; }
+			tc_fence_after_sync();
+			if(ew == 0 && lane == 0) trace(p, TR_EPI_ACC_FULL, local);
+			const uint32_t accMain = tmemBase + set * accStride + (static_cast<uint32_t>(quad * 32) << 16)
+				+ static_cast<uint32_t>(half * HALF_COLS);
+			if(useRes) load_res(0, res);
+
+			// accumulators leave TMEM in groups of up to 32 columns (main and cross issued together, one wait), each
+			// group then goes through the 16-column transpose / store passes
+#pragma unroll
+			for(int g0 = 0; g0 < CHUNKS; g0 += 2) {
+				const bool wide = g0 + 1 < CHUNKS; // 32 columns in this group, else 16
+				uint32_t vm[32], vx[32];
+				if(wide) {
+					tmem_ld32_issue(accMain + g0 * 16, vm);
+					if(threeX) tmem_ld32_issue(accMain + ACC_COLS + g0 * 16, vx);
+				} else {
+					tmem_ld16_issue(accMain + g0 * 16, vm);
+					if(threeX) tmem_ld16_issue(accMain + ACC_COLS + g0 * 16, vx);
+				}
+				tmem_ld_wait();
+				if(g0 + 2 >= CHUNKS) {
+					// last TMEM read of this tile: hand the accumulator set back to the MMA warp
+					tc_fence_before_sync();
+					mbar_arrive(&accEmptyBar[set]);
+					if(ew == 0 && lane == 0) trace(p, TR_EPI_TMEM_READ, local);
+				}
+#pragma unroll
+				for(int sub = 0; sub < 2; ++sub) {
+					const int ch = g0 + sub;
+					if(ch >= CHUNKS) break;
+					const int n = colBase + ch * 16 + c4 * 4; // first of this lane's four columns in the transposed phase
+					const bool colsFull = n + 4 <= p.N;
+					if(useRes && ch + 1 < CHUNKS) load_res(ch + 1, resNext);
+					float v[16];
+#pragma unroll
+					for(int i = 0; i < 16; ++i) {
+						v[i] = __uint_as_float(vm[sub * 16 + i]);
+						if(threeX) v[i] += __uint_as_float(vx[sub * 16 + i]);
+					}
+					// transpose through shared memory: row-per-lane -> 8 rows x 64 B per warp access
+#pragma unroll
+					for(int q = 0; q < 4; ++q) {
+						*reinterpret_cast<float4*>(stg + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+							make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+					}
+					__syncwarp();
+					const float4 bias4 = *reinterpret_cast<const float4*>(biasStrip + ch * 16 + c4 * 4);
+#pragma unroll
+					for(int i = 0; i < 4; ++i) {
+						const int r = 8 * i + rowInGroup;
+						const int m = rowBase + r;
+						float4 o = *reinterpret_cast<const float4*>(stg + r * 64 + ((c4 ^ ((r >> 1) & 3)) << 4));
+						if(m >= p.M || n >= p.N || (p.debugSkip & 4)) continue;
+						o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
+						float* dst = C + static_cast<size_t>(m) * p.ldc + n;
+						if(vec && colsFull) {
+							if(R != nullptr) { o.x += res[i].x; o.y += res[i].y; o.z += res[i].z; o.w += res[i].w; }
+							o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
+							o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
+							if(p.accumulate) {
+								const float4 cv = *reinterpret_cast<const float4*>(dst);
+								o.x += cv.x; o.y += cv.y; o.z += cv.z; o.w += cv.w;
+							}
+							*reinterpret_cast<float4*>(dst) = o;
+						} else {
+							const float e[4] = { o.x, o.y, o.z, o.w };
+#pragma unroll
+							for(int t = 0; t < 4; ++t) {
+								if(n + t < p.N) {
+									float x = e[t];
+									if(R != nullptr) x += R[static_cast<size_t>(m) * p.ldr + n + t];
+									x = apply_act(x, p.act, p.act_param);
+									if(p.accumulate) x += dst[t];
+									dst[t] = x;
+								}
+							}
+						}
+					}
+#pragma unroll
+					for(int i = 0; i < 4; ++i) res[i] = resNext[i];
+					__syncwarp(); // the staging slice is rewritten by the next column chunk
+				}
+			}
+			if(ew == 0 && lane == 0) trace(p, TR_EPI_TILE_DONE, local);
+		}
 	}
 
 	tc_fence_before_sync();
 	__syncthreads();
-	if(warp == 8) {
+	if(warp == MMA_WARP) {
 		tc_fence_after_sync();
 		tmem_dealloc(tmemBase, tmemCols);
 	}
 }
 
-template<int BN>
-int launch_bn(const ContractionParams& p, int batch, cudaStream_t stream)
+// ---- tensor maps ----------------------------------------------------------------------------------------------------
+// The driver entry points are fetched through the runtime so that this library does not link libcuda and still loads
+// on a machine without a driver.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+	const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+	CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+	const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+	CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encodeTiled = nullptr;
+EncodeIm2colFn g_encodeIm2col = nullptr;
+bool g_encodeLooked = false;
+
+void lookup_encoders()
 {
-	ContractionParams q = p;
+	if(g_encodeLooked) return;
+	g_encodeLooked = true;
+	void* fn = nullptr;
+	cudaDriverEntryPointQueryResult q;
+	if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess
+		&& q == cudaDriverEntryPointSuccess) {
+		g_encodeTiled = reinterpret_cast<EncodeTiledFn>(fn);
+	}
+	fn = nullptr;
+	if(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) == cudaSuccess
+		&& q == cudaDriverEntryPointSuccess) {
+		g_encodeIm2col = reinterpret_cast<EncodeIm2colFn>(fn);
+	}
+	cudaGetLastError();
+}
+
+// Row-addressed operand as a 3-D tensor (k fastest, then rows, then batch); box = 32 k x boxRows rows, 128-byte swizzle.
+bool make_rows_map(CUtensorMap* map, const float* base, int k, long long rows, long long ld, int batch,
+	long long batchStride, int boxRows)
+{
+	lookup_encoders();
+	if(g_encodeTiled == nullptr) return false;
+	if(!aligned16(base) || ld % 4 != 0 || (batch > 1 && batchStride % 4 != 0)) return false;
+	const cuuint64_t dims[3] = { static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch) };
+	const cuuint64_t strides[2] = { static_cast<cuuint64_t>(ld) * 4,
+		static_cast<cuuint64_t>(batch > 1 ? batchStride : rows * ld) * 4 };
+	if(strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
+	const cuuint32_t box[3] = { BK, static_cast<cuuint32_t>(boxRows), 1 };
+	const cuuint32_t elemStrides[3] = { 1, 1, 1 };
+	return g_encodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box,
+		elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Channels-last image (C, W, H, N) in im2col mode: a load delivers 128 consecutive output positions x 32 channels of
+// one filter tap; the window origins run over [-pad, dim + pad - (filter - 1) * dilation) with the convolution stride.
+bool make_im2col_map(CUtensorMap* map, const ContractionParams& p, int batchImages, int filterH)
+{
+	lookup_encoders();
+	if(g_encodeIm2col == nullptr) return false;
+	if(!aligned16(p.A) || p.Cin % BK != 0) return false;
+	const cuuint64_t dims[4] = { static_cast<cuuint64_t>(p.Cin), static_cast<cuuint64_t>(p.W), static_cast<cuuint64_t>(p.H),
+		static_cast<cuuint64_t>(batchImages) };
+	const cuuint64_t strides[3] = { static_cast<cuuint64_t>(p.Cin) * 4, static_cast<cuuint64_t>(p.W) * p.Cin * 4,
+		static_cast<cuuint64_t>(p.H) * p.W * p.Cin * 4 };
+	const int lower[2] = { -p.padW, -p.padH };
+	const int upper[2] = { p.padW - (p.S - 1) * p.dilW, p.padH - (filterH - 1) * p.dilH };
+	// hardware limits of the im2col descriptor: corners in [-128, 127], tap offsets below 256, strides up to 8
+	if(lower[0] < -128 || lower[1] < -128 || upper[0] < -128 || upper[1] < -128 || upper[0] > 127 || upper[1] > 127) return false;
+	if((p.S - 1) * p.dilW > 255 || (filterH - 1) * p.dilH > 255 || p.strW > 8 || p.strH > 8) return false;
+	const cuuint32_t elemStrides[4] = { 1, static_cast<cuuint32_t>(p.strW), static_cast<cuuint32_t>(p.strH), 1 };
+	return g_encodeIm2col(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(p.A), dims, strides, lower, upper,
+		BK, BM, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+		CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+unsigned long long* g_traceBuffer = nullptr;
+int g_traceSteps = 0;
+int g_debugSkip = 0;
+
+template<int BN>
+int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
+{
+	ContractionParams p = p0;
+	p.trace = g_traceBuffer;
+	p.traceSteps = g_traceSteps;
+	p.debugSkip = g_debugSkip;
 	const bool threeX = p.precision == NB200_PREC_3XTF32;
-	const int stageBytes = (A_TILE_BYTES + BN * BK * 4) * (threeX ? 2 : 1);
-	const int numKb = (p.K + BK - 1) / BK;
-	// as many stages as fit below ~200 KB, at most 6, at least 2, never more than the K blocks there are
-	int stages = (200 * 1024) / stageBytes;
-	if(stages > 6) stages = 6;
-	if(stages > numKb) stages = numKb;
-	if(stages < 2) stages = 2;
-	if(p.stages > 0) stages = p.stages;
-	q.stages = stages;
-	const size_t smemBytes = static_cast<size_t>(stages) * stageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+	const int slotBytes = A_TILE_BYTES + BN * BK * 4;
+	const int fixedBytes = EPI_WARPS * STAGING_BYTES_PER_WARP + EPI_WARPS * 256 /*bias strips*/ + 512 /*barriers*/ + 1024 /*alignment slack*/
+		+ (threeX ? LO_SLOTS * slotBytes : 0);
+	// as many raw slots as fit the 227 KB a CTA may use: the copies run that many K blocks ahead
+	int rawSlots = (227 * 1024 - fixedBytes) / slotBytes;
+	if(rawSlots > MAX_RAW_SLOTS) rawSlots = MAX_RAW_SLOTS;
+	if(p.stages > 1 && p.stages < rawSlots) rawSlots = p.stages;
+	if(rawSlots < 2) return NB200_ETOOBIG;
+	const size_t smemBytes = static_cast<size_t>(rawSlots) * slotBytes + fixedBytes;
 	// the attribute is per device; one engine per device may live in this process
 	static bool attrSet[64] = {};
 	int dev = 0;
 	if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NB200_ENODEVICE;
 	if(!attrSet[dev]) {
-		if(cudaFuncSetAttribute(contraction_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024)
+		if(cudaFuncSetAttribute(contraction_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
 			!= cudaSuccess) {
 			cudaGetLastError();
 			return NB200_ENODEVICE;
@@ -375,39 +673,60 @@ int launch_bn(const ContractionParams& p, int batch, cudaStream_t stream)
 	}
 	const long long mTiles = (static_cast<long long>(p.M) + BM - 1) / BM;
 	const long long nTiles = (p.N + BN - 1) / BN;
-	if(mTiles * nTiles > 0x7fffffffLL) return NB200_ETOOBIG;
-	for(int b0 = 0; b0 < batch; b0 += 65535) {
-		const int nb = batch - b0 < 65535 ? batch - b0 : 65535;
-		ContractionParams r = q;
-		r.A += b0 * q.strideA; r.B += b0 * q.strideB; r.C += b0 * q.strideC;
-		if(r.residual != nullptr) r.residual += b0 * q.strideC;
-		dim3 grid(static_cast<unsigned>(mTiles * nTiles), static_cast<unsigned>(nb), 1);
-		contraction_tc_kernel<BN><<<grid, THREADS, smemBytes, stream>>>(r);
-		count_launch();
+	const long long tilesPerBatch = mTiles * nTiles;
+	const long long numTiles = tilesPerBatch * batch;
+	if(numTiles > 0x7fffffffLL || numTiles * ((p.K + BK - 1) / BK) > 0x7fffffffLL) return NB200_ETOOBIG;
+	const int sms = sm_count();
+	const int grid = numTiles < sms ? static_cast<int>(numTiles) : sms;
+	// operands that TMA can describe are loaded by it; everything else (odd alignment, column-major B, channel counts
+	// that do not fill a 32-wide K block) is gathered with cp.async by the copy warps
+	alignas(64) CUtensorMap mapA, mapB;
+	memset(&mapA, 0, sizeof(mapA));
+	memset(&mapB, 0, sizeof(mapB));
+	p.a_tma = 0;
+	p.b_tma = 0;
+	if(!(g_debugSkip & 16)) {
+		if(p.a_mode == A_ROWS) {
+			if(p.a_vec && make_rows_map(&mapA, p.A, p.K, p.M, p.lda, batch, p.strideA, BM)) p.a_tma = 1;
+		} else if(p.a_vec && batch == 1) {
+			const int filterH = p.K / (p.S * p.Cin);
+			const int images = p.M / (p.Ho * p.Wo);
+			if(make_im2col_map(&mapA, p, images, filterH)) p.a_tma = 2;
+		}
+		if(p.b_mode == B_ROWS && p.b_vec && make_rows_map(&mapB, p.B, p.K, p.N, p.ldb, batch, p.strideB, BN)) p.b_tma = 1;
 	}
+	contraction_tc_kernel<BN><<<grid, THREADS, smemBytes, stream>>>(p, static_cast<int>(numTiles),
+		static_cast<int>(nTiles), static_cast<int>(tilesPerBatch), rawSlots, mapA, mapB);
+	count_launch();
 	return check_launch();
 }
 
 } // namespace
+
+void set_contraction_trace(unsigned long long* buffer, int steps, int debugSkip)
+{
+	g_traceBuffer = buffer;
+	g_traceSteps = steps;
+	g_debugSkip = debugSkip;
+}
 
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream)
 {
 	if(p.M <= 0 || p.N <= 0 || batch <= 0) return NB200_OK;
 	if(p.K <= 0) return NB200_EINVAL;
 	// tile width: least zero-padded columns over all tiles; ties go to the wider tile (fewer re-reads of A)
-	const int widths[5] = { 256, 192, 128, 64, 32 };
-	int best = 256;
+	const int widths[4] = { 128, 96, 64, 32 };
+	int best = 128;
 	long long bestPadded = -1;
-	for(int i = 0; i < 5; ++i) {
+	for(int i = 0; i < 4; ++i) {
 		const long long padded = (static_cast<long long>(p.N) + widths[i] - 1) / widths[i] * widths[i];
 		if(bestPadded < 0 || padded < bestPadded) { bestPadded = padded; best = widths[i]; }
 	}
 	switch(best) {
 		case 32: return launch_bn<32>(p, batch, stream);
 		case 64: return launch_bn<64>(p, batch, stream);
-		case 128: return launch_bn<128>(p, batch, stream);
-		case 192: return launch_bn<192>(p, batch, stream);
-		default: return launch_bn<256>(p, batch, stream);
+		case 96: return launch_bn<96>(p, batch, stream);
+		default: return launch_bn<128>(p, batch, stream);
 	}
 }
 

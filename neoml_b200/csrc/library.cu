@@ -67,10 +67,13 @@ int sm_count()
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 
+thread_local cudaError_t t_lastCudaError = cudaSuccess;
+
 int check_launch()
 {
 	const cudaError_t e = cudaGetLastError();
 	if(e == cudaSuccess) return NB200_OK;
+	t_lastCudaError = e;
 	return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? NB200_ENODEVICE : NB200_ELAUNCH;
 }
 
@@ -114,6 +117,8 @@ int nb200_device_status(void* stream, int reset)
 	}
 	return value;
 }
+
+const char* nb200_last_cuda_error(void) { return cudaGetErrorString(t_lastCudaError); }
 
 uint64_t nb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

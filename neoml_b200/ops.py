@@ -86,7 +86,7 @@ def MultiplyMatrixByMatrix(first, second, result=None, *, precision=PREC_3XTF32)
 
 
 def BlobConvolution(source, filter, free_term=None, result=None, *, padding=(0, 0), stride=(1, 1), dilation=(1, 1),
-                    residual=None, act=ACT_NONE, act_param=0.0, precision=PREC_3XTF32):
+                    residual=None, act=ACT_NONE, act_param=0.0, precision=PREC_3XTF32, use_scratch=True):
     n, h, w, c = source.shape
     k, r, s, c2 = filter.shape
     assert c == c2
@@ -97,8 +97,12 @@ def BlobConvolution(source, filter, free_term=None, result=None, *, padding=(0, 
     desc = capi.ConvDesc(n, h, w, c, k, r, s, padding[0], padding[1], stride[0], stride[1], dilation[0], dilation[1],
                          ho, wo)
     epi = _epilogue(free_term, residual, k, act, act_param)
-    capi.check("BlobConvolution", capi.load().nb200_blob_convolution(
-        _stream(), C.byref(desc), _ptr(_f32(source)), _ptr(_f32(filter)), _ptr(result), C.byref(epi), precision))
+    lib = capi.load()
+    need = lib.nb200_blob_convolution_scratch_floats(C.byref(desc)) if use_scratch else 0
+    scratch = torch.empty(need, dtype=torch.float32, device=source.device) if need else None
+    capi.check("BlobConvolution", lib.nb200_blob_convolution(
+        _stream(), C.byref(desc), _ptr(_f32(source)), _ptr(_f32(filter)), _ptr(result), _ptr(scratch), C.byref(epi),
+        precision))
     return result
 
 

@@ -1,5 +1,6 @@
-"""Test-side access to the checkers under oracle/: the plain-C oracle (always) and, where it has been built, the
-reference's own CPU math engine behind oracle/_ref/libref_shim.so.  numpy in, numpy out."""
+"""TEST INFRASTRUCTURE ONLY.  Python access to the checkers in this directory: the plain-C oracle (always) and,
+where it has been built, the reference's own CPU math engine behind _ref/libref_shim.so.  numpy in, numpy out.
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline / reference legs import this module."""
 from __future__ import annotations
 
 import ctypes as C
@@ -8,8 +9,8 @@ from pathlib import Path
 
 import numpy as np
 
-ROOT = Path(__file__).resolve().parent.parent
-ORACLE_DIR = ROOT / "oracle"
+ORACLE_DIR = Path(__file__).resolve().parent
+ROOT = ORACLE_DIR.parent
 
 _fp = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _ip = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")

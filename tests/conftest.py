@@ -4,7 +4,7 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-for p in (ROOT, ROOT / "tests", ROOT / "tests" / "golden"):
+for p in (ROOT, ROOT / "oracle", ROOT / "tests", ROOT / "tests" / "golden"):
     if str(p) not in sys.path:
         sys.path.insert(0, str(p))
 

@@ -13,6 +13,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent))
+sys.path.insert(0, str(HERE.parent.parent / "oracle"))
 sys.path.insert(0, str(HERE))
 
 import cases  # noqa: E402
