@@ -68,20 +68,29 @@ def build_kernels(verbose: bool = False) -> Path:
 
 
 def build_engine(verbose: bool = False) -> Path | None:
+    """g++ build of the IMathEngine implementation.  The class is generated/compiled against the NeoMathEngine headers
+    of a NeoML checkout; the base-class symbols (IMathEngine's key functions, the exception handler, CBlobDesc) stay
+    undefined in this library and bind at load time to the libNeoMathEngine.so of the hosting NeoML process."""
     ref = Path(os.environ.get("NEOML_REFERENCE_DIR", "/root/reference"))
     eng = ROOT / "engine"
     out = LIB / "libNeoMathEngineB200.so"
     sources = sorted(eng.glob("*.cpp"))
+    header = ref / "NeoMathEngine" / "include" / "NeoMathEngine" / "NeoMathEngine.h"
     if not sources:
         return None
-    if not (ref / "NeoMathEngine" / "include").exists():
+    if not header.exists():
         return out if out.exists() else None
-    deps = sorted(eng.glob("*.h")) + sorted(INCLUDE.glob("*.h"))
+    LIB.mkdir(exist_ok=True)
+    gen = OBJ / "engine_gen"
+    deps = sorted(eng.glob("*.h")) + sorted(eng.glob("*.py")) + sorted(INCLUDE.glob("*.h")) + [header]
     if out.exists() and not any(_newer(s, out, deps) for s in sources):
         return out
-    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-D_LINUX", "-DBUILD_NEOMATHENGINE",
-           f"-I{ref}/NeoMathEngine/include", f"-I{INCLUDE}", "-I/usr/local/cuda/include",
-           *map(str, sources), "-o", str(out),
+    r = subprocess.run([sys.executable, str(eng / "gen_stubs.py"), str(header), str(gen)], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"stub generation failed:\n{r.stdout}{r.stderr}")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-D_LINUX", "-w",
+           f"-I{ref}/NeoMathEngine/include", f"-I{INCLUDE}", f"-I{eng}", f"-I{gen}", "-I/usr/local/cuda/include",
+           *map(str, sources), str(gen / "B200MathEngineStubs.cpp"), "-o", str(out),
            f"-L{LIB}", "-lneoml_b200", "-L/usr/local/cuda/lib64", "-lcudart_static", "-ldl", "-lrt", "-lpthread",
            "-Wl,-rpath,$ORIGIN"]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,0 +1,152 @@
+// Distributed part of the engine API: CreateDistributedB200MathEngines, AllReduce (mean), Broadcast, AbortDistributed.
+// Semantics follow the reference's NCCL communicator (NeoMathEngine/src/GPU/CUDA/CudaMathEngineDnnDistributed.cpp:39-115):
+// one communicator per engine inside one process, AllReduce is an in-place fp32 AVERAGE, Broadcast sends from `root`.
+// The collectives run on the engine's own stream, so they are ordered with its kernels, and the call returns after the
+// stream has drained.  Inference is batch-sharded and uses none of this; the calls exist for the distributed-engine API.
+// NCCL is opened with dlopen when the first distributed engine is created (the reference does the same, NcclDll.cpp:17-55),
+// so a process that never distributes does not load it.
+#include "B200MathEngine.h"
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <atomic>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace NeoML {
+
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+enum { ncclSuccessCode = 0, ncclInProgressCode = 7 };
+enum { ncclFloat32 = 7 };
+enum { ncclSumOp = 0, ncclAvgOp = 4 };
+
+struct CNccl {
+	int ( *CommInitAll )( ncclComm_t*, int, const int* ) = nullptr;
+	int ( *CommDestroy )( ncclComm_t ) = nullptr;
+	int ( *CommAbort )( ncclComm_t ) = nullptr;
+	int ( *AllReduce )( const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t ) = nullptr;
+	int ( *Bcast )( const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t ) = nullptr;
+	int ( *CommGetAsyncError )( ncclComm_t, int* ) = nullptr;
+	void* lib = nullptr;
+
+	bool Load()
+	{
+		if( lib != nullptr ) return true;
+		lib = dlopen( "libnccl.so.2", RTLD_NOW | RTLD_LOCAL );
+		if( lib == nullptr ) lib = dlopen( "libnccl.so", RTLD_NOW | RTLD_LOCAL );
+		if( lib == nullptr ) return false;
+		CommInitAll = reinterpret_cast<decltype( CommInitAll )>( dlsym( lib, "ncclCommInitAll" ) );
+		CommDestroy = reinterpret_cast<decltype( CommDestroy )>( dlsym( lib, "ncclCommDestroy" ) );
+		CommAbort = reinterpret_cast<decltype( CommAbort )>( dlsym( lib, "ncclCommAbort" ) );
+		AllReduce = reinterpret_cast<decltype( AllReduce )>( dlsym( lib, "ncclAllReduce" ) );
+		Bcast = reinterpret_cast<decltype( Bcast )>( dlsym( lib, "ncclBroadcast" ) );
+		CommGetAsyncError = reinterpret_cast<decltype( CommGetAsyncError )>( dlsym( lib, "ncclCommGetAsyncError" ) );
+		return CommInitAll && CommDestroy && CommAbort && AllReduce && Bcast && CommGetAsyncError;
+	}
+};
+
+CNccl g_nccl;
+
+// shared by the engines of one distributed group: raised by AbortDistributed, seen by every waiting peer
+struct CGroupState {
+	std::atomic<bool> aborted{ false };
+};
+
+struct CCommHolder {
+	ncclComm_t comm;
+	std::shared_ptr<CGroupState> group;
+};
+
+void raise( const std::string& message )
+{
+	GetMathEngineExceptionHandler()->OnAssert( message.c_str(), L"B200Distributed", 0, 0 );
+}
+
+// Waits for the stream like the reference's ncclStreamSynchronize: polls the stream, the communicator's async error
+// and the group's abort flag, so a peer that failed on the host cannot leave this rank waiting forever.
+void waitCollective( cudaStream_t stream, CCommHolder* holder )
+{
+	while( true ) {
+		const cudaError_t q = cudaStreamQuery( stream );
+		if( q == cudaSuccess ) return;
+		if( q != cudaErrorNotReady ) { cudaGetLastError(); raise( "collective failed on the stream" ); return; }
+		int asyncError = ncclSuccessCode;
+		g_nccl.CommGetAsyncError( holder->comm, &asyncError );
+		if( asyncError != ncclSuccessCode && asyncError != ncclInProgressCode ) { raise( "NCCL reported an asynchronous error" ); return; }
+		if( holder->group->aborted.load() ) { raise( "Stopping due to error in another thread." ); return; }
+	}
+}
+
+} // namespace
+
+void CB200MathEngine::SetDistributedCommunicator( void* holder, const CMathEngineDistributedInfo& info )
+{
+	comm = holder;
+	distributedInfo = info;
+}
+
+void CB200MathEngine::AllReduce( const CFloatHandle& handle, int size )
+{
+	if( comm == nullptr ) return; // a single engine is its own average
+	CCommHolder* holder = static_cast<CCommHolder*>( comm );
+	setDevice();
+	float* data = raw( handle );
+	cudaStream_t s = static_cast<cudaStream_t>( stream );
+	if( g_nccl.AllReduce( data, data, static_cast<size_t>( size ), ncclFloat32, ncclAvgOp, holder->comm, s ) != ncclSuccessCode ) {
+		raise( "ncclAllReduce failed" );
+		return;
+	}
+	waitCollective( s, holder );
+}
+
+void CB200MathEngine::Broadcast( const CFloatHandle& handle, int size, int root )
+{
+	if( comm == nullptr ) return;
+	CCommHolder* holder = static_cast<CCommHolder*>( comm );
+	setDevice();
+	float* data = raw( handle );
+	cudaStream_t s = static_cast<cudaStream_t>( stream );
+	if( g_nccl.Bcast( data, data, static_cast<size_t>( size ), ncclFloat32, root, holder->comm, s ) != ncclSuccessCode ) {
+		raise( "ncclBroadcast failed" );
+		return;
+	}
+	waitCollective( s, holder );
+}
+
+void CB200MathEngine::AbortDistributed()
+{
+	if( comm == nullptr ) return;
+	CCommHolder* holder = static_cast<CCommHolder*>( comm );
+	holder->group->aborted.store( true );
+	g_nccl.CommAbort( holder->comm );
+}
+
+void CreateDistributedB200MathEngines( IMathEngine** mathEngines, int devsCount, const int* cudaDevs, size_t memoryLimit )
+{
+	for( int i = 0; i < devsCount; ++i ) mathEngines[i] = nullptr;
+	if( devsCount <= 0 ) return;
+	if( !g_nccl.Load() ) { raise( "libnccl.so.2 could not be loaded" ); return; }
+	std::vector<ncclComm_t> comms( devsCount );
+	if( g_nccl.CommInitAll( comms.data(), devsCount, cudaDevs ) != ncclSuccessCode ) { raise( "ncclCommInitAll failed" ); return; }
+	std::shared_ptr<CGroupState> group = std::make_shared<CGroupState>();
+	for( int i = 0; i < devsCount; ++i ) {
+		CB200MathEngine* engine = static_cast<CB200MathEngine*>( CreateB200MathEngine( cudaDevs[i], memoryLimit, 0 ) );
+		if( engine == nullptr ) { raise( "a distributed B200 engine could not be created" ); return; }
+		engine->SetDistributedCommunicator( new CCommHolder{ comms[i], group }, CMathEngineDistributedInfo( i, devsCount ) );
+		mathEngines[i] = engine;
+	}
+}
+
+} // namespace NeoML
+
+extern "C" __attribute__((visibility("default"))) int nb200_create_distributed_math_engines( void** engines, int count,
+	const int* devices, size_t memoryLimit )
+{
+	NeoML::CreateDistributedB200MathEngines( reinterpret_cast<NeoML::IMathEngine**>( engines ), count, devices, memoryLimit );
+	for( int i = 0; i < count; ++i ) if( engines[i] == nullptr ) return -1;
+	return 0;
+}

@@ -1,0 +1,306 @@
+// CB200MathEngine: lifecycle, memory, host<->device exchange, gauges, timing, factory.
+// Compute methods live in B200MathEngineOps.cpp; everything else on the interface is a generated weak stub.
+#include "B200MathEngine.h"
+
+#include <neoml_b200.h>
+
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+namespace NeoML {
+
+namespace {
+
+void raiseAssert( const std::string& message )
+{
+	GetMathEngineExceptionHandler()->OnAssert( message.c_str(), L"B200MathEngine", 0, 0 );
+}
+
+// Time-only counter that drains the engine's stream before reading the clock, so that CDnn's per-layer profile
+// (NeoML/src/Dnn/BaseLayer.cpp:469-497) measures device work and not launch time.
+class CB200PerformanceCounters : public IPerformanceCounters {
+public:
+	CB200PerformanceCounters( int _device, void* _stream ) : IPerformanceCounters( &counter ), device( _device ), stream( _stream )
+	{
+		counter.Name = "time ns";
+		counter.Value = 0;
+		CounterCount() = 1;
+		last = now();
+	}
+	void Synchronise() override
+	{
+		cudaSetDevice( device );
+		cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
+		const uint64_t t = now();
+		counter.Value = t - last;
+		last = t;
+	}
+
+private:
+	static uint64_t now()
+	{
+		return static_cast<uint64_t>( std::chrono::duration_cast<std::chrono::nanoseconds>(
+			std::chrono::steady_clock::now().time_since_epoch() ).count() );
+	}
+	CCounter counter;
+	const int device;
+	void* const stream;
+	uint64_t last;
+};
+
+} // namespace
+
+//---------------------------------------------------------------------------------------------------------------------
+
+CB200MathEngine::CB200MathEngine( int _device, size_t memoryLimit, int flags ) :
+	device( _device ),
+	precision( ( flags & GpuMathEngineCublasUseTensorCoresTF32Flag ) != 0 ? NB200_PREC_TF32 : NB200_PREC_3XTF32 ),
+	memory( _device, memoryLimit )
+{
+	if( nb200_device_count() <= 0 || cudaSetDevice( device ) != cudaSuccess ) {
+		cudaGetLastError();
+		return;
+	}
+	cudaStream_t s = nullptr;
+	if( cudaStreamCreateWithFlags( &s, cudaStreamNonBlocking ) != cudaSuccess ) {
+		cudaGetLastError();
+		return;
+	}
+	stream = s;
+	initialized = true;
+}
+
+CB200MathEngine::~CB200MathEngine()
+{
+	if( stream != nullptr ) {
+		cudaSetDevice( device );
+		cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
+		for( auto& b : hostBuffers ) cudaFreeHost( b.host );
+		cudaStreamDestroy( static_cast<cudaStream_t>( stream ) );
+	}
+}
+
+void CB200MathEngine::notImplemented( const char* method ) const
+{
+	raiseAssert( std::string( "CB200MathEngine::" ) + method + " is not implemented: it lies outside the inference hot path "
+		"this engine covers, and the engine has no CPU fallback" );
+}
+
+void CB200MathEngine::check( int code, const char* method ) const
+{
+	if( code == NB200_OK ) return;
+	std::string msg = std::string( "CB200MathEngine::" ) + method + ": " + nb200_error_string( code );
+	if( code == NB200_ELAUNCH || code == NB200_ENODEVICE ) msg += std::string( " (" ) + nb200_last_cuda_error() + ")";
+	raiseAssert( msg );
+}
+
+void CB200MathEngine::setDevice() const
+{
+	// any host thread may call any engine (the reference does the same at the top of every method,
+	// GPU/CUDA/CudaMathEngineDnnConv.cu:67)
+	cudaSetDevice( device );
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// identity
+
+TMathEngineType CB200MathEngine::GetType() const { return MET_Cuda; }
+
+void CB200MathEngine::GetMathEngineInfo( CMathEngineInfo& info ) const
+{
+	info = CMathEngineInfo( MET_Cuda, 0, device );
+	cudaDeviceProp prop;
+	if( cudaGetDeviceProperties( &prop, device ) == cudaSuccess ) {
+		std::snprintf( info.Name, sizeof( info.Name ), "%s (B200 engine)", prop.name );
+		info.AvailableMemory = prop.totalGlobalMem;
+	} else {
+		cudaGetLastError();
+	}
+}
+
+bool CB200MathEngine::IsInitialized() const { return initialized; }
+
+//---------------------------------------------------------------------------------------------------------------------
+// memory
+
+void CB200MathEngine::SetReuseMemoryMode( bool ) {} // blocks are always recycled on this engine
+bool CB200MathEngine::GetReuseMemoryMode() const { return true; }
+void CB200MathEngine::SetThreadBufferMemoryThreshold( size_t ) {}
+size_t CB200MathEngine::GetThreadBufferMemoryThreshold() const { return 0; }
+
+CMemoryHandle CB200MathEngine::HeapAlloc( size_t count )
+{
+	setDevice();
+	void* p = memory.Alloc( count );
+	if( p == nullptr ) {
+		GetMathEngineExceptionHandler()->OnMemoryError();
+		return CMemoryHandle();
+	}
+	return CMemoryHandleInternal::Create( this, p );
+}
+
+void CB200MathEngine::HeapFree( const CMemoryHandle& handle )
+{
+	if( handle.IsNull() ) return;
+	if( handle.GetMathEngine() != this ) { raiseAssert( "HeapFree: the handle belongs to another math engine" ); return; }
+	memory.Free( const_cast<void*>( CMemoryHandleInternal::Base( handle ) ) );
+}
+
+void CB200MathEngine::TransferHandleToThisThread( const CMemoryHandle&, size_t ) {} // heap blocks are not thread-bound here
+
+CMemoryHandle CB200MathEngine::StackAlloc( size_t count )
+{
+	setDevice();
+	void* p = memory.StackAlloc( count );
+	if( p == nullptr ) {
+		GetMathEngineExceptionHandler()->OnMemoryError();
+		return CMemoryHandle();
+	}
+	return CMemoryHandleInternal::Create( this, p );
+}
+
+void CB200MathEngine::StackFree( const CMemoryHandle& handle )
+{
+	if( handle.IsNull() ) return;
+	memory.StackFree( CMemoryHandleInternal::GetRaw( handle ) );
+}
+
+size_t CB200MathEngine::GetFreeMemorySize() const { return memory.FreeOnDevice(); }
+size_t CB200MathEngine::GetPeakMemoryUsage() const { return memory.Peak(); }
+void CB200MathEngine::ResetPeakMemoryUsage() { memory.ResetPeak(); }
+size_t CB200MathEngine::GetCurrentMemoryUsage() const { return memory.Current(); }
+size_t CB200MathEngine::GetMemoryInPools() const { return memory.InPools(); }
+
+void CB200MathEngine::CleanUp()
+{
+	setDevice();
+	if( stream != nullptr ) cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
+	memory.CleanUp();
+}
+
+void CB200MathEngine::CleanUpSpecial() {}
+
+//---------------------------------------------------------------------------------------------------------------------
+// exchange
+
+void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* source, size_t size )
+{
+	if( size == 0 ) return;
+	if( result.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
+	setDevice();
+	cudaStream_t s = static_cast<cudaStream_t>( stream );
+	if( cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), source, size, cudaMemcpyHostToDevice, s ) != cudaSuccess
+		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
+		raiseAssert( std::string( "DataExchangeRaw host->device: " ) + cudaGetErrorString( cudaGetLastError() ) );
+	}
+}
+
+void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source, size_t size )
+{
+	if( size == 0 ) return;
+	if( source.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
+	setDevice();
+	cudaStream_t s = static_cast<cudaStream_t>( stream );
+	if( cudaMemcpyAsync( result, CMemoryHandleInternal::GetRaw( source ), size, cudaMemcpyDeviceToHost, s ) != cudaSuccess
+		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
+		raiseAssert( std::string( "DataExchangeRaw device->host: " ) + cudaGetErrorString( cudaGetLastError() ) );
+	}
+	// a kernel that gave up on a bounded wait leaves its mark in the status word: surface it at the first sync point
+	const int status = nb200_device_status( stream, 1 );
+	if( status > 0 ) raiseAssert( "a B200 kernel reported a bounded-wait timeout (status " + std::to_string( status ) + ")" );
+}
+
+void* CB200MathEngine::GetBuffer( const CMemoryHandle& handle, size_t pos, size_t size, bool exchange )
+{
+	void* host = nullptr;
+	setDevice();
+	if( cudaMallocHost( &host, size == 0 ? 1 : size ) != cudaSuccess ) {
+		cudaGetLastError();
+		GetMathEngineExceptionHandler()->OnMemoryError();
+		return nullptr;
+	}
+	if( exchange && size > 0 ) {
+		const CMemoryHandle at = CMemoryHandleInternal::Create( this,
+			static_cast<const char*>( CMemoryHandleInternal::GetRaw( handle ) ) + pos );
+		DataExchangeRaw( host, at, size );
+	}
+	std::lock_guard<std::mutex> lock( hostMutex );
+	hostBuffers.push_back( { host, size, handle, pos } );
+	return host;
+}
+
+void CB200MathEngine::ReleaseBuffer( const CMemoryHandle& handle, void* ptr, bool exchange )
+{
+	CHostBuffer buf{};
+	{
+		std::lock_guard<std::mutex> lock( hostMutex );
+		if( hostBuffers.empty() || hostBuffers.back().host != ptr ) { raiseAssert( "ReleaseBuffer: buffers are released in LIFO order" ); return; }
+		buf = hostBuffers.back();
+		hostBuffers.pop_back();
+	}
+	if( exchange && buf.size > 0 ) {
+		const CMemoryHandle at = CMemoryHandleInternal::Create( this,
+			static_cast<const char*>( CMemoryHandleInternal::GetRaw( handle ) ) + buf.pos );
+		DataExchangeRaw( at, ptr, buf.size );
+	}
+	setDevice();
+	cudaFreeHost( ptr );
+}
+
+CMemoryHandle CB200MathEngine::CopyFrom( const CMemoryHandle& handle, size_t size )
+{
+	CMemoryHandle result = HeapAlloc( size );
+	if( result.IsNull() || size == 0 ) return result;
+	IMathEngine* other = handle.GetMathEngine();
+	if( other == this ) {
+		setDevice();
+		cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), CMemoryHandleInternal::GetRaw( handle ), size,
+			cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>( stream ) );
+		return result;
+	}
+	// through the host, like the reference (MemoryEngineMixin.cpp:218-226)
+	std::vector<char> staging( size );
+	other->DataExchangeRaw( staging.data(), handle, size );
+	DataExchangeRaw( result, staging.data(), size );
+	return result;
+}
+
+IPerformanceCounters* CB200MathEngine::CreatePerformanceCounters( bool ) const
+{
+	return new CB200PerformanceCounters( device, stream );
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// factory
+
+IMathEngine* CreateB200MathEngine( int deviceIndex, size_t memoryLimit, int flags )
+{
+	if( nb200_device_count() <= 0 ) return nullptr; // like CreateGpuMathEngine: null when no usable GPU exists
+	int count = 0;
+	if( cudaGetDeviceCount( &count ) != cudaSuccess ) { cudaGetLastError(); return nullptr; }
+	if( deviceIndex < 0 ) deviceIndex = 0;
+	if( deviceIndex >= count ) return nullptr;
+	CB200MathEngine* engine = new CB200MathEngine( deviceIndex, memoryLimit, flags );
+	if( !engine->IsInitialized() ) {
+		delete engine;
+		return nullptr;
+	}
+	return engine;
+}
+
+} // namespace NeoML
+
+// C entry points for hosts that load the engine library dynamically (ctypes, dlopen)
+extern "C" __attribute__((visibility("default"))) void* nb200_create_math_engine( int device, size_t memoryLimit, int flags )
+{
+	return NeoML::CreateB200MathEngine( device, memoryLimit, flags );
+}
+
+extern "C" __attribute__((visibility("default"))) void nb200_destroy_math_engine( void* engine )
+{
+	delete static_cast<NeoML::IMathEngine*>( engine );
+}

@@ -1,0 +1,128 @@
+// CB200MathEngine: a NeoML::IMathEngine for NVIDIA B200 (sm_100a).
+//
+// The class is compiled against the unmodified NeoMathEngine public headers of a NeoML checkout and is created
+// through a factory with the signature shape of the reference's GPU factory (NeoMathEngine.h:1282-1311).  Every
+// compute method is a thin translation of the NeoML call (handles, element counts, descriptors) into one call of the
+// C ABI in include/neoml_b200.h; there is no CPU fallback: methods outside the inference hot path raise
+// "not implemented" through the process-wide IMathEngineExceptionHandler.
+//
+// Execution model: one CUDA stream per engine, calls are enqueued in program order of the calling thread(s);
+// DataExchangeRaw / GetBuffer / perf-counter reads synchronise, exactly where the reference's blocking memcpy
+// (GPU/CUDA/CudaMathEngine.cpp:38-48) made results visible to the host.
+#pragma once
+
+#include <NeoMathEngine/NeoMathEngine.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <map>
+#include <mutex>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+namespace NeoML {
+
+// The public handle type keeps its fields protected and befriends a class of this name (MemoryHandle.h:47-50);
+// the reference defines it in a private header, an engine living outside that source tree defines its own.
+class CMemoryHandleInternal {
+public:
+	static void* GetRaw( const CMemoryHandle& h ) { return const_cast<char*>( static_cast<const char*>( h.Object ) ) + h.Offset; }
+	template<class T> static T* GetRaw( const CTypedMemoryHandle<T>& h ) { return static_cast<T*>( GetRaw( static_cast<const CMemoryHandle&>( h ) ) ); }
+	template<class T> static const T* GetRaw( const CTypedMemoryHandle<const T>& h ) { return static_cast<const T*>( GetRaw( static_cast<const CMemoryHandle&>( h ) ) ); }
+	static CMemoryHandle Create( IMathEngine* engine, const void* object ) { return CMemoryHandle( engine, object, 0 ); }
+	static const void* Base( const CMemoryHandle& h ) { return h.Object; }
+	static std::ptrdiff_t Offset( const CMemoryHandle& h ) { return h.Offset; }
+};
+
+// Device memory: size-class free lists over cudaMalloc (blocks are recycled, the reference's "reuse mode" is always on
+// for GPU engines, MemoryEngineMixin.cpp:38-85) and one growing LIFO stack per host thread.
+class CB200Memory {
+public:
+	CB200Memory( int device, size_t memoryLimit );
+	~CB200Memory();
+
+	void* Alloc( size_t bytes );          // nullptr when the limit or the device is exhausted
+	void Free( void* ptr );
+	void* StackAlloc( size_t bytes );
+	void StackFree( void* ptr );
+	void CleanUp();                       // releases every cached block and the calling thread's stack
+	size_t Current() const { return current; }
+	size_t Peak() const { return peak; }
+	void ResetPeak() { peak = current; }
+	size_t InPools() const { return pooled; }
+	size_t FreeOnDevice() const;
+
+private:
+	struct CStack {
+		std::vector<std::pair<char*, size_t>> slabs; // base, capacity
+		struct CMark { int slab; size_t offset; size_t bytes; };
+		std::vector<CMark> marks;                     // position before each live allocation and its size
+		int slab = 0;
+		size_t offset = 0;
+	};
+	static size_t sizeClass( size_t bytes );
+	void* rawAlloc( size_t bytes );
+
+	const int device;
+	const size_t limit;
+	mutable std::mutex mutex;
+	std::map<size_t, std::vector<void*>> freeLists;  // class size -> cached blocks
+	std::unordered_map<void*, size_t> live;           // block -> class size
+	std::unordered_map<std::thread::id, CStack> stacks;
+	size_t current = 0, peak = 0, pooled = 0, reserved = 0;
+};
+
+class CB200MathEngine : public IMathEngine {
+public:
+	CB200MathEngine( int device, size_t memoryLimit, int flags );
+	~CB200MathEngine() override;
+
+	// precision selected by the factory flags: 3xTF32 unless GpuMathEngineCublasUseTensorCoresTF32Flag is given
+	int Precision() const { return precision; }
+	void* Stream() const { return stream; }
+
+	// non-pure virtuals of the interface
+	CMathEngineDistributedInfo GetDistributedInfo() override { return distributedInfo; }
+	void AbortDistributed() override;
+	bool IsDistributed() const override { return comm != nullptr; }
+	void SetDistributedCommunicator( void* ncclComm, const CMathEngineDistributedInfo& info );
+
+	// every pure virtual of IVectorMathEngine / IBlasEngine / IDnnEngine / IMathEngine, generated at build time from
+	// the NeoMathEngine header this file is compiled against
+#include "B200MathEngineDecl.inc"
+
+private:
+	void notImplemented( const char* method ) const;
+	void check( int code, const char* method ) const;
+	void setDevice() const;
+	// device pointer behind a handle of this engine
+	template<class T> T* raw( const CTypedMemoryHandle<T>& h ) const
+	{
+		if( !h.IsNull() && h.GetMathEngine() != this ) notImplemented( "use of a handle that belongs to another math engine" );
+		return CMemoryHandleInternal::GetRaw( h );
+	}
+	void vectorOp( int op, const float* a, const float* b, const float* scalar, float value, float* y, int n,
+		const char* method );
+
+	const int device;
+	const int precision;
+	void* stream = nullptr;
+	CB200Memory memory;
+	bool initialized = false;
+	void* comm = nullptr; // ncclComm_t
+	CMathEngineDistributedInfo distributedInfo;
+	// pinned staging buffers handed out by GetBuffer, LIFO per engine
+	struct CHostBuffer { void* host; size_t size; CMemoryHandle handle; size_t pos; };
+	std::vector<CHostBuffer> hostBuffers;
+	std::mutex hostMutex;
+};
+
+// Factory (the reference's signatures, NeoMathEngine.h:1282,1311, under names that do not collide with a
+// libNeoMathEngine.so loaded in the same process).
+extern "C++" {
+IMathEngine* CreateB200MathEngine( int deviceIndex, size_t memoryLimit, int flags );
+void CreateDistributedB200MathEngines( IMathEngine** mathEngines, int devsCount, const int* cudaDevs, size_t memoryLimit );
+}
+
+} // namespace NeoML

@@ -18,8 +18,12 @@ _i, _f, _vp = C.c_int, C.c_float, C.c_void_p
 
 
 def _opt(a):
-    """ctypes argument for an optional float array."""
-    return None if a is None else a.ctypes.data_as(_vp)
+    """ctypes argument for an optional array: numpy (host) or anything with data_ptr() (a torch device tensor)."""
+    if a is None:
+        return None
+    if hasattr(a, "data_ptr"):
+        return _vp(a.data_ptr())
+    return a.ctypes.data_as(_vp)
 
 
 def out_size(size, filt, pad, stride, dil=1):
@@ -162,6 +166,8 @@ class Oracle:
 
 
 class Reference:
+    ENGINE_LIB = None  # set by subclasses that drive another IMathEngine through the same shim
+
     """The reference's own CPU math engine (oracle/_ref, built by `make -C oracle ref`).  Same method names and
     argument order as Oracle.  `available()` is False where the reference build does not exist."""
 
@@ -179,6 +185,16 @@ class Reference:
         assert self.engine.value, "reference CPU engine could not be created"
         self.last_seconds = 0.0
 
+    # array plumbing, overridden by engines whose memory is not host memory
+    def _zeros(self, shape, dtype=np.float32):
+        return np.zeros(shape, dtype)
+
+    def _scalar(self, value):
+        return np.array([value], np.float32)
+
+    def _copy(self, a):
+        return a.copy()
+
     def close(self):
         if self.engine is not None and self.engine.value:
             self.lib.ref_engine_destroy(self.engine)
@@ -193,7 +209,7 @@ class Reference:
         n = b.shape[0] if n is None else n
         lda = a.shape[1] if lda is None else lda
         ldb = b.shape[1] if ldb is None else ldb
-        c = np.zeros((m, n), np.float32)
+        c = self._zeros((m, n), np.float32)
         sec = C.c_double(0)
         self._chk(self.lib.ref_multiply_matrix_by_transposed_matrix(self.engine, _opt(a), m, k, lda, _opt(b), n, ldb,
                                                                     _opt(c), n, C.byref(sec)))
@@ -203,7 +219,7 @@ class Reference:
     def multiply_matrix_by_matrix(self, a, b):
         batch, m, k = a.shape
         n = b.shape[2]
-        c = np.zeros((batch, m, n), np.float32)
+        c = self._zeros((batch, m, n), np.float32)
         sec = C.c_double(0)
         self._chk(self.lib.ref_multiply_matrix_by_matrix(self.engine, batch, _opt(a), m, k, _opt(b), n, _opt(c),
                                                          C.byref(sec)))
@@ -214,7 +230,7 @@ class Reference:
         n, h, w, c = x.shape
         k, r, s, _ = flt.shape
         ho, wo = out_size(h, r, padding[0], stride[0], dilation[0]), out_size(w, s, padding[1], stride[1], dilation[1])
-        y = np.zeros((n, ho, wo, k), np.float32) if out is None else out
+        y = self._zeros((n, ho, wo, k), np.float32) if out is None else out
         sec = C.c_double(0)
         self._chk(self.lib.ref_blob_convolution(self.engine, n, h, w, c, k, r, s, padding[0], padding[1], stride[0],
                                                 stride[1], dilation[0], dilation[1], _opt(x), _opt(flt),
@@ -226,7 +242,7 @@ class Reference:
         n, h, w, c = x.shape
         r, s, _ = flt.shape
         ho, wo = out_size(h, r, padding[0], stride[0]), out_size(w, s, padding[1], stride[1])
-        y = np.zeros((n, ho, wo, c), np.float32)
+        y = self._zeros((n, ho, wo, c), np.float32)
         sec = C.c_double(0)
         self._chk(self.lib.ref_blob_channelwise_convolution(self.engine, n, h, w, c, r, s, padding[0], padding[1],
                                                             stride[0], stride[1], _opt(x), _opt(flt), _opt(free_term),
@@ -239,7 +255,7 @@ class Reference:
         n, h, w, c_in = x.shape
         c_exp, c_out = w_exp.shape[0], w_down.shape[0]
         ho, wo = out_size(h, 3, 1, stride), out_size(w, 3, 1, stride)
-        y = np.zeros((n, ho, wo, c_out), np.float32)
+        y = self._zeros((n, ho, wo, c_out), np.float32)
         sec = C.c_double(0)
         self._chk(self.lib.ref_mobilenetv2_block(self.engine, n, h, w, c_in, c_exp, c_out, stride, int(residual),
                                                  act_exp, _f(act_exp_param), act_dw, _f(act_dw_param), _opt(x),
@@ -250,86 +266,107 @@ class Reference:
 
     def vector_op(self, op, a=None, b=None, scalar=0.0, count=None):
         ref = a if a is not None else b
-        n = count if count is not None else ref.size
-        y = np.zeros(n, np.float32)
-        sc = np.array([scalar], np.float32)
+        n = count if count is not None else int(np.prod(ref.shape))
+        y = self._zeros((n,), np.float32)
+        sc = self._scalar(scalar)
         self._chk(self.lib.ref_vector_op(self.engine, op, _opt(a), _opt(b), _opt(sc), _f(scalar), _opt(y), n))
         return y
 
     def add_vector_to_matrix_rows(self, batch, x, height, width, v):
-        y = np.zeros_like(x)
+        y = self._zeros(x.shape)
         self._chk(self.lib.ref_add_vector_to_matrix_rows(self.engine, batch, _opt(x), _opt(y), height, width, _opt(v)))
         return y
 
     def add_vector_to_matrix_columns(self, x, height, width, v):
-        y = np.zeros_like(x)
+        y = self._zeros(x.shape)
         self._chk(self.lib.ref_add_vector_to_matrix_columns(self.engine, _opt(x), _opt(y), height, width, _opt(v)))
         return y
 
     def sum_matrix_rows(self, batch, x, height, width, init=None):
-        y = np.zeros((batch, width), np.float32) if init is None else init.copy()
+        y = self._zeros((batch, width), np.float32) if init is None else self._copy(init)
         self._chk(self.lib.ref_sum_matrix_rows(self.engine, batch, _opt(y), _opt(x), height, width, int(init is not None)))
         return y
 
     def sum_matrix_columns(self, x, height, width):
-        y = np.zeros(height, np.float32)
+        y = self._zeros((height,), np.float32)
         self._chk(self.lib.ref_sum_matrix_columns(self.engine, _opt(y), _opt(x), height, width))
         return y
 
     def multiply_diag_matrix_by_matrix(self, d, height, x, width):
-        y = np.zeros_like(x)
+        y = self._zeros(x.shape)
         self._chk(self.lib.ref_multiply_diag_matrix_by_matrix(self.engine, _opt(d), height, _opt(x), width, _opt(y)))
         return y
 
     def multiply_matrix_by_diag_matrix(self, batch, x, height, width, d, diag_stride):
-        y = np.zeros_like(x)
+        y = self._zeros(x.shape)
         self._chk(self.lib.ref_multiply_matrix_by_diag_matrix(self.engine, batch, _opt(x), height, width, _opt(d),
                                                               diag_stride, _opt(y)))
         return y
 
     def matrix_softmax_by_rows(self, x, height, width):
-        y = np.zeros_like(x)
+        y = self._zeros(x.shape)
         self._chk(self.lib.ref_matrix_softmax_by_rows(self.engine, _opt(x), height, width, _opt(y)))
         return y
 
     def transpose_matrix(self, batch, x, height, medium, width, channels):
-        y = np.zeros_like(x)
+        y = self._zeros(x.shape)
         self._chk(self.lib.ref_transpose_matrix(self.engine, batch, _opt(x), height, medium, width, channels, _opt(y)))
         return y
 
     def find_max_value_in_rows(self, x, height, width):
-        v, i = np.zeros(height, np.float32), np.zeros(height, np.int32)
-        self._chk(self.lib.ref_find_max_value_in_rows(self.engine, _opt(x), height, width, _opt(v), i.ctypes.data_as(_vp)))
+        v, i = self._zeros((height,), np.float32), self._zeros((height,), np.int32)
+        self._chk(self.lib.ref_find_max_value_in_rows(self.engine, _opt(x), height, width, _opt(v), _opt(i)))
         return v, i
 
     def find_max_value_in_columns(self, batch, x, height, width):
-        v, i = np.zeros((batch, width), np.float32), np.zeros((batch, width), np.int32)
+        v, i = self._zeros((batch, width), np.float32), self._zeros((batch, width), np.int32)
         self._chk(self.lib.ref_find_max_value_in_columns(self.engine, batch, _opt(x), height, width, _opt(v),
-                                                         i.ctypes.data_as(_vp)))
+                                                         _opt(i)))
         return v, i
 
     def blob_max_pooling(self, x, fsize, stride):
         n, h, w, c = x.shape
         ho, wo = (h - fsize[0]) // stride[0] + 1, (w - fsize[1]) // stride[1] + 1
-        y, idx = np.zeros((n, ho, wo, c), np.float32), np.zeros((n, ho, wo, c), np.int32)
+        y, idx = self._zeros((n, ho, wo, c), np.float32), self._zeros((n, ho, wo, c), np.int32)
         self._chk(self.lib.ref_blob_max_pooling(self.engine, n, h, w, c, fsize[0], fsize[1], stride[0], stride[1],
-                                                _opt(x), _opt(y), idx.ctypes.data_as(_vp)))
+                                                _opt(x), _opt(y), _opt(idx)))
         return y, idx
 
     def blob_mean_pooling(self, x, fsize, stride):
         n, h, w, c = x.shape
         ho, wo = (h - fsize[0]) // stride[0] + 1, (w - fsize[1]) // stride[1] + 1
-        y = np.zeros((n, ho, wo, c), np.float32)
+        y = self._zeros((n, ho, wo, c), np.float32)
         self._chk(self.lib.ref_blob_mean_pooling(self.engine, n, h, w, c, fsize[0], fsize[1], stride[0], stride[1],
                                                  _opt(x), _opt(y)))
         return y
 
     def blob_resize_image(self, x, dl, dr, dt, db, padding=0, default_value=0.0):
         n, h, w, c = x.shape
-        y = np.zeros((n, h + dt + db, w + dl + dr, c), np.float32)
+        y = self._zeros((n, h + dt + db, w + dl + dr, c), np.float32)
         self._chk(self.lib.ref_blob_resize_image(self.engine, n, h, w, c, dl, dr, dt, db, padding, _f(default_value),
                                                  _opt(x), _opt(y)))
         return y
+
+    # ---- engine-level calls (memory, exchange, identity), the same for any IMathEngine behind the shim
+    def roundtrip(self, x: np.ndarray):
+        """Engine-owned memory + typed exchange + stack variables: returns (2*x+1 computed on the engine, gauges) with
+        gauges = (current bytes, peak bytes, pooled bytes after free, pooled bytes after CleanUp)."""
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros_like(x)
+        g = (C.c_ulonglong * 4)()
+        self._chk(self.lib.ref_engine_roundtrip(self.engine, _opt(x), _opt(y), x.size, g))
+        return y, tuple(int(v) for v in g)
+
+    def info(self):
+        """(TMathEngineType, available memory, device name, device id)"""
+        t, mem, name = C.c_int(0), C.c_ulonglong(0), C.create_string_buffer(256)
+        self.lib.ref_engine_info.restype = _i
+        dev = self.lib.ref_engine_info(self.engine, C.byref(t), C.byref(mem), name, 256)
+        return t.value, int(mem.value), name.value.decode(errors="replace"), dev
+
+    def training_method_raises(self, x) -> bool:
+        return bool(self.lib.ref_engine_training_method_raises(self.engine, _opt(x), int(np.prod(x.shape))))
+
 
 
 def rel_err(got: np.ndarray, want: np.ndarray, floor: float = 1e-3) -> float:
@@ -354,3 +391,58 @@ TOL_TF32 = 1e-2   # opt-in plain TF32
 
 def gate_err(got, want) -> float:
     return rel_err(got, want, GATE_FLOOR)
+
+
+class ShimmedB200Engine(Reference):
+    """The B200 IMathEngine (neoml_b200/lib/libNeoMathEngineB200.so) driven through the same C shim as the reference
+    CPU engine: the shim only wraps raw pointers into handles and makes IMathEngine virtual calls, so the same test
+    code exercises either engine.  Arrays are torch CUDA tensors.  Needs oracle/_ref (the shim and the
+    libNeoMathEngine.so that supplies IMathEngine's base-class symbols) and a GPU."""
+
+    ENGINE_SO = ROOT / "neoml_b200" / "lib" / "libNeoMathEngineB200.so"
+
+    @classmethod
+    def available(cls) -> bool:
+        return cls.SO.exists() and cls.ENGINE_SO.exists()
+
+    def __init__(self, device: int = 0, flags: int = 0):
+        import torch
+        self.torch = torch
+        # the engine library leaves IMathEngine's key functions undefined: they bind to the NeoMathEngine library of
+        # the hosting process, which therefore has to be loaded first and globally
+        C.CDLL(str(self.SO.parent / "libNeoMathEngine.so"), mode=C.RTLD_GLOBAL)
+        self.lib = C.CDLL(str(self.SO))
+        self.engine_lib = C.CDLL(str(self.ENGINE_SO))
+        self.engine_lib.nb200_create_math_engine.restype = _vp
+        self.engine_lib.nb200_create_math_engine.argtypes = [_i, C.c_size_t, _i]
+        self.engine_lib.nb200_destroy_math_engine.argtypes = [_vp]
+        self.engine = _vp(self.engine_lib.nb200_create_math_engine(device, 0, flags))
+        assert self.engine.value, "CreateB200MathEngine returned null"
+        self.last_seconds = 0.0
+
+    def close(self):
+        if self.engine is not None and self.engine.value:
+            self.torch.cuda.synchronize()
+            self.engine_lib.nb200_destroy_math_engine(self.engine)
+            self.engine = None
+
+    def sync(self):
+        """The engine runs on its own stream; the shim has no sync call, so drain the whole device."""
+        self.torch.cuda.synchronize()
+
+    def _zeros(self, shape, dtype=np.float32):
+        # torch fills on its own stream, the engine computes on another: finish the fill before handing the tensor over
+        t = self.torch.int32 if dtype == np.int32 else self.torch.float32
+        y = self.torch.zeros(tuple(shape) if not isinstance(shape, int) else (shape,), dtype=t, device="cuda")
+        self.torch.cuda.synchronize()
+        return y
+
+    def _scalar(self, value):
+        y = self.torch.tensor([value], dtype=self.torch.float32, device="cuda")
+        self.torch.cuda.synchronize()
+        return y
+
+    def _copy(self, a):
+        y = a.clone()
+        self.torch.cuda.synchronize()
+        return y

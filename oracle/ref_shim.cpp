@@ -289,4 +289,58 @@ int ref_blob_resize_image( void* eng, int batch, int h, int w, int c, int dl, in
 	SHIM_CATCH
 }
 
+// The way NeoML code really drives an engine: engine-owned memory, typed exchange, a stack variable.
+// y = 2 * x + 1 computed on the engine; gauges[0..3] = current / peak / in-pools bytes after the work and the
+// in-pools bytes after CleanUp().  Returns 0 on success.
+int ref_engine_roundtrip( void* eng, const float* hostIn, float* hostOut, int n, unsigned long long* gauges )
+{
+	SHIM_TRY
+	IMathEngine* e = static_cast<IMathEngine*>( eng );
+	e->ResetPeakMemoryUsage();
+	{
+		CFloatHandle x = e->HeapAllocTyped<float>( n );
+		e->DataExchangeTyped( x, hostIn, n );
+		{
+			CFloatHandleStackVar twice( *e, n ), one( *e, 1 );
+			one.SetValue( 1.f );
+			e->VectorAdd( x, x, twice, n );
+			e->VectorAddValue( twice, x, n, one );
+		}
+		gauges[0] = e->GetCurrentMemoryUsage();
+		gauges[1] = e->GetPeakMemoryUsage();
+		e->DataExchangeTyped( hostOut, CConstFloatHandle( x ), n );
+		e->HeapFree( x );
+	}
+	gauges[2] = e->GetMemoryInPools();
+	e->CleanUp();
+	gauges[3] = e->GetMemoryInPools();
+	SHIM_CATCH
+}
+
+// type: TMathEngineType of the engine; returns the device id the engine reports
+int ref_engine_info( void* eng, int* type, unsigned long long* availableMemory, char* name, int nameSize )
+{
+	IMathEngine* e = static_cast<IMathEngine*>( eng );
+	CMathEngineInfo info;
+	e->GetMathEngineInfo( info );
+	*type = static_cast<int>( e->GetType() );
+	*availableMemory = info.AvailableMemory;
+	std::strncpy( name, info.Name, nameSize - 1 );
+	name[nameSize - 1] = 0;
+	return info.Id;
+}
+
+// Calls a training-only method (outside the inference hot path).  1 = the engine raised through the exception
+// handler, 0 = it ran.
+int ref_engine_training_method_raises( void* eng, float* x, int n )
+{
+	IMathEngine* e = static_cast<IMathEngine*>( eng );
+	try {
+		e->VectorHuberDerivative( cfh( e, x ), fh( e, x ), n );
+	} catch( std::exception& ) {
+		return 1;
+	}
+	return 0;
+}
+
 } // extern "C"

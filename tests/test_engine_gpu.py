@@ -1,0 +1,141 @@
+"""The C++ IMathEngine implementation (CB200MathEngine) exercised through real IMathEngine virtual calls.
+
+The same C shim that drives the reference CPU engine (oracle/ref_shim.cpp) wraps device pointers into NeoML handles
+and calls Init*/Blob*/Multiply*/... on the engine object created by the B200 factory; results are compared with the
+reference CPU engine's committed outputs and the plain-C oracle.  Needs a B200 and oracle/_ref (for the shim and for
+the libNeoMathEngine.so that provides IMathEngine's base-class symbols)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle_lib import TOL_FP32, TOL_TF32, ShimmedB200Engine, gate_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def engine():
+    assert torch.cuda.is_available()
+    if not ShimmedB200Engine.available():
+        pytest.skip("oracle/_ref or libNeoMathEngineB200.so not built")
+    e = ShimmedB200Engine()
+    yield e
+    e.close()
+
+
+def dev(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(e, t):
+    e.sync()
+    return t.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONV_CASES))
+def test_blob_convolution(engine, golden, name):
+    x, f, b, kw = cases.conv_inputs(name)
+    y = engine.blob_convolution(dev(x), dev(f), dev(b), **kw)
+    assert gate_err(host(engine, y), golden[f"conv/{name}"]) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", sorted(cases.MMT_CASES))
+def test_multiply_matrix_by_transposed_matrix(engine, golden, name):
+    a, b, kw = cases.mmt_inputs(name)
+    y = engine.multiply_matrix_by_transposed_matrix(dev(a), dev(b), **kw)
+    assert gate_err(host(engine, y), golden[f"mmt/{name}"]) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", sorted(cases.MM_CASES))
+def test_multiply_matrix_by_matrix(engine, golden, name):
+    a, b = cases.mm_inputs(name)
+    y = engine.multiply_matrix_by_matrix(dev(a), dev(b))
+    assert gate_err(host(engine, y), golden[f"mm/{name}"]) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", sorted(cases.CHCONV_CASES))
+def test_channelwise_convolution(engine, golden, name):
+    x, f, b, kw = cases.chconv_inputs(name)
+    y = engine.blob_channelwise_convolution(dev(x), dev(f), dev(b), **kw)
+    assert gate_err(host(engine, y), golden[f"chconv/{name}"]) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", sorted(cases.MBV2_CASES))
+def test_mobilenetv2_block(engine, golden, name):
+    args, kw = cases.mbv2_inputs(name)
+    y = engine.mobilenetv2_block(*[dev(a) for a in args], **kw)
+    assert gate_err(host(engine, y), golden[f"mbv2/{name}"]) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", sorted(cases.SOFTMAX_CASES))
+def test_softmax(engine, golden, name):
+    x, h, w = cases.softmax_inputs(name)
+    y = engine.matrix_softmax_by_rows(dev(x), h, w)
+    assert gate_err(host(engine, y), golden[f"softmax/{name}"]) < 1e-5
+
+
+def test_vector_and_matrix_helpers(engine, oracle):
+    a, b = cases.uniform(11, (1001,), -4, 4), cases.uniform(12, (1001,), -4, 4)
+    for op in (0, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18):
+        a_ = np.abs(a) + 0.1 if op in (11, 12) else a
+        b_ = np.abs(b) + 0.5 if op == 17 else b
+        got = host(engine, engine.vector_op(op, dev(a_), dev(b_), 0.7))
+        assert gate_err(got, oracle.vector_op(op, a_, b_, 0.7)) < 1e-5, op
+    m = cases.uniform(21, (3 * 5 * 7,))
+    v21, v15 = cases.uniform(22, (21,)), cases.uniform(23, (15,))
+    assert np.array_equal(host(engine, engine.add_vector_to_matrix_rows(3, dev(m), 5, 7, dev(v21))),
+                          oracle.add_vector_to_matrix_rows(3, m, 5, 7, v21))
+    assert np.array_equal(host(engine, engine.add_vector_to_matrix_columns(dev(m), 15, 7, dev(v15))),
+                          oracle.add_vector_to_matrix_columns(m, 15, 7, v15))
+    assert gate_err(host(engine, engine.sum_matrix_rows(3, dev(m), 5, 7)), oracle.sum_matrix_rows(3, m, 5, 7)) < 1e-5
+    assert gate_err(host(engine, engine.sum_matrix_columns(dev(m), 15, 7)), oracle.sum_matrix_columns(m, 15, 7)) < 1e-5
+    t = cases.uniform(26, (2 * 3 * 4 * 5 * 6,))
+    assert np.array_equal(host(engine, engine.transpose_matrix(2, dev(t), 3, 4, 5, 6)), oracle.transpose_matrix(2, t, 3, 4, 5, 6))
+    am = cases.uniform(27, (13 * 37,))
+    v, i = engine.find_max_value_in_rows(dev(am), 13, 37)
+    ov, oi = oracle.find_max_value_in_rows(am, 13, 37)
+    assert np.array_equal(host(engine, v), ov) and np.array_equal(host(engine, i), oi)
+
+
+def test_pooling_and_resize(engine, oracle):
+    x = cases.uniform(31, (2, 10, 12, 8))
+    assert np.array_equal(host(engine, engine.blob_max_pooling(dev(x), (3, 3), (2, 2))[0]), oracle.blob_max_pooling(x, (3, 3), (2, 2))[0])
+    assert gate_err(host(engine, engine.blob_mean_pooling(dev(x), (3, 2), (2, 1))), oracle.blob_mean_pooling(x, (3, 2), (2, 1))) < 1e-6
+    for pad in (0, 1, 2):
+        assert np.array_equal(host(engine, engine.blob_resize_image(dev(x), 1, 2, 2, 1, pad, 0.5)),
+                              oracle.blob_resize_image(x, 1, 2, 2, 1, pad, 0.5))
+
+
+def test_tf32_flag_selects_the_opt_in_arithmetic(golden):
+    if not ShimmedB200Engine.available():
+        pytest.skip("oracle/_ref or libNeoMathEngineB200.so not built")
+    e = ShimmedB200Engine(flags=2)  # GpuMathEngineCublasUseTensorCoresTF32Flag
+    try:
+        a, b, kw = cases.mmt_inputs("aligned")
+        y = host(e, e.multiply_matrix_by_transposed_matrix(dev(a), dev(b), **kw))
+        err = gate_err(y, golden["mmt/aligned"])
+        assert 1e-6 < err < TOL_TF32  # visibly TF32, and inside its own tolerance
+    finally:
+        e.close()
+
+
+def test_engine_memory_exchange_and_gauges(engine):
+    x = cases.uniform(41, (100_003,))
+    y, (current, peak, pooled, pooled_after_cleanup) = engine.roundtrip(x)
+    assert np.array_equal(y, 2 * x + 1)
+    # one heap block of n floats is live when the gauges are read; the two stack variables pushed the peak higher
+    assert current >= 4 * x.size and peak >= current + 4 * x.size
+    assert pooled >= 4 * x.size          # the freed heap block is cached for reuse ...
+    assert pooled_after_cleanup == 0     # ... until CleanUp() gives it back to the driver
+
+
+def test_engine_identity(engine):
+    kind, available, name, device = engine.info()
+    assert kind == 2                     # MET_Cuda: NeoML code that branches on the engine type takes its GPU paths
+    assert device == 0 and available > (1 << 30) and name
+
+
+def test_training_methods_raise_instead_of_falling_back(engine):
+    x = dev(cases.uniform(42, (64,)))
+    assert engine.training_method_raises(x)

@@ -97,3 +97,12 @@ def test_image_helpers_live(oracle, reference):
     for pad in (0, 1, 2):
         assert np.array_equal(oracle.blob_resize_image(x, 1, 2, 2, 1, pad, 0.5), reference.blob_resize_image(x, 1, 2, 2, 1, pad, 0.5))
     assert np.array_equal(oracle.blob_resize_image(x, -1, -2, -2, 1, 0, 0.5), reference.blob_resize_image(x, -1, -2, -2, 1, 0, 0.5))
+
+
+def test_reference_engine_roundtrip_through_the_shim(reference):
+    """The engine-level shim calls (used on the GPU against the B200 engine) behave on the reference CPU engine."""
+    x = cases.uniform(41, (1003,))
+    y, (current, peak, pooled, pooled_after_cleanup) = reference.roundtrip(x)
+    assert np.array_equal(y, 2 * x + 1)
+    assert current >= 4 * x.size and peak >= current and pooled_after_cleanup == 0
+    assert reference.info()[0] == 1      # MET_Cpu
