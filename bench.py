@@ -36,7 +36,7 @@ IMAGE = (224, 224, 3)
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch")
@@ -136,7 +136,8 @@ def run_reference_arm(args):
 
 # ---------------------------------------------------------------------------------------------------- GPU arm
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of this rank's GPU, sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons of this rank's GPU, sampled every 50 ms; started before the warm-up
+    steps (the tool needs a few hundred ms to come up) and stopped after the timed regions."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -148,7 +149,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -162,7 +163,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
@@ -171,15 +172,17 @@ class ClockSampler:
             try:
                 sm.append(float(parts[0]))
                 mx.append(float(parts[1]))
+                pw.append(float(parts[2]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        # the busiest half of the samples is "under load"
-        load = sorted(sm)[len(sm) // 2:] if sm else []
+        # "under load" = the samples whose board power is within 40 % of the highest one seen
+        load = [c for c, w in zip(sm, pw) if w >= 0.6 * max(pw)] if sm else []
         return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_under_load": len(load),
+                "power_w_max": max(pw) if pw else None}
 
 
 class ContractionTimer:
@@ -207,7 +210,7 @@ def run_ours(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from neoml_b200 import _capi, resnet50
+    from neoml_b200 import _capi, resnet50, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -238,11 +241,11 @@ def run_ours(args):
         return resnet50.forward(be, weights, x, fuse=fuse)
 
     # ---- device-resident timing -------------------------------------------------------------------------
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(dev_x)
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     launches0 = lib.nb200_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -253,7 +256,6 @@ def run_ours(args):
     barrier()
     launches = lib.nb200_launch_count() - launches0
     ms_total = start.elapsed_time(stop)
-    clocks = sampler.stop()
 
     # ---- end to end: pinned host batch -> device -> forward -> result back, double-buffered ---------------------------
     copy_stream = torch.cuda.Stream()
@@ -286,12 +288,10 @@ def run_ours(args):
     e2e_loop(args.steps)
     barrier()
     e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
 
-    # max over ranks
-    times = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(times[0]), float(times[1])
+    # a step is as slow as its slowest rank
+    ms_total, e2e_ms = sharding.max_over_ranks([ms_total, e2e_s * 1e3], device="cuda")
 
     status = lib.nb200_device_status(None, 0)
     if status != 0:
