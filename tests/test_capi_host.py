@@ -34,6 +34,9 @@ def test_every_declaration_cites_the_reference_interface():
                     "nb200_vector_fill_int"):
             continue
         head = text[:text.index(name + "(")]
+        if name == "nb200_blob_convolution_static_scratch":
+            assert "No counterpart in the reference" in head[-1400:]  # an addition of this library, and says so
+            continue
         # the citing comment sits directly above the declaration (a desc struct may lie between them)
         assert "NME.h:" in head[-1400:], name
 
