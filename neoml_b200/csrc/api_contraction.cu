@@ -66,6 +66,25 @@ __global__ void __launch_bounds__(256) pad_channels_kernel(const float* __restri
 	}
 }
 
+// Prepares the filter for the tensor-core kernel once per call, so that no CTA has to convert its B tiles:
+// mode 0 (3xTF32): y = x - trunc_tf32(x), the "lo" part of the split (the filter itself serves as "hi");
+// mode 1 (TF32):   y = x rounded to the nearest TF32.
+__global__ void __launch_bounds__(256) prepare_filter_kernel(const float* __restrict__ x, float* __restrict__ y,
+	long long n, int mode)
+{
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+		const float v = __ldg(x + i);
+		y[i] = mode == 0 ? v - __uint_as_float(__float_as_uint(v) & 0xffffe000u) : to_tf32(v);
+	}
+}
+
+// floats of scratch for the prepared filter (rounded up so that what follows stays 16-byte aligned)
+size_t prepared_filter_floats(long long k, long long r, long long s, long long c)
+{
+	return static_cast<size_t>((k * r * s * c + 3) / 4 * 4);
+}
+
 bool wants_channel_padding(const nb200_conv_desc* d)
 {
 	const bool pointwise = d->r == 1 && d->s == 1 && d->pad_h == 0 && d->pad_w == 0 && d->stride_h == 1 && d->stride_w == 1;
@@ -76,9 +95,12 @@ extern "C" {
 
 size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* d)
 {
-	if(d == nullptr || d->c <= 0 || !wants_channel_padding(d)) return 0;
+	if(d == nullptr || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0) return 0;
 	const size_t c4 = static_cast<size_t>((d->c + 3) / 4 * 4);
-	return (static_cast<size_t>(d->batch) * d->h * d->w + static_cast<size_t>(d->k) * d->r * d->s) * c4 + 8;
+	// the prepared filter (always), and for channel counts that are not a multiple of four the widened image and filter
+	size_t floats = prepared_filter_floats(d->k, d->r, d->s, static_cast<long long>(c4)) + 8;
+	if(wants_channel_padding(d)) floats += (static_cast<size_t>(d->batch) * d->h * d->w + static_cast<size_t>(d->k) * d->r * d->s) * c4 + 8;
+	return floats;
 }
 
 void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int skip_mask)
@@ -158,7 +180,7 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 		if(rc != NB200_OK) return rc;
 		nb200_conv_desc padded = *d;
 		padded.c = c4;
-		return nb200_blob_convolution(stream, &padded, xs, fs, y, nullptr, epi, precision);
+		return nb200_blob_convolution(stream, &padded, xs, fs, y, fs + taps * c4, epi, precision);
 	}
 	if(d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0
 		|| d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
@@ -194,6 +216,28 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 		// gathered rows; 16-byte copies when a chunk of four K indices never straddles a filter tap
 		p.a_mode = A_CONV_TAP;
 		p.a_vec = d->c % 4 == 0 && aligned16(x) ? 1 : 0;
+	}
+	// with scratch the filter is prepared once here (one small pass over K*R*S*C floats) instead of being converted
+	// tile by tile by every CTA; needs the all-TMA pipeline: 16-byte-aligned operands and 32-channel K blocks
+	p.Blo = nullptr;
+	p.b_ready = 0;
+	const bool tmaShape = aligned16(x) && aligned16(filter) && (pointwise ? d->c % 4 == 0 : d->c % 32 == 0) && kk % 4 == 0;
+	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && tmaShape && outRows > 0) {
+		float* prepared = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
+		const long long n = static_cast<long long>(d->k) * kk;
+		prepare_filter_kernel<<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>(filter, prepared, n,
+			precision == NB200_PREC_3XTF32 ? 0 : 1);
+		count_launch(1);
+		const int rc = check_launch();
+		if(rc != NB200_OK) return rc;
+		if(precision == NB200_PREC_3XTF32) p.Blo = prepared; else p.B = prepared;
+		p.b_ready = 1;
+		const int rc2 = run(p, 1, stream, precision);
+		if(rc2 != NB200_EINVAL) return rc2;
+		// the launcher could not describe an operand to TMA after all: fall back to in-kernel conversion
+		p.B = filter;
+		p.Blo = nullptr;
+		p.b_ready = 0;
 	}
 	return run(p, 1, stream, precision);
 }

@@ -66,10 +66,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 	uint32_t done;
 	asm volatile(
 		"{\n\t.reg .pred P;\n\t"
-		"mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+		"mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
 		"selp.b32 %0, 1, 0, P;\n\t}"
 		: "=r"(done)
-		: "r"(smem_u32(bar)), "r"(parity)
+		: "r"(smem_u32(bar)), "r"(parity), "r"(4000u) /* may stay suspended up to 4 us per try: a waiting lane then costs
+		                                                    the other warps of its scheduler almost no issue slots */
 		: "memory");
 	return done != 0;
 }
@@ -90,12 +91,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 	int* status, int site)
 {
 	if(mbar_try_wait(bar, parity)) return true;
-	const uint64_t t0 = global_timer_ns();
+	// the wall clock is looked at only after a few thousand failed polls: reading %globaltimer is slow, and an ordinary
+	// wait in a running pipeline ends long before that
+	uint64_t t0 = 0;
 	for(uint32_t it = 1;; ++it) {
 		if(mbar_try_wait(bar, parity)) return true;
-		if((it & 63u) == 0u) {
+		if((it & 4095u) == 0u) {
 			if(*abort_flag != 0) return false;
-			if(global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+			const uint64_t now = global_timer_ns();
+			if(t0 == 0) t0 = now;
+			else if(now - t0 > WAIT_LIMIT_NS) break;
 		}
 	}
 	*abort_flag = 1;
@@ -179,6 +184,31 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r)
 		  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
 		: "r"(taddr));
 }
+// Register -> TMEM: the calling warp writes 32 columns of its 32 lanes (lane quarter = warp index % 4), value r[j] of
+// lane l going to (lane base + l, column base + j).
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r)
+{
+	asm volatile(
+		"tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+		"%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+		::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+		  "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+		  "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+		  "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+		: "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r)
+{
+	asm volatile(
+		"tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+		::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+		  "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+		: "memory");
+}
+__device__ __forceinline__ void tmem_st_wait()
+{
+	asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait()
 {
 	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -219,6 +249,19 @@ __device__ __forceinline__ void umma_tf32_ss(uint32_t tmem_d, uint64_t desc_a, u
 		"setp.ne.b32 p, %4, 0;\n\t"
 		"tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
 		::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 8 tf32 of K, row m in lane m, element k in column
+// tmem_a + k) is read from tensor memory, so only B costs shared-memory bandwidth.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+	uint32_t accumulate)
+{
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+		::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
 		: "memory");
 }
 

@@ -27,6 +27,9 @@ struct ContractionParams {
 	int c_vec;  // 16-byte stores legal for C (and loads for residual)
 	int a_tma;  // A arrives by TMA (1: tiled rows, 2: im2col); the launcher decides, 0 = cp.async gather
 	int b_tma;  // B arrives by TMA (tiled rows)
+	const float* Blo; // optional: lo(B) = B - trunc_tf32(B) prepared by the caller (same shape and strides as B); with it,
+	                  // and for plain TF32 a pre-rounded B passed as B itself, the kernel does no per-step work on B
+	int b_ready;      // 1: B needs no conversion in the kernel (Blo given for 3xTF32 / B already rounded for TF32)
 	// convolution geometry (a_mode != A_ROWS)
 	int H, W, Cin, Ho, Wo, S, padH, padW, strH, strW, dilH, dilW;
 	// epilogue

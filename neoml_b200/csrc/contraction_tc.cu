@@ -50,7 +50,7 @@ constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int THREADS = (EPI_WARP0 + EPI_WARPS) * 32;
 constexpr int A_TILE_BYTES = BM * BK * 4; // 16 KB
 constexpr int STAGING_BYTES_PER_WARP = 32 * 64; // 32 rows x 16 floats
-constexpr int LO_SLOTS = 2;
+constexpr int LO_SLOTS = 2;              // B-lo tiles in shared memory == A stages in tensor memory
 constexpr int MAX_RAW_SLOTS = 8;
 
 enum {
@@ -71,7 +71,8 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk)
 
 // debug aid: per-role time stamps of the first traceSteps K-block steps of CTA 0
 enum { TR_COPY_ISSUED = 0, TR_RAW_FULL = 1, TR_CVT_DONE = 2, TR_MMA_ISSUED = 3, TR_COPY_SLOT_FREE = 4, TR_COPY_A_DONE = 5, TR_COPY_B_DONE = 6,
-	TR_EPI_ACC_FULL = 7, TR_EPI_TMEM_READ = 8, TR_EPI_TILE_DONE = 9, TR_MMA_TILE_COMMITTED = 10, TR_ROLES = 11 }; // 7..10 are per tile
+	TR_EPI_ACC_FULL = 7, TR_EPI_TMEM_READ = 8, TR_EPI_TILE_DONE = 9, TR_MMA_TILE_COMMITTED = 10, TR_EPI_LD0 = 11, TR_EPI_STS0 = 12,
+	TR_EPI_STG0 = 13, TR_EPI_CH1 = 14, TR_ROLES = 16 }; // 7..14 are per tile
 __device__ __forceinline__ void trace(const ContractionParams& p, int role, int step)
 {
 	if(p.trace != nullptr && blockIdx.x == 0 && step < p.traceSteps) p.trace[role * p.traceSteps + step] = clock64();
@@ -92,9 +93,12 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int nTiles, int tilesP
 	return t;
 }
 
-template<int BN>
+// GATHER = false: both operands arrive by TMA and the cp.async gather code (with its per-row bookkeeping registers) is
+// not even compiled in; GATHER = true: the general kernel.
+template<int BN, bool GATHER, bool THREEX>
 __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p, int numTiles, int nTiles,
-	int tilesPerBatch, int rawSlots, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB)
+	int tilesPerBatch, int rawSlots, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+	const __grid_constant__ CUtensorMap mapBlo)
 {
 	extern __shared__ uint8_t smem_raw[];
 	// once any CTA on this device has given up on a wait, later CTAs do not start: a broken pipeline must not
@@ -104,25 +108,42 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	// the swizzle pattern is a function of the absolute shared-memory address: tiles must start on 1024 B
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
-	const bool threeX = p.precision == NB200_PREC_3XTF32;
+	constexpr bool threeX = THREEX; // 3xTF32 split (three MMAs per product) or plain TF32
 	constexpr int B_TILE_BYTES = BN * BK * 4;
-	constexpr int SLOT_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+	// B needs no work in the kernel when the caller prepared it (lo(B) in global memory for 3xTF32, a pre-rounded B for
+	// plain TF32); a raw slot then also receives the lo tile by TMA and no lo ring exists
+	const bool preB = p.b_ready != 0;
+	const bool loByTma = preB && threeX;
+	const int SLOT_BYTES = A_TILE_BYTES + B_TILE_BYTES + (loByTma ? B_TILE_BYTES : 0);
 
-	constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)); // power of two
-	const uint32_t accStride = threeX ? 2 * ACC_COLS : ACC_COLS;  // main [+ cross] accumulator of one set
-	const int accSets = 2 * accStride <= 512 ? 2 : 1;
-	const uint32_t tmemCols = accStride * accSets;                   // 32 .. 512, a power of two
+	// Tensor memory (512 columns): two main accumulators (BN columns each) so that the epilogue of tile i overlaps the
+	// MMAs of tile i + 1; for 3xTF32 the cross accumulators, two if they fit, else one that the epilogue folds into
+	// the main accumulator first thing (TMEM -> registers -> TMEM) and hands back at once; then two stages of the A
+	// operand (32 columns of hi [+ 32 of lo] per stage: row m of the tile in lane m, K index in the column).
+	constexpr uint32_t ACC_COLS = BN;
+	constexpr uint32_t A_STAGE_COLS = threeX ? 64 : 32;
+	constexpr int CROSS_SETS = !threeX ? 0 : (4 * ACC_COLS + LO_SLOTS * A_STAGE_COLS <= 512 ? 2 : 1);
+	constexpr bool FOLD = CROSS_SETS == 1;
+	constexpr uint32_t CROSS_BASE = 2 * ACC_COLS;
+	constexpr uint32_t A_BASE = CROSS_BASE + CROSS_SETS * ACC_COLS;
+	constexpr uint32_t TMEM_USED = A_BASE + LO_SLOTS * A_STAGE_COLS;
+	static_assert(TMEM_USED <= 512, "tensor memory budget");
+	constexpr uint32_t tmemCols = TMEM_USED <= 32 ? 32 : (TMEM_USED <= 64 ? 64 : (TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512)));
+	constexpr uint32_t aBaseCol = A_BASE;
+	constexpr uint32_t aStageCols = A_STAGE_COLS;
+	constexpr int accSets = 2;
 
 	uint8_t* rawRing = smem;
 	uint8_t* loRing = rawRing + static_cast<size_t>(rawSlots) * SLOT_BYTES;
-	uint8_t* staging = loRing + (threeX ? LO_SLOTS * SLOT_BYTES : 0);
+	uint8_t* staging = loRing + (threeX && !preB ? LO_SLOTS * B_TILE_BYTES : 0);
 	uint64_t* rawFullBar = reinterpret_cast<uint64_t*>(staging + EPI_WARPS * STAGING_BYTES_PER_WARP + EPI_WARPS * 256);
 	uint64_t* rawEmptyBar = rawFullBar + MAX_RAW_SLOTS;
 	uint64_t* cvtFullBar = rawEmptyBar + MAX_RAW_SLOTS;
 	uint64_t* loEmptyBar = cvtFullBar + MAX_RAW_SLOTS;
 	uint64_t* accFullBar = loEmptyBar + LO_SLOTS;
 	uint64_t* accEmptyBar = accFullBar + 2;
-	uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmptyBar + 2);
+	uint64_t* crossEmptyBar = accEmptyBar + 2; // fold scheme only: the single cross accumulator is free again
+	uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(crossEmptyBar + 1);
 	volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
 	const int tid = threadIdx.x;
@@ -131,18 +152,21 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	const int numKb = (p.K + BK - 1) / BK;
 	const int myTiles = blockIdx.x < numTiles ? (numTiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
 	const int totalSteps = myTiles * numKb;
+	const bool allTma = !GATHER || (p.a_tma != 0 && p.b_tma != 0);
 
 	if(tid == 0) {
 		for(int s = 0; s < MAX_RAW_SLOTS; ++s) {
-			mbar_init(&rawFullBar[s], COPY_THREADS + 1); // every copy thread's cp.async arrival + the TMA issuer's expect_tx
+			// every copy thread's cp.async arrival (only when something is gathered) + the TMA issuer's expect_tx
+			mbar_init(&rawFullBar[s], allTma ? 1 : COPY_THREADS + 1);
 			mbar_init(&rawEmptyBar[s], 1);
-			mbar_init(&cvtFullBar[s], CVT_THREADS);
+			mbar_init(&cvtFullBar[s], CVT_WARPS);
 		}
 		for(int s = 0; s < LO_SLOTS; ++s) mbar_init(&loEmptyBar[s], 1);
 		for(int b = 0; b < 2; ++b) {
 			mbar_init(&accFullBar[b], 1);
-			mbar_init(&accEmptyBar[b], EPI_THREADS);
+			mbar_init(&accEmptyBar[b], EPI_WARPS);
 		}
+		mbar_init(crossEmptyBar, EPI_WARPS);
 		*abortFlag = 0;
 		mbar_init_fence();
 	}
@@ -159,8 +183,50 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	tc_fence_after_sync();
 	const uint32_t tmemBase = *tmemSlot;
 
-	if(warp < COPY_WARPS) {
-		// ------------------------------------------------------------------ copy
+	if(warp < COPY_WARPS && allTma) {
+		// ------------------------------------------------------------------ copy, both operands by TMA
+		// One thread feeds the ring: wait for the slot, announce the bytes, issue the two tensor copies.  All slot,
+		// phase and filter-tap bookkeeping is incremental (no division in the loop).
+		if(tid == 0) {
+			int tile = blockIdx.x;
+			int slot = 0;
+			uint32_t parity = 1; // the first pass over the ring finds every slot free
+			int step = 0;
+			bool ok = true;
+			const int hw = p.Ho * p.Wo;
+			for(int local = 0; local < myTiles && ok; ++local, tile += gridDim.x) {
+				const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
+				int w0 = 0, h0 = 0, img = 0;
+				if(p.a_tma == 2) {
+					img = tc.m0 / hw;
+					const int rem = tc.m0 - img * hw;
+					const int oy = rem / p.Wo;
+					w0 = (rem - oy * p.Wo) * p.strW - p.padW;
+					h0 = oy * p.strH - p.padH;
+				}
+				int c0 = 0, fs = 0, fr = 0; // channel offset inside the filter tap, tap column, tap row
+				for(int kb = 0; kb < numKb; ++kb, ++step) {
+					if(!mbar_wait_bounded(&rawEmptyBar[slot], parity, abortFlag, p.status, SITE_RAW_EMPTY)) { ok = false; break; }
+					trace(p, TR_COPY_SLOT_FREE, step);
+					const uint32_t aTile = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES);
+					mbar_arrive_expect_tx(&rawFullBar[slot], SLOT_BYTES);
+					if(p.a_tma == 1) {
+						tma_load_3d(aTile, &mapA, &rawFullBar[slot], kb * BK, tc.m0, tc.batch);
+					} else {
+						tma_load_im2col_4d(aTile, &mapA, &rawFullBar[slot], c0, w0, h0, img,
+							static_cast<uint16_t>(fs * p.dilW), static_cast<uint16_t>(fr * p.dilH));
+						c0 += BK;
+						if(c0 >= p.Cin) { c0 = 0; if(++fs == p.S) { fs = 0; ++fr; } }
+					}
+					tma_load_3d(aTile + A_TILE_BYTES, &mapB, &rawFullBar[slot], kb * BK, tc.n0, tc.batch);
+					if(loByTma) tma_load_3d(aTile + A_TILE_BYTES + B_TILE_BYTES, &mapBlo, &rawFullBar[slot], kb * BK, tc.n0, tc.batch);
+					trace(p, TR_COPY_ISSUED, step);
+					if(++slot == rawSlots) { slot = 0; parity ^= 1; }
+				}
+			}
+		}
+	} else if(GATHER && warp < COPY_WARPS) {
+		// ------------------------------------------------------------------ copy, gathered operands
 		// piece ownership: chunk tid%8 of rows tid/8 + 8*q.  Column-major B ([k][n]): consecutive lanes take
 		// consecutive n so that each 4-byte copy is coalesced: rows tid%32 + 32*(q/4), chunks tid/32 + 2*(q%4).
 		constexpr int A_PIECES = BM / 8, B_PIECES = BN / 8;
@@ -310,54 +376,85 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					}
 				}
 				if(tid == 0) trace(p, TR_COPY_B_DONE, step);
-				cp_async_arrive_on(&rawFullBar[slot]);
+				if(!allTma) cp_async_arrive_on(&rawFullBar[slot]);
 				if(tid == 0) trace(p, TR_COPY_ISSUED, step);
 			}
 		}
 		cp_async_wait<0>();
 	} else if(warp >= CVT_WARP0 && warp < EPI_WARP0) {
 		// ------------------------------------------------------------------ convert
-		constexpr int A_PIECES = BM / 16, B_PIECES = BN / 16;
+		// A: thread ct owns row ct of the tile.  It reads the row's 32 floats from the raw slot and stores them as the
+		// tensor core's A operand in tensor memory (lane ct): hi = x with the low 13 mantissa bits cleared,
+		// lo = x - hi (exact in fp32) for 3xTF32; x rounded to nearest TF32 for plain TF32.  The MMAs then read A from
+		// tensor memory, which leaves shared-memory bandwidth to the B operand and the copies.
+		// B: 3xTF32 writes lo(B) into a shared-memory lo slot (the raw slot itself serves as hi: the tensor core
+		// ignores the low mantissa bits); plain TF32 rounds the raw B tile in place.
+		constexpr int B_PIECES = BN / 16;
 		const int ct = tid - CVT_WARP0 * 32;
 		const int row0 = ct >> 3, chunk0 = ct & 7;
+		const uint32_t aLane = tmemBase + (static_cast<uint32_t>((warp & 3) * 32) << 16) + aBaseCol;
 		bool ok = true;
+		int slot = 0;
+		uint32_t rawParity = 0;
 		for(int i = 0; i < totalSteps && ok; ++i) {
-			const int slot = i % rawSlots;
-			if(!mbar_wait_bounded_warp(&rawFullBar[slot], (i / rawSlots) & 1, abortFlag, p.status, SITE_RAW_FULL)) { ok = false; break; }
-			uint8_t* raw = rawRing + static_cast<size_t>(slot) * SLOT_BYTES;
+			if(!mbar_wait_bounded_warp(&rawFullBar[slot], rawParity, abortFlag, p.status, SITE_RAW_FULL)) { ok = false; break; }
 			if(ct == 0) trace(p, TR_RAW_FULL, i);
-			if(threeX) {
-				const int ls = i % LO_SLOTS;
-				if(!mbar_wait_bounded_warp(&loEmptyBar[ls], ((i / LO_SLOTS) & 1) ^ 1, abortFlag, p.status, SITE_LO_EMPTY)) { ok = false; break; }
-				uint8_t* lo = loRing + static_cast<size_t>(ls) * SLOT_BYTES;
+			const int ls = i % LO_SLOTS;
+			// the A stage and the lo slot of step i - 2 are free once that step's MMAs have completed
+			if(!mbar_wait_bounded_warp(&loEmptyBar[ls], ((i / LO_SLOTS) & 1) ^ 1, abortFlag, p.status, SITE_LO_EMPTY)) { ok = false; break; }
+			tc_fence_after_sync();
+			if(ct == 0) trace(p, 15, i); // debug: the A stage was seen free
+			uint8_t* raw = rawRing + static_cast<size_t>(slot) * SLOT_BYTES;
+			{
+				// two halves of 16 K indices keep the live registers at 32
 #pragma unroll
-				for(int q = 0; q < A_PIECES + B_PIECES && !(p.debugSkip & 2); ++q) {
-					const uint32_t off = q < A_PIECES ? swz(row0 + 16 * q, chunk0)
-						: static_cast<uint32_t>(A_TILE_BYTES) + swz(row0 + 16 * (q - A_PIECES), chunk0);
-					const float4 v = *reinterpret_cast<const float4*>(raw + off);
-					float4 l;
-					l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-					l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-					l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-					l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-					*reinterpret_cast<float4*>(lo + off) = l;
-				}
-				if(!(p.debugSkip & 8)) fence_proxy_async_smem();
-				mbar_arrive(&cvtFullBar[ls]);
-				if(ct == 0) trace(p, TR_CVT_DONE, i);
-			} else {
-				// plain TF32: round to nearest in place (the tensor core alone would truncate)
+				for(int half = 0; half < 2; ++half) {
+					uint32_t hi[16], lo[16];
 #pragma unroll
-				for(int q = 0; q < A_PIECES + B_PIECES; ++q) {
-					const uint32_t off = q < A_PIECES ? swz(row0 + 16 * q, chunk0)
-						: static_cast<uint32_t>(A_TILE_BYTES) + swz(row0 + 16 * (q - A_PIECES), chunk0);
-					float4 v = *reinterpret_cast<const float4*>(raw + off);
-					v.x = to_tf32(v.x); v.y = to_tf32(v.y); v.z = to_tf32(v.z); v.w = to_tf32(v.w);
-					*reinterpret_cast<float4*>(raw + off) = v;
+					for(int c = 0; c < 4; ++c) {
+						const float4 v = *reinterpret_cast<const float4*>(raw + swz(ct, 4 * half + c));
+						const float x[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+						for(int e = 0; e < 4; ++e) {
+							if(threeX) {
+								hi[4 * c + e] = __float_as_uint(x[e]) & 0xffffe000u;
+								lo[4 * c + e] = __float_as_uint(x[e] - __uint_as_float(hi[4 * c + e]));
+							} else {
+								hi[4 * c + e] = __float_as_uint(to_tf32(x[e]));
+							}
+						}
+					}
+					tmem_st16(aLane + ls * aStageCols + 16 * half, hi);
+					if(threeX) tmem_st16(aLane + ls * aStageCols + 32 + 16 * half, lo);
 				}
-				fence_proxy_async_smem();
-				mbar_arrive(&cvtFullBar[slot]);
+				if(ct == 0) trace(p, TR_COPY_A_DONE, i);
+				uint8_t* rawB = raw + A_TILE_BYTES;
+				uint8_t* loB = loRing + static_cast<size_t>(ls) * B_TILE_BYTES;
+#pragma unroll
+				for(int q = 0; q < (preB ? 0 : B_PIECES); ++q) {
+					const uint32_t off = swz(row0 + 16 * q, chunk0);
+					float4 v = *reinterpret_cast<const float4*>(rawB + off);
+					if(threeX) {
+						float4 l;
+						l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+						l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+						l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+						l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+						*reinterpret_cast<float4*>(loB + off) = l;
+					} else {
+						v.x = to_tf32(v.x); v.y = to_tf32(v.y); v.z = to_tf32(v.z); v.w = to_tf32(v.w);
+						*reinterpret_cast<float4*>(rawB + off) = v;
+					}
+				}
+				if(ct == 0) trace(p, TR_COPY_B_DONE, i);
+				tmem_st_wait();
 			}
+			if(!preB) fence_proxy_async_smem();
+			tc_fence_before_sync();
+			__syncwarp();
+			if(lane == 0) mbar_arrive(&cvtFullBar[ls]);
+			if(ct == 0) trace(p, TR_CVT_DONE, i);
+			if(++slot == rawSlots) { slot = 0; rawParity ^= 1; }
 		}
 	} else if(warp == MMA_WARP) {
 		// ------------------------------------------------------------------ MMA issuer
@@ -365,42 +462,41 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			const uint32_t idesc = umma_idesc_tf32(BM, BN);
 			bool ok = true;
 			int it = 0;
+			int slot = 0;
 			for(int local = 0; local < myTiles && ok; ++local) {
-				const int set = local % accSets;
-				const uint32_t accParity = ((local / accSets) & 1) ^ 1;
+				const int set = local & 1;
+				const uint32_t accParity = ((local >> 1) & 1) ^ 1;
 				if(!mbar_wait_bounded(&accEmptyBar[set], accParity, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
+				if(FOLD && !mbar_wait_bounded(crossEmptyBar, (local & 1) ^ 1, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
 				tc_fence_after_sync();
-				const uint32_t accMain = tmemBase + set * accStride;
-				const uint32_t accCross = accMain + ACC_COLS;
+				const uint32_t accMain = tmemBase + set * ACC_COLS;
+				const uint32_t accCross = tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS);
 				for(int kb = 0; kb < numKb; ++kb, ++it) {
-					const int slot = it % rawSlots;
 					const int ls = it % LO_SLOTS;
-					uint64_t* ready = threeX ? &cvtFullBar[ls] : &cvtFullBar[slot];
-					const uint32_t parity = threeX ? (it / LO_SLOTS) & 1 : (it / rawSlots) & 1;
-					if(!mbar_wait_bounded(ready, parity, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
+					if(!mbar_wait_bounded(&cvtFullBar[ls], (it / LO_SLOTS) & 1, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
 					tc_fence_after_sync();
-					const uint32_t aHi = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES);
-					const uint32_t bHi = aHi + A_TILE_BYTES;
-					const uint32_t aLo = smem_u32(loRing + static_cast<size_t>(ls) * SLOT_BYTES);
-					const uint32_t bLo = aLo + A_TILE_BYTES;
+					const uint32_t aHi = tmemBase + aBaseCol + ls * aStageCols;   // tensor-memory columns of this stage
+					const uint32_t aLo = aHi + 32;
+					const uint32_t bHi = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES) + A_TILE_BYTES;
+					const uint32_t bLo = loByTma ? bHi + B_TILE_BYTES : smem_u32(loRing + static_cast<size_t>(ls) * B_TILE_BYTES);
 					const int kLeft = p.K - kb * BK;
 					const int kSteps = kLeft >= BK ? BK / 8 : (kLeft + 7) / 8;
-					for(int ks = 0; ks < kSteps && !(p.debugSkip & 1); ++ks) {
+					for(int ks = 0; ks < kSteps; ++ks) {
 						const uint32_t kOff = static_cast<uint32_t>(ks) * 32u; // 8 floats inside the 128-byte row
-						const uint64_t dAhi = umma_desc_k128(aHi + kOff);
+						const uint32_t aCol = static_cast<uint32_t>(ks) * 8u;  // 8 columns of the A stage
 						const uint64_t dBhi = umma_desc_k128(bHi + kOff);
 						const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
 						if(threeX) {
-							const uint64_t dAlo = umma_desc_k128(aLo + kOff);
 							const uint64_t dBlo = umma_desc_k128(bLo + kOff);
-							umma_tf32_ss(accCross, dAlo, dBhi, idesc, acc);
-							umma_tf32_ss(accCross, dAhi, dBlo, idesc, 1u);
+							umma_tf32_ts(accCross, aLo + aCol, dBhi, idesc, acc);
+							umma_tf32_ts(accCross, aHi + aCol, dBlo, idesc, 1u);
 						}
-						umma_tf32_ss(accMain, dAhi, dBhi, idesc, acc);
+						umma_tf32_ts(accMain, aHi + aCol, dBhi, idesc, acc);
 					}
 					umma_commit(&rawEmptyBar[slot]);
-					if(threeX) umma_commit(&loEmptyBar[ls]);
+					umma_commit(&loEmptyBar[ls]);
 					trace(p, TR_MMA_ISSUED, it);
+					if(++slot == rawSlots) slot = 0;
 				}
 				if(ok) umma_commit(&accFullBar[set]);
 				trace(p, TR_MMA_TILE_COMMITTED, local);
@@ -426,14 +522,18 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		const bool vec = p.c_vec != 0;
 		float* biasStrip = reinterpret_cast<float*>(staging + EPI_WARPS * STAGING_BYTES_PER_WARP) + ew * 64;
 		int biasCol = -1;
+		// uniform epilogue options, decided once: the fast store path has no branch per element
+		const bool fastStore = vec && p.accumulate == 0 && p.act != NB200_ACT_HSWISH;
+		const bool clampOn = p.act == NB200_ACT_RELU;
+		const float clampHi = p.act_param > 0.f ? p.act_param : __int_as_float(0x7f800000);
 		bool ok = true;
 		for(int local = 0; local < myTiles && ok; ++local) {
 			const int tile = blockIdx.x + local * gridDim.x;
 			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
 			float* __restrict__ C = p.C + tc.batch * p.strideC;
 			const float* __restrict__ R = p.residual != nullptr ? p.residual + tc.batch * p.strideC : nullptr;
-			const int set = local % accSets;
-			const uint32_t accParity = (local / accSets) & 1;
+			const int set = local & 1;
+			const uint32_t accParity = (local >> 1) & 1;
 			const int rowBase = tc.m0 + quad * 32;
 			const int colBase = tc.n0 + half * HALF_COLS;
 			const bool useRes = vec && R != nullptr;
@@ -473,42 +573,56 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			if(!mbar_wait_bounded_warp(&accFullBar[set], accParity, abortFlag, p.status, SITE_ACC_FULL)) { ok = false; break; }
 			tc_fence_after_sync();
 			if(ew == 0 && lane == 0) trace(p, TR_EPI_ACC_FULL, local);
-			const uint32_t accMain = tmemBase + set * accStride + (static_cast<uint32_t>(quad * 32) << 16)
-				+ static_cast<uint32_t>(half * HALF_COLS);
-			if(useRes) load_res(0, res);
-
-			// accumulators leave TMEM in groups of up to 32 columns (main and cross issued together, one wait), each
-			// group then goes through the 16-column transpose / store passes
+			const uint32_t laneCol = (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * HALF_COLS);
+			const uint32_t accMain = tmemBase + set * ACC_COLS + laneCol;
+			const uint32_t accCross = tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS) + laneCol;
+			if(useRes && !FOLD) load_res(0, res);
+			if(FOLD) {
+				// one cross accumulator serves all tiles: add it into the main accumulator in place and hand it back, so
+				// that the cross MMAs of the next tile wait for a few hundred cycles instead of for the whole epilogue
 #pragma unroll
-			for(int g0 = 0; g0 < CHUNKS; g0 += 2) {
-				const bool wide = g0 + 1 < CHUNKS; // 32 columns in this group, else 16
-				uint32_t vm[32], vx[32];
-				if(wide) {
-					tmem_ld32_issue(accMain + g0 * 16, vm);
-					if(threeX) tmem_ld32_issue(accMain + ACC_COLS + g0 * 16, vx);
-				} else {
-					tmem_ld16_issue(accMain + g0 * 16, vm);
-					if(threeX) tmem_ld16_issue(accMain + ACC_COLS + g0 * 16, vx);
+				for(int g = 0; g < CHUNKS; ++g) {
+					uint32_t a[16], b[16];
+					tmem_ld16_issue(accMain + g * 16, a);
+					tmem_ld16_issue(accCross + g * 16, b);
+					tmem_ld_wait();
+#pragma unroll
+					for(int i = 0; i < 16; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(b[i]));
+					tmem_st16(accMain + g * 16, a);
 				}
+				tmem_st_wait();
+				tc_fence_before_sync();
+				__syncwarp();
+				if(lane == 0) mbar_arrive(crossEmptyBar);
+				if(useRes) load_res(0, res);
+			}
+
+			// accumulators leave TMEM 16 columns at a time (main and cross issued together, one wait); each chunk then
+			// goes through the shared-memory transpose and the coalesced store pass
+#pragma unroll
+			for(int g0 = 0; g0 < CHUNKS; ++g0) {
+				uint32_t vm[16], vx[16];
+				tmem_ld16_issue(accMain + g0 * 16, vm);
+				if(threeX && !FOLD) tmem_ld16_issue(accCross + g0 * 16, vx);
 				tmem_ld_wait();
-				if(g0 + 2 >= CHUNKS) {
+				if(g0 == 0 && ew == 0 && lane == 0) trace(p, TR_EPI_LD0, local);
+				if(g0 + 1 >= CHUNKS) {
 					// last TMEM read of this tile: hand the accumulator set back to the MMA warp
 					tc_fence_before_sync();
-					mbar_arrive(&accEmptyBar[set]);
+					__syncwarp();
+					if(lane == 0) mbar_arrive(&accEmptyBar[set]);
 					if(ew == 0 && lane == 0) trace(p, TR_EPI_TMEM_READ, local);
 				}
-#pragma unroll
-				for(int sub = 0; sub < 2; ++sub) {
-					const int ch = g0 + sub;
-					if(ch >= CHUNKS) break;
+				{
+					const int ch = g0;
 					const int n = colBase + ch * 16 + c4 * 4; // first of this lane's four columns in the transposed phase
 					const bool colsFull = n + 4 <= p.N;
 					if(useRes && ch + 1 < CHUNKS) load_res(ch + 1, resNext);
 					float v[16];
 #pragma unroll
 					for(int i = 0; i < 16; ++i) {
-						v[i] = __uint_as_float(vm[sub * 16 + i]);
-						if(threeX) v[i] += __uint_as_float(vx[sub * 16 + i]);
+						v[i] = __uint_as_float(vm[i]);
+						if(threeX && !FOLD) v[i] += __uint_as_float(vx[i]);
 					}
 					// transpose through shared memory: row-per-lane -> 8 rows x 64 B per warp access
 #pragma unroll
@@ -517,26 +631,41 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 							make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
 					}
 					__syncwarp();
+					if(ch == 0 && ew == 0 && lane == 0) trace(p, TR_EPI_STS0, local);
 					const float4 bias4 = *reinterpret_cast<const float4*>(biasStrip + ch * 16 + c4 * 4);
+					// all four transposed reads first: the stores below are generic-address stores, which the compiler will
+					// not move shared-memory loads across
+					float4 ov[4];
 #pragma unroll
 					for(int i = 0; i < 4; ++i) {
 						const int r = 8 * i + rowInGroup;
-						const int m = rowBase + r;
-						float4 o = *reinterpret_cast<const float4*>(stg + r * 64 + ((c4 ^ ((r >> 1) & 3)) << 4));
-						if(m >= p.M || n >= p.N || (p.debugSkip & 4)) continue;
-						o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
-						float* dst = C + static_cast<size_t>(m) * p.ldc + n;
-						if(vec && colsFull) {
-							if(R != nullptr) { o.x += res[i].x; o.y += res[i].y; o.z += res[i].z; o.w += res[i].w; }
-							o.x = apply_act(o.x, p.act, p.act_param); o.y = apply_act(o.y, p.act, p.act_param);
-							o.z = apply_act(o.z, p.act, p.act_param); o.w = apply_act(o.w, p.act, p.act_param);
-							if(p.accumulate) {
-								const float4 cv = *reinterpret_cast<const float4*>(dst);
-								o.x += cv.x; o.y += cv.y; o.z += cv.z; o.w += cv.w;
+						ov[i] = *reinterpret_cast<const float4*>(stg + r * 64 + ((c4 ^ ((r >> 1) & 3)) << 4));
+					}
+					if(fastStore && colsFull) {
+						// the common case, free of branches: bias, optional residual, clamp by select, predicated 16-byte store
+#pragma unroll
+						for(int i = 0; i < 4; ++i) {
+							const int m = rowBase + 8 * i + rowInGroup;
+							float4 o = ov[i];
+							o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
+							if(useRes) { o.x += res[i].x; o.y += res[i].y; o.z += res[i].z; o.w += res[i].w; }
+							o.x = clampOn ? fminf(fmaxf(o.x, 0.f), clampHi) : o.x;
+							o.y = clampOn ? fminf(fmaxf(o.y, 0.f), clampHi) : o.y;
+							o.z = clampOn ? fminf(fmaxf(o.z, 0.f), clampHi) : o.z;
+							o.w = clampOn ? fminf(fmaxf(o.w, 0.f), clampHi) : o.w;
+							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
+							if(m < p.M) {
+								asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
 							}
-							*reinterpret_cast<float4*>(dst) = o;
-						} else {
-							const float e[4] = { o.x, o.y, o.z, o.w };
+						}
+					} else {
+#pragma unroll
+						for(int i = 0; i < 4; ++i) {
+							const int m = rowBase + 8 * i + rowInGroup;
+							const float4 o = ov[i];
+							if(m >= p.M || n >= p.N) continue;
+							const float e[4] = { o.x + bias4.x, o.y + bias4.y, o.z + bias4.z, o.w + bias4.w };
+							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
 #pragma unroll
 							for(int t = 0; t < 4; ++t) {
 								if(n + t < p.N) {
@@ -551,6 +680,8 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					}
 #pragma unroll
 					for(int i = 0; i < 4; ++i) res[i] = resNext[i];
+					if(ch == 0 && ew == 0 && lane == 0) trace(p, TR_EPI_STG0, local);
+					if(ch == 1 && ew == 0 && lane == 0) trace(p, TR_EPI_CH1, local);
 					__syncwarp(); // the staging slice is rewritten by the next column chunk
 				}
 			}
@@ -650,9 +781,10 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	p.traceSteps = g_traceSteps;
 	p.debugSkip = g_debugSkip;
 	const bool threeX = p.precision == NB200_PREC_3XTF32;
-	const int slotBytes = A_TILE_BYTES + BN * BK * 4;
+	const bool preB = p.b_ready != 0;
+	const int slotBytes = A_TILE_BYTES + BN * BK * 4 * (preB && threeX ? 2 : 1);
 	const int fixedBytes = EPI_WARPS * STAGING_BYTES_PER_WARP + EPI_WARPS * 256 /*bias strips*/ + 512 /*barriers*/ + 1024 /*alignment slack*/
-		+ (threeX ? LO_SLOTS * slotBytes : 0);
+		+ (threeX && !preB ? LO_SLOTS * BN * BK * 4 : 0);
 	// as many raw slots as fit the 227 KB a CTA may use: the copies run that many K blocks ahead
 	int rawSlots = (227 * 1024 - fixedBytes) / slotBytes;
 	if(rawSlots > MAX_RAW_SLOTS) rawSlots = MAX_RAW_SLOTS;
@@ -664,8 +796,12 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	int dev = 0;
 	if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NB200_ENODEVICE;
 	if(!attrSet[dev]) {
-		if(cudaFuncSetAttribute(contraction_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
-			!= cudaSuccess) {
+		const int bytes = 227 * 1024;
+		const cudaFuncAttribute attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+		if(cudaFuncSetAttribute(contraction_tc_kernel<BN, true, true>, attr, bytes) != cudaSuccess
+			|| cudaFuncSetAttribute(contraction_tc_kernel<BN, false, true>, attr, bytes) != cudaSuccess
+			|| cudaFuncSetAttribute(contraction_tc_kernel<BN, true, false>, attr, bytes) != cudaSuccess
+			|| cudaFuncSetAttribute(contraction_tc_kernel<BN, false, false>, attr, bytes) != cudaSuccess) {
 			cudaGetLastError();
 			return NB200_ENODEVICE;
 		}
@@ -680,9 +816,10 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	const int grid = numTiles < sms ? static_cast<int>(numTiles) : sms;
 	// operands that TMA can describe are loaded by it; everything else (odd alignment, column-major B, channel counts
 	// that do not fill a 32-wide K block) is gathered with cp.async by the copy warps
-	alignas(64) CUtensorMap mapA, mapB;
+	alignas(64) CUtensorMap mapA, mapB, mapBlo;
 	memset(&mapA, 0, sizeof(mapA));
 	memset(&mapB, 0, sizeof(mapB));
+	memset(&mapBlo, 0, sizeof(mapBlo));
 	p.a_tma = 0;
 	p.b_tma = 0;
 	if(!(g_debugSkip & 16)) {
@@ -695,8 +832,19 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 		}
 		if(p.b_mode == B_ROWS && p.b_vec && make_rows_map(&mapB, p.B, p.K, p.N, p.ldb, batch, p.strideB, BN)) p.b_tma = 1;
 	}
-	contraction_tc_kernel<BN><<<grid, THREADS, smemBytes, stream>>>(p, static_cast<int>(numTiles),
-		static_cast<int>(nTiles), static_cast<int>(tilesPerBatch), rawSlots, mapA, mapB);
+	// a prepared B is only usable by the all-TMA pipeline
+	if(preB && (!p.a_tma || !p.b_tma || (threeX && !make_rows_map(&mapBlo, p.Blo, p.K, p.N, p.ldb, batch, p.strideB, BN)))) {
+		return NB200_EINVAL;
+	}
+	const int nt = static_cast<int>(numTiles), nn = static_cast<int>(nTiles), tpb = static_cast<int>(tilesPerBatch);
+	const bool gather = p.a_tma == 0 || p.b_tma == 0;
+	if(threeX) {
+		if(gather) contraction_tc_kernel<BN, true, true><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
+		else contraction_tc_kernel<BN, false, true><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
+	} else {
+		if(gather) contraction_tc_kernel<BN, true, false><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
+		else contraction_tc_kernel<BN, false, false><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
+	}
 	count_launch();
 	return check_launch();
 }
