@@ -85,6 +85,65 @@ size_t prepared_filter_floats(long long k, long long r, long long s, long long c
 	return static_cast<size_t>((k * r * s * c + 3) / 4 * 4);
 }
 
+// Row-window form of a convolution with few channels (the network stem): the image is copied once with its spatial
+// zero padding and its channels widened to a multiple of four, so that the S taps of one filter row are ONE contiguous
+// run of at most 32 floats per output position; the filter rows are widened to 32 floats with zeros.
+struct WindowPlan {
+	int c4, taps, hp, wp; // padded channels, pixels per 128-byte window, padded image height and width
+	size_t imageFloats, filterFloats;
+};
+
+bool plan_row_window(const nb200_conv_desc* d, WindowPlan* w)
+{
+	if(d->c <= 0 || d->c >= 32 || d->dil_h != 1 || d->dil_w != 1 || d->wo > 128 || d->wo <= 0 || d->ho <= 0) return false;
+	w->c4 = (d->c + 3) / 4 * 4;
+	if(d->s * w->c4 > 32 || 32 % w->c4 != 0) return false;
+	if(d->r == 1 && d->s == 1) return false; // a pointwise convolution is a plain matrix product already
+	w->taps = 32 / w->c4;
+	const int needW = (d->wo - 1) * d->stride_w + w->taps, needH = (d->ho - 1) * d->stride_h + d->r;
+	w->wp = d->w + 2 * d->pad_w > needW ? d->w + 2 * d->pad_w : needW;
+	w->hp = d->h + 2 * d->pad_h > needH ? d->h + 2 * d->pad_h : needH;
+	w->imageFloats = static_cast<size_t>(d->batch) * w->hp * w->wp * w->c4;
+	w->filterFloats = static_cast<size_t>(d->k) * d->r * 32;
+	return w->imageFloats <= 0x7fffffffULL;
+}
+
+// y[n][yp][xp][0..c4) = x[n][yp - padH][xp - padW][0..c) inside the image, 0 elsewhere
+__global__ void __launch_bounds__(256) pad_image_kernel(const float* __restrict__ x, float* __restrict__ y, int batch,
+	int h, int w, int c, int hp, int wp, int c4, int padH, int padW)
+{
+	const long long total = static_cast<long long>(batch) * hp * wp * (c4 / 4);
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+		const int q = static_cast<int>(i % (c4 / 4));
+		long long px = i / (c4 / 4);
+		const int xp = static_cast<int>(px % wp); px /= wp;
+		const int yp = static_cast<int>(px % hp);
+		const int n = static_cast<int>(px / hp);
+		const int sy = yp - padH, sx = xp - padW;
+		float v[4] = { 0.f, 0.f, 0.f, 0.f };
+		if(sy >= 0 && sy < h && sx >= 0 && sx < w) {
+			const float* src = x + ((static_cast<long long>(n) * h + sy) * w + sx) * c;
+#pragma unroll
+			for(int e = 0; e < 4; ++e) if(4 * q + e < c) v[e] = __ldg(src + 4 * q + e);
+		}
+		reinterpret_cast<float4*>(y)[i] = make_float4(v[0], v[1], v[2], v[3]);
+	}
+}
+
+// y[k][r][j] for j < 32: tap j / c4, channel j % c4 of filter row r, zero beyond the real taps and channels
+__global__ void __launch_bounds__(256) widen_filter_rows_kernel(const float* __restrict__ f, float* __restrict__ y,
+	int kCount, int r, int s, int c, int c4)
+{
+	const int total = kCount * r * 32;
+	for(int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+		const int j = i & 31;
+		const int row = i >> 5; // k * r + filter row
+		const int tap = j / c4, ch = j - tap * c4;
+		y[i] = (tap < s && ch < c) ? __ldg(f + (static_cast<long long>(row) * s + tap) * c + ch) : 0.f;
+	}
+}
+
 bool wants_channel_padding(const nb200_conv_desc* d)
 {
 	const bool pointwise = d->r == 1 && d->s == 1 && d->pad_h == 0 && d->pad_w == 0 && d->stride_h == 1 && d->stride_w == 1;
@@ -98,6 +157,8 @@ size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* d)
 	if(d == nullptr || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0) return 0;
 	const size_t c4 = static_cast<size_t>((d->c + 3) / 4 * 4);
 	// the prepared filter (always), and for channel counts that are not a multiple of four the widened image and filter
+	WindowPlan win;
+	if(plan_row_window(d, &win)) return win.imageFloats + 2 * win.filterFloats + 16;
 	size_t floats = prepared_filter_floats(d->k, d->r, d->s, static_cast<long long>(c4)) + 8;
 	if(wants_channel_padding(d)) floats += (static_cast<size_t>(d->batch) * d->h * d->w + static_cast<size_t>(d->k) * d->r * d->s) * c4 + 8;
 	return floats;
@@ -161,6 +222,40 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 	float* scratch, const nb200_epilogue* epi, int precision)
 {
 	if(d == nullptr) return NB200_EINVAL;
+	WindowPlan win;
+	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && d->batch > 0 && d->k > 0 && d->r > 0 && d->s > 0
+		&& d->h > 0 && d->w > 0 && d->stride_h > 0 && d->stride_w > 0 && d->pad_h >= 0 && d->pad_w >= 0
+		&& d->ho == 1 + (d->h - d->r + 2 * d->pad_h) / d->stride_h && d->wo == 1 + (d->w - d->s + 2 * d->pad_w) / d->stride_w
+		&& plan_row_window(d, &win) && x != nullptr && filter != nullptr && y != nullptr) {
+		if(device_status_word() == nullptr) return NB200_ENODEVICE;
+		float* xs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
+		float* fs = xs + (win.imageFloats + 3) / 4 * 4;
+		float* fprep = fs + win.filterFloats;
+		pad_image_kernel<<<grid_for(static_cast<long long>(win.imageFloats / 4), 256, 16), 256, 0, as_stream(stream)>>>(
+			x, xs, d->batch, d->h, d->w, d->c, win.hp, win.wp, win.c4, d->pad_h, d->pad_w);
+		widen_filter_rows_kernel<<<grid_for(static_cast<long long>(win.filterFloats), 256, 8), 256, 0, as_stream(stream)>>>(
+			filter, fs, d->k, d->r, d->s, d->c, win.c4);
+		prepare_filter_kernel<<<grid_for(static_cast<long long>(win.filterFloats), 256, 8), 256, 0, as_stream(stream)>>>(
+			fs, fprep, static_cast<long long>(win.filterFloats), precision == NB200_PREC_3XTF32 ? 0 : 1);
+		count_launch(3);
+		int rc = check_launch();
+		if(rc != NB200_OK) return rc;
+		ContractionParams p = {};
+		p.A = xs; p.B = precision == NB200_PREC_3XTF32 ? fs : fprep; p.C = y;
+		p.Blo = precision == NB200_PREC_3XTF32 ? fprep : nullptr;
+		p.b_ready = 1;
+		p.M = d->batch * d->ho * d->wo; p.N = d->k; p.K = d->r * 32;
+		p.lda = 0; p.ldb = p.K; p.ldc = d->k;
+		p.a_mode = A_CONV_WINDOW; p.b_mode = B_ROWS; p.a_vec = 1; p.b_vec = 1;
+		p.tileM = d->wo;
+		p.H = win.hp; p.W = win.wp; p.Cin = win.c4; p.Ho = d->ho; p.Wo = d->wo; p.S = win.taps;
+		p.padH = 0; p.padW = 0; p.strH = d->stride_h; p.strW = d->stride_w; p.dilH = 1; p.dilW = 1;
+		fill_epilogue(p, epi);
+		if(p.residual == nullptr) p.ldr = d->k;
+		rc = run(p, 1, stream, precision);
+		if(rc != NB200_EINVAL) return rc;
+		// the tensor maps could not be built: fall through to the general paths below
+	}
 	if(scratch != nullptr && d->c > 0 && d->batch > 0 && wants_channel_padding(d) && precision != NB200_PREC_FP32_SIMT) {
 		// channel counts that are not a multiple of four (the 3-channel stem) would be gathered element by element;
 		// with scratch the image and the filter are first widened to 4-channel pixels (zeros in the new channels add

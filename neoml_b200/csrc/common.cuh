@@ -285,6 +285,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap,
 		"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
 		::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst_smem, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
+	int c3, int c4)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+		::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+		: "memory");
+}
 // im2col load from a channels-last image map (C, W, H, N): `pixelsPerColumn` output positions starting at the window
 // origin (w, h) of image n, channels [c, c + channelsPerPixel), filter tap offset (off_w, off_h) in input pixels.
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst_smem, const void* tmap, uint64_t* bar, int c, int w,

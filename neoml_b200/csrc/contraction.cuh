@@ -6,7 +6,7 @@
 
 namespace nb200 {
 
-enum { A_ROWS = 0, A_CONV_TAP = 1 };
+enum { A_ROWS = 0, A_CONV_TAP = 1, A_CONV_WINDOW = 2 };
 enum { B_ROWS = 0, B_COLS = 1 };
 
 struct ContractionParams {
@@ -21,11 +21,16 @@ struct ContractionParams {
 	int a_mode; // A_ROWS: element (m,k) at A[m*lda + k]
 	            // A_CONV_TAP: channels-last image gather, k = (r*S + s)*Cin + c; a_vec says whether Cin % 4 == 0 and the
 	            //             image is 16-byte aligned (then four consecutive k share a filter tap and move as 16 bytes)
+	            // A_CONV_WINDOW: tensor-core kernel only.  A is an image already padded in space and channels whose filter
+	            //             rows span at most 32 floats: K block kb = filter row kb, and row m's 32 floats are the
+	            //             contiguous window that starts at padded pixel (oy*strH + kb, ox*strW).  One tile = the Wo (<= 128)
+	            //             positions of one output row (tileM = Wo); H, W are the padded sizes, Cin the padded channels
+	int tileM;  // output rows a tile advances by (128 except for A_CONV_WINDOW); rows beyond it are computed but not stored
 	int b_mode; // B_ROWS: element (n,k) at B[n*ldb + k];  B_COLS: element (n,k) at B[k*ldb + n]
 	int a_vec;  // 16-byte loads are legal for A (base and all row starts 16-byte aligned)
 	int b_vec;
 	int c_vec;  // 16-byte stores legal for C (and loads for residual)
-	int a_tma;  // A arrives by TMA (1: tiled rows, 2: im2col); the launcher decides, 0 = cp.async gather
+	int a_tma;  // A arrives by TMA (1: tiled rows, 2: im2col, 3: row windows); the launcher decides, 0 = cp.async gather
 	int b_tma;  // B arrives by TMA (tiled rows)
 	const float* Blo; // optional: lo(B) = B - trunc_tf32(B) prepared by the caller (same shape and strides as B); with it,
 	                  // and for plain TF32 a pre-rounded B passed as B itself, the kernel does no per-step work on B

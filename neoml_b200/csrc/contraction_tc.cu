@@ -42,12 +42,9 @@ constexpr int COPY_WARPS = 2;
 constexpr int COPY_THREADS = COPY_WARPS * 32;
 constexpr int MMA_WARP = 2;            // warp 3 is a spare that goes straight to the final barrier
 constexpr int CVT_WARP0 = 4;
-constexpr int CVT_WARPS = 4;
-constexpr int CVT_THREADS = CVT_WARPS * 32;
-constexpr int EPI_WARP0 = CVT_WARP0 + CVT_WARPS;
-constexpr int EPI_WARPS = 8;
-constexpr int EPI_THREADS = EPI_WARPS * 32;
-constexpr int THREADS = (EPI_WARP0 + EPI_WARPS) * 32;
+constexpr int WORK_WARPS = 12;         // warps 4..15 are split between converting and the epilogue: 4 + 8 or 8 + 4
+constexpr int MAX_EPI_WARPS = 8;
+constexpr int THREADS = (CVT_WARP0 + WORK_WARPS) * 32;
 constexpr int A_TILE_BYTES = BM * BK * 4; // 16 KB
 constexpr int STAGING_BYTES_PER_WARP = 32 * 64; // 32 rows x 16 floats
 constexpr int LO_SLOTS = 2;              // B-lo tiles in shared memory == A stages in tensor memory
@@ -82,13 +79,13 @@ struct TileCoord {
 	int m0, n0, batch;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int nTiles, int tilesPerBatch, int bn)
+__device__ __forceinline__ TileCoord tile_coord(int tile, int nTiles, int tilesPerBatch, int bn, int tileM)
 {
 	TileCoord t;
 	t.batch = tile / tilesPerBatch;
 	const int r = tile - t.batch * tilesPerBatch;
 	const int mTile = r / nTiles;
-	t.m0 = mTile * BM;
+	t.m0 = mTile * tileM;
 	t.n0 = (r - mTile * nTiles) * bn;
 	return t;
 }
@@ -109,6 +106,10 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
 	constexpr bool threeX = THREEX; // 3xTF32 split (three MMAs per product) or plain TF32
+	constexpr int CVT_WARPS = 4; // eight (the two groups splitting a row's K range) measured no faster: the MMA issue rate bounds a step
+	constexpr int CVT_THREADS = CVT_WARPS * 32;
+	constexpr int EPI_WARP0 = CVT_WARP0 + CVT_WARPS;
+	constexpr int EPI_WARPS = WORK_WARPS - CVT_WARPS;
 	constexpr int B_TILE_BYTES = BN * BK * 4;
 	// B needs no work in the kernel when the caller prepared it (lo(B) in global memory for 3xTF32, a pre-rounded B for
 	// plain TF32); a raw slot then also receives the lo tile by TMA and no lo ring exists
@@ -136,7 +137,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	uint8_t* rawRing = smem;
 	uint8_t* loRing = rawRing + static_cast<size_t>(rawSlots) * SLOT_BYTES;
 	uint8_t* staging = loRing + (threeX && !preB ? LO_SLOTS * B_TILE_BYTES : 0);
-	uint64_t* rawFullBar = reinterpret_cast<uint64_t*>(staging + EPI_WARPS * STAGING_BYTES_PER_WARP + EPI_WARPS * 256);
+	uint64_t* rawFullBar = reinterpret_cast<uint64_t*>(staging + MAX_EPI_WARPS * STAGING_BYTES_PER_WARP + MAX_EPI_WARPS * 256);
 	uint64_t* rawEmptyBar = rawFullBar + MAX_RAW_SLOTS;
 	uint64_t* cvtFullBar = rawEmptyBar + MAX_RAW_SLOTS;
 	uint64_t* loEmptyBar = cvtFullBar + MAX_RAW_SLOTS;
@@ -195,9 +196,13 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			bool ok = true;
 			const int hw = p.Ho * p.Wo;
 			for(int local = 0; local < myTiles && ok; ++local, tile += gridDim.x) {
-				const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
+				const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN, p.tileM);
 				int w0 = 0, h0 = 0, img = 0;
-				if(p.a_tma == 2) {
+				if(p.a_tma == 3) {
+					const int outRow = tc.m0 / p.tileM; // = image * Ho + oy
+					img = outRow / p.Ho;
+					h0 = outRow - img * p.Ho;
+				} else if(p.a_tma == 2) {
 					img = tc.m0 / hw;
 					const int rem = tc.m0 - img * hw;
 					const int oy = rem / p.Wo;
@@ -212,6 +217,8 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					mbar_arrive_expect_tx(&rawFullBar[slot], SLOT_BYTES);
 					if(p.a_tma == 1) {
 						tma_load_3d(aTile, &mapA, &rawFullBar[slot], kb * BK, tc.m0, tc.batch);
+					} else if(p.a_tma == 3) {
+						tma_load_5d(aTile, &mapA, &rawFullBar[slot], 0, 0, kb, h0, img);
 					} else {
 						tma_load_im2col_4d(aTile, &mapA, &rawFullBar[slot], c0, w0, h0, img,
 							static_cast<uint16_t>(fs * p.dilW), static_cast<uint16_t>(fr * p.dilH));
@@ -238,7 +245,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		int step = 0;
 		bool ok = true;
 		for(int local = 0; local < myTiles && ok; ++local, tile += gridDim.x) {
-			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
+			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN, p.tileM);
 			const float* A = p.A + tc.batch * p.strideA;
 			const float* B = p.B + tc.batch * p.strideB;
 			// where this thread's rows start: an element offset into A (row-major) or the image origin (convolution)
@@ -389,9 +396,14 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		// tensor memory, which leaves shared-memory bandwidth to the B operand and the copies.
 		// B: 3xTF32 writes lo(B) into a shared-memory lo slot (the raw slot itself serves as hi: the tensor core
 		// ignores the low mantissa bits); plain TF32 rounds the raw B tile in place.
-		constexpr int B_PIECES = BN / 16;
+		// With eight converter warps the two groups of four split a row's 32 K indices in halves.
+		constexpr int K_PER_THREAD = CVT_WARPS == 8 ? 16 : 32;
+		constexpr int B_ROWS_PER_PASS = CVT_THREADS / 8;
+		constexpr int B_PIECES = BN / B_ROWS_PER_PASS;
 		const int ct = tid - CVT_WARP0 * 32;
 		const int row0 = ct >> 3, chunk0 = ct & 7;
+		const int aRow = (warp & 3) * 32 + lane;                  // the tile row (= tensor-memory lane) of this thread
+		const int kHalf = CVT_WARPS == 8 ? (warp - CVT_WARP0) >> 2 : 0; // which 16 K indices (eight warps only)
 		const uint32_t aLane = tmemBase + (static_cast<uint32_t>((warp & 3) * 32) << 16) + aBaseCol;
 		bool ok = true;
 		int slot = 0;
@@ -408,11 +420,12 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			{
 				// two halves of 16 K indices keep the live registers at 32
 #pragma unroll
-				for(int half = 0; half < 2; ++half) {
+				for(int h2 = 0; h2 < K_PER_THREAD / 16; ++h2) {
+					const int half = K_PER_THREAD == 16 ? kHalf : h2;
 					uint32_t hi[16], lo[16];
 #pragma unroll
 					for(int c = 0; c < 4; ++c) {
-						const float4 v = *reinterpret_cast<const float4*>(raw + swz(ct, 4 * half + c));
+						const float4 v = *reinterpret_cast<const float4*>(raw + swz(aRow, 4 * half + c));
 						const float x[4] = { v.x, v.y, v.z, v.w };
 #pragma unroll
 						for(int e = 0; e < 4; ++e) {
@@ -432,7 +445,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 				uint8_t* loB = loRing + static_cast<size_t>(ls) * B_TILE_BYTES;
 #pragma unroll
 				for(int q = 0; q < (preB ? 0 : B_PIECES); ++q) {
-					const uint32_t off = swz(row0 + 16 * q, chunk0);
+					const uint32_t off = swz(row0 + B_ROWS_PER_PASS * q, chunk0);
 					float4 v = *reinterpret_cast<const float4*>(rawB + off);
 					if(threeX) {
 						float4 l;
@@ -446,7 +459,6 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 						*reinterpret_cast<float4*>(rawB + off) = v;
 					}
 				}
-				if(ct == 0) trace(p, TR_COPY_B_DONE, i);
 				tmem_st_wait();
 			}
 			if(!preB) fence_proxy_async_smem();
@@ -471,27 +483,40 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 				tc_fence_after_sync();
 				const uint32_t accMain = tmemBase + set * ACC_COLS;
 				const uint32_t accCross = tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS);
+				uint32_t acc = 0u; // the first MMA of a tile overwrites the accumulators
 				for(int kb = 0; kb < numKb; ++kb, ++it) {
 					const int ls = it % LO_SLOTS;
 					if(!mbar_wait_bounded(&cvtFullBar[ls], (it / LO_SLOTS) & 1, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
 					tc_fence_after_sync();
+					trace(p, TR_COPY_B_DONE, it); // debug: the MMA thread has seen the converted step
 					const uint32_t aHi = tmemBase + aBaseCol + ls * aStageCols;   // tensor-memory columns of this stage
 					const uint32_t aLo = aHi + 32;
 					const uint32_t bHi = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES) + A_TILE_BYTES;
 					const uint32_t bLo = loByTma ? bHi + B_TILE_BYTES : smem_u32(loRing + static_cast<size_t>(ls) * B_TILE_BYTES);
+					// one descriptor per tile and step; the four 8-wide K slices of a 128-byte row are 32 bytes apart, which
+					// is +2 in the descriptor's address field (units of 16 bytes)
+					const uint64_t dBhi = umma_desc_k128(bHi);
+					const uint64_t dBlo = umma_desc_k128(bLo);
 					const int kLeft = p.K - kb * BK;
-					const int kSteps = kLeft >= BK ? BK / 8 : (kLeft + 7) / 8;
-					for(int ks = 0; ks < kSteps; ++ks) {
-						const uint32_t kOff = static_cast<uint32_t>(ks) * 32u; // 8 floats inside the 128-byte row
-						const uint32_t aCol = static_cast<uint32_t>(ks) * 8u;  // 8 columns of the A stage
-						const uint64_t dBhi = umma_desc_k128(bHi + kOff);
-						const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
-						if(threeX) {
-							const uint64_t dBlo = umma_desc_k128(bLo + kOff);
-							umma_tf32_ts(accCross, aLo + aCol, dBhi, idesc, acc);
-							umma_tf32_ts(accCross, aHi + aCol, dBlo, idesc, 1u);
+					if(kLeft >= BK) {
+#pragma unroll
+						for(int ks = 0; ks < BK / 8; ++ks) {
+							// main between the two cross products: consecutive MMAs never target the same accumulator
+							if(threeX) umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, acc);
+							umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, acc);
+							if(threeX) umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
+							acc = 1u;
 						}
-						umma_tf32_ts(accMain, aHi + aCol, dBhi, idesc, acc);
+					} else {
+						const int kSteps = (kLeft + 7) / 8;
+						for(int ks = 0; ks < kSteps; ++ks) {
+							if(threeX) {
+								umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, acc);
+								umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
+							}
+							umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, acc);
+							acc = 1u;
+						}
 					}
 					umma_commit(&rawEmptyBar[slot]);
 					umma_commit(&loEmptyBar[ls]);
@@ -511,7 +536,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		__syncwarp();
 	} else if(warp >= EPI_WARP0) {
 		// ------------------------------------------------------------------ epilogue
-		constexpr int HALF_COLS = BN / 2;
+		constexpr int HALF_COLS = BN / (EPI_WARPS / 4); // columns per warp: half of the tile with eight warps, all with four
 		constexpr int CHUNKS = HALF_COLS / 16;
 		const int ew = warp - EPI_WARP0;
 		const int quad = warp & 3;  // the TMEM lane quarter this warp may read
@@ -520,7 +545,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		const int rowInGroup = lane >> 2;  // 0..7: which of the 8 rows a warp-wide 16-byte access covers
 		const int c4 = lane & 3;           // which 16-byte piece of the 64-byte row slice
 		const bool vec = p.c_vec != 0;
-		float* biasStrip = reinterpret_cast<float*>(staging + EPI_WARPS * STAGING_BYTES_PER_WARP) + ew * 64;
+		float* biasStrip = reinterpret_cast<float*>(staging + MAX_EPI_WARPS * STAGING_BYTES_PER_WARP) + ew * HALF_COLS;
 		int biasCol = -1;
 		// uniform epilogue options, decided once: the fast store path has no branch per element
 		const bool fastStore = vec && p.accumulate == 0 && p.act != NB200_ACT_HSWISH;
@@ -529,7 +554,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		bool ok = true;
 		for(int local = 0; local < myTiles && ok; ++local) {
 			const int tile = blockIdx.x + local * gridDim.x;
-			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN);
+			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN, p.tileM);
 			float* __restrict__ C = p.C + tc.batch * p.strideC;
 			const float* __restrict__ R = p.residual != nullptr ? p.residual + tc.batch * p.strideC : nullptr;
 			const int set = local & 1;
@@ -537,6 +562,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			const int rowBase = tc.m0 + quad * 32;
 			const int colBase = tc.n0 + half * HALF_COLS;
 			const bool useRes = vec && R != nullptr;
+			const int mEnd = min(p.M, tc.m0 + p.tileM); // rows of this tile that exist and belong to it
 
 			auto load_res = [&](int ch, float4* dst) {
 				const int n = colBase + ch * 16 + c4 * 4;
@@ -544,7 +570,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 				for(int i = 0; i < 4; ++i) {
 					const int m = rowBase + 8 * i + rowInGroup;
 					dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-					if(m < p.M && n + 4 <= p.N) dst[i] = *reinterpret_cast<const float4*>(R + static_cast<size_t>(m) * p.ldr + n);
+					if(m < mEnd && n + 4 <= p.N) dst[i] = *reinterpret_cast<const float4*>(R + static_cast<size_t>(m) * p.ldr + n);
 				}
 			};
 
@@ -654,7 +680,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 							o.z = clampOn ? fminf(fmaxf(o.z, 0.f), clampHi) : o.z;
 							o.w = clampOn ? fminf(fmaxf(o.w, 0.f), clampHi) : o.w;
 							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
-							if(m < p.M) {
+							if(m < mEnd) {
 								asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
 							}
 						}
@@ -663,7 +689,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 						for(int i = 0; i < 4; ++i) {
 							const int m = rowBase + 8 * i + rowInGroup;
 							const float4 o = ov[i];
-							if(m >= p.M || n >= p.N) continue;
+							if(m >= mEnd || n >= p.N) continue;
 							const float e[4] = { o.x + bias4.x, o.y + bias4.y, o.z + bias4.z, o.w + bias4.w };
 							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
 #pragma unroll
@@ -769,6 +795,25 @@ bool make_im2col_map(CUtensorMap* map, const ContractionParams& p, int batchImag
 		CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Padded channels-last image as a 5-D tensor (32 floats of a filter-row window, output column, filter row, output row,
+// image): the windows of neighbouring output columns overlap in memory, which a tensor map expresses as a stride
+// (strW pixels) smaller than the window.  A load delivers one filter row's windows for all columns of one output row.
+bool make_window_map(CUtensorMap* map, const ContractionParams& p, int images, int filterH)
+{
+	lookup_encoders();
+	if(g_encodeTiled == nullptr || !aligned16(p.A) || p.Cin % 4 != 0 || p.Wo > BM) return false;
+	const cuuint64_t pixel = static_cast<cuuint64_t>(p.Cin) * 4;
+	const cuuint64_t dims[5] = { BK, static_cast<cuuint64_t>(p.Wo), static_cast<cuuint64_t>(filterH),
+		static_cast<cuuint64_t>(p.Ho), static_cast<cuuint64_t>(images) };
+	const cuuint64_t strides[4] = { p.strW * pixel, p.W * pixel, static_cast<cuuint64_t>(p.strH) * p.W * pixel,
+		static_cast<cuuint64_t>(p.H) * p.W * pixel };
+	const cuuint32_t box[5] = { BK, BM, 1, 1, 1 };
+	const cuuint32_t elemStrides[5] = { 1, 1, 1, 1, 1 };
+	return g_encodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(p.A), dims, strides, box,
+		elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 unsigned long long* g_traceBuffer = nullptr;
 int g_traceSteps = 0;
 int g_debugSkip = 0;
@@ -783,7 +828,7 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	const bool threeX = p.precision == NB200_PREC_3XTF32;
 	const bool preB = p.b_ready != 0;
 	const int slotBytes = A_TILE_BYTES + BN * BK * 4 * (preB && threeX ? 2 : 1);
-	const int fixedBytes = EPI_WARPS * STAGING_BYTES_PER_WARP + EPI_WARPS * 256 /*bias strips*/ + 512 /*barriers*/ + 1024 /*alignment slack*/
+	const int fixedBytes = MAX_EPI_WARPS * STAGING_BYTES_PER_WARP + MAX_EPI_WARPS * 256 /*bias strips*/ + 512 /*barriers*/ + 1024 /*alignment slack*/
 		+ (threeX && !preB ? LO_SLOTS * BN * BK * 4 : 0);
 	// as many raw slots as fit the 227 KB a CTA may use: the copies run that many K blocks ahead
 	int rawSlots = (227 * 1024 - fixedBytes) / slotBytes;
@@ -807,7 +852,8 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 		}
 		attrSet[dev] = true;
 	}
-	const long long mTiles = (static_cast<long long>(p.M) + BM - 1) / BM;
+	if(p.tileM <= 0 || p.tileM > BM || p.a_mode != A_CONV_WINDOW) p.tileM = BM;
+	const long long mTiles = (static_cast<long long>(p.M) + p.tileM - 1) / p.tileM;
 	const long long nTiles = (p.N + BN - 1) / BN;
 	const long long tilesPerBatch = mTiles * nTiles;
 	const long long numTiles = tilesPerBatch * batch;
@@ -825,6 +871,8 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	if(!(g_debugSkip & 16)) {
 		if(p.a_mode == A_ROWS) {
 			if(p.a_vec && make_rows_map(&mapA, p.A, p.K, p.M, p.lda, batch, p.strideA, BM)) p.a_tma = 1;
+		} else if(p.a_mode == A_CONV_WINDOW) {
+			if(batch == 1 && make_window_map(&mapA, p, p.M / (p.Ho * p.Wo), p.K / BK)) p.a_tma = 3;
 		} else if(p.a_vec && batch == 1) {
 			const int filterH = p.K / (p.S * p.Cin);
 			const int images = p.M / (p.Ho * p.Wo);
@@ -832,19 +880,20 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 		}
 		if(p.b_mode == B_ROWS && p.b_vec && make_rows_map(&mapB, p.B, p.K, p.N, p.ldb, batch, p.strideB, BN)) p.b_tma = 1;
 	}
+	if(p.a_mode == A_CONV_WINDOW && (p.a_tma != 3 || !p.b_tma)) return NB200_EINVAL; // no gather form of this mode
 	// a prepared B is only usable by the all-TMA pipeline
 	if(preB && (!p.a_tma || !p.b_tma || (threeX && !make_rows_map(&mapBlo, p.Blo, p.K, p.N, p.ldb, batch, p.strideB, BN)))) {
 		return NB200_EINVAL;
 	}
 	const int nt = static_cast<int>(numTiles), nn = static_cast<int>(nTiles), tpb = static_cast<int>(tilesPerBatch);
 	const bool gather = p.a_tma == 0 || p.b_tma == 0;
+#define NB200_LAUNCH(G, X) contraction_tc_kernel<BN, G, X><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo)
 	if(threeX) {
-		if(gather) contraction_tc_kernel<BN, true, true><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
-		else contraction_tc_kernel<BN, false, true><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
+		if(gather) NB200_LAUNCH(true, true); else NB200_LAUNCH(false, true);
 	} else {
-		if(gather) contraction_tc_kernel<BN, true, false><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
-		else contraction_tc_kernel<BN, false, false><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo);
+		if(gather) NB200_LAUNCH(true, false); else NB200_LAUNCH(false, false);
 	}
+#undef NB200_LAUNCH
 	count_launch();
 	return check_launch();
 }
