@@ -37,6 +37,8 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
 	return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// True in exactly one lane of a fully converged warp.  Code that issues tcgen05 / TMA instructions this way stays
+// warp-uniform up to the instruction itself, which lets the compiler keep descriptors and addresses in uniform registers.
 __device__ __forceinline__ bool elect_one()
 {
 	uint32_t pred = 0;
@@ -108,15 +110,33 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 	return false;
 }
 
-// Warp-wide form: lane 0 polls, the result is shared by shuffle.  Keeps 31 of 32 lanes off the shared-memory
-// pipeline while a whole warp waits for the same phase (the __shfl_sync also orders the warp's later reads).
+// Warp-wide form for a converged warp: every lane polls (one instruction, one broadcast shared-memory access per
+// try), so there is no divergent branch and no shuffle on the way out; the lanes agree on the outcome by vote.
 __device__ __forceinline__ bool mbar_wait_bounded_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
 	int* status, int site)
 {
-	int done = 0;
-	if((threadIdx.x & 31) == 0) done = mbar_wait_bounded(bar, parity, abort_flag, status, site) ? 1 : 0;
-	done = __shfl_sync(0xffffffffu, done, 0);
-	return done != 0;
+	bool ok = mbar_try_wait(bar, parity);
+	if(!__all_sync(0xffffffffu, ok)) {
+		uint64_t t0 = 0;
+		for(uint32_t it = 1;; ++it) {
+			ok = mbar_try_wait(bar, parity);
+			if(__all_sync(0xffffffffu, ok)) break;
+			if((it & 4095u) == 0u) {
+				const bool aborted = *abort_flag != 0;
+				const uint64_t now = global_timer_ns();
+				if(t0 == 0) t0 = now;
+				const bool late = now - t0 > WAIT_LIMIT_NS;
+				if(__any_sync(0xffffffffu, aborted || late)) {
+					if(late && (threadIdx.x & 31) == 0) {
+						*abort_flag = 1;
+						if(status != nullptr) atomicCAS(status, 0, site);
+					}
+					return false;
+				}
+			}
+		}
+	}
+	return true;
 }
 
 // -- proxy / tcgen05 fences --------------------------------------------------------------------------------------

@@ -188,7 +188,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		// ------------------------------------------------------------------ copy, both operands by TMA
 		// One thread feeds the ring: wait for the slot, announce the bytes, issue the two tensor copies.  All slot,
 		// phase and filter-tap bookkeeping is incremental (no division in the loop).
-		if(tid == 0) {
+		if(warp == 0) { // the whole warp walks the loop, one elected lane issues the copies
 			int tile = blockIdx.x;
 			int slot = 0;
 			uint32_t parity = 1; // the first pass over the ring finds every slot free
@@ -211,9 +211,10 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 				}
 				int c0 = 0, fs = 0, fr = 0; // channel offset inside the filter tap, tap column, tap row
 				for(int kb = 0; kb < numKb; ++kb, ++step) {
-					if(!mbar_wait_bounded(&rawEmptyBar[slot], parity, abortFlag, p.status, SITE_RAW_EMPTY)) { ok = false; break; }
-					trace(p, TR_COPY_SLOT_FREE, step);
+					if(!mbar_wait_bounded_warp(&rawEmptyBar[slot], parity, abortFlag, p.status, SITE_RAW_EMPTY)) { ok = false; break; }
+					if(lane == 0) trace(p, TR_COPY_SLOT_FREE, step);
 					const uint32_t aTile = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES);
+					if(elect_one()) {
 					mbar_arrive_expect_tx(&rawFullBar[slot], SLOT_BYTES);
 					if(p.a_tma == 1) {
 						tma_load_3d(aTile, &mapA, &rawFullBar[slot], kb * BK, tc.m0, tc.batch);
@@ -222,12 +223,16 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					} else {
 						tma_load_im2col_4d(aTile, &mapA, &rawFullBar[slot], c0, w0, h0, img,
 							static_cast<uint16_t>(fs * p.dilW), static_cast<uint16_t>(fr * p.dilH));
-						c0 += BK;
-						if(c0 >= p.Cin) { c0 = 0; if(++fs == p.S) { fs = 0; ++fr; } }
 					}
 					tma_load_3d(aTile + A_TILE_BYTES, &mapB, &rawFullBar[slot], kb * BK, tc.n0, tc.batch);
 					if(loByTma) tma_load_3d(aTile + A_TILE_BYTES + B_TILE_BYTES, &mapBlo, &rawFullBar[slot], kb * BK, tc.n0, tc.batch);
-					trace(p, TR_COPY_ISSUED, step);
+					}
+					__syncwarp();
+					if(p.a_tma == 2) {
+						c0 += BK;
+						if(c0 >= p.Cin) { c0 = 0; if(++fs == p.S) { fs = 0; ++fr; } }
+					}
+					if(lane == 0) trace(p, TR_COPY_ISSUED, step);
 					if(++slot == rawSlots) { slot = 0; parity ^= 1; }
 				}
 			}
@@ -470,7 +475,8 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		}
 	} else if(warp == MMA_WARP) {
 		// ------------------------------------------------------------------ MMA issuer
-		if(lane == 0) {
+		// The whole warp walks the loop (waits are shared by shuffle); one elected lane issues the instructions.
+		{
 			const uint32_t idesc = umma_idesc_tf32(BM, BN);
 			bool ok = true;
 			int it = 0;
@@ -478,17 +484,17 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			for(int local = 0; local < myTiles && ok; ++local) {
 				const int set = local & 1;
 				const uint32_t accParity = ((local >> 1) & 1) ^ 1;
-				if(!mbar_wait_bounded(&accEmptyBar[set], accParity, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
-				if(FOLD && !mbar_wait_bounded(crossEmptyBar, (local & 1) ^ 1, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
+				if(!mbar_wait_bounded_warp(&accEmptyBar[set], accParity, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
+				if(FOLD && !mbar_wait_bounded_warp(crossEmptyBar, (local & 1) ^ 1, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
 				tc_fence_after_sync();
 				const uint32_t accMain = tmemBase + set * ACC_COLS;
 				const uint32_t accCross = tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS);
 				uint32_t acc = 0u; // the first MMA of a tile overwrites the accumulators
 				for(int kb = 0; kb < numKb; ++kb, ++it) {
 					const int ls = it % LO_SLOTS;
-					if(!mbar_wait_bounded(&cvtFullBar[ls], (it / LO_SLOTS) & 1, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
+					if(!mbar_wait_bounded_warp(&cvtFullBar[ls], (it / LO_SLOTS) & 1, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
 					tc_fence_after_sync();
-					trace(p, TR_COPY_B_DONE, it); // debug: the MMA thread has seen the converted step
+					if(lane == 0) trace(p, TR_COPY_B_DONE, it); // debug: the MMA warp has seen the converted step
 					const uint32_t aHi = tmemBase + aBaseCol + ls * aStageCols;   // tensor-memory columns of this stage
 					const uint32_t aLo = aHi + 32;
 					const uint32_t bHi = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES) + A_TILE_BYTES;
@@ -498,35 +504,37 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					const uint64_t dBhi = umma_desc_k128(bHi);
 					const uint64_t dBlo = umma_desc_k128(bLo);
 					const int kLeft = p.K - kb * BK;
-					if(kLeft >= BK) {
+					if(elect_one()) {
+						// main between the two cross products: consecutive MMAs never target the same accumulator
+						if(kLeft >= BK) {
 #pragma unroll
-						for(int ks = 0; ks < BK / 8; ++ks) {
-							// main between the two cross products: consecutive MMAs never target the same accumulator
-							if(threeX) umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, acc);
-							umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, acc);
-							if(threeX) umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
-							acc = 1u;
-						}
-					} else {
-						const int kSteps = (kLeft + 7) / 8;
-						for(int ks = 0; ks < kSteps; ++ks) {
-							if(threeX) {
-								umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, acc);
-								umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
+							for(int ks = 0; ks < BK / 8; ++ks) {
+								const uint32_t a = ks == 0 ? acc : 1u;
+								if(threeX) umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, a);
+								umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, a);
+								if(threeX) umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
 							}
-							umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, acc);
-							acc = 1u;
+						} else {
+							const int kSteps = (kLeft + 7) / 8;
+							for(int ks = 0; ks < kSteps; ++ks) {
+								const uint32_t a = ks == 0 ? acc : 1u;
+								if(threeX) umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, a);
+								umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, a);
+								if(threeX) umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
+							}
 						}
+						umma_commit(&rawEmptyBar[slot]);
+						umma_commit(&loEmptyBar[ls]);
+						if(kb == numKb - 1) umma_commit(&accFullBar[set]);
 					}
-					umma_commit(&rawEmptyBar[slot]);
-					umma_commit(&loEmptyBar[ls]);
-					trace(p, TR_MMA_ISSUED, it);
+					acc = 1u; // every later step of the tile accumulates
+					__syncwarp();
+					if(lane == 0) trace(p, TR_MMA_ISSUED, it);
 					if(++slot == rawSlots) slot = 0;
 				}
-				if(ok) umma_commit(&accFullBar[set]);
-				trace(p, TR_MMA_TILE_COMMITTED, local);
+				if(lane == 0) trace(p, TR_MMA_TILE_COMMITTED, local);
 			}
-			if(!ok) {
+			if(!ok && lane == 0) {
 				// something timed out: give whatever was issued time to finish before TMEM is freed
 				const uint64_t t0 = global_timer_ns();
 				while(global_timer_ns() - t0 < 1000000ull) {
