@@ -11,6 +11,7 @@
 #include <dlfcn.h>
 
 #include <atomic>
+#include <chrono>
 #include <memory>
 #include <string>
 #include <vector>
@@ -67,9 +68,11 @@ void raise( const std::string& message )
 }
 
 // Waits for the stream like the reference's ncclStreamSynchronize: polls the stream, the communicator's async error
-// and the group's abort flag, so a peer that failed on the host cannot leave this rank waiting forever.
+// and the group's abort flag, so a peer that failed on the host cannot leave this rank waiting forever; a peer that
+// never arrives at all is given two minutes, after which the communicator is aborted.
 void waitCollective( cudaStream_t stream, CCommHolder* holder )
 {
+	const auto start = std::chrono::steady_clock::now();
 	while( true ) {
 		const cudaError_t q = cudaStreamQuery( stream );
 		if( q == cudaSuccess ) return;
@@ -78,6 +81,12 @@ void waitCollective( cudaStream_t stream, CCommHolder* holder )
 		g_nccl.CommGetAsyncError( holder->comm, &asyncError );
 		if( asyncError != ncclSuccessCode && asyncError != ncclInProgressCode ) { raise( "NCCL reported an asynchronous error" ); return; }
 		if( holder->group->aborted.load() ) { raise( "Stopping due to error in another thread." ); return; }
+		if( std::chrono::steady_clock::now() - start > std::chrono::seconds( 120 ) ) {
+			holder->group->aborted.store( true );
+			g_nccl.CommAbort( holder->comm );
+			raise( "collective timed out: a peer did not join within two minutes" );
+			return;
+		}
 	}
 }
 
@@ -148,5 +157,29 @@ extern "C" __attribute__((visibility("default"))) int nb200_create_distributed_m
 {
 	NeoML::CreateDistributedB200MathEngines( reinterpret_cast<NeoML::IMathEngine**>( engines ), count, devices, memoryLimit );
 	for( int i = 0; i < count; ++i ) if( engines[i] == nullptr ) return -1;
+	return 0;
+}
+
+// C entry points for hosts that hold plain device pointers: the collective methods of the engine made on memory the
+// caller owns.  Each engine's call comes from its own host thread (the calls are collective), 0 = done.
+extern "C" __attribute__((visibility("default"))) int nb200_engine_all_reduce( void* engine, float* data, int size )
+{
+	NeoML::IMathEngine* e = static_cast<NeoML::IMathEngine*>( engine );
+	try {
+		e->AllReduce( NeoML::CFloatHandle( NeoML::CMemoryHandleInternal::Create( e, data ) ), size );
+	} catch( ... ) {
+		return -1;
+	}
+	return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int nb200_engine_broadcast( void* engine, float* data, int size, int root )
+{
+	NeoML::IMathEngine* e = static_cast<NeoML::IMathEngine*>( engine );
+	try {
+		e->Broadcast( NeoML::CFloatHandle( NeoML::CMemoryHandleInternal::Create( e, data ) ), size, root );
+	} catch( ... ) {
+		return -1;
+	}
 	return 0;
 }
