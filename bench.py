@@ -330,7 +330,11 @@ def run_ours(args):
     roofline = {
         "bound": "tensor", "kernel": "contraction_tc_kernel (tcgen05 kind::tf32, implicit-GEMM conv + FC)",
         "achieved": round(achieved_tf, 2), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved_tf / peak_tf, 4),
-        "peak_source": peak_src, "traffic": None,
+        "peak_source": peak_src,
+        # ncu dram__bytes_read.sum + dram__bytes_write.sum of the 54 contraction launches of one batch-64 step is 5.44 GB
+        # = 85.0 MB per image (profiles/resnet50_b256_launch_list.md); activations dominate, so it scales with the batch
+        "traffic": round(85.0e6 * batch / max(tc_launches, 1) / 1e9, 4), "traffic_unit": "GB per launch (average)",
+        "algorithmic_bytes_per_launch_gb": round(28.05 * batch / 256 / max(tc_launches, 1), 4),
         "launches_per_step": tc_launches, "ms_per_step_in_kernel": round(tc_ms, 3),
         "algorithmic_gflop_per_step": round(flops / 1e9, 2),
         "effective_peak_for_this_arithmetic": round(eff_peak, 1),

@@ -284,3 +284,38 @@ def test_config5_gemm_1024(ops, oracle):
     check(host(yt), want_t, TOL_FP32, "gemm 1024 NT")
     y_tf32 = ops.MultiplyMatrixByMatrix(dev(a), dev(b), precision=ops.PREC_TF32)
     check(host(y_tf32), want, TOL_TF32, "gemm 1024 NN tf32")
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_config5_gemm_large_by_random_projection(ops, n):
+    """BASELINE config 5 (M = N = K = 4096 / 8192): the O(n^3) product is checked in O(n^2) on the host:
+    (A B) v must equal A (B v) for random v (Freivalds), evaluated in float64; and rows sampled exactly."""
+    rng = np.random.default_rng(500 + n)
+    a = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    y = host(ops.MultiplyMatrixByMatrix(dev(a), dev(b)))
+    a64 = a.astype(np.float64)
+    for seed in range(3):
+        v = np.random.default_rng(seed).uniform(-1, 1, (n,))
+        want = a64 @ (b.astype(np.float64) @ v)
+        got = y.astype(np.float64) @ v
+        assert np.max(np.abs(got - want)) / np.sqrt(np.mean(want ** 2)) < TOL_FP32, f"projection {seed}"
+    rows = rng.integers(0, n, 8)
+    want_rows = (a64[rows] @ b.astype(np.float64)).astype(np.float32)
+    check(y[rows], want_rows, TOL_FP32, f"gemm {n} sampled rows")
+
+
+def test_config2_mobilenetv2_block_full_size(ops, reference):
+    """BASELINE config 2 at its own size (64x56x56x32, expand 192, ReLU6, residual) against the reference CPU engine."""
+    rng = np.random.default_rng(222)
+    n, hw, c_in, c_exp = 64, 56, 32, 192
+    x = rng.uniform(0, 1, (n, hw, hw, c_in)).astype(np.float32)
+    w_exp = (rng.standard_normal((c_exp, c_in)) * np.sqrt(2.0 / c_in)).astype(np.float32)
+    w_dw = (rng.standard_normal((3, 3, c_exp)) * np.sqrt(2.0 / 9)).astype(np.float32)
+    w_down = (rng.standard_normal((c_in, c_exp)) * np.sqrt(2.0 / c_exp)).astype(np.float32)
+    b_exp, b_dw = rng.uniform(-0.1, 0.1, c_exp).astype(np.float32), rng.uniform(-0.1, 0.1, c_exp).astype(np.float32)
+    b_down = rng.uniform(-0.1, 0.1, c_in).astype(np.float32)
+    want = reference.mobilenetv2_block(x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, stride=1, residual=True)
+    got = ops.MobileNetV2Block(dev(x), dev(w_exp), dev(b_exp), dev(w_dw), dev(b_dw), dev(w_down), dev(b_down),
+                               stride=1, residual=True)
+    check(host(got), want, TOL_FP32, "config2 block vs reference CPU engine")
