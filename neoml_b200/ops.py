@@ -71,8 +71,11 @@ def BatchMultiplyMatrixByTransposedMatrix(first, second, result=None, *, precisi
     return result
 
 
-def MultiplyMatrixByMatrix(first, second, result=None, *, precision=PREC_3XTF32):
-    """first [B, M, K] (or [M, K]), second [B, K, N] (or [K, N]) -> result [B, M, N]."""
+def MultiplyMatrixByMatrix(first, second, result=None, *, precision=PREC_3XTF32, use_scratch=True):
+    """first [B, M, K] (or [M, K]), second [B, K, N] (or [K, N]) -> result [B, M, N].
+    With use_scratch (what the engine does with its stack allocator) the second operand is transposed once into
+    scratch and the product runs as A * (B^T)^T on the TMA-fed path; without, the kernel gathers the column-major
+    operand itself."""
     squeeze = first.dim() == 2
     if squeeze:
         first, second = first.unsqueeze(0), second.unsqueeze(0)
@@ -80,8 +83,16 @@ def MultiplyMatrixByMatrix(first, second, result=None, *, precision=PREC_3XTF32)
     n = second.shape[2]
     if result is None:
         result = torch.empty((b, m, n), dtype=torch.float32, device=first.device)
-    capi.check("MultiplyMatrixByMatrix", capi.load().nb200_multiply_matrix_by_matrix(
-        _stream(), b, _ptr(_f32(first)), m, k, _ptr(_f32(second)), n, _ptr(result), None, precision))
+    lib = capi.load()
+    if use_scratch and k >= 4 and n >= 4:
+        transposed = torch.empty((b, n, k), dtype=torch.float32, device=first.device)
+        capi.check("TransposeMatrix", lib.nb200_transpose_matrix(_stream(), b, _ptr(_f32(second)), k, 1, n, 1,
+                                                                 _ptr(transposed)))
+        capi.check("MultiplyMatrixByMatrix", lib.nb200_batch_multiply_matrix_by_transposed_matrix(
+            _stream(), b, _ptr(_f32(first)), m, k, _ptr(transposed), n, _ptr(result), None, precision))
+    else:
+        capi.check("MultiplyMatrixByMatrix", lib.nb200_multiply_matrix_by_matrix(
+            _stream(), b, _ptr(_f32(first)), m, k, _ptr(_f32(second)), n, _ptr(result), None, precision))
     return result[0] if squeeze else result
 
 

@@ -122,6 +122,9 @@ def test_mmt_strided_result_and_bias(ops, oracle):
 def test_multiply_matrix_by_matrix(ops, golden, name, prec, tol):
     a, b = cases.mm_inputs(name)
     check(host(ops.MultiplyMatrixByMatrix(dev(a), dev(b), precision=prec)), golden[f"mm/{name}"], tol, f"mm/{name}")
+    # the kernel's own gather of the column-major operand (what a caller without scratch memory gets)
+    check(host(ops.MultiplyMatrixByMatrix(dev(a), dev(b), precision=prec, use_scratch=False)), golden[f"mm/{name}"], tol,
+          f"mm/{name} (no scratch)")
 
 
 def test_batch_mmt(ops, oracle):
