@@ -39,7 +39,7 @@ class _NumpyBackend:
         return self.impl.vector_op(6, s.ravel(), None, 1.0 / (h * w)).reshape(n, c)
 
     def fully_connected(self, x, w, b):
-        y = self.impl.multiply_matrix_by_transposed_matrix(np.ascontiguousarray(x), w)
+        y = self.impl.multiply_matrix_by_transposed_matrix(x if hasattr(x, "data_ptr") else np.ascontiguousarray(x), w)
         return self.impl.add_vector_to_matrix_rows(1, y.ravel(), y.shape[0], y.shape[1], b).reshape(y.shape)
 
     def softmax(self, x):
@@ -60,3 +60,19 @@ class RefBackend(_NumpyBackend):
 class OracleBackend(_NumpyBackend):
     def __init__(self):
         super().__init__(Oracle())
+
+
+class ShimmedEngineBackend(_NumpyBackend):
+    """The B200 IMathEngine (C++ object, real virtual calls through the shim) behind the same graph; arrays are torch
+    CUDA tensors.  The unfused call sequence only: that is what a CDnn issues."""
+
+    def __init__(self, precision_flags: int = 0):
+        from oracle_lib import ShimmedB200Engine
+        super().__init__(ShimmedB200Engine(flags=precision_flags))
+
+    def upload(self, weights):
+        import torch
+        return {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in weights.items()}
+
+    def close(self):
+        self.impl.close()

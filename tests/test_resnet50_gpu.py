@@ -40,6 +40,28 @@ def test_resnet50_matches_cpu_engine(net, precision, tol, fuse):
     assert np.array_equal(idx, want_idx)
 
 
+@gpu
+def test_resnet50_through_the_cpp_engine(net):
+    """The same graph issued as IMathEngine virtual calls on CB200MathEngine (stack-allocated scratch, engine stream,
+    handles): what a CDnn built on this engine executes."""
+    import ref_backend
+    from oracle_lib import ShimmedB200Engine
+    if not ShimmedB200Engine.available():
+        pytest.skip("libNeoMathEngineB200.so or the shim not built")
+    weights, x, want_probs, want_idx = net
+    be = ref_backend.ShimmedEngineBackend()
+    try:
+        probs, idx = resnet50.forward(be, be.upload(weights), torch.from_numpy(x).cuda(), fuse=False)
+        be.impl.sync()
+        probs, idx = probs.cpu().numpy(), idx.cpu().numpy()
+    finally:
+        be.close()
+    g = gate_err(probs, want_probs)
+    print(f"resnet50 through CB200MathEngine: probabilities gate {g:.3e}")
+    assert g < TOL_FP32
+    assert np.array_equal(idx, want_idx)
+
+
 def test_flop_count_matches_published_figure():
     assert abs(resnet50.flops_per_image() / 1e9 - 8.178) < 0.01
     assert len(resnet50.conv_specs()) == 53
