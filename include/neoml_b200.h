@@ -58,6 +58,9 @@ typedef struct nb200_epilogue {
 	int act;                 /* NB200_ACT_* */
 	float act_param;         /* ReLU upper threshold (<=0: none) */
 	int accumulate;          /* 1: y += result (the ...AndAdd variants); 0: overwrite */
+	const float* act_param_device; /* optional: the ReLU threshold as one float in device memory, read by the kernel
+	                                * (NeoML keeps it there: VectorReLU takes it as a handle, NME.h:143-145); NULL = use
+	                                * act_param.  Lets the engine fuse a following VectorReLU without a host read. */
 } nb200_epilogue;
 
 /* ---- library ------------------------------------------------------------------------------------------- */

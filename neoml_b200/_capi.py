@@ -21,7 +21,7 @@ VEC = {name: i for i, name in enumerate(VEC_OPS)}
 
 class Epilogue(C.Structure):
     _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("ld_residual", C.c_int), ("act", C.c_int),
-                ("act_param", C.c_float), ("accumulate", C.c_int)]
+                ("act_param", C.c_float), ("accumulate", C.c_int), ("act_param_device", C.c_void_p)]
 
 
 class ConvDesc(C.Structure):

@@ -12,6 +12,7 @@ void fill_epilogue(ContractionParams& p, const nb200_epilogue* epi)
 	p.ldr = 0;
 	p.act = NB200_ACT_NONE;
 	p.act_param = 0.f;
+	p.act_param_device = nullptr;
 	p.accumulate = 0;
 	if(epi != nullptr) {
 		p.bias = epi->bias;
@@ -19,6 +20,7 @@ void fill_epilogue(ContractionParams& p, const nb200_epilogue* epi)
 		p.ldr = epi->ld_residual;
 		p.act = epi->act;
 		p.act_param = epi->act_param;
+		p.act_param_device = epi->act_param_device;
 		p.accumulate = epi->accumulate;
 	}
 }

@@ -40,6 +40,7 @@ struct ContractionParams {
 	// epilogue
 	int act;
 	float act_param;
+	const float* act_param_device; // optional: the ReLU threshold lives in device memory (one float), read by the kernel
 	int accumulate;
 	int precision;
 	int stages;

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(TILE * TILE / 4) contraction_simt_kernel(const
 		float x = acc[i];
 		if(p.bias != nullptr) x += p.bias[n];
 		if(R != nullptr) x += R[static_cast<size_t>(m) * p.ldr + n];
-		x = apply_act(x, p.act, p.act_param);
+		x = apply_act(x, p.act, p.act_param_device != nullptr ? __ldg(p.act_param_device) : p.act_param);
 		float* dst = C + static_cast<size_t>(m) * p.ldc + n;
 		if(p.accumulate) x += *dst;
 		*dst = x;

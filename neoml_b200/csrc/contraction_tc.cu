@@ -558,7 +558,8 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		// uniform epilogue options, decided once: the fast store path has no branch per element
 		const bool fastStore = vec && p.accumulate == 0 && p.act != NB200_ACT_HSWISH;
 		const bool clampOn = p.act == NB200_ACT_RELU;
-		const float clampHi = p.act_param > 0.f ? p.act_param : __int_as_float(0x7f800000);
+		const float actParam = p.act_param_device != nullptr ? __ldg(p.act_param_device) : p.act_param;
+		const float clampHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
 		bool ok = true;
 		for(int local = 0; local < myTiles && ok; ++local) {
 			const int tile = blockIdx.x + local * gridDim.x;
@@ -705,7 +706,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 								if(n + t < p.N) {
 									float x = e[t];
 									if(R != nullptr) x += R[static_cast<size_t>(m) * p.ldr + n + t];
-									x = apply_act(x, p.act, p.act_param);
+									x = apply_act(x, p.act, actParam);
 									if(p.accumulate) x += dst[t];
 									dst[t] = x;
 								}

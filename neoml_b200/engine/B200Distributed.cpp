@@ -102,7 +102,7 @@ void CB200MathEngine::AllReduce( const CFloatHandle& handle, int size )
 {
 	if( comm == nullptr ) return; // a single engine is its own average
 	CCommHolder* holder = static_cast<CCommHolder*>( comm );
-	setDevice();
+	enter();
 	float* data = raw( handle );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( g_nccl.AllReduce( data, data, static_cast<size_t>( size ), ncclFloat32, ncclAvgOp, holder->comm, s ) != ncclSuccessCode ) {
@@ -116,7 +116,7 @@ void CB200MathEngine::Broadcast( const CFloatHandle& handle, int size, int root 
 {
 	if( comm == nullptr ) return;
 	CCommHolder* holder = static_cast<CCommHolder*>( comm );
-	setDevice();
+	enter();
 	float* data = raw( handle );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( g_nccl.Bcast( data, data, static_cast<size_t>( size ), ncclFloat32, root, holder->comm, s ) != ncclSuccessCode ) {

@@ -105,6 +105,57 @@ void CB200MathEngine::setDevice() const
 	cudaSetDevice( device );
 }
 
+void CB200MathEngine::enter() const
+{
+	cudaSetDevice( device );
+	flushPending();
+}
+
+void CB200MathEngine::flushPending() const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( !pending.active ) return;
+	pending.active = false;
+	nb200_epilogue epi = {};
+	epi.bias = pending.freeTerm;
+	epi.residual = pending.residual;
+	epi.ld_residual = pending.d.k;
+	epi.act = pending.relu ? NB200_ACT_RELU : NB200_ACT_NONE;
+	epi.act_param_device = pending.threshold;
+	// scratch (prepared filter, widened pixels) comes from the block pool: the stream orders its reuse
+	const size_t scratchFloats = nb200_blob_convolution_scratch_floats( &pending.d );
+	float* scratch = scratchFloats > 0 ? static_cast<float*>( memory.Alloc( scratchFloats * sizeof( float ) ) ) : nullptr;
+	const int rc = nb200_blob_convolution( stream, &pending.d, pending.source, pending.filter, pending.result, scratch, &epi,
+		precision );
+	if( scratch != nullptr ) memory.Free( scratch );
+	check( rc, "BlobConvolution" );
+}
+
+bool CB200MathEngine::fuseReLU( const float* first, float* result, int size, const float* thresholdOnDevice ) const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( !pending.active || pending.relu || first != pending.result || result != pending.result
+		|| size != pending.resultFloats ) {
+		return false;
+	}
+	pending.relu = true;
+	pending.threshold = thresholdOnDevice;
+	cudaSetDevice( device );
+	flushPending(); // nothing fuses behind the activation, and the threshold is read while it certainly still exists
+	return true;
+}
+
+bool CB200MathEngine::fuseAdd( const float* first, const float* second, float* result, int size ) const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( !pending.active || pending.relu || pending.residual != nullptr || result != pending.result
+		|| size != pending.resultFloats || ( first != pending.result && second != pending.result ) || first == second ) {
+		return false;
+	}
+	pending.residual = first == pending.result ? second : first;
+	return true;
+}
+
 //---------------------------------------------------------------------------------------------------------------------
 // identity
 
@@ -177,7 +228,7 @@ size_t CB200MathEngine::GetMemoryInPools() const { return memory.InPools(); }
 
 void CB200MathEngine::CleanUp()
 {
-	setDevice();
+	enter();
 	if( stream != nullptr ) cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
 	memory.CleanUp();
 }
@@ -191,7 +242,7 @@ void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* 
 {
 	if( size == 0 ) return;
 	if( result.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
-	setDevice();
+	enter();
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), source, size, cudaMemcpyHostToDevice, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
@@ -203,7 +254,7 @@ void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source
 {
 	if( size == 0 ) return;
 	if( source.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
-	setDevice();
+	enter();
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( cudaMemcpyAsync( result, CMemoryHandleInternal::GetRaw( source ), size, cudaMemcpyDeviceToHost, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
@@ -257,7 +308,7 @@ CMemoryHandle CB200MathEngine::CopyFrom( const CMemoryHandle& handle, size_t siz
 	if( result.IsNull() || size == 0 ) return result;
 	IMathEngine* other = handle.GetMathEngine();
 	if( other == this ) {
-		setDevice();
+		enter();
 		cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), CMemoryHandleInternal::GetRaw( handle ), size,
 			cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>( stream ) );
 		return result;

@@ -13,6 +13,8 @@
 
 #include <NeoMathEngine/NeoMathEngine.h>
 
+#include "neoml_b200.h"
+
 #include <cstddef>
 #include <cstdint>
 #include <map>
@@ -96,6 +98,12 @@ private:
 	void notImplemented( const char* method ) const;
 	void check( int code, const char* method ) const;
 	void setDevice() const;
+	// Entry of every method that reads or writes device data: selects the device and launches a convolution that was
+	// held back for fusion (see CPendingConvolution).
+	void enter() const;
+	void flushPending() const;
+	bool fuseReLU( const float* first, float* result, int size, const float* thresholdOnDevice ) const;
+	bool fuseAdd( const float* first, const float* second, float* result, int size ) const;
 	// device pointer behind a handle of this engine
 	template<class T> T* raw( const CTypedMemoryHandle<T>& h ) const
 	{
@@ -105,10 +113,29 @@ private:
 	void vectorOp( int op, const float* a, const float* b, const float* scalar, float value, float* y, int n,
 		const char* method );
 
+	// Deferred-execution fusion of the calls a CDnn makes for conv -> [eltwise sum ->] ReLU: BlobConvolution records
+	// the call instead of launching it; an in-place VectorAdd onto its result becomes the residual of the epilogue, an
+	// in-place VectorReLU its activation (threshold read from device memory by the kernel).  Any other call that
+	// touches data launches the recorded convolution first, so results are exactly those of the unfused sequence.
+	struct CPendingConvolution {
+		bool active = false;
+		nb200_conv_desc d;
+		const float* source = nullptr;
+		const float* filter = nullptr;
+		const float* freeTerm = nullptr;
+		float* result = nullptr;
+		const float* residual = nullptr;
+		bool relu = false;
+		const float* threshold = nullptr;
+		long long resultFloats = 0;
+	};
+	mutable CPendingConvolution pending;
+	mutable std::recursive_mutex pendingMutex;
+
 	const int device;
 	const int precision;
 	void* stream = nullptr;
-	CB200Memory memory;
+	mutable CB200Memory memory;
 	bool initialized = false;
 	void* comm = nullptr; // ncclComm_t
 	CMathEngineDistributedInfo distributedInfo;

@@ -87,17 +87,18 @@ void CB200MathEngine::BlobConvolution( const CConvolutionDesc& convDesc, const C
 	const CConstFloatHandle& filter, const CConstFloatHandle* freeTerm, const CFloatHandle& result )
 {
 	const nb200_conv_desc& d = static_cast<const CB200ConvolutionDesc&>( convDesc ).d;
-	setDevice();
-	nb200_epilogue epi = {};
-	epi.bias = freeTerm != nullptr ? raw( *freeTerm ) : nullptr;
-	// channel counts that are not a multiple of four run on widened pixels kept on this thread's device stack
-	const size_t scratchFloats = nb200_blob_convolution_scratch_floats( &d );
-	CMemoryHandle scratch;
-	if( scratchFloats > 0 ) scratch = StackAlloc( scratchFloats * sizeof( float ) );
-	const int rc = nb200_blob_convolution( stream, &d, raw( source ), raw( filter ), raw( result ),
-		scratchFloats > 0 ? static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) ) : nullptr, &epi, precision );
-	if( scratchFloats > 0 ) StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
-	check( rc, "BlobConvolution" );
+	enter(); // launches an earlier convolution that is still held back
+	// The call is recorded, not launched: an in-place VectorAdd / VectorReLU that follows rides in its epilogue, any
+	// other call launches it first (enter()), so the caller cannot observe the delay.
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	pending = CPendingConvolution();
+	pending.d = d;
+	pending.source = raw( source );
+	pending.filter = raw( filter );
+	pending.freeTerm = freeTerm != nullptr ? raw( *freeTerm ) : nullptr;
+	pending.result = raw( result );
+	pending.resultFloats = static_cast<long long>( d.batch ) * d.ho * d.wo * d.k;
+	pending.active = true;
 }
 
 CChannelwiseConvolutionDesc* CB200MathEngine::InitBlobChannelwiseConvolution( const CBlobDesc& input, int paddingHeight,
@@ -113,7 +114,7 @@ void CB200MathEngine::BlobChannelwiseConvolution( const CChannelwiseConvolutionD
 	const CConstFloatHandle& filter, const CConstFloatHandle* freeTerm, const CFloatHandle& result )
 {
 	const nb200_chconv_desc& d = static_cast<const CB200ChannelwiseDesc&>( convDesc ).d;
-	setDevice();
+	enter();
 	check( nb200_blob_channelwise_convolution( stream, &d, raw( source ), raw( filter ),
 		freeTerm != nullptr ? raw( *freeTerm ) : nullptr, raw( result ), NB200_ACT_NONE, 0.f ), "BlobChannelwiseConvolution" );
 }
@@ -131,7 +132,7 @@ void CB200MathEngine::BlobMaxPooling( const CMaxPoolingDesc& poolDesc, const CCo
 	const CIntHandle* maxIndices, const CFloatHandle& result )
 {
 	const CB200PoolingGeometry& g = static_cast<const CB200MaxPoolingDesc&>( poolDesc ).g;
-	setDevice();
+	enter();
 	check( nb200_blob_max_pooling( stream, g.batch, g.h, g.w, g.c, g.fh, g.fw, g.sh, g.sw, raw( source ), raw( result ),
 		maxIndices != nullptr ? raw( *maxIndices ) : nullptr ), "BlobMaxPooling" );
 }
@@ -148,7 +149,7 @@ CMeanPoolingDesc* CB200MathEngine::InitMeanPooling( const CBlobDesc& source, int
 void CB200MathEngine::BlobMeanPooling( const CMeanPoolingDesc& poolDesc, const CConstFloatHandle& source, const CFloatHandle& result )
 {
 	const CB200PoolingGeometry& g = static_cast<const CB200MeanPoolingDesc&>( poolDesc ).g;
-	setDevice();
+	enter();
 	check( nb200_blob_mean_pooling( stream, g.batch, g.h, g.w, g.c, g.fh, g.fw, g.sh, g.sw, raw( source ), raw( result ) ),
 		"BlobMeanPooling" );
 }
@@ -156,7 +157,7 @@ void CB200MathEngine::BlobMeanPooling( const CMeanPoolingDesc& poolDesc, const C
 void CB200MathEngine::BlobResizeImage( const CBlobDesc& from, const CFloatHandle& fromData, int deltaLeft, int deltaRight,
 	int deltaTop, int deltaBottom, TBlobResizePadding padding, float defaultValue, const CBlobDesc&, const CFloatHandle& toData )
 {
-	setDevice();
+	enter();
 	check( nb200_blob_resize_image( stream, from.ObjectCount(), from.Height(), from.Width(), from.Depth() * from.Channels(),
 		deltaLeft, deltaRight, deltaTop, deltaBottom, static_cast<int>( padding ), defaultValue, raw( fromData ), raw( toData ) ),
 		"BlobResizeImage" );
@@ -212,7 +213,7 @@ void CB200MathEngine::MobileNetV2Block( const CBlobDesc& inputDesc, const CBlobD
 	nb200_mbv2_desc d = { inputDesc.ObjectCount(), inputDesc.Height(), inputDesc.Width(), op->inputChannels,
 		op->expandedChannels, op->outputChannels, op->stride, op->residual ? 1 : 0, op->actExpand, op->actChannelwise,
 		op->actExpandParam, op->actChannelwiseParam };
-	setDevice();
+	enter();
 	const size_t scratchFloats = nb200_mobilenetv2_scratch_floats( &d );
 	CMemoryHandle scratch = StackAlloc( scratchFloats * sizeof( float ) );
 	const int rc = nb200_mobilenetv2_block( stream, &d, raw( inputHandle ), op->expandFilter, op->expandFreeTerm,

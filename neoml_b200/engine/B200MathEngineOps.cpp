@@ -22,7 +22,7 @@ void raise( const char* message )
 void CB200MathEngine::vectorOp( int op, const float* a, const float* b, const float* scalar, float value, float* y, int n,
 	const char* method )
 {
-	setDevice();
+	enter();
 	check( nb200_vector_op( stream, op, a, b, scalar, value, y, n ), method );
 }
 
@@ -36,7 +36,7 @@ void CB200MathEngine::VectorCopy( const CFloatHandle& first, const CConstFloatHa
 
 void CB200MathEngine::VectorCopy( const CIntHandle& first, const CConstIntHandle& second, int vectorSize )
 {
-	setDevice();
+	enter();
 	check( nb200_vector_copy_int( stream, raw( second ), raw( first ), vectorSize ), "VectorCopy" );
 }
 
@@ -47,7 +47,7 @@ void CB200MathEngine::VectorFill( const CFloatHandle& result, float value, int v
 
 void CB200MathEngine::VectorFill( const CIntHandle& result, int value, int vectorSize )
 {
-	setDevice();
+	enter();
 	check( nb200_vector_fill_int( stream, value, raw( result ), vectorSize ), "VectorFill" );
 }
 
@@ -59,6 +59,7 @@ void CB200MathEngine::VectorFill( const CFloatHandle& result, int vectorSize, co
 void CB200MathEngine::VectorReLU( const CConstFloatHandle& firstHandle, const CFloatHandle& resultHandle, int vectorSize,
 	const CConstFloatHandle& upperThresholdHandle )
 {
+	if( fuseReLU( raw( firstHandle ), raw( resultHandle ), vectorSize, raw( upperThresholdHandle ) ) ) return;
 	vectorOp( NB200_VEC_RELU, raw( firstHandle ), nullptr, raw( upperThresholdHandle ), 0.f, raw( resultHandle ), vectorSize, "VectorReLU" );
 }
 
@@ -81,6 +82,7 @@ void CB200MathEngine::VectorExp( const CConstFloatHandle& firstHandle, const CFl
 void CB200MathEngine::VectorAdd( const CConstFloatHandle& firstHandle, const CConstFloatHandle& secondHandle,
 	const CFloatHandle& resultHandle, int vectorSize )
 {
+	if( fuseAdd( raw( firstHandle ), raw( secondHandle ), raw( resultHandle ), vectorSize ) ) return;
 	vectorOp( NB200_VEC_ADD, raw( firstHandle ), raw( secondHandle ), nullptr, 0.f, raw( resultHandle ), vectorSize, "VectorAdd" );
 }
 
@@ -152,7 +154,7 @@ void CB200MathEngine::VectorTanh( const CConstFloatHandle& firstHandle, const CF
 void CB200MathEngine::AddVectorToMatrixRows( int batchSize, const CConstFloatHandle& matrixHandle, const CFloatHandle& resultHandle,
 	int matrixHeight, int matrixWidth, const CConstFloatHandle& vectorHandle )
 {
-	setDevice();
+	enter();
 	check( nb200_add_vector_to_matrix_rows( stream, batchSize, raw( matrixHandle ), raw( resultHandle ), matrixHeight, matrixWidth,
 		raw( vectorHandle ) ), "AddVectorToMatrixRows" );
 }
@@ -160,7 +162,7 @@ void CB200MathEngine::AddVectorToMatrixRows( int batchSize, const CConstFloatHan
 void CB200MathEngine::AddVectorToMatrixColumns( const CConstFloatHandle& matrixHandle, const CFloatHandle& resultHandle,
 	int matrixHeight, int matrixWidth, const CConstFloatHandle& vectorHandle )
 {
-	setDevice();
+	enter();
 	check( nb200_add_vector_to_matrix_columns( stream, raw( matrixHandle ), raw( resultHandle ), matrixHeight, matrixWidth,
 		raw( vectorHandle ) ), "AddVectorToMatrixColumns" );
 }
@@ -168,27 +170,27 @@ void CB200MathEngine::AddVectorToMatrixColumns( const CConstFloatHandle& matrixH
 void CB200MathEngine::SumMatrixRowsAdd( int batchSize, const CFloatHandle& resultHandle, const CConstFloatHandle& matrixHandle,
 	int matrixHeight, int matrixWidth )
 {
-	setDevice();
+	enter();
 	check( nb200_sum_matrix_rows( stream, batchSize, raw( resultHandle ), raw( matrixHandle ), matrixHeight, matrixWidth, 1 ), "SumMatrixRowsAdd" );
 }
 
 void CB200MathEngine::SumMatrixRows( int batchSize, const CFloatHandle& resultHandle, const CConstFloatHandle& matrixHandle,
 	int matrixHeight, int matrixWidth )
 {
-	setDevice();
+	enter();
 	check( nb200_sum_matrix_rows( stream, batchSize, raw( resultHandle ), raw( matrixHandle ), matrixHeight, matrixWidth, 0 ), "SumMatrixRows" );
 }
 
 void CB200MathEngine::SumMatrixColumns( const CFloatHandle& resultHandle, const CConstFloatHandle& matrixHandle, int matrixHeight,
 	int matrixWidth )
 {
-	setDevice();
+	enter();
 	check( nb200_sum_matrix_columns( stream, raw( resultHandle ), raw( matrixHandle ), matrixHeight, matrixWidth ), "SumMatrixColumns" );
 }
 
 void CB200MathEngine::MatrixSoftmaxByRows( const CConstFloatHandle& matrix, int height, int width, const CFloatHandle& result )
 {
-	setDevice();
+	enter();
 	check( nb200_matrix_softmax_by_rows( stream, raw( matrix ), height, width, raw( result ) ), "MatrixSoftmaxByRows" );
 }
 
@@ -196,7 +198,7 @@ void CB200MathEngine::FindMaxValueInRows( const CConstFloatHandle& matrixHandle,
 	const CFloatHandle& resultHandle, const CIntHandle& columnIndices, int vectorSize )
 {
 	if( vectorSize < matrixHeight ) { raise( "FindMaxValueInRows: result buffer too small" ); return; }
-	setDevice();
+	enter();
 	check( nb200_find_max_value_in_rows( stream, raw( matrixHandle ), matrixHeight, matrixWidth, raw( resultHandle ),
 		raw( columnIndices ) ), "FindMaxValueInRows" );
 }
@@ -205,7 +207,7 @@ void CB200MathEngine::FindMaxValueInRows( const CConstFloatHandle& matrixHandle,
 	const CFloatHandle& resultHandle, int vectorSize )
 {
 	if( vectorSize < matrixHeight ) { raise( "FindMaxValueInRows: result buffer too small" ); return; }
-	setDevice();
+	enter();
 	check( nb200_find_max_value_in_rows( stream, raw( matrixHandle ), matrixHeight, matrixWidth, raw( resultHandle ), nullptr ),
 		"FindMaxValueInRows" );
 }
@@ -214,7 +216,7 @@ void CB200MathEngine::FindMaxValueInColumns( int batchSize, const CConstFloatHan
 	const CFloatHandle& resultHandle, const CIntHandle& rowIndices, int vectorSize )
 {
 	if( vectorSize < batchSize * matrixWidth ) { raise( "FindMaxValueInColumns: result buffer too small" ); return; }
-	setDevice();
+	enter();
 	check( nb200_find_max_value_in_columns( stream, batchSize, raw( matrixHandle ), matrixHeight, matrixWidth, raw( resultHandle ),
 		raw( rowIndices ) ), "FindMaxValueInColumns" );
 }
@@ -223,7 +225,7 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 	int firstRowSize, const CConstFloatHandle& secondHandle, int secondHeight, int secondRowSize, const CFloatHandle& resultHandle,
 	int resultRowSize, int )
 {
-	setDevice();
+	enter();
 	check( nb200_multiply_matrix_by_transposed_matrix( stream, raw( firstHandle ), firstHeight, firstWidth, firstRowSize,
 		raw( secondHandle ), secondHeight, secondRowSize, raw( resultHandle ), resultRowSize, nullptr, precision ),
 		"MultiplyMatrixByTransposedMatrix" );
@@ -232,7 +234,7 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 void CB200MathEngine::MultiplyMatrixByTransposedMatrix( int batchSize, const CConstFloatHandle& firstHandle, int firstHeight,
 	int firstWidth, const CConstFloatHandle& secondHandle, int secondHeight, const CFloatHandle& resultHandle, int )
 {
-	setDevice();
+	enter();
 	check( nb200_batch_multiply_matrix_by_transposed_matrix( stream, batchSize, raw( firstHandle ), firstHeight, firstWidth,
 		raw( secondHandle ), secondHeight, raw( resultHandle ), nullptr, precision ), "MultiplyMatrixByTransposedMatrix" );
 }
@@ -240,7 +242,7 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( int batchSize, const CCo
 void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHandle& firstHandle, int firstHeight, int firstWidth,
 	const CConstFloatHandle& secondHandle, int secondWidth, const CFloatHandle& resultHandle, int )
 {
-	setDevice();
+	enter();
 	// The second operand is [K x N]: the tensor-core kernel wants both operands K-major.  One transposing pass over it
 	// (into stack memory) costs a read and a write of the operand and lets the product run on the TMA-fed path, which
 	// is several times faster than gathering a column-major operand element by element.
@@ -264,7 +266,7 @@ void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHa
 void CB200MathEngine::MultiplyDiagMatrixByMatrix( const CConstFloatHandle& firstHandle, int firstSize,
 	const CConstFloatHandle& secondHandle, int secondWidth, const CFloatHandle& resultHandle, int )
 {
-	setDevice();
+	enter();
 	check( nb200_multiply_diag_matrix_by_matrix( stream, raw( firstHandle ), firstSize, raw( secondHandle ), secondWidth,
 		raw( resultHandle ) ), "MultiplyDiagMatrixByMatrix" );
 }
@@ -275,7 +277,7 @@ void CB200MathEngine::BatchMultiplyMatrixByDiagMatrix( int batchSize, const CCon
 	// the kernel assumes densely packed matrices; the reference allows a zero offset to reuse one matrix for all batches
 	if( batchSize > 1 && firstMatrixOffset != height * width ) { notImplemented( "BatchMultiplyMatrixByDiagMatrix (strided first operand)" ); return; }
 	if( secondMatrixOffset != 0 && secondMatrixOffset != width ) { notImplemented( "BatchMultiplyMatrixByDiagMatrix (strided diagonal)" ); return; }
-	setDevice();
+	enter();
 	check( nb200_multiply_matrix_by_diag_matrix( stream, batchSize, raw( firstHandle ), height, width, raw( secondHandle ),
 		secondMatrixOffset, raw( resultHandle ) ), "BatchMultiplyMatrixByDiagMatrix" );
 }
@@ -283,7 +285,7 @@ void CB200MathEngine::BatchMultiplyMatrixByDiagMatrix( int batchSize, const CCon
 void CB200MathEngine::TransposeMatrix( int batchSize, const CConstFloatHandle& firstHandle, int height, int medium, int width,
 	int channels, const CFloatHandle& resultHandle, int )
 {
-	setDevice();
+	enter();
 	check( nb200_transpose_matrix( stream, batchSize, raw( firstHandle ), height, medium, width, channels, raw( resultHandle ) ),
 		"TransposeMatrix" );
 }
@@ -291,7 +293,7 @@ void CB200MathEngine::TransposeMatrix( int batchSize, const CConstFloatHandle& f
 void CB200MathEngine::TransposeMatrix( int batchSize, const CConstIntHandle& firstHandle, int height, int medium, int width,
 	int channels, const CIntHandle& resultHandle, int )
 {
-	setDevice();
+	enter();
 	check( nb200_transpose_matrix( stream, batchSize, raw( firstHandle ), height, medium, width, channels, raw( resultHandle ) ),
 		"TransposeMatrix" );
 }

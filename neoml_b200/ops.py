@@ -31,8 +31,10 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def _epilogue(bias=None, residual=None, ld_residual=0, act=ACT_NONE, act_param=0.0, accumulate=False):
-    return capi.Epilogue(_ptr(bias), _ptr(residual), ld_residual, act, float(act_param), int(accumulate))
+def _epilogue(bias=None, residual=None, ld_residual=0, act=ACT_NONE, act_param=0.0, accumulate=False,
+              act_param_device=None):
+    return capi.Epilogue(_ptr(bias), _ptr(residual), ld_residual, act, float(act_param), int(accumulate),
+                         _ptr(act_param_device))
 
 
 def conv_output_size(size: int, filt: int, pad: int, stride: int, dil: int = 1) -> int:

@@ -264,10 +264,10 @@ class Reference:
         self.last_seconds = sec.value
         return y
 
-    def vector_op(self, op, a=None, b=None, scalar=0.0, count=None):
+    def vector_op(self, op, a=None, b=None, scalar=0.0, count=None, out=None):
         ref = a if a is not None else b
         n = count if count is not None else int(np.prod(ref.shape))
-        y = self._zeros((n,), np.float32)
+        y = self._zeros((n,), np.float32) if out is None else out
         sc = self._scalar(scalar)
         self._chk(self.lib.ref_vector_op(self.engine, op, _opt(a), _opt(b), _opt(sc), _f(scalar), _opt(y), n))
         return y
@@ -427,7 +427,12 @@ class ShimmedB200Engine(Reference):
             self.engine = None
 
     def sync(self):
-        """The engine runs on its own stream; the shim has no sync call, so drain the whole device."""
+        """Results become visible the way NeoML reads them: through a data exchange on the engine (it launches
+        whatever the engine still holds back for fusion and drains the engine's stream)."""
+        if not hasattr(self, "_probe"):
+            self._probe = self.torch.zeros(1, dtype=self.torch.float32, device="cuda")
+            self.torch.cuda.synchronize()
+        self._chk(self.lib.ref_engine_sync(self.engine, _vp(self._probe.data_ptr())))
         self.torch.cuda.synchronize()
 
     def _zeros(self, shape, dtype=np.float32):

@@ -317,6 +317,16 @@ int ref_engine_roundtrip( void* eng, const float* hostIn, float* hostOut, int n,
 	SHIM_CATCH
 }
 
+// Makes every result of the calls so far visible, the way NeoML code reads results: a typed exchange of one float.
+int ref_engine_sync( void* eng, const float* anyEngineFloat )
+{
+	SHIM_TRY
+	IMathEngine* e = static_cast<IMathEngine*>( eng );
+	float value = 0.f;
+	e->DataExchangeTyped( &value, cfh( e, anyEngineFloat ), 1 );
+	SHIM_CATCH
+}
+
 // type: TMathEngineType of the engine; returns the device id the engine reports
 int ref_engine_info( void* eng, int* type, unsigned long long* availableMemory, char* name, int nameSize )
 {

@@ -36,7 +36,10 @@ def host(e, t):
 @pytest.mark.parametrize("name", sorted(cases.CONV_CASES))
 def test_blob_convolution(engine, golden, name):
     x, f, b, kw = cases.conv_inputs(name)
-    y = engine.blob_convolution(dev(x), dev(f), dev(b), **kw)
+    # the engine may hold the convolution back until the next call that touches data: like the blobs of a network, the
+    # operands stay alive until the result has been read
+    dx, df, db = dev(x), dev(f), dev(b)
+    y = engine.blob_convolution(dx, df, db, **kw)
     assert gate_err(host(engine, y), golden[f"conv/{name}"]) < TOL_FP32
 
 
@@ -139,3 +142,31 @@ def test_engine_identity(engine):
 def test_training_methods_raise_instead_of_falling_back(engine):
     x = dev(cases.uniform(42, (64,)))
     assert engine.training_method_raises(x)
+
+
+def test_in_place_add_and_relu_ride_in_the_convolution_epilogue(engine, oracle):
+    """conv -> VectorAdd(y, r, y) -> VectorReLU(y, y) as a CDnn issues them: the engine holds the convolution back,
+    folds the two in-place calls into its epilogue and launches once; the result is that of the three separate calls."""
+    from neoml_b200 import _capi
+    lib = _capi.load()
+    x, f, b = cases.uniform(51, (2, 14, 14, 64)), cases.uniform(52, (96, 3, 3, 64)), cases.uniform(53, (96,))
+    r = cases.uniform(54, (2, 14, 14, 96))
+    want = np.maximum(oracle.blob_convolution(x, f, b, padding=(1, 1)) + r, 0.0)
+
+    def run(fused: bool):
+        dx, df, db, dr = dev(x), dev(f), dev(b), dev(r)
+        engine.sync()
+        before = lib.nb200_launch_count()
+        y = engine.blob_convolution(dx, df, db, padding=(1, 1))
+        if not fused:
+            engine.sync()                                   # forces the convolution out before the next call
+        engine.vector_op(3, y.reshape(-1), dr.reshape(-1), out=y.reshape(-1))       # VectorAdd in place
+        engine.vector_op(9, y.reshape(-1), None, 0.0, out=y.reshape(-1))            # VectorReLU in place
+        got = host(engine, y)
+        return got, lib.nb200_launch_count() - before
+
+    fused, fused_launches = run(True)
+    plain, plain_launches = run(False)
+    assert gate_err(fused, want) < TOL_FP32 and gate_err(plain, want) < TOL_FP32
+    assert np.array_equal(fused, plain)                     # same arithmetic, same order of additions per element
+    assert plain_launches == fused_launches + 2             # the add and the ReLU launched nothing of their own
