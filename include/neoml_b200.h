@@ -73,11 +73,11 @@ NB200_API const char* nb200_error_string(int code);
 NB200_API int nb200_device_status(void* stream, int reset);
 /* Text of the CUDA runtime error behind the calling thread's last NB200_ELAUNCH / NB200_ENODEVICE. */
 NB200_API const char* nb200_last_cuda_error(void);
-/* Debug aid: when device_buffer is non-NULL, CTA 0 of every later contraction launch stores clock64() stamps of its
- * pipeline roles for the first `steps` K-block steps at device_buffer[role * steps + step] (11 stamp kinds, 8-byte words; kinds 0-6 are per K-block step, 7-10 per tile).
- * skip_mask switches pipeline stages off to time the others in isolation (results are then wrong): bit 0 no MMA,
- * bit 1 converters move no data, bit 2 the epilogue stores nothing.  0 for normal operation. */
-NB200_API void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int skip_mask);
+/* Diagnostic aid: when device_buffer is non-NULL, CTA 0 of every later contraction launch stores clock64() stamps of
+ * its pipeline roles at device_buffer[kind * steps + index] (16 stamp kinds, 8-byte words; kinds 0-6 and 15 are indexed
+ * by K-block step, 7-14 by tile; indices >= steps are dropped).  options bit 4 (value 16): use the cp.async gather
+ * kernel even where TMA applies (results are the same; for timing and testing that path).  (NULL, 0, 0) = normal. */
+NB200_API void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int options);
 /* Kernels launched by this library in this process since load (for launch accounting in benchmarks). */
 NB200_API uint64_t nb200_launch_count(void);
 

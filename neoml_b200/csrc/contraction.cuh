@@ -48,7 +48,6 @@ struct ContractionParams {
 	// optional pipeline trace (debug aid): CTA 0 stores clock64() at [role * traceSteps + step]; nullptr = off
 	unsigned long long* trace;
 	int traceSteps;
-	int debugSkip; // debug aid, bit 0: issue no MMA, bit 1: converters move no data, bit 2: epilogue stores nothing
 };
 
 // Decodes output row m of a convolution into the image base offset and the top-left input coordinate.
@@ -104,7 +103,7 @@ __device__ __forceinline__ float gather_b(const ContractionParams& p, const floa
 		: __ldg(B + static_cast<size_t>(k) * p.ldb + n);
 }
 
-void set_contraction_trace(unsigned long long* buffer, int steps, int debugSkip);
+void set_contraction_trace(unsigned long long* buffer, int steps, int options);
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
 int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
 

@@ -1,33 +1,36 @@
 // Implicit-GEMM contraction on the 5th-generation tensor cores (tcgen05.mma kind::tf32, accumulators in TMEM).
 //
 // Persistent kernel: one CTA per SM walks the 128 x BN output tiles (tile = blockIdx.x + i * gridDim.x, the N tile
-// index fastest so that CTAs running together share the same rows of A in L2).  Sixteen warps (four per SM sub-partition, so every thread may hold 128 registers), four roles:
-//   warps 0-1   copy.  Every 32-wide K block of A (128 rows) and B (BN rows) is gathered straight from global memory
-//               (no im2col matrix exists anywhere) by asynchronous copies (cp.async, zero-fill for padding and
-//               tails) into a ring of "raw" shared-memory slots laid out in the 128-byte-swizzled K-major format
-//               the MMA reads.  The copy warps never wait for data: a slot's completion is signalled by
-//               cp.async.mbarrier.arrive, and they run as many slots ahead as the ring holds, which is what keeps
-//               ~100 KB per SM in flight without holding registers.  Operands that are a plain box of a tensor
-//               (row-major A and B with 16-byte-aligned rows) or an im2col column block of a channels-last image
-//               with C % 32 == 0 are loaded by TMA instead: thread 0 issues one cp.async.bulk.tensor per operand
-//               tile and announces the bytes on the same barrier.  The cp.async gather remains for everything TMA
-//               cannot describe (4-byte-aligned handles, column-major B, odd channel counts).
-//   warps 4-7   convert.  3xTF32: the tensor core reads an fp32 word as TF32 by ignoring the low 13 mantissa bits,
-//               so a raw slot *is* the "hi" operand; these warps form lo = x - trunc_tf32(x) (exact in fp32) into a
-//               2-deep ring of "lo" slots.  Plain TF32: they round the raw slot to nearest TF32 in place.
-//   warp 2      allocates TMEM; one lane issues the MMAs: per 8-wide K step lo*hi, hi*lo (into a "cross"
-//               accumulator) and hi*hi (into the main accumulator) for 3xTF32, hi*hi only for plain TF32.
-//               The tensor core truncates on every accumulate, so the main accumulator takes one add per K step,
-//               not three; the lo*lo term is below fp32 resolution and is dropped.
+// index fastest so that CTAs running together share the same rows of A in L2).  Sixteen warps (four per SM
+// sub-partition, so every thread may hold 128 registers), four roles:
+//   warp 0      copy (TMA).  Each 32-wide K block of A (128 rows) and B (BN rows) arrives in a ring of "raw"
+//               shared-memory slots in the 128-byte-swizzled K-major layout: plain matrices as tiled boxes, a
+//               channels-last image with C % 32 == 0 as im2col boxes (no im2col matrix exists anywhere), a padded
+//               few-channel image as row windows.  The warp walks its loop as a whole; an elected lane announces the
+//               bytes on the slot's barrier and issues the copies.
+//   warps 0-1   copy (gather; only in the GATHER instantiation).  Everything TMA cannot describe (4-byte-aligned
+//               handles, column-major B, odd channel counts) is gathered by cp.async with zero fill; a slot's
+//               completion is signalled by cp.async.mbarrier.arrive.
+//   warps 4-7   convert.  Thread = tile row: it reads the row's 32 floats from the raw slot and stores the A operand
+//               of the tensor core into one of two stages in tensor memory (tcgen05.st): for 3xTF32 hi = x with the
+//               low 13 mantissa bits cleared and lo = x - hi (exact in fp32), for plain TF32 x rounded to nearest.
+//               B needs no work when the caller prepared it (lo(B) / rounded B in global memory, fetched by TMA);
+//               otherwise these warps also write lo(B) into a 2-slot shared-memory ring (or round B in place).
+//   warp 2      allocates TMEM and issues the MMAs (TS form: A from tensor memory, B from shared memory) through an
+//               elected lane: per 8-wide K step lo*hi and hi*lo into a "cross" accumulator and hi*hi into the main
+//               accumulator for 3xTF32, hi*hi only for plain TF32.  The tensor core truncates on every accumulate,
+//               so the small cross terms are kept apart from the large sum; lo*lo is below fp32 resolution.
 //   warps 8-15  epilogue: each warp owns 32 rows x BN/2 columns.  It prefetches its residual block into L2 before it
-//               waits for the accumulators, then per 16 columns: tcgen05.ld (main + cross) -> shared-memory
-//               transpose -> bias / residual (loaded one chunk ahead) / activation -> coalesced 16-byte stores.  With two
-//               accumulator sets in TMEM (when 4 x BN columns fit in 512) the epilogue of tile i overlaps the main
-//               loop of tile i+1.
-// Hand-over is by mbarriers: rawFull[r] (64 cp.async arrivals + the TMA issuer's expect_tx), cvtFull[.] (128 converter arrivals after a
-// generic->async proxy fence), rawEmpty[r] / loEmpty[l] / accFull[b] (tcgen05.commit), accEmpty[b] (256 epilogue
-// arrivals).  Every wait is bounded; on timeout the CTA raises an abort flag, records the site in the device status
-// word and every role falls through to the common teardown that frees TMEM.
+//               waits for the accumulators, then per 16 columns: tcgen05.ld -> shared-memory transpose -> bias /
+//               residual (loaded one chunk ahead) / clamp -> coalesced 16-byte stores, free of branches.  Two main
+//               accumulators let the epilogue of tile i overlap the MMAs of tile i + 1; where only one cross
+//               accumulator fits (BN = 128) the epilogue first folds it into the main one in place.
+// Hand-over is by mbarriers: rawFull[r] (TMA bytes [+ 64 cp.async arrivals]), cvtFull[l] (one arrival per converter
+// warp after tcgen05.wait::st and the proxy fence), rawEmpty[r] / loEmpty[l] / accFull[b] (tcgen05.commit),
+// accEmpty[b] / crossEmpty (one arrival per epilogue warp).  Waits poll with all lanes of a warp and agree by vote:
+// divergent single-lane polling and issue cost several hundred cycles per step.  Every wait is bounded; on timeout the
+// CTA raises an abort flag, records the site in the device status word and every role falls through to the common
+// teardown that frees TMEM.
 #include "contraction.cuh"
 #include <cuda.h>
 #include <string.h>
@@ -67,9 +70,15 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk)
 }
 
 // debug aid: per-role time stamps of the first traceSteps K-block steps of CTA 0
-enum { TR_COPY_ISSUED = 0, TR_RAW_FULL = 1, TR_CVT_DONE = 2, TR_MMA_ISSUED = 3, TR_COPY_SLOT_FREE = 4, TR_COPY_A_DONE = 5, TR_COPY_B_DONE = 6,
+enum {
+	// indexed by K-block step
+	TR_COPY_ISSUED = 0, TR_RAW_FULL = 1, TR_CVT_DONE = 2, TR_MMA_ISSUED = 3, TR_COPY_SLOT_FREE = 4, TR_CVT_A_STORED = 5,
+	TR_MMA_SAW_STEP = 6, TR_CVT_STAGE_FREE = 15,
+	// indexed by tile
 	TR_EPI_ACC_FULL = 7, TR_EPI_TMEM_READ = 8, TR_EPI_TILE_DONE = 9, TR_MMA_TILE_COMMITTED = 10, TR_EPI_LD0 = 11, TR_EPI_STS0 = 12,
-	TR_EPI_STG0 = 13, TR_EPI_CH1 = 14, TR_ROLES = 16 }; // 7..14 are per tile
+	TR_EPI_STG0 = 13, TR_EPI_CH1 = 14,
+	TR_ROLES = 16
+};
 __device__ __forceinline__ void trace(const ContractionParams& p, int role, int step)
 {
 	if(p.trace != nullptr && blockIdx.x == 0 && step < p.traceSteps) p.trace[role * p.traceSteps + step] = clock64();
@@ -357,7 +366,6 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 						}
 					}
 				}
-				if(tid == 0) trace(p, TR_COPY_A_DONE, step);
 #pragma unroll
 				for(int j = 0; j < (p.b_tma ? 0 : B_PIECES); ++j) {
 					const int row = bCols ? (tid & 31) + 32 * (j >> 2) : row0 + 8 * j;
@@ -387,7 +395,6 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 						}
 					}
 				}
-				if(tid == 0) trace(p, TR_COPY_B_DONE, step);
 				if(!allTma) cp_async_arrive_on(&rawFullBar[slot]);
 				if(tid == 0) trace(p, TR_COPY_ISSUED, step);
 			}
@@ -420,7 +427,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			// the A stage and the lo slot of step i - 2 are free once that step's MMAs have completed
 			if(!mbar_wait_bounded_warp(&loEmptyBar[ls], ((i / LO_SLOTS) & 1) ^ 1, abortFlag, p.status, SITE_LO_EMPTY)) { ok = false; break; }
 			tc_fence_after_sync();
-			if(ct == 0) trace(p, 15, i); // debug: the A stage was seen free
+			if(ct == 0) trace(p, TR_CVT_STAGE_FREE, i);
 			uint8_t* raw = rawRing + static_cast<size_t>(slot) * SLOT_BYTES;
 			{
 				// two halves of 16 K indices keep the live registers at 32
@@ -445,7 +452,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					tmem_st16(aLane + ls * aStageCols + 16 * half, hi);
 					if(threeX) tmem_st16(aLane + ls * aStageCols + 32 + 16 * half, lo);
 				}
-				if(ct == 0) trace(p, TR_COPY_A_DONE, i);
+				if(ct == 0) trace(p, TR_CVT_A_STORED, i);
 				uint8_t* rawB = raw + A_TILE_BYTES;
 				uint8_t* loB = loRing + static_cast<size_t>(ls) * B_TILE_BYTES;
 #pragma unroll
@@ -494,7 +501,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					const int ls = it % LO_SLOTS;
 					if(!mbar_wait_bounded_warp(&cvtFullBar[ls], (it / LO_SLOTS) & 1, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
 					tc_fence_after_sync();
-					if(lane == 0) trace(p, TR_COPY_B_DONE, it); // debug: the MMA warp has seen the converted step
+					if(lane == 0) trace(p, TR_MMA_SAW_STEP, it);
 					const uint32_t aHi = tmemBase + aBaseCol + ls * aStageCols;   // tensor-memory columns of this stage
 					const uint32_t aLo = aHi + 32;
 					const uint32_t bHi = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES) + A_TILE_BYTES;
@@ -825,7 +832,7 @@ bool make_window_map(CUtensorMap* map, const ContractionParams& p, int images, i
 
 unsigned long long* g_traceBuffer = nullptr;
 int g_traceSteps = 0;
-int g_debugSkip = 0;
+int g_traceOptions = 0;
 
 template<int BN>
 int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
@@ -833,7 +840,6 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	ContractionParams p = p0;
 	p.trace = g_traceBuffer;
 	p.traceSteps = g_traceSteps;
-	p.debugSkip = g_debugSkip;
 	const bool threeX = p.precision == NB200_PREC_3XTF32;
 	const bool preB = p.b_ready != 0;
 	const int slotBytes = A_TILE_BYTES + BN * BK * 4 * (preB && threeX ? 2 : 1);
@@ -877,7 +883,7 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	memset(&mapBlo, 0, sizeof(mapBlo));
 	p.a_tma = 0;
 	p.b_tma = 0;
-	if(!(g_debugSkip & 16)) {
+	if(!(g_traceOptions & 16)) {
 		if(p.a_mode == A_ROWS) {
 			if(p.a_vec && make_rows_map(&mapA, p.A, p.K, p.M, p.lda, batch, p.strideA, BM)) p.a_tma = 1;
 		} else if(p.a_mode == A_CONV_WINDOW) {
@@ -909,11 +915,11 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 
 } // namespace
 
-void set_contraction_trace(unsigned long long* buffer, int steps, int debugSkip)
+void set_contraction_trace(unsigned long long* buffer, int steps, int options)
 {
 	g_traceBuffer = buffer;
 	g_traceSteps = steps;
-	g_debugSkip = debugSkip;
+	g_traceOptions = options;
 }
 
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream)

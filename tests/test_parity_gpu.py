@@ -322,3 +322,24 @@ def test_config2_mobilenetv2_block_full_size(ops, reference):
     got = ops.MobileNetV2Block(dev(x), dev(w_exp), dev(b_exp), dev(w_dw), dev(b_dw), dev(w_down), dev(b_down),
                                stride=1, residual=True)
     check(host(got), want, TOL_FP32, "config2 block vs reference CPU engine")
+
+
+def test_gather_kernel_agrees_with_the_tma_kernel(ops):
+    """Shapes that normally ride on TMA, pushed through the cp.async gather instantiation (diagnostic option 16): the
+    K order of the accumulation is the same, so the two kernels must agree bit for bit."""
+    from neoml_b200 import _capi
+    lib = _capi.load()
+    x, f, b = dev(cases.uniform(61, (3, 20, 20, 64))), dev(cases.uniform(62, (80, 3, 3, 64))), dev(cases.uniform(63, (80,)))
+    a, w = dev(cases.uniform(64, (300, 160))), dev(cases.uniform(65, (72, 160)))
+    want_conv = ops.BlobConvolution(x, f, b, padding=(1, 1), act=ops.ACT_RELU)
+    want_mmt = ops.MultiplyMatrixByTransposedMatrix(a, w)
+    torch.cuda.synchronize()
+    lib.nb200_debug_set_contraction_trace(None, 0, 16)
+    try:
+        got_conv = ops.BlobConvolution(x, f, b, padding=(1, 1), act=ops.ACT_RELU)
+        got_mmt = ops.MultiplyMatrixByTransposedMatrix(a, w)
+        torch.cuda.synchronize()
+    finally:
+        lib.nb200_debug_set_contraction_trace(None, 0, 0)
+    assert torch.equal(got_conv, want_conv)
+    assert torch.equal(got_mmt, want_mmt)
