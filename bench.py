@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--unfused", action="store_true", help="issue conv / add / ReLU as separate engine calls")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", action="store_true", help="print the per-contraction timing table to stderr")
+    ap.add_argument("--ops", action="store_true",
+                    help="instead of the network: time the bandwidth-bound kernels at the configs' sizes (one JSON line each)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
     return ap.parse_args()
 
@@ -371,10 +373,85 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ops(args):
+    """The bandwidth-bound kernels of the path at the sizes the configs give them, against the measured HBM peak.
+    Algorithmic bytes = unique input elements * 4 + output elements * 4 (in place counts read + write).  Every tensor
+    is larger than L2 (126 MB) or the op is repeated over several buffers so that L2 does not serve the reads."""
+    import torch
+    from neoml_b200 import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --ops needs a CUDA device: the product path has no CPU fallback")
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
+    peak_src = "MEASURED_PEAKS.json hbm_gbs" if peaks_path.exists() else "fallback: 6.65 TB/s measured on this pool earlier"
+    dev = "cuda"
+    rnd = lambda *shape: torch.rand(*shape, device=dev)
+    zero = torch.zeros(1, device=dev)
+    cases = []
+    # config 3 (ResNet-50, batch 256): activations of the stem and of stage 1
+    a, b2 = rnd(256, 112, 112, 64), rnd(256, 112, 112, 64)          # 822 MB each
+    cases.append(("VectorAdd 205M (stem output size)", lambda: ops.VectorAdd(a, b2, result=a), 3 * a.numel() * 4))
+    cases.append(("VectorReLU 205M in place", lambda: ops.VectorReLU(a, result=a, threshold=zero), 2 * a.numel() * 4))
+    padded = torch.empty(256, 114, 114, 64, device=dev)
+    cases.append(("BlobResizeImage 256x112x112x64 +1 each side", lambda: ops.BlobResizeImage(a, 1, 1, 1, 1, 0, 0.0, result=padded),
+                  (a.numel() + padded.numel()) * 4))
+    pooled = torch.empty(256, 56, 56, 64, device=dev)
+    cases.append(("BlobMaxPooling 3x3/2 on 256x114x114x64", lambda: ops.BlobMaxPooling(padded, (3, 3), (2, 2), result=pooled),
+                  (padded.numel() + pooled.numel()) * 4))
+    feat = rnd(1024, 7, 7, 2048)                                     # 411 MB: global mean pool of a batch-1024 shard
+    cases.append(("SumMatrixRows 1024x49x2048 (global pool)", lambda: ops.SumMatrixRows(1024, feat, 49, 2048), feat.numel() * 4))
+    # config 2: depthwise 3x3 of the MobileNetV2 block
+    dwx, dww, dwb = rnd(64, 56, 56, 192), rnd(3, 3, 192), rnd(192)
+    dwy = torch.empty_like(dwx)
+    cases.append(("BlobChannelwiseConvolution 3x3 64x56x56x192", lambda: ops.BlobChannelwiseConvolution(
+        dwx, dww, dwb, result=dwy, padding=(1, 1), act=ops.ACT_RELU, act_param=6.0), 2 * dwx.numel() * 4))
+    # config 4 (transformer, batch 64 x seq 512): scores, projections
+    scores = rnd(768 * 512, 512)                                    # 805 MB
+    cases.append(("MatrixSoftmaxByRows 393216x512 in place", lambda: ops.MatrixSoftmaxByRows(scores, 768 * 512, 512, result=scores),
+                  2 * scores.numel() * 4))
+    mask = rnd(512 * 512)
+    cases.append(("AddVectorToMatrixRows 768 x 262144 (mask)", lambda: ops.AddVectorToMatrixRows(1, scores, mask, 768, 512 * 512, result=scores),
+                  2 * scores.numel() * 4))
+    scale = torch.full((1,), 0.125, device=dev)
+    cases.append(("VectorMultiply 201M (score scale)", lambda: ops.vector_op("MULTIPLY", scores.view(-1), scalar=scale, result=scores.view(-1)),
+                  2 * scores.numel() * 4))
+    q = rnd(64 * 512 * 12 * 64)                                      # 100 MB: four of them rotate to defeat L2
+    qs = [rnd(64 * 512 * 12 * 64) for _ in range(4)]
+    qt = torch.empty_like(q)
+    rot = {"i": 0}
+
+    def transpose():
+        rot["i"] = (rot["i"] + 1) % 4
+        return ops.TransposeMatrix(64, qs[rot["i"]], 512, 1, 12, 64, result=qt)
+    cases.append(("TransposeMatrix [64,512,12,64] -> [64,12,512,64]", transpose, 2 * q.numel() * 4))
+    hid = rnd(32768, 3072)                                           # 403 MB
+    cases.append(("VectorSigmoid 100M (GELU gate)", lambda: ops.vector_op("SIGMOID", hid.view(-1), result=hid.view(-1)), 2 * hid.numel() * 4))
+    colsum = torch.empty(32768, device=dev)
+    cases.append(("SumMatrixColumns 32768x3072 (layer norm)", lambda: ops.SumMatrixColumns(hid, 32768, 3072, result=colsum), hid.numel() * 4))
+
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn, nbytes in cases:
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+        gbs = nbytes / ms / 1e6
+        print(json.dumps({"op": name, "ms": round(ms, 4), "algorithmic_mb": round(nbytes / 1e6, 1),
+                          "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                                       "frac": round(gbs / peak, 3), "peak_source": peak_src}}))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.ops:
+        run_ops(args)
     else:
         run_ours(args)
 

@@ -157,68 +157,62 @@ __global__ void __launch_bounds__(256) chconv_kernel(const nb200_chconv_desc p, 
 }
 
 // 3x3 depthwise convolution, padding 1, stride 1 or 2, channels a multiple of four: a thread owns four channels of a
-// strip of TW neighbouring output columns and slides the window along the strip, so each input column (three rows of
-// four channels) is loaded once per strip instead of three times, and the index arithmetic is paid once per strip.
-// Consecutive threads take consecutive channel quads: every load and store of a warp is one contiguous run.
-constexpr int CH3_TW = 8;
-
+// strip of TW neighbouring output columns.  It first loads every input column the strip touches (three rows of four
+// channels each; TW + 2 columns for stride 1, 2 TW + 1 for stride 2) -- all independent loads, in flight together --
+// and then forms the outputs from registers, so each input column is fetched once per strip instead of three times
+// and the index arithmetic is paid once per strip.  Consecutive threads take consecutive channel quads: every load
+// and store of a warp is one contiguous run.
 template<int STRIDE>
 __global__ void __launch_bounds__(256) chconv3x3_kernel(const nb200_chconv_desc p, const float* __restrict__ x,
 	const float* __restrict__ filter, const float* __restrict__ freeTerm, float* __restrict__ y, int act,
-	float actParam, int strips, long long total)
+	float actParam, int strips, unsigned total)
 {
-	const int cv = p.c / 4;
+	constexpr int TW = STRIDE == 1 ? 4 : 2;
+	constexpr int COLS = STRIDE == 1 ? TW + 2 : 2 * TW + 1;
+	const unsigned cv = p.c / 4;
 	const bool relu = act == NB200_ACT_RELU;
 	const float reluHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
-	const long long gstride = static_cast<long long>(gridDim.x) * blockDim.x;
-	for(long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += gstride) {
-		long long r = t;
-		const int cq = static_cast<int>(r % cv); r /= cv;
-		const int sx = static_cast<int>(r % strips); r /= strips;
+	for(unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+		unsigned r = t;
+		const unsigned cq = r % cv; r /= cv;
+		const unsigned sx = r % strips; r /= strips;
 		const int oy = static_cast<int>(r % p.ho);
-		const long long n = r / p.ho;
-		const int ox0 = sx * CH3_TW;
-		const float4* img = reinterpret_cast<const float4*>(x + n * p.h * p.w * p.c) + cq;
+		const unsigned n = r / p.ho;
+		const int ox0 = sx * TW;
+		const float4* img = reinterpret_cast<const float4*>(x) + static_cast<size_t>(n) * p.h * p.w * cv + cq;
+		const int iy0 = oy * STRIDE - 1, ix0 = ox0 * STRIDE - 1;
+		float4 col[COLS][3];
+#pragma unroll
+		for(int k = 0; k < COLS; ++k) {
+			const int ix = ix0 + k;
+			const bool colOk = static_cast<unsigned>(ix) < static_cast<unsigned>(p.w);
+#pragma unroll
+			for(int fy = 0; fy < 3; ++fy) {
+				const int iy = iy0 + fy;
+				col[k][fy] = make_float4(0.f, 0.f, 0.f, 0.f);
+				if(colOk && static_cast<unsigned>(iy) < static_cast<unsigned>(p.h)) {
+					col[k][fy] = __ldg(img + (static_cast<size_t>(iy) * p.w + ix) * cv);
+				}
+			}
+		}
 		const float4* flt = reinterpret_cast<const float4*>(filter) + cq;
 		float4 f[9];
 #pragma unroll
 		for(int i = 0; i < 9; ++i) f[i] = __ldg(flt + i * cv);
 		const float4 b = freeTerm != nullptr ? __ldg(reinterpret_cast<const float4*>(freeTerm) + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
-		const int iy0 = oy * STRIDE - 1;
-		bool rowOk[3];
+		float4* out = reinterpret_cast<float4*>(y) + ((static_cast<size_t>(n) * p.ho + oy) * p.wo + ox0) * cv + cq;
 #pragma unroll
-		for(int fy = 0; fy < 3; ++fy) rowOk[fy] = static_cast<unsigned>(iy0 + fy) < static_cast<unsigned>(p.h);
-		auto column = [&](int ix, float4* col) {
-			const bool colOk = static_cast<unsigned>(ix) < static_cast<unsigned>(p.w);
-#pragma unroll
-			for(int fy = 0; fy < 3; ++fy) {
-				col[fy] = make_float4(0.f, 0.f, 0.f, 0.f);
-				if(colOk && rowOk[fy]) col[fy] = __ldg(img + (static_cast<long long>(iy0 + fy) * p.w + ix) * cv);
-			}
-		};
-		float4 c0[3], c1[3], c2[3];
-		column(ox0 * STRIDE - 1, c0);
-		if(STRIDE == 1) column(ox0, c1);
-		float4* out = reinterpret_cast<float4*>(y) + ((n * p.ho + oy) * p.wo + ox0) * cv + cq;
-#pragma unroll
-		for(int j = 0; j < CH3_TW; ++j) {
-			const int ox = ox0 + j;
-			if(ox >= p.wo) break;
-			if(STRIDE == 1) {
-				column(ox + 1, c2);
-			} else {
-				column(ox * 2, c1);
-				column(ox * 2 + 1, c2);
-			}
+		for(int j = 0; j < TW; ++j) {
+			if(ox0 + j >= p.wo) break;
 			float4 a = b;
 #pragma unroll
 			for(int fy = 0; fy < 3; ++fy) {
-				a.x = fmaf(c0[fy].x, f[3 * fy].x, a.x); a.y = fmaf(c0[fy].y, f[3 * fy].y, a.y);
-				a.z = fmaf(c0[fy].z, f[3 * fy].z, a.z); a.w = fmaf(c0[fy].w, f[3 * fy].w, a.w);
-				a.x = fmaf(c1[fy].x, f[3 * fy + 1].x, a.x); a.y = fmaf(c1[fy].y, f[3 * fy + 1].y, a.y);
-				a.z = fmaf(c1[fy].z, f[3 * fy + 1].z, a.z); a.w = fmaf(c1[fy].w, f[3 * fy + 1].w, a.w);
-				a.x = fmaf(c2[fy].x, f[3 * fy + 2].x, a.x); a.y = fmaf(c2[fy].y, f[3 * fy + 2].y, a.y);
-				a.z = fmaf(c2[fy].z, f[3 * fy + 2].z, a.z); a.w = fmaf(c2[fy].w, f[3 * fy + 2].w, a.w);
+#pragma unroll
+				for(int fx = 0; fx < 3; ++fx) {
+					const float4 v = col[j * STRIDE + fx][fy];
+					const float4 w = f[3 * fy + fx];
+					a.x = fmaf(v.x, w.x, a.x); a.y = fmaf(v.y, w.y, a.y); a.z = fmaf(v.z, w.z, a.z); a.w = fmaf(v.w, w.w, a.w);
+				}
 			}
 			if(act == NB200_ACT_HSWISH) {
 				a.x = apply_act(a.x, act, actParam); a.y = apply_act(a.y, act, actParam);
@@ -227,11 +221,54 @@ __global__ void __launch_bounds__(256) chconv3x3_kernel(const nb200_chconv_desc 
 				a.x = relu ? fminf(fmaxf(a.x, 0.f), reluHi) : a.x; a.y = relu ? fminf(fmaxf(a.y, 0.f), reluHi) : a.y;
 				a.z = relu ? fminf(fmaxf(a.z, 0.f), reluHi) : a.z; a.w = relu ? fminf(fmaxf(a.w, 0.f), reluHi) : a.w;
 			}
-			out[static_cast<long long>(j) * cv] = a;
+			out[static_cast<size_t>(j) * cv] = a;
+		}
+	}
+}
+
+// 3x3 / stride 2 max pooling without indices (the inference form; ResNet's stem pool), channels a multiple of four:
+// a thread owns four channels of a strip of TW output columns and slides along it, so the column shared by two
+// neighbouring windows is loaded once.  Window order (rows outer, columns inner) and the `v > best` comparison are those
+// of the general kernel, so the results are identical.
+constexpr int MP3_TW = 4;
+
+__global__ void __launch_bounds__(256) maxpool3x3s2_kernel(const Pool2d p, const float* __restrict__ x, float* __restrict__ y,
+	int strips, unsigned total)
+{
+	const unsigned cv = p.c / 4;
+	for(unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+		unsigned r = t;
+		const unsigned cq = r % cv; r /= cv;
+		const unsigned sx = r % strips; r /= strips;
+		const unsigned oy = r % p.ho;
+		const unsigned n = r / p.ho;
+		const int ox0 = sx * MP3_TW;
+		const float4* img = reinterpret_cast<const float4*>(x) + (static_cast<size_t>(n) * p.h + 2 * oy) * p.w * cv + cq;
+		float4* out = reinterpret_cast<float4*>(y) + ((static_cast<size_t>(n) * p.ho + oy) * p.wo + ox0) * cv + cq;
+		const int outs = min(MP3_TW, p.wo - ox0);
+		// all columns of the strip first (2 * outs + 1 of them, three rows each): many independent loads in flight
+		float4 col[2 * MP3_TW + 1][3];
+#pragma unroll
+		for(int k = 0; k < 2 * MP3_TW + 1; ++k) {
+			if(k <= 2 * outs) {
+#pragma unroll
+				for(int fy = 0; fy < 3; ++fy) col[k][fy] = __ldg(img + (static_cast<size_t>(fy) * p.w + 2 * ox0 + k) * cv);
+			}
+		}
+#pragma unroll
+		for(int j = 0; j < MP3_TW; ++j) {
+			if(j >= outs) break;
+			float4 best = col[2 * j][0];
 #pragma unroll
 			for(int fy = 0; fy < 3; ++fy) {
-				if(STRIDE == 1) { c0[fy] = c1[fy]; c1[fy] = c2[fy]; } else { c0[fy] = c2[fy]; }
+#pragma unroll
+				for(int fx = 0; fx < 3; ++fx) {
+					const float4 v = col[2 * j + fx][fy];
+					best.x = v.x > best.x ? v.x : best.x; best.y = v.y > best.y ? v.y : best.y;
+					best.z = v.z > best.z ? v.z : best.z; best.w = v.w > best.w ? v.w : best.w;
+				}
 			}
+			out[static_cast<size_t>(j) * cv] = best;
 		}
 	}
 }
@@ -249,7 +286,12 @@ int pool_common(void* stream, bool isMax, int batch, int h, int w, int c, int fh
 	if(device_status_word() == nullptr) return NB200_ENODEVICE;
 	const bool vec = c % 4 == 0 && aligned16(x) && aligned16(y);
 	cudaStream_t s = as_stream(stream);
-	if(vec) {
+	if(vec && isMax && maxIndices == nullptr && fh == 3 && fw == 3 && sh == 2 && sw == 2 && outElems / 4 < 0x7fffffffLL
+		&& static_cast<long long>(batch) * h * w * c < 0x7fffffffLL) {
+		const int strips = (p.wo + MP3_TW - 1) / MP3_TW;
+		const long long total = static_cast<long long>(batch) * p.ho * strips * (c / 4);
+		maxpool3x3s2_kernel<<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, strips, static_cast<unsigned>(total));
+	} else if(vec) {
 		const long long total = outElems / 4;
 		if(isMax) pool_kernel<true, 4><<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, maxIndices, total);
 		else pool_kernel<false, 4><<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, nullptr, total);
@@ -319,11 +361,13 @@ int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* d,
 	cudaStream_t s = as_stream(stream);
 	const bool vec = d->c % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(filter)
 		&& (free_term == nullptr || aligned16(free_term));
-	if(vec && d->r == 3 && d->s == 3 && d->pad_h == 1 && d->pad_w == 1 && d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2)) {
-		const int strips = (wo + CH3_TW - 1) / CH3_TW;
+	if(vec && d->r == 3 && d->s == 3 && d->pad_h == 1 && d->pad_w == 1 && d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2)
+		&& static_cast<long long>(d->batch) * d->h * d->w * d->c < 0x7fffffffLL) {
+		const int tw = d->stride_h == 1 ? 4 : 2;
+		const int strips = (wo + tw - 1) / tw;
 		const long long total = static_cast<long long>(d->batch) * ho * strips * (d->c / 4);
-		if(d->stride_h == 1) chconv3x3_kernel<1><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, total);
-		else chconv3x3_kernel<2><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, total);
+		if(d->stride_h == 1) chconv3x3_kernel<1><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, static_cast<unsigned>(total));
+		else chconv3x3_kernel<2><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, static_cast<unsigned>(total));
 	} else if(vec) {
 		chconv_kernel<4><<<grid_for(outElems / 4, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, outElems / 4);
 	} else {

@@ -101,6 +101,44 @@ __global__ void __launch_bounds__(256) sum_rows_kernel(float* __restrict__ y, co
 	}
 }
 
+// The same for widths that are a multiple of four and 16-byte-aligned operands: a block owns 256 columns (64 float4
+// lanes) of one batch entry and four row lanes; each warp access is 512 contiguous bytes.
+__global__ void __launch_bounds__(256) sum_rows_vec_kernel(float* __restrict__ y, const float* __restrict__ x,
+	int height, int width, int rowSlices, int add)
+{
+	__shared__ float4 part[4][64];
+	const int b = blockIdx.z;
+	const int q = threadIdx.x & 63;             // float4 lane inside the block's 256 columns
+	const int lane4 = threadIdx.x >> 6;         // row lane
+	const int w4 = blockIdx.x * 64 + q;         // float4 column
+	const int width4 = width >> 2;
+	const int slice = blockIdx.y;
+	const int rowsPerSlice = (height + rowSlices - 1) / rowSlices;
+	const int h0 = slice * rowsPerSlice;
+	const int h1 = min(height, h0 + rowsPerSlice);
+	float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+	if(w4 < width4) {
+		const float4* src = reinterpret_cast<const float4*>(x) + static_cast<size_t>(b) * height * width4 + w4;
+		for(int h = h0 + lane4; h < h1; h += 4) {
+			const float4 v = __ldg(src + static_cast<size_t>(h) * width4);
+			acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+		}
+	}
+	part[lane4][q] = acc;
+	__syncthreads();
+	if(lane4 == 0 && w4 < width4) {
+		float4 s = part[0][q];
+#pragma unroll
+		for(int i = 1; i < 4; ++i) { s.x += part[i][q].x; s.y += part[i][q].y; s.z += part[i][q].z; s.w += part[i][q].w; }
+		float* dst = y + static_cast<size_t>(b) * width + 4 * w4;
+		if(rowSlices > 1 || add) {
+			atomicAdd(dst, s.x); atomicAdd(dst + 1, s.y); atomicAdd(dst + 2, s.z); atomicAdd(dst + 3, s.w);
+		} else {
+			*reinterpret_cast<float4*>(dst) = s;
+		}
+	}
+}
+
 // y[h] = sum_w x[h][w]: one warp per row
 __global__ void __launch_bounds__(256) sum_cols_kernel(float* __restrict__ y, const float* __restrict__ x,
 	int height, int width)
@@ -213,6 +251,22 @@ __global__ void __launch_bounds__(256) transpose_rows_kernel(const uint32_t* __r
 		const int w = static_cast<int>(t % width); t /= width;
 		const long long b = t;
 		y[o] = x[(((b * height + h) * medium + m) * width + w) * channels + c];
+	}
+}
+
+// The same with 16-byte pieces for channel counts that are a multiple of four (attention heads: 64 channels): a
+// quarter of the index arithmetic per byte, all of it in 32 bits.
+__global__ void __launch_bounds__(256) transpose_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y,
+	unsigned height, unsigned medium, unsigned width, unsigned channels4, unsigned total)
+{
+	for(unsigned o = blockIdx.x * blockDim.x + threadIdx.x; o < total; o += gridDim.x * blockDim.x) {
+		unsigned t = o;
+		const unsigned c = t % channels4; t /= channels4;
+		const unsigned h = t % height; t /= height;
+		const unsigned m = t % medium; t /= medium;
+		const unsigned w = t % width;
+		const unsigned b = t / width;
+		y[o] = __ldg(x + ((((static_cast<size_t>(b) * height + h) * medium + m) * width + w) * channels4 + c));
 	}
 }
 
@@ -379,8 +433,13 @@ int nb200_sum_matrix_rows(void* stream, int batch, float* y, const float* x, int
 		if(!add) cudaMemsetAsync(y, 0, static_cast<size_t>(batch) * width * sizeof(float), as_stream(stream));
 		return check_launch();
 	}
-	dim3 grid(colBlocks, rowSlices, batch);
-	sum_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(y, x, height, width, rowSlices, add);
+	if(width % 4 == 0 && aligned16(x) && aligned16(y)) {
+		dim3 grid((width / 4 + 63) / 64, rowSlices, batch);
+		sum_rows_vec_kernel<<<grid, 256, 0, as_stream(stream)>>>(y, x, height, width, rowSlices, add);
+	} else {
+		dim3 grid(colBlocks, rowSlices, batch);
+		sum_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(y, x, height, width, rowSlices, add);
+	}
 	count_launch(launches);
 	return check_launch();
 }
@@ -429,6 +488,9 @@ int nb200_transpose_matrix(void* stream, int batch, const void* x, int height, i
 	if(channels == 1 && medium == 1 && height > 1 && width > 1 && batch <= 65535 && (height + 31) / 32 <= 65535) {
 		dim3 grid((width + 31) / 32, (height + 31) / 32, batch);
 		transpose_tile_kernel<<<grid, 256, 0, s>>>(src, dst, height, width);
+	} else if(channels % 4 == 0 && total / 4 < 0x7fffffffLL && aligned16(x) && aligned16(y)) {
+		transpose_rows_vec_kernel<<<grid_for(total / 4, 256, 16), 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y),
+			height, medium, width, channels / 4, static_cast<unsigned>(total / 4));
 	} else {
 		transpose_rows_kernel<<<grid_for(total, 256, 16), 256, 0, s>>>(src, dst, height, medium, width, channels, total);
 	}

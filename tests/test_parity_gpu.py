@@ -343,3 +343,19 @@ def test_gather_kernel_agrees_with_the_tma_kernel(ops):
         lib.nb200_debug_set_contraction_trace(None, 0, 0)
     assert torch.equal(got_conv, want_conv)
     assert torch.equal(got_mmt, want_mmt)
+
+
+def test_vectorised_helper_variants(ops, oracle):
+    """The 16-byte forms of row sums, the channel-vector transpose and the strip max-pool against the oracle."""
+    for (bsz, h, w) in [(3, 49, 2048), (1, 700, 260), (2, 5, 4)]:     # the second splits its rows over slices
+        m = cases.uniform(71, (bsz * h * w,))
+        assert gate_err(host(ops.SumMatrixRows(bsz, dev(m), h, w)), oracle.sum_matrix_rows(bsz, m, h, w)) < 1e-5
+        init = cases.uniform(72, (bsz, w))
+        assert gate_err(host(ops.SumMatrixRows(bsz, dev(m), h, w, result=dev(init), add=True)),
+                        oracle.sum_matrix_rows(bsz, m, h, w, init)) < 1e-5
+    for (b, h, mm, w, c) in [(2, 48, 1, 12, 64), (2, 5, 3, 7, 8), (1, 9, 1, 1, 4)]:
+        t = cases.uniform(73, (b * h * mm * w * c,))
+        assert np.array_equal(host(ops.TransposeMatrix(b, dev(t), h, mm, w, c)), oracle.transpose_matrix(b, t, h, mm, w, c))
+    for shape in [(2, 23, 31, 8), (1, 7, 9, 64), (3, 3, 3, 4)]:          # odd sizes: partial strips at the right edge
+        x = cases.uniform(74, shape)
+        assert np.array_equal(host(ops.BlobMaxPooling(dev(x), (3, 3), (2, 2))), oracle.blob_max_pooling(x, (3, 3), (2, 2))[0])
