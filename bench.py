@@ -385,49 +385,53 @@ def run_ops(args):
     peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
     peak_src = "MEASURED_PEAKS.json hbm_gbs" if peaks_path.exists() else "fallback: 6.65 TB/s measured on this pool earlier"
     dev = "cuda"
+    n = args.batch            # images of config 3; --batch 128 halves every tensor (for profiler captures)
+    tb = max(1, 64 * n // 256)  # sequences of config 4
     rnd = lambda *shape: torch.rand(*shape, device=dev)
     zero = torch.zeros(1, device=dev)
     cases = []
     # config 3 (ResNet-50, batch 256): activations of the stem and of stage 1
-    a, b2 = rnd(256, 112, 112, 64), rnd(256, 112, 112, 64)          # 822 MB each
-    cases.append(("VectorAdd 205M (stem output size)", lambda: ops.VectorAdd(a, b2, result=a), 3 * a.numel() * 4))
-    cases.append(("VectorReLU 205M in place", lambda: ops.VectorReLU(a, result=a, threshold=zero), 2 * a.numel() * 4))
-    padded = torch.empty(256, 114, 114, 64, device=dev)
-    cases.append(("BlobResizeImage 256x112x112x64 +1 each side", lambda: ops.BlobResizeImage(a, 1, 1, 1, 1, 0, 0.0, result=padded),
+    a, b2 = rnd(n, 112, 112, 64), rnd(n, 112, 112, 64)              # 822 MB each at batch 256
+    cases.append((f"VectorAdd {n}x112x112x64 (stem output size)", lambda: ops.VectorAdd(a, b2, result=a), 3 * a.numel() * 4))
+    cases.append((f"VectorReLU {n}x112x112x64 in place", lambda: ops.VectorReLU(a, result=a, threshold=zero), 2 * a.numel() * 4))
+    padded = torch.empty(n, 114, 114, 64, device=dev)
+    cases.append((f"BlobResizeImage {n}x112x112x64 +1 each side", lambda: ops.BlobResizeImage(a, 1, 1, 1, 1, 0, 0.0, result=padded),
                   (a.numel() + padded.numel()) * 4))
-    pooled = torch.empty(256, 56, 56, 64, device=dev)
-    cases.append(("BlobMaxPooling 3x3/2 on 256x114x114x64", lambda: ops.BlobMaxPooling(padded, (3, 3), (2, 2), result=pooled),
+    pooled = torch.empty(n, 56, 56, 64, device=dev)
+    cases.append((f"BlobMaxPooling 3x3/2 on {n}x114x114x64", lambda: ops.BlobMaxPooling(padded, (3, 3), (2, 2), result=pooled),
                   (padded.numel() + pooled.numel()) * 4))
-    feat = rnd(1024, 7, 7, 2048)                                     # 411 MB: global mean pool of a batch-1024 shard
-    cases.append(("SumMatrixRows 1024x49x2048 (global pool)", lambda: ops.SumMatrixRows(1024, feat, 49, 2048), feat.numel() * 4))
+    feat = rnd(4 * n, 7, 7, 2048)                                    # 411 MB: global mean pool of a batch-1024 shard
+    cases.append((f"SumMatrixRows {4 * n}x49x2048 (global pool)", lambda: ops.SumMatrixRows(4 * n, feat, 49, 2048), feat.numel() * 4))
     # config 2: depthwise 3x3 of the MobileNetV2 block
-    dwx, dww, dwb = rnd(64, 56, 56, 192), rnd(3, 3, 192), rnd(192)
+    dwx, dww, dwb = rnd(max(1, n // 4), 56, 56, 192), rnd(3, 3, 192), rnd(192)
     dwy = torch.empty_like(dwx)
-    cases.append(("BlobChannelwiseConvolution 3x3 64x56x56x192", lambda: ops.BlobChannelwiseConvolution(
+    cases.append((f"BlobChannelwiseConvolution 3x3 {max(1, n // 4)}x56x56x192", lambda: ops.BlobChannelwiseConvolution(
         dwx, dww, dwb, result=dwy, padding=(1, 1), act=ops.ACT_RELU, act_param=6.0), 2 * dwx.numel() * 4))
     # config 4 (transformer, batch 64 x seq 512): scores, projections
-    scores = rnd(768 * 512, 512)                                    # 805 MB
-    cases.append(("MatrixSoftmaxByRows 393216x512 in place", lambda: ops.MatrixSoftmaxByRows(scores, 768 * 512, 512, result=scores),
+    heads = 12 * tb
+    scores = rnd(heads * 512, 512)                                  # 805 MB at batch 64 x 12 heads
+    cases.append((f"MatrixSoftmaxByRows {heads * 512}x512 in place", lambda: ops.MatrixSoftmaxByRows(scores, heads * 512, 512, result=scores),
                   2 * scores.numel() * 4))
     mask = rnd(512 * 512)
-    cases.append(("AddVectorToMatrixRows 768 x 262144 (mask)", lambda: ops.AddVectorToMatrixRows(1, scores, mask, 768, 512 * 512, result=scores),
+    cases.append((f"AddVectorToMatrixRows {heads} x 262144 (mask)", lambda: ops.AddVectorToMatrixRows(1, scores, mask, heads, 512 * 512, result=scores),
                   2 * scores.numel() * 4))
     scale = torch.full((1,), 0.125, device=dev)
-    cases.append(("VectorMultiply 201M (score scale)", lambda: ops.vector_op("MULTIPLY", scores.view(-1), scalar=scale, result=scores.view(-1)),
+    cases.append((f"VectorMultiply {heads}x512x512 (score scale)", lambda: ops.vector_op("MULTIPLY", scores.view(-1), scalar=scale, result=scores.view(-1)),
                   2 * scores.numel() * 4))
-    q = rnd(64 * 512 * 12 * 64)                                      # 100 MB: four of them rotate to defeat L2
-    qs = [rnd(64 * 512 * 12 * 64) for _ in range(4)]
+    q = rnd(tb * 512 * 12 * 64)                                      # 100 MB: four of them rotate to defeat L2
+    qs = [rnd(tb * 512 * 12 * 64) for _ in range(4)]
     qt = torch.empty_like(q)
     rot = {"i": 0}
 
     def transpose():
         rot["i"] = (rot["i"] + 1) % 4
-        return ops.TransposeMatrix(64, qs[rot["i"]], 512, 1, 12, 64, result=qt)
-    cases.append(("TransposeMatrix [64,512,12,64] -> [64,12,512,64]", transpose, 2 * q.numel() * 4))
-    hid = rnd(32768, 3072)                                           # 403 MB
-    cases.append(("VectorSigmoid 100M (GELU gate)", lambda: ops.vector_op("SIGMOID", hid.view(-1), result=hid.view(-1)), 2 * hid.numel() * 4))
-    colsum = torch.empty(32768, device=dev)
-    cases.append(("SumMatrixColumns 32768x3072 (layer norm)", lambda: ops.SumMatrixColumns(hid, 32768, 3072, result=colsum), hid.numel() * 4))
+        return ops.TransposeMatrix(tb, qs[rot["i"]], 512, 1, 12, 64, result=qt)
+    cases.append((f"TransposeMatrix [{tb},512,12,64] -> [{tb},12,512,64]", transpose, 2 * q.numel() * 4))
+    rows = tb * 512
+    hid = rnd(rows, 3072)                                            # 403 MB
+    cases.append((f"VectorSigmoid {rows}x3072 (GELU gate)", lambda: ops.vector_op("SIGMOID", hid.view(-1), result=hid.view(-1)), 2 * hid.numel() * 4))
+    colsum = torch.empty(rows, device=dev)
+    cases.append((f"SumMatrixColumns {rows}x3072 (layer norm)", lambda: ops.SumMatrixColumns(hid, rows, 3072, result=colsum), hid.numel() * 4))
 
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for name, fn, nbytes in cases:
