@@ -65,3 +65,26 @@ def test_resnet50_through_the_cpp_engine(net):
 def test_flop_count_matches_published_figure():
     assert abs(resnet50.flops_per_image() / 1e9 - 8.178) < 0.01
     assert len(resnet50.conv_specs()) == 53
+
+
+@gpu
+def test_forward_pass_replays_from_a_cuda_graph(net):
+    """The library allocates nothing and keeps no per-call host state: a captured forward pass replays bit for bit."""
+    weights, x, _, _ = net
+    be = resnet50.EngineBackend()
+    dw = be.upload(weights)
+    dx = torch.from_numpy(x).cuda()
+    probs, idx = resnet50.forward(be, dw, dx, fuse=True)          # also the one-time set-up, outside capture
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            g_probs, g_idx = resnet50.forward(be, dw, dx, fuse=True)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        g_probs.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(g_probs, probs) and torch.equal(g_idx, idx)
