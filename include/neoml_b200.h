@@ -101,24 +101,25 @@ typedef struct nb200_conv_desc {
 	int pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
 	int ho, wo;                  /* result */
 } nb200_conv_desc;
-/* `scratch` is optional (NULL = none): nb200_blob_convolution_scratch_floats(desc) floats of device memory (0 for most
- * shapes) that let a convolution whose channel count is not a multiple of four (the 3-channel network stem) run on
- * 16-byte pieces: the image and the filter are widened to 4-channel pixels there first.  The engine takes it from
- * its stack allocator; without it the same result is computed by a slower element-wise gather. */
+/* `scratch` is optional (NULL = none): nb200_blob_convolution_scratch_floats(desc) floats of device memory for what
+ * the fast paths prepare once per call: the filter split for the tensor core (lo part / rounded copy, so that no CTA
+ * converts its filter tiles), and for few-channel images (the 3-channel network stem) a copy of the image with its
+ * spatial padding and 4-channel pixels plus the filter widened to match.  The engine takes it from its block pool;
+ * without it the same result is computed by slower in-kernel conversion and element-wise gathers. */
 NB200_API size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* desc);
 NB200_API int nb200_blob_convolution(void* stream, const nb200_conv_desc* desc, const float* x,
 	const float* filter, float* y, float* scratch, const nb200_epilogue* epi, int precision);
 /* No counterpart in the reference.  The same convolution for callers that cannot provide scratch memory at the moment
  * of the call (all device memory already in their own pool; a loop that must not stall on cudaMalloc; a fixed memory
- * budget): the channel-padding work space is a fixed array of NB200_STATIC_SCRATCH_FLOATS floats inside the library's
- * device module, and neither this call nor anything under it allocates or frees memory.
+ * budget): the work space (prepared filter, padded image) is a fixed array of NB200_STATIC_SCRATCH_FLOATS floats inside
+ * the library's device module, and neither this call nor anything under it allocates or frees memory.
  *  - A shape that needs more than NB200_STATIC_SCRATCH_FLOATS floats of scratch
  *    (nb200_blob_convolution_scratch_floats(desc)) is refused with NB200_ETOOBIG before anything is launched.
  *  - The first call on each device looks the array up (and may load the module): make it during set-up, with that
  *    device current, before a stream capture begins.
  *  - One work space per device: calls that overlap in time on one device (other streams, other threads) race on it;
  *    calls on one stream are ordered.  Nothing in it needs to be zero beforehand. */
-#define NB200_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024) /* 16 MiB: e.g. a batch of 20 RGB 224x224 images + 7x7x64 filter */
+#define NB200_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024) /* 16 MiB: e.g. 19 padded RGB 224x224 images + a 7x7x64 filter */
 NB200_API int nb200_blob_convolution_static_scratch(void* stream, const nb200_conv_desc* desc, const float* x,
 	const float* filter, float* y, const nb200_epilogue* epi, int precision);
 

@@ -1,7 +1,7 @@
-// Convolution with channel padding whose work space belongs to the library itself.
+// Convolution whose work space belongs to the library itself.
 //
-// nb200_blob_convolution() widens a 3-channel (or any C % 4 != 0) image and its filter to 4-channel pixels in scratch
-// memory that the CALLER has to provide.  Some callers have no way to provide it at the moment of the call: a host
+// nb200_blob_convolution() prepares its operands (the split filter; for few-channel images a padded copy with
+// 4-channel pixels) in scratch memory that the CALLER has to provide.  Some callers have no way to provide it at the moment of the call: a host
 // whose device memory has all been handed to a pool of its own, a real-time loop in which cudaMalloc would stall every
 // stream of the device, a layer that is called with a fixed memory budget it may not exceed.  For them this file keeps a
 // fixed work space inside the module image (a file-scope __device__ array, placed by the driver when the module is
@@ -16,7 +16,7 @@
 //  * there is ONE work space per device: two calls that are in flight at the same time on one device (different
 //    streams, or different threads) race on it.  Calls on one stream are ordered and safe;
 //  * nothing in the work space has to be zero beforehand: every float the convolution reads, the zeros of the added
-//    channels included, is written by the same call first.
+//    channels and of the spatial padding included, is written by the same call first.
 #include "contraction.cuh"
 
 #include <mutex>
