@@ -343,9 +343,75 @@ IMathEngine* CreateB200MathEngine( int deviceIndex, size_t memoryLimit, int flag
 	return engine;
 }
 
+// The sm_100 devices as the reference's GPU manager lists them: every entry is MET_Cuda, Id = CUDA device index,
+// AvailableMemory = the device's total memory (what the reference reports too, GPU/CUDA/CudaDevice.cpp).
+class CB200MathEngineManager : public IGpuMathEngineManager {
+public:
+	CB200MathEngineManager()
+	{
+		int count = 0;
+		if( nb200_device_count() <= 0 || cudaGetDeviceCount( &count ) != cudaSuccess ) { cudaGetLastError(); return; }
+		for( int i = 0; i < count; ++i ) {
+			cudaDeviceProp prop;
+			if( cudaGetDeviceProperties( &prop, i ) != cudaSuccess ) { cudaGetLastError(); continue; }
+			if( prop.major != 10 ) continue;
+			CMathEngineInfo info( MET_Cuda, prop.totalGlobalMem, i );
+			std::snprintf( info.Name, sizeof( info.Name ), "%s", prop.name );
+			devices.push_back( info );
+		}
+	}
+
+	int GetMathEngineCount() const override { return static_cast<int>( devices.size() ); }
+
+	void GetMathEngineInfo( int index, CMathEngineInfo& info ) const override
+	{
+		info = index >= 0 && index < GetMathEngineCount() ? devices[index] : CMathEngineInfo();
+	}
+
+	IMathEngine* CreateMathEngine( int index, size_t memoryLimit, int flags ) const override
+	{
+		if( devices.empty() || index >= GetMathEngineCount() ) return nullptr;
+		return CreateB200MathEngine( devices[index >= 0 ? index : 0].Id, memoryLimit, flags );
+	}
+
+private:
+	std::vector<CMathEngineInfo> devices;
+};
+
+IGpuMathEngineManager* CreateB200MathEngineManager()
+{
+	return new CB200MathEngineManager();
+}
+
 } // namespace NeoML
 
 // C entry points for hosts that load the engine library dynamically (ctypes, dlopen)
+extern "C" __attribute__((visibility("default"))) void* nb200_create_math_engine_manager()
+{
+	return NeoML::CreateB200MathEngineManager();
+}
+
+// Devices the manager lists; with engine != NULL also creates an engine on entry `index` through the manager.
+extern "C" __attribute__((visibility("default"))) int nb200_manager_probe( void* manager, int index, void** engine,
+	unsigned long long* memory, char* name, int nameSize )
+{
+	NeoML::IGpuMathEngineManager* m = static_cast<NeoML::IGpuMathEngineManager*>( manager );
+	const int count = m->GetMathEngineCount();
+	if( index >= 0 && index < count ) {
+		NeoML::CMathEngineInfo info;
+		m->GetMathEngineInfo( index, info );
+		if( memory != nullptr ) *memory = info.AvailableMemory;
+		if( name != nullptr && nameSize > 0 ) std::snprintf( name, nameSize, "%s", info.Name );
+		if( engine != nullptr ) *engine = m->CreateMathEngine( index, 0, 0 );
+	}
+	return count;
+}
+
+extern "C" __attribute__((visibility("default"))) void nb200_destroy_math_engine_manager( void* manager )
+{
+	delete static_cast<NeoML::IGpuMathEngineManager*>( manager );
+}
+
 extern "C" __attribute__((visibility("default"))) void* nb200_create_math_engine( int device, size_t memoryLimit, int flags )
 {
 	return NeoML::CreateB200MathEngine( device, memoryLimit, flags );

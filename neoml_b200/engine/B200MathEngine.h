@@ -149,6 +149,8 @@ private:
 // libNeoMathEngine.so loaded in the same process).
 extern "C++" {
 IMathEngine* CreateB200MathEngine( int deviceIndex, size_t memoryLimit, int flags );
+// The B200 devices of this machine behind the reference's manager interface (NeoMathEngine.h:1286-1305)
+IGpuMathEngineManager* CreateB200MathEngineManager();
 void CreateDistributedB200MathEngines( IMathEngine** mathEngines, int devsCount, const int* cudaDevs, size_t memoryLimit );
 }
 

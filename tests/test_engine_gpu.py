@@ -170,3 +170,25 @@ def test_in_place_add_and_relu_ride_in_the_convolution_epilogue(engine, oracle):
     assert gate_err(fused, want) < TOL_FP32 and gate_err(plain, want) < TOL_FP32
     assert np.array_equal(fused, plain)                     # same arithmetic, same order of additions per element
     assert plain_launches == fused_launches + 2             # the add and the ReLU launched nothing of their own
+
+
+def test_gpu_manager_lists_the_device_and_creates_engines(engine):
+    """IGpuMathEngineManager as NeoML's device pickers use it: count, info, CreateMathEngine(index)."""
+    import ctypes as C
+    lib = engine.engine_lib
+    lib.nb200_create_math_engine_manager.restype = C.c_void_p
+    lib.nb200_manager_probe.restype = C.c_int
+    lib.nb200_manager_probe.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_ulonglong), C.c_char_p, C.c_int]
+    lib.nb200_destroy_math_engine_manager.argtypes = [C.c_void_p]
+    lib.nb200_destroy_math_engine.argtypes = [C.c_void_p]
+    manager = C.c_void_p(lib.nb200_create_math_engine_manager())
+    try:
+        created, memory, name = C.c_void_p(), C.c_ulonglong(0), C.create_string_buffer(256)
+        count = lib.nb200_manager_probe(manager, 0, C.byref(created), C.byref(memory), name, 256)
+        assert count == torch.cuda.device_count() >= 1
+        assert b"B200" in name.value and memory.value > (100 << 30)
+        assert created.value
+        lib.nb200_destroy_math_engine(created)
+        assert lib.nb200_manager_probe(manager, count, None, None, None, 0) == count     # out of range: nothing happens
+    finally:
+        lib.nb200_destroy_math_engine_manager(manager)
