@@ -198,6 +198,12 @@ NB200_API int nb200_multiply_matrix_by_diag_matrix(void* stream, int batch, cons
 	const float* d, int diag_stride, float* y);
 /* MatrixSoftmaxByRows (NME.h:450): row-wise softmax, may run in place. */
 NB200_API int nb200_matrix_softmax_by_rows(void* stream, const float* x, int height, int width, float* y);
+/* The same with the attention chain's two preceding calls folded in (CMultiheadAttentionLayer: VectorMultiply by a
+ * device scalar, NME.h:268-269, then AddVectorToMatrixRows of the mask, NME.h:419-420):
+ * y = softmax_rows(x * *scale_device + row_bias[h % bias_rows][.]), each step rounded to fp32 like the separate calls.
+ * Either of scale_device / row_bias may be NULL; width <= 1024 when one is given (NB200_ETOOBIG otherwise). */
+NB200_API int nb200_matrix_softmax_by_rows_fused(void* stream, const float* x, int height, int width,
+	const float* scale_device, const float* row_bias, int bias_rows, float* y);
 /* TransposeMatrix (NME.h:599-603): x [batch][height][medium][width][channels] -> y [batch][width][medium][height][channels]. */
 NB200_API int nb200_transpose_matrix(void* stream, int batch, const void* x, int height, int medium, int width,
 	int channels, void* y);

@@ -156,20 +156,30 @@ __global__ void __launch_bounds__(256) sum_cols_kernel(float* __restrict__ y, co
 
 // Row softmax, one warp per row when the row fits 32 registers per lane (width <= 1024), kept in registers between
 // the three passes so x is read once and y written once.
+// Optional prologue (the attention chain's scale and mask, folded in by the engine): the element becomes
+// x * *scale (+) bias[h % biasRows][w], each step rounded to fp32 like the separate VectorMultiply and
+// AddVectorToMatrixRows calls it replaces.
 template<int PER_LANE>
 __global__ void __launch_bounds__(256) softmax_rows_reg_kernel(const float* __restrict__ x, float* __restrict__ y,
-	int height, int width)
+	int height, int width, const float* __restrict__ scale, const float* __restrict__ bias, int biasRows)
 {
 	const int warpsPerBlock = blockDim.x >> 5;
 	const int lane = threadIdx.x & 31;
+	const float mul = scale != nullptr ? __ldg(scale) : 1.f;
 	for(int h = blockIdx.x * warpsPerBlock + (threadIdx.x >> 5); h < height; h += gridDim.x * warpsPerBlock) {
 		const float* row = x + static_cast<size_t>(h) * width;
+		const float* biasRow = bias != nullptr ? bias + static_cast<size_t>(h % biasRows) * width : nullptr;
 		float v[PER_LANE];
 		float mx = -FLT_MAX;
 #pragma unroll
 		for(int i = 0; i < PER_LANE; ++i) {
 			const int w = lane + 32 * i;
-			v[i] = w < width ? row[w] : -FLT_MAX;
+			v[i] = -FLT_MAX;
+			if(w < width) {
+				v[i] = row[w];
+				if(scale != nullptr) v[i] = __fmul_rn(v[i], mul);
+				if(biasRow != nullptr) v[i] = __fadd_rn(v[i], __ldg(biasRow + w));
+			}
 			mx = fmaxf(mx, v[i]);
 		}
 		mx = warp_max(mx);
@@ -455,7 +465,8 @@ int nb200_sum_matrix_columns(void* stream, float* y, const float* x, int height,
 	return check_launch();
 }
 
-int nb200_matrix_softmax_by_rows(void* stream, const float* x, int height, int width, float* y)
+int nb200_matrix_softmax_by_rows_fused(void* stream, const float* x, int height, int width, const float* scale_device,
+	const float* row_bias, int bias_rows, float* y)
 {
 	if(height < 0 || width < 0) return NB200_EINVAL;
 	if(height == 0 || width == 0) return NB200_OK;
@@ -463,15 +474,22 @@ int nb200_matrix_softmax_by_rows(void* stream, const float* x, int height, int w
 	NB200_REQUIRE_DEVICE();
 	cudaStream_t s = as_stream(stream);
 	const int grid = grid_for(height, 8, 16);
-	if(width <= 32) softmax_rows_reg_kernel<1><<<grid, 256, 0, s>>>(x, y, height, width);
-	else if(width <= 64) softmax_rows_reg_kernel<2><<<grid, 256, 0, s>>>(x, y, height, width);
-	else if(width <= 128) softmax_rows_reg_kernel<4><<<grid, 256, 0, s>>>(x, y, height, width);
-	else if(width <= 256) softmax_rows_reg_kernel<8><<<grid, 256, 0, s>>>(x, y, height, width);
-	else if(width <= 512) softmax_rows_reg_kernel<16><<<grid, 256, 0, s>>>(x, y, height, width);
-	else if(width <= 1024) softmax_rows_reg_kernel<32><<<grid, 256, 0, s>>>(x, y, height, width);
+	if((scale_device != nullptr || row_bias != nullptr) && width > 1024) return NB200_ETOOBIG; // prologue: register kernel only
+	if(row_bias != nullptr && bias_rows <= 0) return NB200_EINVAL;
+	if(width <= 32) softmax_rows_reg_kernel<1><<<grid, 256, 0, s>>>(x, y, height, width, scale_device, row_bias, bias_rows);
+	else if(width <= 64) softmax_rows_reg_kernel<2><<<grid, 256, 0, s>>>(x, y, height, width, scale_device, row_bias, bias_rows);
+	else if(width <= 128) softmax_rows_reg_kernel<4><<<grid, 256, 0, s>>>(x, y, height, width, scale_device, row_bias, bias_rows);
+	else if(width <= 256) softmax_rows_reg_kernel<8><<<grid, 256, 0, s>>>(x, y, height, width, scale_device, row_bias, bias_rows);
+	else if(width <= 512) softmax_rows_reg_kernel<16><<<grid, 256, 0, s>>>(x, y, height, width, scale_device, row_bias, bias_rows);
+	else if(width <= 1024) softmax_rows_reg_kernel<32><<<grid, 256, 0, s>>>(x, y, height, width, scale_device, row_bias, bias_rows);
 	else softmax_rows_wide_kernel<<<grid_for(height, 1, 16), 256, 0, s>>>(x, y, height, width);
 	count_launch();
 	return check_launch();
+}
+
+int nb200_matrix_softmax_by_rows(void* stream, const float* x, int height, int width, float* y)
+{
+	return nb200_matrix_softmax_by_rows_fused(stream, x, height, width, nullptr, nullptr, 0, y);
 }
 
 int nb200_transpose_matrix(void* stream, int batch, const void* x, int height, int medium, int width, int channels,

@@ -109,6 +109,23 @@ void CB200MathEngine::enter() const
 {
 	cudaSetDevice( device );
 	flushPending();
+	flushRowOps();
+}
+
+void CB200MathEngine::flushRowOps() const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( !pendingRows.active ) return;
+	const CPendingRowOps p = pendingRows;
+	pendingRows = CPendingRowOps();
+	if( p.scale != nullptr ) {
+		check( nb200_vector_op( stream, NB200_VEC_MULTIPLY, p.data, nullptr, p.scale, 0.f, p.data, static_cast<int>( p.size ) ),
+			"VectorMultiply" );
+	}
+	if( p.bias != nullptr ) {
+		check( nb200_add_vector_to_matrix_rows( stream, 1, p.data, p.data, p.biasHeight, p.biasWidth, p.bias ),
+			"AddVectorToMatrixRows" );
+	}
 }
 
 void CB200MathEngine::flushPending() const

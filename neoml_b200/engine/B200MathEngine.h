@@ -130,6 +130,19 @@ private:
 		long long resultFloats = 0;
 	};
 	mutable CPendingConvolution pending;
+	// The same idea for the score path of attention (and FC bias -> softmax): an in-place VectorMultiply by a device
+	// scalar and / or an in-place AddVectorToMatrixRows( batch 1 ) are held back; an in-place MatrixSoftmaxByRows of the
+	// same buffer then runs as ONE pass (scale, mask, softmax), anything else launches them as they were called.
+	struct CPendingRowOps {
+		bool active = false;
+		float* data = nullptr;
+		long long size = 0;
+		const float* scale = nullptr;   // device scalar of the held-back VectorMultiply
+		const float* bias = nullptr;    // vector of the held-back AddVectorToMatrixRows
+		int biasHeight = 0, biasWidth = 0;
+	};
+	mutable CPendingRowOps pendingRows;
+	void flushRowOps() const;
 	mutable std::recursive_mutex pendingMutex;
 
 	const int device;

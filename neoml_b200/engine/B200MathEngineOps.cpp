@@ -107,6 +107,17 @@ void CB200MathEngine::VectorMultiplyAndAdd( const CConstFloatHandle& firstHandle
 void CB200MathEngine::VectorMultiply( const CConstFloatHandle& firstHandle, const CFloatHandle& resultHandle, int vectorSize,
 	const CConstFloatHandle& multiplierHandle )
 {
+	if( raw( firstHandle ) == raw( resultHandle ) && vectorSize > 0 ) {
+		// in place: held back, a softmax over the same buffer may absorb it (see CPendingRowOps)
+		enter();
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		pendingRows = CPendingRowOps();
+		pendingRows.data = raw( resultHandle );
+		pendingRows.size = vectorSize;
+		pendingRows.scale = raw( multiplierHandle );
+		pendingRows.active = true;
+		return;
+	}
 	vectorOp( NB200_VEC_MULTIPLY, raw( firstHandle ), nullptr, raw( multiplierHandle ), 0.f, raw( resultHandle ), vectorSize, "VectorMultiply" );
 }
 
@@ -154,6 +165,23 @@ void CB200MathEngine::VectorTanh( const CConstFloatHandle& firstHandle, const CF
 void CB200MathEngine::AddVectorToMatrixRows( int batchSize, const CConstFloatHandle& matrixHandle, const CFloatHandle& resultHandle,
 	int matrixHeight, int matrixWidth, const CConstFloatHandle& vectorHandle )
 {
+	const long long size = static_cast<long long>( matrixHeight ) * matrixWidth;
+	if( batchSize == 1 && raw( matrixHandle ) == raw( resultHandle ) && size > 0 ) {
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		if( pendingRows.active && pendingRows.data == raw( resultHandle ) && pendingRows.size == size && pendingRows.bias == nullptr ) {
+			// joins a held-back VectorMultiply of the same buffer
+		} else {
+			enter();
+			pendingRows = CPendingRowOps();
+			pendingRows.data = raw( resultHandle );
+			pendingRows.size = size;
+			pendingRows.active = true;
+		}
+		pendingRows.bias = raw( vectorHandle );
+		pendingRows.biasHeight = matrixHeight;
+		pendingRows.biasWidth = matrixWidth;
+		return;
+	}
 	enter();
 	check( nb200_add_vector_to_matrix_rows( stream, batchSize, raw( matrixHandle ), raw( resultHandle ), matrixHeight, matrixWidth,
 		raw( vectorHandle ) ), "AddVectorToMatrixRows" );
@@ -190,6 +218,19 @@ void CB200MathEngine::SumMatrixColumns( const CFloatHandle& resultHandle, const 
 
 void CB200MathEngine::MatrixSoftmaxByRows( const CConstFloatHandle& matrix, int height, int width, const CFloatHandle& result )
 {
+	{
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const CPendingRowOps p = pendingRows;
+		if( p.active && p.data == raw( result ) && raw( matrix ) == raw( result ) && width > 0 && width <= 1024
+			&& p.size == static_cast<long long>( height ) * width && ( p.bias == nullptr || p.biasWidth % width == 0 ) ) {
+			// scale, mask and softmax in one pass over the scores
+			pendingRows = CPendingRowOps();
+			enter();
+			check( nb200_matrix_softmax_by_rows_fused( stream, p.data, height, width, p.scale, p.bias,
+				p.bias != nullptr ? p.biasWidth / width : 0, p.data ), "MatrixSoftmaxByRows" );
+			return;
+		}
+	}
 	enter();
 	check( nb200_matrix_softmax_by_rows( stream, raw( matrix ), height, width, raw( result ) ), "MatrixSoftmaxByRows" );
 }

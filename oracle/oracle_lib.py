@@ -272,8 +272,8 @@ class Reference:
         self._chk(self.lib.ref_vector_op(self.engine, op, _opt(a), _opt(b), _opt(sc), _f(scalar), _opt(y), n))
         return y
 
-    def add_vector_to_matrix_rows(self, batch, x, height, width, v):
-        y = self._zeros(x.shape)
+    def add_vector_to_matrix_rows(self, batch, x, height, width, v, out=None):
+        y = self._zeros(x.shape) if out is None else out
         self._chk(self.lib.ref_add_vector_to_matrix_rows(self.engine, batch, _opt(x), _opt(y), height, width, _opt(v)))
         return y
 
@@ -303,8 +303,8 @@ class Reference:
                                                               diag_stride, _opt(y)))
         return y
 
-    def matrix_softmax_by_rows(self, x, height, width):
-        y = self._zeros(x.shape)
+    def matrix_softmax_by_rows(self, x, height, width, out=None):
+        y = self._zeros(x.shape) if out is None else out
         self._chk(self.lib.ref_matrix_softmax_by_rows(self.engine, _opt(x), height, width, _opt(y)))
         return y
 

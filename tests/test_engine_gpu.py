@@ -192,3 +192,39 @@ def test_gpu_manager_lists_the_device_and_creates_engines(engine):
         assert lib.nb200_manager_probe(manager, count, None, None, None, 0) == count     # out of range: nothing happens
     finally:
         lib.nb200_destroy_math_engine_manager(manager)
+
+
+def test_in_place_scale_and_mask_ride_in_the_softmax(engine, oracle):
+    """The score path of attention as CMultiheadAttentionLayer issues it, in place: VectorMultiply by a device scalar,
+    AddVectorToMatrixRows of the mask, MatrixSoftmaxByRows.  The engine runs the three as one pass; the result is
+    bit for bit that of the separate calls, which the oracle confirms to tolerance."""
+    from neoml_b200 import _capi
+    lib = _capi.load()
+    heads, seq = 6, 48
+    scores = cases.uniform(81, (heads * seq * seq,), -4, 4)
+    mask = (np.triu(np.ones((seq, seq), np.float32), k=1) * -1e9).reshape(-1)
+    want = oracle.matrix_softmax_by_rows(
+        oracle.add_vector_to_matrix_rows(1, oracle.vector_op(6, scores, None, 0.125), heads, seq * seq, mask), heads * seq, seq)
+
+    def run(fused: bool):
+        x, m = dev(scores), dev(mask)
+        engine.sync()
+        before = lib.nb200_launch_count()
+        engine.vector_op(6, x, None, 0.125, out=x)
+        if not fused:
+            engine.sync()
+        engine.add_vector_to_matrix_rows(1, x, heads, seq * seq, m, out=x)
+        if not fused:
+            engine.sync()
+        engine.matrix_softmax_by_rows(x, heads * seq, seq, out=x)
+        return host(engine, x), lib.nb200_launch_count() - before
+
+    fused, fused_launches = run(True)
+    plain, plain_launches = run(False)
+    assert np.array_equal(fused, plain)
+    assert gate_err(fused, want) < 1e-5
+    assert (fused_launches, plain_launches) == (1, 3)
+    # a held-back multiply that nothing absorbs is simply launched by the next call
+    y = dev(scores)
+    engine.vector_op(6, y, None, 0.5, out=y)
+    assert np.array_equal(host(engine, y), scores * np.float32(0.5))
