@@ -376,6 +376,7 @@ def run_ours(args):
         "algorithmic_gflop_per_step": round(flops / 1e9, 2),
         "effective_peak_for_this_arithmetic": round(eff_peak, 1),
         "frac_of_effective_peak": round(achieved_tf / eff_peak, 4),
+        "frac_ceiling_for_this_arithmetic": round(eff_peak / peak_tf, 4),
         "note": "peak is dense bf16; TF32 = 1/2 of it, 3xTF32 = 1/6 (algorithmic flops counted once)",
     }
 
