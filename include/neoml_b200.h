@@ -149,7 +149,8 @@ NB200_API int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* desc,
 
 /* ---- memory-bound vector / matrix ops ---------------------------------------------------------------------- */
 /* Elementwise family (IVectorMathEngine, NME.h:69-384).  `op` selects the method; operands unused by an op
- * are NULL.  Scalars that NeoML keeps on the device arrive as device pointers (`scalar`), true scalars in `value`. */
+ * are NULL.  Scalars that NeoML keeps on the device arrive as device pointers (`scalar`); with scalar == NULL the ops
+ * marked *scalar use `value` instead (true scalars: `value`). */
 enum {
 	NB200_VEC_COPY = 0,          /* VectorCopy           y = a                         NME.h:73  */
 	NB200_VEC_FILL = 1,          /* VectorFill(value)    y = value                     NME.h:86  */

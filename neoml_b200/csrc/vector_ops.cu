@@ -115,10 +115,11 @@ int nb200_vector_op(void* stream, int op, const float* a, const float* b, const 
 	if(y == nullptr) return NB200_EINVAL;
 	if(device_status_word() == nullptr) return NB200_ENODEVICE;
 	cudaStream_t s = as_stream(stream);
-	const bool needsScalarPtr = op == NB200_VEC_FILL_HANDLE || op == NB200_VEC_MULTIPLY || op == NB200_VEC_NEG_MULTIPLY
+	// ops whose scalar NeoML keeps in device memory take it from `scalar`; with scalar == NULL they use `value`
+	const bool takesScalar = op == NB200_VEC_FILL_HANDLE || op == NB200_VEC_MULTIPLY || op == NB200_VEC_NEG_MULTIPLY
 		|| op == NB200_VEC_ADD_VALUE || op == NB200_VEC_RELU || op == NB200_VEC_MUL_ADD;
-	if(needsScalarPtr && scalar == nullptr) return NB200_EINVAL;
-	if(!needsScalarPtr) scalar = nullptr;
+	if(op == NB200_VEC_FILL_HANDLE && scalar == nullptr) return NB200_EINVAL;
+	if(!takesScalar) scalar = nullptr;
 	switch(op) {
 #define NB200_CASE(OP) case OP: return launch_vec<OP>(s, a, b, scalar, value, y, count);
 		NB200_CASE(NB200_VEC_COPY)

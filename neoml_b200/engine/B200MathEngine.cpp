@@ -112,6 +112,19 @@ void CB200MathEngine::enter() const
 	flushRowOps();
 }
 
+float* CB200MathEngine::WorkAlloc( size_t floats ) const
+{
+	if( floats == 0 ) return nullptr;
+	float* p = static_cast<float*>( memory.Alloc( floats * sizeof( float ) ) );
+	if( p == nullptr ) GetMathEngineExceptionHandler()->OnMemoryError();
+	return p;
+}
+
+void CB200MathEngine::WorkFree( float* ptr ) const
+{
+	if( ptr != nullptr ) memory.Free( ptr );
+}
+
 void CB200MathEngine::flushRowOps() const
 {
 	std::lock_guard<std::recursive_mutex> lock( pendingMutex );

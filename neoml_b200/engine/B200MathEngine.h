@@ -83,6 +83,13 @@ public:
 	// precision selected by the factory flags: 3xTF32 unless GpuMathEngineCublasUseTensorCoresTF32Flag is given
 	int Precision() const { return precision; }
 	void* Stream() const { return stream; }
+	// for the operation objects of B200Rowwise.cpp: work memory from the block pool (stream-ordered reuse), result
+	// check, entry bookkeeping
+	float* WorkAlloc( size_t floats ) const;
+	void WorkFree( float* ptr ) const;
+	void Check( int code, const char* method ) const { check( code, method ); }
+	void Enter() const { enter(); }
+	template<class T> T* Raw( const CTypedMemoryHandle<T>& h ) const { return raw( h ); }
 
 	// non-pure virtuals of the interface
 	CMathEngineDistributedInfo GetDistributedInfo() override { return distributedInfo; }

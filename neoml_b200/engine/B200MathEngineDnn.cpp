@@ -1,5 +1,5 @@
 // CB200MathEngine: the IDnnEngine methods of the inference hot path (convolution, channelwise convolution, pooling,
-// image resize, the fused MobileNetV2 block and the rowwise descriptors it needs).
+// image resize).  The rowwise operations live in B200Rowwise.cpp.
 #include "B200MathEngine.h"
 
 #include <neoml_b200.h>
@@ -41,21 +41,6 @@ struct CB200MaxPoolingDesc : public CMaxPoolingDesc {
 struct CB200MeanPoolingDesc : public CMeanPoolingDesc {
 	CB200PoolingGeometry g;
 };
-// The rowwise MobileNetV2 descriptor captures the weight pointers, as the reference's does
-// (GPU/CUDA/Rowwise/CudaRowwiseMobileNetV2.h:94-108)
-struct CB200RowwiseMobileNetV2 : public CRowwiseOperationDesc {
-	int inputChannels, expandedChannels, outputChannels, stride;
-	bool residual;
-	int actExpand, actChannelwise;
-	float actExpandParam, actChannelwiseParam;
-	const float* expandFilter;
-	const float* expandFreeTerm;
-	const float* channelwiseFilter;
-	const float* channelwiseFreeTerm;
-	const float* downFilter;
-	const float* downFreeTerm;
-};
-
 // A blob as a channels-last image batch: objects x height x width x (depth * channels)
 CB200PoolingGeometry imageOf( const CBlobDesc& b )
 {
@@ -161,76 +146,6 @@ void CB200MathEngine::BlobResizeImage( const CBlobDesc& from, const CFloatHandle
 	check( nb200_blob_resize_image( stream, from.ObjectCount(), from.Height(), from.Width(), from.Depth() * from.Channels(),
 		deltaLeft, deltaRight, deltaTop, deltaBottom, static_cast<int>( padding ), defaultValue, raw( fromData ), raw( toData ) ),
 		"BlobResizeImage" );
-}
-
-//---------------------------------------------------------------------------------------------------------------------
-// fused MobileNetV2 block and the rowwise plumbing CMobileNetV2BlockLayer::Reshape calls
-// (NeoML/src/Dnn/Layers/MobileNetV2BlockLayer.cpp:218-251)
-
-CRowwiseOperationDesc* CB200MathEngine::InitRowwiseMobileNetV2( int inputChannels, const CConstFloatHandle& expandFilter,
-	const CConstFloatHandle* expandFreeTerm, int expandedChannels, TActivationFunction expandActivation, float expandReluParam,
-	const CConstFloatHandle& channelwiseFilter, const CConstFloatHandle* channelwiseFreeTerm, int stride,
-	TActivationFunction channelwiseActivation, float channelwiseReluParam, const CConstFloatHandle& downFilter,
-	const CConstFloatHandle* downFreeTerm, int outputChannels, bool residual )
-{
-	int a1 = 0, a2 = 0;
-	if( !activationOf( expandActivation, a1 ) || !activationOf( channelwiseActivation, a2 ) ) {
-		notImplemented( "InitRowwiseMobileNetV2 (activation other than linear / ReLU / HSwish)" );
-		return nullptr;
-	}
-	CB200RowwiseMobileNetV2* desc = new CB200RowwiseMobileNetV2();
-	desc->inputChannels = inputChannels; desc->expandedChannels = expandedChannels; desc->outputChannels = outputChannels;
-	desc->stride = stride; desc->residual = residual;
-	desc->actExpand = a1; desc->actChannelwise = a2;
-	desc->actExpandParam = expandReluParam; desc->actChannelwiseParam = channelwiseReluParam;
-	desc->expandFilter = raw( expandFilter );
-	desc->expandFreeTerm = expandFreeTerm != nullptr ? raw( *expandFreeTerm ) : nullptr;
-	desc->channelwiseFilter = raw( channelwiseFilter );
-	desc->channelwiseFreeTerm = channelwiseFreeTerm != nullptr ? raw( *channelwiseFreeTerm ) : nullptr;
-	desc->downFilter = raw( downFilter );
-	desc->downFreeTerm = downFreeTerm != nullptr ? raw( *downFreeTerm ) : nullptr;
-	return desc;
-}
-
-CBlobDesc CB200MathEngine::RowwiseReshape( CRowwiseOperationDesc** operations, int operationCount, const CBlobDesc& input )
-{
-	CBlobDesc output = input;
-	for( int i = 0; i < operationCount; ++i ) {
-		const CB200RowwiseMobileNetV2* op = dynamic_cast<const CB200RowwiseMobileNetV2*>( operations[i] );
-		if( op == nullptr ) { notImplemented( "RowwiseReshape (operation other than MobileNetV2)" ); return output; }
-		output.SetDimSize( BD_Height, 1 + ( output.Height() - 1 ) / op->stride );
-		output.SetDimSize( BD_Width, 1 + ( output.Width() - 1 ) / op->stride );
-		output.SetDimSize( BD_Channels, op->outputChannels );
-	}
-	return output;
-}
-
-void CB200MathEngine::MobileNetV2Block( const CBlobDesc& inputDesc, const CBlobDesc&, const CRowwiseOperationDesc& rowwiseDesc,
-	const CChannelwiseConvolutionDesc&, const CConstFloatHandle& inputHandle, const CFloatHandle& outputHandle )
-{
-	const CB200RowwiseMobileNetV2* op = dynamic_cast<const CB200RowwiseMobileNetV2*>( &rowwiseDesc );
-	if( op == nullptr ) { raise( "MobileNetV2Block: the rowwise descriptor was not created by this engine" ); return; }
-	nb200_mbv2_desc d = { inputDesc.ObjectCount(), inputDesc.Height(), inputDesc.Width(), op->inputChannels,
-		op->expandedChannels, op->outputChannels, op->stride, op->residual ? 1 : 0, op->actExpand, op->actChannelwise,
-		op->actExpandParam, op->actChannelwiseParam };
-	enter();
-	const size_t scratchFloats = nb200_mobilenetv2_scratch_floats( &d );
-	CMemoryHandle scratch = StackAlloc( scratchFloats * sizeof( float ) );
-	const int rc = nb200_mobilenetv2_block( stream, &d, raw( inputHandle ), op->expandFilter, op->expandFreeTerm,
-		op->channelwiseFilter, op->channelwiseFreeTerm, op->downFilter, op->downFreeTerm, raw( outputHandle ),
-		static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) ), precision );
-	StackFree( scratch );
-	check( rc, "MobileNetV2Block" );
-}
-
-void CB200MathEngine::RowwiseExecute( const CBlobDesc& inputDesc, CRowwiseOperationDesc** operations, int operationCount,
-	const CFloatHandle& input, const CFloatHandle& output )
-{
-	if( operationCount != 1 ) { notImplemented( "RowwiseExecute (chains longer than one MobileNetV2 block)" ); return; }
-	const CB200RowwiseMobileNetV2* op = dynamic_cast<const CB200RowwiseMobileNetV2*>( operations[0] );
-	if( op == nullptr ) { notImplemented( "RowwiseExecute (operation other than MobileNetV2)" ); return; }
-	CB200ChannelwiseDesc unused;
-	MobileNetV2Block( inputDesc, inputDesc, *op, unused, input, output );
 }
 
 } // namespace NeoML

@@ -347,6 +347,19 @@ class Reference:
                                                  _opt(x), _opt(y)))
         return y
 
+    def rowwise_chain(self, x, conv_f, conv_b, w_exp, b_exp, w_dw, b_dw, w_down, b_down, ch_f, ch_b, ch1_f, ch1_b, c1_f,
+                      c1_b):
+        """The eight-operation rowwise chain of ref_shim.cpp::ref_rowwise_chain on this engine; returns the result."""
+        n, h, w, c = x.shape
+        k, cexp, kout = conv_f.shape[0], w_exp.shape[0], c1_f.shape[0]
+        dims = (C.c_int * 4)()
+        args = [_opt(a) for a in (x, conv_f, conv_b, w_exp, b_exp, w_dw, b_dw, w_down, b_down, ch_f, ch_b, ch1_f, ch1_b,
+                                  c1_f, c1_b)]
+        self._chk(self.lib.ref_rowwise_chain(self.engine, n, h, w, c, k, cexp, kout, *args, None, dims))
+        y = self._zeros(tuple(dims), np.float32)
+        self._chk(self.lib.ref_rowwise_chain(self.engine, n, h, w, c, k, cexp, kout, *args, _opt(y), dims))
+        return y
+
     # ---- engine-level calls (memory, exchange, identity), the same for any IMathEngine behind the shim
     def roundtrip(self, x: np.ndarray):
         """Engine-owned memory + typed exchange + stack variables: returns (2*x+1 computed on the engine, gauges) with

@@ -353,4 +353,41 @@ int ref_engine_training_method_raises( void* eng, float* x, int n )
 	return 0;
 }
 
+// A chain of rowwise operations as NeoML's optimizer builds them (NeoMathEngine.h:1084-1110):
+// resize(+1 on every side, zeros) -> max pool 3x3/2 -> conv 3x3 pad 1 (c -> k) -> ReLU(6) -> MobileNetV2 block
+// (k -> cexp -> k, stride 1, residual, ReLU6 twice) -> channelwise 3x3 pad 1 -> HSwish -> channelwise 3x3/2 + ReLU +
+// 1x1 conv (k -> kout).  outDims receives {objects, height, width, channels} of the result; y must hold it.
+int ref_rowwise_chain( void* eng, int batch, int h, int w, int c, int k, int cexp, int kout, const float* x,
+	const float* convF, const float* convB, const float* wExp, const float* bExp, const float* wDw, const float* bDw,
+	const float* wDown, const float* bDown, const float* chF, const float* chB, const float* ch1F, const float* ch1B,
+	const float* c1F, const float* c1B, float* y, int* outDims )
+{
+	SHIM_TRY
+	IMathEngine* e = static_cast<IMathEngine*>( eng );
+	CBlobDesc input = image_desc( batch, h, w, c );
+	CBlobDesc convFilter( CT_Float );
+	convFilter.SetDimSize( BD_BatchWidth, k ); convFilter.SetDimSize( BD_Height, 3 ); convFilter.SetDimSize( BD_Width, 3 );
+	convFilter.SetDimSize( BD_Channels, c );
+	CBlobDesc chFilter( CT_Float );
+	chFilter.SetDimSize( BD_Height, 3 ); chFilter.SetDimSize( BD_Width, 3 ); chFilter.SetDimSize( BD_Channels, k );
+	CConstFloatHandle hConvB = cfh( e, convB ), hBExp = cfh( e, bExp ), hBDw = cfh( e, bDw ), hBDown = cfh( e, bDown ),
+		hChB = cfh( e, chB ), hCh1B = cfh( e, ch1B ), hC1B = cfh( e, c1B );
+	std::unique_ptr<CRowwiseOperationDesc> ops[8];
+	ops[0].reset( e->InitRowwiseResizeImage( TBlobResizePadding::Constant, 0.f, 1, 1, 1, 1 ) );
+	ops[1].reset( e->InitRowwise2DPooling( true, 3, 3, 2, 2 ) );
+	ops[2].reset( e->InitRowwiseConv( 1, 1, 1, 1, 1, 1, convFilter, cfh( e, convF ), &hConvB ) );
+	ops[3].reset( e->InitRowwiseActivation( CActivationDesc( AF_ReLU, CReLUActivationParam{ 6.f } ) ) );
+	ops[4].reset( e->InitRowwiseMobileNetV2( k, cfh( e, wExp ), &hBExp, cexp, AF_ReLU, 6.f, cfh( e, wDw ), &hBDw, 1, AF_ReLU, 6.f,
+		cfh( e, wDown ), &hBDown, k, true ) );
+	ops[5].reset( e->InitRowwiseChConv( 1, 1, 1, 1, chFilter, cfh( e, chF ), &hChB ) );
+	ops[6].reset( e->InitRowwiseActivation( CActivationDesc( AF_HSwish ) ) );
+	ops[7].reset( e->InitRowwiseChWith1x1( 2, cfh( e, ch1F ), &hCh1B, AF_ReLU, 0.f, cfh( e, c1F ), &hC1B, kout, false ) );
+	CRowwiseOperationDesc* raw[8];
+	for( int i = 0; i < 8; ++i ) raw[i] = ops[i].get();
+	const CBlobDesc out = e->RowwiseReshape( raw, 8, input );
+	outDims[0] = out.ObjectCount(); outDims[1] = out.Height(); outDims[2] = out.Width(); outDims[3] = out.Channels();
+	if( y != nullptr ) e->RowwiseExecute( input, raw, 8, fh( e, const_cast<float*>( x ) ), fh( e, y ) );
+	SHIM_CATCH
+}
+
 } // extern "C"

@@ -228,3 +228,31 @@ def test_in_place_scale_and_mask_ride_in_the_softmax(engine, oracle):
     y = dev(scores)
     engine.vector_op(6, y, None, 0.5, out=y)
     assert np.array_equal(host(engine, y), scores * np.float32(0.5))
+
+
+def _rowwise_chain_inputs():
+    n, h, w, c, k, cexp, kout = 2, 21, 18, 8, 16, 48, 24
+    he = lambda seed, shape, fan: cases.normal(seed, shape, float(np.sqrt(2.0 / fan)))
+    bias = lambda seed, m: cases.uniform(seed, (m,), -0.1, 0.1)
+    return (cases.uniform(91, (n, h, w, c), 0, 1), he(92, (k, 3, 3, c), 9 * c), bias(93, k), he(94, (cexp, k), k), bias(95, cexp),
+            he(96, (3, 3, cexp), 9), bias(97, cexp), he(98, (k, cexp), cexp), bias(99, k), he(100, (3, 3, k), 9), bias(101, k),
+            he(102, (3, 3, k), 9), bias(103, k), he(104, (kout, k), k), bias(105, kout))
+
+
+def test_rowwise_chain_matches_the_reference_cpu_engine(engine, reference):
+    """A chain of eight rowwise operations (resize, pooling, conv + ReLU, MobileNetV2 block, channelwise conv + HSwish,
+    channelwise-with-1x1) as the optimizer of NeoML emits them, on both engines through the same IMathEngine calls."""
+    from neoml_b200 import _capi
+    args = _rowwise_chain_inputs()
+    want = reference.rowwise_chain(*args)
+    held = [dev(a) for a in args]
+    engine.sync()
+    before = _capi.load().nb200_launch_count()
+    got = engine.rowwise_chain(*held)
+    result = host(engine, got)
+    launches = _capi.load().nb200_launch_count() - before
+    assert result.shape == want.shape == (2, 6, 5, 24)
+    assert gate_err(result, want) < TOL_FP32
+    # resize 1, pool 1, few-channel conv 4 (image padding, filter widening, filter preparation, contraction; ReLU folded
+    # in), block 3, channelwise 1 (HSwish folded in), channelwise + 1x1 2: the two activations launch nothing
+    assert launches == 12

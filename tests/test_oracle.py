@@ -106,3 +106,10 @@ def test_reference_engine_roundtrip_through_the_shim(reference):
     assert np.array_equal(y, 2 * x + 1)
     assert current >= 4 * x.size and peak >= current and pooled_after_cleanup == 0
     assert reference.info()[0] == 1      # MET_Cpu
+
+
+def test_reference_engine_runs_the_rowwise_chain(reference):
+    """The rowwise-chain driver of the shim on the reference CPU engine: shape and sanity of what the GPU test compares with."""
+    import test_engine_gpu
+    y = reference.rowwise_chain(*test_engine_gpu._rowwise_chain_inputs())
+    assert y.shape == (2, 6, 5, 24) and np.isfinite(y).all() and float(np.abs(y).max()) > 0
