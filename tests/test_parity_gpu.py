@@ -359,3 +359,60 @@ def test_vectorised_helper_variants(ops, oracle):
     for shape in [(2, 23, 31, 8), (1, 7, 9, 64), (3, 3, 3, 4)]:          # odd sizes: partial strips at the right edge
         x = cases.uniform(74, shape)
         assert np.array_equal(host(ops.BlobMaxPooling(dev(x), (3, 3), (2, 2))), oracle.blob_max_pooling(x, (3, 3), (2, 2))[0])
+
+
+def test_blob_convolution_random_shapes(ops, oracle):
+    """Sixty seeded random geometries against the plain-C oracle: channel counts on both sides of every path switch
+    (row windows below 32 channels, im2col boxes at multiples of 32, gathers elsewhere), filters up to 5x5, strides,
+    dilations and paddings up to the filter size, with and without free term, ReLU and residual."""
+    rng = np.random.default_rng(20240607)
+    channel_pool = [1, 2, 3, 4, 5, 8, 12, 16, 24, 31, 32, 33, 48, 64, 96]
+    worst = 0.0
+    for case in range(60):
+        c = int(rng.choice(channel_pool))
+        k = int(rng.choice([1, 3, 8, 16, 31, 32, 64, 72, 130]))
+        r, s = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+        dil = (int(rng.integers(1, 3)), int(rng.integers(1, 3)))
+        stride = (int(rng.integers(1, 4)), int(rng.integers(1, 4)))
+        pad = (int(rng.integers(0, r)), int(rng.integers(0, s)))          # below the filter size: see cases.py on the reference
+        h = int(rng.integers((r - 1) * dil[0] + 1, (r - 1) * dil[0] + 14))
+        w = int(rng.integers((s - 1) * dil[1] + 1, (s - 1) * dil[1] + 14))
+        n = int(rng.integers(1, 4))
+        x = rng.uniform(-1, 1, (n, h, w, c)).astype(np.float32)
+        f = rng.uniform(-1, 1, (k, r, s, c)).astype(np.float32)
+        b = rng.uniform(-1, 1, (k,)).astype(np.float32) if rng.random() < 0.7 else None
+        want = oracle.blob_convolution(x, f, b, padding=pad, stride=stride, dilation=dil)
+        relu, with_res = bool(rng.random() < 0.5), bool(rng.random() < 0.4)
+        res = rng.uniform(-1, 1, want.shape).astype(np.float32) if with_res else None
+        if with_res:
+            want = want + res
+        if relu:
+            want = np.maximum(want, 0.0)
+        got = host(ops.BlobConvolution(dev(x), dev(f), dev(b), padding=pad, stride=stride, dilation=dil, residual=dev(res),
+                                       act=ops.ACT_RELU if relu else ops.ACT_NONE))
+        err = gate_err(got, want)
+        worst = max(worst, err)
+        assert got.shape == want.shape and err < TOL_FP32, \
+            f"case {case}: n={n} h={h} w={w} c={c} k={k} r={r} s={s} pad={pad} stride={stride} dil={dil} relu={relu} res={with_res}: {err:.3e}"
+    print(f"random convolutions: worst gate error {worst:.3e}")
+
+
+def test_matrix_products_random_shapes(ops, oracle):
+    """Forty seeded random products with row strides wider than the matrices, both orientations, batched."""
+    rng = np.random.default_rng(777)
+    for case in range(40):
+        m, k, n = int(rng.integers(1, 300)), int(rng.integers(1, 300)), int(rng.integers(1, 300))
+        lda, ldb = k + int(rng.integers(0, 9)), k + int(rng.integers(0, 9))
+        a = rng.uniform(-1, 1, (m, lda)).astype(np.float32)
+        b = rng.uniform(-1, 1, (n, ldb)).astype(np.float32)
+        want = oracle.multiply_matrix_by_transposed_matrix(a, b, m=m, k=k, n=n, lda=lda, ldb=ldb)
+        got = host(ops.MultiplyMatrixByTransposedMatrix(dev(a), dev(b), first_height=m, first_width=k, second_height=n,
+                                                        first_row_size=lda, second_row_size=ldb))
+        assert gate_err(got, want) < TOL_FP32, f"mmt case {case}: m={m} k={k} n={n} lda={lda} ldb={ldb}"
+        batch = int(rng.integers(1, 4))
+        a3 = rng.uniform(-1, 1, (batch, m, k)).astype(np.float32)
+        b3 = rng.uniform(-1, 1, (batch, k, n)).astype(np.float32)
+        want3 = oracle.multiply_matrix_by_matrix(a3, b3)
+        for scratch in (True, False):
+            got3 = host(ops.MultiplyMatrixByMatrix(dev(a3), dev(b3), use_scratch=scratch))
+            assert gate_err(got3, want3) < TOL_FP32, f"mm case {case}: batch={batch} m={m} k={k} n={n} scratch={scratch}"
