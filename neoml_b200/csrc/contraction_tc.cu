@@ -34,6 +34,8 @@
 #include "contraction.cuh"
 #include <cuda.h>
 #include <string.h>
+#include <atomic>
+#include <mutex>
 
 namespace nb200 {
 
@@ -751,24 +753,26 @@ typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 EncodeTiledFn g_encodeTiled = nullptr;
 EncodeIm2colFn g_encodeIm2col = nullptr;
-bool g_encodeLooked = false;
+std::once_flag g_encodeOnce;
 
+// Several engines may make their first call at the same moment from different host threads (one thread per replica):
+// the lookup runs once, and everybody sees its result.
 void lookup_encoders()
 {
-	if(g_encodeLooked) return;
-	g_encodeLooked = true;
-	void* fn = nullptr;
-	cudaDriverEntryPointQueryResult q;
-	if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess
-		&& q == cudaDriverEntryPointSuccess) {
-		g_encodeTiled = reinterpret_cast<EncodeTiledFn>(fn);
-	}
-	fn = nullptr;
-	if(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) == cudaSuccess
-		&& q == cudaDriverEntryPointSuccess) {
-		g_encodeIm2col = reinterpret_cast<EncodeIm2colFn>(fn);
-	}
-	cudaGetLastError();
+	std::call_once(g_encodeOnce, [] {
+		void* fn = nullptr;
+		cudaDriverEntryPointQueryResult q;
+		if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess
+			&& q == cudaDriverEntryPointSuccess) {
+			g_encodeTiled = reinterpret_cast<EncodeTiledFn>(fn);
+		}
+		fn = nullptr;
+		if(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) == cudaSuccess
+			&& q == cudaDriverEntryPointSuccess) {
+			g_encodeIm2col = reinterpret_cast<EncodeIm2colFn>(fn);
+		}
+		cudaGetLastError();
+	});
 }
 
 // Row-addressed operand as a 3-D tensor (k fastest, then rows, then batch); box = 32 k x boxRows rows, 128-byte swizzle.
@@ -852,10 +856,10 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	if(rawSlots < 2) return NB200_ETOOBIG;
 	const size_t smemBytes = static_cast<size_t>(rawSlots) * slotBytes + fixedBytes;
 	// the attribute is per device; one engine per device may live in this process
-	static bool attrSet[64] = {};
+	static std::atomic<bool> attrSet[64];
 	int dev = 0;
 	if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NB200_ENODEVICE;
-	if(!attrSet[dev]) {
+	if(!attrSet[dev].load()) {
 		const int bytes = 227 * 1024;
 		const cudaFuncAttribute attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
 		if(cudaFuncSetAttribute(contraction_tc_kernel<BN, true, true>, attr, bytes) != cudaSuccess
@@ -865,7 +869,7 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 			cudaGetLastError();
 			return NB200_ENODEVICE;
 		}
-		attrSet[dev] = true;
+		attrSet[dev].store(true);
 	}
 	if(p.tileM <= 0 || p.tileM > BM || p.a_mode != A_CONV_WINDOW) p.tileM = BM;
 	const long long mTiles = (static_cast<long long>(p.M) + p.tileM - 1) / p.tileM;

@@ -256,3 +256,41 @@ def test_rowwise_chain_matches_the_reference_cpu_engine(engine, reference):
     # resize 1, pool 1, few-channel conv 4 (image padding, filter widening, filter preparation, contraction; ReLU folded
     # in), block 3, channelwise 1 (HSwish folded in), channelwise + 1x1 2: the two activations launch nothing
     assert launches == 12
+
+
+def test_two_engines_on_two_host_threads(golden):
+    """One engine per host thread, as NeoML's replica drivers run them: both issue convolutions and products at the
+    same time on their own streams; every result is still the golden one (no shared per-call state in the library)."""
+    import threading
+    if not ShimmedB200Engine.available():
+        pytest.skip("libNeoMathEngineB200.so or the shim not built")
+    engines = [ShimmedB200Engine(), ShimmedB200Engine()]
+    names = sorted(cases.CONV_CASES)
+    inputs = {n: cases.conv_inputs(n) for n in names}
+    held = {n: tuple(dev(a) for a in inputs[n][:3]) for n in names}
+    a, b, kw = cases.mmt_inputs("aligned")
+    da, db = dev(a), dev(b)
+    want = {n: np.array(golden[f"conv/{n}"]) for n in names}    # the archive reader is not for concurrent use
+    want_mmt = np.array(golden["mmt/aligned"])
+    failures = []
+
+    def worker(e, order):
+        try:
+            for _ in range(3):
+                for n in order:
+                    dx, df, dbias = held[n]
+                    y = e.blob_convolution(dx, df, dbias, **inputs[n][3])
+                    m = e.multiply_matrix_by_transposed_matrix(da, db, **kw)
+                    e.sync()
+                    if gate_err(y.cpu().numpy(), want[n]) >= TOL_FP32 or gate_err(m.cpu().numpy(), want_mmt) >= TOL_FP32:
+                        failures.append(n)
+        except Exception as exc:  # noqa: BLE001 - reported below
+            failures.append(repr(exc))
+
+    threads = [threading.Thread(target=worker, args=(engines[0], names)),
+               threading.Thread(target=worker, args=(engines[1], names[::-1]))]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    for e in engines:
+        e.close()
+    assert not failures, failures
