@@ -52,7 +52,10 @@ constexpr int MAX_EPI_WARPS = 8;
 constexpr int THREADS = (CVT_WARP0 + WORK_WARPS) * 32;
 constexpr int A_TILE_BYTES = BM * BK * 4; // 16 KB
 constexpr int STAGING_BYTES_PER_WARP = 32 * 64; // 32 rows x 16 floats
-constexpr int LO_SLOTS = 2;              // B-lo tiles in shared memory == A stages in tensor memory
+constexpr int MAX_LO_SLOTS = 4;
+// A stages in tensor memory (== B-lo tiles in shared memory when B is converted in the kernel): four where the
+// accumulators leave room for them, so that the converters can run further ahead of the tensor core
+__host__ __device__ constexpr int lo_slots_for(int bn) { return bn <= 64 ? 4 : 2; }
 constexpr int MAX_RAW_SLOTS = 8;
 
 enum {
@@ -132,6 +135,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	// MMAs of tile i + 1; for 3xTF32 the cross accumulators, two if they fit, else one that the epilogue folds into
 	// the main accumulator first thing (TMEM -> registers -> TMEM) and hands back at once; then two stages of the A
 	// operand (32 columns of hi [+ 32 of lo] per stage: row m of the tile in lane m, K index in the column).
+	constexpr int LO_SLOTS = lo_slots_for(BN);
 	constexpr uint32_t ACC_COLS = BN;
 	constexpr uint32_t A_STAGE_COLS = threeX ? 64 : 32;
 	constexpr int CROSS_SETS = !threeX ? 0 : (4 * ACC_COLS + LO_SLOTS * A_STAGE_COLS <= 512 ? 2 : 1);
@@ -152,7 +156,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	uint64_t* rawEmptyBar = rawFullBar + MAX_RAW_SLOTS;
 	uint64_t* cvtFullBar = rawEmptyBar + MAX_RAW_SLOTS;
 	uint64_t* loEmptyBar = cvtFullBar + MAX_RAW_SLOTS;
-	uint64_t* accFullBar = loEmptyBar + LO_SLOTS;
+	uint64_t* accFullBar = loEmptyBar + MAX_LO_SLOTS;
 	uint64_t* accEmptyBar = accFullBar + 2;
 	uint64_t* crossEmptyBar = accEmptyBar + 2; // fold scheme only: the single cross accumulator is free again
 	uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(crossEmptyBar + 1);
@@ -848,7 +852,7 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	const bool preB = p.b_ready != 0;
 	const int slotBytes = A_TILE_BYTES + BN * BK * 4 * (preB && threeX ? 2 : 1);
 	const int fixedBytes = MAX_EPI_WARPS * STAGING_BYTES_PER_WARP + MAX_EPI_WARPS * 256 /*bias strips*/ + 512 /*barriers*/ + 1024 /*alignment slack*/
-		+ (threeX && !preB ? LO_SLOTS * BN * BK * 4 : 0);
+		+ (threeX && !preB ? lo_slots_for(BN) * BN * BK * 4 : 0);
 	// as many raw slots as fit the 227 KB a CTA may use: the copies run that many K blocks ahead
 	int rawSlots = (227 * 1024 - fixedBytes) / slotBytes;
 	if(rawSlots > MAX_RAW_SLOTS) rawSlots = MAX_RAW_SLOTS;
