@@ -76,7 +76,8 @@ NB200_API const char* nb200_last_cuda_error(void);
 /* Diagnostic aid: when device_buffer is non-NULL, CTA 0 of every later contraction launch stores clock64() stamps of
  * its pipeline roles at device_buffer[kind * steps + index] (16 stamp kinds, 8-byte words; kinds 0-6 and 15 are indexed
  * by K-block step, 7-14 by tile; indices >= steps are dropped).  options bit 4 (value 16): use the cp.async gather
- * kernel even where TMA applies (results are the same; for timing and testing that path).  (NULL, 0, 0) = normal. */
+ * kernel even where TMA applies (results are the same; for timing and testing that path).  options bit 5 (value 32):
+ * never split the K loop of a few-tile convolution.  (NULL, 0, 0) = normal. */
 NB200_API void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int options);
 /* Kernels launched by this library in this process since load (for launch accounting in benchmarks). */
 NB200_API uint64_t nb200_launch_count(void);
@@ -104,8 +105,10 @@ typedef struct nb200_conv_desc {
 /* `scratch` is optional (NULL = none): nb200_blob_convolution_scratch_floats(desc) floats of device memory for what
  * the fast paths prepare once per call: the filter split for the tensor core (lo part / rounded copy, so that no CTA
  * converts its filter tiles), and for few-channel images (the 3-channel network stem) a copy of the image with its
- * spatial padding and 4-channel pixels plus the filter widened to match.  The engine takes it from its block pool;
- * without it the same result is computed by slower in-kernel conversion and element-wise gathers. */
+ * spatial padding and 4-channel pixels plus the filter widened to match; for convolutions with few output tiles
+ * (small batches) also room for the partial results of a split K loop, which a finishing pass sums in a fixed order
+ * (results do not vary from run to run).  The engine takes it from its block pool; without it the same result is
+ * computed by slower in-kernel conversion and element-wise gathers, unsplit. */
 NB200_API size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* desc);
 NB200_API int nb200_blob_convolution(void* stream, const nb200_conv_desc* desc, const float* x,
 	const float* filter, float* y, float* scratch, const nb200_epilogue* epi, int precision);
@@ -113,8 +116,9 @@ NB200_API int nb200_blob_convolution(void* stream, const nb200_conv_desc* desc, 
  * of the call (all device memory already in their own pool; a loop that must not stall on cudaMalloc; a fixed memory
  * budget): the work space (prepared filter, padded image) is a fixed array of NB200_STATIC_SCRATCH_FLOATS floats inside
  * the library's device module, and neither this call nor anything under it allocates or frees memory.
- *  - A shape that needs more than NB200_STATIC_SCRATCH_FLOATS floats of scratch
- *    (nb200_blob_convolution_scratch_floats(desc)) is refused with NB200_ETOOBIG before anything is launched.
+ *  - A shape whose prepared operands need more than NB200_STATIC_SCRATCH_FLOATS floats is refused with NB200_ETOOBIG
+ *    before anything is launched (nb200_blob_convolution_scratch_floats(desc) is an upper bound of that need: it
+ *    includes the optional room for a split K loop, which this entry point uses only as far as the array reaches).
  *  - The first call on each device looks the array up (and may load the module): make it during set-up, with that
  *    device current, before a stream capture begins.
  *  - One work space per device: calls that overlap in time on one device (other streams, other threads) race on it;

@@ -81,6 +81,17 @@ __global__ void __launch_bounds__(256) prepare_filter_kernel(const float* __rest
 	}
 }
 
+// Room for the partial results of a split-K launch: only launches with few tiles split (at most 74 tiles of 128 x 128
+// outputs, cut in as many parts as fill the machine), so the product of parts and outputs is bounded.
+constexpr long long SPLIT_TILES_MAX = 74;
+constexpr size_t SPLIT_SCRATCH_FLOATS = static_cast<size_t>(148) * 128 * 128;
+
+size_t split_scratch_floats(long long outRows, long long n, long long kk)
+{
+	const long long tiles = ((outRows + 127) / 128) * ((n + 127) / 128);
+	return tiles <= SPLIT_TILES_MAX && kk >= 256 && n % 4 == 0 ? SPLIT_SCRATCH_FLOATS + 8 : 0;
+}
+
 // floats of scratch for the prepared filter (rounded up so that what follows stays 16-byte aligned)
 size_t prepared_filter_floats(long long k, long long r, long long s, long long c)
 {
@@ -152,9 +163,9 @@ bool wants_channel_padding(const nb200_conv_desc* d)
 	return !pointwise && d->c % 4 != 0;
 }
 
-extern "C" {
+namespace nb200 {
 
-size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* d)
+size_t convolution_scratch_floats(const nb200_conv_desc* d, bool withSplitRoom)
 {
 	if(d == nullptr || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0) return 0;
 	const size_t c4 = static_cast<size_t>((d->c + 3) / 4 * 4);
@@ -163,7 +174,20 @@ size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* d)
 	if(plan_row_window(d, &win)) return win.imageFloats + 2 * win.filterFloats + 16;
 	size_t floats = prepared_filter_floats(d->k, d->r, d->s, static_cast<long long>(c4)) + 8;
 	if(wants_channel_padding(d)) floats += (static_cast<size_t>(d->batch) * d->h * d->w + static_cast<size_t>(d->k) * d->r * d->s) * c4 + 8;
+	// last, so that a caller with less room loses only the split
+	if(withSplitRoom && d->ho > 0 && d->wo > 0) {
+		floats += split_scratch_floats(static_cast<long long>(d->batch) * d->ho * d->wo, d->k, static_cast<long long>(d->r) * d->s * c4);
+	}
 	return floats;
+}
+
+} // namespace nb200
+
+extern "C" {
+
+size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* d)
+{
+	return convolution_scratch_floats(d, true);
 }
 
 void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int skip_mask)
@@ -223,6 +247,17 @@ int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int
 int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
 	float* scratch, const nb200_epilogue* epi, int precision)
 {
+	return blob_convolution(stream, d, x, filter, y, scratch, scratch != nullptr ? convolution_scratch_floats(d, true) : 0,
+		epi, precision);
+}
+
+} // extern "C"
+
+namespace nb200 {
+
+int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
+	float* scratch, size_t scratchFloats, const nb200_epilogue* epi, int precision)
+{
 	if(d == nullptr) return NB200_EINVAL;
 	WindowPlan win;
 	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && d->batch > 0 && d->k > 0 && d->r > 0 && d->s > 0
@@ -277,7 +312,9 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 		if(rc != NB200_OK) return rc;
 		nb200_conv_desc padded = *d;
 		padded.c = c4;
-		return nb200_blob_convolution(stream, &padded, xs, fs, y, fs + taps * c4, epi, precision);
+		const size_t used = static_cast<size_t>(fs + taps * c4 - scratch);
+		return blob_convolution(stream, &padded, xs, fs, y, fs + taps * c4, scratchFloats > used ? scratchFloats - used : 0,
+			epi, precision);
 	}
 	if(d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0
 		|| d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
@@ -329,14 +366,23 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 		if(rc != NB200_OK) return rc;
 		if(precision == NB200_PREC_3XTF32) p.Blo = prepared; else p.B = prepared;
 		p.b_ready = 1;
+		// whatever the caller's scratch holds beyond the prepared filter is room for split-K partial results
+		float* const rest = prepared + prepared_filter_floats(d->k, d->r, d->s, d->c);
+		const size_t used = static_cast<size_t>(rest - scratch);
+		if(scratchFloats > used + 4 && split_scratch_floats(outRows, d->k, kk) > 0) {
+			p.splitScratch = rest;
+			p.splitScratchFloats = static_cast<long long>(scratchFloats - used);
+			if(p.splitScratchFloats > static_cast<long long>(SPLIT_SCRATCH_FLOATS)) p.splitScratchFloats = SPLIT_SCRATCH_FLOATS;
+		}
 		const int rc2 = run(p, 1, stream, precision);
 		if(rc2 != NB200_EINVAL) return rc2;
 		// the launcher could not describe an operand to TMA after all: fall back to in-kernel conversion
 		p.B = filter;
 		p.Blo = nullptr;
 		p.b_ready = 0;
+		p.splitScratch = nullptr;
 	}
 	return run(p, 1, stream, precision);
 }
 
-} // extern "C"
+} // namespace nb200

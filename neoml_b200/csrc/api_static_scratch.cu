@@ -56,7 +56,8 @@ extern "C" int nb200_blob_convolution_static_scratch(void* stream, const nb200_c
 	const float* filter, float* y, const nb200_epilogue* epi, int precision)
 {
 	if(desc == nullptr) return NB200_EINVAL;
-	const size_t need = nb200_blob_convolution_scratch_floats(desc);
+	// the room for split-K partial results is optional: without it a few-tile convolution runs unsplit
+	const size_t need = nb200::convolution_scratch_floats(desc, false);
 	if(need == 0) {
 		// this shape reads its operands in place: the plain entry point already works without memory of any kind
 		return nb200_blob_convolution(stream, desc, x, filter, y, nullptr, epi, precision);
@@ -64,5 +65,5 @@ extern "C" int nb200_blob_convolution_static_scratch(void* stream, const nb200_c
 	if(need > static_cast<size_t>(NB200_STATIC_SCRATCH_FLOATS)) return NB200_ETOOBIG;
 	float* scratch = static_scratch();
 	if(scratch == nullptr) return NB200_ENODEVICE;
-	return nb200_blob_convolution(stream, desc, x, filter, y, scratch, epi, precision);
+	return nb200::blob_convolution(stream, desc, x, filter, y, scratch, NB200_STATIC_SCRATCH_FLOATS, epi, precision);
 }

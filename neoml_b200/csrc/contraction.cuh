@@ -34,6 +34,12 @@ struct ContractionParams {
 	int b_tma;  // B arrives by TMA (tiled rows)
 	const float* Blo; // optional: lo(B) = B - trunc_tf32(B) prepared by the caller (same shape and strides as B); with it,
 	                  // and for plain TF32 a pre-rounded B passed as B itself, the kernel does no per-step work on B
+	int kSplits;      // > 1: every tile's K loop is cut into this many equal parts that run as separate work items (few-tile
+	                  // launches: latency at small batch).  Part i stores its partial result at C + i * M * ldc, where C
+	                  // is then the caller's split scratch; a finishing pass sums the parts in order (deterministic) and
+	                  // applies bias, residual and activation.  Set by the launcher.
+	float* splitScratch;          // optional room for those partial results (NULL: never split)
+	long long splitScratchFloats;
 	int b_ready;      // 1: B needs no conversion in the kernel (Blo given for 3xTF32 / B already rounded for TF32)
 	// convolution geometry (a_mode != A_ROWS)
 	int H, W, Cin, Ho, Wo, S, padH, padW, strH, strW, dilH, dilW;
@@ -106,5 +112,11 @@ __device__ __forceinline__ float gather_b(const ContractionParams& p, const floa
 void set_contraction_trace(unsigned long long* buffer, int steps, int options);
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
 int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
+
+// Scratch floats of a convolution (api_contraction.cu); the room for split-K partial results comes last and is optional.
+size_t convolution_scratch_floats(const nb200_conv_desc* d, bool withSplitRoom);
+// nb200_blob_convolution with the size of the scratch stated
+int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
+	float* scratch, size_t scratchFloats, const nb200_epilogue* epi, int precision);
 
 } // namespace nb200

@@ -167,7 +167,10 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	const int lane = tid & 31;
 	const int numKb = (p.K + BK - 1) / BK;
 	const int myTiles = blockIdx.x < numTiles ? (numTiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
-	const int totalSteps = myTiles * numKb;
+	// with split K the unit of work is (tile, K part): `numTiles` counts those, each covers kbPer K blocks
+	const int kSplits = GATHER || p.kSplits < 1 ? 1 : p.kSplits;
+	const int kbPer = numKb / kSplits;
+	const int totalSteps = myTiles * kbPer;
 	const bool allTma = !GATHER || (p.a_tma != 0 && p.b_tma != 0);
 
 	if(tid == 0) {
@@ -211,7 +214,9 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			bool ok = true;
 			const int hw = p.Ho * p.Wo;
 			for(int local = 0; local < myTiles && ok; ++local, tile += gridDim.x) {
-				const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN, p.tileM);
+				const int tileIdx = tile / kSplits;
+				const int kbBegin = (tile - tileIdx * kSplits) * kbPer;
+				const TileCoord tc = tile_coord(tileIdx, nTiles, tilesPerBatch, BN, p.tileM);
 				int w0 = 0, h0 = 0, img = 0;
 				if(p.a_tma == 3) {
 					const int outRow = tc.m0 / p.tileM; // = image * Ho + oy
@@ -225,7 +230,13 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 					h0 = oy * p.strH - p.padH;
 				}
 				int c0 = 0, fs = 0, fr = 0; // channel offset inside the filter tap, tap column, tap row
-				for(int kb = 0; kb < numKb; ++kb, ++step) {
+				if(p.a_tma == 2 && kbBegin > 0) {
+					const int tap = kbBegin * BK / p.Cin;
+					c0 = kbBegin * BK - tap * p.Cin;
+					fr = tap / p.S;
+					fs = tap - fr * p.S;
+				}
+				for(int kb = kbBegin; kb < kbBegin + kbPer; ++kb, ++step) {
 					if(!mbar_wait_bounded_warp(&rawEmptyBar[slot], parity, abortFlag, p.status, SITE_RAW_EMPTY)) { ok = false; break; }
 					if(lane == 0) trace(p, TR_COPY_SLOT_FREE, step);
 					const uint32_t aTile = smem_u32(rawRing + static_cast<size_t>(slot) * SLOT_BYTES);
@@ -503,7 +514,9 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 				const uint32_t accMain = tmemBase + set * ACC_COLS;
 				const uint32_t accCross = tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS);
 				uint32_t acc = 0u; // the first MMA of a tile overwrites the accumulators
-				for(int kb = 0; kb < numKb; ++kb, ++it) {
+				const int work = blockIdx.x + local * gridDim.x;
+				const int kbBegin = (work % kSplits) * kbPer;
+				for(int kb = kbBegin; kb < kbBegin + kbPer; ++kb, ++it) {
 					const int ls = it % LO_SLOTS;
 					if(!mbar_wait_bounded_warp(&cvtFullBar[ls], (it / LO_SLOTS) & 1, abortFlag, p.status, SITE_CVT_FULL)) { ok = false; break; }
 					tc_fence_after_sync();
@@ -538,7 +551,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 						}
 						umma_commit(&rawEmptyBar[slot]);
 						umma_commit(&loEmptyBar[ls]);
-						if(kb == numKb - 1) umma_commit(&accFullBar[set]);
+						if(kb == kbBegin + kbPer - 1) umma_commit(&accFullBar[set]);
 					}
 					acc = 1u; // every later step of the tile accumulates
 					__syncwarp();
@@ -575,9 +588,11 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		const float clampHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
 		bool ok = true;
 		for(int local = 0; local < myTiles && ok; ++local) {
-			const int tile = blockIdx.x + local * gridDim.x;
+			const int work = blockIdx.x + local * gridDim.x;
+			const int tile = work / kSplits;
 			const TileCoord tc = tile_coord(tile, nTiles, tilesPerBatch, BN, p.tileM);
-			float* __restrict__ C = p.C + tc.batch * p.strideC;
+			// a K part of a split launch stores its partial sums in its own slab
+			float* __restrict__ C = p.C + tc.batch * p.strideC + static_cast<size_t>(work - tile * kSplits) * p.M * p.ldc;
 			const float* __restrict__ R = p.residual != nullptr ? p.residual + tc.batch * p.strideC : nullptr;
 			const int set = local & 1;
 			const uint32_t accParity = (local >> 1) & 1;
@@ -838,6 +853,46 @@ bool make_window_map(CUtensorMap* map, const ContractionParams& p, int images, i
 		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tail of a split-K launch: out = act(part 0 + part 1 + ... (in this order) + bias[n] + residual[m][n]).
+struct SplitFinish {
+	float* out;
+	int parts;
+	long long slab; // floats per part
+	const float* bias;
+	const float* residual;
+	int ldr;
+	int act;
+	float actParam;
+	const float* actParamDevice;
+};
+
+__global__ void __launch_bounds__(256) split_finish_kernel(const float* __restrict__ partials, int n4, long long quads,
+	const SplitFinish f)
+{
+	const float param = f.actParamDevice != nullptr ? __ldg(f.actParamDevice) : f.actParam;
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < quads; i += stride) {
+		const long long row = i / n4;
+		const int q = static_cast<int>(i - row * n4);
+		float4 v = __ldg(reinterpret_cast<const float4*>(partials) + i);
+		for(int part = 1; part < f.parts; ++part) {
+			const float4 w = __ldg(reinterpret_cast<const float4*>(partials + part * f.slab) + i);
+			v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+		}
+		if(f.bias != nullptr) {
+			const float4 b = __ldg(reinterpret_cast<const float4*>(f.bias) + q);
+			v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+		}
+		if(f.residual != nullptr) {
+			const float4 r = __ldg(reinterpret_cast<const float4*>(f.residual + row * f.ldr) + q);
+			v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+		}
+		v.x = apply_act(v.x, f.act, param); v.y = apply_act(v.y, f.act, param);
+		v.z = apply_act(v.z, f.act, param); v.w = apply_act(v.w, f.act, param);
+		reinterpret_cast<float4*>(f.out)[i] = v;
+	}
+}
+
 unsigned long long* g_traceBuffer = nullptr;
 int g_traceSteps = 0;
 int g_traceOptions = 0;
@@ -882,7 +937,6 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	const long long numTiles = tilesPerBatch * batch;
 	if(numTiles > 0x7fffffffLL || numTiles * ((p.K + BK - 1) / BK) > 0x7fffffffLL) return NB200_ETOOBIG;
 	const int sms = sm_count();
-	const int grid = numTiles < sms ? static_cast<int>(numTiles) : sms;
 	// operands that TMA can describe are loaded by it; everything else (odd alignment, column-major B, channel counts
 	// that do not fill a 32-wide K block) is gathered with cp.async by the copy warps
 	alignas(64) CUtensorMap mapA, mapB, mapBlo;
@@ -908,8 +962,33 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	if(preB && (!p.a_tma || !p.b_tma || (threeX && !make_rows_map(&mapBlo, p.Blo, p.K, p.N, p.ldb, batch, p.strideB, BN)))) {
 		return NB200_EINVAL;
 	}
-	const int nt = static_cast<int>(numTiles), nn = static_cast<int>(nTiles), tpb = static_cast<int>(tilesPerBatch);
 	const bool gather = p.a_tma == 0 || p.b_tma == 0;
+	// Few tiles and a long K loop (small batches: a handful of CTAs would walk dozens of K blocks while the other SMs
+	// idle): cut every tile's K loop into equal parts that run as separate work items and store their partial sums in
+	// slabs of the caller's scratch; a finishing pass sums the slabs in order and applies bias, residual, activation.
+	const int numKb = (p.K + BK - 1) / BK;
+	int kSplits = 1;
+	const long long slab = static_cast<long long>(p.M) * p.N;
+	if(!gather && numTiles * 2 <= sms && numKb >= 8 && p.c_vec && !p.accumulate && batch == 1 && p.ldc == p.N
+		&& p.splitScratch != nullptr && aligned16(p.splitScratch) && !(g_traceOptions & 32)) {
+		const long long room = sms / numTiles;
+		// at least four K blocks per part (measured: two is no better, eight is slower at batch 1)
+		for(int d = 2; d <= numKb / 4 && d <= room && d * slab <= p.splitScratchFloats; ++d) {
+			if(numKb % d == 0) kSplits = d; // the largest divisor of the K-block count that fits the machine and the scratch
+		}
+	}
+	SplitFinish finish = {};
+	if(kSplits > 1) {
+		finish.bias = p.bias; finish.residual = p.residual; finish.ldr = p.ldr; finish.act = p.act; finish.actParam = p.act_param;
+		finish.actParamDevice = p.act_param_device;
+		finish.out = p.C; finish.parts = kSplits; finish.slab = slab;
+		p.bias = nullptr; p.residual = nullptr; p.act = NB200_ACT_NONE; p.act_param_device = nullptr;
+		p.C = p.splitScratch;
+	}
+	p.kSplits = kSplits;
+	const long long numWork = numTiles * kSplits;
+	const int grid = numWork < sms ? static_cast<int>(numWork) : sms;
+	const int nt = static_cast<int>(numWork), nn = static_cast<int>(nTiles), tpb = static_cast<int>(tilesPerBatch);
 #define NB200_LAUNCH(G, X) contraction_tc_kernel<BN, G, X><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo)
 	if(threeX) {
 		if(gather) NB200_LAUNCH(true, true); else NB200_LAUNCH(false, true);
@@ -918,6 +997,11 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	}
 #undef NB200_LAUNCH
 	count_launch();
+	if(kSplits > 1) {
+		const long long quads = slab / 4;
+		split_finish_kernel<<<grid_for(quads, 256, 16), 256, 0, stream>>>(p.splitScratch, p.N / 4, quads, finish);
+		count_launch();
+	}
 	return check_launch();
 }
 

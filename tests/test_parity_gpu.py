@@ -331,11 +331,12 @@ def test_gather_kernel_agrees_with_the_tma_kernel(ops):
     lib = _capi.load()
     x, f, b = dev(cases.uniform(61, (3, 20, 20, 64))), dev(cases.uniform(62, (80, 3, 3, 64))), dev(cases.uniform(63, (80,)))
     a, w = dev(cases.uniform(64, (300, 160))), dev(cases.uniform(65, (72, 160)))
-    want_conv = ops.BlobConvolution(x, f, b, padding=(1, 1), act=ops.ACT_RELU)
-    want_mmt = ops.MultiplyMatrixByTransposedMatrix(a, w)
-    torch.cuda.synchronize()
-    lib.nb200_debug_set_contraction_trace(None, 0, 16)
+    lib.nb200_debug_set_contraction_trace(None, 0, 32)   # one work item per tile in both kernels (the gather one never splits K)
     try:
+        want_conv = ops.BlobConvolution(x, f, b, padding=(1, 1), act=ops.ACT_RELU)
+        want_mmt = ops.MultiplyMatrixByTransposedMatrix(a, w)
+        torch.cuda.synchronize()
+        lib.nb200_debug_set_contraction_trace(None, 0, 16)
         got_conv = ops.BlobConvolution(x, f, b, padding=(1, 1), act=ops.ACT_RELU)
         got_mmt = ops.MultiplyMatrixByTransposedMatrix(a, w)
         torch.cuda.synchronize()
@@ -343,6 +344,45 @@ def test_gather_kernel_agrees_with_the_tma_kernel(ops):
         lib.nb200_debug_set_contraction_trace(None, 0, 0)
     assert torch.equal(got_conv, want_conv)
     assert torch.equal(got_mmt, want_mmt)
+
+
+def test_split_k_convolutions(ops, oracle):
+    """Few-tile convolutions cut their K loop into parts that run on otherwise idle SMs and are summed in a fixed
+    order by a finishing pass: same answer as the oracle, the same bits on every run, and within rounding of the
+    unsplit launch (diagnostic option 32) with bias, residual and every activation."""
+    from neoml_b200 import _capi
+    lib = _capi.load()
+    shapes = [((1, 14, 14, 256), (64, 3, 3, 256), 1, 1),     # 2 tiles, 72 K blocks
+              ((1, 7, 7, 512), (512, 1, 1, 512), 0, 1),      # pointwise, 1 x 4 tiles, 16 K blocks
+              ((2, 9, 11, 96), (40, 5, 5, 96), 2, 2),        # ragged M and N, stride 2
+              ((4, 28, 28, 128), (128, 3, 3, 128), 1, 1)]    # 25 tiles: a small split
+    for i, (xs, fs, pad, stride) in enumerate(shapes):
+        x, f, b = cases.uniform(400 + i, xs), cases.uniform(410 + i, fs) * 0.2, cases.uniform(420 + i, (fs[0],))
+        want = oracle.blob_convolution(x, f, b, padding=(pad, pad), stride=(stride, stride))
+        res = cases.uniform(430 + i, want.shape)
+        dx, df, db, dres = dev(x), dev(f), dev(b), dev(res)
+        for act, param, post in [(ops.ACT_NONE, 0.0, lambda v: v), (ops.ACT_RELU, 0.0, lambda v: np.maximum(v, 0)),
+                                 (ops.ACT_RELU, 1.5, lambda v: np.clip(v, 0, 1.5)),
+                                 (ops.ACT_HSWISH, 0.0, lambda v: v * np.clip(v + 3, 0, 6) / 6)]:
+            launches = lib.nb200_launch_count()
+            got = ops.BlobConvolution(dx, df, db, padding=(pad, pad), stride=(stride, stride), act=act, act_param=param,
+                                      residual=dres)
+            again = ops.BlobConvolution(dx, df, db, padding=(pad, pad), stride=(stride, stride), act=act, act_param=param,
+                                        residual=dres)
+            torch.cuda.synchronize()
+            # filter preparation + contraction + the finishing pass that only a split launch has
+            assert lib.nb200_launch_count() - launches == 6, f"shape {i} did not split"
+            assert torch.equal(got, again), f"shape {i}: split results differ between runs"
+            check(host(got), post((want + res).astype(np.float64)).astype(np.float32), TOL_FP32, f"split conv {i} act {act}/{param}")
+            lib.nb200_debug_set_contraction_trace(None, 0, 32)
+            try:
+                unsplit = ops.BlobConvolution(dx, df, db, padding=(pad, pad), stride=(stride, stride), act=act,
+                                              act_param=param, residual=dres)
+                torch.cuda.synchronize()
+            finally:
+                lib.nb200_debug_set_contraction_trace(None, 0, 0)
+            # not tighter: the shorter accumulation chains of the parts are the more accurate of the two
+            check(host(got), host(unsplit), TOL_FP32, f"split vs unsplit {i}")
 
 
 def test_vectorised_helper_variants(ops, oracle):
