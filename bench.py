@@ -49,6 +49,9 @@ def parse_args():
                          "115 launches per pass)")
     ap.add_argument("--ops", action="store_true",
                     help="instead of the network: time the bandwidth-bound kernels at the configs' sizes (one JSON line each)")
+    ap.add_argument("--kernel-options", type=int, default=0,
+                    help="diagnostic switches of the contraction launcher (16 gather kernel, 32 no split K, 64 no "
+                         "programmatic dependent launch); for A/B timing only")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
     return ap.parse_args()
 
@@ -228,6 +231,8 @@ def run_ours(args):
     lib = _capi.load()
     if lib.nb200_device_count() < 1:
         raise SystemExit("libneoml_b200.so sees no sm_100 device")
+    if args.kernel_options:
+        lib.nb200_debug_set_contraction_trace(None, 0, args.kernel_options)
 
     def barrier():
         if world > 1:

@@ -74,6 +74,9 @@ __global__ void __launch_bounds__(256) pad_channels_kernel(const float* __restri
 __global__ void __launch_bounds__(256) prepare_filter_kernel(const float* __restrict__ x, float* __restrict__ y,
 	long long n, int mode)
 {
+	// the scratch this writes may still be read by the convolution before it in the stream
+	dependent_wait();
+	dependents_may_start();
 	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
 	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
 		const float v = __ldg(x + i);
@@ -359,8 +362,8 @@ int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, con
 	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && tmaShape && outRows > 0) {
 		float* prepared = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
 		const long long n = static_cast<long long>(d->k) * kk;
-		prepare_filter_kernel<<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>(filter, prepared, n,
-			precision == NB200_PREC_3XTF32 ? 0 : 1);
+		launch_dependent(overlap_launches(), prepare_filter_kernel, dim3(grid_for(n, 256, 8)), dim3(256), 0, as_stream(stream),
+			filter, prepared, n, precision == NB200_PREC_3XTF32 ? 0 : 1);
 		count_launch(1);
 		const int rc = check_launch();
 		if(rc != NB200_OK) return rc;

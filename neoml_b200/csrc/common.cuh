@@ -20,6 +20,25 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Grid size for grid-stride kernels: a whole number of waves over the SMs of the current device.
 int sm_count();
+// Launch `kernel` so that it may overlap the tail of the kernel before it in `stream` (the kernel itself orders its
+// memory accesses with dependent_wait()).  `overlap` false: an ordinary launch.
+template<typename... Params, typename... Args>
+inline cudaError_t launch_dependent(bool overlap, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smemBytes,
+	cudaStream_t stream, Args&&... args)
+{
+	cudaLaunchConfig_t config = {};
+	config.gridDim = grid;
+	config.blockDim = block;
+	config.dynamicSmemBytes = smemBytes;
+	config.stream = stream;
+	cudaLaunchAttribute attribute[1];
+	attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attribute[0].val.programmaticStreamSerializationAllowed = 1;
+	config.attrs = attribute;
+	config.numAttrs = overlap ? 1 : 0;
+	return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 inline int grid_for(long long work_items, int per_block, int waves_cap = 8)
 {
 	long long blocks = (work_items + per_block - 1) / per_block;
@@ -39,6 +58,20 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
 
 // True in exactly one lane of a fully converged warp.  Code that issues tcgen05 / TMA instructions this way stays
 // warp-uniform up to the instruction itself, which lets the compiler keep descriptors and addresses in uniform registers.
+// Programmatic dependent launch: a kernel launched with launch_dependent() may start while the kernel before it in
+// the stream is still running.  It must call dependent_wait() before it touches global memory that an earlier kernel
+// wrote or still reads (the wait returns when every earlier kernel has completed and its writes are visible), and it
+// calls dependents_may_start() to let the kernel behind it be scheduled as soon as SMs fall free.  Both are no-ops in
+// a kernel that was launched the ordinary way.
+__device__ __forceinline__ void dependent_wait()
+{
+	asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void dependents_may_start()
+{
+	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ bool elect_one()
 {
 	uint32_t pred = 0;

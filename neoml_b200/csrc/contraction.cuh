@@ -113,6 +113,8 @@ void set_contraction_trace(unsigned long long* buffer, int steps, int options);
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
 int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
 
+// false when diagnostic option 64 asks for ordinary launches instead of programmatic dependent ones
+bool overlap_launches();
 // Scratch floats of a convolution (api_contraction.cu); the room for split-K partial results comes last and is optional.
 size_t convolution_scratch_floats(const nb200_conv_desc* d, bool withSplitRoom);
 // nb200_blob_convolution with the size of the scratch stated

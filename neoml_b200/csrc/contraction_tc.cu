@@ -201,6 +201,10 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	__syncthreads();
 	tc_fence_after_sync();
 	const uint32_t tmemBase = *tmemSlot;
+	// everything above touched only this CTA's own state and ran while the previous kernel was finishing; from here on
+	// the operands are read and the result is written
+	dependent_wait();
+	dependents_may_start();
 
 	if(warp < COPY_WARPS && allTma) {
 		// ------------------------------------------------------------------ copy, both operands by TMA
@@ -869,6 +873,8 @@ struct SplitFinish {
 __global__ void __launch_bounds__(256) split_finish_kernel(const float* __restrict__ partials, int n4, long long quads,
 	const SplitFinish f)
 {
+	dependent_wait();
+	dependents_may_start();
 	const float param = f.actParamDevice != nullptr ? __ldg(f.actParamDevice) : f.actParam;
 	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
 	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < quads; i += stride) {
@@ -989,7 +995,9 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	const long long numWork = numTiles * kSplits;
 	const int grid = numWork < sms ? static_cast<int>(numWork) : sms;
 	const int nt = static_cast<int>(numWork), nn = static_cast<int>(nTiles), tpb = static_cast<int>(tilesPerBatch);
-#define NB200_LAUNCH(G, X) contraction_tc_kernel<BN, G, X><<<grid, THREADS, smemBytes, stream>>>(p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo)
+	const bool overlap = overlap_launches();
+#define NB200_LAUNCH(G, X) launch_dependent(overlap, contraction_tc_kernel<BN, G, X>, dim3(grid), dim3(THREADS), smemBytes, stream, \
+	p, nt, nn, tpb, rawSlots, mapA, mapB, mapBlo)
 	if(threeX) {
 		if(gather) NB200_LAUNCH(true, true); else NB200_LAUNCH(false, true);
 	} else {
@@ -999,13 +1007,19 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	count_launch();
 	if(kSplits > 1) {
 		const long long quads = slab / 4;
-		split_finish_kernel<<<grid_for(quads, 256, 16), 256, 0, stream>>>(p.splitScratch, p.N / 4, quads, finish);
+		launch_dependent(overlap, split_finish_kernel, dim3(grid_for(quads, 256, 16)), dim3(256), 0, stream,
+			static_cast<const float*>(p.splitScratch), p.N / 4, quads, finish);
 		count_launch();
 	}
 	return check_launch();
 }
 
 } // namespace
+
+bool overlap_launches()
+{
+	return !(g_traceOptions & 64);
+}
 
 void set_contraction_trace(unsigned long long* buffer, int steps, int options)
 {

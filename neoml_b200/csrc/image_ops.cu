@@ -226,6 +226,94 @@ __global__ void __launch_bounds__(256) chconv3x3_kernel(const nb200_chconv_desc 
 	}
 }
 
+// The same convolution for large images: a thread owns four channels of a block of TH output rows by TW output columns
+// and walks down the rows with a window of input rows in registers, so every input row of its columns is loaded once
+// per block instead of once per output row (stride 1: (TH + 2) * 6 loads for TH * 4 outputs against 18 per 4).  The
+// rows of the NEXT output row are requested before the current one is computed (the window holds one output row more
+// than it needs), and the filter sits in shared memory, which leaves the registers to the window.  The loop over the
+// rows is fully unrolled: the window rotates by renaming, not by moves.  The sums are formed in the order of the strip
+// kernel (bias first, filter rows outer, columns inner), so the two kernels agree bit for bit.
+template<int STRIDE, int TH>
+__global__ void __launch_bounds__(128, 4) chconv3x3_rows_kernel(const nb200_chconv_desc p, const float* __restrict__ x,
+	const float* __restrict__ filter, const float* __restrict__ freeTerm, float* __restrict__ y, int act,
+	float actParam, int strips, int rowGroups, unsigned total)
+{
+	constexpr int TW = STRIDE == 1 ? 4 : 2;
+	constexpr int COLS = STRIDE == 1 ? TW + 2 : 2 * TW + 1;
+	constexpr int WIN = 3; // input rows held
+	extern __shared__ float4 filterShared[]; // [9][c / 4]
+	const unsigned cv = p.c / 4;
+	for(unsigned i = threadIdx.x; i < 9 * cv; i += blockDim.x) filterShared[i] = __ldg(reinterpret_cast<const float4*>(filter) + i);
+	__syncthreads();
+	const bool relu = act == NB200_ACT_RELU;
+	const float reluHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
+	for(unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+		unsigned r = t;
+		const unsigned cq = r % cv; r /= cv;
+		const unsigned sx = r % strips; r /= strips;
+		const int oy0 = static_cast<int>(r % rowGroups) * TH;
+		const unsigned n = r / rowGroups;
+		const int ox0 = sx * TW;
+		const int ix0 = ox0 * STRIDE - 1;
+		const float4* img = reinterpret_cast<const float4*>(x) + static_cast<size_t>(n) * p.h * p.w * cv + cq;
+		bool colOk[COLS];
+#pragma unroll
+		for(int k = 0; k < COLS; ++k) colOk[k] = static_cast<unsigned>(ix0 + k) < static_cast<unsigned>(p.w);
+		auto loadRow = [&](int iy, float4 (&row)[COLS]) {
+			const bool rowOk = static_cast<unsigned>(iy) < static_cast<unsigned>(p.h);
+			const float4* src = img + (static_cast<ptrdiff_t>(iy) * p.w + ix0) * static_cast<ptrdiff_t>(cv);
+#pragma unroll
+			for(int k = 0; k < COLS; ++k) {
+				row[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+				if(rowOk && colOk[k]) row[k] = __ldg(src + static_cast<size_t>(k) * cv);
+			}
+		};
+		const float4 b = freeTerm != nullptr ? __ldg(reinterpret_cast<const float4*>(freeTerm) + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
+		float4* out = reinterpret_cast<float4*>(y) + ((static_cast<size_t>(n) * p.ho + oy0) * p.wo + ox0) * cv + cq;
+		// input row iy sits in slot (iy - first) % WIN, first = the row above the block
+		const int first = oy0 * STRIDE - 1;
+		float4 win[WIN][COLS];
+#pragma unroll
+		for(int k = 0; k < 3 - STRIDE; ++k) loadRow(first + k, win[k]);
+#pragma unroll
+		for(int j = 0; j < TH; ++j) {
+			if(oy0 + j >= p.ho) break;
+			const int top = STRIDE * j; // offset of this output row's first input row from `first`
+#pragma unroll
+			for(int k = 3 - STRIDE; k < 3; ++k) loadRow(first + top + k, win[(top + k) % WIN]);
+			float4 a[TW];
+#pragma unroll
+			for(int i = 0; i < TW; ++i) a[i] = b;
+#pragma unroll
+			for(int fy = 0; fy < 3; ++fy) {
+#pragma unroll
+				for(int fx = 0; fx < 3; ++fx) {
+					const float4 w = filterShared[(3 * fy + fx) * cv + cq];
+#pragma unroll
+					for(int i = 0; i < TW; ++i) {
+						const float4 v = win[(top + fy) % WIN][i * STRIDE + fx];
+						a[i].x = fmaf(v.x, w.x, a[i].x); a[i].y = fmaf(v.y, w.y, a[i].y);
+						a[i].z = fmaf(v.z, w.z, a[i].z); a[i].w = fmaf(v.w, w.w, a[i].w);
+					}
+				}
+			}
+#pragma unroll
+			for(int i = 0; i < TW; ++i) {
+				if(ox0 + i >= p.wo) break;
+				float4 o = a[i];
+				if(act == NB200_ACT_HSWISH) {
+					o.x = apply_act(o.x, act, actParam); o.y = apply_act(o.y, act, actParam);
+					o.z = apply_act(o.z, act, actParam); o.w = apply_act(o.w, act, actParam);
+				} else {
+					o.x = relu ? fminf(fmaxf(o.x, 0.f), reluHi) : o.x; o.y = relu ? fminf(fmaxf(o.y, 0.f), reluHi) : o.y;
+					o.z = relu ? fminf(fmaxf(o.z, 0.f), reluHi) : o.z; o.w = relu ? fminf(fmaxf(o.w, 0.f), reluHi) : o.w;
+				}
+				out[(static_cast<size_t>(j) * p.wo + i) * cv] = o;
+			}
+		}
+	}
+}
+
 // 3x3 / stride 2 max pooling without indices (the inference form; ResNet's stem pool), channels a multiple of four:
 // a thread owns four channels of a strip of TW output columns and slides along it, so the column shared by two
 // neighbouring windows is loaded once.  Window order (rows outer, columns inner) and the `v > best` comparison are those
@@ -366,7 +454,15 @@ int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* d,
 		const int tw = d->stride_h == 1 ? 4 : 2;
 		const int strips = (wo + tw - 1) / tw;
 		const long long total = static_cast<long long>(d->batch) * ho * strips * (d->c / 4);
-		if(d->stride_h == 1) chconv3x3_kernel<1><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, static_cast<unsigned>(total));
+		// row blocks when that still gives every SM a few thousand threads
+		constexpr int TH = 8;
+		const int rowGroups = (ho + TH - 1) / TH;
+		const long long totalRows = static_cast<long long>(d->batch) * rowGroups * strips * (d->c / 4);
+		const size_t filterBytes = static_cast<size_t>(9) * d->c * sizeof(float);
+		if(ho >= TH && totalRows >= 148LL * 1536 && totalRows < 0xffffffffLL && filterBytes <= 40 * 1024) {
+			if(d->stride_h == 1) chconv3x3_rows_kernel<1, TH><<<grid_for(totalRows, 128, 24), 128, filterBytes, s>>>(*d, x, filter, free_term, y, act, act_param, strips, rowGroups, static_cast<unsigned>(totalRows));
+			else chconv3x3_rows_kernel<2, TH><<<grid_for(totalRows, 128, 24), 128, filterBytes, s>>>(*d, x, filter, free_term, y, act, act_param, strips, rowGroups, static_cast<unsigned>(totalRows));
+		} else if(d->stride_h == 1) chconv3x3_kernel<1><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, static_cast<unsigned>(total));
 		else chconv3x3_kernel<2><<<grid_for(total, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, strips, static_cast<unsigned>(total));
 	} else if(vec) {
 		chconv_kernel<4><<<grid_for(outElems / 4, 256, 16), 256, 0, s>>>(*d, x, filter, free_term, y, act, act_param, outElems / 4);
