@@ -90,6 +90,15 @@ NB200_API int nb200_multiply_matrix_by_transposed_matrix(void* stream, const flo
 /* Batched overload (NME.h:533-535): `batch` contiguous problems of identical shape, dense strides. */
 NB200_API int nb200_batch_multiply_matrix_by_transposed_matrix(void* stream, int batch, const float* a, int m,
 	int k, const float* b, int n, float* c, const nb200_epilogue* epi, int precision);
+/* Both overloads of IBlasEngine::MultiplyMatrixByTransposedMatrix (NME.h:529-535) with work space, the form the engine
+ * calls: `batch` problems whose operands follow one another (A_b = a + b*m*lda, B_b = b + b*n*ldb, C_b = c + b*m*ldc).
+ * `scratch` (NULL = none) holds nb200_matrix_product_scratch_floats(batch, m, n, k, ldb) floats of device memory:
+ * for tall products the second operand is split for the tensor core once per call instead of tile by tile in every
+ * CTA, and products with few output tiles (a classifier at batch 1) cut their K loop into parts summed in fixed order. */
+NB200_API size_t nb200_matrix_product_scratch_floats(int batch, int m, int n, int k, int ldb);
+NB200_API int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int batch, const float* a, int m,
+	int k, int lda, const float* b, int n, int ldb, float* c, int ldc, float* scratch, const nb200_epilogue* epi,
+	int precision);
 /* IBlasEngine::MultiplyMatrixByMatrix (NME.h:580-582): C_b[M x N] = A_b[M x K] * B_b[K x N], dense row-major. */
 NB200_API int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int m, int k,
 	const float* b, int n, float* c, const nb200_epilogue* epi, int precision);

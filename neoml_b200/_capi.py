@@ -54,6 +54,9 @@ SIGNATURES = {
     "nb200_launch_count": (C.c_uint64, []),
     "nb200_multiply_matrix_by_transposed_matrix": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _EP, _i]),
     "nb200_batch_multiply_matrix_by_transposed_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
+    "nb200_matrix_product_scratch_floats": (C.c_size_t, [_i, _i, _i, _i, _i]),
+    "nb200_multiply_matrix_by_transposed_matrix_with_scratch": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp,
+                                                                     _EP, _i]),
     "nb200_multiply_matrix_by_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
     "nb200_blob_convolution_scratch_floats": (C.c_size_t, [C.POINTER(ConvDesc)]),
     "nb200_blob_convolution": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _vp, _EP, _i]),

@@ -87,6 +87,9 @@ __global__ void __launch_bounds__(256) prepare_filter_kernel(const float* __rest
 // Room for the partial results of a split-K launch: only launches with few tiles split (at most 74 tiles of 128 x 128
 // outputs, cut in as many parts as fill the machine), so the product of parts and outputs is bounded.
 constexpr long long SPLIT_TILES_MAX = 74;
+// Rows of the first operand from which preparing the second one pays (8 row tiles: every prepared tile is then used
+// eight times).  Attention's per-head products (512 rows, measured) are faster with the conversion left in the kernel.
+constexpr int PREPARE_B_MIN_ROWS = 1024;
 constexpr size_t SPLIT_SCRATCH_FLOATS = static_cast<size_t>(148) * 128 * 128;
 
 size_t split_scratch_floats(long long outRows, long long n, long long kk)
@@ -227,6 +230,60 @@ int nb200_batch_multiply_matrix_by_transposed_matrix(void* stream, int batch, co
 	fill_epilogue(p, epi);
 	if(p.residual == nullptr) p.ldr = n;
 	p.a_vec = vec_ok(a, k, p.strideA); p.b_vec = vec_ok(b, k, p.strideB);
+	return run(p, batch, stream, precision);
+}
+
+size_t nb200_matrix_product_scratch_floats(int batch, int m, int n, int k, int ldb)
+{
+	if(batch <= 0 || m <= 0 || n <= 0 || k <= 0 || ldb < k) return 0;
+	size_t floats = 0;
+	// the split second operand pays when it is reused by several row tiles
+	if(m >= PREPARE_B_MIN_ROWS) floats += (static_cast<size_t>(batch) * n * ldb + 3) / 4 * 4 + 8;
+	if(batch == 1) floats += split_scratch_floats(m, n, k);
+	return floats;
+}
+
+int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int batch, const float* a, int m, int k,
+	int lda, const float* b, int n, int ldb, float* c, int ldc, float* scratch, const nb200_epilogue* epi, int precision)
+{
+	if(batch < 0 || m < 0 || n < 0 || k <= 0 || lda < k || ldb < k || ldc < n) return NB200_EINVAL;
+	ContractionParams p = {};
+	p.A = a; p.B = b; p.C = c;
+	p.M = m; p.N = n; p.K = k;
+	p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+	p.strideA = static_cast<long long>(m) * lda; p.strideB = static_cast<long long>(n) * ldb;
+	p.strideC = static_cast<long long>(m) * ldc;
+	p.a_mode = A_ROWS; p.b_mode = B_ROWS;
+	fill_epilogue(p, epi);
+	if(p.residual == nullptr) p.ldr = ldc;
+	p.a_vec = vec_ok(a, lda, p.strideA); p.b_vec = vec_ok(b, ldb, p.strideB);
+	if(scratch == nullptr || precision == NB200_PREC_FP32_SIMT || batch == 0 || m == 0 || n == 0 || !p.a_vec || !p.b_vec
+		|| static_cast<long long>(batch) * n * ldb > 0x7fffffffLL) {
+		return run(p, batch, stream, precision);
+	}
+	float* rest = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
+	const bool prepare = m >= PREPARE_B_MIN_ROWS;
+	if(prepare) {
+		// one pass over the second operand as it lies in memory (the floats between its rows, if any, are carried along)
+		if(device_status_word() == nullptr) return NB200_ENODEVICE;
+		const long long span = static_cast<long long>(batch - 1) * p.strideB + static_cast<long long>(n - 1) * ldb + k;
+		launch_dependent(overlap_launches(), prepare_filter_kernel, dim3(grid_for(span, 256, 8)), dim3(256), 0, as_stream(stream),
+			b, rest, span, precision == NB200_PREC_3XTF32 ? 0 : 1);
+		count_launch(1);
+		const int rc = check_launch();
+		if(rc != NB200_OK) return rc;
+		if(precision == NB200_PREC_3XTF32) p.Blo = rest; else p.B = rest;
+		p.b_ready = 1;
+		rest += (static_cast<size_t>(batch) * n * ldb + 3) / 4 * 4;
+	}
+	if(batch == 1 && split_scratch_floats(m, n, k) > 0) {
+		p.splitScratch = rest;
+		p.splitScratchFloats = static_cast<long long>(SPLIT_SCRATCH_FLOATS);
+	}
+	const int rc = run(p, batch, stream, precision);
+	if(rc != NB200_EINVAL || !prepare) return rc;
+	// the launcher could not describe an operand to TMA after all: in-kernel conversion, unsplit
+	p.B = b; p.Blo = nullptr; p.b_ready = 0; p.splitScratch = nullptr;
 	return run(p, batch, stream, precision);
 }
 

@@ -150,6 +150,8 @@ private:
 	};
 	mutable CPendingRowOps pendingRows;
 	void flushRowOps() const;
+	int productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
+		const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize );
 	mutable std::recursive_mutex pendingMutex;
 
 	const int device;

@@ -267,17 +267,34 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 	int resultRowSize, int )
 {
 	enter();
-	check( nb200_multiply_matrix_by_transposed_matrix( stream, raw( firstHandle ), firstHeight, firstWidth, firstRowSize,
-		raw( secondHandle ), secondHeight, secondRowSize, raw( resultHandle ), resultRowSize, nullptr, precision ),
-		"MultiplyMatrixByTransposedMatrix" );
+	check( productWithScratch( 1, raw( firstHandle ), firstHeight, firstWidth, firstRowSize, raw( secondHandle ), secondHeight,
+		secondRowSize, raw( resultHandle ), resultRowSize ), "MultiplyMatrixByTransposedMatrix" );
+}
+
+// first * second^T with work space from the stack allocator: a prepared second operand for tall products, room for
+// split-K partial results for products with few output tiles
+int CB200MathEngine::productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
+	const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize )
+{
+	const size_t floats = nb200_matrix_product_scratch_floats( batchSize, firstHeight, secondHeight, firstWidth, secondRowSize );
+	if( floats == 0 ) {
+		return nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
+			firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize, nullptr, nullptr, precision );
+	}
+	CMemoryHandle scratch = StackAlloc( floats * sizeof( float ) );
+	const int rc = nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
+		firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize,
+		static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) ), nullptr, precision );
+	StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
+	return rc;
 }
 
 void CB200MathEngine::MultiplyMatrixByTransposedMatrix( int batchSize, const CConstFloatHandle& firstHandle, int firstHeight,
 	int firstWidth, const CConstFloatHandle& secondHandle, int secondHeight, const CFloatHandle& resultHandle, int )
 {
 	enter();
-	check( nb200_batch_multiply_matrix_by_transposed_matrix( stream, batchSize, raw( firstHandle ), firstHeight, firstWidth,
-		raw( secondHandle ), secondHeight, raw( resultHandle ), nullptr, precision ), "MultiplyMatrixByTransposedMatrix" );
+	check( productWithScratch( batchSize, raw( firstHandle ), firstHeight, firstWidth, firstWidth, raw( secondHandle ),
+		secondHeight, firstWidth, raw( resultHandle ), secondHeight ), "MultiplyMatrixByTransposedMatrix" );
 }
 
 void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHandle& firstHandle, int firstHeight, int firstWidth,
@@ -293,8 +310,8 @@ void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHa
 		float* transposed = static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) );
 		int rc = nb200_transpose_matrix( stream, batchSize, raw( secondHandle ), firstWidth, 1, secondWidth, 1, transposed );
 		if( rc == 0 ) {
-			rc = nb200_batch_multiply_matrix_by_transposed_matrix( stream, batchSize, raw( firstHandle ), firstHeight, firstWidth,
-				transposed, secondWidth, raw( resultHandle ), nullptr, precision );
+			rc = productWithScratch( batchSize, raw( firstHandle ), firstHeight, firstWidth, firstWidth, transposed, secondWidth,
+				firstWidth, raw( resultHandle ), secondWidth );
 		}
 		StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
 		check( rc, "MultiplyMatrixByMatrix" );

@@ -45,9 +45,11 @@ def conv_output_size(size: int, filt: int, pad: int, stride: int, dil: int = 1) 
 def MultiplyMatrixByTransposedMatrix(first, second, result=None, *, first_row_size=None, second_row_size=None,
                                      result_row_size=None, first_height=None, first_width=None, second_height=None,
                                      free_term=None, residual=None, act=ACT_NONE, act_param=0.0, accumulate=False,
-                                     precision=PREC_3XTF32):
+                                     precision=PREC_3XTF32, use_scratch=True):
     """result[M x N] = first[M x K] * second[N x K]^T (+ fused tail).  2-D tensors give the shapes; pass explicit
-    heights/widths/row sizes to address a sub-matrix of a larger buffer, as the reference allows."""
+    heights/widths/row sizes to address a sub-matrix of a larger buffer, as the reference allows.  With use_scratch
+    (what the engine does with its stack allocator) the library gets work space for a prepared second operand and
+    for split-K partial results."""
     m = first_height if first_height is not None else first.shape[0]
     k = first_width if first_width is not None else first.shape[1]
     n = second_height if second_height is not None else second.shape[0]
@@ -57,20 +59,39 @@ def MultiplyMatrixByTransposedMatrix(first, second, result=None, *, first_row_si
     if result is None:
         result = torch.empty((m, ldc), dtype=torch.float32, device=first.device)
     epi = _epilogue(free_term, residual, ldc, act, act_param, accumulate)
-    capi.check("MultiplyMatrixByTransposedMatrix", capi.load().nb200_multiply_matrix_by_transposed_matrix(
-        _stream(), _ptr(_f32(first)), m, k, lda, _ptr(_f32(second)), n, ldb, _ptr(result), ldc, C.byref(epi), precision))
+    lib = capi.load()
+    need = lib.nb200_matrix_product_scratch_floats(1, m, n, k, ldb) if use_scratch else 0
+    if need:
+        scratch = torch.empty(need, dtype=torch.float32, device=first.device)
+        capi.check("MultiplyMatrixByTransposedMatrix", lib.nb200_multiply_matrix_by_transposed_matrix_with_scratch(
+            _stream(), 1, _ptr(_f32(first)), m, k, lda, _ptr(_f32(second)), n, ldb, _ptr(result), ldc, _ptr(scratch),
+            C.byref(epi), precision))
+    else:
+        capi.check("MultiplyMatrixByTransposedMatrix", lib.nb200_multiply_matrix_by_transposed_matrix(
+            _stream(), _ptr(_f32(first)), m, k, lda, _ptr(_f32(second)), n, ldb, _ptr(result), ldc, C.byref(epi), precision))
     return result
 
 
-def BatchMultiplyMatrixByTransposedMatrix(first, second, result=None, *, precision=PREC_3XTF32):
+def BatchMultiplyMatrixByTransposedMatrix(first, second, result=None, *, precision=PREC_3XTF32, use_scratch=True):
     """first [B, M, K], second [B, N, K] -> result [B, M, N]."""
     b, m, k = first.shape
     n = second.shape[1]
     if result is None:
         result = torch.empty((b, m, n), dtype=torch.float32, device=first.device)
-    capi.check("BatchMultiplyMatrixByTransposedMatrix", capi.load().nb200_batch_multiply_matrix_by_transposed_matrix(
-        _stream(), b, _ptr(_f32(first)), m, k, _ptr(_f32(second)), n, _ptr(result), None, precision))
+    _batch_mmt(b, _f32(first), m, k, _f32(second), n, result, precision, use_scratch)
     return result
+
+
+def _batch_mmt(b, first, m, k, second, n, result, precision, use_scratch):
+    lib = capi.load()
+    need = lib.nb200_matrix_product_scratch_floats(b, m, n, k, k) if use_scratch else 0
+    if need:
+        scratch = torch.empty(need, dtype=torch.float32, device=first.device)
+        capi.check("BatchMultiplyMatrixByTransposedMatrix", lib.nb200_multiply_matrix_by_transposed_matrix_with_scratch(
+            _stream(), b, _ptr(first), m, k, k, _ptr(second), n, k, _ptr(result), n, _ptr(scratch), None, precision))
+    else:
+        capi.check("BatchMultiplyMatrixByTransposedMatrix", lib.nb200_batch_multiply_matrix_by_transposed_matrix(
+            _stream(), b, _ptr(first), m, k, _ptr(second), n, _ptr(result), None, precision))
 
 
 def MultiplyMatrixByMatrix(first, second, result=None, *, precision=PREC_3XTF32, use_scratch=True):
@@ -90,8 +111,7 @@ def MultiplyMatrixByMatrix(first, second, result=None, *, precision=PREC_3XTF32,
         transposed = torch.empty((b, n, k), dtype=torch.float32, device=first.device)
         capi.check("TransposeMatrix", lib.nb200_transpose_matrix(_stream(), b, _ptr(_f32(second)), k, 1, n, 1,
                                                                  _ptr(transposed)))
-        capi.check("MultiplyMatrixByMatrix", lib.nb200_batch_multiply_matrix_by_transposed_matrix(
-            _stream(), b, _ptr(_f32(first)), m, k, _ptr(transposed), n, _ptr(result), None, precision))
+        _batch_mmt(b, _f32(first), m, k, transposed, n, result, precision, True)
     else:
         capi.check("MultiplyMatrixByMatrix", lib.nb200_multiply_matrix_by_matrix(
             _stream(), b, _ptr(_f32(first)), m, k, _ptr(_f32(second)), n, _ptr(result), None, precision))

@@ -3,6 +3,13 @@ from pathlib import Path
 
 import pytest
 
+# torch first: importing it after the reference engine's shared library (its OpenMP and BLAS pieces) has been loaded
+# into the process crashes inside torch's own start-up
+try:
+    import torch  # noqa: F401
+except ImportError:
+    pass
+
 ROOT = Path(__file__).resolve().parent.parent
 for p in (ROOT, ROOT / "oracle", ROOT / "tests", ROOT / "tests" / "golden"):
     if str(p) not in sys.path:

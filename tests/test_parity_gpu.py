@@ -385,6 +385,49 @@ def test_split_k_convolutions(ops, oracle):
             check(host(got), host(unsplit), TOL_FP32, f"split vs unsplit {i}")
 
 
+def test_matrix_products_with_work_space(ops, oracle):
+    """MultiplyMatrixByTransposedMatrix with scratch: the second operand is split once per call (tall products; the
+    same bits as the in-kernel split), few-tile products split their K loop (classifier at small batch); batched
+    and strided forms included."""
+    from neoml_b200 import _capi
+    lib = _capi.load()
+    # tall, unsplit: prepared operand, bit-identical to the in-kernel conversion
+    for (m, k, n) in [(1500, 160, 72), (1040, 96, 200)]:
+        a, b = cases.uniform(500 + m, (m, k)), cases.uniform(501 + m, (n, k))
+        da, db = dev(a), dev(b)
+        launches = lib.nb200_launch_count()
+        with_ws = ops.MultiplyMatrixByTransposedMatrix(da, db)
+        assert lib.nb200_launch_count() - launches == 2          # preparation + product
+        plain = ops.MultiplyMatrixByTransposedMatrix(da, db, use_scratch=False)
+        assert torch.equal(with_ws, plain)
+        check(host(with_ws), oracle.multiply_matrix_by_transposed_matrix(a, b), TOL_FP32, f"mmt with scratch {m}x{k}x{n}")
+    # strided operands inside larger buffers
+    m, k, n, lda, ldb, ldc = 1100, 64, 40, 80, 72, 48
+    a, b = cases.uniform(520, (m, lda)), cases.uniform(521, (n, ldb))
+    got = ops.MultiplyMatrixByTransposedMatrix(dev(a), dev(b), first_width=k, second_height=n, first_row_size=lda,
+                                               second_row_size=ldb, result_row_size=ldc)
+    check(host(got)[:, :n], oracle.multiply_matrix_by_transposed_matrix(a[:, :k].copy(), b[:, :k].copy()), TOL_FP32,
+          "strided mmt with scratch")
+    # few tiles, long K: split K (a classifier layer at batch 1 and 8), with bias
+    for (m, k, n) in [(1, 2048, 1000), (8, 2048, 1000), (200, 1024, 256)]:
+        a, b, bias = cases.uniform(530 + m, (m, k)), cases.uniform(531 + m, (n, k)) * 0.1, cases.uniform(532 + m, (n,))
+        da, db, dbias = dev(a), dev(b), dev(bias)
+        launches = lib.nb200_launch_count()
+        got = ops.MultiplyMatrixByTransposedMatrix(da, db, free_term=dbias)
+        assert lib.nb200_launch_count() - launches == 2          # product in K parts + finishing pass
+        again = ops.MultiplyMatrixByTransposedMatrix(da, db, free_term=dbias)
+        assert torch.equal(got, again)
+        check(host(got), oracle.multiply_matrix_by_transposed_matrix(a, b) + bias, TOL_FP32, f"split mmt {m}x{k}x{n}")
+    # batched, tall: prepared operand per batch entry
+    bsz, m, k, n = 3, 1024, 64, 96
+    a, b = cases.uniform(540, (bsz, m, k)), cases.uniform(541, (bsz, n, k))
+    with_ws = ops.BatchMultiplyMatrixByTransposedMatrix(dev(a), dev(b))
+    plain = ops.BatchMultiplyMatrixByTransposedMatrix(dev(a), dev(b), use_scratch=False)
+    assert torch.equal(with_ws, plain)
+    for i in range(bsz):
+        check(host(with_ws)[i], oracle.multiply_matrix_by_transposed_matrix(a[i], b[i]), TOL_FP32, f"batched mmt {i}")
+
+
 def test_vectorised_helper_variants(ops, oracle):
     """The 16-byte forms of row sums, the channel-vector transpose and the strip max-pool against the oracle."""
     for (bsz, h, w) in [(3, 49, 2048), (1, 700, 260), (2, 5, 4)]:     # the second splits its rows over slices
