@@ -20,6 +20,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Grid size for grid-stride kernels: a whole number of waves over the SMs of the current device.
 int sm_count();
+// Tiled tensor map (CUtensorMap behind the void pointer) over a channels-last image batch, no swizzle, zero fill outside
+// the image (contraction_tc.cu, where the driver's encoder is looked up).
+bool make_image_box_map(void* map, const float* base, int c, int w, int h, int n, int boxC, int boxW, int boxH);
 // Launch `kernel` so that it may overlap the tail of the kernel before it in `stream` (the kernel itself orders its
 // memory accesses with dependent_wait()).  `overlap` false: an ordinary launch.
 template<typename... Params, typename... Args>
@@ -337,6 +340,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap,
 	asm volatile(
 		"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
 		::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+		::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 __device__ __forceinline__ void tma_load_5d(uint32_t dst_smem, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
 	int c3, int c4)

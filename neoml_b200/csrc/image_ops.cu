@@ -3,7 +3,9 @@
 // output pixel when channels % 4 == 0 and the buffers are 16-byte aligned, so every access is a coalesced 16-byte
 // load/store along the channel dimension; the stencil re-reads hit L1/L2.
 #include "common.cuh"
+#include <cuda.h>
 #include <float.h>
+#include <atomic>
 
 namespace nb200 {
 
@@ -314,6 +316,139 @@ __global__ void __launch_bounds__(128, 4) chconv3x3_rows_kernel(const nb200_chco
 	}
 }
 
+// The same convolution for large images with the input staged by TMA: a CTA walks tiles of th output rows x tw output
+// columns x 32 channels of one image; one thread issues the bulk copies of the NEXT tiles' input boxes (halo included,
+// zeros delivered by the copy engine where the box leaves the image, so the padding costs no test) into the other
+// stages of a shared-memory ring (as many stages as fit, up to four) while all threads compute the current tile.
+// The bytes in flight per SM are whole input boxes (tens of KB) whatever the register budget of the compute threads.
+// A thread owns four channels of DW_RPP output rows x TW output columns and slides a three-row register window down
+// its rows; the sums are formed in the order of the other kernels (bias, filter rows outer, columns inner): identical
+// results.
+constexpr int DW_RPP = 2;  // output rows per thread: two CTAs of eight warps per SM issue better than one CTA with four rows per thread (measured)
+constexpr int DW_CC = 32;  // channels per tile: one 128-byte line per pixel
+constexpr int DW_MAX_STAGES = 4;
+constexpr int SITE_DW_FULL = 0x201;
+
+template<int STRIDE>
+__global__ void __launch_bounds__(256, 2) chconv3x3_tma_kernel(const nb200_chconv_desc p, const __grid_constant__ CUtensorMap map,
+	const float* __restrict__ filter, const float* __restrict__ freeTerm, float* __restrict__ y, int act, float actParam,
+	int strips, int rowParts, int tilesX, int tilesY, int chunks, unsigned numTiles, int stages, int* status)
+{
+	constexpr int TW = STRIDE == 1 ? 4 : 2;
+	constexpr int COLS = STRIDE == 1 ? TW + 2 : 2 * TW + 1;
+	constexpr int EXTRA = STRIDE == 1 ? 2 : 1; // input rows / columns beyond STRIDE * outputs
+	extern __shared__ uint8_t dwSmemRaw[];
+	__shared__ uint64_t fullBar[DW_MAX_STAGES];
+	__shared__ int abortFlag;
+	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dwSmemRaw) + 127) & ~static_cast<uintptr_t>(127));
+	const int tid = threadIdx.x;
+	const int tw = strips * TW, th = rowParts * DW_RPP;
+	const int colsIn = tw * STRIDE + EXTRA, rowsIn = th * STRIDE + EXTRA;
+	const uint32_t stageBytes = static_cast<uint32_t>(rowsIn) * colsIn * DW_CC * 4;
+	if(tid == 0) {
+		for(int i = 0; i < DW_MAX_STAGES; ++i) mbar_init(&fullBar[i], 1);
+		abortFlag = 0;
+		mbar_init_fence();
+		tma_prefetch_descriptor(&map);
+	}
+	__syncthreads();
+
+	auto issue = [&](unsigned t, int stage) {
+		const int chunk = t % chunks; t /= chunks;
+		const int tx = t % tilesX; t /= tilesX;
+		const int ty = t % tilesY;
+		const int n = t / tilesY;
+		mbar_arrive_expect_tx(&fullBar[stage], stageBytes);
+		tma_load_4d(smem_u32(smem + stage * stageBytes), &map, &fullBar[stage], chunk * DW_CC, tx * tw * STRIDE - 1,
+			ty * th * STRIDE - 1, n);
+	};
+
+	const int q = tid & 7;
+	const int strip = (tid >> 3) % strips;
+	const int part = (tid >> 3) / strips;
+	const bool active = part < rowParts;
+	const bool relu = act == NB200_ACT_RELU;
+	const float reluHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
+	const unsigned cv = p.c / 4;
+
+	if(tid == 0) {
+		for(int i = 0; i < stages - 1; ++i) {
+			const unsigned long long t = blockIdx.x + static_cast<unsigned long long>(i) * gridDim.x;
+			if(t < numTiles) issue(static_cast<unsigned>(t), i);
+		}
+	}
+	int it = 0;
+	for(unsigned t = blockIdx.x; t < numTiles; t += gridDim.x, ++it) {
+		const int stage = it % stages;
+		// the stage this copy fills was read in the previous iteration, which ended with a CTA-wide barrier
+		const unsigned long long ahead = t + static_cast<unsigned long long>(stages - 1) * gridDim.x;
+		if(tid == 0 && ahead < numTiles) issue(static_cast<unsigned>(ahead), (it + stages - 1) % stages);
+		if(!mbar_wait_bounded(&fullBar[stage], (it / stages) & 1, &abortFlag, status, SITE_DW_FULL)) break;
+		unsigned r = t;
+		const int chunk = r % chunks; r /= chunks;
+		const int tx = r % tilesX; r /= tilesX;
+		const int ty = r % tilesY;
+		const unsigned n = r / tilesY;
+		const unsigned cq = chunk * (DW_CC / 4) + q;
+		if(active && cq < cv) {
+			const float4* flt = reinterpret_cast<const float4*>(filter) + cq;
+			float4 f[9];
+#pragma unroll
+			for(int i = 0; i < 9; ++i) f[i] = __ldg(flt + i * cv);
+			const float4 b = freeTerm != nullptr ? __ldg(reinterpret_cast<const float4*>(freeTerm) + cq) : make_float4(0.f, 0.f, 0.f, 0.f);
+			const int oy0 = ty * th + part * DW_RPP, ox0 = tx * tw + strip * TW;
+			// this thread's corner of the input box, in 16-byte units (a pixel is 8 of them)
+			const float4* box = reinterpret_cast<const float4*>(smem + stage * stageBytes)
+				+ (static_cast<size_t>(part * DW_RPP * STRIDE) * colsIn + strip * TW * STRIDE) * (DW_CC / 4) + q;
+			auto loadRow = [&](int row, float4 (&dst)[COLS]) {
+#pragma unroll
+				for(int k = 0; k < COLS; ++k) dst[k] = box[(row * colsIn + k) * (DW_CC / 4)];
+			};
+			float4* out = reinterpret_cast<float4*>(y) + ((static_cast<size_t>(n) * p.ho + oy0) * p.wo + ox0) * cv + cq;
+			float4 win[3][COLS];
+#pragma unroll
+			for(int k = 0; k < 3 - STRIDE; ++k) loadRow(k, win[k]);
+#pragma unroll
+			for(int j = 0; j < DW_RPP; ++j) {
+				if(oy0 + j >= p.ho) break;
+				const int top = STRIDE * j;
+#pragma unroll
+				for(int k = 3 - STRIDE; k < 3; ++k) loadRow(top + k, win[(top + k) % 3]);
+				float4 a[TW];
+#pragma unroll
+				for(int i = 0; i < TW; ++i) a[i] = b;
+#pragma unroll
+				for(int fy = 0; fy < 3; ++fy) {
+#pragma unroll
+					for(int fx = 0; fx < 3; ++fx) {
+						const float4 w = f[3 * fy + fx];
+#pragma unroll
+						for(int i = 0; i < TW; ++i) {
+							const float4 v = win[(top + fy) % 3][i * STRIDE + fx];
+							a[i].x = fmaf(v.x, w.x, a[i].x); a[i].y = fmaf(v.y, w.y, a[i].y);
+							a[i].z = fmaf(v.z, w.z, a[i].z); a[i].w = fmaf(v.w, w.w, a[i].w);
+						}
+					}
+				}
+#pragma unroll
+				for(int i = 0; i < TW; ++i) {
+					if(ox0 + i >= p.wo) break;
+					float4 o = a[i];
+					if(act == NB200_ACT_HSWISH) {
+						o.x = apply_act(o.x, act, actParam); o.y = apply_act(o.y, act, actParam);
+						o.z = apply_act(o.z, act, actParam); o.w = apply_act(o.w, act, actParam);
+					} else {
+						o.x = relu ? fminf(fmaxf(o.x, 0.f), reluHi) : o.x; o.y = relu ? fminf(fmaxf(o.y, 0.f), reluHi) : o.y;
+						o.z = relu ? fminf(fmaxf(o.z, 0.f), reluHi) : o.z; o.w = relu ? fminf(fmaxf(o.w, 0.f), reluHi) : o.w;
+					}
+					out[(static_cast<size_t>(j) * p.wo + i) * cv] = o;
+				}
+			}
+		}
+		__syncthreads(); // every thread has read this stage: a later copy may overwrite it
+	}
+}
+
 // 3x3 / stride 2 max pooling without indices (the inference form; ResNet's stem pool), channels a multiple of four:
 // a thread owns four channels of a strip of TW output columns and slides along it, so the column shared by two
 // neighbouring windows is loaded once.  Window order (rows outer, columns inner) and the `v > best` comparison are those
@@ -391,6 +526,65 @@ int pool_common(void* stream, bool isMax, int batch, int h, int w, int c, int fh
 	return check_launch();
 }
 
+// Launches the TMA-staged kernel when the image is large enough to give every SM several tiles; false = not applicable
+// (the register kernels take over).
+bool chconv3x3_by_tma(const nb200_chconv_desc* d, const float* x, const float* filter, const float* freeTerm, float* y,
+	int act, float actParam, cudaStream_t s)
+{
+	const int stride = d->stride_h;
+	const int tw1 = stride == 1 ? 4 : 2, extra = stride == 1 ? 2 : 1;
+	int strips = (d->wo + tw1 - 1) / tw1;
+	if(strips > 32) strips = 32;
+	// balance the column tiles (57 columns: two tiles of 8 strips, not 14 + 1)
+	const int tilesX0 = (d->wo + strips * tw1 - 1) / (strips * tw1);
+	strips = ((d->wo + tilesX0 - 1) / tilesX0 + tw1 - 1) / tw1;
+	const int tw = strips * tw1;
+	const int tilesX = (d->wo + tw - 1) / tw;
+	int rowParts = 256 / (8 * strips);
+	const int wantParts = (d->ho + DW_RPP - 1) / DW_RPP;
+	if(rowParts > wantParts) rowParts = wantParts;
+	const int colsIn = tw * stride + extra;
+	auto stage_bytes = [&](int parts) { return static_cast<size_t>(parts * DW_RPP * stride + extra) * colsIn * DW_CC * 4; };
+	while(rowParts > 1 && stage_bytes(rowParts) > 100 * 1024) --rowParts;
+	if(stage_bytes(rowParts) > 100 * 1024) return false;
+	const int th = rowParts * DW_RPP;
+	const int tilesY = (d->ho + th - 1) / th;
+	const int chunks = (d->c + DW_CC - 1) / DW_CC;
+	const long long numTiles = static_cast<long long>(d->batch) * tilesY * tilesX * chunks;
+	const int sms = sm_count();
+	if(numTiles < 8LL * sms || numTiles > 0x7fffffffLL) return false;
+	alignas(64) CUtensorMap map;
+	if(!make_image_box_map(&map, x, d->c, d->w, d->h, d->batch, DW_CC, colsIn, th * stride + extra)) return false;
+	// two CTAs per SM when two stages each fit, else one CTA with as many stages as fit
+	int stages = static_cast<int>((112 * 1024) / stage_bytes(rowParts));
+	if(stages < 2) stages = static_cast<int>((225 * 1024) / stage_bytes(rowParts));
+	if(stages > DW_MAX_STAGES) stages = DW_MAX_STAGES;
+	const size_t smemBytes = stages * stage_bytes(rowParts) + 128;
+	static std::atomic<bool> attrSet[64];
+	int dev = 0;
+	if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+	if(!attrSet[dev].load()) {
+		if(cudaFuncSetAttribute(chconv3x3_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess
+			|| cudaFuncSetAttribute(chconv3x3_tma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) {
+			cudaGetLastError();
+			return false;
+		}
+		attrSet[dev].store(true);
+	}
+	const long long perSm = static_cast<long long>(227 * 1024) / static_cast<long long>(smemBytes + 1024);
+	long long grid = sms * (perSm < 1 ? 1 : (perSm > 2 ? 2 : perSm));
+	if(grid > numTiles) grid = numTiles;
+	int* status = device_status_word();
+	if(stride == 1) {
+		chconv3x3_tma_kernel<1><<<static_cast<unsigned>(grid), 256, smemBytes, s>>>(*d, map, filter, freeTerm, y, act, actParam,
+			strips, rowParts, tilesX, tilesY, chunks, static_cast<unsigned>(numTiles), stages, status);
+	} else {
+		chconv3x3_tma_kernel<2><<<static_cast<unsigned>(grid), 256, smemBytes, s>>>(*d, map, filter, freeTerm, y, act, actParam,
+			strips, rowParts, tilesX, tilesY, chunks, static_cast<unsigned>(numTiles), stages, status);
+	}
+	return true;
+}
+
 } // namespace
 } // namespace nb200
 
@@ -458,6 +652,10 @@ int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* d,
 		constexpr int TH = 8;
 		const int rowGroups = (ho + TH - 1) / TH;
 		const long long totalRows = static_cast<long long>(d->batch) * rowGroups * strips * (d->c / 4);
+		if(chconv3x3_by_tma(d, x, filter, free_term, y, act, act_param, s)) {
+			count_launch();
+			return check_launch();
+		}
 		const size_t filterBytes = static_cast<size_t>(9) * d->c * sizeof(float);
 		if(ho >= TH && totalRows >= 148LL * 1536 && totalRows < 0xffffffffLL && filterBytes <= 40 * 1024) {
 			if(d->stride_h == 1) chconv3x3_rows_kernel<1, TH><<<grid_for(totalRows, 128, 24), 128, filterBytes, s>>>(*d, x, filter, free_term, y, act, act_param, strips, rowGroups, static_cast<unsigned>(totalRows));

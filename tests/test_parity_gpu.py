@@ -428,6 +428,22 @@ def test_matrix_products_with_work_space(ops, oracle):
         check(host(with_ws)[i], oracle.multiply_matrix_by_transposed_matrix(a[i], b[i]), TOL_FP32, f"batched mmt {i}")
 
 
+@pytest.mark.parametrize("stride", [1, 2])
+def test_channelwise_convolution_large_images(ops, oracle, stride):
+    """Depthwise 3x3 on images large enough for the TMA-staged kernel (tiles of 32 channels; here 144 channels leave a
+    half-filled last tile, 57 x 45 pixels leave ragged tiles on both axes) and for the row-block kernel."""
+    for i, (n, h, w, c) in enumerate([(16, 57, 45, 144), (40, 30, 29, 64), (3, 120, 130, 32)]):
+        x, f, b = cases.uniform(600 + i, (n, h, w, c)), cases.uniform(610 + i, (3, 3, c)), cases.uniform(620 + i, (c,))
+        want = oracle.blob_channelwise_convolution(x, f, b, padding=(1, 1), stride=(stride, stride))
+        for act, param, post in [(ops.ACT_NONE, 0.0, lambda v: v), (ops.ACT_RELU, 6.0, lambda v: np.clip(v, 0, 6)),
+                                 (ops.ACT_HSWISH, 0.0, lambda v: v * np.clip(v + 3, 0, 6) / 6)]:
+            got = ops.BlobChannelwiseConvolution(dev(x * 4), dev(f), dev(b), padding=(1, 1), stride=(stride, stride),
+                                                 act=act, act_param=param)
+            want4 = oracle.blob_channelwise_convolution(x * 4, f, b, padding=(1, 1), stride=(stride, stride))
+            check(host(got), post(want4.astype(np.float64)).astype(np.float32), TOL_FP32, f"depthwise {i} stride {stride} act {act}")
+        assert want.shape == host(got).shape
+
+
 def test_vectorised_helper_variants(ops, oracle):
     """The 16-byte forms of row sums, the channel-vector transpose and the strip max-pool against the oracle."""
     for (bsz, h, w) in [(3, 49, 2048), (1, 700, 260), (2, 5, 4)]:     # the second splits its rows over slices
