@@ -459,6 +459,9 @@ def run_ops(args):
     scale = torch.full((1,), 0.125, device=dev)
     cases.append((f"VectorMultiply {heads}x512x512 (score scale)", lambda: ops.vector_op("MULTIPLY", scores.view(-1), scalar=scale, result=scores.view(-1)),
                   2 * scores.numel() * 4))
+    cases.append((f"scale + mask + MatrixSoftmaxByRows {heads * 512}x512 as one pass (engine fusion)",
+                  lambda: ops.MatrixSoftmaxByRowsFused(scores, heads * 512, 512, scale=scale, row_bias=mask, bias_rows=512, result=scores),
+                  2 * scores.numel() * 4 + mask.numel() * 4))
     q = rnd(tb * 512 * 12 * 64)                                      # 100 MB: four of them rotate to defeat L2
     qs = [rnd(tb * 512 * 12 * 64) for _ in range(4)]
     qt = torch.empty_like(q)

@@ -255,6 +255,16 @@ def MatrixSoftmaxByRows(matrix, height, width, result=None):
     return result
 
 
+def MatrixSoftmaxByRowsFused(matrix, height, width, scale=None, row_bias=None, bias_rows=0, result=None):
+    """softmax over the rows of (matrix * *scale + row_bias[h % bias_rows]): what the engine launches when an in-place
+    VectorMultiply by a device scalar and an in-place AddVectorToMatrixRows precede an in-place MatrixSoftmaxByRows."""
+    if result is None:
+        result = torch.empty_like(matrix)
+    capi.check("MatrixSoftmaxByRows (fused)", capi.load().nb200_matrix_softmax_by_rows_fused(
+        _stream(), _ptr(matrix), height, width, _ptr(scale), _ptr(row_bias), bias_rows, _ptr(result)))
+    return result
+
+
 def TransposeMatrix(batch, first, height, medium, width, channels, result=None):
     if result is None:
         result = torch.empty_like(first)
