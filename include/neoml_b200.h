@@ -143,6 +143,11 @@ typedef struct nb200_chconv_desc {
 } nb200_chconv_desc;
 NB200_API int nb200_blob_channelwise_convolution(void* stream, const nb200_chconv_desc* desc, const float* x,
 	const float* filter, const float* free_term, float* y, int act, float act_param);
+/* The squeeze-and-excite gate inside IDnnEngine::MobileNetV3PostSEBlock (NME.h:1078-1082; CPU
+ * CpuMathEngineDnnChannelwiseConv.cpp:216-221): y[b][pixel][c] = act(x[b][pixel][c] * scale[b][c]); the engine runs
+ * the block's 1x1 convolution on y with bias and residual in the epilogue. */
+NB200_API int nb200_scale_channels_activation(void* stream, int batch, int pixels, int channels, const float* x,
+	const float* scale, int act, float act_param, float* y);
 
 /* IDnnEngine::InitRowwiseMobileNetV2 + MobileNetV2Block (NME.h:1095-1101,1069-1071;
  * CPU CpuRowwiseMobileNetV2.h:151-295):

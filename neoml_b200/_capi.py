@@ -55,6 +55,7 @@ SIGNATURES = {
     "nb200_multiply_matrix_by_transposed_matrix": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _EP, _i]),
     "nb200_batch_multiply_matrix_by_transposed_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
     "nb200_matrix_product_scratch_floats": (C.c_size_t, [_i, _i, _i, _i, _i]),
+    "nb200_scale_channels_activation": (_i, [_vp, _i, _i, _i, _vp, _vp, _i, C.c_float, _vp]),
     "nb200_multiply_matrix_by_transposed_matrix_with_scratch": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp,
                                                                      _EP, _i]),
     "nb200_multiply_matrix_by_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),

@@ -585,6 +585,28 @@ bool chconv3x3_by_tma(const nb200_chconv_desc* d, const float* x, const float* f
 	return true;
 }
 
+// y[image][pixel][c] = act(x[image][pixel][c] * scale[image][c]): the squeeze-and-excite gate of a MobileNetV3 block
+// applied to the channelwise convolution's output, with the activation that follows it.  V = 4: 16-byte pieces.
+template<int V>
+__global__ void __launch_bounds__(256) scale_channels_act_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+	float* __restrict__ y, long long total, int channelVecs, long long imageVecs, int act, float actParam)
+{
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+		const long long image = i / imageVecs;
+		const int cv = static_cast<int>(i % channelVecs);
+		if(V == 4) {
+			float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
+			const float4 g = __ldg(reinterpret_cast<const float4*>(scale) + image * channelVecs + cv);
+			v.x = apply_act(v.x * g.x, act, actParam); v.y = apply_act(v.y * g.y, act, actParam);
+			v.z = apply_act(v.z * g.z, act, actParam); v.w = apply_act(v.w * g.w, act, actParam);
+			reinterpret_cast<float4*>(y)[i] = v;
+		} else {
+			y[i] = apply_act(__ldg(x + i) * __ldg(scale + image * channelVecs + cv), act, actParam);
+		}
+	}
+}
+
 } // namespace
 } // namespace nb200
 
@@ -620,6 +642,26 @@ int nb200_blob_resize_image(void* stream, int batch, int h, int w, int c, int de
 		resize_kernel<4><<<grid_for(outElems / 4, 256, 16), 256, 0, s>>>(p, x, y, outElems / 4);
 	} else {
 		resize_kernel<1><<<grid_for(outElems, 256, 16), 256, 0, s>>>(p, x, y, outElems);
+	}
+	count_launch();
+	return check_launch();
+}
+
+int nb200_scale_channels_activation(void* stream, int batch, int pixels, int channels, const float* x, const float* scale,
+	int act, float act_param, float* y)
+{
+	if(batch < 0 || pixels < 0 || channels < 0) return NB200_EINVAL;
+	const long long total = static_cast<long long>(batch) * pixels * channels;
+	if(total == 0) return NB200_OK;
+	if(x == nullptr || scale == nullptr || y == nullptr) return NB200_EINVAL;
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	cudaStream_t s = as_stream(stream);
+	if(channels % 4 == 0 && aligned16(x) && aligned16(y) && aligned16(scale)) {
+		scale_channels_act_kernel<4><<<grid_for(total / 4, 256, 16), 256, 0, s>>>(x, scale, y, total / 4, channels / 4,
+			static_cast<long long>(pixels) * (channels / 4), act, act_param);
+	} else {
+		scale_channels_act_kernel<1><<<grid_for(total, 256, 16), 256, 0, s>>>(x, scale, y, total, channels,
+			static_cast<long long>(pixels) * channels, act, act_param);
 	}
 	count_launch();
 	return check_launch();

@@ -75,6 +75,11 @@ private:
 	size_t current = 0, peak = 0, pooled = 0, reserved = 0;
 };
 
+// Descriptor of a channelwise convolution: a plain copy of the geometry, owned by the caller (NeoMathEngine.h:723,750)
+struct CB200ChannelwiseDesc : public CChannelwiseConvolutionDesc {
+	nb200_chconv_desc d;
+};
+
 class CB200MathEngine : public IMathEngine {
 public:
 	CB200MathEngine( int device, size_t memoryLimit, int flags );

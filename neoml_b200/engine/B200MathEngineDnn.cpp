@@ -29,9 +29,6 @@ bool activationOf( TActivationFunction f, int& act )
 struct CB200ConvolutionDesc : public CConvolutionDesc {
 	nb200_conv_desc d;
 };
-struct CB200ChannelwiseDesc : public CChannelwiseConvolutionDesc {
-	nb200_chconv_desc d;
-};
 struct CB200PoolingGeometry {
 	int batch, h, w, c, fh, fw, sh, sw;
 };

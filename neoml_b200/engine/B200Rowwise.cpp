@@ -429,6 +429,86 @@ void CB200MathEngine::MobileNetV2Block( const CBlobDesc& inputDesc, const CBlobD
 	op->RunOn( *this, inputDesc, raw( inputHandle ), raw( outputHandle ) );
 }
 
+// MobileNetV3 block up to its squeeze-and-excite branch (NeoMathEngine.h:1072-1077; CPU
+// CpuMathEngineDnnChannelwiseConv.cpp:76-185): output = act2( channelwise( act1( input * expandFilter^T + bias ) ) ).
+// The expanded image lives in pool memory; both activations ride in the kernels that produce their inputs.
+void CB200MathEngine::MobileNetV3PreSEBlock( const CBlobDesc& inputDesc, const CBlobDesc&,
+	const CChannelwiseConvolutionDesc& convDesc, const CConstFloatHandle& inputHandle,
+	const CConstFloatHandle& expandFilter, const CConstFloatHandle* expandFreeTerm,
+	TActivationFunction expandActivation, float expandReluParam, const CConstFloatHandle& channelwiseFilter,
+	const CConstFloatHandle* channelwiseFreeTerm, TActivationFunction channelwiseActivation,
+	float channelwiseReluParam, const CFloatHandle& outputHandle )
+{
+	const nb200_chconv_desc& d = static_cast<const CB200ChannelwiseDesc&>( convDesc ).d;
+	CTail expandTail, channelwiseTail;
+	if( !tailOf( expandActivation, expandReluParam, expandTail )
+		|| !tailOf( channelwiseActivation, channelwiseReluParam, channelwiseTail ) ) {
+		notImplemented( "MobileNetV3PreSEBlock (activation other than linear, ReLU, HSwish)" );
+		return;
+	}
+	enter();
+	const int rows = inputDesc.ObjectCount() * inputDesc.Height() * inputDesc.Width();
+	const int inputChannels = imageChannels( inputDesc );
+	if( inputDesc.Height() != d.h || inputDesc.Width() != d.w || inputDesc.ObjectCount() != d.batch ) {
+		raise( "MobileNetV3PreSEBlock: the convolution descriptor does not fit the input" );
+		return;
+	}
+	float* expanded = WorkAlloc( static_cast<size_t>( rows ) * d.c );
+	const size_t scratchFloats = nb200_matrix_product_scratch_floats( 1, rows, d.c, inputChannels, inputChannels );
+	float* scratch = scratchFloats > 0 ? WorkAlloc( scratchFloats ) : nullptr;
+	nb200_epilogue epi = {};
+	epi.bias = expandFreeTerm != nullptr ? raw( *expandFreeTerm ) : nullptr;
+	epi.act = expandTail.act;
+	epi.act_param = expandTail.param;
+	int rc = nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, 1, raw( inputHandle ), rows, inputChannels,
+		inputChannels, raw( expandFilter ), d.c, inputChannels, expanded, d.c, scratch, &epi, precision );
+	if( rc == 0 ) {
+		rc = nb200_blob_channelwise_convolution( stream, &d, expanded, raw( channelwiseFilter ),
+			channelwiseFreeTerm != nullptr ? raw( *channelwiseFreeTerm ) : nullptr, raw( outputHandle ), channelwiseTail.act,
+			channelwiseTail.param );
+	}
+	if( scratch != nullptr ) WorkFree( scratch );
+	WorkFree( expanded );
+	check( rc, "MobileNetV3PreSEBlock" );
+}
+
+// MobileNetV3 block after its squeeze-and-excite branch (NeoMathEngine.h:1078-1082; CPU
+// CpuMathEngineDnnChannelwiseConv.cpp:187-258): output = act( input * se[image][channel] ) * downFilter^T + bias
+// (+ residual).  One pass scales and activates into pool memory, the 1x1 convolution adds bias and residual in its
+// epilogue.
+void CB200MathEngine::MobileNetV3PostSEBlock( const CBlobDesc& channelwiseOutputDesc, int outputChannels,
+	const CConstFloatHandle& channelwiseOutputHandle, const CConstFloatHandle& squeezeAndExciteHandle,
+	const CConstFloatHandle* residualHandle, TActivationFunction activation, float reluParam,
+	const CConstFloatHandle& downFilterHandle, const CConstFloatHandle* downFreeTermHandle,
+	const CFloatHandle& outputHandle )
+{
+	CTail tail;
+	if( !tailOf( activation, reluParam, tail ) ) {
+		notImplemented( "MobileNetV3PostSEBlock (activation other than linear, ReLU, HSwish)" );
+		return;
+	}
+	enter();
+	const int batch = channelwiseOutputDesc.ObjectCount();
+	const int pixels = channelwiseOutputDesc.Height() * channelwiseOutputDesc.Width();
+	const int channels = imageChannels( channelwiseOutputDesc );
+	const int rows = batch * pixels;
+	float* scaled = WorkAlloc( static_cast<size_t>( rows ) * channels );
+	int rc = nb200_scale_channels_activation( stream, batch, pixels, channels, raw( channelwiseOutputHandle ),
+		raw( squeezeAndExciteHandle ), tail.act, tail.param, scaled );
+	if( rc == 0 ) {
+		const size_t scratchFloats = nb200_matrix_product_scratch_floats( 1, rows, outputChannels, channels, channels );
+		float* scratch = scratchFloats > 0 ? WorkAlloc( scratchFloats ) : nullptr;
+		nb200_epilogue epi = {};
+		epi.bias = downFreeTermHandle != nullptr ? raw( *downFreeTermHandle ) : nullptr;
+		if( residualHandle != nullptr ) { epi.residual = raw( *residualHandle ); epi.ld_residual = outputChannels; }
+		rc = nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, 1, scaled, rows, channels, channels,
+			raw( downFilterHandle ), outputChannels, channels, raw( outputHandle ), outputChannels, scratch, &epi, precision );
+		if( scratch != nullptr ) WorkFree( scratch );
+	}
+	WorkFree( scaled );
+	check( rc, "MobileNetV3PostSEBlock" );
+}
+
 void CB200MathEngine::ChannelwiseWith1x1( const CBlobDesc& inputDesc, const CBlobDesc&, const CRowwiseOperationDesc& rowwiseDesc,
 	const CChannelwiseConvolutionDesc&, const CConstFloatHandle& inputHandle, const CFloatHandle& outputHandle )
 {

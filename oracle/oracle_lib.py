@@ -360,6 +360,23 @@ class Reference:
         self._chk(self.lib.ref_rowwise_chain(self.engine, n, h, w, c, k, cexp, kout, *args, _opt(y), dims))
         return y
 
+    def mobilenetv3_block(self, x, w_exp, b_exp, w_dw, b_dw, se, w_down, b_down, stride=1, residual=False,
+                          acts=((2, 0.0), (2, 0.0), (0, 0.0))):
+        """MobileNetV3PreSEBlock + MobileNetV3PostSEBlock around the given squeeze-and-excite vector `se`
+        [batch, expanded channels]; acts = (expand, channelwise, post-gate) as (0 linear | 1 ReLU | 2 HSwish, param).
+        Returns (channelwise output, block output)."""
+        n, h, w, c = x.shape
+        cexp, kout, r = w_exp.shape[0], w_down.shape[0], w_dw.shape[0]
+        pad = r // 2
+        ho, wo = out_size(h, r, pad, stride), out_size(w, r, pad, stride)
+        mid, y = self._zeros((n, ho, wo, cexp), np.float32), self._zeros((n, ho, wo, kout), np.float32)
+        (a1, p1), (a2, p2), (a3, p3) = acts
+        self.lib.ref_mobilenetv3_block.argtypes = [C.c_void_p] + [_i] * 9 + [_i, C.c_float] * 3 + [C.c_void_p] * 10
+        self._chk(self.lib.ref_mobilenetv3_block(self.engine, n, h, w, c, cexp, kout, r, stride, int(residual), a1, p1, a2,
+                                                 p2, a3, p3, _opt(x), _opt(w_exp), _opt(b_exp), _opt(w_dw), _opt(b_dw),
+                                                 _opt(se), _opt(w_down), _opt(b_down), _opt(mid), _opt(y)))
+        return mid, y
+
     # ---- engine-level calls (memory, exchange, identity), the same for any IMathEngine behind the shim
     def roundtrip(self, x: np.ndarray):
         """Engine-owned memory + typed exchange + stack variables: returns (2*x+1 computed on the engine, gauges) with

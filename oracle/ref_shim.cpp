@@ -390,4 +390,28 @@ int ref_rowwise_chain( void* eng, int batch, int h, int w, int c, int k, int cex
 	SHIM_CATCH
 }
 
+// A MobileNetV3 block around a given squeeze-and-excite vector, as CMobileNetV3PreSEBlockLayer / PostSEBlockLayer call
+// the engine (NeoMathEngine.h:1072-1082): expand 1x1 (c -> cexp) + act1, channelwise r x r (stride, padding r / 2) +
+// act2 -> mid; then mid * se[image][channel] -> act3 -> down 1x1 (cexp -> kout) + bias (+ x when residual).
+// Activations: 0 linear, 1 ReLU(param), 2 HSwish.  y must hold batch x ho x wo x kout floats.
+int ref_mobilenetv3_block( void* eng, int batch, int h, int w, int c, int cexp, int kout, int r, int stride, int residual,
+	int act1, float p1, int act2, float p2, int act3, float p3, const float* x, const float* wExp, const float* bExp,
+	const float* wDw, const float* bDw, const float* se, const float* wDown, const float* bDown, float* mid, float* y )
+{
+	SHIM_TRY
+	IMathEngine* e = static_cast<IMathEngine*>( eng );
+	const int pad = r / 2;
+	const int ho = 1 + ( h - r + 2 * pad ) / stride, wo = 1 + ( w - r + 2 * pad ) / stride;
+	CBlobDesc in = image_desc( batch, h, w, c ), expanded = image_desc( batch, h, w, cexp ), out = image_desc( batch, ho, wo, cexp );
+	CBlobDesc flt = image_desc( 1, r, r, cexp ), ftDesc = image_desc( 1, 1, 1, cexp );
+	std::unique_ptr<CChannelwiseConvolutionDesc> desc( e->InitBlobChannelwiseConvolution( expanded, pad, pad, stride, stride,
+		flt, bDw != nullptr ? &ftDesc : nullptr, out ) );
+	CConstFloatHandle hBExp = cfh( e, bExp ), hBDw = cfh( e, bDw ), hBDown = cfh( e, bDown ), hRes = cfh( e, x );
+	e->MobileNetV3PreSEBlock( in, out, *desc, cfh( e, x ), cfh( e, wExp ), bExp != nullptr ? &hBExp : nullptr, act_of( act1 ), p1,
+		cfh( e, wDw ), bDw != nullptr ? &hBDw : nullptr, act_of( act2 ), p2, fh( e, mid ) );
+	e->MobileNetV3PostSEBlock( out, kout, cfh( e, mid ), cfh( e, se ), residual ? &hRes : nullptr, act_of( act3 ), p3,
+		cfh( e, wDown ), bDown != nullptr ? &hBDown : nullptr, fh( e, y ) );
+	SHIM_CATCH
+}
+
 } // extern "C"

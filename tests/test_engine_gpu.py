@@ -258,6 +258,35 @@ def test_rowwise_chain_matches_the_reference_cpu_engine(engine, reference):
     assert launches == 12
 
 
+@pytest.mark.parametrize("r,stride,residual,acts", [
+    (3, 1, True, ((1, 6.0), (1, 6.0), (0, 0.0))),        # ReLU6 block with residual
+    (5, 2, False, ((2, 0.0), (2, 0.0), (2, 0.0))),       # 5x5 / stride 2, HSwish everywhere
+    (5, 1, True, ((2, 0.0), (1, 0.0), (1, 4.0))),
+])
+def test_mobilenetv3_block_matches_the_reference_cpu_engine(engine, reference, r, stride, residual, acts):
+    """MobileNetV3PreSEBlock + MobileNetV3PostSEBlock (expand 1x1, channelwise r x r, squeeze-and-excite gate, down
+    1x1, residual) on both engines through the same IMathEngine calls."""
+    n, h, w, c, cexp = 3, 13, 11, 24, 72
+    kout = c if residual else 40
+    rng = np.random.default_rng(900 + r + stride)
+    x = rng.uniform(-1, 1, (n, h, w, c)).astype(np.float32)
+    w_exp = (rng.standard_normal((cexp, c)) * np.sqrt(2.0 / c)).astype(np.float32)
+    w_dw = (rng.standard_normal((r, r, cexp)) * np.sqrt(2.0 / (r * r))).astype(np.float32)
+    w_down = (rng.standard_normal((kout, cexp)) * np.sqrt(2.0 / cexp)).astype(np.float32)
+    b_exp, b_dw = rng.uniform(-0.1, 0.1, cexp).astype(np.float32), rng.uniform(-0.1, 0.1, cexp).astype(np.float32)
+    b_down = rng.uniform(-0.1, 0.1, kout).astype(np.float32)
+    se = rng.uniform(0, 1, (n, cexp)).astype(np.float32)       # what the block's pooled + FC + hard-sigmoid branch yields
+    args = (x, w_exp, b_exp, w_dw, b_dw, se, w_down, b_down)
+    want_mid, want = reference.mobilenetv3_block(*args, stride=stride, residual=residual, acts=acts)
+    held = [dev(a) for a in args]
+    engine.sync()
+    got_mid, got = engine.mobilenetv3_block(*held, stride=stride, residual=residual, acts=acts)
+    got_mid, got = host(engine, got_mid), host(engine, got)
+    assert got.shape == want.shape and got_mid.shape == want_mid.shape
+    assert gate_err(got_mid, want_mid) < TOL_FP32
+    assert gate_err(got, want) < TOL_FP32
+
+
 def test_two_engines_on_two_host_threads(golden):
     """One engine per host thread, as NeoML's replica drivers run them: both issue convolutions and products at the
     same time on their own streams; every result is still the golden one (no shared per-call state in the library)."""
