@@ -90,6 +90,7 @@ constexpr long long SPLIT_TILES_MAX = 74;
 // Rows of the first operand from which preparing the second one pays (8 row tiles: every prepared tile is then used
 // eight times).  Attention's per-head products (512 rows, measured) are faster with the conversion left in the kernel.
 constexpr int PREPARE_B_MIN_ROWS = 1024;
+static const long long g_prepareMinRows = getenv("NB200_PREP_MIN") ? atoll(getenv("NB200_PREP_MIN")) : 0;
 constexpr size_t SPLIT_SCRATCH_FLOATS = static_cast<size_t>(148) * 128 * 128;
 
 size_t split_scratch_floats(long long outRows, long long n, long long kk)
@@ -418,14 +419,19 @@ int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, con
 	const bool tmaShape = aligned16(x) && aligned16(filter) && (pointwise ? d->c % 4 == 0 : d->c % 32 == 0) && kk % 4 == 0;
 	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && tmaShape && outRows > 0) {
 		float* prepared = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
-		const long long n = static_cast<long long>(d->k) * kk;
-		launch_dependent(overlap_launches(), prepare_filter_kernel, dim3(grid_for(n, 256, 8)), dim3(256), 0, as_stream(stream),
-			filter, prepared, n, precision == NB200_PREC_3XTF32 ? 0 : 1);
-		count_launch(1);
-		const int rc = check_launch();
-		if(rc != NB200_OK) return rc;
-		if(precision == NB200_PREC_3XTF32) p.Blo = prepared; else p.B = prepared;
-		p.b_ready = 1;
+		// with few output rows (small batches) every filter tile is used by a handful of CTAs at most: the extra launch
+		// costs more than converting those tiles in the kernel
+		const bool prepare = outRows >= g_prepareMinRows;
+		if(prepare) {
+			const long long n = static_cast<long long>(d->k) * kk;
+			launch_dependent(overlap_launches(), prepare_filter_kernel, dim3(grid_for(n, 256, 8)), dim3(256), 0, as_stream(stream),
+				filter, prepared, n, precision == NB200_PREC_3XTF32 ? 0 : 1);
+			count_launch(1);
+			const int rc = check_launch();
+			if(rc != NB200_OK) return rc;
+			if(precision == NB200_PREC_3XTF32) p.Blo = prepared; else p.B = prepared;
+			p.b_ready = 1;
+		}
 		// whatever the caller's scratch holds beyond the prepared filter is room for split-K partial results
 		float* const rest = prepared + prepared_filter_floats(d->k, d->r, d->s, d->c);
 		const size_t used = static_cast<size_t>(rest - scratch);
