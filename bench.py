@@ -16,6 +16,7 @@ contraction launch in one extra, instrumented step.  `cpu_baseline` times the re
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -345,10 +346,26 @@ def run_ours(args):
         return
 
     # ---- roofline of the dominant kernel (rank 0, one instrumented step) -----------------------------------------------
+    # The library brackets every contraction launch with CUDA events on its stream (operand preparation, allocations and
+    # host gaps stay outside); the Python timer supplies the flops of each launch, in the same order.
     timer = ContractionTimer(torch)
     be_t = resnet50.EngineBackend(precision=args.precision, timer=timer)
-    resnet50.forward(be_t, weights, dev_x, fuse=fuse)
-    flops, tc_ms, tc_launches, per_layer = timer.totals()
+    timed_steps = 3
+    lib.nb200_debug_time_contractions(1)
+    for _ in range(timed_steps):
+        resnet50.forward(be_t, weights, dev_x, fuse=fuse)
+    torch.cuda.synchronize()
+    lib.nb200_debug_time_contractions(0)
+    flops, _, tc_launches, per_layer = timer.totals()
+    times = (ctypes.c_float * tc_launches)()
+    got = lib.nb200_debug_contraction_times(ctypes.cast(times, ctypes.c_void_p), tc_launches)
+    if got != tc_launches:
+        raise SystemExit(f"the library timed {got} contraction launches, the graph issued {tc_launches}")
+    flops /= timed_steps
+    tc_launches //= timed_steps
+    kernel_ms = [sum(times[i + s * tc_launches] for s in range(timed_steps)) / timed_steps for i in range(tc_launches)]
+    per_layer = [(k, f, kernel_ms[i]) for i, (k, f, _) in enumerate(per_layer[:tc_launches])]
+    tc_ms = sum(kernel_ms)
     if args.layers:
         names = [sp.name for sp in resnet50.conv_specs()]
         order = ["stem"]

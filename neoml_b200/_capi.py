@@ -52,6 +52,8 @@ SIGNATURES = {
     "nb200_last_cuda_error": (C.c_char_p, []),
     "nb200_debug_set_contraction_trace": (None, [_vp, _i, _i]),
     "nb200_launch_count": (C.c_uint64, []),
+    "nb200_debug_time_contractions": (None, [_i]),
+    "nb200_debug_contraction_times": (_i, [_vp, _i]),
     "nb200_multiply_matrix_by_transposed_matrix": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _EP, _i]),
     "nb200_batch_multiply_matrix_by_transposed_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
     "nb200_matrix_product_scratch_floats": (C.c_size_t, [_i, _i, _i, _i, _i]),

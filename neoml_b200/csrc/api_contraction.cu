@@ -202,6 +202,17 @@ void nb200_debug_set_contraction_trace(void* device_buffer, int steps, int skip_
 	set_contraction_trace(static_cast<unsigned long long*>(device_buffer), steps, skip_mask);
 }
 
+void nb200_debug_time_contractions(int enable)
+{
+	time_contractions(enable != 0);
+}
+
+int nb200_debug_contraction_times(float* ms, int capacity)
+{
+	if(ms == nullptr || capacity < 0) return NB200_EINVAL;
+	return contraction_times(ms, capacity);
+}
+
 int nb200_multiply_matrix_by_transposed_matrix(void* stream, const float* a, int m, int k, int lda,
 	const float* b, int n, int ldb, float* c, int ldc, const nb200_epilogue* epi, int precision)
 {

@@ -38,6 +38,7 @@ struct ContractionParams {
 	                  // launches: latency at small batch).  Part i stores its partial result at C + i * M * ldc, where C
 	                  // is then the caller's split scratch; a finishing pass sums the parts in order (deterministic) and
 	                  // applies bias, residual and activation.  Set by the launcher.
+	int b_resident;   // set by the launcher (short-K kernels): B stays in shared memory for all tiles of a CTA
 	float* splitScratch;          // optional room for those partial results (NULL: never split)
 	long long splitScratchFloats;
 	int b_ready;      // 1: B needs no conversion in the kernel (Blo given for 3xTF32 / B already rounded for TF32)
@@ -113,6 +114,9 @@ void set_contraction_trace(unsigned long long* buffer, int steps, int options);
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
 int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
 
+// Event timing of the contraction launches (see nb200_debug_time_contractions)
+void time_contractions(bool enable);
+int contraction_times(float* ms, int capacity);
 // false when diagnostic option 64 asks for ordinary launches instead of programmatic dependent ones
 bool overlap_launches();
 // Scratch floats of a convolution (api_contraction.cu); the room for split-K partial results comes last and is optional.

@@ -30,6 +30,7 @@ def test_every_declaration_cites_the_reference_interface():
     # each compute entry point is preceded by a comment naming the IMathEngine method and its line
     for name in _declared():
         if name in ("nb200_version", "nb200_device_count", "nb200_error_string", "nb200_device_status", "nb200_last_cuda_error", "nb200_debug_set_contraction_trace",
+                    "nb200_debug_time_contractions", "nb200_debug_contraction_times",
                     "nb200_launch_count", "nb200_mobilenetv2_scratch_floats", "nb200_blob_convolution_scratch_floats", "nb200_vector_copy_int",
                     "nb200_vector_fill_int"):
             continue
