@@ -148,8 +148,13 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 	constexpr int LO_SLOTS = lo_slots_for(BN);
 	constexpr uint32_t ACC_COLS = BN;
 	constexpr uint32_t A_STAGE_COLS = threeX ? 64 : 32;
-	constexpr int CROSS_SETS = !threeX ? 0 : (4 * ACC_COLS + LO_SLOTS * A_STAGE_COLS <= 512 ? 2 : 1);
+	// Short-K kernels add the cross products straight into the main accumulator: over at most four K blocks the
+	// truncating accumulate costs a few 1e-7 (the separate accumulator exists for the long sums), and the single cross
+	// accumulator of BN = 128 would otherwise chain every tile's first MMAs to the previous tile's fold.
+	constexpr bool MIX_CROSS = BRES;
+	constexpr int CROSS_SETS = (!threeX || MIX_CROSS) ? 0 : (4 * ACC_COLS + LO_SLOTS * A_STAGE_COLS <= 512 ? 2 : 1);
 	constexpr bool FOLD = CROSS_SETS == 1;
+	constexpr bool SEP_CROSS = CROSS_SETS > 0; // cross products in an accumulator of their own
 	constexpr uint32_t CROSS_BASE = 2 * ACC_COLS;
 	constexpr uint32_t A_BASE = CROSS_BASE + CROSS_SETS * ACC_COLS;
 	constexpr uint32_t TMEM_USED = A_BASE + LO_SLOTS * A_STAGE_COLS;
@@ -550,7 +555,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 				if(FOLD && !mbar_wait_bounded_warp(crossEmptyBar, (local & 1) ^ 1, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
 				tc_fence_after_sync();
 				const uint32_t accMain = tmemBase + set * ACC_COLS;
-				const uint32_t accCross = tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS);
+				const uint32_t accCross = SEP_CROSS ? tmemBase + CROSS_BASE + (FOLD ? 0 : set * ACC_COLS) : accMain;
 				uint32_t acc = 0u; // the first MMA of a tile overwrites the accumulators
 				const int work = blockIdx.x + local * gridDim.x;
 				const int kbBegin = (work % kSplits) * kbPer;
@@ -576,7 +581,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 							for(int ks = 0; ks < BK / 8; ++ks) {
 								const uint32_t a = ks == 0 ? acc : 1u;
 								if(threeX) umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, a);
-								umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, a);
+								umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, (threeX && !SEP_CROSS) ? 1u : a);
 								if(threeX) umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
 							}
 						} else {
@@ -584,7 +589,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 							for(int ks = 0; ks < kSteps; ++ks) {
 								const uint32_t a = ks == 0 ? acc : 1u;
 								if(threeX) umma_tf32_ts(accCross, aLo + 8 * ks, dBhi + 2 * ks, idesc, a);
-								umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, a);
+								umma_tf32_ts(accMain, aHi + 8 * ks, dBhi + 2 * ks, idesc, (threeX && !SEP_CROSS) ? 1u : a);
 								if(threeX) umma_tf32_ts(accCross, aHi + 8 * ks, dBlo + 2 * ks, idesc, 1u);
 							}
 						}
@@ -736,7 +741,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			// cycles; waited for chunk by chunk it was most of the epilogue).
 			uint32_t vm[16], vx[16];
 			tmem_ld16_issue(accMain, vm);
-			if(threeX && !FOLD) tmem_ld16_issue(accCross, vx);
+			if(SEP_CROSS && !FOLD) tmem_ld16_issue(accCross, vx);
 #pragma unroll
 			for(int g0 = 0; g0 < CHUNKS; ++g0) {
 				tmem_ld_wait();
@@ -745,11 +750,11 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 #pragma unroll
 				for(int i = 0; i < 16; ++i) {
 					v[i] = __uint_as_float(vm[i]);
-					if(threeX && !FOLD) v[i] += __uint_as_float(vx[i]);
+					if(SEP_CROSS && !FOLD) v[i] += __uint_as_float(vx[i]);
 				}
 				if(g0 + 1 < CHUNKS) {
 					tmem_ld16_issue(accMain + (g0 + 1) * 16, vm);
-					if(threeX && !FOLD) tmem_ld16_issue(accCross + (g0 + 1) * 16, vx);
+					if(SEP_CROSS && !FOLD) tmem_ld16_issue(accCross + (g0 + 1) * 16, vx);
 				}
 				if(g0 + 1 >= CHUNKS) {
 					// last TMEM read of this tile: hand the accumulator set back to the MMA warp
@@ -1137,19 +1142,19 @@ int launch_bn(const ContractionParams& p0, int batch, cudaStream_t stream)
 	// (-7 %) and loses from eight on.
 	bool shortK = false;
 	p.b_resident = 0;
-	if(!gather && kSplits == 1 && batch == 1 && numKb <= 4 && p.a_mode != A_CONV_WINDOW && !(g_traceOptions & 128)) {
+	if(!gather && kSplits == 1 && numKb <= 4 && p.a_mode != A_CONV_WINDOW && !(g_traceOptions & 128)) {
 		const int resRing = p.residual != nullptr && p.c_vec ? MAX_EPI_WARPS * RES_DEPTH * STAGING_BYTES_PER_WARP : 0;
 		const int residentBytes = numKb * bStepBytes;
 		const int room = 227 * 1024 - fixedBytes - resRing - residentBytes;
 		const int gridRes = static_cast<int>((sms / nTiles) * nTiles);
-		if(preB && numKb <= 2 && room >= 4 * A_TILE_BYTES && nTiles <= sms && gridRes * 10 >= sms * 9 && numTiles >= 4LL * gridRes) {
+		if(preB && batch == 1 && numKb <= 2 && room >= 4 * A_TILE_BYTES && nTiles <= sms && gridRes * 10 >= sms * 9 && numTiles >= 4LL * gridRes) {
 			shortK = true;
 			p.b_resident = 1;
 			grid = gridRes;
 			slotBytes = A_TILE_BYTES;
 			fixedBytes += resRing + residentBytes;
 			rawSlots = room / A_TILE_BYTES;
-		} else if(resRing > 0 && (227 * 1024 - fixedBytes - resRing) / slotBytes >= 2) {
+		} else if((227 * 1024 - fixedBytes - resRing) / slotBytes >= 2) {
 			shortK = true;
 			fixedBytes += resRing;
 			rawSlots = (227 * 1024 - fixedBytes) / slotBytes;
