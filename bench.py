@@ -50,6 +50,9 @@ def parse_args():
                          "115 launches per pass)")
     ap.add_argument("--ops", action="store_true",
                     help="instead of the network: time the bandwidth-bound kernels at the configs' sizes (one JSON line each)")
+    ap.add_argument("--products", action="store_true",
+                    help="time the dense contractions of the other configs (config 1 convolution, config 2 MobileNetV2 "
+                         "block, config 4 FC and attention products, config 5 matrix products) against the tensor roofline")
     ap.add_argument("--kernel-options", type=int, default=0,
                     help="diagnostic switches of the contraction launcher (16 gather kernel, 32 no split K, 64 no "
                          "programmatic dependent launch); for A/B timing only")
@@ -511,10 +514,69 @@ def run_ops(args):
                                        "frac": round(gbs / peak, 3), "peak_source": peak_src}}))
 
 
+def run_products(args):
+    """The dense contractions of configs 1, 2, 4 and 5 at full size: algorithmic flops (2*M*N*K, counted once) over the
+    CUDA-event time of the public call (operand preparation and scratch allocation included), against the tensor peak
+    of this arithmetic (measured sustained bf16 / 2 for TF32 / 3 MMAs per product for 3xTF32)."""
+    import torch
+    from neoml_b200 import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --products needs a CUDA device: the product path has no CPU fallback")
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["bf16_tflops_sustained"]) if peaks_path.exists() else 1390.7
+    eff = peak / 2 / (3 if args.precision == 0 else 1)
+    dev, prec = "cuda", args.precision
+    rnd = lambda *shape: torch.rand(*shape, device=dev) - 0.5
+    cases = []
+    # config 1: one 3x3 convolution, 32x56x56x64 -> 64
+    x1, f1, b1 = rnd(32, 56, 56, 64), rnd(64, 3, 3, 64), rnd(64)
+    cases.append(("cfg1 BlobConvolution 32x56x56x64, 3x3 -> 64", 2.0 * 32 * 56 * 56 * 64 * 576,
+                  lambda: ops.BlobConvolution(x1, f1, b1, padding=(1, 1), precision=prec)))
+    # config 2: MobileNetV2 block 64x56x56x32, expand 192, ReLU6 twice, residual
+    x2, we, wd, wo = torch.rand(64, 56, 56, 32, device=dev), rnd(192, 32), rnd(3, 3, 192), rnd(32, 192) * 0.2
+    be, bd, bo = rnd(192) * 0.2, rnd(192) * 0.2, rnd(32) * 0.2
+    cases.append(("cfg2 MobileNetV2Block 64x56x56x32 (expand 192)", 5.63e9,
+                  lambda: ops.MobileNetV2Block(x2, we, be, wd, bd, wo, bo, stride=1, residual=True)))
+    # config 4: the FC products of an encoder layer (32768 tokens) and the per-head attention products
+    for m, k, n in [(32768, 768, 768), (32768, 768, 3072), (32768, 3072, 768)]:
+        a, b = rnd(m, k), rnd(n, k)
+        cases.append((f"cfg4 MultiplyMatrixByTransposedMatrix {m}x{k} * ({n}x{k})^T", 2.0 * m * k * n,
+                      lambda a=a, b=b: ops.MultiplyMatrixByTransposedMatrix(a, b, precision=prec)))
+    q, kk, sc = rnd(768, 512, 64), rnd(768, 512, 64), torch.empty(768, 512, 512, device=dev)
+    cases.append(("cfg4 QK^T: batch 768, 512x64 * (512x64)^T", 2.0 * 768 * 512 * 512 * 64,
+                  lambda: ops.BatchMultiplyMatrixByTransposedMatrix(q, kk, result=sc, precision=prec)))
+    pr, v, ctx = torch.rand(768, 512, 512, device=dev), rnd(768, 512, 64), torch.empty(768, 512, 64, device=dev)
+    cases.append(("cfg4 PV: batch 768, MultiplyMatrixByMatrix 512x512 * 512x64", 2.0 * 768 * 512 * 512 * 64,
+                  lambda: ops.MultiplyMatrixByMatrix(pr, v, result=ctx, precision=prec)))
+    # config 5: square MultiplyMatrixByMatrix
+    for size in (1024, 4096, 8192):
+        a, b, c = rnd(1, size, size), rnd(1, size, size), torch.empty(1, size, size, device=dev)
+        cases.append((f"cfg5 MultiplyMatrixByMatrix {size}^3", 2.0 * size ** 3,
+                      lambda a=a, b=b, c=c: ops.MultiplyMatrixByMatrix(a, b, result=c, precision=prec)))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, flops, fn in cases:
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+        tf = flops / ms / 1e9
+        print(json.dumps({"op": name, "ms": round(ms, 4), "algorithmic_gflop": round(flops / 1e9, 2),
+                          "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s",
+                                       "frac": round(tf / peak, 4), "effective_peak_for_this_arithmetic": round(eff, 1),
+                                       "frac_of_effective_peak": round(tf / eff, 3)}}))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.products:
+        run_products(args)
     elif args.ops:
         run_ops(args)
     else:

@@ -315,6 +315,37 @@ __global__ void __launch_bounds__(256) transpose_tile_kernel(const uint32_t* __r
 	}
 }
 
+// The same for height and width both a multiple of four and 16-byte-aligned matrices: 64 x 64 tiles moved with
+// 16-byte loads and stores (four rows x four columns per thread and direction), 16 KB in flight per block instead
+// of 4 KB.  The tile is padded to 65 words per row so that the column-wise reads of the store pass hit 32 banks.
+__global__ void __launch_bounds__(256) transpose_tile64_kernel(const uint32_t* __restrict__ x, uint32_t* __restrict__ y,
+	int height, int width)
+{
+	__shared__ uint32_t tile[64][65];
+	const size_t base = static_cast<size_t>(blockIdx.z) * height * width;
+	const int w0 = blockIdx.x * 64, h0 = blockIdx.y * 64;
+	const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4; // 16 x 16 threads
+#pragma unroll
+	for(int i = 0; i < 4; ++i) {
+		const int r = ty + 16 * i;
+		const int h = h0 + r, w = w0 + 4 * tx;
+		if(h < height && w < width) {
+			const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + base + static_cast<size_t>(h) * width + w));
+			tile[r][4 * tx] = v.x; tile[r][4 * tx + 1] = v.y; tile[r][4 * tx + 2] = v.z; tile[r][4 * tx + 3] = v.w;
+		}
+	}
+	__syncthreads();
+#pragma unroll
+	for(int i = 0; i < 4; ++i) {
+		const int c = ty + 16 * i;           // column of the source tile = row of the result
+		const int w = w0 + c, h = h0 + 4 * tx;
+		if(w < width && h < height) {
+			const uint4 v = make_uint4(tile[4 * tx][c], tile[4 * tx + 1][c], tile[4 * tx + 2][c], tile[4 * tx + 3][c]);
+			*reinterpret_cast<uint4*>(y + base + static_cast<size_t>(w) * height + h) = v;
+		}
+	}
+}
+
 // Row arg-max: one warp per row, first maximum wins.
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int height, int width,
 	float* __restrict__ maxValues, int* __restrict__ maxIndices)
@@ -520,8 +551,13 @@ int nb200_transpose_matrix(void* stream, int batch, const void* x, int height, i
 	const uint32_t* src = static_cast<const uint32_t*>(x);
 	uint32_t* dst = static_cast<uint32_t*>(y);
 	if(channels == 1 && medium == 1 && height > 1 && width > 1 && batch <= 65535 && (height + 31) / 32 <= 65535) {
-		dim3 grid((width + 31) / 32, (height + 31) / 32, batch);
-		transpose_tile_kernel<<<grid, 256, 0, s>>>(src, dst, height, width);
+		if(height % 4 == 0 && width % 4 == 0 && aligned16(x) && aligned16(y)) {
+			dim3 grid((width + 63) / 64, (height + 63) / 64, batch);
+			transpose_tile64_kernel<<<grid, 256, 0, s>>>(src, dst, height, width);
+		} else {
+			dim3 grid((width + 31) / 32, (height + 31) / 32, batch);
+			transpose_tile_kernel<<<grid, 256, 0, s>>>(src, dst, height, width);
+		}
 	} else if(channels % 4 == 0 && total / 4 < 0x7fffffffLL && aligned16(x) && aligned16(y)) {
 		transpose_rows_vec_kernel<<<grid_for(total / 4, 256, 16), 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y),
 			height, medium, width, channels / 4, static_cast<unsigned>(total / 4));
