@@ -34,6 +34,9 @@ UNIT = "images/s"
 IMAGE = (224, 224, 3)
 
 
+SETTLE_STEPS = 12   # untimed steps ahead of the warm-up steps (see run_ours)
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -50,6 +53,8 @@ def parse_args():
                          "115 launches per pass)")
     ap.add_argument("--ops", action="store_true",
                     help="instead of the network: time the bandwidth-bound kernels at the configs' sizes (one JSON line each)")
+    ap.add_argument("--settle", type=int, default=SETTLE_STEPS,
+                    help="untimed steps ahead of the warm-up steps (clocks and power settle on a fresh box); 0 for profiler captures")
     ap.add_argument("--products", action="store_true",
                     help="time the dense contractions of the other configs (config 1 convolution, config 2 MobileNetV2 "
                          "block, config 4 FC and attention products, config 5 matrix products) against the tensor roofline")
@@ -283,6 +288,10 @@ def run_ours(args):
     # ---- device-resident timing -------------------------------------------------------------------------
     sampler = ClockSampler(local)
     sampler.start()
+    # A fresh box needs a moment under load before clocks and power settle (a first timed loop right after three
+    # warm-up steps has measured 15 % slow): a fixed number of extra untimed steps precedes the W warm-up steps.
+    for _ in range(max(args.settle, 0)):
+        step(dev_x)
     for _ in range(max(args.warmup, 3)):
         step(dev_x)
     barrier()
@@ -355,6 +364,10 @@ def run_ours(args):
     be_t = resnet50.EngineBackend(precision=args.precision, timer=timer)
     timed_steps = 3
     lib.nb200_debug_time_contractions(1)
+    resnet50.forward(be_t, weights, dev_x, fuse=fuse)     # creates the library's events; not counted
+    torch.cuda.synchronize()
+    timer.records.clear()
+    lib.nb200_debug_time_contractions(1)                   # clears the list
     for _ in range(timed_steps):
         resnet50.forward(be_t, weights, dev_x, fuse=fuse)
     torch.cuda.synchronize()
@@ -414,7 +427,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": "resnet50_v1.5_infer_b256_224x224x3" if batch == 256 else f"resnet50_v1.5_infer_b{batch}",
                    "per_gpu_batch": batch, "global_batch": batch * world, "parallelism": f"batch-sharded x{world}",
-                   "fused_epilogues": fuse, "cuda_graph": bool(args.graph), "l2": "inputs and activations larger than L2 (154 MB batch, 822 MB stem output)"},
+                   "fused_epilogues": fuse, "cuda_graph": bool(args.graph), "settle_steps_before_warmup": max(args.settle, 0), "l2": "inputs and activations larger than L2 (154 MB batch, 822 MB stem output)"},
         "clocks": clocks,
         "e2e": {"value": round(images / (e2e_ms * 1e-3), 2), "unit": UNIT,
                 "h2d_bytes_per_step": host_x.numel() * 4, "d2h_bytes_per_step": host_idx.numel() * 4 + host_probs.numel() * 4,
