@@ -213,7 +213,9 @@ def test_matrix_helpers(ops, oracle):
 
 
 def test_transpose(ops, oracle):
-    for (b, h, m, w, c) in [(2, 3, 4, 5, 6), (2, 48, 1, 12, 64), (3, 50, 1, 70, 1), (1, 1, 1, 9, 4), (2, 33, 1, 1, 5)]:
+    # the last four are plain matrices with both extents a multiple of four: the 64 x 64-tile kernel, ragged tiles included
+    for (b, h, m, w, c) in [(2, 3, 4, 5, 6), (2, 48, 1, 12, 64), (3, 50, 1, 70, 1), (1, 1, 1, 9, 4), (2, 33, 1, 1, 5),
+                            (3, 100, 1, 36, 1), (2, 68, 1, 132, 1), (1, 256, 1, 512, 1), (5, 64, 1, 4, 1)]:
         t = cases.uniform(26, (b * h * m * w * c,))
         assert np.array_equal(host(ops.TransposeMatrix(b, dev(t), h, m, w, c)), oracle.transpose_matrix(b, t, h, m, w, c))
 
@@ -444,6 +446,44 @@ def test_channelwise_convolution_large_images(ops, oracle, stride):
             want4 = oracle.blob_channelwise_convolution(x * 4, f, b, padding=(1, 1), stride=(stride, stride))
             check(host(got), post(want4.astype(np.float64)).astype(np.float32), TOL_FP32, f"depthwise {i} stride {stride} act {act}")
         assert want.shape == host(got).shape
+
+
+def test_short_k_kernels_and_launch_timing(ops, oracle):
+    """Contractions of at most four K blocks run on the short-K kernels (cross products added into the main
+    accumulator, residual through a shared-memory ring, B resident for one or two K blocks); diagnostic option 128
+    sends the same call to the general kernels.  Both must hold the fp32 bar, and differ only in the last bits.  The
+    library's launch timing reports one duration per contraction launch."""
+    from neoml_b200 import _capi
+    import ctypes
+    lib = _capi.load()
+    shapes = [((6, 40, 40, 64), 256, True),      # K = 64: resident B, 2 column tiles, residual
+              ((5, 28, 28, 128), 512, True),     # K = 128: ring without residency
+              ((6, 40, 40, 32), 192, False),     # one K block, N = 192 (96-wide tiles)
+              ((3, 17, 19, 96), 40, True)]       # ragged rows and columns
+    lib.nb200_debug_time_contractions(1)
+    launches = 0
+    for i, (xs, k, with_res) in enumerate(shapes):
+        x, f, b = cases.uniform(700 + i, xs), cases.uniform(710 + i, (k, 1, 1, xs[3])) * 0.3, cases.uniform(720 + i, (k,))
+        want = oracle.blob_convolution(x, f, b)
+        res = cases.uniform(730 + i, want.shape) if with_res else None
+        ref = np.maximum(want + (res if with_res else 0), 0)
+        dx, df, db, dres = dev(x), dev(f), dev(b), dev(res) if with_res else None
+        short = ops.BlobConvolution(dx, df, db, residual=dres, act=ops.ACT_RELU)
+        lib.nb200_debug_set_contraction_trace(None, 0, 128)
+        try:
+            general = ops.BlobConvolution(dx, df, db, residual=dres, act=ops.ACT_RELU)
+            torch.cuda.synchronize()
+        finally:
+            lib.nb200_debug_set_contraction_trace(None, 0, 0)
+        launches += 2
+        check(host(short), ref, TOL_FP32, f"short-K {i}")
+        check(host(general), ref, TOL_FP32, f"general {i}")
+        check(host(short), host(general), 2e-5, f"short-K vs general {i}")
+    lib.nb200_debug_time_contractions(0)
+    times = (ctypes.c_float * 64)()
+    n = lib.nb200_debug_contraction_times(ctypes.cast(times, ctypes.c_void_p), 64)
+    assert n == launches
+    assert all(0.0 < times[i] < 50.0 for i in range(n))      # milliseconds
 
 
 def test_vectorised_helper_variants(ops, oracle):
