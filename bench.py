@@ -504,6 +504,17 @@ def run_ops(args):
         rot["i"] = (rot["i"] + 1) % 4
         return ops.TransposeMatrix(tb, qs[rot["i"]], 512, 1, 12, 64, result=qt)
     cases.append((f"TransposeMatrix [{tb},512,12,64] -> [{tb},12,512,64]", transpose, 2 * q.numel() * 4))
+    side = 8192 * n // 256 if n >= 64 else 2048                       # 268 MB at the full size
+    big, big_t = rnd(side, side), torch.empty(side, side, device=dev)
+    cases.append((f"TransposeMatrix {side}x{side} (the transposing pass of MultiplyMatrixByMatrix)",
+                  lambda: ops.TransposeMatrix(1, big, side, 1, side, 1, result=big_t), 2 * big.numel() * 4))
+    vals = [rnd(12 * tb, 512, 64) for _ in range(4)]                  # 100 MB each: four rotate to defeat L2
+    val_t = torch.empty(12 * tb, 64, 512, device=dev)
+
+    def transpose_values():
+        rot["i"] = (rot["i"] + 1) % 4
+        return ops.TransposeMatrix(12 * tb, vals[rot["i"]], 512, 1, 64, 1, result=val_t)
+    cases.append((f"TransposeMatrix {12 * tb} x [512,64] -> [64,512] (attention values)", transpose_values, 2 * val_t.numel() * 4))
     rows = tb * 512
     hid = rnd(rows, 3072)                                            # 403 MB
     cases.append((f"VectorSigmoid {rows}x3072 (GELU gate)", lambda: ops.vector_op("SIGMOID", hid.view(-1), result=hid.view(-1)), 2 * hid.numel() * 4))
