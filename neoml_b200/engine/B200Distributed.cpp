@@ -60,7 +60,17 @@ struct CGroupState {
 struct CCommHolder {
 	ncclComm_t comm;
 	std::shared_ptr<CGroupState> group;
+	std::atomic<bool> commAborted{ false }; // this engine's own communicator has been given to ncclCommAbort
+
+	CCommHolder( ncclComm_t c, std::shared_ptr<CGroupState> g ) : comm( c ), group( std::move( g ) ) {}
+	// ends whatever this communicator still has in flight (a collective its peers never joined) -- once
+	void AbortOwn();
 };
+
+void CCommHolder::AbortOwn()
+{
+	if( !commAborted.exchange( true ) ) g_nccl.CommAbort( comm );
+}
 
 void raise( const std::string& message )
 {
@@ -80,10 +90,14 @@ void waitCollective( cudaStream_t stream, CCommHolder* holder )
 		int asyncError = ncclSuccessCode;
 		g_nccl.CommGetAsyncError( holder->comm, &asyncError );
 		if( asyncError != ncclSuccessCode && asyncError != ncclInProgressCode ) { raise( "NCCL reported an asynchronous error" ); return; }
-		if( holder->group->aborted.load() ) { raise( "Stopping due to error in another thread." ); return; }
+		if( holder->group->aborted.load() ) {
+			holder->AbortOwn(); // the collective on this stream will never complete: take it off the device
+			raise( "Stopping due to error in another thread." );
+			return;
+		}
 		if( std::chrono::steady_clock::now() - start > std::chrono::seconds( 120 ) ) {
 			holder->group->aborted.store( true );
-			g_nccl.CommAbort( holder->comm );
+			holder->AbortOwn();
 			raise( "collective timed out: a peer did not join within two minutes" );
 			return;
 		}
@@ -96,6 +110,16 @@ void CB200MathEngine::SetDistributedCommunicator( void* holder, const CMathEngin
 {
 	comm = holder;
 	distributedInfo = info;
+}
+
+void CB200MathEngine::ReleaseDistributedCommunicator()
+{
+	if( comm == nullptr ) return;
+	CCommHolder* holder = static_cast<CCommHolder*>( comm );
+	comm = nullptr;
+	// ncclCommDestroy waits for the communicator's outstanding work: after an abort there may be work that never ends
+	if( holder->group->aborted.load() ) holder->AbortOwn(); else g_nccl.CommDestroy( holder->comm );
+	delete holder;
 }
 
 void CB200MathEngine::AllReduce( const CFloatHandle& handle, int size )
@@ -130,8 +154,10 @@ void CB200MathEngine::AbortDistributed()
 {
 	if( comm == nullptr ) return;
 	CCommHolder* holder = static_cast<CCommHolder*>( comm );
+	// The flag reaches every peer: each polls it while it waits for a collective (waitCollective), aborts its own
+	// communicator and gives up with the reference's message.  This engine's communicator is aborted here.
 	holder->group->aborted.store( true );
-	g_nccl.CommAbort( holder->comm );
+	holder->AbortOwn();
 }
 
 void CreateDistributedB200MathEngines( IMathEngine** mathEngines, int devsCount, const int* cudaDevs, size_t memoryLimit )
@@ -144,8 +170,14 @@ void CreateDistributedB200MathEngines( IMathEngine** mathEngines, int devsCount,
 	std::shared_ptr<CGroupState> group = std::make_shared<CGroupState>();
 	for( int i = 0; i < devsCount; ++i ) {
 		CB200MathEngine* engine = static_cast<CB200MathEngine*>( CreateB200MathEngine( cudaDevs[i], memoryLimit, 0 ) );
-		if( engine == nullptr ) { raise( "a distributed B200 engine could not be created" ); return; }
-		engine->SetDistributedCommunicator( new CCommHolder{ comms[i], group }, CMathEngineDistributedInfo( i, devsCount ) );
+		if( engine == nullptr ) {
+			// nothing half-made is left behind: the engines made so far own (and destroy) their communicators
+			for( int j = 0; j < i; ++j ) { delete mathEngines[j]; mathEngines[j] = nullptr; }
+			for( int j = i; j < devsCount; ++j ) g_nccl.CommDestroy( comms[j] );
+			raise( "a distributed B200 engine could not be created" );
+			return;
+		}
+		engine->SetDistributedCommunicator( new CCommHolder( comms[i], group ), CMathEngineDistributedInfo( i, devsCount ) );
 		mathEngines[i] = engine;
 	}
 }

@@ -78,10 +78,32 @@ CB200MathEngine::~CB200MathEngine()
 {
 	if( stream != nullptr ) {
 		cudaSetDevice( device );
+		ReleaseDistributedCommunicator(); // first: after an abort only this lets the stream drain
 		cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
+		for( void* p : deferredFrees ) memory.Free( p );
 		for( auto& b : hostBuffers ) cudaFreeHost( b.host );
+		for( auto& b : hostCache ) cudaFreeHost( b.first );
 		cudaStreamDestroy( static_cast<cudaStream_t>( stream ) );
 	}
+}
+
+bool CB200MathEngine::pendingRefersTo( const void* begin, size_t bytes ) const
+{
+	const char* lo = static_cast<const char*>( begin );
+	const char* hi = lo + bytes;
+	auto inside = [&]( const void* p ) { return p != nullptr && static_cast<const char*>( p ) >= lo && static_cast<const char*>( p ) < hi; };
+	if( pending.active && ( inside( pending.source ) || inside( pending.filter ) || inside( pending.freeTerm )
+		|| inside( pending.result ) || inside( pending.residual ) || inside( pending.threshold ) ) ) {
+		return true;
+	}
+	return pendingRows.active && ( inside( pendingRows.data ) || inside( pendingRows.scale ) || inside( pendingRows.bias ) );
+}
+
+void CB200MathEngine::releaseDeferredFrees() const
+{
+	if( pending.active || pendingRows.active ) return;
+	for( void* p : deferredFrees ) memory.Free( p );
+	deferredFrees.clear();
 }
 
 void CB200MathEngine::notImplemented( const char* method ) const
@@ -139,6 +161,7 @@ void CB200MathEngine::flushRowOps() const
 		check( nb200_add_vector_to_matrix_rows( stream, 1, p.data, p.data, p.biasHeight, p.biasWidth, p.bias ),
 			"AddVectorToMatrixRows" );
 	}
+	releaseDeferredFrees();
 }
 
 void CB200MathEngine::flushPending() const
@@ -158,6 +181,7 @@ void CB200MathEngine::flushPending() const
 	const int rc = nb200_blob_convolution( stream, &pending.d, pending.source, pending.filter, pending.result, scratch, &epi,
 		precision );
 	if( scratch != nullptr ) memory.Free( scratch );
+	releaseDeferredFrees();
 	check( rc, "BlobConvolution" );
 }
 
@@ -228,7 +252,15 @@ void CB200MathEngine::HeapFree( const CMemoryHandle& handle )
 {
 	if( handle.IsNull() ) return;
 	if( handle.GetMathEngine() != this ) { raiseAssert( "HeapFree: the handle belongs to another math engine" ); return; }
-	memory.Free( const_cast<void*>( CMemoryHandleInternal::Base( handle ) ) );
+	void* block = const_cast<void*>( CMemoryHandleInternal::Base( handle ) );
+	{
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		if( ( pending.active || pendingRows.active ) && pendingRefersTo( block, memory.BlockBytes( block ) ) ) {
+			deferredFrees.push_back( block ); // returned to the pool once the recorded call has been launched
+			return;
+		}
+	}
+	memory.Free( block );
 }
 
 void CB200MathEngine::TransferHandleToThisThread( const CMemoryHandle&, size_t ) {} // heap blocks are not thread-bound here
@@ -247,6 +279,12 @@ CMemoryHandle CB200MathEngine::StackAlloc( size_t count )
 void CB200MathEngine::StackFree( const CMemoryHandle& handle )
 {
 	if( handle.IsNull() ) return;
+	{
+		// a recorded call may read a stack variable (NeoML keeps scalars such as a multiplier there): launch it before
+		// the variable's memory can be handed out again; the stack is LIFO, so the free itself cannot be postponed
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		if( pending.active || pendingRows.active ) enter();
+	}
 	memory.StackFree( CMemoryHandleInternal::GetRaw( handle ) );
 }
 
@@ -297,10 +335,10 @@ void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source
 
 void* CB200MathEngine::GetBuffer( const CMemoryHandle& handle, size_t pos, size_t size, bool exchange )
 {
-	void* host = nullptr;
 	setDevice();
-	if( cudaMallocHost( &host, size == 0 ? 1 : size ) != cudaSuccess ) {
-		cudaGetLastError();
+	size_t capacity = 0;
+	void* host = takeHostBuffer( size, capacity );
+	if( host == nullptr ) {
 		GetMathEngineExceptionHandler()->OnMemoryError();
 		return nullptr;
 	}
@@ -310,8 +348,46 @@ void* CB200MathEngine::GetBuffer( const CMemoryHandle& handle, size_t pos, size_
 		DataExchangeRaw( host, at, size );
 	}
 	std::lock_guard<std::mutex> lock( hostMutex );
-	hostBuffers.push_back( { host, size, handle, pos } );
+	hostBuffers.push_back( { host, size, capacity, handle, pos } );
 	return host;
+}
+
+// Pinned staging memory in power-of-two sizes; released buffers are cached (at most 256 MB in total) and reused.
+void* CB200MathEngine::takeHostBuffer( size_t size, size_t& capacity )
+{
+	capacity = 4096;
+	while( capacity < size ) capacity *= 2;
+	{
+		std::lock_guard<std::mutex> lock( hostMutex );
+		for( size_t i = 0; i < hostCache.size(); ++i ) {
+			if( hostCache[i].second == capacity ) {
+				void* host = hostCache[i].first;
+				hostCacheBytes -= capacity;
+				hostCache.erase( hostCache.begin() + i );
+				return host;
+			}
+		}
+	}
+	void* host = nullptr;
+	if( cudaMallocHost( &host, capacity ) != cudaSuccess ) {
+		cudaGetLastError();
+		return nullptr;
+	}
+	return host;
+}
+
+void CB200MathEngine::keepHostBuffer( void* host, size_t capacity )
+{
+	{
+		std::lock_guard<std::mutex> lock( hostMutex );
+		if( hostCacheBytes + capacity <= ( size_t( 256 ) << 20 ) ) {
+			hostCache.emplace_back( host, capacity );
+			hostCacheBytes += capacity;
+			return;
+		}
+	}
+	setDevice();
+	cudaFreeHost( host );
 }
 
 void CB200MathEngine::ReleaseBuffer( const CMemoryHandle& handle, void* ptr, bool exchange )
@@ -328,8 +404,7 @@ void CB200MathEngine::ReleaseBuffer( const CMemoryHandle& handle, void* ptr, boo
 			static_cast<const char*>( CMemoryHandleInternal::GetRaw( handle ) ) + buf.pos );
 		DataExchangeRaw( at, ptr, buf.size );
 	}
-	setDevice();
-	cudaFreeHost( ptr );
+	keepHostBuffer( ptr, buf.capacity );
 }
 
 CMemoryHandle CB200MathEngine::CopyFrom( const CMemoryHandle& handle, size_t size )
@@ -445,6 +520,16 @@ extern "C" __attribute__((visibility("default"))) void nb200_destroy_math_engine
 extern "C" __attribute__((visibility("default"))) void* nb200_create_math_engine( int device, size_t memoryLimit, int flags )
 {
 	return NeoML::CreateB200MathEngine( device, memoryLimit, flags );
+}
+
+// The CUDA stream an engine made by this library enqueues its work on (NULL for any other IMathEngine): lets a host
+// bracket engine calls with its own events.
+extern "C" __attribute__((visibility("default"))) void* nb200_engine_stream( void* engine )
+{
+	NeoML::CB200MathEngine* e = dynamic_cast<NeoML::CB200MathEngine*>( static_cast<NeoML::IMathEngine*>( engine ) );
+	if( e == nullptr ) return nullptr;
+	e->Enter(); // a recorded call is launched, so that an event recorded next lies behind all work issued so far
+	return e->Stream();
 }
 
 extern "C" __attribute__((visibility("default"))) void nb200_destroy_math_engine( void* engine )

@@ -54,6 +54,7 @@ public:
 	void ResetPeak() { peak = current; }
 	size_t InPools() const { return pooled; }
 	size_t FreeOnDevice() const;
+	size_t BlockBytes( const void* ptr ) const;  // size of the live heap block that starts at ptr, 0 when unknown
 
 private:
 	struct CStack {
@@ -101,6 +102,7 @@ public:
 	void AbortDistributed() override;
 	bool IsDistributed() const override { return comm != nullptr; }
 	void SetDistributedCommunicator( void* ncclComm, const CMathEngineDistributedInfo& info );
+	void ReleaseDistributedCommunicator(); // destroys (or, after an abort, aborts) the NCCL communicator
 
 	// every pure virtual of IVectorMathEngine / IBlasEngine / IDnnEngine / IMathEngine, generated at build time from
 	// the NeoMathEngine header this file is compiled against
@@ -158,6 +160,12 @@ private:
 	int productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
 		const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize );
 	mutable std::recursive_mutex pendingMutex;
+	// NeoML frees a layer's input blobs right after its RunOnce (reuse-memory mode), i.e. possibly while a recorded
+	// call still refers to them.  Such a heap block goes back to the pool only after the recorded call has been
+	// launched: the stream then orders every later user of the block behind it.
+	bool pendingRefersTo( const void* begin, size_t bytes ) const;
+	void releaseDeferredFrees() const;
+	mutable std::vector<void*> deferredFrees;
 
 	const int device;
 	const int precision;
@@ -166,9 +174,14 @@ private:
 	bool initialized = false;
 	void* comm = nullptr; // ncclComm_t
 	CMathEngineDistributedInfo distributedInfo;
-	// pinned staging buffers handed out by GetBuffer, LIFO per engine
-	struct CHostBuffer { void* host; size_t size; CMemoryHandle handle; size_t pos; };
+	// pinned staging buffers handed out by GetBuffer, LIFO per engine; released ones are kept for the next call
+	// (cudaMallocHost / cudaFreeHost cost milliseconds and synchronise the device, and CDnnBlob maps buffers routinely)
+	struct CHostBuffer { void* host; size_t size; size_t capacity; CMemoryHandle handle; size_t pos; };
 	std::vector<CHostBuffer> hostBuffers;
+	std::vector<std::pair<void*, size_t>> hostCache; // pointer, capacity
+	size_t hostCacheBytes = 0;
+	void* takeHostBuffer( size_t size, size_t& capacity );
+	void keepHostBuffer( void* host, size_t capacity );
 	std::mutex hostMutex;
 };
 

@@ -160,6 +160,13 @@ void CB200Memory::CleanUp()
 	}
 }
 
+size_t CB200Memory::BlockBytes( const void* ptr ) const
+{
+	std::lock_guard<std::mutex> lock( mutex );
+	auto it = live.find( const_cast<void*>( ptr ) );
+	return it == live.end() ? 0 : it->second;
+}
+
 size_t CB200Memory::FreeOnDevice() const
 {
 	size_t freeBytes = 0, total = 0;

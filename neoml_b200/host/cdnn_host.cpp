@@ -1,0 +1,677 @@
+// CDnn graphs of the benchmark configurations behind a C interface (ctypes-friendly): NeoML builds, loads and runs
+// the networks; the math engine under them is whatever the NeoMathEngine factory returns --
+// CreateCpuMathEngine (NeoML's own CPU engine) or CreateGpuMathEngine / the GPU manager / the distributed factory
+// (the B200 engine when libNeoMathEngine.so was built with this repository's factory).
+//
+// A "model" is an engine-independent NeoML archive in host memory: the network is assembled once on a CPU engine with
+// the given weights and serialised (CDnn::Serialize into a CMemoryFile -- the way CDistributedTraining clones a
+// network onto its engines, NeoML/src/Dnn/DnnDistributed.cpp:235-243,277-286); a "net" is that archive loaded into a
+// CDnn on one engine.  Both engines therefore run bit-identical weights through NeoML's own loading path.
+//
+//   resnet50     ResNet-50 v1.5: CConvLayer (+ free term = folded BatchNorm) / CReLULayer / CImageResizeLayer +
+//                CMaxPoolingLayer (padded pool) / CEltwiseSumLayer / CGlobalMeanPoolingLayer / CFullyConnectedLayer /
+//                CSoftmaxLayer / CArgmaxLayer; sinks "probs" (float) and "argmax" (int)
+//   transformer  n x CTransformerEncoderLayer (post-norm, GELU, dropout 0) with an optional MT_OneObject mask input
+//   conv         one CConvLayer;  mbv2  one CMobileNetV2BlockLayer;  matmul  one CMatrixMultiplicationLayer
+//
+// Every entry point catches NeoML's exceptions (std::exception-derived in this build) and reports them through
+// cdnn_last_error(); a "not implemented" assert of the engine arrives here as such a message.
+#include <NeoML/NeoML.h>
+#include <NeoML/Dnn/DnnDistributed.h>
+
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <thread>
+#include <vector>
+
+using namespace NeoML;
+
+#define CDNN_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local std::string lastError;
+
+template<class F> int guarded( F&& f )
+{
+	try {
+		f();
+		return 0;
+	} catch( const std::exception& e ) {
+		lastError = e.what();
+	} catch( ... ) {
+		lastError = "unknown exception";
+	}
+	return -1;
+}
+
+template<class F> void* guardedPtr( F&& f )
+{
+	void* result = nullptr;
+	return guarded( [&] { result = f(); } ) == 0 ? result : nullptr;
+}
+
+struct CModel {
+	std::vector<unsigned char> archive;
+};
+
+struct CNet {
+	IMathEngine* engine = nullptr;
+	CRandom random{ 0x5eed };
+	std::unique_ptr<CDnn> dnn;
+};
+
+// counter-based generator: the same seed gives the same weights wherever the model is built
+struct CSplitMix {
+	uint64_t state;
+	explicit CSplitMix( uint64_t seed ) : state( seed ) {}
+	uint64_t next()
+	{
+		uint64_t z = ( state += 0x9E3779B97F4A7C15ull );
+		z = ( z ^ ( z >> 30 ) ) * 0xBF58476D1CE4E5B9ull;
+		z = ( z ^ ( z >> 27 ) ) * 0x94D049BB133111EBull;
+		return z ^ ( z >> 31 );
+	}
+	double uniform() { return ( next() >> 11 ) * ( 1.0 / 9007199254740992.0 ); }
+	float normal( float sigma )
+	{
+		const double u1 = 1.0 - uniform(), u2 = uniform();
+		return static_cast<float>( sigma * std::sqrt( -2.0 * std::log( u1 ) ) * std::cos( 6.283185307179586 * u2 ) );
+	}
+};
+
+CPtr<CDnnBlob> blobFrom( IMathEngine& engine, const float* data, std::initializer_list<int> dims7 )
+{
+	CPtr<CDnnBlob> blob = CDnnBlob::CreateTensor( engine, CT_Float, dims7 );
+	blob->CopyFrom( data );
+	return blob;
+}
+
+void storeModel( CDnn& dnn, CModel& model )
+{
+	CMemoryFile file;
+	{
+		CArchive archive( &file, CArchive::SD_Storing );
+		dnn.Serialize( archive );
+		archive.Close();
+	}
+	model.archive.resize( static_cast<size_t>( file.GetLength() ) );
+	file.SeekToBegin();
+	file.Read( model.archive.data(), static_cast<int>( model.archive.size() ) );
+}
+
+CPtr<CSourceLayer> addSource( CDnn& dnn, const char* name )
+{
+	CPtr<CSourceLayer> source = new CSourceLayer( dnn.GetMathEngine() );
+	source->SetName( name );
+	dnn.AddLayer( *source );
+	return source;
+}
+
+void addSink( CDnn& dnn, const char* name, CBaseLayer& from, int output = 0 )
+{
+	CPtr<CSinkLayer> sink = new CSinkLayer( dnn.GetMathEngine() );
+	sink->SetName( name );
+	sink->Connect( 0, from, output );
+	dnn.AddLayer( *sink );
+}
+
+CPtr<CConvLayer> addConv( CDnn& dnn, const char* name, CBaseLayer& input, int cin, int cout, int fh, int fw, int strideH,
+	int strideW, int padH, int padW, int dilH, int dilW, const float* filter, const float* bias )
+{
+	IMathEngine& engine = dnn.GetMathEngine();
+	CPtr<CConvLayer> conv = new CConvLayer( engine );
+	conv->SetName( name );
+	conv->SetFilterCount( cout );
+	conv->SetFilterHeight( fh );
+	conv->SetFilterWidth( fw );
+	conv->SetStrideHeight( strideH );
+	conv->SetStrideWidth( strideW );
+	conv->SetPaddingHeight( padH );
+	conv->SetPaddingWidth( padW );
+	conv->SetDilationHeight( dilH );
+	conv->SetDilationWidth( dilW );
+	conv->SetFilterData( blobFrom( engine, filter, { 1, cout, 1, fh, fw, 1, cin } ) );
+	if( bias != nullptr ) {
+		conv->SetFreeTermData( blobFrom( engine, bias, { 1, 1, 1, 1, 1, 1, cout } ) );
+	} else {
+		conv->SetZeroFreeTerm( true );
+	}
+	conv->Connect( input );
+	dnn.AddLayer( *conv );
+	return conv;
+}
+
+CPtr<CBaseLayer> addReLU( CDnn& dnn, const std::string& name, CBaseLayer& input )
+{
+	CPtr<CReLULayer> relu = new CReLULayer( dnn.GetMathEngine() );
+	relu->SetName( name.c_str() );
+	relu->Connect( input );
+	dnn.AddLayer( *relu );
+	return relu.Ptr();
+}
+
+// walks a layer graph (composites included) and hands every fully connected layer to `visit`, in name order
+template<class F> void forEachFullyConnected( CDnnLayerGraph& graph, const std::string& prefix, F&& visit )
+{
+	CArray<const char*> names;
+	graph.GetLayerList( names );
+	std::vector<std::string> sorted;
+	for( int i = 0; i < names.Size(); ++i ) sorted.emplace_back( names[i] );
+	std::sort( sorted.begin(), sorted.end() );
+	for( const std::string& name : sorted ) {
+		CPtr<CBaseLayer> layer = graph.GetLayer( name.c_str() );
+		const std::string path = prefix + "/" + name;
+		if( CFullyConnectedLayer* fc = dynamic_cast<CFullyConnectedLayer*>( layer.Ptr() ) ) {
+			visit( path, *fc );
+		} else if( CCompositeLayer* composite = dynamic_cast<CCompositeLayer*>( layer.Ptr() ) ) {
+			forEachFullyConnected( *composite, path, visit );
+		}
+	}
+}
+
+uint64_t hashName( const std::string& s, uint64_t seed )
+{
+	uint64_t h = 1469598103934665603ull ^ seed;
+	for( unsigned char c : s ) h = ( h ^ c ) * 1099511628211ull;
+	return h;
+}
+
+} // namespace
+
+//---------------------------------------------------------------------------------------------------------------------
+
+CDNN_API const char* cdnn_last_error() { return lastError.c_str(); }
+
+// kind 0: CreateCpuMathEngine; 1: CreateGpuMathEngine (the recommended GPU); 2: entry `device` of
+// CreateGpuMathEngineManager.  Returns NULL (message in cdnn_last_error) when the factory returns none.
+CDNN_API void* cdnn_engine_create( int kind, int device, unsigned long long memoryLimit, int flags )
+{
+	return guardedPtr( [&]() -> void* {
+		SetMathEngineExceptionHandler( GetExceptionHandler() ); // what NeoML's own GetRecommendedGpuMathEngine does
+		IMathEngine* engine = nullptr;
+		if( kind == 0 ) {
+			engine = CreateCpuMathEngine( static_cast<size_t>( memoryLimit ) );
+		} else if( kind == 1 ) {
+			engine = CreateGpuMathEngine( static_cast<size_t>( memoryLimit ), flags );
+		} else {
+			std::unique_ptr<IGpuMathEngineManager> manager( CreateGpuMathEngineManager() );
+			engine = manager->CreateMathEngine( device, static_cast<size_t>( memoryLimit ), flags );
+		}
+		if( engine == nullptr ) lastError = "the math engine factory returned no engine";
+		return engine;
+	} );
+}
+
+CDNN_API void cdnn_engine_destroy( void* engine )
+{
+	guarded( [&] { delete static_cast<IMathEngine*>( engine ); } );
+}
+
+CDNN_API int cdnn_engine_info( void* engine, int* type, char* name, int nameSize, unsigned long long* peakBytes )
+{
+	return guarded( [&] {
+		IMathEngine* e = static_cast<IMathEngine*>( engine );
+		CMathEngineInfo info;
+		e->GetMathEngineInfo( info );
+		if( type != nullptr ) *type = static_cast<int>( e->GetType() );
+		if( name != nullptr && nameSize > 0 ) std::snprintf( name, nameSize, "%s", info.Name );
+		if( peakBytes != nullptr ) *peakBytes = e->GetPeakMemoryUsage();
+	} );
+}
+
+CDNN_API int cdnn_gpu_count()
+{
+	int count = -1;
+	guarded( [&] {
+		std::unique_ptr<IGpuMathEngineManager> manager( CreateGpuMathEngineManager() );
+		count = manager->GetMathEngineCount();
+	} );
+	return count;
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// models
+
+CDNN_API void cdnn_model_destroy( void* model ) { delete static_cast<CModel*>( model ); }
+CDNN_API long long cdnn_model_bytes( void* model ) { return static_cast<long long>( static_cast<CModel*>( model )->archive.size() ); }
+
+// One CConvLayer.  geometry = { cin, cout, fh, fw, strideH, strideW, padH, padW, dilH, dilW }; filter [cout, fh, fw, cin]
+CDNN_API void* cdnn_model_conv( const int* g, const float* filter, const float* bias )
+{
+	return guardedPtr( [&]() -> void* {
+		std::unique_ptr<IMathEngine> cpu( CreateCpuMathEngine( 0 ) );
+		CRandom random( 1 );
+		std::unique_ptr<CModel> model( new CModel );
+		{
+			CDnn dnn( random, *cpu );
+			CPtr<CSourceLayer> in = addSource( dnn, "in" );
+			CPtr<CConvLayer> conv = addConv( dnn, "conv", *in, g[0], g[1], g[2], g[3], g[4], g[5], g[6], g[7], g[8], g[9],
+				filter, bias );
+			addSink( dnn, "out", *conv );
+			storeModel( dnn, *model );
+		}
+		return model.release();
+	} );
+}
+
+// One CMobileNetV2BlockLayer.  relu thresholds: > 0 ReLU with that upper threshold, 0 plain ReLU, < 0 HSwish.
+CDNN_API void* cdnn_model_mbv2( int cin, int cexp, int cout, int stride, int residual, float act1, float act2,
+	const float* expandFilter, const float* expandBias, const float* channelwiseFilter, const float* channelwiseBias,
+	const float* downFilter, const float* downBias )
+{
+	return guardedPtr( [&]() -> void* {
+		std::unique_ptr<IMathEngine> cpu( CreateCpuMathEngine( 0 ) );
+		CRandom random( 1 );
+		std::unique_ptr<CModel> model( new CModel );
+		{
+			CDnn dnn( random, *cpu );
+			CPtr<CSourceLayer> in = addSource( dnn, "in" );
+			auto activation = []( float v ) {
+				return v < 0 ? CActivationDesc( AF_HSwish ) : CActivationDesc( AF_ReLU, CReLUActivationParam{ v } );
+			};
+			auto optional = [&]( const float* data, int n ) -> CPtr<CDnnBlob> {
+				return data == nullptr ? nullptr : blobFrom( *cpu, data, { 1, 1, 1, 1, 1, 1, n } );
+			};
+			CPtr<CMobileNetV2BlockLayer> block = new CMobileNetV2BlockLayer( *cpu,
+				blobFrom( *cpu, expandFilter, { 1, cexp, 1, 1, 1, 1, cin } ), optional( expandBias, cexp ), activation( act1 ),
+				stride, blobFrom( *cpu, channelwiseFilter, { 1, 1, 1, 3, 3, 1, cexp } ), optional( channelwiseBias, cexp ),
+				activation( act2 ), blobFrom( *cpu, downFilter, { 1, cout, 1, 1, 1, 1, cexp } ), optional( downBias, cout ),
+				residual != 0 );
+			block->SetName( "block" );
+			block->Connect( *in );
+			dnn.AddLayer( *block );
+			addSink( dnn, "out", *block );
+			storeModel( dnn, *model );
+		}
+		return model.release();
+	} );
+}
+
+// One CMatrixMultiplicationLayer: inputs "a" [batch, M, K] and "b" [batch, K, N] (as height x channels matrices per
+// object), output "out".
+CDNN_API void* cdnn_model_matmul()
+{
+	return guardedPtr( [&]() -> void* {
+		std::unique_ptr<IMathEngine> cpu( CreateCpuMathEngine( 0 ) );
+		CRandom random( 1 );
+		std::unique_ptr<CModel> model( new CModel );
+		{
+			CDnn dnn( random, *cpu );
+			CPtr<CSourceLayer> a = addSource( dnn, "a" );
+			CPtr<CSourceLayer> b = addSource( dnn, "b" );
+			CPtr<CMatrixMultiplicationLayer> mm = new CMatrixMultiplicationLayer( *cpu );
+			mm->SetName( "mm" );
+			mm->Connect( 0, *a );
+			mm->Connect( 1, *b );
+			dnn.AddLayer( *mm );
+			addSink( dnn, "out", *mm );
+			storeModel( dnn, *model );
+		}
+		return model.release();
+	} );
+}
+
+// ResNet-50 v1.5.  `params` holds, in network order (stem; per block: [down], c1, c2, c3 -- `down` first in a
+// stage's first block; then the classifier), each convolution's filter [cout, k, k, cin] followed by its cout free
+// terms, then the classifier's weights [classes, 2048] and free terms.  v1.5: the stride of a stage sits on the 3x3.
+CDNN_API void* cdnn_model_resnet50( const float* params, long long count, int classes )
+{
+	return guardedPtr( [&]() -> void* {
+		std::unique_ptr<IMathEngine> cpu( CreateCpuMathEngine( 0 ) );
+		CRandom random( 1 );
+		std::unique_ptr<CModel> model( new CModel );
+		const float* p = params;
+		const float* const end = params + count;
+		auto take = [&]( long long n ) {
+			const float* at = p;
+			p += n;
+			if( p > end ) throw std::logic_error( "cdnn_model_resnet50: the parameter array is too short" );
+			return at;
+		};
+		{
+			CDnn dnn( random, *cpu );
+			auto conv = [&]( const std::string& name, CBaseLayer& input, int cin, int cout, int k, int stride, int pad ) {
+				const float* w = take( 1LL * cout * k * k * cin );
+				const float* b = take( cout );
+				return addConv( dnn, name.c_str(), input, cin, cout, k, k, stride, stride, pad, pad, 1, 1, w, b );
+			};
+			CPtr<CSourceLayer> in = addSource( dnn, "in" );
+			CPtr<CBaseLayer> t = addReLU( dnn, "stem_relu", *conv( "stem", *in, 3, 64, 7, 2, 3 ) );
+			// 3x3/2 max pooling with padding 1: NeoML's pooling takes no padding, the image is widened first (what
+			// NeoOnnx emits for a padded pool, NeoOnnx/src/Operators/PoolOperator.cpp:66-76); inputs are >= 0 here
+			CPtr<CImageResizeLayer> pad = new CImageResizeLayer( *cpu );
+			pad->SetName( "pool_pad" );
+			for( int side = 0; side < CImageResizeLayer::IS_Count; ++side ) {
+				pad->SetDelta( static_cast<CImageResizeLayer::TImageSide>( side ), 1 );
+			}
+			pad->SetDefaultValue( 0.f );
+			pad->Connect( *t );
+			dnn.AddLayer( *pad );
+			CPtr<CMaxPoolingLayer> pool = new CMaxPoolingLayer( *cpu );
+			pool->SetName( "pool" );
+			pool->SetFilterHeight( 3 );
+			pool->SetFilterWidth( 3 );
+			pool->SetStrideHeight( 2 );
+			pool->SetStrideWidth( 2 );
+			pool->Connect( *pad );
+			dnn.AddLayer( *pool );
+			t = pool.Ptr();
+
+			const int stages[4][4] = { { 64, 256, 3, 1 }, { 128, 512, 4, 2 }, { 256, 1024, 6, 2 }, { 512, 2048, 3, 2 } };
+			int cin = 64;
+			for( int si = 0; si < 4; ++si ) {
+				const int mid = stages[si][0], out = stages[si][1];
+				for( int bi = 0; bi < stages[si][2]; ++bi ) {
+					const int stride = bi == 0 ? stages[si][3] : 1;
+					const std::string prefix = "s" + std::to_string( si + 1 ) + "b" + std::to_string( bi + 1 );
+					CPtr<CBaseLayer> shortcut = t;
+					if( bi == 0 ) shortcut = conv( prefix + "_down", *t, cin, out, 1, stride, 0 ).Ptr();
+					CPtr<CBaseLayer> u = addReLU( dnn, prefix + "_r1", *conv( prefix + "_c1", *t, cin, mid, 1, 1, 0 ) );
+					u = addReLU( dnn, prefix + "_r2", *conv( prefix + "_c2", *u, mid, mid, 3, stride, 1 ) );
+					CPtr<CConvLayer> c3 = conv( prefix + "_c3", *u, mid, out, 1, 1, 0 );
+					CPtr<CEltwiseSumLayer> sum = new CEltwiseSumLayer( *cpu );
+					sum->SetName( ( prefix + "_sum" ).c_str() );
+					sum->Connect( 0, *c3 );
+					sum->Connect( 1, *shortcut );
+					dnn.AddLayer( *sum );
+					t = addReLU( dnn, prefix + "_r3", *sum );
+					cin = out;
+				}
+			}
+			CPtr<CGlobalMeanPoolingLayer> mean = new CGlobalMeanPoolingLayer( *cpu );
+			mean->SetName( "mean" );
+			mean->Connect( *t );
+			dnn.AddLayer( *mean );
+			CPtr<CFullyConnectedLayer> fc = new CFullyConnectedLayer( *cpu );
+			fc->SetName( "fc" );
+			fc->SetNumberOfElements( classes );
+			{
+				const float* w = take( 1LL * classes * cin );
+				const float* b = take( classes );
+				CPtr<CDnnBlob> weights = blobFrom( *cpu, w, { 1, classes, 1, 1, 1, 1, cin } );
+				CPtr<CDnnBlob> freeTerms = blobFrom( *cpu, b, { 1, 1, 1, 1, 1, 1, classes } );
+				fc->SetWeightsData( weights );
+				fc->SetFreeTermData( freeTerms );
+			}
+			fc->Connect( *mean );
+			dnn.AddLayer( *fc );
+			CPtr<CSoftmaxLayer> softmax = new CSoftmaxLayer( *cpu );
+			softmax->SetName( "softmax" );
+			softmax->Connect( *fc );
+			dnn.AddLayer( *softmax );
+			CPtr<CArgmaxLayer> argmax = new CArgmaxLayer( *cpu );
+			argmax->SetName( "argmax_layer" );
+			argmax->SetDimension( BD_Channels );
+			argmax->Connect( *softmax );
+			dnn.AddLayer( *argmax );
+			addSink( dnn, "probs", *softmax );
+			addSink( dnn, "argmax", *argmax );
+			if( p != end ) throw std::logic_error( "cdnn_model_resnet50: the parameter array is too long" );
+			storeModel( dnn, *model );
+		}
+		return model.release();
+	} );
+}
+
+// `layers` x CTransformerEncoderLayer (post-norm, AF_GELU in its default sigmoid-approximate mode, dropout 0), input
+// "in" [1, batch, seq, 1, 1, 1, hidden]; with useMask != 0 a second input "mask" [1, 1, 1, 1, seq, 1, seq] (1 = ignored
+// position, MT_OneObject).  Every fully connected layer gets weights and free terms ~ N(0, sigma) from `seed`.
+CDNN_API void* cdnn_model_transformer( int layers, int hidden, int heads, int ffn, unsigned long long seed, float sigma,
+	int useMask )
+{
+	return guardedPtr( [&]() -> void* {
+		std::unique_ptr<IMathEngine> cpu( CreateCpuMathEngine( 0 ) );
+		CRandom random( 1 );
+		std::unique_ptr<CModel> model( new CModel );
+		{
+			CDnn dnn( random, *cpu );
+			CPtr<CSourceLayer> in = addSource( dnn, "in" );
+			CPtr<CSourceLayer> mask = useMask != 0 ? addSource( dnn, "mask" ) : nullptr;
+			CPtr<CBaseLayer> t = in.Ptr();
+			for( int i = 0; i < layers; ++i ) {
+				CPtr<CTransformerEncoderLayer> layer = new CTransformerEncoderLayer( *cpu );
+				layer->SetName( ( "encoder" + std::to_string( i ) ).c_str() );
+				layer->SetHeadCount( heads );
+				layer->SetHiddenSize( hidden );
+				layer->SetFeedForwardSize( ffn );
+				layer->SetDropoutRate( 0.f );
+				layer->SetActivation( CActivationDesc( AF_GELU ) );
+				layer->Connect( 0, *t );
+				if( mask != nullptr ) layer->Connect( 1, *mask );
+				dnn.AddLayer( *layer );
+				t = layer.Ptr();
+			}
+			addSink( dnn, "out", *t );
+			// one pass over a two-token sequence creates the parameter blobs; then they are overwritten
+			const int seq = 2;
+			std::vector<float> zeros( static_cast<size_t>( seq ) * std::max( hidden, seq ), 0.f );
+			in->SetBlob( blobFrom( *cpu, zeros.data(), { 1, 1, seq, 1, 1, 1, hidden } ) );
+			if( mask != nullptr ) mask->SetBlob( blobFrom( *cpu, zeros.data(), { 1, 1, 1, 1, seq, 1, seq } ) );
+			dnn.RunOnce();
+			forEachFullyConnected( dnn, "", [&]( const std::string& path, CFullyConnectedLayer& fc ) {
+				CSplitMix rng( hashName( path, seed ) );
+				CPtr<CDnnBlob> w = fc.GetWeightsData();
+				std::vector<float> values( static_cast<size_t>( w->GetDataSize() ) );
+				for( float& v : values ) v = rng.normal( sigma );
+				w->CopyFrom( values.data() );
+				fc.SetWeightsData( w );
+				CPtr<CDnnBlob> b = fc.GetFreeTermData();
+				if( b != nullptr ) {
+					values.resize( static_cast<size_t>( b->GetDataSize() ) );
+					for( float& v : values ) v = rng.normal( sigma );
+					b->CopyFrom( values.data() );
+					fc.SetFreeTermData( b );
+				}
+			} );
+			storeModel( dnn, *model );
+		}
+		return model.release();
+	} );
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// nets
+
+CDNN_API void* cdnn_net_create( void* engine, void* model )
+{
+	return guardedPtr( [&]() -> void* {
+		std::unique_ptr<CNet> net( new CNet );
+		net->engine = static_cast<IMathEngine*>( engine );
+		net->dnn.reset( new CDnn( net->random, *net->engine ) );
+		CModel* m = static_cast<CModel*>( model );
+		CMemoryFile file;
+		file.Write( m->archive.data(), static_cast<int>( m->archive.size() ) );
+		file.SeekToBegin();
+		CArchive archive( &file, CArchive::SD_Loading );
+		net->dnn->Serialize( archive );
+		archive.Close();
+		return net.release();
+	} );
+}
+
+CDNN_API void cdnn_net_destroy( void* net )
+{
+	guarded( [&] { delete static_cast<CNet*>( net ); } );
+}
+
+// Gives source layer `name` a blob of the seven dimensions `dims` (NeoML order: BatchLength, BatchWidth, ListSize,
+// Height, Width, Depth, Channels) filled from `host`.  A blob of the same shape is reused: the call is then one
+// host-to-device exchange (CDnnBlob::CopyFrom -> IMathEngine::DataExchangeRaw).
+CDNN_API int cdnn_net_set_input( void* netPtr, const char* name, const float* host, const int* dims )
+{
+	return guarded( [&] {
+		CNet* net = static_cast<CNet*>( netPtr );
+		CPtr<CSourceLayer> source = CheckCast<CSourceLayer>( net->dnn->GetLayer( name ) );
+		CPtr<CDnnBlob> blob = source->GetBlob();
+		bool same = blob != nullptr && blob->GetDataType() == CT_Float;
+		for( int i = 0; same && i < 7; ++i ) same = blob->DimSize( i ) == dims[i];
+		if( !same ) {
+			blob = CDnnBlob::CreateTensor( *net->engine, CT_Float, { dims[0], dims[1], dims[2], dims[3], dims[4], dims[5], dims[6] } );
+		}
+		blob->CopyFrom( host );
+		if( !same ) source->SetBlob( blob );
+	} );
+}
+
+CDNN_API int cdnn_net_run( void* net )
+{
+	return guarded( [&] { static_cast<CNet*>( net )->dnn->RunOnce(); } );
+}
+
+// Copies the blob of sink `name` to `host` (device-to-host exchange: results are complete when this returns).
+// dims receives the seven dimensions, isInt whether the data are 32-bit integers.  With host == NULL only the shape.
+CDNN_API int cdnn_net_get_output( void* netPtr, const char* name, void* host, long long capacityBytes, int* dims, int* isInt )
+{
+	return guarded( [&] {
+		CNet* net = static_cast<CNet*>( netPtr );
+		CPtr<CSinkLayer> sink = CheckCast<CSinkLayer>( net->dnn->GetLayer( name ) );
+		CPtr<CDnnBlob> blob = sink->GetBlob();
+		if( blob == nullptr ) throw std::logic_error( "the sink holds no blob: run the net first" );
+		for( int i = 0; dims != nullptr && i < 7; ++i ) dims[i] = blob->DimSize( i );
+		if( isInt != nullptr ) *isInt = blob->GetDataType() == CT_Int ? 1 : 0;
+		if( host == nullptr ) return;
+		if( capacityBytes < static_cast<long long>( blob->GetDataSize() ) * 4 ) throw std::logic_error( "output buffer too small" );
+		if( blob->GetDataType() == CT_Int ) {
+			blob->CopyTo( static_cast<int*>( host ) );
+		} else {
+			blob->CopyTo( static_cast<float*>( host ) );
+		}
+	} );
+}
+
+// Wall-clock seconds of `steps` x ( [host -> source blob] RunOnce [sink -> host] ) on this net, for the CPU baseline
+// and other host-timed runs.  input/output may be NULL (then the source keeps its blob / nothing is read back except
+// a final 4-byte read that waits for the device).
+CDNN_API double cdnn_net_time_steps( void* netPtr, int steps, const char* sourceName, const float* input, const char* sinkName,
+	void* output, long long outputBytes )
+{
+	double seconds = -1;
+	guarded( [&] {
+		CNet* net = static_cast<CNet*>( netPtr );
+		CPtr<CSourceLayer> source = sourceName != nullptr ? CheckCast<CSourceLayer>( net->dnn->GetLayer( sourceName ) ) : nullptr;
+		CPtr<CSinkLayer> sink = CheckCast<CSinkLayer>( net->dnn->GetLayer( sinkName ) );
+		const auto t0 = std::chrono::steady_clock::now();
+		for( int i = 0; i < steps; ++i ) {
+			if( input != nullptr ) source->GetBlob()->CopyFrom( input );
+			net->dnn->RunOnce();
+			if( output != nullptr ) {
+				CPtr<CDnnBlob> blob = sink->GetBlob();
+				if( outputBytes < static_cast<long long>( blob->GetDataSize() ) * 4 ) throw std::logic_error( "output buffer too small" );
+				if( blob->GetDataType() == CT_Int ) blob->CopyTo( static_cast<int*>( output ) ); else blob->CopyTo( static_cast<float*>( output ) );
+			}
+		}
+		if( output == nullptr ) {
+			// any device-to-host exchange completes the work issued before it
+			CPtr<CDnnBlob> blob = sink->GetBlob();
+			int word = 0;
+			if( blob->GetDataType() == CT_Int ) {
+				net->engine->DataExchangeRaw( &word, blob->GetData<int>(), sizeof( word ) );
+			} else {
+				net->engine->DataExchangeRaw( &word, blob->GetData<float>(), sizeof( word ) );
+			}
+		}
+		seconds = std::chrono::duration<double>( std::chrono::steady_clock::now() - t0 ).count();
+	} );
+	return seconds;
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// Several replicas of one model, one math engine and one host thread each: the shape of NeoML's
+// CDistributedInference / CDistributedTraining (NeoML/src/Dnn/DnnDistributed.cpp:270-296,343-375,551-607), with the
+// engines made by the factory's distributed entry points.
+
+namespace {
+
+struct CReplicas {
+	std::vector<IMathEngine*> engines;
+	std::vector<std::unique_ptr<CNet>> nets;
+};
+
+} // namespace
+
+// kind 0: `count` CPU engines (CreateCpuMathEngine each); kind 1: CreateDistributedCudaMathEngines on devices[0..count)
+CDNN_API void* cdnn_replicas_create( int kind, int count, const int* devices, void* model )
+{
+	return guardedPtr( [&]() -> void* {
+		SetMathEngineExceptionHandler( GetExceptionHandler() );
+		std::unique_ptr<CReplicas> r( new CReplicas );
+		r->engines.assign( count, nullptr );
+		if( kind == 0 ) {
+			for( int i = 0; i < count; ++i ) r->engines[i] = CreateCpuMathEngine( 0 );
+		} else {
+			CreateDistributedCudaMathEngines( r->engines.data(), count, devices, 0 );
+		}
+		for( int i = 0; i < count; ++i ) {
+			if( r->engines[i] == nullptr ) throw std::logic_error( "the distributed factory returned no engine" );
+			r->nets.emplace_back( static_cast<CNet*>( cdnn_net_create( r->engines[i], model ) ) );
+			if( r->nets.back() == nullptr ) throw std::logic_error( lastError );
+		}
+		return r.release();
+	} );
+}
+
+CDNN_API void cdnn_replicas_destroy( void* replicas )
+{
+	guarded( [&] {
+		CReplicas* r = static_cast<CReplicas*>( replicas );
+		r->nets.clear();
+		for( IMathEngine* e : r->engines ) delete e;
+		delete r;
+	} );
+}
+
+CDNN_API void* cdnn_replicas_net( void* replicas, int index )
+{
+	CReplicas* r = static_cast<CReplicas*>( replicas );
+	return index >= 0 && index < static_cast<int>( r->nets.size() ) ? r->nets[index].get() : nullptr;
+}
+
+// Every replica, on its own host thread, runs `steps` x ( host -> source, RunOnce, sink -> host ) on its slice:
+// replica i reads inputs + i * inputFloatsPerReplica and writes outputs + i * outputBytesPerReplica.  All threads
+// start together; returns the wall-clock seconds until the last one finished (after `warmup` untimed steps each).
+CDNN_API double cdnn_replicas_time_steps( void* replicas, int warmup, int steps, const char* sourceName, const float* inputs,
+	long long inputFloatsPerReplica, const char* sinkName, char* outputs, long long outputBytesPerReplica )
+{
+	CReplicas* r = static_cast<CReplicas*>( replicas );
+	const int n = static_cast<int>( r->nets.size() );
+	std::atomic<int> ready{ 0 };
+	std::atomic<bool> go{ false };
+	std::vector<std::string> errors( n );
+	std::vector<std::thread> threads;
+	std::vector<std::chrono::steady_clock::time_point> finished( n );
+	for( int i = 0; i < n; ++i ) {
+		threads.emplace_back( [&, i] {
+			SetMathEngineExceptionHandler( GetExceptionHandler() );
+			const float* in = inputs != nullptr ? inputs + i * inputFloatsPerReplica : nullptr;
+			char* out = outputs != nullptr ? outputs + i * outputBytesPerReplica : nullptr;
+			if( warmup > 0 && cdnn_net_time_steps( r->nets[i].get(), warmup, sourceName, in, sinkName, out, outputBytesPerReplica ) < 0 ) {
+				errors[i] = lastError;
+			}
+			ready.fetch_add( 1 );
+			while( !go.load() ) std::this_thread::yield();
+			if( errors[i].empty() && cdnn_net_time_steps( r->nets[i].get(), steps, sourceName, in, sinkName, out, outputBytesPerReplica ) < 0 ) {
+				errors[i] = lastError;
+			}
+			finished[i] = std::chrono::steady_clock::now();
+		} );
+	}
+	while( ready.load() < n ) std::this_thread::yield();
+	const auto t0 = std::chrono::steady_clock::now();
+	go.store( true );
+	for( std::thread& t : threads ) t.join();
+	double seconds = 0;
+	for( int i = 0; i < n; ++i ) {
+		if( !errors[i].empty() ) {
+			lastError = errors[i];
+			return -1;
+		}
+		seconds = std::max( seconds, std::chrono::duration<double>( finished[i] - t0 ).count() );
+	}
+	return seconds;
+}
