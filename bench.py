@@ -1,17 +1,25 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: ResNet-50 v1.5 fp32-accurate inference (images/s) through the B200 math-engine kernels.
+"""Benchmark of the hot path: ResNet-50 v1.5 fp32-accurate inference (images/s) as a NeoML CDnn on the B200 math engine.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
+The timed call is NeoML's own `CDnn::RunOnce()` on the engine that NeoML's factory returns (`CreateGpuMathEngine` /
+`IGpuMathEngineManager` of the hosted libNeoMathEngine.so: the B200 engine); NeoML itself is built unmodified.
 N > 1 is launched by torch.distributed.run (one rank per GPU); inference is batch-sharded with no data-path
 collective (weak scaling: every rank runs the full per-GPU batch).  Rank 0 prints ONE JSON line.
 
 A step is one forward pass over one synthetic batch (256 x 224 x 224 x 3, uniform[0,1], seeded; He-normal weights with
-the BatchNorm folded into the free terms).  `value` is timed with the batch already resident in HBM; `e2e` runs the
-same call with the batch in pinned host memory, host->device copy and device->host read of the result inside the
-timed region.  `roofline` describes the dominant kernel (the tcgen05 contraction) from CUDA-event timings of every
-contraction launch in one extra, instrumented step.  `cpu_baseline` times the reference's own CPU math engine
-(oracle/_ref) on a bounded sample of the same workload on this host's cores.
+the BatchNorm folded into the free terms).  `value` is timed with the batch already resident in HBM (the source
+layer's blob), CUDA events on the engine's stream; `e2e` is the same through the calls a NeoML user makes with HOST
+buffers: per step `CDnnBlob::CopyFrom(host)` of the batch from pinned memory, `RunOnce()`, `CopyTo(host)` of the
+probabilities and arg-max indices.  `roofline` describes the dominant kernel (the tcgen05 contraction) from CUDA-event
+timings of every contraction launch in three extra, instrumented steps.  `cpu_baseline` / `--impl reference` time the
+same CDnn on the reference's own CPU math engine (oracle/_ref: NeoML and NeoMathEngine built unmodified), one engine
+per host thread on slices of the same 256-image batch.
+
+Other modes: --sweep (per-GPU batch 1/32/256/1024 on 1/2/4/8 engines of ONE process made by NeoML's
+CreateDistributedCudaMathEngines, one host thread per engine), --transformer (configuration 4 as a CDnn), --ops and
+--products (kernel-level figures at the configurations' sizes).
 """
 from __future__ import annotations
 
@@ -22,7 +30,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -32,9 +39,7 @@ sys.path.insert(0, str(ROOT))
 METRIC = "resnet50_fp32_infer_images_per_s"
 UNIT = "images/s"
 IMAGE = (224, 224, 3)
-
-
-SETTLE_STEPS = 12   # untimed steps ahead of the warm-up steps (see run_ours)
+WORKLOAD = "resnet50_v1.5_infer_b256_224x224x3"
 
 
 def parse_args():
@@ -45,23 +50,23 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch")
     ap.add_argument("--precision", type=int, default=0, help="0 = 3xTF32 (default), 1 = TF32 opt-in")
-    ap.add_argument("--unfused", action="store_true", help="issue conv / add / ReLU as separate engine calls")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-peak", action="store_true", help="skip the TF32 peak measurement (profiler captures)")
     ap.add_argument("--layers", action="store_true", help="print the per-contraction timing table to stderr")
-    ap.add_argument("--graph", action="store_true",
-                    help="capture the forward pass in a CUDA graph and replay it (small batches are launch-bound: "
-                         "115 launches per pass)")
+    ap.add_argument("--settle-seconds", type=float, default=3.0,
+                    help="upper bound of the untimed settling phase (20-step blocks until two agree within 2 %%); "
+                         "0 for profiler captures")
     ap.add_argument("--ops", action="store_true",
                     help="instead of the network: time the bandwidth-bound kernels at the configs' sizes (one JSON line each)")
-    ap.add_argument("--settle", type=int, default=SETTLE_STEPS,
-                    help="untimed steps ahead of the warm-up steps (clocks and power settle on a fresh box); 0 for profiler captures")
     ap.add_argument("--products", action="store_true",
                     help="time the dense contractions of the other configs (config 1 convolution, config 2 MobileNetV2 "
                          "block, config 4 FC and attention products, config 5 matrix products) against the tensor roofline")
+    ap.add_argument("--sweep", action="store_true",
+                    help="per-GPU batch 1/32/256/1024 on 1/2/4/8 engines of one process (CreateDistributedCudaMathEngines)")
+    ap.add_argument("--transformer", action="store_true", help="configuration 4 (12 encoder layers, 64 x 512 x 768) as a CDnn")
     ap.add_argument("--kernel-options", type=int, default=0,
                     help="diagnostic switches of the contraction launcher (16 gather kernel, 32 no split K, 64 no "
                          "programmatic dependent launch); for A/B timing only")
-    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU-baseline sample")
     return ap.parse_args()
 
 
@@ -73,78 +78,48 @@ def host_cores() -> int:
         return os.cpu_count() or 1
 
 
-def cpu_reference_run(per_thread_batch: int, rounds_budget_s: float, min_rounds: int, max_rounds: int, warm: int):
-    """Times the reference CPU math engine (or, where it was not built, the plain-C oracle port) on ResNet-50:
-    one engine per host thread, each thread a replica on its own slice of the batch -- the reference's own
-    multi-core model (CDistributedInference).  Returns (images/s, ms per round, cores, kind, sample text)."""
-    sys.path.insert(0, str(ROOT / "oracle"))
-    import numpy as np
-    from neoml_b200 import resnet50
-    import ref_backend
-    from oracle_lib import Reference
-
-    kind = "reference" if Reference.available() else "port"
-    cores = host_cores() if kind == "reference" else 1
-    weights = resnet50.make_weights()
-    rng = np.random.default_rng(7)
-    inputs = [rng.uniform(0, 1, (per_thread_batch, *IMAGE)).astype(np.float32) for _ in range(cores)]
-    backends = [None] * cores
-    barrier = threading.Barrier(cores + 1)
-    stop = {"flag": False}
-
-    def worker(i):
-        backends[i] = ref_backend.RefBackend() if kind == "reference" else ref_backend.OracleBackend()
-        while True:
-            barrier.wait()
-            if stop["flag"]:
-                break
-            resnet50.forward(backends[i], weights, inputs[i], fuse=False)
-            barrier.wait()
-
-    threads = [threading.Thread(target=worker, args=(i,), daemon=True) for i in range(cores)]
-    for t in threads:
-        t.start()
-    times = []
-    t_start = time.perf_counter()
-    rounds = 0
-    while True:
-        barrier.wait()
-        t0 = time.perf_counter()
-        barrier.wait()
-        dt = time.perf_counter() - t0
-        rounds += 1
-        if rounds > warm:
-            times.append(dt)
-        timed = len(times)
-        if timed >= max_rounds or (timed >= min_rounds and time.perf_counter() - t_start > rounds_budget_s):
-            break
-    stop["flag"] = True
-    barrier.wait()
-    for t in threads:
-        t.join()
-    images = per_thread_batch * cores
-    total = sum(times)
-    ips = images * len(times) / total
-    sample = (f"ResNet-50 forward, {cores} engine(s) x batch {per_thread_batch} per round, {len(times)} timed rounds "
-              f"after {warm} warm-up; sgemm = MLAS (no MKL on this host)" if kind == "reference" else
-              f"plain-C oracle port, 1 thread x batch {per_thread_batch}, {len(times)} rounds")
-    return ips, 1e3 * total / len(times), cores, kind, sample
-
-
 def run_reference_arm(args):
+    """The reference's own CPU path for the same step: the ResNet-50 CDnn on NeoML's CPU math engine (oracle/_ref:
+    NeoML and NeoMathEngine compiled unmodified), one engine and one host thread per slice of the 256-image batch --
+    NeoML's multi-core model (CDistributedInference).  Every step copies its slice from host memory into the source
+    blob, runs, and copies probabilities and arg-max indices back."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    ips, ms, cores, kind, sample = cpu_reference_run(per_thread_batch=1, rounds_budget_s=0.0, min_rounds=args.steps,
-                                                     max_rounds=args.steps, warm=args.warmup)
+    import numpy as np
+    from neoml_b200 import cdnn, resnet50
+    ref_dir = ROOT / "oracle" / "_ref"
+    if not (ref_dir / "libcdnn_host.so").exists():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref is not built (make -C oracle ref needs a NeoML checkout)"}))
+        return
+    cdnn.use_directory(ref_dir)
+    cdnn.load()
+    batch = args.batch
+    threads = 1
+    while threads * 2 <= host_cores() and batch % (threads * 2) == 0:
+        threads *= 2
+    per = batch // threads
+    model = cdnn.Model.resnet50(resnet50.make_weights())
+    x = np.random.default_rng(1234).uniform(0, 1, (batch, *IMAGE)).astype(np.float32)
+    out_floats = per * (resnet50.CLASSES + 1)
+    out = np.empty(threads * out_floats, np.float32)
+    reps = cdnn.Replicas("cpu", model, count=threads)
+    for i in range(threads):
+        reps.net(i).set_input("in", x[i * per:(i + 1) * per])
+    seconds = reps.time_steps(args.warmup, args.steps, "in", x.ctypes.data, x.size // threads, "probs,argmax",
+                              out.ctypes.data, out_floats * 4)
+    reps.close()
+    ips = batch * args.steps / seconds
+    sample = (f"ResNet-50 CDnn, {threads} CPU engines x {per} images = one {batch}-image step, {args.steps} timed steps "
+              f"after {args.warmup} warm-up; sgemm = MLAS (no MKL on this host)")
     line = {
         "impl": "reference", "metric": METRIC, "value": round(ips, 3), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": "resnet50_v1.5_infer_b256_224x224x3", "per_gpu_batch": 256,
-                   "step": f"bounded sample of the workload: {cores} host threads x 1 image per step",
-                   "engine": "reference CPU math engine (MLAS sgemm)"},
-        "cpu_baseline": {"value": round(ips, 3), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(1e3 * seconds / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": WORKLOAD if batch == 256 else f"resnet50_v1.5_infer_b{batch}", "per_gpu_batch": batch,
+                   "step": f"one {batch}-image batch: {threads} host threads x {per} images, host buffers in and out",
+                   "engine": "reference CPU math engine (MLAS sgemm) under the reference's CDnn"},
+        "cpu_baseline": {"value": round(ips, 3), "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample},
         "e2e": {"value": round(ips, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -202,32 +177,94 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None}
 
 
-class ContractionTimer:
-    """CUDA events around every contraction launch of one instrumented step."""
+class HostedEngine:
+    """A GPU engine from NeoML's factory plus the two things a benchmark needs beyond the NeoML interface: the CUDA
+    stream the engine enqueues on (for events) and the kernel library's launch counter."""
 
-    def __init__(self, torch):
-        self.torch, self.records, self._start = torch, [], None
+    def __init__(self, device: int, precision: int):
+        import torch
+        from neoml_b200 import _capi, cdnn
+        self.torch, self.cdnn = torch, cdnn
+        self.kernels = _capi.load()
+        cdnn.load()
+        self.hosted = ctypes.CDLL(str(cdnn.directory() / "libNeoMathEngine.so"))
+        self.hosted.nb200_engine_stream.restype = ctypes.c_void_p
+        self.hosted.nb200_engine_stream.argtypes = [ctypes.c_void_p]
+        # entry `device` of IGpuMathEngineManager; flags: the reference's TF32 opt-in bit
+        self.engine = cdnn.Engine("manager", device=device, flags=2 if precision == 1 else 0)
+        ptr = self.hosted.nb200_engine_stream(self.engine.ptr)
+        if not ptr:
+            raise SystemExit("the GPU engine NeoML's factory returned is not the B200 engine")
+        self.stream = torch.cuda.ExternalStream(ptr, device=device)
 
-    def begin(self):
-        self._start = self.torch.cuda.Event(enable_timing=True)
-        self._start.record()
+    def record(self, event):
+        # the call also makes the engine launch anything it still holds back for fusion
+        self.hosted.nb200_engine_stream(self.engine.ptr)
+        event.record(self.stream)
 
-    def end(self, kind, flops):
-        e = self.torch.cuda.Event(enable_timing=True)
+    def timed(self, fn) -> float:
+        """Milliseconds of fn() on the engine's stream."""
+        start, stop = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+        self.record(start)
+        fn()
+        self.record(stop)
+        stop.synchronize()
+        return start.elapsed_time(stop)
+
+
+def settle(engine: HostedEngine, step, budget_s: float):
+    """Untimed 20-step blocks until two consecutive blocks agree within 2 % (clocks and power settle on a box that has
+    been idle), bounded by budget_s.  Returns the block times in ms per step."""
+    blocks = []
+    t0 = time.perf_counter()
+    while budget_s > 0 and time.perf_counter() - t0 < budget_s:
+        blocks.append(engine.timed(lambda: [step() for _ in range(20)]) / 20)
+        if len(blocks) >= 2 and abs(blocks[-1] - blocks[-2]) <= 0.02 * blocks[-1]:
+            break
+    return blocks
+
+
+def measure_tf32_peak(torch, seconds: float = 2.0):
+    """Dense TF32 tensor throughput of this GPU, measured the way MEASURED_PEAKS.json's bf16 figure was: a library
+    8192^3 product (torch.matmul with TF32 allowed), best of 10 single calls (burst) and back to back for `seconds`
+    (sustained).  Yardstick only: nothing of the product path runs here."""
+    n = 8192
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        c = torch.empty(n, n, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        best = float("inf")
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(10):
+            s.record()
+            torch.matmul(a, b, out=c)
+            e.record()
+            e.synchronize()
+            best = min(best, s.elapsed_time(e))
+        reps = max(10, int(seconds * 1e3 / best))
+        s.record()
+        for _ in range(reps):
+            torch.matmul(a, b, out=c)
         e.record()
-        self.records.append((kind, flops, self._start, e))
-
-    def totals(self):
-        self.torch.cuda.synchronize()
-        ms = [(k, f, s.elapsed_time(e)) for k, f, s, e in self.records]
-        return sum(f for _, f, _ in ms), sum(t for _, _, t in ms), len(ms), ms
+        e.synchronize()
+        sustained_ms = s.elapsed_time(e) / reps
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    return {"burst_tflops": round(flops / best / 1e9, 1), "sustained_tflops": round(flops / sustained_ms / 1e9, 1),
+            "how": f"torch.matmul fp32 with TF32 allowed, {n}^3: best of 10 (burst), {reps} calls back to back (sustained)"}
 
 
 def run_ours(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from neoml_b200 import _capi, resnet50, sharding
+    from neoml_b200 import cdnn, resnet50, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -237,7 +274,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    lib = _capi.load()
+    eng = HostedEngine(local, args.precision)
+    lib = eng.kernels
     if lib.nb200_device_count() < 1:
         raise SystemExit("libneoml_b200.so sees no sm_100 device")
     if args.kernel_options:
@@ -249,98 +287,42 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     batch = args.batch
-    be = resnet50.EngineBackend(precision=args.precision)
-    weights = be.upload(resnet50.make_weights())
+    model = cdnn.Model.resnet50(resnet50.make_weights())
+    net = cdnn.Net(eng.engine, model)
     rng = np.random.default_rng(1234 + rank)
     host_x = torch.from_numpy(rng.uniform(0, 1, (batch, *IMAGE)).astype(np.float32)).pin_memory()
-    dev_x = host_x.cuda()
-    fuse = not args.unfused
-
-    def eager_step(x):
-        return resnet50.forward(be, weights, x, fuse=fuse)
-
-    step = eager_step
-    if args.graph:
-        # The library allocates nothing and keeps no per-call host state, so a forward pass captures as it is: the
-        # scratch and result tensors come from torch's capture-aware allocator, tensor maps travel as kernel arguments.
-        for _ in range(3):
-            eager_step(dev_x)       # one-time set-up (function attributes, driver entry points) happens outside capture
-        torch.cuda.synchronize()
-        graph_in = [dev_x, torch.empty_like(dev_x), torch.empty_like(dev_x)]   # the device loop and the two e2e buffers
-        graphs = []
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for buf in graph_in:
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    out = eager_step(buf)
-                graphs.append((g, out))
-        torch.cuda.current_stream().wait_stream(side)
-
-        def step(x):
-            for buf, (g, out) in zip(graph_in, graphs):
-                if buf.data_ptr() == x.data_ptr():
-                    g.replay()
-                    return out
-            raise RuntimeError("graph replay needs one of the captured input buffers")
+    dims = (1, batch, 1, IMAGE[0], IMAGE[1], 1, IMAGE[2])
+    net.set_input_ptr("in", host_x.data_ptr(), dims)       # the source blob now holds the batch in HBM
+    host_out = torch.empty(batch * (resnet50.CLASSES + 1), dtype=torch.float32).pin_memory()
+    step = net.run
 
     # ---- device-resident timing -------------------------------------------------------------------------
     sampler = ClockSampler(local)
     sampler.start()
-    # A fresh box needs a moment under load before clocks and power settle (a first timed loop right after three
-    # warm-up steps has measured 15 % slow): a fixed number of extra untimed steps precedes the W warm-up steps.
-    for _ in range(max(args.settle, 0)):
-        step(dev_x)
+    step()
+    settle_blocks = settle(eng, step, args.settle_seconds)
     for _ in range(max(args.warmup, 3)):
-        step(dev_x)
+        step()
     barrier()
     launches0 = lib.nb200_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    start.record()
+    eng.record(start)
     for _ in range(args.steps):
-        probs, idx = step(dev_x)
-    stop.record()
+        step()
+    eng.record(stop)
     barrier()
     launches = lib.nb200_launch_count() - launches0
-    if args.graph:
-        # a replayed graph launches the captured kernels without passing through the library's counter
-        before = lib.nb200_launch_count()
-        eager_step(dev_x)
-        torch.cuda.synchronize()
-        launches = (lib.nb200_launch_count() - before) * args.steps
     ms_total = start.elapsed_time(stop)
 
-    # ---- end to end: pinned host batch -> device -> forward -> result back, double-buffered ---------------------------
-    copy_stream = torch.cuda.Stream()
-    main = torch.cuda.current_stream()
-    bufs = graph_in[1:] if args.graph else [torch.empty_like(dev_x) for _ in range(2)]
-    copied = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-    host_idx = torch.empty(batch, dtype=torch.int32).pin_memory()
-    host_probs = torch.empty((batch, resnet50.CLASSES), dtype=torch.float32).pin_memory()
-
-    def e2e_loop(n):
-        for i in range(n):
-            b = i % 2
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(consumed[b])  # the forward two steps ago has finished reading this buffer
-                bufs[b].copy_(host_x, non_blocking=True)
-                copied[b].record(copy_stream)
-            main.wait_event(copied[b])
-            p, ix = step(bufs[b])
-            consumed[b].record(main)
-            host_idx.copy_(ix, non_blocking=True)
-            host_probs.copy_(p, non_blocking=True)
-        torch.cuda.synchronize()
-
-    for b in range(2):
-        consumed[b].record(main)
-    e2e_loop(2)
+    # ---- end to end: what a NeoML user calls, host buffers in and out --------------------------------------------------
+    def e2e(n):
+        return net.time_steps(n, "probs,argmax", source="in", input_ptr=host_x.data_ptr(),
+                              output_ptr=host_out.data_ptr(), output_bytes=host_out.numel() * 4)
+    e2e(2)
     barrier()
     t0 = time.perf_counter()
-    e2e_loop(args.steps)
+    e2e(args.steps)
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop()
@@ -357,94 +339,184 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant kernel (rank 0, one instrumented step) -----------------------------------------------
+    # ---- roofline of the dominant kernel (rank 0, three instrumented steps) --------------------------------------------
     # The library brackets every contraction launch with CUDA events on its stream (operand preparation, allocations and
-    # host gaps stay outside); the Python timer supplies the flops of each launch, in the same order.
-    timer = ContractionTimer(torch)
-    be_t = resnet50.EngineBackend(precision=args.precision, timer=timer)
+    # host gaps stay outside) and notes the algorithmic flops of the call each launch belongs to.
     timed_steps = 3
     lib.nb200_debug_time_contractions(1)
-    resnet50.forward(be_t, weights, dev_x, fuse=fuse)     # creates the library's events; not counted
+    step()                                                  # creates the library's events; not counted
     torch.cuda.synchronize()
-    timer.records.clear()
-    lib.nb200_debug_time_contractions(1)                   # clears the list
+    lib.nb200_debug_time_contractions(1)                    # clears the list
     for _ in range(timed_steps):
-        resnet50.forward(be_t, weights, dev_x, fuse=fuse)
-    torch.cuda.synchronize()
+        step()
+    eng.record(stop)
+    stop.synchronize()
     lib.nb200_debug_time_contractions(0)
-    flops, _, tc_launches, per_layer = timer.totals()
-    times = (ctypes.c_float * tc_launches)()
-    got = lib.nb200_debug_contraction_times(ctypes.cast(times, ctypes.c_void_p), tc_launches)
-    if got != tc_launches:
-        raise SystemExit(f"the library timed {got} contraction launches, the graph issued {tc_launches}")
-    flops /= timed_steps
-    tc_launches //= timed_steps
+    cap = 4096
+    times, flop = (ctypes.c_float * cap)(), (ctypes.c_double * cap)()
+    got = lib.nb200_debug_contraction_records(ctypes.cast(times, ctypes.c_void_p), ctypes.cast(flop, ctypes.c_void_p), cap)
+    if got <= 0 or got % timed_steps:
+        raise SystemExit(f"the library timed {got} contraction launches over {timed_steps} steps")
+    tc_launches = got // timed_steps
     kernel_ms = [sum(times[i + s * tc_launches] for s in range(timed_steps)) / timed_steps for i in range(tc_launches)]
-    per_layer = [(k, f, kernel_ms[i]) for i, (k, f, _) in enumerate(per_layer[:tc_launches])]
+    layer_flops = [flop[i] for i in range(tc_launches)]
+    flops = sum(layer_flops)
+    expected = resnet50.flops_per_image() * batch
+    if abs(flops - expected) > 1e-6 * expected:
+        raise SystemExit(f"the timed launches account for {flops:.4e} flops, the network has {expected:.4e}")
     tc_ms = sum(kernel_ms)
     if args.layers:
-        names = [sp.name for sp in resnet50.conv_specs()]
-        order = ["stem"]
-        for si, (_, _, blocks, _) in enumerate(resnet50.STAGES):
-            for bi in range(blocks):
-                p = f"s{si + 1}b{bi + 1}"
-                order += ([p + "_down"] if bi == 0 else []) + [p + "_c1", p + "_c2", p + "_c3"]
-        order.append("fc")
-        assert len(order) == len(per_layer) and set(order) == set(names) | {"fc"}
-        for name, (_, f, t) in zip(order, per_layer):
-            print(f"{name:10s} {f / 1e9:9.2f} GFLOP {t:8.3f} ms {f / t / 1e9:8.1f} TFLOP/s", file=sys.stderr)
+        for i, (f, t) in enumerate(zip(layer_flops, kernel_ms)):
+            print(f"launch {i:3d} {f / 1e9:9.2f} GFLOP {t:8.3f} ms {f / t / 1e9:8.1f} TFLOP/s", file=sys.stderr)
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     if peaks_path.exists():
         pk = json.loads(peaks_path.read_text())
-        peak_tf, peak_src = float(pk["bf16_tflops_sustained"]), "MEASURED_PEAKS.json bf16_tflops_sustained"
+        peak_tf, peak_src = float(pk["bf16_tflops_sustained"]), "MEASURED_PEAKS.json bf16_tflops_sustained (of measured)"
     else:
-        peak_tf, peak_src = 1390.7, "fallback (MEASURED_PEAKS.json absent): sustained cuBLAS bf16 measured on this pool"
+        peak_tf, peak_src = 1390.7, "fallback: sustained cuBLAS bf16, an earlier measurement (of fallback)"
     achieved_tf = flops / (tc_ms * 1e-3) / 1e12
     mma_per_product = 3 if args.precision == 0 else 1
-    eff_peak = peak_tf / 2 / mma_per_product  # TF32 runs at half the bf16 rate; 3xTF32 issues three MMAs per product
+    tf32 = None if args.no_peak else measure_tf32_peak(torch)
+    if tf32 is not None:
+        eff_peak, eff_src = tf32["sustained_tflops"] / mma_per_product, "TF32 sustained, measured in this run"
+    else:
+        eff_peak, eff_src = peak_tf / 2 / mma_per_product, "bf16 sustained / 2 (not measured in this run)"
+    act_bytes = resnet50.contraction_bytes_per_image() * batch + resnet50.weight_bytes()
     roofline = {
         "bound": "tensor", "kernel": "contraction_tc_kernel (tcgen05 kind::tf32, implicit-GEMM conv + FC)",
         "achieved": round(achieved_tf, 2), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(achieved_tf / peak_tf, 4),
         "peak_source": peak_src,
-        # ncu dram__bytes_read.sum + dram__bytes_write.sum of the 54 contraction launches of one batch-64 step is 5.44 GB
-        # = 85.0 MB per image (profiles/resnet50_b256_launch_list.md); activations dominate, so it scales with the batch
-        "traffic": round(85.0e6 * batch / max(tc_launches, 1) / 1e9, 4), "traffic_unit": "GB per launch (average)",
-        "algorithmic_bytes_per_launch_gb": round(28.05 * batch / 256 / max(tc_launches, 1), 4),
+        "traffic": round(TRAFFIC_MB_PER_IMAGE * 1e6 * batch / max(tc_launches, 1) / 1e9, 4),
+        "traffic_unit": "GB per launch (average)",
+        "traffic_source": TRAFFIC_SOURCE,
+        "algorithmic_bytes_per_launch_gb": round(act_bytes / max(tc_launches, 1) / 1e9, 4),
         "launches_per_step": tc_launches, "ms_per_step_in_kernel": round(tc_ms, 3),
         "algorithmic_gflop_per_step": round(flops / 1e9, 2),
+        "tf32_peak_measured": tf32,
         "effective_peak_for_this_arithmetic": round(eff_peak, 1),
+        "effective_peak_source": f"{eff_src}, / {mma_per_product} MMAs per product",
         "frac_of_effective_peak": round(achieved_tf / eff_peak, 4),
-        "frac_ceiling_for_this_arithmetic": round(eff_peak / peak_tf, 4),
-        "note": "peak is dense bf16; TF32 = 1/2 of it, 3xTF32 = 1/6 (algorithmic flops counted once)",
+        "whole_step_frac_of_effective_peak": round(flops / (ms_total / args.steps * 1e-3) / 1e12 / eff_peak, 4),
+        "note": "peak is dense bf16; this arithmetic is TF32 (3 MMAs per product in the default 3xTF32 mode), "
+                "algorithmic flops counted once",
     }
 
     images = batch * world * args.steps
+    ms_step = ms_total / args.steps
     line = {
         "metric": METRIC, "value": round(images / (ms_total * 1e-3), 2), "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_total / args.steps, 3),
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (3xTF32 split on tcgen05, fp32 accumulate)" if args.precision == 0 else "tf32",
         "data": "synthetic",
-        "config": {"workload": "resnet50_v1.5_infer_b256_224x224x3" if batch == 256 else f"resnet50_v1.5_infer_b{batch}",
+        "config": {"workload": WORKLOAD if batch == 256 else f"resnet50_v1.5_infer_b{batch}",
                    "per_gpu_batch": batch, "global_batch": batch * world, "parallelism": f"batch-sharded x{world}",
-                   "fused_epilogues": fuse, "cuda_graph": bool(args.graph), "settle_steps_before_warmup": max(args.settle, 0), "l2": "inputs and activations larger than L2 (154 MB batch, 822 MB stem output)"},
-        "clocks": clocks,
+                   "call": "NeoML CDnn::RunOnce on the engine from IGpuMathEngineManager::CreateMathEngine",
+                   "fused_epilogues": "by the engine (conv -> add -> ReLU calls folded at run time)",
+                   "settle_blocks_ms_per_step": [round(b, 3) for b in settle_blocks],
+                   "l2": "inputs and activations larger than L2 (154 MB batch, 822 MB stem output)"},
+        "clocks": dict(clocks, ms_times_mhz=round(ms_step * clocks["sm_mhz"], 1) if clocks.get("sm_mhz") else None),
         "e2e": {"value": round(images / (e2e_ms * 1e-3), 2), "unit": UNIT,
-                "h2d_bytes_per_step": host_x.numel() * 4, "d2h_bytes_per_step": host_idx.numel() * 4 + host_probs.numel() * 4,
+                "h2d_bytes_per_step": host_x.numel() * 4, "d2h_bytes_per_step": host_out.numel() * 4,
                 "ms_per_step": round(e2e_ms / args.steps, 3)},
         "gpu_launches": int(launches),
         "roofline": roofline,
     }
     if world == 1 and not args.no_cpu_baseline:
+        # in a process of its own: the reference's NeoMathEngine library and the hosted one carry the same soname
         try:
-            ips, ms, cores, kind, sample = cpu_reference_run(per_thread_batch=1, rounds_budget_s=args.cpu_seconds,
-                                                             min_rounds=2, max_rounds=50, warm=1)
-            line["cpu_baseline"] = {"value": round(ips, 3), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
+            r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "3", "--warmup", "1",
+                                "--batch", str(batch)], capture_output=True, text=True, timeout=600)
+            ref = json.loads(r.stdout.strip().splitlines()[-1])
+            line["cpu_baseline"] = ref.get("cpu_baseline") or {"value": None, "unit": UNIT, "cores": 0, "kind": "reference",
+                                                               "sample": ref.get("unavailable", "no line")}
         except Exception as exc:  # the baseline is reported, never required
-            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": f"failed: {exc}"}
     print(json.dumps(line), flush=True)
+    net.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+# DRAM traffic of the contraction launches: dram__bytes_read.sum + dram__bytes_write.sum of the 54 launches of one
+# batch-64 step in an ncu capture, per image; activations dominate, so it scales with the batch.  A constant from
+# that capture, not a figure of this run.
+TRAFFIC_MB_PER_IMAGE = 85.0
+TRAFFIC_SOURCE = "constant: ncu capture of a batch-64 step (54 launches, 5.44 GB), scaled by the batch; not measured in this run"
+
+
+def run_sweep(args):
+    """Configuration 5's scaling sweep the way NeoML distributes a network: ONE process, the engines made by
+    CreateDistributedCudaMathEngines, one host thread per engine, every engine a replica of the ResNet-50 CDnn on its
+    own per-GPU batch (host buffers in and out every step).  One JSON line per (engines, batch)."""
+    import torch
+    from neoml_b200 import cdnn, resnet50
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --sweep needs CUDA devices: the product path has no CPU fallback")
+    cdnn.load()
+    visible = torch.cuda.device_count()
+    model = cdnn.Model.resnet50(resnet50.make_weights())
+    batches = [1, 32, 256, 1024]
+    x = torch.rand(max(batches), *IMAGE).pin_memory()
+    rows = []
+    for n in [g for g in (1, 2, 4, 8) if g <= min(visible, args.gpus)]:
+        reps = cdnn.Replicas("gpu", model, devices=list(range(n)))
+        out = torch.empty(n * max(batches) * (resnet50.CLASSES + 1)).pin_memory()
+        for b in batches:
+            for i in range(n):
+                reps.net(i).set_input_ptr("in", x.data_ptr(), (1, b, 1, IMAGE[0], IMAGE[1], 1, IMAGE[2]))
+            steps = {1: 200, 32: 60, 256: args.steps, 1024: max(4, args.steps // 4)}[b]
+            per_out = b * (resnet50.CLASSES + 1) * 4
+            secs = reps.time_steps(max(args.warmup, 3), steps, "in", x.data_ptr(), 0, "probs,argmax", out.data_ptr(), per_out)
+            row = {"mode": "sweep", "engines": n, "per_gpu_batch": b, "steps": steps,
+                   "images_per_s": round(n * b * steps / secs, 1), "ms_per_step": round(1e3 * secs / steps, 3),
+                   "call": "CreateDistributedCudaMathEngines, one host thread per engine, host buffers in and out"}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+        reps.close()
+    base = {r["per_gpu_batch"]: r["images_per_s"] for r in rows if r["engines"] == 1}
+    print(json.dumps({"mode": "sweep_summary", "scaling_vs_one_engine": {
+        f"b{r['per_gpu_batch']}_x{r['engines']}": round(r["images_per_s"] / base[r["per_gpu_batch"]], 3) for r in rows}}))
+
+
+def run_transformer(args):
+    """Configuration 4 as a NeoML CDnn on the GPU engine: 12 x CTransformerEncoderLayer, 64 x 512 x 768, 12 heads,
+    FFN 3072, GELU, mask input.  Algorithmic flops per layer: 4 FC products of 32768 x 768 x 768 (Q, K, V, output),
+    the FFN pair 32768 x 768 x 3072 twice, and the two attention products 768 x (512 x 512 x 64)."""
+    import numpy as np
+    import torch
+    from neoml_b200 import cdnn
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --transformer needs a CUDA device: the product path has no CPU fallback")
+    eng = HostedEngine(0, args.precision)
+    layers, b, s, hid, heads, ffn = 12, 64, 512, 768, 12, 3072
+    model = cdnn.Model.transformer(layers, hid, heads, ffn, seed=7, sigma=0.02, mask=True)
+    net = cdnn.Net(eng.engine, model)
+    rng = np.random.default_rng(404)
+    net.set_input("in", rng.standard_normal((b, s, hid)).astype(np.float32))
+    net.set_input("mask", np.zeros((s, s), np.float32), (1, 1, 1, 1, s, 1, s))
+    tokens = b * s
+    flops = layers * (2.0 * tokens * hid * hid * 4 + 2.0 * tokens * hid * ffn * 2 + 2.0 * (b * heads) * s * s * (hid // heads) * 2)
+    net.run()
+    settle(eng, net.run, args.settle_seconds)
+    lib = eng.kernels
+    launches0 = lib.nb200_launch_count()
+    ms = eng.timed(lambda: [net.run() for _ in range(args.steps)]) / args.steps
+    launches = (lib.nb200_launch_count() - launches0) // args.steps
+    tf32 = None if args.no_peak else measure_tf32_peak(torch)
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak_tf = float(json.loads(peaks_path.read_text())["bf16_tflops_sustained"]) if peaks_path.exists() else 1390.7
+    mma = 3 if args.precision == 0 else 1
+    eff = (tf32["sustained_tflops"] if tf32 else peak_tf / 2) / mma
+    tf = flops / ms / 1e9
+    print(json.dumps({"mode": "transformer", "workload": "transformer_encoder_12x_b64_s512_h768 (CDnn::RunOnce)",
+                      "ms_per_step": round(ms, 3), "sequences_per_s": round(b / ms * 1e3, 1), "launches_per_step": int(launches),
+                      "algorithmic_gflop_per_step": round(flops / 1e9, 1),
+                      "roofline": {"bound": "tensor (whole step, bandwidth-bound passes included)", "achieved": round(tf, 1),
+                                   "peak": peak_tf, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4),
+                                   "tf32_peak_measured": tf32, "effective_peak_for_this_arithmetic": round(eff, 1),
+                                   "frac_of_effective_peak": round(tf / eff, 3)}}))
+    net.close()
 
 
 def run_ops(args):
@@ -457,7 +529,7 @@ def run_ops(args):
         raise SystemExit("bench.py --ops needs a CUDA device: the product path has no CPU fallback")
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
-    peak_src = "MEASURED_PEAKS.json hbm_gbs" if peaks_path.exists() else "fallback: 6.65 TB/s measured on this pool earlier"
+    peak_src = "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks_path.exists() else "fallback: 6.65 TB/s, an earlier measurement (of fallback)"
     dev = "cuda"
     n = args.batch            # images of config 3; --batch 128 halves every tensor (for profiler captures)
     tb = max(1, 64 * n // 256)  # sequences of config 4
@@ -599,6 +671,10 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.sweep:
+        run_sweep(args)
+    elif args.transformer:
+        run_transformer(args)
     elif args.products:
         run_products(args)
     elif args.ops:

@@ -50,10 +50,7 @@ SIGNATURES = {
     "nb200_error_string": (C.c_char_p, [_i]),
     "nb200_device_status": (_i, [_vp, _i]),
     "nb200_last_cuda_error": (C.c_char_p, []),
-    "nb200_debug_set_contraction_trace": (None, [_vp, _i, _i]),
     "nb200_launch_count": (C.c_uint64, []),
-    "nb200_debug_time_contractions": (None, [_i]),
-    "nb200_debug_contraction_times": (_i, [_vp, _i]),
     "nb200_multiply_matrix_by_transposed_matrix": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _EP, _i]),
     "nb200_batch_multiply_matrix_by_transposed_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
     "nb200_matrix_product_scratch_floats": (C.c_size_t, [_i, _i, _i, _i, _i]),
@@ -86,6 +83,16 @@ SIGNATURES = {
     "nb200_blob_resize_image": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp]),
 }
 
+# Diagnostic entry points (neoml_b200/csrc/diagnostics.h): exported for the benchmark and the tests, not part of the
+# product interface the public header declares
+DIAGNOSTICS = {
+    "nb200_debug_set_contraction_trace": (None, [_vp, _i, _i]),
+    "nb200_debug_time_contractions": (None, [_i]),
+    "nb200_debug_contraction_times": (_i, [_vp, _i]),
+    "nb200_debug_contraction_records": (_i, [_vp, _vp, _i]),
+    "nb200_debug_wait_probe": (_i, [_vp, C.c_ulonglong]),
+}
+
 _lib = None
 
 
@@ -105,7 +112,7 @@ def load() -> C.CDLL:
         if not LIB_PATH.exists():
             raise RuntimeError(f"{LIB_PATH} is missing: run `python -m neoml_b200.build` (no fallback exists)")
         lib = C.CDLL(str(LIB_PATH))
-        for name, (res, args) in SIGNATURES.items():
+        for name, (res, args) in {**SIGNATURES, **DIAGNOSTICS}.items():
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args

@@ -67,11 +67,30 @@ def build_kernels(verbose: bool = False) -> Path:
     return out
 
 
+def reference_dir() -> Path:
+    return Path(os.environ.get("NEOML_REFERENCE_DIR", "/root/reference"))
+
+
+def build_hosted(verbose: bool = False) -> Path | None:
+    """make -C neoml_b200/host: NeoML (unmodified) + a libNeoMathEngine.so with this repository's factory and engine +
+    the CDnn harness, into neoml_b200/lib/host.  Needs a NeoML checkout; where there is none the prebuilt files stay."""
+    out = LIB / "host" / "libcdnn_host.so"
+    if not (reference_dir() / "NeoML" / "src").exists():
+        return out if out.exists() else None
+    r = subprocess.run(["make", "-C", str(ROOT / "host"), f"-j{min(8, os.cpu_count() or 1)}", f"REF={reference_dir()}",
+                        f"PYTHON={sys.executable}"], capture_output=True, text=True)
+    if verbose:
+        print(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError(f"hosted build failed:\n{r.stdout[-3000:]}{r.stderr[-3000:]}")
+    return out
+
+
 def build_engine(verbose: bool = False) -> Path | None:
     """g++ build of the IMathEngine implementation.  The class is generated/compiled against the NeoMathEngine headers
     of a NeoML checkout; the base-class symbols (IMathEngine's key functions, the exception handler, CBlobDesc) stay
     undefined in this library and bind at load time to the libNeoMathEngine.so of the hosting NeoML process."""
-    ref = Path(os.environ.get("NEOML_REFERENCE_DIR", "/root/reference"))
+    ref = reference_dir()
     eng = ROOT / "engine"
     out = LIB / "libNeoMathEngineB200.so"
     sources = sorted(eng.glob("*.cpp"))
@@ -105,6 +124,7 @@ def main() -> None:
     verbose = "-v" in sys.argv
     print(build_kernels(verbose))
     print(build_engine(verbose))
+    print(build_hosted(verbose))
 
 
 if __name__ == "__main__":

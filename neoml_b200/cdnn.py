@@ -14,6 +14,7 @@ from pathlib import Path
 import numpy as np
 
 HOST_DIR = Path(__file__).resolve().parent / "lib" / "host"
+_dir = HOST_DIR
 _lib = None
 
 _fp = C.POINTER(C.c_float)
@@ -21,14 +22,27 @@ _ip = C.POINTER(C.c_int)
 
 
 def available() -> bool:
-    return (HOST_DIR / "libcdnn_host.so").exists()
+    return (_dir / "libcdnn_host.so").exists()
+
+
+def use_directory(path) -> None:
+    """Before the first load(): take libcdnn_host.so (and the NeoML / NeoMathEngine libraries beside it) from `path`
+    instead of neoml_b200/lib/host -- e.g. a build of the same harness on an unmodified NeoMathEngine."""
+    global _dir
+    if _lib is not None:
+        raise RuntimeError("the libraries are loaded already")
+    _dir = Path(path)
+
+
+def directory() -> Path:
+    return _dir
 
 
 def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = HOST_DIR / "libcdnn_host.so"
+    path = _dir / "libcdnn_host.so"
     if not path.exists():
         raise RuntimeError(f"{path} is missing: run `make -C neoml_b200/host` where a NeoML checkout is available")
     lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
@@ -66,6 +80,9 @@ def load():
     lib.cdnn_replicas_time_steps.restype = C.c_double
     lib.cdnn_replicas_time_steps.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_char_p, C.c_void_p, C.c_longlong,
                                              C.c_char_p, C.c_void_p, C.c_longlong]
+    if hasattr(lib, "cdnn_selftest_free_while_pending"):
+        lib.cdnn_selftest_free_while_pending.argtypes = [C.c_void_p, _fp]
+        lib.cdnn_selftest_abort_distributed.argtypes = [_ip, C.c_char_p, C.c_int]
     _lib = lib
     return lib
 
@@ -225,6 +242,24 @@ class Net:
         if self.ptr and self.owned:
             load().cdnn_net_destroy(self.ptr)
         self.ptr = None
+
+
+def selftest_free_while_pending(engine: Engine) -> float:
+    """See cdnn_selftest_free_while_pending in host/cdnn_host.cpp: largest difference between a convolution + ReLU
+    whose source blob was freed right after the convolution call and the same with the source kept alive."""
+    worst = C.c_float(-1.0)
+    if load().cdnn_selftest_free_while_pending(engine.ptr, C.byref(worst)) != 0:
+        _fail("selftest_free_while_pending")
+    return worst.value
+
+
+def selftest_abort_distributed(devices=(0, 1)) -> str:
+    """See cdnn_selftest_abort_distributed: returns the message of the AllReduce that followed a peer's abort."""
+    d = (C.c_int * 2)(*devices)
+    message = C.create_string_buffer(1024)
+    if load().cdnn_selftest_abort_distributed(d, message, len(message)) != 0:
+        _fail("selftest_abort_distributed")
+    return message.value.decode(errors="replace")
 
 
 class Replicas:

@@ -1,5 +1,6 @@
 // C-ABI entry points for the dense contractions: argument checks, then one description for the shared kernels.
 #include "contraction.cuh"
+#include "diagnostics.h"
 
 using namespace nb200;
 
@@ -210,13 +211,20 @@ void nb200_debug_time_contractions(int enable)
 int nb200_debug_contraction_times(float* ms, int capacity)
 {
 	if(ms == nullptr || capacity < 0) return NB200_EINVAL;
-	return contraction_times(ms, capacity);
+	return contraction_times(ms, nullptr, capacity);
+}
+
+int nb200_debug_contraction_records(float* ms, double* flops, int capacity)
+{
+	if(ms == nullptr || flops == nullptr || capacity < 0) return NB200_EINVAL;
+	return contraction_times(ms, flops, capacity);
 }
 
 int nb200_multiply_matrix_by_transposed_matrix(void* stream, const float* a, int m, int k, int lda,
 	const float* b, int n, int ldb, float* c, int ldc, const nb200_epilogue* epi, int precision)
 {
 	if(m < 0 || n < 0 || k <= 0 || lda < k || ldb < k || ldc < n) return NB200_EINVAL;
+	set_call_flops(2.0 * m * n * k);
 	ContractionParams p = {};
 	p.A = a; p.B = b; p.C = c;
 	p.M = m; p.N = n; p.K = k;
@@ -232,6 +240,7 @@ int nb200_batch_multiply_matrix_by_transposed_matrix(void* stream, int batch, co
 	int k, const float* b, int n, float* c, const nb200_epilogue* epi, int precision)
 {
 	if(batch < 0 || m < 0 || n < 0 || k <= 0) return NB200_EINVAL;
+	set_call_flops(2.0 * batch * m * n * k);
 	ContractionParams p = {};
 	p.A = a; p.B = b; p.C = c;
 	p.M = m; p.N = n; p.K = k;
@@ -259,6 +268,7 @@ int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int ba
 	int lda, const float* b, int n, int ldb, float* c, int ldc, float* scratch, const nb200_epilogue* epi, int precision)
 {
 	if(batch < 0 || m < 0 || n < 0 || k <= 0 || lda < k || ldb < k || ldc < n) return NB200_EINVAL;
+	set_call_flops(2.0 * batch * m * n * k);
 	ContractionParams p = {};
 	p.A = a; p.B = b; p.C = c;
 	p.M = m; p.N = n; p.K = k;
@@ -303,6 +313,7 @@ int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int
 	const float* b, int n, float* c, const nb200_epilogue* epi, int precision)
 {
 	if(batch < 0 || m < 0 || n < 0 || k <= 0) return NB200_EINVAL;
+	set_call_flops(2.0 * batch * m * n * k);
 	ContractionParams p = {};
 	p.A = a; p.B = b; p.C = c;
 	p.M = m; p.N = n; p.K = k;
@@ -319,6 +330,7 @@ int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int
 int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
 	float* scratch, const nb200_epilogue* epi, int precision)
 {
+	if(d != nullptr) set_call_flops(2.0 * d->batch * d->ho * d->wo * d->k * d->r * d->s * d->c);
 	return blob_convolution(stream, d, x, filter, y, scratch, scratch != nullptr ? convolution_scratch_floats(d, true) : 0,
 		epi, precision);
 }
@@ -335,7 +347,8 @@ int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, con
 	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && d->batch > 0 && d->k > 0 && d->r > 0 && d->s > 0
 		&& d->h > 0 && d->w > 0 && d->stride_h > 0 && d->stride_w > 0 && d->pad_h >= 0 && d->pad_w >= 0
 		&& d->ho == 1 + (d->h - d->r + 2 * d->pad_h) / d->stride_h && d->wo == 1 + (d->w - d->s + 2 * d->pad_w) / d->stride_w
-		&& plan_row_window(d, &win) && x != nullptr && filter != nullptr && y != nullptr) {
+		&& plan_row_window(d, &win) && x != nullptr && filter != nullptr && y != nullptr
+		&& scratchFloats >= win.imageFloats + 2 * win.filterFloats + 16 && !gather_forced()) {
 		if(device_status_word() == nullptr) return NB200_ENODEVICE;
 		float* xs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
 		float* fs = xs + (win.imageFloats + 3) / 4 * 4;

@@ -59,7 +59,8 @@ extern "C" int nb200_blob_convolution_static_scratch(void* stream, const nb200_c
 	// the room for split-K partial results is optional: without it a few-tile convolution runs unsplit
 	const size_t need = nb200::convolution_scratch_floats(desc, false);
 	if(need == 0) {
-		// this shape reads its operands in place: the plain entry point already works without memory of any kind
+		// only a descriptor with a non-positive channel, filter-count or filter-size field needs no room: the plain
+		// entry point answers it (with NB200_EINVAL) without memory of any kind
 		return nb200_blob_convolution(stream, desc, x, filter, y, nullptr, epi, precision);
 	}
 	if(need > static_cast<size_t>(NB200_STATIC_SCRATCH_FLOATS)) return NB200_ETOOBIG;

@@ -126,7 +126,7 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-	int* status, int site)
+	int* status, int site, uint64_t limit_ns = WAIT_LIMIT_NS)
 {
 	if(mbar_try_wait(bar, parity)) return true;
 	// the wall clock is looked at only after a few thousand failed polls: reading %globaltimer is slow, and an ordinary
@@ -138,7 +138,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 			if(*abort_flag != 0) return false;
 			const uint64_t now = global_timer_ns();
 			if(t0 == 0) t0 = now;
-			else if(now - t0 > WAIT_LIMIT_NS) break;
+			else if(now - t0 > limit_ns) break;
 		}
 	}
 	*abort_flag = 1;

@@ -114,9 +114,13 @@ void set_contraction_trace(unsigned long long* buffer, int steps, int options);
 int launch_contraction_tc(const ContractionParams& p, int batch, cudaStream_t stream);
 int launch_contraction_simt(const ContractionParams& p, int batch, cudaStream_t stream);
 
-// Event timing of the contraction launches (see nb200_debug_time_contractions)
+// Event timing of the contraction launches (diagnostics.h)
 void time_contractions(bool enable);
-int contraction_times(float* ms, int capacity);
+int contraction_times(float* ms, double* flops, int capacity);
+// algorithmic flops of the entry-point call that is about to launch (noted beside each timed launch)
+void set_call_flops(double flops);
+// true when diagnostic option 16 asks for the cp.async gather kernel even where TMA applies
+bool gather_forced();
 // false when diagnostic option 64 asks for ordinary launches instead of programmatic dependent ones
 bool overlap_launches();
 // Scratch floats of a convolution (api_contraction.cu); the room for split-K partial results comes last and is optional.

@@ -1013,9 +1013,11 @@ struct LaunchTiming {
 	std::mutex mutex;
 	bool enabled = false;
 	std::vector<std::pair<cudaEvent_t, cudaEvent_t>> events;
+	std::vector<double> flops;   // algorithmic flops of the entry-point call each launch belongs to
 	size_t used = 0;
 };
 LaunchTiming g_timing;
+thread_local double t_callFlops = 0.0;
 
 // the next pair of events (created on first use, reused afterwards); false when timing is off
 bool timing_events(cudaEvent_t* start, cudaEvent_t* stop)
@@ -1029,7 +1031,9 @@ bool timing_events(cudaEvent_t* start, cudaEvent_t* stop)
 			return false;
 		}
 		g_timing.events.emplace_back(a, b);
+		g_timing.flops.push_back(0.0);
 	}
+	g_timing.flops[g_timing.used] = t_callFlops;
 	*start = g_timing.events[g_timing.used].first;
 	*stop = g_timing.events[g_timing.used].second;
 	++g_timing.used;
@@ -1198,7 +1202,12 @@ void time_contractions(bool enable)
 	if(enable) g_timing.used = 0;
 }
 
-int contraction_times(float* ms, int capacity)
+void set_call_flops(double flops)
+{
+	t_callFlops = flops;
+}
+
+int contraction_times(float* ms, double* flops, int capacity)
 {
 	std::lock_guard<std::mutex> lock(g_timing.mutex);
 	int n = 0;
@@ -1210,6 +1219,7 @@ int contraction_times(float* ms, int capacity)
 			return -1;
 		}
 		ms[n] = t;
+		if(flops != nullptr) flops[n] = g_timing.flops[i];
 	}
 	return n;
 }
@@ -1217,6 +1227,11 @@ int contraction_times(float* ms, int capacity)
 bool overlap_launches()
 {
 	return !(g_traceOptions & 64);
+}
+
+bool gather_forced()
+{
+	return (g_traceOptions & 16) != 0;
 }
 
 void set_contraction_trace(unsigned long long* buffer, int steps, int options)

@@ -77,9 +77,36 @@ int check_launch()
 	return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? NB200_ENODEVICE : NB200_ELAUNCH;
 }
 
+// One warp waits, with the bounded wait every kernel of the library uses, on a barrier that nothing ever completes.
+// After `limit_ns` the wait gives up: the status word receives (0x7e << 8 | 1), the kernel returns normally and the
+// context stays usable -- the path a hung pipeline would take, made to happen on purpose and cheaply.
+__global__ void __launch_bounds__(32) wait_probe_kernel(int* status, unsigned long long limit_ns)
+{
+	__shared__ uint64_t bar;
+	__shared__ int abortFlag;
+	if(threadIdx.x == 0) {
+		mbar_init(&bar, 1);
+		mbar_init_fence();
+		abortFlag = 0;
+	}
+	__syncthreads();
+	if(threadIdx.x == 0) mbar_wait_bounded(&bar, 0, &abortFlag, status, (0x7e << 8) | 1, limit_ns);
+	__syncthreads();
+}
+
 } // namespace nb200
 
 using namespace nb200;
+
+extern "C" __attribute__((visibility("default"))) int nb200_debug_wait_probe(void* stream, unsigned long long limit_ns)
+{
+	int* status = device_status_word();
+	if(status == nullptr) return NB200_ENODEVICE;
+	if(limit_ns == 0 || limit_ns > 1000000000ull) return NB200_EINVAL; // a second at most
+	wait_probe_kernel<<<1, 32, 0, as_stream(stream)>>>(status, limit_ns);
+	count_launch(1);
+	return check_launch();
+}
 
 extern "C" {
 

@@ -2,6 +2,7 @@
 // diagonal scalings, row softmax, generalised transpose, row/column arg-max.  All are HBM-bound: accesses are
 // coalesced along the contiguous dimension, reductions use warp shuffles, 16-byte accesses where alignment allows.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <float.h>
 
 namespace nb200 {
@@ -73,11 +74,15 @@ __global__ void __launch_bounds__(256) col_scale_kernel(const float* __restrict_
 }
 
 // y[b][w] (+)= sum_h x[b][h][w]: a block owns 32 columns of one batch entry and a slice of the rows; threads are
-// (32 columns) x (8 row lanes); partial sums meet in shared memory, slices meet through atomics when rows are split.
+// (32 columns) x (8 row lanes); partial sums meet in shared memory.  When the rows are split over several blocks
+// (rowSlices > 1) those blocks form one thread-block cluster along y: the block of slice 0 reads the others' sums
+// from their shared memory and adds them in slice order, so the result is the same bits on every run (no atomics).
 __global__ void __launch_bounds__(256) sum_rows_kernel(float* __restrict__ y, const float* __restrict__ x,
 	int height, int width, int rowSlices, int add)
 {
+	namespace cg = cooperative_groups;
 	__shared__ float part[8][33];
+	__shared__ float total[32];
 	const int b = blockIdx.z;
 	const int w = blockIdx.x * 32 + (threadIdx.x & 31);
 	const int lane8 = threadIdx.x >> 5;
@@ -92,12 +97,23 @@ __global__ void __launch_bounds__(256) sum_rows_kernel(float* __restrict__ y, co
 	}
 	part[lane8][threadIdx.x & 31] = acc;
 	__syncthreads();
-	if(lane8 == 0 && w < width) {
-		float s = 0.f;
+	float s = 0.f;
+	if(lane8 == 0) {
 #pragma unroll
 		for(int i = 0; i < 8; ++i) s += part[i][threadIdx.x];
+		total[threadIdx.x] = s;
+	}
+	if(rowSlices > 1) {
+		cg::cluster_group cluster = cg::this_cluster();
+		cluster.sync();
+		if(slice == 0 && lane8 == 0) {
+			for(int r = 1; r < rowSlices; ++r) s += cluster.map_shared_rank(total, r)[threadIdx.x];
+		}
+		cluster.sync(); // the other blocks' shared memory stays alive until it has been read
+	}
+	if(slice == 0 && lane8 == 0 && w < width) {
 		float* dst = y + static_cast<size_t>(b) * width + w;
-		if(rowSlices > 1 || add) atomicAdd(dst, s); else *dst = s;
+		*dst = add ? *dst + s : s;
 	}
 }
 
@@ -106,7 +122,9 @@ __global__ void __launch_bounds__(256) sum_rows_kernel(float* __restrict__ y, co
 __global__ void __launch_bounds__(256) sum_rows_vec_kernel(float* __restrict__ y, const float* __restrict__ x,
 	int height, int width, int rowSlices, int add)
 {
+	namespace cg = cooperative_groups;
 	__shared__ float4 part[4][64];
+	__shared__ float4 total[64];
 	const int b = blockIdx.z;
 	const int q = threadIdx.x & 63;             // float4 lane inside the block's 256 columns
 	const int lane4 = threadIdx.x >> 6;         // row lane
@@ -126,16 +144,31 @@ __global__ void __launch_bounds__(256) sum_rows_vec_kernel(float* __restrict__ y
 	}
 	part[lane4][q] = acc;
 	__syncthreads();
-	if(lane4 == 0 && w4 < width4) {
-		float4 s = part[0][q];
+	float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+	if(lane4 == 0) {
+		s = part[0][q];
 #pragma unroll
 		for(int i = 1; i < 4; ++i) { s.x += part[i][q].x; s.y += part[i][q].y; s.z += part[i][q].z; s.w += part[i][q].w; }
-		float* dst = y + static_cast<size_t>(b) * width + 4 * w4;
-		if(rowSlices > 1 || add) {
-			atomicAdd(dst, s.x); atomicAdd(dst + 1, s.y); atomicAdd(dst + 2, s.z); atomicAdd(dst + 3, s.w);
-		} else {
-			*reinterpret_cast<float4*>(dst) = s;
+		total[q] = s;
+	}
+	if(rowSlices > 1) {
+		cg::cluster_group cluster = cg::this_cluster();
+		cluster.sync();
+		if(slice == 0 && lane4 == 0) {
+			for(int r = 1; r < rowSlices; ++r) {
+				const float4 o = cluster.map_shared_rank(total, r)[q];
+				s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+			}
 		}
+		cluster.sync();
+	}
+	if(slice == 0 && lane4 == 0 && w4 < width4) {
+		float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(b) * width + 4 * w4);
+		if(add) {
+			const float4 o = *dst;
+			s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+		}
+		*dst = s;
 	}
 }
 
@@ -467,7 +500,8 @@ int nb200_sum_matrix_rows(void* stream, int batch, float* y, const float* x, int
 	if(batch > 65535) return NB200_ETOOBIG;
 	NB200_REQUIRE_DEVICE();
 	const int colBlocks = (width + 31) / 32;
-	// split the rows when (columns x batch) alone cannot fill the machine
+	// split the rows when (columns x batch) alone cannot fill the machine; the slices of one column block form a
+	// thread-block cluster (at most 8 blocks, the portable cluster size)
 	int rowSlices = 1;
 	const long long blocks = static_cast<long long>(colBlocks) * batch;
 	const int target = sm_count() * 4;
@@ -475,27 +509,30 @@ int nb200_sum_matrix_rows(void* stream, int batch, float* y, const float* x, int
 		rowSlices = static_cast<int>((target + blocks - 1) / blocks);
 		const int maxSlices = height / 64;
 		if(rowSlices > maxSlices) rowSlices = maxSlices;
+		if(rowSlices > 8) rowSlices = 8;
 		if(rowSlices < 1) rowSlices = 1;
 	}
-	int launches = 1;
-	if(rowSlices > 1 && !add) {
-		// slices accumulate with atomics, so the destination starts from zero
-		if(cudaMemsetAsync(y, 0, static_cast<size_t>(batch) * width * sizeof(float), as_stream(stream)) != cudaSuccess) {
-			cudaGetLastError();
-			return NB200_ELAUNCH;
-		}
-		++launches;
-	}
+	const int launches = 1;
 	if(height == 0) {
 		if(!add) cudaMemsetAsync(y, 0, static_cast<size_t>(batch) * width * sizeof(float), as_stream(stream));
 		return check_launch();
 	}
+	cudaLaunchConfig_t config = {};
+	config.blockDim = dim3(256);
+	config.stream = as_stream(stream);
+	cudaLaunchAttribute attribute[1];
+	attribute[0].id = cudaLaunchAttributeClusterDimension;
+	attribute[0].val.clusterDim.x = 1;
+	attribute[0].val.clusterDim.y = rowSlices;
+	attribute[0].val.clusterDim.z = 1;
+	config.attrs = attribute;
+	config.numAttrs = rowSlices > 1 ? 1 : 0;
 	if(width % 4 == 0 && aligned16(x) && aligned16(y)) {
-		dim3 grid((width / 4 + 63) / 64, rowSlices, batch);
-		sum_rows_vec_kernel<<<grid, 256, 0, as_stream(stream)>>>(y, x, height, width, rowSlices, add);
+		config.gridDim = dim3((width / 4 + 63) / 64, rowSlices, batch);
+		cudaLaunchKernelEx(&config, sum_rows_vec_kernel, y, x, height, width, rowSlices, add);
 	} else {
-		dim3 grid(colBlocks, rowSlices, batch);
-		sum_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(y, x, height, width, rowSlices, add);
+		config.gridDim = dim3(colBlocks, rowSlices, batch);
+		cudaLaunchKernelEx(&config, sum_rows_kernel, y, x, height, width, rowSlices, add);
 	}
 	count_launch(launches);
 	return check_launch();

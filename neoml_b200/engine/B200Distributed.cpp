@@ -127,6 +127,8 @@ void CB200MathEngine::AllReduce( const CFloatHandle& handle, int size )
 	if( comm == nullptr ) return; // a single engine is its own average
 	CCommHolder* holder = static_cast<CCommHolder*>( comm );
 	enter();
+	// a peer that has given up will not join: nothing is launched for it to be waited for
+	if( holder->group->aborted.load() ) { raise( "Stopping due to error in another thread." ); return; }
 	float* data = raw( handle );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( g_nccl.AllReduce( data, data, static_cast<size_t>( size ), ncclFloat32, ncclAvgOp, holder->comm, s ) != ncclSuccessCode ) {
@@ -141,6 +143,7 @@ void CB200MathEngine::Broadcast( const CFloatHandle& handle, int size, int root 
 	if( comm == nullptr ) return;
 	CCommHolder* holder = static_cast<CCommHolder*>( comm );
 	enter();
+	if( holder->group->aborted.load() ) { raise( "Stopping due to error in another thread." ); return; }
 	float* data = raw( handle );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( g_nccl.Bcast( data, data, static_cast<size_t>( size ), ncclFloat32, root, holder->comm, s ) != ncclSuccessCode ) {

@@ -545,30 +545,46 @@ CDNN_API int cdnn_net_get_output( void* netPtr, const char* name, void* host, lo
 	} );
 }
 
-// Wall-clock seconds of `steps` x ( [host -> source blob] RunOnce [sink -> host] ) on this net, for the CPU baseline
-// and other host-timed runs.  input/output may be NULL (then the source keeps its blob / nothing is read back except
-// a final 4-byte read that waits for the device).
-CDNN_API double cdnn_net_time_steps( void* netPtr, int steps, const char* sourceName, const float* input, const char* sinkName,
+// Wall-clock seconds of `steps` x ( [host -> source blob] RunOnce [sinks -> host] ) on this net.  sinkNames is one
+// sink or several separated by commas; their blobs are written to `output` one after the other.  input / output may
+// be NULL (then the source keeps its blob / nothing is read back except a final 4-byte read that waits for the device).
+CDNN_API double cdnn_net_time_steps( void* netPtr, int steps, const char* sourceName, const float* input, const char* sinkNames,
 	void* output, long long outputBytes )
 {
 	double seconds = -1;
 	guarded( [&] {
 		CNet* net = static_cast<CNet*>( netPtr );
 		CPtr<CSourceLayer> source = sourceName != nullptr ? CheckCast<CSourceLayer>( net->dnn->GetLayer( sourceName ) ) : nullptr;
-		CPtr<CSinkLayer> sink = CheckCast<CSinkLayer>( net->dnn->GetLayer( sinkName ) );
+		std::vector<CPtr<CSinkLayer>> sinks;
+		{
+			std::string names( sinkNames );
+			size_t at = 0;
+			while( at <= names.size() ) {
+				const size_t comma = names.find( ',', at );
+				const std::string one = names.substr( at, comma == std::string::npos ? std::string::npos : comma - at );
+				sinks.push_back( CheckCast<CSinkLayer>( net->dnn->GetLayer( one.c_str() ) ) );
+				if( comma == std::string::npos ) break;
+				at = comma + 1;
+			}
+		}
 		const auto t0 = std::chrono::steady_clock::now();
 		for( int i = 0; i < steps; ++i ) {
 			if( input != nullptr ) source->GetBlob()->CopyFrom( input );
 			net->dnn->RunOnce();
 			if( output != nullptr ) {
-				CPtr<CDnnBlob> blob = sink->GetBlob();
-				if( outputBytes < static_cast<long long>( blob->GetDataSize() ) * 4 ) throw std::logic_error( "output buffer too small" );
-				if( blob->GetDataType() == CT_Int ) blob->CopyTo( static_cast<int*>( output ) ); else blob->CopyTo( static_cast<float*>( output ) );
+				char* at = static_cast<char*>( output );
+				for( CPtr<CSinkLayer>& sink : sinks ) {
+					CPtr<CDnnBlob> blob = sink->GetBlob();
+					const long long bytes = static_cast<long long>( blob->GetDataSize() ) * 4;
+					if( at + bytes > static_cast<char*>( output ) + outputBytes ) throw std::logic_error( "output buffer too small" );
+					if( blob->GetDataType() == CT_Int ) blob->CopyTo( reinterpret_cast<int*>( at ) ); else blob->CopyTo( reinterpret_cast<float*>( at ) );
+					at += bytes;
+				}
 			}
 		}
 		if( output == nullptr ) {
 			// any device-to-host exchange completes the work issued before it
-			CPtr<CDnnBlob> blob = sink->GetBlob();
+			CPtr<CDnnBlob> blob = sinks[0]->GetBlob();
 			int word = 0;
 			if( blob->GetDataType() == CT_Int ) {
 				net->engine->DataExchangeRaw( &word, blob->GetData<int>(), sizeof( word ) );
@@ -674,4 +690,99 @@ CDNN_API double cdnn_replicas_time_steps( void* replicas, int warmup, int steps,
 		seconds = std::max( seconds, std::chrono::duration<double>( finished[i] - t0 ).count() );
 	}
 	return seconds;
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// Engine checks made of raw IMathEngine calls (what layers do, in orders a test wants to control)
+
+// A convolution whose source blob is freed right after the call, before the in-place ReLU that follows it -- the order
+// in which a CDnn in reuse-memory mode releases a layer's inputs (NeoML/src/Dnn/BaseLayer.cpp, setAllocatedBlobs).
+// The shape is chosen so that the engine's work memory for the call (the prepared filter: 113 x 3 x 3 x 32 floats)
+// falls in the size class of the freed source (32 x 32 x 32 floats).  Writes the largest absolute difference between
+// the result with the early free and the result with the source kept alive; 0 is the only right answer.
+CDNN_API int cdnn_selftest_free_while_pending( void* enginePtr, float* maxDifference )
+{
+	return guarded( [&] {
+		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
+		const int h = 32, w = 32, c = 32, k = 113;
+		CSplitMix rng( 2718 );
+		std::vector<float> x( h * w * c ), f( k * 9 * c ), b( k );
+		for( float& v : x ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+		for( float& v : f ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+		for( float& v : b ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+		auto run = [&]( bool earlyFree ) {
+			CPtr<CDnnBlob> src = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 1, h, w, c );
+			CPtr<CDnnBlob> flt = CDnnBlob::CreateTensor( e, CT_Float, { 1, k, 1, 3, 3, 1, c } );
+			CPtr<CDnnBlob> bias = CDnnBlob::CreateVector( e, CT_Float, k );
+			CPtr<CDnnBlob> out = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 1, h, w, k );
+			CPtr<CDnnBlob> zero = CDnnBlob::CreateVector( e, CT_Float, 1 );
+			src->CopyFrom( x.data() );
+			flt->CopyFrom( f.data() );
+			bias->CopyFrom( b.data() );
+			zero->Fill( 0.f );
+			std::unique_ptr<CConvolutionDesc> desc( e.InitBlobConvolution( src->GetDesc(), 1, 1, 1, 1, 1, 1, flt->GetDesc(),
+				out->GetDesc() ) );
+			const CConstFloatHandle freeTerm = bias->GetData();
+			e.BlobConvolution( *desc, src->GetData(), flt->GetData(), &freeTerm, out->GetData() );
+			if( earlyFree ) src = nullptr;
+			e.VectorReLU( out->GetData(), out->GetData(), out->GetDataSize(), zero->GetData() );
+			std::vector<float> y( static_cast<size_t>( out->GetDataSize() ) );
+			out->CopyTo( y.data() );
+			return y;
+		};
+		const std::vector<float> kept = run( false ), freed = run( true );
+		float worst = 0.f;
+		for( size_t i = 0; i < kept.size(); ++i ) worst = std::max( worst, std::fabs( kept[i] - freed[i] ) );
+		*maxDifference = worst;
+	} );
+}
+
+// Two distributed engines (CreateDistributedCudaMathEngines on devices[0..1]).  First one AllReduce from two host
+// threads: every element must come out as the mean.  Then, between steps and with no collective in flight, engine 1
+// calls AbortDistributed; the next AllReduce on engine 0 has to end with NeoML's "Stopping due to error in another
+// thread." instead of waiting for a peer that will not come.  `message` receives what that call raised.
+CDNN_API int cdnn_selftest_abort_distributed( const int* devices, char* message, int messageSize )
+{
+	return guarded( [&] {
+		SetMathEngineExceptionHandler( GetExceptionHandler() );
+		IMathEngine* raw[2] = { nullptr, nullptr };
+		CreateDistributedCudaMathEngines( raw, 2, devices, 0 );
+		std::unique_ptr<IMathEngine> engines[2] = { std::unique_ptr<IMathEngine>( raw[0] ), std::unique_ptr<IMathEngine>( raw[1] ) };
+		if( !engines[0] || !engines[1] ) throw std::logic_error( "the distributed factory returned no engines" );
+		if( !engines[0]->IsDistributed() || engines[1]->GetDistributedInfo().Threads != 2 ) throw std::logic_error( "distributed info is wrong" );
+		const int n = 1000;
+		std::string errors[2];
+		{
+			std::thread workers[2];
+			for( int r = 0; r < 2; ++r ) {
+				workers[r] = std::thread( [&, r] {
+					try {
+						CFloatHandleVar data( *engines[r], n );
+						std::vector<float> host( n );
+						for( int i = 0; i < n; ++i ) host[i] = static_cast<float>( ( r + 1 ) * i );
+						engines[r]->DataExchangeTyped<float>( data.GetHandle(), host.data(), n );
+						engines[r]->AllReduce( data.GetHandle(), n );
+						engines[r]->DataExchangeTyped<float>( host.data(), data.GetHandle(), n );
+						for( int i = 0; i < n; ++i ) {
+							if( host[i] != 1.5f * i ) throw std::logic_error( "AllReduce did not produce the mean" );
+						}
+					} catch( const std::exception& ex ) {
+						errors[r] = ex.what();
+					}
+				} );
+			}
+			for( std::thread& t : workers ) t.join();
+		}
+		if( !errors[0].empty() || !errors[1].empty() ) throw std::logic_error( "AllReduce: " + errors[0] + " " + errors[1] );
+		engines[1]->AbortDistributed();
+		std::string raised;
+		try {
+			CFloatHandleVar data( *engines[0], n );
+			engines[0]->VectorFill( data.GetHandle(), 1.f, n );
+			engines[0]->AllReduce( data.GetHandle(), n );
+		} catch( const std::exception& ex ) {
+			raised = ex.what();
+		}
+		std::snprintf( message, messageSize, "%s", raised.c_str() );
+	} );
 }

@@ -72,6 +72,33 @@ def flops_per_image(height: int = 224, width: int = 224) -> float:
     return total
 
 
+def contraction_bytes_per_image(height: int = 224, width: int = 224) -> float:
+    """Algorithmic bytes the convolutions and the FC layer move per image: every input read once, every output
+    written once, the shortcut read once by the block's last convolution (it rides in that epilogue); fp32."""
+    def out(sz, k, s, p):
+        return 1 + (sz + 2 * p - k) // s
+    h, w = out(height, 7, 2, 3), out(width, 7, 2, 3)
+    floats = height * width * 3 + h * w * 64
+    h, w = out(h, 3, 2, 1), out(w, 3, 2, 1)
+    c_in = 64
+    for mid, o, blocks, stride in STAGES:
+        for bi in range(blocks):
+            s = stride if bi == 0 else 1
+            h2, w2 = out(h, 3, s, 1), out(w, 3, s, 1)
+            floats += h * w * c_in + h * w * mid              # 1x1 reduce
+            floats += h * w * mid + h2 * w2 * mid             # 3x3
+            floats += h2 * w2 * mid + 2 * h2 * w2 * o         # 1x1 expand: input, shortcut, output
+            if bi == 0:
+                floats += h * w * c_in + h2 * w2 * o          # projection shortcut
+            h, w, c_in = h2, w2, o
+    floats += 2048 + CLASSES
+    return 4.0 * floats
+
+
+def weight_bytes() -> float:
+    return 4.0 * (sum(sp.c_out * sp.k * sp.k * sp.c_in + sp.c_out for sp in conv_specs()) + CLASSES * 2048 + CLASSES)
+
+
 RESIDUAL_BRANCH_SCALE = 0.25  # folded BatchNorm scale of each block's last convolution
 
 

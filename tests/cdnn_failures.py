@@ -1,0 +1,88 @@
+"""TEST INFRASTRUCTURE.  Failure paths of the B200 engine under NeoML, each made to happen on the host or by a wait
+that is built to run out -- nothing here faults, traps or hangs a GPU.  Runs in a process of its own (see
+tests/cdnn_parity.py) and prints one JSON line.
+
+    python tests/cdnn_failures.py wait_timeout | memory_limit | free_while_pending | abort_distributed
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from neoml_b200 import _capi, cdnn  # noqa: E402
+
+
+def small_net(engine):
+    rng = np.random.default_rng(5)
+    f = rng.uniform(-1, 1, (16, 3, 3, 8)).astype(np.float32)
+    b = rng.uniform(-1, 1, 16).astype(np.float32)
+    x = rng.uniform(-1, 1, (2, 12, 12, 8)).astype(np.float32)
+    net = cdnn.Net(engine, cdnn.Model.conv(f, b, padding=(1, 1)))
+    net.set_input("in", x)
+    return net
+
+
+def wait_timeout():
+    """A kernel's bounded wait runs out (20 ms limit, a barrier nothing completes): the status word is set, the engine
+    reports it at the next device-to-host exchange and clears it, and the next pass is clean."""
+    lib = _capi.load()
+    engine = cdnn.Engine("gpu")
+    net = small_net(engine)
+    net.run()
+    first = net.output("out")
+    assert lib.nb200_device_status(None, 0) == 0
+    assert lib.nb200_debug_wait_probe(None, 20_000_000) == 0
+    status = lib.nb200_device_status(None, 0)           # reading synchronises the stream the probe ran on
+    raised = ""
+    try:
+        net.run()
+        net.output("out")
+    except cdnn.CDnnError as exc:
+        raised = str(exc)
+    after = lib.nb200_device_status(None, 0)
+    net.run()
+    again = net.output("out")
+    return {"status_after_probe": status, "raised": raised, "status_after_report": after,
+            "clean_pass_matches": bool(np.array_equal(first, again)), "status_at_end": lib.nb200_device_status(None, 0)}
+
+
+def memory_limit():
+    """memoryLimit exceeded -> the exception handler's OnMemoryError (std::bad_alloc under NeoML's handler); an engine
+    with room runs the same net."""
+    small = cdnn.Engine("gpu", memory_limit=1 << 20)    # 1 MiB
+    raised = ""
+    try:
+        rng = np.random.default_rng(6)
+        net = cdnn.Net(small, cdnn.Model.conv(rng.uniform(-1, 1, (64, 3, 3, 64)).astype(np.float32), None, padding=(1, 1)))
+        net.set_input("in", rng.uniform(-1, 1, (8, 56, 56, 64)).astype(np.float32))   # 6.4 MB: over the limit
+        net.run()
+    except cdnn.CDnnError as exc:
+        raised = str(exc)
+    small.close()
+    roomy = cdnn.Engine("gpu", memory_limit=1 << 30)
+    net = small_net(roomy)
+    net.run()
+    ok = bool(np.isfinite(net.output("out")).all())
+    return {"raised": raised, "engine_with_room_runs": ok}
+
+
+def free_while_pending():
+    engine = cdnn.Engine("gpu")
+    return {"max_difference": cdnn.selftest_free_while_pending(engine)}
+
+
+def abort_distributed():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    cdnn.load()
+    return {"raised": cdnn.selftest_abort_distributed((0, 1))}
+
+
+if __name__ == "__main__":
+    print(json.dumps({"case": sys.argv[1], **globals()[sys.argv[1]]()}))

@@ -29,8 +29,7 @@ def test_every_declaration_cites_the_reference_interface():
     text = (ROOT / "include" / "neoml_b200.h").read_text()
     # each compute entry point is preceded by a comment naming the IMathEngine method and its line
     for name in _declared():
-        if name in ("nb200_version", "nb200_device_count", "nb200_error_string", "nb200_device_status", "nb200_last_cuda_error", "nb200_debug_set_contraction_trace",
-                    "nb200_debug_time_contractions", "nb200_debug_contraction_times",
+        if name in ("nb200_version", "nb200_device_count", "nb200_error_string", "nb200_device_status", "nb200_last_cuda_error",
                     "nb200_launch_count", "nb200_mobilenetv2_scratch_floats", "nb200_blob_convolution_scratch_floats", "nb200_vector_copy_int",
                     "nb200_vector_fill_int"):
             continue
@@ -40,6 +39,14 @@ def test_every_declaration_cites_the_reference_interface():
             continue
         # the citing comment sits directly above the declaration (a desc struct may lie between them)
         assert "NME.h:" in head[-1400:], name
+
+
+def test_diagnostics_stay_out_of_the_public_header():
+    text = (ROOT / "include" / "neoml_b200.h").read_text()
+    assert "nb200_debug_" not in text
+    lib = capi.load()
+    for name in capi.DIAGNOSTICS:
+        assert hasattr(lib, name)
 
 
 def test_error_strings():
@@ -72,3 +79,30 @@ def test_no_cpu_fallback_without_a_device():
     rc = lib.nb200_multiply_matrix_by_transposed_matrix(None, C.addressof(buf), 4, 4, 4, C.addressof(buf), 4, 4,
                                                         C.addressof(buf), 4, None, 0)
     assert rc == capi.ENODEVICE
+
+
+def test_hosted_library_exports_the_reference_factory_symbols():
+    """libNeoMathEngine.so of neoml_b200/lib/host is NeoML's math-engine library with this repository's factory: the
+    GPU entry points keep the reference's names and signatures (NeoMathEngine.h:1282,1305,1311), so NeoML links
+    against it unchanged."""
+    path = ROOT / "neoml_b200" / "lib" / "host" / "libNeoMathEngine.so"
+    if not path.exists():
+        pytest.skip("hosted libraries not built (needs a NeoML checkout)")
+    data = path.read_bytes()
+    for mangled in (b"_ZN5NeoML19CreateGpuMathEngineEmi", b"_ZN5NeoML26CreateGpuMathEngineManagerEv",
+                    b"_ZN5NeoML32CreateDistributedCudaMathEnginesEPPNS_11IMathEngineEiPKim",
+                    b"_ZN5NeoML19CreateCpuMathEngineEm", b"_ZN5NeoML29GetMathEngineExceptionHandlerEv"):
+        assert mangled in data, mangled
+
+
+def test_engine_implements_every_method_the_benchmark_graphs_call():
+    """tests/golden/engine_call_closure.json lists, per configuration, the IMathEngine methods NeoML calls while it
+    loads and runs that CDnn (recorded by tests/closure/make_closure.py on the CPU engine behind a recording proxy).
+    Each of them must have a hand-written definition in neoml_b200/engine -- the generated stubs only raise."""
+    import json
+    closure = json.loads((ROOT / "tests" / "golden" / "engine_call_closure.json").read_text())
+    source = "".join(p.read_text() for p in (ROOT / "neoml_b200" / "engine").glob("*.cpp"))
+    defined = set(re.findall(r"CB200MathEngine::(\w+)\s*\(", source))
+    for config, calls in closure.items():
+        missing = sorted(set(calls) - defined)
+        assert not missing, f"{config}: {missing}"

@@ -1,0 +1,47 @@
+"""Failure paths of the engine under NeoML (tests/cdnn_failures.py, one process per case): a bounded device wait that
+runs out, the memory limit, a blob freed while the call that reads it is still recorded, AbortDistributed.
+No case faults, traps or hangs a GPU: waits are built to expire after 20 ms, the abort happens between steps."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+
+
+def run_case(name: str) -> dict:
+    if not (ROOT / "neoml_b200" / "lib" / "host" / "libcdnn_host.so").exists():
+        pytest.skip("hosted NeoML libraries not built")
+    r = subprocess.run([sys.executable, str(ROOT / "tests" / "cdnn_failures.py"), name], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, f"{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_the_engine_stays_usable():
+    row = run_case("wait_timeout")
+    assert row["status_after_probe"] == 0x7E01
+    assert "bounded-wait timeout" in row["raised"]
+    assert row["status_after_report"] == 0 and row["status_at_end"] == 0
+    assert row["clean_pass_matches"]
+
+
+def test_memory_limit_raises_the_memory_error():
+    row = run_case("memory_limit")
+    assert "bad_alloc" in row["raised"], row
+    assert row["engine_with_room_runs"]
+
+
+def test_source_freed_while_the_convolution_is_still_recorded():
+    assert run_case("free_while_pending")["max_difference"] == 0.0
+
+
+def test_abort_distributed_ends_the_peers_next_collective():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    row = run_case("abort_distributed")
+    assert "Stopping due to error in another thread." in row["raised"]

@@ -557,3 +557,53 @@ def test_matrix_products_random_shapes(ops, oracle):
         for scratch in (True, False):
             got3 = host(ops.MultiplyMatrixByMatrix(dev(a3), dev(b3), use_scratch=scratch))
             assert gate_err(got3, want3) < TOL_FP32, f"mm case {case}: batch={batch} m={m} k={k} n={n} scratch={scratch}"
+
+
+def test_forced_gather_on_a_few_channel_convolution_stays_inside_its_scratch():
+    """The 3-channel stem shape with the gather kernel forced (diagnostic option 16): the row-window path must step
+    aside BEFORE it writes anything, the channel-padding path then runs inside the caller's scratch; a guard region
+    behind the scratch stays untouched and the result equals the one computed without scratch."""
+    import ctypes as C
+    from neoml_b200 import _capi, ops as O
+    lib = _capi.load()
+    n, h, w, c, k = 2, 37, 41, 3, 64
+    ho, wo = O.conv_output_size(h, 7, 3, 2, 1), O.conv_output_size(w, 7, 3, 2, 1)
+    desc = _capi.ConvDesc(n, h, w, c, k, 7, 7, 3, 3, 2, 2, 1, 1, ho, wo)
+    need = lib.nb200_blob_convolution_scratch_floats(C.byref(desc))
+    guard = 1 << 16
+    sentinel = 12345.0
+    buf = torch.full((need + guard,), sentinel, dtype=torch.float32, device="cuda")
+    x, f, b = dev(cases.uniform(71, (n, h, w, c))), dev(cases.uniform(72, (k, 7, 7, c))), dev(cases.uniform(73, (k,)))
+    epi = _capi.Epilogue(b.data_ptr(), None, 0, O.ACT_RELU, 0.0, 0)
+    got = torch.empty((n, ho, wo, k), dtype=torch.float32, device="cuda")
+    want = torch.empty_like(got)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    lib.nb200_debug_set_contraction_trace(None, 0, 16)
+    try:
+        _capi.check("BlobConvolution", lib.nb200_blob_convolution(stream, C.byref(desc), C.c_void_p(x.data_ptr()),
+                    C.c_void_p(f.data_ptr()), C.c_void_p(got.data_ptr()), C.c_void_p(buf.data_ptr()), C.byref(epi), O.PREC_3XTF32))
+        _capi.check("BlobConvolution", lib.nb200_blob_convolution(stream, C.byref(desc), C.c_void_p(x.data_ptr()),
+                    C.c_void_p(f.data_ptr()), C.c_void_p(want.data_ptr()), None, C.byref(epi), O.PREC_3XTF32))
+        torch.cuda.synchronize()
+    finally:
+        lib.nb200_debug_set_contraction_trace(None, 0, 0)
+    assert bool((buf[need:] == sentinel).all()), "the call wrote past the scratch it was given"
+    assert lib.nb200_device_status(stream, 0) == 0
+    # two gather instantiations (16-byte pieces over widened pixels / single floats): same products, another order
+    assert gate_err(got.cpu().numpy(), want.cpu().numpy()) < 1e-5
+
+
+def test_sliced_row_sums_are_the_same_bits_on_every_run(ops, oracle):
+    """Tall, narrow matrices split their rows over a thread-block cluster; the slices are added in a fixed order
+    (distributed shared memory, no atomics), so repeated runs agree bit for bit."""
+    for bsz, h, w in ((1, 20000, 64), (2, 4096, 37), (3, 1000, 128)):
+        m = cases.uniform(81, (bsz * h * w,))
+        md = dev(m)
+        first = ops.SumMatrixRows(bsz, md, h, w)
+        assert gate_err(host(first), oracle.sum_matrix_rows(bsz, m, h, w)) < 1e-5
+        for _ in range(5):
+            assert torch.equal(ops.SumMatrixRows(bsz, md, h, w), first)
+        init = cases.uniform(82, (bsz * w,))
+        acc = ops.SumMatrixRows(bsz, md, h, w, result=dev(init), add=True)
+        assert gate_err(host(acc), oracle.sum_matrix_rows(bsz, m, h, w) + init.reshape(bsz, w)) < 1e-5

@@ -49,11 +49,14 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
         capi.check("BlobConvolution", lib.nb200_blob_convolution(
             _stream(), C.byref(desc), _ptr(x), _ptr(f), _ptr(want), _ptr(scratch), C.byref(epi), ops.PREC_3XTF32))
         torch.cuda.synchronize()
-        reserved = torch.cuda.memory_reserved()
+        # torch's own gauge only sees torch's allocator; the driver's free-memory figure sees any cudaMalloc
+        reserved, free_before = torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0]
         capi.check("BlobConvolution(static scratch)", lib.nb200_blob_convolution_static_scratch(
             _stream(), C.byref(desc), _ptr(x), _ptr(f), _ptr(got), C.byref(epi), ops.PREC_3XTF32))
         torch.cuda.synchronize()
         assert torch.cuda.memory_reserved() == reserved
+        if call == 1:   # the first call may load the kernels' code (module loading is lazy); the second one must not move
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert lib.nb200_device_status(_stream(), 0) == 0
         assert torch.equal(got, want), f"call {call}"
 
@@ -83,3 +86,29 @@ def test_other_shapes_give_the_same_result_as_the_plain_entry_point():
         _stream(), C.byref(desc), _ptr(x), _ptr(f), _ptr(got), None, ops.PREC_3XTF32))
     torch.cuda.synchronize()
     assert torch.equal(got, ops.BlobConvolution(x, f, padding=(1, 1)))
+
+
+@pytest.mark.parametrize("shape", [(4, 16, 16, 64, 64, "prepared filter"), (1, 7, 7, 512, 512, "split K")])
+def test_the_work_space_paths_match_caller_scratch_bit_for_bit(shape):
+    """The two ways the fixed array is written besides the padded image: the prepared filter (32-channel K blocks and
+    at least 1024 output positions) and the split-K partial results taken from the array's tail."""
+    lib = capi.load()
+    n, h, w, c, k, _ = shape
+    desc, ho, wo = _desc(n, h, w, c, k, 3, 3, (1, 1), (1, 1))
+    need = lib.nb200_blob_convolution_scratch_floats(C.byref(desc))
+    assert 0 < need <= STATIC_SCRATCH_FLOATS
+    x = torch.from_numpy(cases.uniform(9500, (n, h, w, c))).cuda()
+    f = torch.from_numpy(cases.uniform(9501, (k, 3, 3, c))).cuda()
+    b = torch.from_numpy(cases.uniform(9502, (k,))).cuda()
+    epi = capi.Epilogue(b.data_ptr(), None, 0, ops.ACT_NONE, 0.0, 0)
+    want = torch.empty((n, ho, wo, k), dtype=torch.float32, device="cuda")
+    scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+    capi.check("BlobConvolution", lib.nb200_blob_convolution(
+        _stream(), C.byref(desc), _ptr(x), _ptr(f), _ptr(want), _ptr(scratch), C.byref(epi), ops.PREC_3XTF32))
+    for call in range(2):
+        got = torch.full_like(want, float("nan"))
+        capi.check("BlobConvolution(static scratch)", lib.nb200_blob_convolution_static_scratch(
+            _stream(), C.byref(desc), _ptr(x), _ptr(f), _ptr(got), C.byref(epi), ops.PREC_3XTF32))
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"call {call}"
+    assert lib.nb200_device_status(_stream(), 0) == 0
