@@ -115,6 +115,16 @@ typedef struct nb200_conv_desc {
 NB200_API size_t nb200_blob_convolution_scratch_floats(const nb200_conv_desc* desc);
 NB200_API int nb200_blob_convolution(void* stream, const nb200_conv_desc* desc, const float* x,
 	const float* filter, float* y, float* scratch, const nb200_epilogue* epi, int precision);
+/* The filter-only part of that preparation, made once and kept by the caller for as long as the filter's values do
+ * not change (inference: for ever): nb200_blob_convolution_prepared_filter_floats(desc) floats (0: this shape prepares
+ * nothing from the filter alone), filled by nb200_blob_convolution_prepare_filter for one `precision`; then
+ * nb200_blob_convolution_with_prepared_filter is IDnnEngine::BlobConvolution (NME.h:751-756) without the per-call
+ * filter pass.  `prepared` NULL behaves exactly like nb200_blob_convolution; results are the same bits either way. */
+NB200_API size_t nb200_blob_convolution_prepared_filter_floats(const nb200_conv_desc* desc);
+NB200_API int nb200_blob_convolution_prepare_filter(void* stream, const nb200_conv_desc* desc, const float* filter,
+	float* prepared, int precision);
+NB200_API int nb200_blob_convolution_with_prepared_filter(void* stream, const nb200_conv_desc* desc, const float* x,
+	const float* filter, const float* prepared, float* y, float* scratch, const nb200_epilogue* epi, int precision);
 /* No counterpart in the reference.  The same convolution for callers that cannot provide scratch memory at the moment
  * of the call (all device memory already in their own pool; a loop that must not stall on cudaMalloc; a fixed memory
  * budget): the work space (prepared filter, padded image) is a fixed array of NB200_STATIC_SCRATCH_FLOATS floats inside

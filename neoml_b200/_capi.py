@@ -60,6 +60,9 @@ SIGNATURES = {
     "nb200_multiply_matrix_by_matrix": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _EP, _i]),
     "nb200_blob_convolution_scratch_floats": (C.c_size_t, [C.POINTER(ConvDesc)]),
     "nb200_blob_convolution": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _vp, _EP, _i]),
+    "nb200_blob_convolution_prepared_filter_floats": (C.c_size_t, [C.POINTER(ConvDesc)]),
+    "nb200_blob_convolution_prepare_filter": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _i]),
+    "nb200_blob_convolution_with_prepared_filter": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _vp, _vp, _EP, _i]),
     "nb200_blob_convolution_static_scratch": (_i, [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _EP, _i]),
     "nb200_blob_channelwise_convolution": (_i, [_vp, C.POINTER(ChConvDesc), _vp, _vp, _vp, _vp, _i, _f]),
     "nb200_mobilenetv2_scratch_floats": (C.c_size_t, [C.POINTER(Mbv2Desc)]),

@@ -165,6 +165,17 @@ __global__ void __launch_bounds__(256) widen_filter_rows_kernel(const float* __r
 	}
 }
 
+// the two filter forms of the row-window path: rows widened to 32 floats, then their lo parts / rounded copies
+void prepare_window_filter(void* stream, const nb200_conv_desc* d, const WindowPlan* win, const float* filter, float* out,
+	int precision)
+{
+	widen_filter_rows_kernel<<<grid_for(static_cast<long long>(win->filterFloats), 256, 8), 256, 0, as_stream(stream)>>>(
+		filter, out, d->k, d->r, d->s, d->c, win->c4);
+	prepare_filter_kernel<<<grid_for(static_cast<long long>(win->filterFloats), 256, 8), 256, 0, as_stream(stream)>>>(
+		out, out + win->filterFloats, static_cast<long long>(win->filterFloats), precision == NB200_PREC_3XTF32 ? 0 : 1);
+	count_launch(2);
+}
+
 bool wants_channel_padding(const nb200_conv_desc* d)
 {
 	const bool pointwise = d->r == 1 && d->s == 1 && d->pad_h == 0 && d->pad_w == 0 && d->stride_h == 1 && d->stride_w == 1;
@@ -332,7 +343,49 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 {
 	if(d != nullptr) set_call_flops(2.0 * d->batch * d->ho * d->wo * d->k * d->r * d->s * d->c);
 	return blob_convolution(stream, d, x, filter, y, scratch, scratch != nullptr ? convolution_scratch_floats(d, true) : 0,
-		epi, precision);
+		epi, precision, nullptr);
+}
+
+size_t nb200_blob_convolution_prepared_filter_floats(const nb200_conv_desc* d)
+{
+	if(d == nullptr || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0 || d->ho <= 0 || d->wo <= 0 || d->batch <= 0) return 0;
+	WindowPlan win;
+	if(plan_row_window(d, &win)) return 2 * win.filterFloats;
+	const bool pointwise = d->r == 1 && d->s == 1 && d->pad_h == 0 && d->pad_w == 0 && d->stride_h == 1 && d->stride_w == 1;
+	const long long kk = static_cast<long long>(d->r) * d->s * d->c;
+	const bool tmaShape = (pointwise ? d->c % 4 == 0 : d->c % 32 == 0) && kk % 4 == 0;
+	if(!tmaShape || static_cast<long long>(d->batch) * d->ho * d->wo < PREPARE_B_MIN_ROWS) return 0;
+	return prepared_filter_floats(d->k, d->r, d->s, d->c);
+}
+
+int nb200_blob_convolution_prepare_filter(void* stream, const nb200_conv_desc* d, const float* filter, float* prepared,
+	int precision)
+{
+	const size_t floats = nb200_blob_convolution_prepared_filter_floats(d);
+	if(floats == 0) return NB200_OK;
+	if(filter == nullptr || prepared == nullptr || !aligned16(prepared)
+		|| (precision != NB200_PREC_3XTF32 && precision != NB200_PREC_TF32)) {
+		return NB200_EINVAL;
+	}
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	WindowPlan win;
+	if(plan_row_window(d, &win)) {
+		prepare_window_filter(stream, d, &win, filter, prepared, precision);
+	} else {
+		const long long n = static_cast<long long>(d->k) * d->r * d->s * d->c;
+		prepare_filter_kernel<<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>(filter, prepared, n,
+			precision == NB200_PREC_3XTF32 ? 0 : 1);
+		count_launch(1);
+	}
+	return check_launch();
+}
+
+int nb200_blob_convolution_with_prepared_filter(void* stream, const nb200_conv_desc* d, const float* x, const float* filter,
+	const float* prepared, float* y, float* scratch, const nb200_epilogue* epi, int precision)
+{
+	if(d != nullptr) set_call_flops(2.0 * d->batch * d->ho * d->wo * d->k * d->r * d->s * d->c);
+	return blob_convolution(stream, d, x, filter, y, scratch, scratch != nullptr ? convolution_scratch_floats(d, true) : 0,
+		epi, precision, nb200_blob_convolution_prepared_filter_floats(d) > 0 ? prepared : nullptr);
 }
 
 } // extern "C"
@@ -340,7 +393,7 @@ int nb200_blob_convolution(void* stream, const nb200_conv_desc* d, const float* 
 namespace nb200 {
 
 int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
-	float* scratch, size_t scratchFloats, const nb200_epilogue* epi, int precision)
+	float* scratch, size_t scratchFloats, const nb200_epilogue* epi, int precision, const float* prepared)
 {
 	if(d == nullptr) return NB200_EINVAL;
 	WindowPlan win;
@@ -351,15 +404,17 @@ int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, con
 		&& scratchFloats >= win.imageFloats + 2 * win.filterFloats + 16 && !gather_forced()) {
 		if(device_status_word() == nullptr) return NB200_ENODEVICE;
 		float* xs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
-		float* fs = xs + (win.imageFloats + 3) / 4 * 4;
-		float* fprep = fs + win.filterFloats;
+		const float* fs = prepared;
+		const float* fprep = prepared != nullptr ? prepared + win.filterFloats : nullptr;
 		pad_image_kernel<<<grid_for(static_cast<long long>(win.imageFloats / 4), 256, 16), 256, 0, as_stream(stream)>>>(
 			x, xs, d->batch, d->h, d->w, d->c, win.hp, win.wp, win.c4, d->pad_h, d->pad_w);
-		widen_filter_rows_kernel<<<grid_for(static_cast<long long>(win.filterFloats), 256, 8), 256, 0, as_stream(stream)>>>(
-			filter, fs, d->k, d->r, d->s, d->c, win.c4);
-		prepare_filter_kernel<<<grid_for(static_cast<long long>(win.filterFloats), 256, 8), 256, 0, as_stream(stream)>>>(
-			fs, fprep, static_cast<long long>(win.filterFloats), precision == NB200_PREC_3XTF32 ? 0 : 1);
-		count_launch(3);
+		count_launch(1);
+		if(prepared == nullptr) {
+			float* widened = xs + (win.imageFloats + 3) / 4 * 4;
+			prepare_window_filter(stream, d, &win, filter, widened, precision);
+			fs = widened;
+			fprep = widened + win.filterFloats;
+		}
 		int rc = check_launch();
 		if(rc != NB200_OK) return rc;
 		ContractionParams p = {};
@@ -399,7 +454,7 @@ int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, con
 		padded.c = c4;
 		const size_t used = static_cast<size_t>(fs + taps * c4 - scratch);
 		return blob_convolution(stream, &padded, xs, fs, y, fs + taps * c4, scratchFloats > used ? scratchFloats - used : 0,
-			epi, precision);
+			epi, precision, nullptr);
 	}
 	if(d->batch < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0
 		|| d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
@@ -442,22 +497,26 @@ int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, con
 	p.b_ready = 0;
 	const bool tmaShape = aligned16(x) && aligned16(filter) && (pointwise ? d->c % 4 == 0 : d->c % 32 == 0) && kk % 4 == 0;
 	if(scratch != nullptr && precision != NB200_PREC_FP32_SIMT && tmaShape && outRows > 0) {
-		float* prepared = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
+		float* inScratch = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
 		// with few output rows (small batches) every filter tile is used by a handful of CTAs at most: the extra launch
 		// costs more than converting those tiles in the kernel (ResNet-50 at batch 1: 0.69 -> 0.62 ms per pass)
 		const bool prepare = outRows >= PREPARE_B_MIN_ROWS;
 		if(prepare) {
-			const long long n = static_cast<long long>(d->k) * kk;
-			launch_dependent(overlap_launches(), prepare_filter_kernel, dim3(grid_for(n, 256, 8)), dim3(256), 0, as_stream(stream),
-				filter, prepared, n, precision == NB200_PREC_3XTF32 ? 0 : 1);
-			count_launch(1);
-			const int rc = check_launch();
-			if(rc != NB200_OK) return rc;
-			if(precision == NB200_PREC_3XTF32) p.Blo = prepared; else p.B = prepared;
+			const float* ready = prepared;
+			if(ready == nullptr || !aligned16(ready)) {
+				const long long n = static_cast<long long>(d->k) * kk;
+				launch_dependent(overlap_launches(), prepare_filter_kernel, dim3(grid_for(n, 256, 8)), dim3(256), 0, as_stream(stream),
+					filter, inScratch, n, precision == NB200_PREC_3XTF32 ? 0 : 1);
+				count_launch(1);
+				const int rc = check_launch();
+				if(rc != NB200_OK) return rc;
+				ready = inScratch;
+			}
+			if(precision == NB200_PREC_3XTF32) p.Blo = ready; else p.B = ready;
 			p.b_ready = 1;
 		}
 		// whatever the caller's scratch holds beyond the prepared filter is room for split-K partial results
-		float* const rest = prepared + prepared_filter_floats(d->k, d->r, d->s, d->c);
+		float* const rest = inScratch + prepared_filter_floats(d->k, d->r, d->s, d->c);
 		const size_t used = static_cast<size_t>(rest - scratch);
 		if(scratchFloats > used + 4 && split_scratch_floats(outRows, d->k, kk) > 0) {
 			p.splitScratch = rest;

@@ -126,7 +126,8 @@ bool overlap_launches();
 // Scratch floats of a convolution (api_contraction.cu); the room for split-K partial results comes last and is optional.
 size_t convolution_scratch_floats(const nb200_conv_desc* d, bool withSplitRoom);
 // nb200_blob_convolution with the size of the scratch stated
+// `prepared` (optional): the filter forms of nb200_blob_convolution_prepare_filter, made ahead of the call
 int blob_convolution(void* stream, const nb200_conv_desc* d, const float* x, const float* filter, float* y,
-	float* scratch, size_t scratchFloats, const nb200_epilogue* epi, int precision);
+	float* scratch, size_t scratchFloats, const nb200_epilogue* epi, int precision, const float* prepared = nullptr);
 
 } // namespace nb200

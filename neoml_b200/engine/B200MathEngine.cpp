@@ -80,6 +80,7 @@ CB200MathEngine::~CB200MathEngine()
 		cudaSetDevice( device );
 		ReleaseDistributedCommunicator(); // first: after an abort only this lets the stream drain
 		cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
+		forgetAllPreparedFilters();
 		for( void* p : deferredFrees ) memory.Free( p );
 		for( auto& b : hostBuffers ) cudaFreeHost( b.host );
 		for( auto& b : hostCache ) cudaFreeHost( b.first );
@@ -169,20 +170,91 @@ void CB200MathEngine::flushPending() const
 	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 	if( !pending.active ) return;
 	pending.active = false;
-	nb200_epilogue epi = {};
-	epi.bias = pending.freeTerm;
-	epi.residual = pending.residual;
-	epi.ld_residual = pending.d.k;
-	epi.act = pending.relu ? NB200_ACT_RELU : NB200_ACT_NONE;
-	epi.act_param_device = pending.threshold;
-	// scratch (prepared filter, widened pixels) comes from the block pool: the stream orders its reuse
-	const size_t scratchFloats = nb200_blob_convolution_scratch_floats( &pending.d );
-	float* scratch = scratchFloats > 0 ? static_cast<float*>( memory.Alloc( scratchFloats * sizeof( float ) ) ) : nullptr;
-	const int rc = nb200_blob_convolution( stream, &pending.d, pending.source, pending.filter, pending.result, scratch, &epi,
-		precision );
-	if( scratch != nullptr ) memory.Free( scratch );
+	launchConvolution( pending );
 	releaseDeferredFrees();
+}
+
+void CB200MathEngine::launchConvolution( const CPendingConvolution& call ) const
+{
+	nb200_epilogue epi = {};
+	epi.bias = call.freeTerm;
+	epi.residual = call.residual;
+	epi.ld_residual = call.d.k;
+	epi.act = call.relu ? NB200_ACT_RELU : NB200_ACT_NONE;
+	epi.act_param_device = call.threshold;
+	// scratch (prepared filter, widened pixels) comes from the block pool: the stream orders its reuse
+	const size_t scratchFloats = nb200_blob_convolution_scratch_floats( &call.d );
+	float* scratch = scratchFloats > 0 ? static_cast<float*>( memory.Alloc( scratchFloats * sizeof( float ) ) ) : nullptr;
+	const int rc = nb200_blob_convolution_with_prepared_filter( stream, &call.d, call.source, call.filter,
+		preparedFilterFor( call ), call.result, scratch, &epi, precision );
+	if( scratch != nullptr ) memory.Free( scratch );
 	check( rc, "BlobConvolution" );
+}
+
+// The prepared form of the call's filter: made on first use, then found by the filter's allocation.
+const float* CB200MathEngine::preparedFilterFor( const CPendingConvolution& call ) const
+{
+	if( call.filterAllocation == nullptr ) return nullptr;
+	const size_t floats = nb200_blob_convolution_prepared_filter_floats( &call.d );
+	if( floats == 0 ) return nullptr;
+	std::lock_guard<std::mutex> lock( preparedMutex );
+	auto it = preparedFilters.find( call.filterAllocation );
+	if( it != preparedFilters.end() ) {
+		const CPreparedFilter& f = it->second;
+		if( f.filter == call.filter && f.k == call.d.k && f.r == call.d.r && f.s == call.d.s && f.c == call.d.c ) return f.data;
+		memory.Free( f.data ); // the allocation now serves another filter shape
+		preparedFilters.erase( it );
+	}
+	CPreparedFilter f;
+	f.filter = call.filter;
+	f.k = call.d.k; f.r = call.d.r; f.s = call.d.s; f.c = call.d.c;
+	f.data = static_cast<float*>( memory.Alloc( floats * sizeof( float ) ) );
+	if( f.data == nullptr ) return nullptr; // no room: the call prepares into its scratch as before
+	if( nb200_blob_convolution_prepare_filter( stream, &call.d, call.filter, f.data, precision ) != NB200_OK ) {
+		memory.Free( f.data );
+		return nullptr;
+	}
+	preparedFilters.emplace( call.filterAllocation, f );
+	return f.data;
+}
+
+void CB200MathEngine::forgetPreparedFilter( const void* allocationBase ) const
+{
+	std::lock_guard<std::mutex> lock( preparedMutex );
+	auto it = preparedFilters.find( allocationBase );
+	if( it == preparedFilters.end() ) return;
+	// a recorded convolution may still be about to use it: launch that first (the stream then orders the reuse)
+	float* data = it->second.data;
+	preparedFilters.erase( it );
+	memory.Free( data );
+}
+
+void CB200MathEngine::forgetAllPreparedFilters() const
+{
+	std::lock_guard<std::mutex> lock( preparedMutex );
+	for( auto& kv : preparedFilters ) memory.Free( kv.second.data );
+	preparedFilters.clear();
+}
+
+// True when `call` neither reads what the recorded convolution writes nor writes anything the recorded one reads or
+// writes: the two may then run in either order.  A residual block's projection shortcut arrives between the block's
+// last convolution and the sum that joins them; launching it at once keeps that last convolution recorded, so the sum
+// and the ReLU behind it still ride in its epilogue.
+bool CB200MathEngine::independentOfPending( const CPendingConvolution& call ) const
+{
+	auto overlap = []( const float* a, long long na, const float* b, long long nb ) {
+		return a != nullptr && b != nullptr && a < b + nb && b < a + na;
+	};
+	const CPendingConvolution& p = pending;
+	if( p.relu || p.residual != nullptr ) return false;
+	// what the new call writes against everything the recorded one touches
+	if( overlap( call.result, call.resultFloats, p.result, p.resultFloats ) || overlap( call.result, call.resultFloats, p.source, p.sourceFloats )
+		|| overlap( call.result, call.resultFloats, p.filter, p.filterFloats ) || overlap( call.result, call.resultFloats, p.freeTerm, p.d.k ) ) {
+		return false;
+	}
+	// what the new call reads against what the recorded one writes
+	return !overlap( call.source, call.sourceFloats, p.result, p.resultFloats ) && !overlap( call.filter, call.filterFloats, p.result, p.resultFloats )
+		&& !overlap( call.freeTerm, call.d.k, p.result, p.resultFloats );
 }
 
 bool CB200MathEngine::fuseReLU( const float* first, float* result, int size, const float* thresholdOnDevice ) const
@@ -253,6 +325,7 @@ void CB200MathEngine::HeapFree( const CMemoryHandle& handle )
 	if( handle.IsNull() ) return;
 	if( handle.GetMathEngine() != this ) { raiseAssert( "HeapFree: the handle belongs to another math engine" ); return; }
 	void* block = const_cast<void*>( CMemoryHandleInternal::Base( handle ) );
+	if( !preparedFilters.empty() ) forgetPreparedFilter( block );
 	{
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 		if( ( pending.active || pendingRows.active ) && pendingRefersTo( block, memory.BlockBytes( block ) ) ) {
@@ -285,6 +358,7 @@ void CB200MathEngine::StackFree( const CMemoryHandle& handle )
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 		if( pending.active || pendingRows.active ) enter();
 	}
+	if( !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( handle ) );
 	memory.StackFree( CMemoryHandleInternal::GetRaw( handle ) );
 }
 
@@ -298,6 +372,7 @@ void CB200MathEngine::CleanUp()
 {
 	enter();
 	if( stream != nullptr ) cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
+	forgetAllPreparedFilters();
 	memory.CleanUp();
 }
 
@@ -311,6 +386,7 @@ void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* 
 	if( size == 0 ) return;
 	if( result.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
 	enter();
+	if( !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( result ) );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), source, size, cudaMemcpyHostToDevice, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
@@ -400,6 +476,7 @@ void CB200MathEngine::ReleaseBuffer( const CMemoryHandle& handle, void* ptr, boo
 		hostBuffers.pop_back();
 	}
 	if( exchange && buf.size > 0 ) {
+		if( !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( handle ) );
 		const CMemoryHandle at = CMemoryHandleInternal::Create( this,
 			static_cast<const char*>( CMemoryHandleInternal::GetRaw( handle ) ) + buf.pos );
 		DataExchangeRaw( at, ptr, buf.size );

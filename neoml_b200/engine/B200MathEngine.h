@@ -20,6 +20,7 @@
 #include <map>
 #include <mutex>
 #include <thread>
+#include <type_traits>
 #include <unordered_map>
 #include <vector>
 
@@ -116,12 +117,17 @@ private:
 	// held back for fusion (see CPendingConvolution).
 	void enter() const;
 	void flushPending() const;
+	struct CPendingConvolution;
+	void launchConvolution( const CPendingConvolution& call ) const;
+	bool independentOfPending( const CPendingConvolution& call ) const;
 	bool fuseReLU( const float* first, float* result, int size, const float* thresholdOnDevice ) const;
 	bool fuseAdd( const float* first, const float* second, float* result, int size ) const;
-	// device pointer behind a handle of this engine
+	// device pointer behind a handle of this engine; a handle that may be written through (non-const element type)
+	// ends the life of whatever the engine has prepared from the allocation's earlier contents
 	template<class T> T* raw( const CTypedMemoryHandle<T>& h ) const
 	{
 		if( !h.IsNull() && h.GetMathEngine() != this ) notImplemented( "use of a handle that belongs to another math engine" );
+		if( !std::is_const<T>::value && !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( h ) );
 		return CMemoryHandleInternal::GetRaw( h );
 	}
 	void vectorOp( int op, const float* a, const float* b, const float* scalar, float value, float* y, int n,
@@ -142,6 +148,8 @@ private:
 		bool relu = false;
 		const float* threshold = nullptr;
 		long long resultFloats = 0;
+		long long sourceFloats = 0, filterFloats = 0;
+		const void* filterAllocation = nullptr; // base of the allocation the filter handle points into
 	};
 	mutable CPendingConvolution pending;
 	// The same idea for the score path of attention (and FC bias -> softmax): an in-place VectorMultiply by a device
@@ -166,6 +174,21 @@ private:
 	bool pendingRefersTo( const void* begin, size_t bytes ) const;
 	void releaseDeferredFrees() const;
 	mutable std::vector<void*> deferredFrees;
+	// Filters prepared for the tensor core (their split parts / rounded copies, the widened stem filter), kept per
+	// filter allocation for as long as nothing writes to it: a network's weights are prepared once, not once per pass.
+	// Key: base address of the allocation the filter handle points into.  An entry dies when a method is given a
+	// writable handle into that allocation, when host data are copied into it, and when it is freed.
+	struct CPreparedFilter {
+		const float* filter = nullptr;  // the filter's own address (the handle's, not the allocation's)
+		int k = 0, r = 0, s = 0, c = 0;
+		float* data = nullptr;
+	};
+	mutable std::unordered_map<const void*, CPreparedFilter> preparedFilters;
+	mutable std::mutex preparedMutex;
+	const float* preparedFilterFor( const CPendingConvolution& call ) const;
+	void forgetPreparedFilter( const void* allocationBase ) const;
+	void forgetAllPreparedFilters() const;
+	// allocation base of every conv filter handle, noted at the call (raw pointers carry no allocation)
 
 	const int device;
 	const int precision;

@@ -69,17 +69,27 @@ void CB200MathEngine::BlobConvolution( const CConvolutionDesc& convDesc, const C
 	const CConstFloatHandle& filter, const CConstFloatHandle* freeTerm, const CFloatHandle& result )
 {
 	const nb200_conv_desc& d = static_cast<const CB200ConvolutionDesc&>( convDesc ).d;
+	CPendingConvolution call;
+	call.d = d;
+	call.source = raw( source );
+	call.filter = raw( filter );
+	call.freeTerm = freeTerm != nullptr ? raw( *freeTerm ) : nullptr;
+	call.result = raw( result );
+	call.resultFloats = static_cast<long long>( d.batch ) * d.ho * d.wo * d.k;
+	call.sourceFloats = static_cast<long long>( d.batch ) * d.h * d.w * d.c;
+	call.filterFloats = static_cast<long long>( d.k ) * d.r * d.s * d.c;
+	call.filterAllocation = CMemoryHandleInternal::Base( filter );
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( pending.active && !pendingRows.active && independentOfPending( call ) ) {
+		// the recorded convolution stays recorded (its sum and activation may still follow); this one runs now
+		cudaSetDevice( device );
+		launchConvolution( call );
+		return;
+	}
 	enter(); // launches an earlier convolution that is still held back
 	// The call is recorded, not launched: an in-place VectorAdd / VectorReLU that follows rides in its epilogue, any
 	// other call launches it first (enter()), so the caller cannot observe the delay.
-	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
-	pending = CPendingConvolution();
-	pending.d = d;
-	pending.source = raw( source );
-	pending.filter = raw( filter );
-	pending.freeTerm = freeTerm != nullptr ? raw( *freeTerm ) : nullptr;
-	pending.result = raw( result );
-	pending.resultFloats = static_cast<long long>( d.batch ) * d.ho * d.wo * d.k;
+	pending = call;
 	pending.active = true;
 }
 

@@ -258,6 +258,14 @@ void CB200MathEngine::FindMaxValueInColumns( int batchSize, const CConstFloatHan
 {
 	if( vectorSize < batchSize * matrixWidth ) { raise( "FindMaxValueInColumns: result buffer too small" ); return; }
 	enter();
+	if( matrixWidth == 1 ) {
+		// one column per batch entry (CArgmaxLayer over the last dimension): the maximum of each contiguous run of
+		// matrixHeight values -- a row maximum, which is what the reference CPU engine forwards this case to
+		// (CPU/x86/CpuX86MathEngineBlas.cpp:191-196); first maximum wins in both
+		check( nb200_find_max_value_in_rows( stream, raw( matrixHandle ), batchSize, matrixHeight, raw( resultHandle ),
+			raw( rowIndices ) ), "FindMaxValueInColumns" );
+		return;
+	}
 	check( nb200_find_max_value_in_columns( stream, batchSize, raw( matrixHandle ), matrixHeight, matrixWidth, raw( resultHandle ),
 		raw( rowIndices ) ), "FindMaxValueInColumns" );
 }

@@ -73,6 +73,32 @@ def memory_limit():
     return {"raised": raised, "engine_with_room_runs": ok}
 
 
+def filter_update():
+    """The engine keeps a prepared form of every convolution filter; new filter values (here: a second model loaded
+    into blobs that reuse the first one's memory, and a net whose filter is replaced by a fresh load) must be seen."""
+    engine = cdnn.Engine("gpu")
+    cpu = cdnn.Engine("cpu")
+    rng = np.random.default_rng(9)
+    x = rng.uniform(-1, 1, (8, 16, 16, 64)).astype(np.float32)     # 2048 output positions: the filter is prepared
+    worst = 0.0
+    for round_ in range(3):
+        f = rng.uniform(-1, 1, (64, 3, 3, 64)).astype(np.float32)
+        b = rng.uniform(-1, 1, 64).astype(np.float32)
+        model = cdnn.Model.conv(f, b, padding=(1, 1))
+        got_net, want_net = cdnn.Net(engine, model), cdnn.Net(cpu, model)
+        for net in (got_net, want_net):
+            net.set_input("in", x)
+            net.run()
+        for _ in range(2):                     # a second pass uses the kept form
+            got_net.run()
+        got, want = got_net.output("out"), want_net.output("out")
+        worst = max(worst, float(np.abs(got - want).max() / np.sqrt(np.mean(want * want))))
+        got_net.close()                        # frees the filter blob: the next round's may land on the same memory
+        want_net.close()
+        model.close()
+    return {"worst_gate": worst}
+
+
 def free_while_pending():
     engine = cdnn.Engine("gpu")
     return {"max_difference": cdnn.selftest_free_while_pending(engine)}

@@ -30,7 +30,8 @@ def test_every_declaration_cites_the_reference_interface():
     # each compute entry point is preceded by a comment naming the IMathEngine method and its line
     for name in _declared():
         if name in ("nb200_version", "nb200_device_count", "nb200_error_string", "nb200_device_status", "nb200_last_cuda_error",
-                    "nb200_launch_count", "nb200_mobilenetv2_scratch_floats", "nb200_blob_convolution_scratch_floats", "nb200_vector_copy_int",
+                    "nb200_launch_count", "nb200_mobilenetv2_scratch_floats", "nb200_blob_convolution_scratch_floats", "nb200_blob_convolution_prepared_filter_floats",
+                    "nb200_blob_convolution_prepare_filter", "nb200_vector_copy_int",
                     "nb200_vector_fill_int"):
             continue
         head = text[:text.index(name + "(")]

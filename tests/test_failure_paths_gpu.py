@@ -45,3 +45,7 @@ def test_abort_distributed_ends_the_peers_next_collective():
         pytest.skip("needs two GPUs")
     row = run_case("abort_distributed")
     assert "Stopping due to error in another thread." in row["raised"]
+
+
+def test_prepared_filters_follow_new_filter_values():
+    assert run_case("filter_update")["worst_gate"] < 1e-4

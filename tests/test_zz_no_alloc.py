@@ -88,7 +88,7 @@ def test_other_shapes_give_the_same_result_as_the_plain_entry_point():
     assert torch.equal(got, ops.BlobConvolution(x, f, padding=(1, 1)))
 
 
-@pytest.mark.parametrize("shape", [(4, 16, 16, 64, 64, "prepared filter"), (1, 7, 7, 512, 512, "split K")])
+@pytest.mark.parametrize("shape", [(4, 16, 16, 64, 64, "prepared filter"), (2, 14, 14, 256, 256, "split K")])
 def test_the_work_space_paths_match_caller_scratch_bit_for_bit(shape):
     """The two ways the fixed array is written besides the padded image: the prepared filter (32-channel K blocks and
     at least 1024 output positions) and the split-K partial results taken from the array's tail."""
