@@ -72,6 +72,9 @@ def load():
     lib.cdnn_net_get_output.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong, _ip, _ip]
     lib.cdnn_net_time_steps.restype = C.c_double
     lib.cdnn_net_time_steps.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_void_p, C.c_char_p, C.c_void_p, C.c_longlong]
+    lib.cdnn_net_time_steps_double_buffered.restype = C.c_double
+    lib.cdnn_net_time_steps_double_buffered.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_void_p, C.c_longlong, C.c_char_p,
+                                                        C.c_void_p, C.c_longlong, C.c_longlong]
     lib.cdnn_replicas_create.restype = C.c_void_p
     lib.cdnn_replicas_create.argtypes = [C.c_int, C.c_int, _ip, C.c_void_p]
     lib.cdnn_replicas_destroy.argtypes = [C.c_void_p]
@@ -230,7 +233,19 @@ class Net:
         return out
 
     def time_steps(self, steps: int, sink: str, source: str | None = None, input_ptr: int | None = None,
-                   output_ptr: int | None = None, output_bytes: int = 0) -> float:
+                   output_ptr: int | None = None, output_bytes: int = 0, double_buffered: bool = False,
+                   input_stride_floats: int = 0, output_stride_bytes: int = 0) -> float:
+        """Wall-clock seconds of `steps` x (host -> source blob, RunOnce, sinks -> host).  double_buffered: the input
+        copy of step i+1 is issued before the results of step i are read (see host/cdnn_host.cpp); the strides let
+        every step have its own batch and result buffer."""
+        if double_buffered:
+            t = load().cdnn_net_time_steps_double_buffered(
+                self.ptr, steps, source.encode() if source else None, C.c_void_p(input_ptr) if input_ptr else None,
+                input_stride_floats, sink.encode(), C.c_void_p(output_ptr) if output_ptr else None, output_stride_bytes,
+                output_bytes)
+            if t < 0:
+                _fail("time_steps")
+            return t
         t = load().cdnn_net_time_steps(self.ptr, steps, source.encode() if source else None,
                                        C.c_void_p(input_ptr) if input_ptr else None, sink.encode(),
                                        C.c_void_p(output_ptr) if output_ptr else None, output_bytes)

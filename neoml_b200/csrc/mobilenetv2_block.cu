@@ -11,6 +11,12 @@ extern "C" int nb200_blob_channelwise_convolution(void* stream, const nb200_chco
 
 using namespace nb200;
 
+namespace nb200 {
+// mobilenetv2_fused.cu
+bool launch_mbv2_fused(void* stream, const nb200_mbv2_desc* d, const float* x, const float* wExp, const float* bExp,
+	const float* wDw, const float* bDw, const float* wDown, const float* bDown, float* y, int precision, int* rc);
+}
+
 namespace {
 
 constexpr long long L2_GROUP_BYTES = 384ll << 20; // both intermediates of one group: measured on config 2, a few large
@@ -47,7 +53,7 @@ size_t nb200_mobilenetv2_scratch_floats(const nb200_mbv2_desc* d)
 {
 	Mbv2Plan pl;
 	if(!plan(d, pl)) return 0;
-	return static_cast<size_t>(pl.groupImages) * static_cast<size_t>(pl.expandFloatsPerImage + pl.dwFloatsPerImage);
+	return static_cast<size_t>(pl.groupImages) * static_cast<size_t>(pl.expandFloatsPerImage + pl.dwFloatsPerImage) + 4;
 }
 
 int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* d, const float* x, const float* w_exp,
@@ -59,6 +65,25 @@ int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* d, const float*
 	if(d->batch == 0) return NB200_OK;
 	if(x == nullptr || w_exp == nullptr || w_dw == nullptr || w_down == nullptr || y == nullptr || scratch == nullptr) {
 		return NB200_EINVAL;
+	}
+	// One kernel where the shape allows it (stride 1, 32 input channels, <= 192 expanded, <= 64 output channels): the
+	// expanded activations stay on chip.  A tile reads its neighbours' input pixels, so a call that writes its result
+	// over its input (NeoML runs the block in place when it may) goes through the scratch and is copied into place.
+	{
+		const size_t inBytes = static_cast<size_t>(d->batch) * d->h * d->w * d->c_in * sizeof(float);
+		const size_t outFloats = static_cast<size_t>(d->batch) * pl.ho * pl.wo * d->c_out;
+		const char* xb = reinterpret_cast<const char*>(x);
+		const char* yb = reinterpret_cast<const char*>(y);
+		const bool overlap = xb < yb + outFloats * sizeof(float) && yb < xb + inBytes;
+		float* target = overlap ? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15)) : y;
+		int rc = NB200_OK;
+		if(launch_mbv2_fused(stream, d, x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, target, precision, &rc)) {
+			if(rc != NB200_OK || !overlap) return rc;
+			if(cudaMemcpyAsync(y, target, outFloats * sizeof(float), cudaMemcpyDeviceToDevice, as_stream(stream)) != cudaSuccess) {
+				return check_launch();
+			}
+			return NB200_OK;
+		}
 	}
 	float* expanded = scratch;
 	float* dwOut = scratch + static_cast<size_t>(pl.groupImages) * pl.expandFloatsPerImage;

@@ -71,7 +71,37 @@ CB200MathEngine::CB200MathEngine( int _device, size_t memoryLimit, int flags ) :
 		return;
 	}
 	stream = s;
+	cudaStream_t c = nullptr;
+	cudaEvent_t e = nullptr;
+	if( cudaStreamCreateWithFlags( &c, cudaStreamNonBlocking ) == cudaSuccess
+		&& cudaEventCreateWithFlags( &e, cudaEventDisableTiming ) == cudaSuccess ) {
+		copyStream = c;
+		copyDone = e;
+	} else {
+		cudaGetLastError(); // exchanges then all take the compute stream
+		if( c != nullptr ) cudaStreamDestroy( c );
+	}
 	initialized = true;
+}
+
+void CB200MathEngine::noteUse( const void* allocationBase ) const
+{
+	std::lock_guard<std::mutex> lock( useMutex );
+	lastUse[allocationBase] = opSeq + 1;
+}
+
+bool CB200MathEngine::idleSinceLastDrain( const void* allocationBase ) const
+{
+	std::lock_guard<std::mutex> lock( useMutex );
+	auto it = lastUse.find( allocationBase );
+	return it == lastUse.end() || it->second <= completedSeq;
+}
+
+void CB200MathEngine::freeBlock( void* block ) const
+{
+	if( block == nullptr ) return;
+	noteUse( block ); // whoever gets the block next must assume queued kernels still read or write it
+	memory.Free( block );
 }
 
 CB200MathEngine::~CB200MathEngine()
@@ -82,6 +112,8 @@ CB200MathEngine::~CB200MathEngine()
 		cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
 		forgetAllPreparedFilters();
 		for( void* p : deferredFrees ) memory.Free( p );
+		if( copyStream != nullptr ) cudaStreamDestroy( static_cast<cudaStream_t>( copyStream ) );
+		if( copyDone != nullptr ) cudaEventDestroy( static_cast<cudaEvent_t>( copyDone ) );
 		for( auto& b : hostBuffers ) cudaFreeHost( b.host );
 		for( auto& b : hostCache ) cudaFreeHost( b.first );
 		cudaStreamDestroy( static_cast<cudaStream_t>( stream ) );
@@ -103,7 +135,7 @@ bool CB200MathEngine::pendingRefersTo( const void* begin, size_t bytes ) const
 void CB200MathEngine::releaseDeferredFrees() const
 {
 	if( pending.active || pendingRows.active ) return;
-	for( void* p : deferredFrees ) memory.Free( p );
+	for( void* p : deferredFrees ) freeBlock( p );
 	deferredFrees.clear();
 }
 
@@ -131,6 +163,10 @@ void CB200MathEngine::setDevice() const
 void CB200MathEngine::enter() const
 {
 	cudaSetDevice( device );
+	{
+		std::lock_guard<std::mutex> lock( useMutex );
+		++opSeq;
+	}
 	flushPending();
 	flushRowOps();
 }
@@ -145,7 +181,7 @@ float* CB200MathEngine::WorkAlloc( size_t floats ) const
 
 void CB200MathEngine::WorkFree( float* ptr ) const
 {
-	if( ptr != nullptr ) memory.Free( ptr );
+	freeBlock( ptr );
 }
 
 void CB200MathEngine::flushRowOps() const
@@ -187,7 +223,7 @@ void CB200MathEngine::launchConvolution( const CPendingConvolution& call ) const
 	float* scratch = scratchFloats > 0 ? static_cast<float*>( memory.Alloc( scratchFloats * sizeof( float ) ) ) : nullptr;
 	const int rc = nb200_blob_convolution_with_prepared_filter( stream, &call.d, call.source, call.filter,
 		preparedFilterFor( call ), call.result, scratch, &epi, precision );
-	if( scratch != nullptr ) memory.Free( scratch );
+	freeBlock( scratch );
 	check( rc, "BlobConvolution" );
 }
 
@@ -202,7 +238,7 @@ const float* CB200MathEngine::preparedFilterFor( const CPendingConvolution& call
 	if( it != preparedFilters.end() ) {
 		const CPreparedFilter& f = it->second;
 		if( f.filter == call.filter && f.k == call.d.k && f.r == call.d.r && f.s == call.d.s && f.c == call.d.c ) return f.data;
-		memory.Free( f.data ); // the allocation now serves another filter shape
+		freeBlock( f.data ); // the allocation now serves another filter shape
 		preparedFilters.erase( it );
 	}
 	CPreparedFilter f;
@@ -226,13 +262,13 @@ void CB200MathEngine::forgetPreparedFilter( const void* allocationBase ) const
 	// a recorded convolution may still be about to use it: launch that first (the stream then orders the reuse)
 	float* data = it->second.data;
 	preparedFilters.erase( it );
-	memory.Free( data );
+	freeBlock( data );
 }
 
 void CB200MathEngine::forgetAllPreparedFilters() const
 {
 	std::lock_guard<std::mutex> lock( preparedMutex );
-	for( auto& kv : preparedFilters ) memory.Free( kv.second.data );
+	for( auto& kv : preparedFilters ) freeBlock( kv.second.data );
 	preparedFilters.clear();
 }
 
@@ -333,7 +369,7 @@ void CB200MathEngine::HeapFree( const CMemoryHandle& handle )
 			return;
 		}
 	}
-	memory.Free( block );
+	freeBlock( block );
 }
 
 void CB200MathEngine::TransferHandleToThisThread( const CMemoryHandle&, size_t ) {} // heap blocks are not thread-bound here
@@ -386,12 +422,29 @@ void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* 
 	if( size == 0 ) return;
 	if( result.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
 	enter();
-	if( !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( result ) );
+	const void* base = CMemoryHandleInternal::Base( result );
+	if( !preparedFilters.empty() ) forgetPreparedFilter( base );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
-	if( cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), source, size, cudaMemcpyHostToDevice, s ) != cudaSuccess
+	void* const destination = CMemoryHandleInternal::GetRaw( result );
+	// A large exchange into a heap block that nothing queued can touch overlaps the kernels in flight (see noteUse)
+	if( copyStream != nullptr && size >= ( size_t( 1 ) << 20 ) && memory.BlockBytes( base ) > 0 && idleSinceLastDrain( base ) ) {
+		cudaStream_t c = static_cast<cudaStream_t>( copyStream );
+		cudaEvent_t done = static_cast<cudaEvent_t>( copyDone );
+		std::lock_guard<std::mutex> lock( hostMutex ); // one copy at a time owns the event
+		if( cudaMemcpyAsync( destination, source, size, cudaMemcpyHostToDevice, c ) != cudaSuccess
+			|| cudaEventRecord( done, c ) != cudaSuccess || cudaStreamWaitEvent( s, done, 0 ) != cudaSuccess
+			|| cudaStreamSynchronize( c ) != cudaSuccess ) {
+			raiseAssert( std::string( "DataExchangeRaw host->device: " ) + cudaGetErrorString( cudaGetLastError() ) );
+		}
+		noteUse( base );
+		return;
+	}
+	if( cudaMemcpyAsync( destination, source, size, cudaMemcpyHostToDevice, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
 		raiseAssert( std::string( "DataExchangeRaw host->device: " ) + cudaGetErrorString( cudaGetLastError() ) );
 	}
+	std::lock_guard<std::mutex> lock( useMutex );
+	completedSeq = opSeq; // the compute stream has drained
 }
 
 void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source, size_t size )
@@ -403,6 +456,10 @@ void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source
 	if( cudaMemcpyAsync( result, CMemoryHandleInternal::GetRaw( source ), size, cudaMemcpyDeviceToHost, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
 		raiseAssert( std::string( "DataExchangeRaw device->host: " ) + cudaGetErrorString( cudaGetLastError() ) );
+	}
+	{
+		std::lock_guard<std::mutex> lock( useMutex );
+		completedSeq = opSeq; // the compute stream has drained
 	}
 	// a kernel that gave up on a bounded wait leaves its mark in the status word: surface it at the first sync point
 	const int status = nb200_device_status( stream, 1 );
@@ -491,6 +548,8 @@ CMemoryHandle CB200MathEngine::CopyFrom( const CMemoryHandle& handle, size_t siz
 	IMathEngine* other = handle.GetMathEngine();
 	if( other == this ) {
 		enter();
+		noteUse( CMemoryHandleInternal::Base( result ) );
+		noteUse( CMemoryHandleInternal::Base( handle ) );
 		cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), CMemoryHandleInternal::GetRaw( handle ), size,
 			cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>( stream ) );
 		return result;

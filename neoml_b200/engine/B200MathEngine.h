@@ -128,6 +128,7 @@ private:
 	{
 		if( !h.IsNull() && h.GetMathEngine() != this ) notImplemented( "use of a handle that belongs to another math engine" );
 		if( !std::is_const<T>::value && !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( h ) );
+		if( !h.IsNull() ) noteUse( CMemoryHandleInternal::Base( h ) );
 		return CMemoryHandleInternal::GetRaw( h );
 	}
 	void vectorOp( int op, const float* a, const float* b, const float* scalar, float value, float* y, int n,
@@ -189,6 +190,21 @@ private:
 	void forgetPreparedFilter( const void* allocationBase ) const;
 	void forgetAllPreparedFilters() const;
 	// allocation base of every conv filter handle, noted at the call (raw pointers carry no allocation)
+
+	// Host-to-device exchanges that need not wait for the kernels in flight.  Every allocation carries the sequence
+	// number of the last call that may touch it (noted when a handle into it is resolved and when it is freed);
+	// `completedSeq` is the sequence number reached at the last point where the compute stream was drained.  A large
+	// exchange into a heap block whose last use lies at or before that point cannot conflict with anything queued, so
+	// it runs on a second stream while the compute stream keeps working; the compute stream then waits for the copy
+	// (an event), the host for the copy alone.  Everything else goes in order on the compute stream, as before.
+	void noteUse( const void* allocationBase ) const;
+	bool idleSinceLastDrain( const void* allocationBase ) const;
+	void freeBlock( void* block ) const; // back to the pool, marked as possibly still read by queued kernels
+	mutable std::unordered_map<const void*, uint64_t> lastUse;
+	mutable std::mutex useMutex;
+	mutable uint64_t opSeq = 0, completedSeq = 0;
+	void* copyStream = nullptr;
+	void* copyDone = nullptr; // cudaEvent_t
 
 	const int device;
 	const int precision;

@@ -548,8 +548,30 @@ CDNN_API int cdnn_net_get_output( void* netPtr, const char* name, void* host, lo
 // Wall-clock seconds of `steps` x ( [host -> source blob] RunOnce [sinks -> host] ) on this net.  sinkNames is one
 // sink or several separated by commas; their blobs are written to `output` one after the other.  input / output may
 // be NULL (then the source keeps its blob / nothing is read back except a final 4-byte read that waits for the device).
+static double timeSteps( void* netPtr, int steps, const char* sourceName, const float* input, const char* sinkNames,
+	void* output, long long outputBytes, bool twoInputBlobs, long long inputStrideFloats = 0, long long outputStrideBytes = 0 );
+
 CDNN_API double cdnn_net_time_steps( void* netPtr, int steps, const char* sourceName, const float* input, const char* sinkNames,
 	void* output, long long outputBytes )
+{
+	return timeSteps( netPtr, steps, sourceName, input, sinkNames, output, outputBytes, false );
+}
+
+// The same work per step -- one host -> device copy of the batch, one RunOnce, the sinks copied to the host -- with
+// the input double-buffered by the caller, the way a NeoML user hides the input copy: two blobs alternate as the
+// source layer's blob (CSourceLayer::SetBlob), and the batch of step i + 1 is copied into the idle one right after
+// RunOnce of step i has been issued, before step i's results are read.  An engine that queues its work asynchronously
+// can then overlap that copy with the kernels of step i; on an engine that runs each call to completion nothing changes.
+// Step i reads its batch at input + i * inputStrideFloats and writes its results at output + i * outputStrideBytes
+// (strides of 0: the same batch and the same result buffer every step).
+CDNN_API double cdnn_net_time_steps_double_buffered( void* netPtr, int steps, const char* sourceName, const float* input,
+	long long inputStrideFloats, const char* sinkNames, void* output, long long outputStrideBytes, long long outputBytes )
+{
+	return timeSteps( netPtr, steps, sourceName, input, sinkNames, output, outputBytes, true, inputStrideFloats, outputStrideBytes );
+}
+
+static double timeSteps( void* netPtr, int steps, const char* sourceName, const float* input, const char* sinkNames,
+	void* output, long long outputBytes, bool twoInputBlobs, long long inputStrideFloats, long long outputStrideBytes )
 {
 	double seconds = -1;
 	guarded( [&] {
@@ -567,16 +589,27 @@ CDNN_API double cdnn_net_time_steps( void* netPtr, int steps, const char* source
 				at = comma + 1;
 			}
 		}
+		CPtr<CDnnBlob> inputBlobs[2];
+		if( twoInputBlobs && input != nullptr ) {
+			inputBlobs[0] = source->GetBlob();
+			inputBlobs[1] = CDnnBlob::CreateBlob( *net->engine, CT_Float, inputBlobs[0]->GetDesc() );
+		}
 		const auto t0 = std::chrono::steady_clock::now();
+		if( inputBlobs[1] != nullptr ) inputBlobs[0]->CopyFrom( input );
 		for( int i = 0; i < steps; ++i ) {
-			if( input != nullptr ) source->GetBlob()->CopyFrom( input );
+			if( inputBlobs[1] != nullptr ) {
+				source->SetBlob( inputBlobs[i & 1] );
+			} else if( input != nullptr ) {
+				source->GetBlob()->CopyFrom( input );
+			}
 			net->dnn->RunOnce();
+			if( inputBlobs[1] != nullptr && i + 1 < steps ) inputBlobs[( i + 1 ) & 1]->CopyFrom( input + ( i + 1 ) * inputStrideFloats );
 			if( output != nullptr ) {
-				char* at = static_cast<char*>( output );
+				char* at = static_cast<char*>( output ) + i * outputStrideBytes;
 				for( CPtr<CSinkLayer>& sink : sinks ) {
 					CPtr<CDnnBlob> blob = sink->GetBlob();
 					const long long bytes = static_cast<long long>( blob->GetDataSize() ) * 4;
-					if( at + bytes > static_cast<char*>( output ) + outputBytes ) throw std::logic_error( "output buffer too small" );
+					if( at + bytes > static_cast<char*>( output ) + i * outputStrideBytes + outputBytes ) throw std::logic_error( "output buffer too small" );
 					if( blob->GetDataType() == CT_Int ) blob->CopyTo( reinterpret_cast<int*>( at ) ); else blob->CopyTo( reinterpret_cast<float*>( at ) );
 					at += bytes;
 				}

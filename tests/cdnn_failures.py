@@ -99,6 +99,33 @@ def filter_update():
     return {"worst_gate": worst}
 
 
+def overlapped_input():
+    """Six steps with six different batches through the double-buffered loop (the engine copies step i+1's batch while
+    step i's kernels run) against the same batches fed one at a time: every step's result must be the same bits."""
+    import torch
+    from neoml_b200 import resnet50
+    engine = cdnn.Engine("gpu")
+    model = cdnn.Model.resnet50(resnet50.make_weights())
+    net = cdnn.Net(engine, model)
+    steps, batch, hw = 6, 8, 160                              # 2.4 MB per batch: above the engine's 1 MB threshold
+    rng = np.random.default_rng(11)
+    x = torch.from_numpy(rng.uniform(0, 1, (steps, batch, hw, hw, 3)).astype(np.float32)).pin_memory()
+    per_out = batch * 1001
+    out = torch.zeros(steps * per_out, dtype=torch.float32).pin_memory()
+    net.set_input("in", x[0].numpy())
+    net.time_steps(steps, "probs,argmax", source="in", input_ptr=x.data_ptr(), output_ptr=out.data_ptr(),
+                   output_bytes=per_out * 4, double_buffered=True, input_stride_floats=x[0].numel(),
+                   output_stride_bytes=per_out * 4)
+    got = out.numpy().reshape(steps, per_out).copy()
+    same = True
+    for i in range(steps):
+        net.set_input("in", x[i].numpy())
+        net.run()
+        want = np.concatenate([net.output("probs").ravel(), net.output("argmax").ravel().view(np.float32)])
+        same = same and bool(np.array_equal(got[i].view(np.int32), want.view(np.int32)))
+    return {"all_steps_bit_identical": same}
+
+
 def free_while_pending():
     engine = cdnn.Engine("gpu")
     return {"max_difference": cdnn.selftest_free_while_pending(engine)}

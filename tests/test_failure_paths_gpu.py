@@ -49,3 +49,7 @@ def test_abort_distributed_ends_the_peers_next_collective():
 
 def test_prepared_filters_follow_new_filter_values():
     assert run_case("filter_update")["worst_gate"] < 1e-4
+
+
+def test_input_copies_that_overlap_the_previous_step_change_nothing():
+    assert run_case("overlapped_input")["all_steps_bit_identical"]

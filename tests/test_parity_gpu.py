@@ -607,3 +607,47 @@ def test_sliced_row_sums_are_the_same_bits_on_every_run(ops, oracle):
         init = cases.uniform(82, (bsz * w,))
         acc = ops.SumMatrixRows(bsz, md, h, w, result=dev(init), add=True)
         assert gate_err(host(acc), oracle.sum_matrix_rows(bsz, m, h, w) + init.reshape(bsz, w)) < 1e-5
+
+
+FUSED_MBV2 = [
+    # batch, h, w, c_exp, c_out, residual, act1 (kind, param), act2, biases -- all with 32 input channels and stride 1:
+    # the shapes the one-kernel form of the block covers (ragged tiles, every chunk count, both activations)
+    (2, 8, 16, 32, 32, True, (1, 6.0), (1, 6.0), (True, True, True)),       # exactly one tile per image
+    (1, 19, 23, 96, 32, True, (1, 6.0), (1, 6.0), (True, True, True)),      # ragged in both directions
+    (3, 9, 33, 192, 32, True, (1, 0.0), (2, 0.0), (True, False, True)),     # ReLU without threshold, HSwish
+    (2, 17, 5, 64, 16, False, (2, 0.0), (1, 6.0), (False, True, False)),    # narrower than a tile, 16 outputs
+    (1, 24, 40, 160, 64, False, (1, 6.0), (1, 6.0), (True, True, True)),    # 64 outputs, five chunks
+    (5, 14, 14, 192, 48, False, (1, 6.0), (1, 6.0), (True, True, True)),    # 48 outputs
+]
+
+
+@pytest.mark.parametrize("shape", FUSED_MBV2, ids=lambda s: "x".join(map(str, s[:5])))
+@pytest.mark.parametrize("prec,tol", [(0, TOL_FP32), (1, TOL_TF32)], ids=["3xtf32", "tf32"])
+def test_fused_mobilenetv2_block(ops, oracle, shape, prec, tol):
+    b, h, w, ce, co, res, (a1, p1), (a2, p2), biases = shape
+    seed = 8800 + 7 * FUSED_MBV2.index(shape)
+    x = cases.uniform(seed, (b, h, w, 32), 0.0, 1.0)
+    we = cases.normal(seed + 1, (ce, 32), float(np.sqrt(2.0 / 32)))
+    wd = cases.normal(seed + 2, (3, 3, ce), float(np.sqrt(2.0 / 9)))
+    wp = cases.normal(seed + 3, (co, ce), float(np.sqrt(2.0 / ce)))
+    be = cases.uniform(seed + 4, (ce,), -0.1, 0.1) if biases[0] else None
+    bd = cases.uniform(seed + 5, (ce,), -0.1, 0.1) if biases[1] else None
+    bp = cases.uniform(seed + 6, (co,), -0.1, 0.1) if biases[2] else None
+    kw = dict(stride=1, residual=res, act_exp=a1, act_exp_param=p1, act_dw=a2, act_dw_param=p2)
+    want = oracle.mobilenetv2_block(x, we, be, wd, bd, wp, bp, **kw)
+    from neoml_b200 import _capi
+    lib = _capi.load()
+    launches = lib.nb200_launch_count()
+    y = ops.MobileNetV2Block(dev(x), dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), stride=1, residual=res,
+                             expand_act=a1, expand_act_param=p1, channelwise_act=a2, channelwise_act_param=p2,
+                             precision=prec)
+    got = host(y)
+    assert lib.nb200_launch_count() - launches == 1, "the block did not run as one kernel"
+    assert lib.nb200_device_status(None, 0) == 0
+    check(got, want, tol, f"fused mbv2 {shape[:5]}")
+    if res and prec == 0:
+        # in place over the input, as NeoML calls it when it may: the result goes through the scratch
+        xd = dev(x)
+        ops.MobileNetV2Block(xd, dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), result=xd, stride=1, residual=True,
+                             expand_act=a1, expand_act_param=p1, channelwise_act=a2, channelwise_act_param=p2)
+        assert np.array_equal(host(xd), got)
