@@ -168,6 +168,14 @@ NB200_API size_t nb200_mobilenetv2_scratch_floats(const nb200_mbv2_desc* desc);
 NB200_API int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* desc, const float* x,
 	const float* w_exp, const float* b_exp, const float* w_dw, const float* b_dw,
 	const float* w_down, const float* b_down, float* y, float* scratch, int precision);
+/* The same block (NME.h:1095-1101,1069-1071) as ONE kernel that keeps the expanded activations on chip (DRAM traffic =
+ * input + output + weights).  Shapes: stride 1, c_in = 32, c_exp a multiple of 32 up to 192, c_out a multiple of 16 up
+ * to 64; anything else returns NB200_EINVAL.  `scratch` (batch*h*w*c_out floats + 4) is needed only when y overlaps x.
+ * nb200_mobilenetv2_block takes this path by itself wherever the shape allows; the entry point exists so that a caller
+ * (and the tests) can ask for it explicitly. */
+NB200_API int nb200_mobilenetv2_block_fused(void* stream, const nb200_mbv2_desc* desc, const float* x,
+	const float* w_exp, const float* b_exp, const float* w_dw, const float* b_dw,
+	const float* w_down, const float* b_down, float* y, float* scratch, int precision);
 
 /* ---- memory-bound vector / matrix ops ---------------------------------------------------------------------- */
 /* Elementwise family (IVectorMathEngine, NME.h:69-384).  `op` selects the method; operands unused by an op

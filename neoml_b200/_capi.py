@@ -67,6 +67,7 @@ SIGNATURES = {
     "nb200_blob_channelwise_convolution": (_i, [_vp, C.POINTER(ChConvDesc), _vp, _vp, _vp, _vp, _i, _f]),
     "nb200_mobilenetv2_scratch_floats": (C.c_size_t, [C.POINTER(Mbv2Desc)]),
     "nb200_mobilenetv2_block": (_i, [_vp, C.POINTER(Mbv2Desc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "nb200_mobilenetv2_block_fused": (_i, [_vp, C.POINTER(Mbv2Desc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "nb200_matrix_softmax_by_rows_fused": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _vp]),
     "nb200_vector_op": (_i, [_vp, _i, _vp, _vp, _vp, _f, _vp, _i]),
     "nb200_vector_copy_int": (_i, [_vp, _vp, _vp, _i]),

@@ -11,6 +11,10 @@ extern "C" int nb200_blob_channelwise_convolution(void* stream, const nb200_chco
 
 using namespace nb200;
 
+extern "C" int nb200_mobilenetv2_block_fused(void* stream, const nb200_mbv2_desc* d, const float* x, const float* w_exp,
+	const float* b_exp, const float* w_dw, const float* b_dw, const float* w_down, const float* b_down, float* y,
+	float* scratch, int precision);
+
 namespace nb200 {
 // mobilenetv2_fused.cu
 bool launch_mbv2_fused(void* stream, const nb200_mbv2_desc* d, const float* x, const float* wExp, const float* bExp,
@@ -66,24 +70,10 @@ int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* d, const float*
 	if(x == nullptr || w_exp == nullptr || w_dw == nullptr || w_down == nullptr || y == nullptr || scratch == nullptr) {
 		return NB200_EINVAL;
 	}
-	// One kernel where the shape allows it (stride 1, 32 input channels, <= 192 expanded, <= 64 output channels): the
-	// expanded activations stay on chip.  A tile reads its neighbours' input pixels, so a call that writes its result
-	// over its input (NeoML runs the block in place when it may) goes through the scratch and is copied into place.
+	// one kernel where the shape allows it (the expanded activations stay on chip); three launches otherwise
 	{
-		const size_t inBytes = static_cast<size_t>(d->batch) * d->h * d->w * d->c_in * sizeof(float);
-		const size_t outFloats = static_cast<size_t>(d->batch) * pl.ho * pl.wo * d->c_out;
-		const char* xb = reinterpret_cast<const char*>(x);
-		const char* yb = reinterpret_cast<const char*>(y);
-		const bool overlap = xb < yb + outFloats * sizeof(float) && yb < xb + inBytes;
-		float* target = overlap ? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15)) : y;
-		int rc = NB200_OK;
-		if(launch_mbv2_fused(stream, d, x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, target, precision, &rc)) {
-			if(rc != NB200_OK || !overlap) return rc;
-			if(cudaMemcpyAsync(y, target, outFloats * sizeof(float), cudaMemcpyDeviceToDevice, as_stream(stream)) != cudaSuccess) {
-				return check_launch();
-			}
-			return NB200_OK;
-		}
+		const int rc = nb200_mobilenetv2_block_fused(stream, d, x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, y, scratch, precision);
+		if(rc != NB200_EINVAL) return rc;
 	}
 	float* expanded = scratch;
 	float* dwOut = scratch + static_cast<size_t>(pl.groupImages) * pl.expandFloatsPerImage;
@@ -111,6 +101,34 @@ int nb200_mobilenetv2_block(void* stream, const nb200_mbv2_desc* d, const float*
 		rc = nb200_multiply_matrix_by_transposed_matrix(stream, dwOut, imgs * pl.ho * pl.wo, d->c_exp, d->c_exp,
 			w_down, d->c_out, d->c_exp, yg, d->c_out, &e2, precision);
 		if(rc != NB200_OK) return rc;
+	}
+	return NB200_OK;
+}
+
+// The block as ONE kernel (mobilenetv2_fused.cu): the expanded activations stay on chip.  Covers stride 1 with 32 input
+// channels, c_exp a multiple of 32 up to 192, c_out a multiple of 16 up to 64 (and what fits its shared memory);
+// NB200_EINVAL for any other shape.  A tile reads its neighbours' input pixels, so a call that writes its result over
+// its input goes through `scratch` (batch * h * w * c_out floats, only needed for such calls) and is copied into place.
+int nb200_mobilenetv2_block_fused(void* stream, const nb200_mbv2_desc* d, const float* x, const float* w_exp,
+	const float* b_exp, const float* w_dw, const float* b_dw, const float* w_down, const float* b_down, float* y,
+	float* scratch, int precision)
+{
+	Mbv2Plan pl;
+	if(!plan(d, pl)) return NB200_EINVAL;
+	if(d->batch == 0) return NB200_OK;
+	if(x == nullptr || w_exp == nullptr || w_dw == nullptr || w_down == nullptr || y == nullptr) return NB200_EINVAL;
+	const size_t inBytes = static_cast<size_t>(d->batch) * d->h * d->w * d->c_in * sizeof(float);
+	const size_t outFloats = static_cast<size_t>(d->batch) * pl.ho * pl.wo * d->c_out;
+	const char* xb = reinterpret_cast<const char*>(x);
+	const char* yb = reinterpret_cast<const char*>(y);
+	const bool overlap = xb < yb + outFloats * sizeof(float) && yb < xb + inBytes;
+	if(overlap && scratch == nullptr) return NB200_EINVAL;
+	float* target = overlap ? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15)) : y;
+	int rc = NB200_OK;
+	if(!launch_mbv2_fused(stream, d, x, w_exp, b_exp, w_dw, b_dw, w_down, b_down, target, precision, &rc)) return NB200_EINVAL;
+	if(rc != NB200_OK || !overlap) return rc;
+	if(cudaMemcpyAsync(y, target, outFloats * sizeof(float), cudaMemcpyDeviceToDevice, as_stream(stream)) != cudaSuccess) {
+		return check_launch();
 	}
 	return NB200_OK;
 }

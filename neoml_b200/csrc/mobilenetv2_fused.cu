@@ -3,20 +3,23 @@
 // The expanded activations never leave the SM: algorithmic traffic is the input once (plus its halo), the output once
 // and the weights.
 //
-// A persistent CTA (one per SM) walks output tiles of 8 x 16 pixels.  Per tile:
-//   1. TMA brings the 10 x 18 halo patch of x (32 channels = one 128-byte row per pixel, 128-byte swizzle, zeros
-//      outside the image) into shared memory; the threads derive the "lo" part of the 3xTF32 split beside it.
-//   2. Expand: tcgen05.mma kind::tf32 (A = the patch, 2 x 128 rows; B = W_exp, resident in shared memory; 3 MMAs per
-//      product: lo*hi + hi*hi + hi*lo) into tensor memory, all expanded channels at once.  When the MMAs have
-//      completed the patch buffer is free and the next tile's TMA load is issued: it lands while this tile is worked on.
-//   3. Per chunk of 32 expanded channels: tcgen05.ld -> + bias, activation, zero outside the image (the depthwise
-//      convolution pads the EXPANDED image with zeros) -> shared memory; depthwise 3x3 with a warp per output column
-//      and a lane per channel (a 10 x 3 register window gives eight outputs) + bias + activation -> written, split in
-//      hi / lo, as the K-major A operand of the project product; project: tcgen05.mma accumulates the chunk into the
-//      output tile in tensor memory.
-//   4. tcgen05.ld of the output tile -> + bias, + residual -> global memory (128 bytes per pixel).
-// Every wait is bounded (common.cuh); on a time-out the kernel records it in the status word, frees its tensor memory
-// and returns.
+// A persistent CTA (one per SM, 16 warps) walks output tiles of 4 x 16 pixels as a three-stage pipeline:
+//   expand(t+2)   tensor core   [channels] x [halo pixels] = W_exp (A, resident in shared memory) x patch (B; the
+//                               6 x 18 halo patch of x: TMA, 128-byte rows, zeros outside the image), 3 MMAs per
+//                               product (lo*hi + hi*hi + hi*lo), into tensor memory -- TRANSPOSED, so that a lane
+//                               of tensor memory is a channel and its columns are that channel's halo pixels
+//   depthwise(t)  12 warps      a lane owns ONE channel: tcgen05.ld hands it 72 columns (four halo rows), bias +
+//                               activation + the zero padding of the EXPANDED image are applied on the way, the nine
+//                               taps are FMAs on registers; the result (bias, activation, split in hi / lo) is written
+//                               as the K-major A operand of the project product.  No shared-memory round trip.
+//   project(t-1)  tensor core   all channel chunks into the output tile in tensor memory; then
+//   store(t-1)    4 warps       tcgen05.ld -> + bias, + residual -> global memory (128 bytes per pixel).  The same four
+//                               warps first fetch the patch of tile t+2 and derive its lo part, while the others do the
+//                               depthwise arithmetic.
+// The expand accumulators are double-buffered in tensor memory, so there is ONE block-wide barrier per tile (the A
+// operand of tile t is complete): behind it expand(t+2) and project(t) are issued.  Every wait is bounded (common.cuh)
+// and the barrier carries a vote: on a time-out the kernel records it in the status word, frees its tensor memory and
+// returns.
 #include "contraction.cuh"
 
 #include <cuda.h>
@@ -25,17 +28,18 @@ namespace nb200 {
 
 namespace {
 
-constexpr int TH = 8, TW = 16;              // output tile
+constexpr int TH = 4, TW = 16;              // output tile (64 pixels)
 constexpr int HH = TH + 2, HW = TW + 2;     // halo patch
-constexpr int HALO = HH * HW;               // 180 pixels
+constexpr int HALO = HH * HW;               // 108 pixels
+constexpr int HALO_N = 112;                 // ... as the N extent of the expand product (multiple of 16)
 constexpr int CIN = 32;                     // input channels = K of the expand product = one 128-byte row
-constexpr int CHUNK = 32;                   // expanded channels per depthwise / project step
-constexpr int E_STRIDE = CHUNK + 1;         // floats per pixel of the expanded chunk in shared memory (no bank conflicts
-                                            // for a thread per pixel writing and for a lane per channel reading)
-constexpr int THREADS = 256;
+constexpr int CHUNK = 32;                   // expanded channels per lane quarter = K chunk of the project product
+constexpr int THREADS = 512;
 constexpr int MAX_CEXP = 192, MAX_COUT = 64;
 constexpr int PATCH_BYTES = HALO * 128;     // what one TMA load delivers
-constexpr int PATCH_ROOM = (PATCH_BYTES + 1023) / 1024 * 1024;
+constexpr int PATCH_ROOM = HALO_N * 128;    // what the expand product reads (14336, a multiple of 1024)
+constexpr int A2_CHUNK_BYTES = TH * TW * 128; // 64 pixel rows of 32 channels
+constexpr int TMEM_COLS = 512;
 constexpr int KERNEL_ID = 0x6d;             // in the status word: (KERNEL_ID << 8) | site
 enum { SITE_PATCH = 1, SITE_EXPAND = 2, SITE_PROJECT = 3 };
 
@@ -64,25 +68,55 @@ __device__ __forceinline__ float lo_part(float v)
 	return v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
 }
 
+// ReLU (optionally with an upper threshold) and "no activation" as one clamp, HSwish apart; decided once per kernel
+struct Act {
+	bool hswish;
+	float lo, hi;
+	__device__ __forceinline__ float operator()(float v) const
+	{
+		return hswish ? v * fminf(fmaxf(v + 3.f, 0.f), 6.f) * (1.f / 6.f) : fminf(fmaxf(v, lo), hi);
+	}
+};
+__device__ __forceinline__ Act make_act(int kind, float param)
+{
+	Act a;
+	a.hswish = kind == NB200_ACT_HSWISH;
+	a.lo = kind == NB200_ACT_RELU ? 0.f : -__int_as_float(0x7f800000);
+	a.hi = kind == NB200_ACT_RELU && param > 0.f ? param : __int_as_float(0x7f800000);
+	return a;
+}
+
+// 32 lanes x 32 bit, 8 consecutive columns, issue only (tmem_ld_wait() before the first use)
+__device__ __forceinline__ void tmem_ld8_issue_local(uint32_t taddr, uint32_t* r)
+{
+	asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+		: "r"(taddr));
+}
+
 struct SmemLayout {
-	uint32_t patchHi, patchLo, wExpHi, wExpLo, wDownHi, wDownLo, e, a2Hi, a2Lo, consts, bars, total;
+	uint32_t patchHi, patchLo, wExpHi, wExpLo, wDownHi, wDownLo, a2Hi, a2Lo, consts, bars, total;
 };
 
 __host__ __device__ inline SmemLayout smem_layout(int cExp, int cOut)
 {
+	const uint32_t chunks = cExp / CHUNK;
 	SmemLayout l;
 	uint32_t at = 0;
 	l.patchHi = at; at += PATCH_ROOM;
 	l.patchLo = at; at += PATCH_ROOM;
-	// the second 128-row block of the patch operands reaches 256 rows: whatever follows is read as rows that no one uses
+	// a 128-row MMA operand block that starts at row 128 of W_exp reads on into whatever follows (rows nobody uses)
 	l.wExpHi = at; at += cExp * 128;
 	l.wExpLo = at; at += cExp * 128;
-	l.wDownHi = at; at += (cExp / CHUNK) * cOut * 128;
-	l.wDownLo = at; at += (cExp / CHUNK) * cOut * 128;
-	l.a2Hi = at; at += 128 * 128;
-	l.a2Lo = at; at += 128 * 128;
-	l.e = at; at += (HALO * E_STRIDE * 4 + 15) / 16 * 16;
-	l.consts = at; at += (11 * cExp + cOut) * 4;   // bExp, bDw, wDw[9], bDown
+	l.wDownHi = at; at += chunks * cOut * 128;
+	l.wDownLo = at; at += chunks * cOut * 128;
+	if(at < l.wExpLo + 2 * 128 * 128) at = l.wExpLo + 2 * 128 * 128;
+	// The project product's A tiles: a chunk's 64 pixel rows are rows 64..127 of a 128-row block that begins 8 KB
+	// earlier (the chunk before, or the weights in front of the first chunk): the output pixels then land in tensor
+	// memory lanes 64..127, which the warps that store the tile may read.
+	l.a2Hi = at; at += chunks * A2_CHUNK_BYTES;
+	l.a2Lo = at; at += chunks * A2_CHUNK_BYTES;
+	l.consts = at; at += cOut * 4;                 // bDown
 	at = (at + 15) / 16 * 16;
 	l.bars = at; at += 64;
 	l.total = at;
@@ -95,15 +129,12 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 	extern __shared__ uint8_t smemRaw[];
 	uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
 	const SmemLayout L = smem_layout(p.cExp, p.cOut);
-	float* const e = reinterpret_cast<float*>(smem + L.e);
-	float* const bExp = reinterpret_cast<float*>(smem + L.consts);
-	float* const bDw = bExp + p.cExp;
-	float* const wDw = bDw + p.cExp;            // [9][cExp]
-	float* const bDown = wDw + 9 * p.cExp;
+	float* const bDown = reinterpret_cast<float*>(smem + L.consts);
 	uint64_t* const patchBar = reinterpret_cast<uint64_t*>(smem + L.bars);
-	uint64_t* const expandBar = patchBar + 1;
-	uint64_t* const projectBar = patchBar + 2;
-	uint32_t* const tmemSlot = reinterpret_cast<uint32_t*>(patchBar + 3);
+	uint64_t* const expandBar = patchBar + 1;   // two: expand(e) completes a phase of expandBar[e & 1] (a waiter is then
+	                                            // never more than one phase behind, which parity waits require)
+	uint64_t* const projectBar = patchBar + 3;
+	uint32_t* const tmemSlot = reinterpret_cast<uint32_t*>(patchBar + 4);
 	volatile int* const abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
 	const int tid = threadIdx.x;
@@ -113,14 +144,16 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 
 	if(tid == 0) {
 		mbar_init(patchBar, 1);
-		mbar_init(expandBar, 1);
-		mbar_init(projectBar, 1);
+		mbar_init(&expandBar[0], 1);
+		mbar_init(&expandBar[1], 1);
+		// one commit per warp that issues project MMAs: two when tensor memory has room for a second output accumulator
+		mbar_init(projectBar, (4 * HALO_N + 2 * p.cOut <= TMEM_COLS && p.cExp > CHUNK) ? 2 : 1);
 		*abortFlag = 0;
 		mbar_init_fence();
 		tma_prefetch_descriptor(&mapX);
 	}
 	if(warp == 0) {
-		tmem_alloc(tmemSlot, 512);
+		tmem_alloc(tmemSlot, TMEM_COLS);
 		tmem_relinquish();
 	}
 	// the weights, once per CTA: expand [cExp][32] and project [cOut][cExp] as swizzled K-major tiles, hi and lo
@@ -147,24 +180,48 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 			*reinterpret_cast<float*>(smem + L.wDownHi + off) = to_tf32(v);
 		}
 	}
-	for(int i = tid; i < p.cExp; i += THREADS) {
-		bExp[i] = p.bExp != nullptr ? __ldg(p.bExp + i) : 0.f;
-		bDw[i] = p.bDw != nullptr ? __ldg(p.bDw + i) : 0.f;
-#pragma unroll
-		for(int t = 0; t < 9; ++t) wDw[t * p.cExp + i] = __ldg(p.wDw + t * p.cExp + i);
-	}
 	for(int i = tid; i < p.cOut; i += THREADS) bDown[i] = p.bDown != nullptr ? __ldg(p.bDown + i) : 0.f;
 	fence_proxy_async_smem();
 	tc_fence_before_sync();
 	__syncthreads();
 	tc_fence_after_sync();
 	const uint32_t tmemBase = *tmemSlot;
-	const uint32_t accExpand = tmemBase;                      // two blocks of cExp columns: patch rows 0..127, 128..255
-	const uint32_t accProject = tmemBase + 2 * p.cExp;        // cOut columns
-	const uint32_t idescExpand = umma_idesc_tf32(128, p.cExp);
+	// expand accumulators, two sets (tile parity) of two blocks of HALO_N columns: channels 0..127, 128..255
+	const uint32_t accExpand = tmemBase;
+	const uint32_t accProject = tmemBase + 4 * HALO_N;         // cOut columns; lanes 64..127 = the tile's 64 pixels
+	const uint32_t idescExpand = umma_idesc_tf32(128, HALO_N);
 	const uint32_t idescProject = umma_idesc_tf32(128, p.cOut);
+	const Act actExp = make_act(p.actExp, p.actExpParam), actDw = make_act(p.actDw, p.actDwParam);
 
-	auto tile_origin = [&](int tile, int& n, int& y0, int& x0) {
+	// Roles.  The lane quarter a warp may read (warp % 4) holds the 32 channels of chunk `combo`; a chunk has two
+	// depthwise warps, one per pair of output rows.  Quarters 2 and 3 exist only in the first 128-channel block: of
+	// their other warps, 10 and 11 are the helpers -- they store the finished tile (its pixels sit in lanes 64..127,
+	// their quarters) and fetch and split the next patch -- and warps 14 and 15 issue the MMAs (expand / project;
+	// issuing costs 50-80 cycles per instruction, so they do nothing else and nothing waits on them but the MMAs).
+	const int quad = warp & 3, slot = warp >> 2;
+	const bool helper = warp == 10 || warp == 11;
+	const bool issuerA = warp == 14;                       // expand, and the even chunks of project
+	const bool issuerB = warp == 15;                       // the odd chunks of project, into the second accumulator
+	// (the whole warp walks the issue code and one elected lane issues: instructions issued from a lone lane of a
+	// diverged warp cost about twice as many cycles each)
+	const bool dual = 4 * HALO_N + 2 * p.cOut <= TMEM_COLS && chunks > 1; // room (and use) for two output accumulators
+	const int block = quad < 2 ? slot >> 1 : 0;             // which 128-channel block
+	const int combo = block * 4 + quad;                     // chunk index = channels [32 * combo, +32)
+	const int rowPair = slot & 1;                           // output rows 2 * rowPair, 2 * rowPair + 1
+	const bool worker = (quad < 2 || slot < 2) && combo < chunks;
+	const int helperIndex = (warp - 10) * 32 + lane;       // 0..63 among the helper threads
+	const int ch = combo * CHUNK + lane;
+	float k[9], biasExp = 0.f, biasDw = 0.f;
+	if(worker) {
+#pragma unroll
+		for(int t = 0; t < 9; ++t) k[t] = __ldg(p.wDw + t * p.cExp + ch);
+		biasExp = p.bExp != nullptr ? __ldg(p.bExp + ch) : 0.f;
+		biasDw = p.bDw != nullptr ? __ldg(p.bDw + ch) : 0.f;
+	}
+
+	const int myTiles = static_cast<int>(blockIdx.x) < p.numTiles ? (p.numTiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+	auto tile_origin = [&](int j, int& n, int& y0, int& x0) {   // the CTA's j-th tile
+		const int tile = blockIdx.x + j * gridDim.x;
 		const int perImage = p.tilesX * p.tilesY;
 		n = tile / perImage;
 		const int r = tile - n * perImage;
@@ -172,25 +229,15 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 		y0 = tyi * TH;
 		x0 = (r - tyi * p.tilesX) * TW;
 	};
-	auto load_patch = [&](int tile) {
+	auto load_patch = [&](int j) {
 		int n, y0, x0;
-		tile_origin(tile, n, y0, x0);
+		tile_origin(j, n, y0, x0);
 		mbar_arrive_expect_tx(patchBar, PATCH_BYTES);
 		tma_load_4d(smem_u32(smem + L.patchHi), &mapX, patchBar, 0, x0 - 1, y0 - 1, n);
 	};
-
-	bool ok = true;
-	uint32_t projectCommits = 0; // project commits issued so far (same count in every thread)
-	if(tid == 0 && static_cast<int>(blockIdx.x) < p.numTiles) load_patch(blockIdx.x);
-	int local = 0;
-	for(int tile = blockIdx.x; tile < p.numTiles && ok; tile += gridDim.x, ++local) {
-		int img, y0, x0;
-		tile_origin(tile, img, y0, x0);
-		// ---- 1. the patch has landed; its lo part (or, in plain TF32, its rounded copy) beside it
-		// (every wait is followed by a block-wide vote, so that all threads leave together if one of them gave up)
-		ok = mbar_wait_bounded(patchBar, local & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PATCH);
-		if(!__syncthreads_and(ok)) { ok = false; break; }
-		for(int i = tid; i < HALO * 8; i += THREADS) {
+	// lo part (or, in plain TF32, the rounded copy) of the patch, by `count` threads of which this one is `index`
+	auto split_patch = [&](int index, int count) {
+		for(int i = index; i < HALO * 8; i += count) {
 			float4 v = *reinterpret_cast<const float4*>(smem + L.patchHi + i * 16);
 			if(THREEX) {
 				v.x = lo_part(v.x); v.y = lo_part(v.y); v.z = lo_part(v.z); v.w = lo_part(v.w);
@@ -200,18 +247,19 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 			*reinterpret_cast<float4*>(smem + L.patchLo + i * 16) = v;
 		}
 		fence_proxy_async_smem();
-		tc_fence_before_sync();
-		__syncthreads();
-		// ---- 2. expand, all channels
-		if(tid == 0) {
-			tc_fence_after_sync();
-			const uint64_t bHi = umma_desc_k128(smem_u32(smem + L.wExpHi));
-			const uint64_t bLo = umma_desc_k128(smem_u32(smem + L.wExpLo));
-#pragma unroll
-			for(int mt = 0; mt < 2; ++mt) {
-				const uint64_t aHi = umma_desc_k128(smem_u32(smem + L.patchHi) + mt * 128 * 128);
-				const uint64_t aLo = umma_desc_k128(smem_u32(smem + L.patchLo) + mt * 128 * 128);
-				const uint32_t d = accExpand + mt * p.cExp;
+	};
+	// Issuing an MMA costs the issuing thread 50-80 cycles whatever its size, so the work is split over two warps:
+	// one issues expand and the even chunks of project, the other the odd chunks (into a second accumulator).
+	auto issue_expand = [&](int e) {
+		tc_fence_after_sync();
+		const uint64_t bHi = umma_desc_k128(smem_u32(smem + L.patchHi));
+		const uint64_t bLo = umma_desc_k128(smem_u32(smem + L.patchLo));
+		const int blocks = p.cExp > 128 ? 2 : 1;
+		for(int mt = 0; mt < blocks; ++mt) {
+			const uint64_t aHi = umma_desc_k128(smem_u32(smem + L.wExpHi) + mt * 128 * 128);
+			const uint64_t aLo = umma_desc_k128(smem_u32(smem + L.wExpLo) + mt * 128 * 128);
+			const uint32_t d = accExpand + (e & 1) * 2 * HALO_N + mt * HALO_N;
+			if(elect_one()) {
 #pragma unroll
 				for(int ks = 0; ks < CIN / 8; ++ks) {
 					if(THREEX) {
@@ -219,138 +267,233 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 						umma_tf32_ss(d, aHi + 2 * ks, bHi + 2 * ks, idescExpand, 1u);
 						umma_tf32_ss(d, aHi + 2 * ks, bLo + 2 * ks, idescExpand, 1u);
 					} else {
-						umma_tf32_ss(d, aLo + 2 * ks, bHi + 2 * ks, idescExpand, ks > 0 ? 1u : 0u); // the rounded copy
+						umma_tf32_ss(d, aHi + 2 * ks, bLo + 2 * ks, idescExpand, ks > 0 ? 1u : 0u); // rounded weights x rounded patch
 					}
 				}
 			}
-			umma_commit(expandBar);
+			__syncwarp();
 		}
-		ok = mbar_wait_bounded(expandBar, local & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_EXPAND);
-		if(!__syncthreads_and(ok)) { ok = false; break; }
+		if(elect_one()) umma_commit(&expandBar[e & 1]);
+		__syncwarp();
+	};
+	auto wait_expand = [&](int e) {
+		return mbar_wait_bounded(&expandBar[e & 1], (e >> 1) & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_EXPAND);
+	};
+	// part 0: the even chunks (all chunks when there is one accumulator) into accumulator 0; part 1: the odd chunks
+	// into accumulator 1; the store adds the two.  Each part ends with its own commit.
+	auto issue_project = [&](int part) {
 		tc_fence_after_sync();
-		// the patch buffers are free: the next tile's patch travels while this tile is worked on
-		if(tid == 0 && tile + static_cast<int>(gridDim.x) < p.numTiles) load_patch(tile + gridDim.x);
-
-		const int quad = warp & 3, half = warp >> 2;
-		for(int c = 0; c < chunks && ok; ++c) {
-			// ---- 3a. expanded chunk: tensor memory -> + bias, activation, zero outside the image -> shared memory
+		const uint32_t acc = accProject + part * p.cOut;
+		const int step = dual ? 2 : 1;
+		bool firstMma = true;
+		for(int c = part; c < chunks; c += step) {
+			// the chunk's pixel rows are rows 64..127 of the block that begins one chunk earlier
+			const uint64_t aHi = umma_desc_k128(smem_u32(smem + L.a2Hi) + (c - 1) * A2_CHUNK_BYTES);
+			const uint64_t aLo = umma_desc_k128(smem_u32(smem + L.a2Lo) + (c - 1) * A2_CHUNK_BYTES);
+			const uint64_t bHi = umma_desc_k128(smem_u32(smem + L.wDownHi) + c * p.cOut * 128);
+			const uint64_t bLo = umma_desc_k128(smem_u32(smem + L.wDownLo) + c * p.cOut * 128);
+			if(elect_one()) {
 #pragma unroll
-			for(int mt = 0; mt < 2; ++mt) {
-				const int rowBase = mt * 128 + quad * 32;
-				if(rowBase < HALO) { // warp-uniform
-					float v[16];
-					tmem_ld16(accExpand + (static_cast<uint32_t>(quad * 32) << 16) + mt * p.cExp + c * CHUNK + half * 16, v);
-					const int row = rowBase + lane;
-					if(row < HALO) {
-						const int hy = row / HW, hx = row - hy * HW;
-						const int gy = y0 - 1 + hy, gx = x0 - 1 + hx;
-						const bool inside = gy >= 0 && gy < p.h && gx >= 0 && gx < p.w;
-						float* dst = e + row * E_STRIDE + half * 16;
-						const float* b = bExp + c * CHUNK + half * 16;
-#pragma unroll
-						for(int j = 0; j < 16; ++j) dst[j] = inside ? apply_act(v[j] + b[j], p.actExp, p.actExpParam) : 0.f;
+				for(int ks = 0; ks < CHUNK / 8; ++ks) {
+					const uint32_t first = (firstMma && ks == 0) ? 0u : 1u;
+					if(THREEX) {
+						umma_tf32_ss(acc, aLo + 2 * ks, bHi + 2 * ks, idescProject, first);
+						umma_tf32_ss(acc, aHi + 2 * ks, bHi + 2 * ks, idescProject, 1u);
+						umma_tf32_ss(acc, aHi + 2 * ks, bLo + 2 * ks, idescProject, 1u);
+					} else {
+						umma_tf32_ss(acc, aHi + 2 * ks, bHi + 2 * ks, idescProject, first);
 					}
 				}
 			}
-			// the project MMAs of the chunk before have to be through with the A tile that is overwritten next
-			ok = projectCommits == 0
-				|| mbar_wait_bounded(projectBar, (projectCommits - 1) & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PROJECT);
-			if(!__syncthreads_and(ok)) { ok = false; break; }
-			// ---- 3b. depthwise 3x3: a warp per output column, a lane per channel
-			{
-				const int ch = c * CHUNK + lane;
-				float k[9];
+			firstMma = false;
+			__syncwarp();
+		}
+		if(elect_one()) umma_commit(projectBar);
+		__syncwarp();
+	};
+	// the finished tile j: tensor memory lanes 64..127 -> + bias, + residual -> global memory (helper warps; one
+	// pixel per lane, 16 channels at a time; the residual is in flight together with the tensor-memory loads).
+	// `ready` waits for project(j).
+	auto store_tile = [&](int j, auto&& ready) -> bool {
+		int img, y0, x0;
+		tile_origin(j, img, y0, x0);
+		const int px = (quad - 2) * 32 + lane;
+		const int ty = px / TW, tx = px - ty * TW;
+		const int gy = y0 + ty, gx = x0 + tx;
+		const bool valid = gy < p.h && gx < p.w;
+		const size_t pixel = (static_cast<size_t>(img) * p.h + gy) * p.w + gx;
+		if(!ready()) return false;
+		tc_fence_after_sync();
+		const uint32_t src = accProject + (static_cast<uint32_t>(quad * 32) << 16);
+		float* dst = p.y + pixel * p.cOut;
+		for(int piece = 0; piece * 16 < p.cOut; ++piece) {
+			uint32_t v[16], u[16];
+			tmem_ld16_issue(src + piece * 16, v);
+			if(dual) tmem_ld16_issue(src + p.cOut + piece * 16, u);
+			float4 res[4];
+			if(p.residual && valid) { // c_out == 32 = CIN here; in flight together with the tensor-memory loads
 #pragma unroll
-				for(int t = 0; t < 9; ++t) k[t] = wDw[t * p.cExp + ch];
-				const float bias = bDw[ch];
+				for(int q = 0; q < 4; ++q) res[q] = __ldg(reinterpret_cast<const float4*>(p.x + pixel * CIN + piece * 16) + q);
+			}
+			tmem_ld_wait();
+			if(valid) {
 #pragma unroll
-				for(int col = 0; col < 2; ++col) {
-					const int tx = warp * 2 + col;
-					float win[HH][3];
+				for(int q = 0; q < 4; ++q) {
+					float o[4];
 #pragma unroll
-					for(int hy = 0; hy < HH; ++hy) {
+					for(int i = 0; i < 4; ++i) {
+						o[i] = __uint_as_float(v[4 * q + i]);
+						if(dual) o[i] += __uint_as_float(u[4 * q + i]);
+						o[i] += bDown[piece * 16 + 4 * q + i];
+					}
+					if(p.residual) { o[0] += res[q].x; o[1] += res[q].y; o[2] += res[q].z; o[3] += res[q].w; }
+					reinterpret_cast<float4*>(dst + piece * 16)[q] = make_float4(o[0], o[1], o[2], o[3]);
+				}
+			}
+		}
+		return true;
+	};
+	auto project_done = [&](int j) {
+		bool done = mbar_wait_bounded(projectBar, j & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PROJECT);
+		return static_cast<bool>(__all_sync(0xffffffffu, done));
+	};
+
+	// ---- prologue: patch 0 -> expand 0, patch 1 -> expand 1 (every thread helps to split; later the helpers do)
+	bool ok = true;
+	for(int e = 0; e < 2 && e < myTiles && ok; ++e) {
+		if(e > 0) {
+			ok = wait_expand(e - 1); // the patch buffers are free
+			ok = __syncthreads_and(ok) != 0;
+			if(!ok) break;
+		}
+		if(tid == 0) load_patch(e);
+		ok = mbar_wait_bounded(patchBar, e & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PATCH);
+		ok = __syncthreads_and(ok) != 0;
+		if(!ok) break;
+		split_patch(tid, THREADS);
+		tc_fence_before_sync();
+		__syncthreads();
+		if(issuerA) issue_expand(e);
+	}
+	for(int j = 0; j < myTiles && ok; ++j) {
+		int img, y0, x0;
+		tile_origin(j, img, y0, x0);
+		if(worker) {
+			// ---- depthwise(j): expand(j) is in tensor memory (set j & 1)
+			ok = wait_expand(j);
+			ok = __all_sync(0xffffffffu, ok);
+			float out[2][TW];
+			if(ok) {
+				tc_fence_after_sync();
+				const uint32_t src = accExpand + (static_cast<uint32_t>(quad * 32) << 16) + (j & 1) * 2 * HALO_N + block * HALO_N
+					+ rowPair * 2 * HW;
+				uint32_t raw[56], last[24];
+				tmem_ld32_issue(src, raw);
+				tmem_ld16_issue(src + 32, raw + 32);
+				tmem_ld8_issue_local(src + 48, raw + 48);      // halo rows 0..2 are columns 0..53
+				tmem_ld16_issue(src + 54, last);                // halo row 3: columns 54..69 ...
+				tmem_ld8_issue_local(src + 64, last + 16);      // ... and 70, 71 (elements 6, 7 of this piece)
+				// which halo pixels lie inside the image: bit hx of rowBits[hy] (the same for every lane)
+				uint32_t colBits = 0;
 #pragma unroll
-						for(int dx = 0; dx < 3; ++dx) win[hy][dx] = e[(hy * HW + tx + dx) * E_STRIDE + lane];
+				for(int hx = 0; hx < HW; ++hx) {
+					const int gx = x0 - 1 + hx;
+					colBits |= (gx >= 0 && gx < p.w) ? (1u << hx) : 0u;
+				}
+				uint32_t rowBits[4];
+#pragma unroll
+				for(int r = 0; r < 4; ++r) {
+					const int gy = y0 - 1 + rowPair * 2 + r;
+					rowBits[r] = (gy >= 0 && gy < p.h) ? colBits : 0u;
+				}
+				tmem_ld_wait();
+				float win[3][HW];
+#pragma unroll
+				for(int r = 0; r < 3; ++r) {
+#pragma unroll
+					for(int hx = 0; hx < HW; ++hx) {
+						const float v = actExp(__uint_as_float(raw[r * HW + hx]) + biasExp);
+						win[r][hx] = ((rowBits[r] >> hx) & 1u) ? v : 0.f;
+					}
+				}
+#pragma unroll
+				for(int t = 0; t < 2; ++t) {
+					if(t == 1) {
+						// slide down: halo row 3 takes the place of halo row 0 (row index (t + dy) % 3 below)
+#pragma unroll
+						for(int hx = 0; hx < HW; ++hx) {
+							const uint32_t bits = hx < 16 ? last[hx] : last[16 + 6 + (hx - 16)];
+							const float v = actExp(__uint_as_float(bits) + biasExp);
+							win[0][hx] = ((rowBits[3] >> hx) & 1u) ? v : 0.f;
+						}
 					}
 #pragma unroll
-					for(int ty = 0; ty < TH; ++ty) {
-						float acc = 0.f;
+					for(int tx = 0; tx < TW; ++tx) {
+						float acc = biasDw;
 #pragma unroll
 						for(int dy = 0; dy < 3; ++dy) {
 #pragma unroll
-							for(int dx = 0; dx < 3; ++dx) acc = fmaf(win[ty + dy][dx], k[dy * 3 + dx], acc);
+							for(int dx = 0; dx < 3; ++dx) acc = fmaf(win[(t + dy) % 3][tx + dx], k[dy * 3 + dx], acc);
 						}
-						const float v = apply_act(acc + bias, p.actDw, p.actDwParam);
-						const uint32_t off = swz(ty * TW + tx, lane);
-						if(THREEX) {
-							*reinterpret_cast<float*>(smem + L.a2Hi + off) = v;
-							*reinterpret_cast<float*>(smem + L.a2Lo + off) = lo_part(v);
-						} else {
-							*reinterpret_cast<float*>(smem + L.a2Hi + off) = to_tf32(v);
+						out[t][tx] = actDw(acc);
+					}
+				}
+				// project(j-1) still reads the A tiles when this tile's arithmetic is done early: wait, then write
+				if(j > 0) {
+					ok = mbar_wait_bounded(projectBar, (j - 1) & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PROJECT);
+					ok = __all_sync(0xffffffffu, ok);
+				}
+				if(ok) {
+					// pixel ty * 16 + tx of this chunk's A tile; the swizzle phase of its row is (tx & 7)
+					uint8_t* const aHi = smem + L.a2Hi + combo * A2_CHUNK_BYTES + ((lane & 3u) << 2);
+					uint8_t* const aLo = smem + L.a2Lo + combo * A2_CHUNK_BYTES + ((lane & 3u) << 2);
+					const uint32_t kChunk = static_cast<uint32_t>(lane) >> 2;
+#pragma unroll
+					for(int t = 0; t < 2; ++t) {
+#pragma unroll
+						for(int tx = 0; tx < TW; ++tx) {
+							const float v = out[t][tx];
+							const uint32_t off = ((rowPair * 2 + t) * TW + tx) * 128u + ((kChunk ^ (tx & 7u)) << 4);
+							if(THREEX) {
+								*reinterpret_cast<float*>(aHi + off) = v;
+								*reinterpret_cast<float*>(aLo + off) = lo_part(v);
+							} else {
+								*reinterpret_cast<float*>(aHi + off) = to_tf32(v);
+							}
 						}
 					}
+					fence_proxy_async_smem();
 				}
 			}
-			fence_proxy_async_smem();
-			tc_fence_before_sync();
-			__syncthreads();
-			// ---- 3c. project: this chunk's 32 channels into the output tile
-			if(tid == 0) {
-				tc_fence_after_sync();
-				const uint64_t aHi = umma_desc_k128(smem_u32(smem + L.a2Hi));
-				const uint64_t aLo = umma_desc_k128(smem_u32(smem + L.a2Lo));
-				const uint64_t bHi = umma_desc_k128(smem_u32(smem + L.wDownHi) + c * p.cOut * 128);
-				const uint64_t bLo = umma_desc_k128(smem_u32(smem + L.wDownLo) + c * p.cOut * 128);
-#pragma unroll
-				for(int ks = 0; ks < CHUNK / 8; ++ks) {
-					const uint32_t first = (c > 0 || ks > 0) ? 1u : 0u;
-					if(THREEX) {
-						umma_tf32_ss(accProject, aLo + 2 * ks, bHi + 2 * ks, idescProject, first);
-						umma_tf32_ss(accProject, aHi + 2 * ks, bHi + 2 * ks, idescProject, 1u);
-						umma_tf32_ss(accProject, aHi + 2 * ks, bLo + 2 * ks, idescProject, 1u);
-					} else {
-						umma_tf32_ss(accProject, aHi + 2 * ks, bHi + 2 * ks, idescProject, first);
-					}
+		} else if(helper) {
+			// ---- patch j+2: its buffers are free once expand(j+1) has completed
+			if(j + 2 < myTiles) {
+				ok = wait_expand(j + 1);
+				ok = __all_sync(0xffffffffu, ok);
+				if(ok) {
+					if(helperIndex == 0) load_patch(j + 2);
+					ok = mbar_wait_bounded(patchBar, (j + 2) & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PATCH);
+					ok = __all_sync(0xffffffffu, ok);
+					if(ok) split_patch(helperIndex, 64);
 				}
-				umma_commit(projectBar);
 			}
-			++projectCommits;
-		}
-		if(!ok) break;
-		// ---- 4. the output tile
-		ok = mbar_wait_bounded(projectBar, (projectCommits - 1) & 1, abortFlag, p.status, (KERNEL_ID << 8) | SITE_PROJECT);
-		if(!__syncthreads_and(ok)) { ok = false; break; }
-		tc_fence_after_sync();
-		{
-			const int px = quad * 32 + lane;
-			const int ty = px / TW, tx = px - ty * TW;
-			const int gy = y0 + ty, gx = x0 + tx;
-			const bool valid = gy < p.h && gx < p.w;
-			const size_t pixel = (static_cast<size_t>(img) * p.h + gy) * p.w + gx;
-			for(int piece = half; piece * 16 < p.cOut; piece += 2) {
-				float v[16];
-				tmem_ld16(accProject + (static_cast<uint32_t>(quad * 32) << 16) + piece * 16, v);
-				if(valid) {
-					float* dst = p.y + pixel * p.cOut + piece * 16;
-					const float* res = p.residual ? p.x + pixel * CIN + piece * 16 : nullptr;
-#pragma unroll
-					for(int q = 0; q < 4; ++q) {
-						float4 o = make_float4(v[4 * q] + bDown[piece * 16 + 4 * q], v[4 * q + 1] + bDown[piece * 16 + 4 * q + 1],
-							v[4 * q + 2] + bDown[piece * 16 + 4 * q + 2], v[4 * q + 3] + bDown[piece * 16 + 4 * q + 3]);
-						if(res != nullptr) {
-							const float4 r = __ldg(reinterpret_cast<const float4*>(res) + q);
-							o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
-						}
-						reinterpret_cast<float4*>(dst)[q] = o;
-					}
-				}
+			// ---- store(j-1): its project MMAs were issued behind the last barrier
+			if(ok && j > 0) {
+				ok = store_tile(j - 1, [&] { return project_done(j - 1); });
 			}
 		}
-		// tensor memory and the chunk buffers go back to the next tile
+		// ---- the barrier: tile j's A tiles are written, its expand accumulators read, the output tile of j-1 stored,
+		// patch j+2 split
 		tc_fence_before_sync();
-		__syncthreads();
-		tc_fence_after_sync();
+		if(!__syncthreads_and(ok)) { ok = false; break; }
+		if(issuerA) {
+			if(j + 2 < myTiles) issue_expand(j + 2);
+			issue_project(0);
+		} else if(issuerB && dual) {
+			issue_project(1);
+		}
 	}
+	if(ok && myTiles > 0 && helper) ok = store_tile(myTiles - 1, [&] { return project_done(myTiles - 1); });
 	if(!ok) {
 		// a wait gave up: let whatever was issued (a TMA load, MMAs) come to rest before tensor memory is freed
 		const uint64_t t0 = global_timer_ns();
@@ -359,7 +502,7 @@ __global__ void __launch_bounds__(THREADS, 1) mbv2_fused_kernel(const FusedParam
 	}
 	tc_fence_before_sync();
 	__syncthreads();
-	if(warp == 0) tmem_dealloc(tmemBase, 512);
+	if(warp == 0) tmem_dealloc(tmemBase, TMEM_COLS);
 }
 
 } // namespace
@@ -384,13 +527,13 @@ bool launch_mbv2_fused(void* stream, const nb200_mbv2_desc* d, const float* x, c
 	const long long tiles = static_cast<long long>(d->batch) * p.tilesX * p.tilesY;
 	if(tiles > 0x7fffffffLL) return false;
 	p.numTiles = static_cast<int>(tiles);
+	const SmemLayout L = smem_layout(d->c_exp, d->c_out);
+	const size_t smemBytes = L.total + 1024;
+	if(smemBytes > 227 * 1024) return false;
 	p.status = device_status_word();
 	if(p.status == nullptr) { *rc = NB200_ENODEVICE; return true; }
 	CUtensorMap map;
 	if(!make_image_box_map(&map, x, CIN, d->w, d->h, d->batch, CIN, HW, HH, true)) return false;
-	const SmemLayout L = smem_layout(d->c_exp, d->c_out);
-	const size_t smemBytes = L.total + 1024;
-	if(smemBytes > 227 * 1024) return false;
 	const int grid = p.numTiles < sm_count() ? p.numTiles : sm_count();
 	cudaError_t e;
 	if(precision == NB200_PREC_3XTF32) {

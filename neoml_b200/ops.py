@@ -158,7 +158,8 @@ def BlobChannelwiseConvolution(source, filter, free_term=None, result=None, *, p
 def MobileNetV2Block(source, expand_filter, expand_free_term, channelwise_filter, channelwise_free_term, down_filter,
                      down_free_term, result=None, *, stride=1, residual=False, expand_act=ACT_RELU,
                      expand_act_param=6.0, channelwise_act=ACT_RELU, channelwise_act_param=6.0, scratch=None,
-                     precision=PREC_3XTF32):
+                     precision=PREC_3XTF32, one_kernel=False):
+    """one_kernel: the block as a single kernel (nb200_mobilenetv2_block_fused; raises for shapes it does not cover)."""
     n, h, w, c_in = source.shape
     c_exp = expand_filter.shape[0]
     c_out = down_filter.shape[0]
@@ -171,7 +172,8 @@ def MobileNetV2Block(source, expand_filter, expand_free_term, channelwise_filter
     ho, wo = conv_output_size(h, 3, 1, stride), conv_output_size(w, 3, 1, stride)
     if result is None:
         result = torch.empty((n, ho, wo, c_out), dtype=torch.float32, device=source.device)
-    capi.check("MobileNetV2Block", lib.nb200_mobilenetv2_block(
+    entry = lib.nb200_mobilenetv2_block_fused if one_kernel else lib.nb200_mobilenetv2_block
+    capi.check("MobileNetV2Block", entry(
         _stream(), C.byref(desc), _ptr(source), _ptr(expand_filter), _ptr(expand_free_term), _ptr(channelwise_filter),
         _ptr(channelwise_free_term), _ptr(down_filter), _ptr(down_free_term), _ptr(result), _ptr(scratch), precision))
     return result

@@ -616,8 +616,8 @@ FUSED_MBV2 = [
     (1, 19, 23, 96, 32, True, (1, 6.0), (1, 6.0), (True, True, True)),      # ragged in both directions
     (3, 9, 33, 192, 32, True, (1, 0.0), (2, 0.0), (True, False, True)),     # ReLU without threshold, HSwish
     (2, 17, 5, 64, 16, False, (2, 0.0), (1, 6.0), (False, True, False)),    # narrower than a tile, 16 outputs
-    (1, 24, 40, 160, 64, False, (1, 6.0), (1, 6.0), (True, True, True)),    # 64 outputs, five chunks
-    (5, 14, 14, 192, 48, False, (1, 6.0), (1, 6.0), (True, True, True)),    # 48 outputs
+    (1, 24, 40, 96, 64, False, (1, 6.0), (1, 6.0), (True, True, True)),     # 64 outputs, three chunks
+    (5, 14, 14, 96, 48, False, (1, 6.0), (1, 6.0), (True, True, True)),     # 48 outputs
 ]
 
 
@@ -640,7 +640,7 @@ def test_fused_mobilenetv2_block(ops, oracle, shape, prec, tol):
     launches = lib.nb200_launch_count()
     y = ops.MobileNetV2Block(dev(x), dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), stride=1, residual=res,
                              expand_act=a1, expand_act_param=p1, channelwise_act=a2, channelwise_act_param=p2,
-                             precision=prec)
+                             precision=prec, one_kernel=True)
     got = host(y)
     assert lib.nb200_launch_count() - launches == 1, "the block did not run as one kernel"
     assert lib.nb200_device_status(None, 0) == 0
@@ -649,5 +649,5 @@ def test_fused_mobilenetv2_block(ops, oracle, shape, prec, tol):
         # in place over the input, as NeoML calls it when it may: the result goes through the scratch
         xd = dev(x)
         ops.MobileNetV2Block(xd, dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), result=xd, stride=1, residual=True,
-                             expand_act=a1, expand_act_param=p1, channelwise_act=a2, channelwise_act_param=p2)
+                             expand_act=a1, expand_act_param=p1, channelwise_act=a2, channelwise_act_param=p2, one_kernel=True)
         assert np.array_equal(host(xd), got)
