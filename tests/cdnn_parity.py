@@ -9,7 +9,9 @@ uses one CPU engine per host thread on slices of the batch (what NeoML's CDistri
 NeoML/src/Dnn/DnnDistributed.cpp:551-607); the GPU side runs the whole batch on one engine.
 
 Error figures: gate = max|g - w| / max(|w|, RMS(w)) (norm-wise); strict = the same with the floor 1e-3 * RMS(w).
-Index outputs are compared bit for bit.
+Index outputs are compared bit for bit.  With --exact the same two figures are also given for each engine against an
+evaluation in double precision (torch on the CPU, float64; configurations 1, 2, 3 -- its first 16 images -- and 5):
+the distance of the reference's own CPU engine from the exact result is the yardstick for the other one.
 """
 from __future__ import annotations
 
@@ -20,6 +22,13 @@ import time
 from pathlib import Path
 
 import numpy as np
+
+# torch (used by --exact) has to come first: importing it after NeoML's math-engine library has been loaded crashes
+# inside torch's own start-up
+try:
+    import torch  # noqa: F401
+except ImportError:
+    pass
 
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
@@ -92,6 +101,51 @@ def run_gpu(model, inputs: dict, sinks: list[str], flags: int):
         eng.close()
 
 
+def exact_conv(x, f, bias, pad):
+    import torch
+    import torch.nn.functional as F
+    y = F.conv2d(torch.from_numpy(x).double().permute(0, 3, 1, 2), torch.from_numpy(f).double().permute(0, 3, 1, 2),
+                 torch.from_numpy(bias).double(), padding=pad)
+    return y.permute(0, 2, 3, 1).numpy()
+
+
+def exact_mbv2(x, we, be, wd, bd, wp, bp):
+    import torch
+    import torch.nn.functional as F
+    t = torch.from_numpy(x).double()
+    e = torch.clamp(t @ torch.from_numpy(we).double().T + torch.from_numpy(be).double(), 0, 6)
+    c = we.shape[0]
+    d = F.conv2d(e.permute(0, 3, 1, 2), torch.from_numpy(wd).double().permute(2, 0, 1).unsqueeze(1),
+                 torch.from_numpy(bd).double(), padding=1, groups=c).permute(0, 2, 3, 1)
+    d = torch.clamp(d, 0, 6)
+    return (d @ torch.from_numpy(wp).double().T + torch.from_numpy(bp).double() + t).numpy()
+
+
+def exact_resnet50(weights, x):
+    """Probabilities in double precision, the same graph as neoml_b200.resnet50.forward."""
+    import torch
+    import torch.nn.functional as F
+    w = {k: torch.from_numpy(v).double() for k, v in weights.items()}
+
+    def conv(name, t, stride, pad, relu, residual=None):
+        y = F.conv2d(t, w[name + ".w"].permute(0, 3, 1, 2), w[name + ".b"], stride=stride, padding=pad)
+        if residual is not None:
+            y = y + residual
+        return torch.relu(y) if relu else y
+    t = conv("stem", torch.from_numpy(x).double().permute(0, 3, 1, 2), 2, 3, True)
+    t = F.max_pool2d(t, 3, 2, 1)
+    for si, (mid, out, blocks, stride) in enumerate(resnet50.STAGES):
+        for bi in range(blocks):
+            s = stride if bi == 0 else 1
+            p = f"s{si + 1}b{bi + 1}"
+            shortcut = conv(p + "_down", t, s, 0, False) if bi == 0 else t
+            u = conv(p + "_c1", t, 1, 0, True)
+            u = conv(p + "_c2", u, s, 1, True)
+            t = conv(p + "_c3", u, 1, 0, True, residual=shortcut)
+    logits = t.mean(dim=(2, 3)) @ w["fc.w"].T + w["fc.b"]
+    return torch.softmax(logits, dim=1).numpy()
+
+
 def config(n: str, scale: str):
     full = scale == "full"
     if n == "1":
@@ -101,22 +155,27 @@ def config(n: str, scale: str):
         f = r.uniform(-1, 1, (k, 3, 3, c)).astype(np.float32)
         bias = r.uniform(-1, 1, k).astype(np.float32)
         return dict(name=f"config1 BlobConvolution {b}x{h}x{w}x{c} -> {k}, 3x3/1 pad 1",
-                    model=cdnn.Model.conv(f, bias, padding=(1, 1)), inputs={"in": (x, None, True)}, sinks=["out"])
+                    model=cdnn.Model.conv(f, bias, padding=(1, 1)), inputs={"in": (x, None, True)}, sinks=["out"],
+                    exact=lambda: {"out": exact_conv(x, f, bias, 1).reshape(b, -1)})
     if n == "2":
         b, h, w, c, e = (64, 56, 56, 32, 192) if full else (2, 14, 14, 32, 192)
         r = rng_for(202)
         x = r.uniform(0, 1, (b, h, w, c)).astype(np.float32)
         he = lambda shape, fan: (r.standard_normal(shape) * np.sqrt(2.0 / fan)).astype(np.float32)
         small = lambda m: r.uniform(-0.1, 0.1, m).astype(np.float32)
+        we, be, wd, bd, wp, bp = he((e, c), c), small(e), he((3, 3, e), 9), small(e), he((c, e), e), small(c)
         return dict(name=f"config2 MobileNetV2Block {b}x{h}x{w}x{c}, expand {e}, ReLU6, residual",
-                    model=cdnn.Model.mbv2(he((e, c), c), small(e), he((3, 3, e), 9), small(e), he((c, e), e), small(c)),
-                    inputs={"in": (x, None, True)}, sinks=["out"])
+                    model=cdnn.Model.mbv2(we, be, wd, bd, wp, bp),
+                    inputs={"in": (x, None, True)}, sinks=["out"],
+                    exact=lambda: {"out": exact_mbv2(x, we, be, wd, bd, wp, bp).reshape(b, -1)})
     if n == "3":
         b, hw = (256, 224) if full else (4, 96)
         x = rng_for(303).uniform(0, 1, (b, hw, hw, 3)).astype(np.float32)
+        weights = resnet50.make_weights()
+        rows = min(b, 16)
         return dict(name=f"config3 ResNet-50 v1.5 CDnn, batch {b} x {hw}x{hw}x3",
-                    model=cdnn.Model.resnet50(resnet50.make_weights()), inputs={"in": (x, None, True)},
-                    sinks=["probs", "argmax"])
+                    model=cdnn.Model.resnet50(weights), inputs={"in": (x, None, True)},
+                    sinks=["probs", "argmax"], exact=lambda: {"probs": exact_resnet50(weights, x[:rows])}, exact_rows=rows)
     if n.startswith("4"):
         layers, b, s, hid, heads, ffn = (12, 64, 512, 768, 12, 3072) if full else (2, 4, 64, 128, 4, 256)
         x = rng_for(404).standard_normal((b, s, hid)).astype(np.float32)
@@ -135,18 +194,44 @@ def config(n: str, scale: str):
         d = (1, 1, 1, m, 1, 1, m)
         return dict(name=f"config5 MultiplyMatrixByMatrix {m}^3 (CMatrixMultiplicationLayer)", model=cdnn.Model.matmul(),
                     inputs={"a": (a, d, True), "b": (bm, d, False)}, sinks=["out"], slice_dims={"a": lambda per: d},
-                    unsliced=True)
+                    unsliced=True, exact=lambda: {"out": (a[0].astype(np.float64) @ bm[0].astype(np.float64)).reshape(1, -1)})
     raise SystemExit(f"unknown config {n}")
+
+
+def run_all(args) -> None:
+    import subprocess
+    rows = []
+    for c in ["1", "2", "3", "4", "4ones", "4causal", "5a", "5b", "5c"]:
+        cmd = [sys.executable, __file__, "--config", c, "--scale", args.scale, "--cpu-threads", str(args.cpu_threads),
+               "--flags", str(args.flags)] + (["--exact"] if args.exact else []) + (["--cpu-only"] if args.cpu_only else [])
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise SystemExit(f"config {c} failed:\n{r.stdout[-1000:]}\n{r.stderr[-3000:]}")
+        rows.append(json.loads(r.stdout.strip().splitlines()[-1]))
+        print(json.dumps(rows[-1]), file=sys.stderr)
+    fmt = lambda v: "-" if v is None else (f"{v:.2e}" if isinstance(v, float) else str(v))
+    print("| config | what | gate (GPU vs CPU engine) | strict | CPU engine vs double: gate / strict | GPU engine vs double: gate / strict | index outputs |")
+    print("|---|---|---|---|---|---|---|")
+    for r in rows:
+        sink = "probs" if any("probs" in k for k in r) else "out"
+        idx = f"{r['argmax_count'] - r['argmax_mismatches']} / {r['argmax_count']} equal" if "argmax_count" in r else "-"
+        print(f"| {r['config']} | {r['what']} | {fmt(r.get(sink + '_gate'))} | {fmt(r.get(sink + '_strict'))} | "
+              f"{fmt(r.get('cpu_vs_exact_' + sink + '_gate'))} / {fmt(r.get('cpu_vs_exact_' + sink + '_strict'))} | "
+              f"{fmt(r.get('gpu_vs_exact_' + sink + '_gate'))} / {fmt(r.get('gpu_vs_exact_' + sink + '_strict'))} | {idx} |")
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True)
+    ap.add_argument("--config", required=True, help="1, 2, 3, 4, 4ones, 4causal, 5a, 5b, 5c -- or 'all': every "
+                    "configuration in a process of its own, the rows as a markdown table on stdout")
     ap.add_argument("--scale", default="full", choices=["full", "small"])
     ap.add_argument("--cpu-threads", type=int, default=16)
     ap.add_argument("--flags", type=int, default=0, help="GPU engine flags (2 = the reference's TF32 opt-in)")
     ap.add_argument("--cpu-only", action="store_true", help="run the CPU side only (no GPU in this machine)")
+    ap.add_argument("--exact", action="store_true", help="also compare both engines with a double-precision evaluation")
     args = ap.parse_args()
+    if args.config == "all":
+        return run_all(args)
     cdnn.load()
     cfg = config(args.config, args.scale)
     threads = 1 if cfg.get("unsliced") else args.cpu_threads
@@ -169,6 +254,17 @@ def main() -> None:
         if "probs" in want:
             top2 = np.sort(want["probs"], axis=1)[:, -2:]
             row["cpu_top2_margin_min_rel"] = float(((top2[:, 1] - top2[:, 0]) / top2[:, 1]).min())
+    if args.exact and "exact" in cfg:
+        t0 = time.time()
+        truth = cfg["exact"]()
+        row["exact_seconds"] = round(time.time() - t0, 1)
+        for s, t in truth.items():
+            n = cfg.get("exact_rows", t.shape[0])
+            row[f"cpu_vs_exact_{s}_gate"] = rel_err(want[s][:n], t, 1.0)
+            row[f"cpu_vs_exact_{s}_strict"] = rel_err(want[s][:n], t, 1e-3)
+            if not args.cpu_only:
+                row[f"gpu_vs_exact_{s}_gate"] = rel_err(got[s][:n], t, 1.0)
+                row[f"gpu_vs_exact_{s}_strict"] = rel_err(got[s][:n], t, 1e-3)
     cfg["model"].close()
     print(json.dumps(row))
 
