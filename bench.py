@@ -647,6 +647,13 @@ def run_products(args):
     pr, v, ctx = torch.rand(768, 512, 512, device=dev), rnd(768, 512, 64), torch.empty(768, 512, 64, device=dev)
     cases.append(("cfg4 PV: batch 768, MultiplyMatrixByMatrix 512x512 * 512x64", 2.0 * 768 * 512 * 512 * 64,
                   lambda: ops.MultiplyMatrixByMatrix(pr, v, result=ctx, precision=prec)))
+    if prec == 0:
+        kt4 = rnd(768, 64, 512)
+        scale4 = torch.full((1,), 0.125, device=dev)
+        mask4 = torch.triu(torch.full((512, 512), -1e9, device=dev), diagonal=1)
+        cases.append(("cfg4 attention chain as one kernel: softmax(scale QK^T + mask) V, batch 768, 512 x 512 x 64",
+                      4.0 * 768 * 512 * 512 * 64,
+                      lambda: ops.AttentionScoresValues(q, kt4, v, scale=scale4, mask=mask4)))
     # config 5: square MultiplyMatrixByMatrix
     for size in (1024, 4096, 8192):
         a, b, c = rnd(1, size, size), rnd(1, size, size), torch.empty(1, size, size, device=dev)

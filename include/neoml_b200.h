@@ -96,6 +96,15 @@ NB200_API int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stre
 /* IBlasEngine::MultiplyMatrixByMatrix (NME.h:580-582): C_b[M x N] = A_b[M x K] * B_b[K x N], dense row-major. */
 NB200_API int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int m, int k,
 	const float* b, int n, float* c, const nb200_epilogue* epi, int precision);
+/* The score chain of CMultiheadAttentionLayer (NeoML/src/Dnn/Layers/MultiheadAttentionLayer.cpp:145-223) as one kernel:
+ * batched MultiplyMatrixByMatrix (NME.h:580-582) of q [batch][seq_q x depth] by kt [batch][depth x seq_to],
+ * VectorMultiply by *scale (NME.h:268; NULL = 1), AddVectorToMatrixRows of mask [seq_q x seq_to] (NME.h:456-458; the same
+ * for every batch entry, NULL = none), MatrixSoftmaxByRows (NME.h:501-502), and the batched MultiplyMatrixByMatrix of the
+ * probabilities by v [batch][seq_to x depth] -> out [batch][seq_q x depth].  The scores stay in tensor memory.
+ * depth == 64, seq_q >= 128, seq_to >= 128 and a multiple of 4, 16-byte aligned operands, NB200_PREC_3XTF32;
+ * NB200_EINVAL for anything else: issue the calls one by one then. */
+NB200_API int nb200_attention_scores_values(void* stream, int batch, const float* q, const float* kt, const float* v,
+	int seq_q, int depth, int seq_to, const float* scale, const float* mask, float* out, int precision);
 /* IDnnEngine::InitBlobConvolution + BlobConvolution (NME.h:751-756; CPU CpuMathEngineDnnConv.cpp:43-73,391-431).
  * Channels-last blobs: x [batch,h,w,c], filter [k,r,s,c], y [batch,ho,wo,k];
  * ho = 1 + (h - (r-1)*dil_h - 1 + 2*pad_h) / stride_h (same for wo) must equal the values passed. */
@@ -201,6 +210,9 @@ enum {
 	NB200_VEC_ELTWISE_MAX = 16,  /* VectorEltwiseMax                                   NME.h:169 */
 	NB200_VEC_ELTWISE_DIV = 17,  /* VectorEltwiseDivide  y = a / b                     NME.h:291 */
 	NB200_VEC_MUL_ADD = 18,      /* VectorMultiplyAndAdd y = a + b * *scalar           NME.h:259 */
+	NB200_VEC_SIGMOID_MUL = 19,  /* VectorMultiply, VectorSigmoid, VectorEltwiseMultiply as CGELULayer chains them
+	                                (NeoML/src/Dnn/Layers/GELULayer.cpp, the fast form): y = sigmoid(a * *scalar) * a,
+	                                the same roundings as the three calls, one pass */
 	NB200_VEC_OP_COUNT
 };
 NB200_API int nb200_vector_op(void* stream, int op, const float* a, const float* b, const float* scalar,
@@ -248,6 +260,13 @@ NB200_API int nb200_find_max_value_in_columns(void* stream, int batch, const flo
  * max_indices (optional) receives the flat in-image index of each maximum. */
 NB200_API int nb200_blob_max_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w,
 	int stride_h, int stride_w, const float* x, float* y, int* max_indices);
+/* BlobResizeImage with constant padding (NME.h:1020-1023) followed by BlobMaxPooling (NME.h:817-822) as one pass: the
+ * windows slide over x [batch,h,w,c] surrounded by pad_* rows / columns of pad_value; y is what pooling the padded
+ * image would give, the padded image is never written.  3x3 windows with stride 2 and c % 4 == 0 only (the padded stem
+ * pool of the ResNets); NB200_EINVAL for any other form: pad and pool with the two calls then. */
+NB200_API int nb200_blob_max_pooling_padded(void* stream, int batch, int h, int w, int c, int pad_left, int pad_right,
+	int pad_top, int pad_bottom, float pad_value, int filter_h, int filter_w, int stride_h, int stride_w, const float* x,
+	float* y);
 /* InitMeanPooling + BlobMeanPooling (NME.h:837-841). */
 NB200_API int nb200_blob_mean_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w,
 	int stride_h, int stride_w, const float* x, float* y);

@@ -17,6 +17,7 @@ ACT_NONE, ACT_RELU, ACT_HSWISH = 0, 1, 2
 VEC_OPS = ["COPY", "FILL", "FILL_HANDLE", "ADD", "SUB", "ELTWISE_MUL", "MULTIPLY", "NEG_MULTIPLY", "ADD_VALUE",
            "RELU", "SIGMOID", "SQRT", "INV", "TANH", "EXP", "HSWISH", "ELTWISE_MAX", "ELTWISE_DIV", "MUL_ADD"]
 VEC = {name: i for i, name in enumerate(VEC_OPS)}
+VEC["SIGMOID_MUL"] = len(VEC_OPS)   # the library's own: three of the calls above in one pass (NB200_VEC_SIGMOID_MUL)
 
 
 class Epilogue(C.Structure):
@@ -83,6 +84,8 @@ SIGNATURES = {
     "nb200_find_max_value_in_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "nb200_find_max_value_in_columns": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp]),
     "nb200_blob_max_pooling": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "nb200_attention_scores_values": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i]),
+    "nb200_blob_max_pooling_padded": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp]),
     "nb200_blob_mean_pooling": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "nb200_blob_resize_image": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp]),
 }

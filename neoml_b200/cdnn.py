@@ -86,6 +86,10 @@ def load():
     if hasattr(lib, "cdnn_selftest_free_while_pending"):
         lib.cdnn_selftest_free_while_pending.argtypes = [C.c_void_p, _fp]
         lib.cdnn_selftest_abort_distributed.argtypes = [_ip, C.c_char_p, C.c_int]
+    if hasattr(lib, "cdnn_selftest_padded_pool"):
+        lib.cdnn_selftest_padded_pool.argtypes = [C.c_void_p, _ip, _ip]
+    if hasattr(lib, "cdnn_selftest_attention_chain"):
+        lib.cdnn_selftest_attention_chain.argtypes = [C.c_void_p, _fp, _ip]
     _lib = lib
     return lib
 
@@ -266,6 +270,23 @@ def selftest_free_while_pending(engine: Engine) -> float:
     if load().cdnn_selftest_free_while_pending(engine.ptr, C.byref(worst)) != 0:
         _fail("selftest_free_while_pending")
     return worst.value
+
+
+def selftest_padded_pool(engine: Engine) -> tuple[int, int]:
+    """See cdnn_selftest_padded_pool: (values that differ from the host evaluation, kernels launched by pad + pool)."""
+    wrong, launches = C.c_int(-1), C.c_int(-1)
+    if load().cdnn_selftest_padded_pool(engine.ptr, C.byref(wrong), C.byref(launches)) != 0:
+        _fail("selftest_padded_pool")
+    return wrong.value, launches.value
+
+
+def selftest_attention_chain(engine: Engine) -> tuple[float, int]:
+    """See cdnn_selftest_attention_chain: (largest error relative to the RMS of the expected values, kernels launched by
+    the five calls of the chain)."""
+    worst, launches = C.c_float(-1), C.c_int(-1)
+    if load().cdnn_selftest_attention_chain(engine.ptr, C.byref(worst), C.byref(launches)) != 0:
+        _fail("selftest_attention_chain")
+    return worst.value, launches.value
 
 
 def selftest_abort_distributed(devices=(0, 1)) -> str:

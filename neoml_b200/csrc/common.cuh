@@ -21,10 +21,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Grid size for grid-stride kernels: a whole number of waves over the SMs of the current device.
 int sm_count();
 // Tiled tensor map (CUtensorMap behind the void pointer) over a channels-last image batch, zero fill outside the image
-// (contraction_tc.cu, where the driver's encoder is looked up).  swizzle128: the box lands as 128-byte rows with the
-// 128-byte swizzle (boxC * 4 bytes must then be 128), the layout the tensor core reads; otherwise plain.
+// (contraction_tc.cu, where the driver's encoder is looked up).  swizzle 1: the box lands as 128-byte rows with the
+// 128-byte swizzle of 16-byte units (boxC * 4 bytes must then be 128), the layout the tensor core reads for K-major
+// operands; 2: 128-byte rows whose 32-byte units are permuted (the layout of MN-major tf32 operands); 0: plain.
 bool make_image_box_map(void* map, const float* base, int c, int w, int h, int n, int boxC, int boxW, int boxH,
-	bool swizzle128 = false);
+	int swizzle = 0);
 // Launch `kernel` so that it may overlap the tail of the kernel before it in `stream` (the kernel itself orders its
 // memory accesses with dependent_wait()).  `overlap` false: an ordinary launch.
 template<typename... Params, typename... Args>

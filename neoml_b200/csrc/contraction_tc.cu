@@ -947,10 +947,10 @@ bool make_window_map(CUtensorMap* map, const ContractionParams& p, int images, i
 
 // Channels-last image batch (C, W, H, N) as a plain tiled map without swizzle: a load delivers a box of boxC channels x
 // boxW columns x boxH rows of one image, zeros where the box leaves the image (a convolution's padding for free).
-bool make_image_box_map(void* map, const float* base, int c, int w, int h, int n, int boxC, int boxW, int boxH, bool swizzle128)
+bool make_image_box_map(void* map, const float* base, int c, int w, int h, int n, int boxC, int boxW, int boxH, int swizzle)
 {
 	lookup_encoders();
-	if(swizzle128 && boxC * 4 != 128) return false;
+	if(swizzle != 0 && boxC * 4 != 128) return false;
 	if(g_encodeTiled == nullptr || !aligned16(base) || c % 4 != 0 || boxC % 4 != 0 || boxC > 256 || boxW > 256 || boxH > 256) return false;
 	const cuuint64_t pixel = static_cast<cuuint64_t>(c) * 4;
 	const cuuint64_t dims[4] = { static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h),
@@ -961,7 +961,8 @@ bool make_image_box_map(void* map, const float* base, int c, int w, int h, int n
 	const cuuint32_t elemStrides[4] = { 1, 1, 1, 1 };
 	return g_encodeTiled(static_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims,
 		strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-		swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+		swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
+		CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
 		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

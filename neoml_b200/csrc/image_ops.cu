@@ -455,8 +455,12 @@ __global__ void __launch_bounds__(256, 2) chconv3x3_tma_kernel(const nb200_chcon
 // of the general kernel, so the results are identical.
 constexpr int MP3_TW = 4;
 
+// PADDED: the image the windows slide over is x surrounded by a constant border (`top` rows above, `left` columns to
+// the left, p.h x p.w being the padded extent and inH x inW the extent of x itself); positions in the border read as
+// `border`.  The result is that of padding into a buffer first and pooling that buffer.
+template<bool PADDED>
 __global__ void __launch_bounds__(256) maxpool3x3s2_kernel(const Pool2d p, const float* __restrict__ x, float* __restrict__ y,
-	int strips, unsigned total)
+	int strips, unsigned total, int inH, int inW, int top, int left, float border)
 {
 	const unsigned cv = p.c / 4;
 	for(unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
@@ -466,16 +470,32 @@ __global__ void __launch_bounds__(256) maxpool3x3s2_kernel(const Pool2d p, const
 		const unsigned oy = r % p.ho;
 		const unsigned n = r / p.ho;
 		const int ox0 = sx * MP3_TW;
-		const float4* img = reinterpret_cast<const float4*>(x) + (static_cast<size_t>(n) * p.h + 2 * oy) * p.w * cv + cq;
 		float4* out = reinterpret_cast<float4*>(y) + ((static_cast<size_t>(n) * p.ho + oy) * p.wo + ox0) * cv + cq;
 		const int outs = min(MP3_TW, p.wo - ox0);
 		// all columns of the strip first (2 * outs + 1 of them, three rows each): many independent loads in flight
 		float4 col[2 * MP3_TW + 1][3];
+		if(PADDED) {
+			const float4* img = reinterpret_cast<const float4*>(x) + static_cast<size_t>(n) * inH * inW * cv + cq;
+			const int iy0 = 2 * static_cast<int>(oy) - top, ix0 = 2 * ox0 - left;
 #pragma unroll
-		for(int k = 0; k < 2 * MP3_TW + 1; ++k) {
-			if(k <= 2 * outs) {
+			for(int k = 0; k < 2 * MP3_TW + 1; ++k) {
+				if(k <= 2 * outs) {
 #pragma unroll
-				for(int fy = 0; fy < 3; ++fy) col[k][fy] = __ldg(img + (static_cast<size_t>(fy) * p.w + 2 * ox0 + k) * cv);
+					for(int fy = 0; fy < 3; ++fy) {
+						const int iy = iy0 + fy, ix = ix0 + k;
+						col[k][fy] = iy >= 0 && iy < inH && ix >= 0 && ix < inW
+							? __ldg(img + (static_cast<size_t>(iy) * inW + ix) * cv) : make_float4(border, border, border, border);
+					}
+				}
+			}
+		} else {
+			const float4* img = reinterpret_cast<const float4*>(x) + (static_cast<size_t>(n) * p.h + 2 * oy) * p.w * cv + cq;
+#pragma unroll
+			for(int k = 0; k < 2 * MP3_TW + 1; ++k) {
+				if(k <= 2 * outs) {
+#pragma unroll
+					for(int fy = 0; fy < 3; ++fy) col[k][fy] = __ldg(img + (static_cast<size_t>(fy) * p.w + 2 * ox0 + k) * cv);
+				}
 			}
 		}
 #pragma unroll
@@ -513,7 +533,7 @@ int pool_common(void* stream, bool isMax, int batch, int h, int w, int c, int fh
 		&& static_cast<long long>(batch) * h * w * c < 0x7fffffffLL) {
 		const int strips = (p.wo + MP3_TW - 1) / MP3_TW;
 		const long long total = static_cast<long long>(batch) * p.ho * strips * (c / 4);
-		maxpool3x3s2_kernel<<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, strips, static_cast<unsigned>(total));
+		maxpool3x3s2_kernel<false><<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, strips, static_cast<unsigned>(total), h, w, 0, 0, 0.f);
 	} else if(vec) {
 		const long long total = outElems / 4;
 		if(isMax) pool_kernel<true, 4><<<grid_for(total, 256, 16), 256, 0, s>>>(p, x, y, maxIndices, total);
@@ -618,6 +638,27 @@ int nb200_blob_max_pooling(void* stream, int batch, int h, int w, int c, int fil
 	int stride_w, const float* x, float* y, int* max_indices)
 {
 	return pool_common(stream, true, batch, h, w, c, filter_h, filter_w, stride_h, stride_w, x, y, max_indices);
+}
+
+int nb200_blob_max_pooling_padded(void* stream, int batch, int h, int w, int c, int pad_left, int pad_right, int pad_top,
+	int pad_bottom, float pad_value, int filter_h, int filter_w, int stride_h, int stride_w, const float* x, float* y)
+{
+	if(batch < 0 || h <= 0 || w <= 0 || c <= 0 || pad_left < 0 || pad_right < 0 || pad_top < 0 || pad_bottom < 0) return NB200_EINVAL;
+	const int ph = h + pad_top + pad_bottom, pw = w + pad_left + pad_right;
+	// the one form that exists: 3x3 windows, stride 2, whole float4 channel groups (the stem pool of the ResNets)
+	if(filter_h != 3 || filter_w != 3 || stride_h != 2 || stride_w != 2 || c % 4 != 0 || ph < 3 || pw < 3) return NB200_EINVAL;
+	Pool2d p = { batch, ph, pw, c, 3, 3, 2, 2, (ph - 3) / 2 + 1, (pw - 3) / 2 + 1 };
+	const long long outElems = static_cast<long long>(batch) * p.ho * p.wo * c;
+	if(outElems == 0) return NB200_OK;
+	if(x == nullptr || y == nullptr || !aligned16(x) || !aligned16(y)) return NB200_EINVAL;
+	if(outElems / 4 >= 0x7fffffffLL || static_cast<long long>(batch) * h * w * c >= 0x7fffffffLL) return NB200_EINVAL;
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	const int strips = (p.wo + MP3_TW - 1) / MP3_TW;
+	const long long total = static_cast<long long>(batch) * p.ho * strips * (c / 4);
+	maxpool3x3s2_kernel<true><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p, x, y, strips,
+		static_cast<unsigned>(total), h, w, pad_top, pad_left, pad_value);
+	count_launch();
+	return check_launch();
 }
 
 int nb200_blob_mean_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w, int stride_h,

@@ -533,7 +533,7 @@ bool launch_mbv2_fused(void* stream, const nb200_mbv2_desc* d, const float* x, c
 	p.status = device_status_word();
 	if(p.status == nullptr) { *rc = NB200_ENODEVICE; return true; }
 	CUtensorMap map;
-	if(!make_image_box_map(&map, x, CIN, d->w, d->h, d->batch, CIN, HW, HH, true)) return false;
+	if(!make_image_box_map(&map, x, CIN, d->w, d->h, d->batch, CIN, HW, HH, 1)) return false;
 	const int grid = p.numTiles < sm_count() ? p.numTiles : sm_count();
 	cudaError_t e;
 	if(precision == NB200_PREC_3XTF32) {

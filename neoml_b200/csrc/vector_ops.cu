@@ -32,6 +32,7 @@ __device__ __forceinline__ float vec_apply(float a, float b, float s)
 		case NB200_VEC_ELTWISE_MAX: return fmaxf(a, b);
 		case NB200_VEC_ELTWISE_DIV: return a / b;
 		case NB200_VEC_MUL_ADD: return a + b * s;
+		case NB200_VEC_SIGMOID_MUL: return __fmul_rn(1.f / (1.f + expf(-__fmul_rn(a, s))), a);
 	}
 	return 0.f;
 }
@@ -117,7 +118,7 @@ int nb200_vector_op(void* stream, int op, const float* a, const float* b, const 
 	cudaStream_t s = as_stream(stream);
 	// ops whose scalar NeoML keeps in device memory take it from `scalar`; with scalar == NULL they use `value`
 	const bool takesScalar = op == NB200_VEC_FILL_HANDLE || op == NB200_VEC_MULTIPLY || op == NB200_VEC_NEG_MULTIPLY
-		|| op == NB200_VEC_ADD_VALUE || op == NB200_VEC_RELU || op == NB200_VEC_MUL_ADD;
+		|| op == NB200_VEC_ADD_VALUE || op == NB200_VEC_RELU || op == NB200_VEC_MUL_ADD || op == NB200_VEC_SIGMOID_MUL;
 	if(op == NB200_VEC_FILL_HANDLE && scalar == nullptr) return NB200_EINVAL;
 	if(!takesScalar) scalar = nullptr;
 	switch(op) {
@@ -141,6 +142,7 @@ int nb200_vector_op(void* stream, int op, const float* a, const float* b, const 
 		NB200_CASE(NB200_VEC_ELTWISE_MAX)
 		NB200_CASE(NB200_VEC_ELTWISE_DIV)
 		NB200_CASE(NB200_VEC_MUL_ADD)
+		NB200_CASE(NB200_VEC_SIGMOID_MUL)
 #undef NB200_CASE
 	}
 	return NB200_EINVAL;

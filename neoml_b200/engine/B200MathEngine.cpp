@@ -111,6 +111,7 @@ CB200MathEngine::~CB200MathEngine()
 		ReleaseDistributedCommunicator(); // first: after an abort only this lets the stream drain
 		cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
 		forgetAllPreparedFilters();
+		lazy.clear(); // nobody is left to read a noted result
 		for( void* p : deferredFrees ) memory.Free( p );
 		if( copyStream != nullptr ) cudaStreamDestroy( static_cast<cudaStream_t>( copyStream ) );
 		if( copyDone != nullptr ) cudaEventDestroy( static_cast<cudaEvent_t>( copyDone ) );
@@ -129,14 +130,144 @@ bool CB200MathEngine::pendingRefersTo( const void* begin, size_t bytes ) const
 		|| inside( pending.result ) || inside( pending.residual ) || inside( pending.threshold ) ) ) {
 		return true;
 	}
-	return pendingRows.active && ( inside( pendingRows.data ) || inside( pendingRows.scale ) || inside( pendingRows.bias ) );
+	if( pendingRows.active && ( inside( pendingRows.data ) || inside( pendingRows.scale ) || inside( pendingRows.bias ) ) ) return true;
+	if( pendingProduct.active && ( inside( pendingProduct.first ) || inside( pendingProduct.second ) || inside( pendingProduct.result ) ) ) {
+		return true;
+	}
+	return pendingGate.active && ( inside( pendingGate.input ) || inside( pendingGate.output ) || inside( pendingGate.scale ) );
 }
 
 void CB200MathEngine::releaseDeferredFrees() const
 {
-	if( pending.active || pendingRows.active ) return;
-	for( void* p : deferredFrees ) freeBlock( p );
-	deferredFrees.clear();
+	if( deferredFrees.empty() ) return;
+	std::vector<void*> kept;
+	for( void* p : deferredFrees ) {
+		if( pendingRefersTo( p, memory.BlockBytes( p ) ) || lazyReads( p ) ) kept.push_back( p );
+		else freeBlock( p );
+	}
+	deferredFrees.swap( kept );
+}
+
+//---------------------------------------------------------------------------------------------------------------------
+// noted results (see CLazyResult)
+
+bool CB200MathEngine::noteLazy( const CLazyResult& note ) const
+{
+	if( note.resultBase == nullptr || memory.BlockBytes( note.resultBase ) == 0 ) return false;
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	lazy.push_back( note );
+	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
+	return true;
+}
+
+int CB200MathEngine::findLazy( const void* result, CLazyResult::TKind kind ) const
+{
+	for( size_t i = 0; i < lazy.size(); ++i ) {
+		if( lazy[i].result == result && lazy[i].kind == kind ) return static_cast<int>( i );
+	}
+	return -1;
+}
+
+bool CB200MathEngine::lazyReads( const void* allocationBase ) const
+{
+	for( const CLazyResult& note : lazy ) {
+		for( const void* base : note.inputBases ) {
+			if( base == allocationBase ) return true;
+		}
+	}
+	return false;
+}
+
+void CB200MathEngine::materializeLazy( size_t index ) const
+{
+	CB200MathEngine* self = const_cast<CB200MathEngine*>( this );
+	const CLazyResult note = lazy[index];
+	lazy.erase( lazy.begin() + index );
+	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
+	cudaSetDevice( device );
+	// the kernels launched now read and write these allocations, whenever the calls were noted
+	noteUse( note.resultBase );
+	for( const void* base : note.inputBases ) noteUse( base );
+	if( note.kind == CLazyResult::K_Resize ) {
+		check( nb200_blob_resize_image( stream, note.batch, note.h, note.w, note.c, note.left, note.right, note.top, note.bottom,
+			0, note.value, note.from, note.result ), "BlobResizeImage" );
+	} else {
+		check( self->launchProduct( note.batch, note.first, note.seqQ, note.depth, note.second, note.seqTo, note.result ),
+			"MultiplyMatrixByMatrix" );
+		const int rows = note.batch * note.seqQ;
+		if( note.softmax && note.seqTo <= 1024 && ( note.scale != nullptr || note.mask != nullptr ) ) {
+			check( nb200_matrix_softmax_by_rows_fused( stream, note.result, rows, note.seqTo, note.scale, note.mask,
+				note.mask != nullptr ? note.seqQ : 0, note.result ), "MatrixSoftmaxByRows" );
+		} else {
+			if( note.scale != nullptr ) {
+				check( nb200_vector_op( stream, NB200_VEC_MULTIPLY, note.result, nullptr, note.scale, 0.f, note.result,
+					static_cast<int>( note.resultFloats ) ), "VectorMultiply" );
+			}
+			if( note.mask != nullptr ) {
+				check( nb200_add_vector_to_matrix_rows( stream, 1, note.result, note.result, note.batch, note.seqQ * note.seqTo,
+					note.mask ), "AddVectorToMatrixRows" );
+			}
+			if( note.softmax ) {
+				check( nb200_matrix_softmax_by_rows( stream, note.result, rows, note.seqTo, note.result ), "MatrixSoftmaxByRows" );
+			}
+		}
+	}
+	releaseDeferredFrees();
+}
+
+void CB200MathEngine::materializeAllLazy() const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	while( !lazy.empty() ) materializeLazy( 0 );
+}
+
+void CB200MathEngine::touchLazy( const void* allocationBase, bool mayWrite ) const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	for( ;; ) {
+		int hit = -1;
+		for( size_t i = 0; i < lazy.size() && hit < 0; ++i ) {
+			if( lazy[i].resultBase == allocationBase ) hit = static_cast<int>( i );
+			for( size_t k = 0; mayWrite && hit < 0 && k < lazy[i].inputBases.size(); ++k ) {
+				if( lazy[i].inputBases[k] == allocationBase ) hit = static_cast<int>( i );
+			}
+		}
+		if( hit < 0 ) return;
+		materializeLazy( static_cast<size_t>( hit ) );
+	}
+}
+
+CB200MathEngine::CLazyResult* CB200MathEngine::deriveScores( int sourceNote, const CFloatHandle& resultHandle ) const
+{
+	const float* const source = lazy[sourceNote].result;
+	if( peek( resultHandle ) == source ) return &lazy[sourceNote];
+	CLazyResult copy = lazy[sourceNote];
+	const void* base = CMemoryHandleInternal::Base( resultHandle );
+	if( base == copy.resultBase || memory.BlockBytes( base ) == 0 ) return nullptr;
+	for( const void* input : copy.inputBases ) {
+		if( input == base ) return nullptr;
+	}
+	copy.result = raw( resultHandle ); // whatever was noted for that buffer, or reads it, is carried out first
+	copy.resultBase = base;
+	if( findLazy( source, CLazyResult::K_Scores ) < 0 ) return nullptr; // that included the source
+	lazy.push_back( copy );
+	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
+	return &lazy.back();
+}
+
+bool CB200MathEngine::forgetLazyResultIn( const void* allocationBase ) const
+{
+	bool any = false;
+	for( size_t i = 0; i < lazy.size(); ) {
+		if( lazy[i].resultBase == allocationBase ) {
+			lazy.erase( lazy.begin() + i );
+			any = true;
+		} else {
+			++i;
+		}
+	}
+	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
+	return any;
 }
 
 void CB200MathEngine::notImplemented( const char* method ) const
@@ -168,7 +299,9 @@ void CB200MathEngine::enter() const
 		++opSeq;
 	}
 	flushPending();
+	flushProduct();
 	flushRowOps();
+	flushGate();
 }
 
 float* CB200MathEngine::WorkAlloc( size_t floats ) const
@@ -197,6 +330,30 @@ void CB200MathEngine::flushRowOps() const
 	if( p.bias != nullptr ) {
 		check( nb200_add_vector_to_matrix_rows( stream, 1, p.data, p.data, p.biasHeight, p.biasWidth, p.bias ),
 			"AddVectorToMatrixRows" );
+	}
+	releaseDeferredFrees();
+}
+
+void CB200MathEngine::flushProduct( const float* bias ) const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( !pendingProduct.active ) return;
+	const CPendingProduct p = pendingProduct;
+	pendingProduct = CPendingProduct();
+	check( productWithScratch( 1, p.first, p.firstHeight, p.firstWidth, p.firstRowSize, p.second, p.secondHeight,
+		p.secondRowSize, p.result, p.resultRowSize, bias ), "MultiplyMatrixByTransposedMatrix" );
+	releaseDeferredFrees();
+}
+
+void CB200MathEngine::flushGate() const
+{
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	if( !pendingGate.active ) return;
+	const CPendingSigmoidGate g = pendingGate;
+	pendingGate = CPendingSigmoidGate();
+	check( nb200_vector_op( stream, NB200_VEC_MULTIPLY, g.input, nullptr, g.scale, 0.f, g.output, g.size ), "VectorMultiply" );
+	if( g.sigmoid ) {
+		check( nb200_vector_op( stream, NB200_VEC_SIGMOID, g.output, nullptr, nullptr, 0.f, g.output, g.size ), "VectorSigmoid" );
 	}
 	releaseDeferredFrees();
 }
@@ -364,10 +521,13 @@ void CB200MathEngine::HeapFree( const CMemoryHandle& handle )
 	if( !preparedFilters.empty() ) forgetPreparedFilter( block );
 	{
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
-		if( ( pending.active || pendingRows.active ) && pendingRefersTo( block, memory.BlockBytes( block ) ) ) {
+		const bool forgot = !lazy.empty() && forgetLazyResultIn( block ); // nobody can read the noted result any more
+		if( ( anythingRecorded() && pendingRefersTo( block, memory.BlockBytes( block ) ) )
+			|| ( !lazy.empty() && lazyReads( block ) ) ) {
 			deferredFrees.push_back( block ); // returned to the pool once the recorded call has been launched
 			return;
 		}
+		if( forgot ) releaseDeferredFrees();
 	}
 	freeBlock( block );
 }
@@ -392,7 +552,8 @@ void CB200MathEngine::StackFree( const CMemoryHandle& handle )
 		// a recorded call may read a stack variable (NeoML keeps scalars such as a multiplier there): launch it before
 		// the variable's memory can be handed out again; the stack is LIFO, so the free itself cannot be postponed
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
-		if( pending.active || pendingRows.active ) enter();
+		if( anythingRecorded() ) enter();
+		if( !lazy.empty() ) touchLazy( CMemoryHandleInternal::Base( handle ), true );
 	}
 	if( !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( handle ) );
 	memory.StackFree( CMemoryHandleInternal::GetRaw( handle ) );
@@ -407,6 +568,7 @@ size_t CB200MathEngine::GetMemoryInPools() const { return memory.InPools(); }
 void CB200MathEngine::CleanUp()
 {
 	enter();
+	materializeAllLazy();
 	if( stream != nullptr ) cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) );
 	forgetAllPreparedFilters();
 	memory.CleanUp();
@@ -424,6 +586,7 @@ void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* 
 	enter();
 	const void* base = CMemoryHandleInternal::Base( result );
 	if( !preparedFilters.empty() ) forgetPreparedFilter( base );
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( base, true );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	void* const destination = CMemoryHandleInternal::GetRaw( result );
 	// A large exchange into a heap block that nothing queued can touch overlaps the kernels in flight (see noteUse)
@@ -452,6 +615,7 @@ void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source
 	if( size == 0 ) return;
 	if( source.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
 	enter();
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( CMemoryHandleInternal::Base( source ), false );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( cudaMemcpyAsync( result, CMemoryHandleInternal::GetRaw( source ), size, cudaMemcpyDeviceToHost, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
@@ -548,6 +712,7 @@ CMemoryHandle CB200MathEngine::CopyFrom( const CMemoryHandle& handle, size_t siz
 	IMathEngine* other = handle.GetMathEngine();
 	if( other == this ) {
 		enter();
+		if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( CMemoryHandleInternal::Base( handle ), false );
 		noteUse( CMemoryHandleInternal::Base( result ) );
 		noteUse( CMemoryHandleInternal::Base( handle ) );
 		cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), CMemoryHandleInternal::GetRaw( handle ), size,

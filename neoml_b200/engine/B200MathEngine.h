@@ -15,6 +15,7 @@
 
 #include "neoml_b200.h"
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <map>
@@ -129,6 +130,15 @@ private:
 		if( !h.IsNull() && h.GetMathEngine() != this ) notImplemented( "use of a handle that belongs to another math engine" );
 		if( !std::is_const<T>::value && !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( h ) );
 		if( !h.IsNull() ) noteUse( CMemoryHandleInternal::Base( h ) );
+		if( lazyCount.load( std::memory_order_relaxed ) != 0 && !h.IsNull() ) {
+			touchLazy( CMemoryHandleInternal::Base( h ), !std::is_const<T>::value );
+		}
+		return CMemoryHandleInternal::GetRaw( h );
+	}
+	// the pointer alone: for a method that first looks whether its operand is a result noted below
+	template<class T> T* peek( const CTypedMemoryHandle<T>& h ) const
+	{
+		if( !h.IsNull() && h.GetMathEngine() != this ) notImplemented( "use of a handle that belongs to another math engine" );
 		return CMemoryHandleInternal::GetRaw( h );
 	}
 	void vectorOp( int op, const float* a, const float* b, const float* scalar, float value, float* y, int n,
@@ -166,8 +176,76 @@ private:
 	};
 	mutable CPendingRowOps pendingRows;
 	void flushRowOps() const;
+	// The fully connected layer's pair: MultiplyMatrixByTransposedMatrix is recorded, an in-place AddVectorToMatrixRows
+	// of its whole result that follows becomes the bias of the product's epilogue (one pass less over the result).
+	struct CPendingProduct {
+		bool active = false;
+		const float* first = nullptr;
+		int firstHeight = 0, firstWidth = 0, firstRowSize = 0;
+		const float* second = nullptr;
+		int secondHeight = 0, secondRowSize = 0;
+		float* result = nullptr;
+		int resultRowSize = 0;
+	};
+	mutable CPendingProduct pendingProduct;
+	void flushProduct( const float* bias = nullptr ) const;
+	// CGELULayer's fast form: VectorMultiply( x -> y, *scale ), VectorSigmoid( y -> y ), VectorEltwiseMultiply( x, y -> y )
+	// are recorded one after the other and, when all three came, run as one pass with the same roundings.
+	struct CPendingSigmoidGate {
+		bool active = false, sigmoid = false;
+		const float* input = nullptr;
+		float* output = nullptr;
+		int size = 0;
+		const float* scale = nullptr;
+	};
+	mutable CPendingSigmoidGate pendingGate;
+	void flushGate() const;
+	bool anythingRecorded() const { return pending.active || pendingRows.active || pendingProduct.active || pendingGate.active; }
+	// Results that are noted, not computed.  BlobResizeImage with constant padding, and the score chain of attention
+	// (a batched MultiplyMatrixByMatrix, then in place VectorMultiply / AddVectorToMatrixRows / MatrixSoftmaxByRows)
+	// only note what they would write.  The consumer that usually follows -- BlobMaxPooling over the padded image,
+	// MultiplyMatrixByMatrix of the probabilities by the values -- then runs as ONE kernel over the inputs of the
+	// noted calls, and the noted result is never written.  Nobody can observe that: a handle into the result's
+	// allocation that reaches raw() has the noted calls launched first, so has a handle that may be written through
+	// into an allocation the noted calls read; freeing such an allocation is postponed; freeing the result's own
+	// allocation forgets the note.  Only results in heap blocks of this engine are noted (their end of life is seen).
+	struct CLazyResult {
+		enum TKind { K_Resize, K_Scores };
+		TKind kind = K_Resize;
+		const void* resultBase = nullptr;         // allocation the result lies in
+		float* result = nullptr;
+		long long resultFloats = 0;
+		std::vector<const void*> inputBases;      // allocations the noted calls read
+		// K_Resize: result = from (batch x h x w x c) with a border of `value`
+		int batch = 0, h = 0, w = 0, c = 0, left = 0, right = 0, top = 0, bottom = 0;
+		float value = 0.f;
+		const float* from = nullptr;
+		// K_Scores: result[b] = first[b] (seqQ x depth) * second[b] (depth x seqTo), b < batch; then, as noted,
+		// * *scale, + mask (maskWidth = seqQ * seqTo values, the same for every b), softmax over each row
+		int seqQ = 0, depth = 0, seqTo = 0;
+		const float* first = nullptr;
+		const float* second = nullptr;
+		const float* scale = nullptr;
+		const float* mask = nullptr;
+		bool softmax = false;
+	};
+	mutable std::vector<CLazyResult> lazy;   // under pendingMutex
+	mutable std::atomic<int> lazyCount{ 0 };
+	bool noteLazy( const CLazyResult& note ) const;              // false: the result is not in a heap block of this engine
+	int findLazy( const void* result, CLazyResult::TKind kind ) const;
+	void materializeLazy( size_t index ) const;                  // launches the noted calls, forgets the note
+	void materializeAllLazy() const;
+	void touchLazy( const void* allocationBase, bool mayWrite ) const;
+	bool lazyReads( const void* allocationBase ) const;
+	bool forgetLazyResultIn( const void* allocationBase ) const; // true if a note was forgotten
+	// `result = op( source )` over a noted score matrix: the note that describes `result` -- the source's own when the
+	// call is in place, a copy bound to the new buffer otherwise; nullptr when `result` cannot carry a note
+	CLazyResult* deriveScores( int sourceNote, const CFloatHandle& resultHandle ) const;
+	int launchProduct( int batchSize, const float* first, int firstHeight, int firstWidth, const float* second,
+		int secondWidth, float* result ) const;
 	int productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
-		const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize );
+		const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize,
+		const float* bias = nullptr ) const;
 	mutable std::recursive_mutex pendingMutex;
 	// NeoML frees a layer's input blobs right after its RunOnce (reuse-memory mode), i.e. possibly while a recorded
 	// call still refers to them.  Such a heap block goes back to the pool only after the recorded call has been

@@ -125,6 +125,21 @@ void CB200MathEngine::BlobMaxPooling( const CMaxPoolingDesc& poolDesc, const CCo
 {
 	const CB200PoolingGeometry& g = static_cast<const CB200MaxPoolingDesc&>( poolDesc ).g;
 	enter();
+	if( maxIndices == nullptr && lazyCount.load( std::memory_order_relaxed ) != 0 ) {
+		// pooling over an image whose padding was only noted (BlobResizeImage): one pass over the unpadded image
+		float* const out = raw( result ); // first: a result that overlaps what the note reads has the note carried out
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( source ), CLazyResult::K_Resize );
+		if( at >= 0 ) {
+			const CLazyResult& note = lazy[at];
+			if( note.batch == g.batch && note.h + note.top + note.bottom == g.h && note.w + note.left + note.right == g.w
+				&& note.c == g.c && nb200_blob_max_pooling_padded( stream, note.batch, note.h, note.w, note.c, note.left, note.right,
+					note.top, note.bottom, note.value, g.fh, g.fw, g.sh, g.sw, note.from, out ) == NB200_OK ) {
+				for( const void* base : note.inputBases ) noteUse( base );
+				return;
+			}
+		}
+	}
 	check( nb200_blob_max_pooling( stream, g.batch, g.h, g.w, g.c, g.fh, g.fw, g.sh, g.sw, raw( source ), raw( result ),
 		maxIndices != nullptr ? raw( *maxIndices ) : nullptr ), "BlobMaxPooling" );
 }
@@ -150,7 +165,25 @@ void CB200MathEngine::BlobResizeImage( const CBlobDesc& from, const CFloatHandle
 	int deltaTop, int deltaBottom, TBlobResizePadding padding, float defaultValue, const CBlobDesc&, const CFloatHandle& toData )
 {
 	enter();
-	check( nb200_blob_resize_image( stream, from.ObjectCount(), from.Height(), from.Width(), from.Depth() * from.Channels(),
+	const int channels = from.Depth() * from.Channels();
+	if( static_cast<int>( padding ) == 0 && deltaLeft >= 0 && deltaRight >= 0 && deltaTop >= 0 && deltaBottom >= 0
+		&& CMemoryHandleInternal::Base( fromData ) != CMemoryHandleInternal::Base( toData ) ) {
+		// a constant border: noted, not written -- the pooling that usually follows reads the unpadded image instead
+		// (see CLazyResult); anything else that touches the padded image finds it written
+		CLazyResult note;
+		note.kind = CLazyResult::K_Resize;
+		note.result = raw( toData );
+		note.resultBase = CMemoryHandleInternal::Base( toData );
+		note.batch = from.ObjectCount(); note.h = from.Height(); note.w = from.Width(); note.c = channels;
+		note.left = deltaLeft; note.right = deltaRight; note.top = deltaTop; note.bottom = deltaBottom;
+		note.value = defaultValue;
+		note.resultFloats = static_cast<long long>( note.batch ) * ( note.h + deltaTop + deltaBottom )
+			* ( note.w + deltaLeft + deltaRight ) * channels;
+		note.from = raw( CConstFloatHandle( fromData ) );
+		note.inputBases.push_back( CMemoryHandleInternal::Base( fromData ) );
+		if( noteLazy( note ) ) return;
+	}
+	check( nb200_blob_resize_image( stream, from.ObjectCount(), from.Height(), from.Width(), channels,
 		deltaLeft, deltaRight, deltaTop, deltaBottom, static_cast<int>( padding ), defaultValue, raw( fromData ), raw( toData ) ),
 		"BlobResizeImage" );
 }

@@ -107,6 +107,18 @@ void CB200MathEngine::VectorMultiplyAndAdd( const CConstFloatHandle& firstHandle
 void CB200MathEngine::VectorMultiply( const CConstFloatHandle& firstHandle, const CFloatHandle& resultHandle, int vectorSize,
 	const CConstFloatHandle& multiplierHandle )
 {
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( firstHandle ) == peek( resultHandle ) ) {
+		// in place on a noted score matrix (see CLazyResult): the factor joins the note
+		const float* const factor = raw( multiplierHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( firstHandle ), CLazyResult::K_Scores );
+		if( at >= 0 && lazy[at].resultFloats == vectorSize && lazy[at].scale == nullptr && lazy[at].mask == nullptr
+			&& !lazy[at].softmax ) {
+			lazy[at].scale = factor;
+			lazy[at].inputBases.push_back( CMemoryHandleInternal::Base( multiplierHandle ) );
+			return;
+		}
+	}
 	if( raw( firstHandle ) == raw( resultHandle ) && vectorSize > 0 ) {
 		// in place: held back, a softmax over the same buffer may absorb it (see CPendingRowOps)
 		enter();
@@ -116,6 +128,19 @@ void CB200MathEngine::VectorMultiply( const CConstFloatHandle& firstHandle, cons
 		pendingRows.size = vectorSize;
 		pendingRows.scale = raw( multiplierHandle );
 		pendingRows.active = true;
+		return;
+	}
+	const std::ptrdiff_t apart = peek( resultHandle ) - peek( firstHandle );
+	if( vectorSize > 0 && ( apart >= vectorSize || -apart >= vectorSize ) ) {
+		// into another buffer: held back, CGELULayer's sigmoid and gate may follow (see CPendingSigmoidGate)
+		enter();
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		pendingGate = CPendingSigmoidGate();
+		pendingGate.input = raw( firstHandle );
+		pendingGate.output = raw( resultHandle );
+		pendingGate.size = vectorSize;
+		pendingGate.scale = raw( multiplierHandle );
+		pendingGate.active = true;
 		return;
 	}
 	vectorOp( NB200_VEC_MULTIPLY, raw( firstHandle ), nullptr, raw( multiplierHandle ), 0.f, raw( resultHandle ), vectorSize, "VectorMultiply" );
@@ -130,6 +155,19 @@ void CB200MathEngine::VectorNegMultiply( const CConstFloatHandle& firstHandle, c
 void CB200MathEngine::VectorEltwiseMultiply( const CConstFloatHandle& firstHandle, const CConstFloatHandle& secondHandle,
 	const CFloatHandle& resultHandle, int vectorSize )
 {
+	{
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const CPendingSigmoidGate g = pendingGate;
+		if( g.active && g.sigmoid && raw( resultHandle ) == g.output && vectorSize == g.size
+			&& ( ( raw( firstHandle ) == g.input && raw( secondHandle ) == g.output )
+				|| ( raw( firstHandle ) == g.output && raw( secondHandle ) == g.input ) ) ) {
+			pendingGate = CPendingSigmoidGate();
+			enter();
+			check( nb200_vector_op( stream, NB200_VEC_SIGMOID_MUL, g.input, nullptr, g.scale, 0.f, g.output, g.size ),
+				"VectorEltwiseMultiply" );
+			return;
+		}
+	}
 	vectorOp( NB200_VEC_ELTWISE_MUL, raw( firstHandle ), raw( secondHandle ), nullptr, 0.f, raw( resultHandle ), vectorSize, "VectorEltwiseMultiply" );
 }
 
@@ -151,6 +189,14 @@ void CB200MathEngine::VectorInv( const CConstFloatHandle& firstHandle, const CFl
 
 void CB200MathEngine::VectorSigmoid( const CConstFloatHandle& firstHandle, const CFloatHandle& resultHandle, int vectorSize )
 {
+	{
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		if( pendingGate.active && !pendingGate.sigmoid && raw( firstHandle ) == pendingGate.output
+			&& raw( resultHandle ) == pendingGate.output && vectorSize == pendingGate.size ) {
+			pendingGate.sigmoid = true;
+			return;
+		}
+	}
 	vectorOp( NB200_VEC_SIGMOID, raw( firstHandle ), nullptr, nullptr, 0.f, raw( resultHandle ), vectorSize, "VectorSigmoid" );
 }
 
@@ -166,8 +212,29 @@ void CB200MathEngine::AddVectorToMatrixRows( int batchSize, const CConstFloatHan
 	int matrixHeight, int matrixWidth, const CConstFloatHandle& vectorHandle )
 {
 	const long long size = static_cast<long long>( matrixHeight ) * matrixWidth;
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && batchSize == 1 ) {
+		// the mask of attention added to a noted score matrix (see CLazyResult), in place or into another buffer
+		const float* const mask = raw( vectorHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( matrixHandle ), CLazyResult::K_Scores );
+		if( at >= 0 && lazy[at].resultFloats == size && matrixHeight == lazy[at].batch
+			&& matrixWidth == lazy[at].seqQ * lazy[at].seqTo && lazy[at].mask == nullptr && !lazy[at].softmax ) {
+			CLazyResult* note = deriveScores( at, resultHandle );
+			if( note != nullptr ) {
+				note->mask = mask;
+				note->inputBases.push_back( CMemoryHandleInternal::Base( vectorHandle ) );
+				return;
+			}
+		}
+	}
 	if( batchSize == 1 && raw( matrixHandle ) == raw( resultHandle ) && size > 0 ) {
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		if( pendingProduct.active && pendingProduct.result == raw( resultHandle ) && pendingProduct.firstHeight == matrixHeight
+			&& pendingProduct.secondHeight == matrixWidth && pendingProduct.resultRowSize == matrixWidth ) {
+			cudaSetDevice( device );
+			flushProduct( raw( vectorHandle ) ); // the product with the vector as its bias
+			return;
+		}
 		if( pendingRows.active && pendingRows.data == raw( resultHandle ) && pendingRows.size == size && pendingRows.bias == nullptr ) {
 			// joins a held-back VectorMultiply of the same buffer
 		} else {
@@ -218,6 +285,19 @@ void CB200MathEngine::SumMatrixColumns( const CFloatHandle& resultHandle, const 
 
 void CB200MathEngine::MatrixSoftmaxByRows( const CConstFloatHandle& matrix, int height, int width, const CFloatHandle& result )
 {
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) {
+		// over a noted score matrix (see CLazyResult): noted as well
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( matrix ), CLazyResult::K_Scores );
+		if( at >= 0 && !lazy[at].softmax && width == lazy[at].seqTo
+			&& static_cast<long long>( height ) == static_cast<long long>( lazy[at].batch ) * lazy[at].seqQ ) {
+			CLazyResult* note = deriveScores( at, result );
+			if( note != nullptr ) {
+				note->softmax = true;
+				return;
+			}
+		}
+	}
 	{
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 		const CPendingRowOps p = pendingRows;
@@ -275,25 +355,37 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 	int resultRowSize, int )
 {
 	enter();
-	check( productWithScratch( 1, raw( firstHandle ), firstHeight, firstWidth, firstRowSize, raw( secondHandle ), secondHeight,
-		secondRowSize, raw( resultHandle ), resultRowSize ), "MultiplyMatrixByTransposedMatrix" );
+	// recorded: the bias that a fully connected layer adds next rides in the epilogue (see CPendingProduct); any other
+	// call launches the product first
+	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	pendingProduct.first = raw( firstHandle );
+	pendingProduct.firstHeight = firstHeight; pendingProduct.firstWidth = firstWidth; pendingProduct.firstRowSize = firstRowSize;
+	pendingProduct.second = raw( secondHandle );
+	pendingProduct.secondHeight = secondHeight; pendingProduct.secondRowSize = secondRowSize;
+	pendingProduct.result = raw( resultHandle );
+	pendingProduct.resultRowSize = resultRowSize;
+	pendingProduct.active = true;
 }
 
 // first * second^T with work space from the stack allocator: a prepared second operand for tall products, room for
 // split-K partial results for products with few output tiles
 int CB200MathEngine::productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
-	const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize )
+	const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize, const float* bias ) const
 {
+	CB200MathEngine* self = const_cast<CB200MathEngine*>( this );
+	nb200_epilogue withBias = {};
+	withBias.bias = bias;
+	const nb200_epilogue* const epi = bias != nullptr ? &withBias : nullptr;
 	const size_t floats = nb200_matrix_product_scratch_floats( batchSize, firstHeight, secondHeight, firstWidth, secondRowSize );
 	if( floats == 0 ) {
 		return nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
-			firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize, nullptr, nullptr, precision );
+			firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize, nullptr, epi, precision );
 	}
-	CMemoryHandle scratch = StackAlloc( floats * sizeof( float ) );
+	CMemoryHandle scratch = self->StackAlloc( floats * sizeof( float ) );
 	const int rc = nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
 		firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize,
-		static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) ), nullptr, precision );
-	StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
+		static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) ), epi, precision );
+	self->StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
 	return rc;
 }
 
@@ -309,24 +401,68 @@ void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHa
 	const CConstFloatHandle& secondHandle, int secondWidth, const CFloatHandle& resultHandle, int )
 {
 	enter();
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) {
+		// probabilities * values, the probabilities being a noted score matrix (see CLazyResult): the whole chain as one
+		// kernel over the queries, keys and values; the score matrix stays unwritten
+		const float* const values = raw( secondHandle );
+		float* const out = raw( resultHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( firstHandle ), CLazyResult::K_Scores );
+		if( at >= 0 && lazy[at].softmax && lazy[at].batch == batchSize && lazy[at].seqQ == firstHeight
+			&& lazy[at].seqTo == firstWidth && lazy[at].depth == secondWidth ) {
+			const CLazyResult& note = lazy[at];
+			if( nb200_attention_scores_values( stream, batchSize, note.first, note.second, values, note.seqQ, note.depth,
+					note.seqTo, note.scale, note.mask, out, precision ) == NB200_OK ) {
+				for( const void* base : note.inputBases ) noteUse( base );
+				return;
+			}
+		}
+	}
+	const long long scores = static_cast<long long>( batchSize ) * firstHeight * secondWidth;
+	if( precision == NB200_PREC_3XTF32 && batchSize > 0 && firstWidth == 64 && firstHeight >= 128 && secondWidth >= 128
+		&& secondWidth % 4 == 0 && scores < ( 1ll << 31 )
+		&& CMemoryHandleInternal::Base( resultHandle ) != CMemoryHandleInternal::Base( firstHandle )
+		&& CMemoryHandleInternal::Base( resultHandle ) != CMemoryHandleInternal::Base( secondHandle ) ) {
+		// the shape of queries * keys in attention: noted, not launched -- scale, mask, softmax and the product with the
+		// values may follow and then run as one kernel (see CLazyResult); anything else that touches the result finds
+		// it written
+		CLazyResult note;
+		note.kind = CLazyResult::K_Scores;
+		note.first = raw( firstHandle );
+		note.second = raw( secondHandle );
+		note.result = raw( resultHandle );
+		note.resultBase = CMemoryHandleInternal::Base( resultHandle );
+		note.resultFloats = scores;
+		note.batch = batchSize; note.seqQ = firstHeight; note.depth = firstWidth; note.seqTo = secondWidth;
+		note.inputBases.push_back( CMemoryHandleInternal::Base( firstHandle ) );
+		note.inputBases.push_back( CMemoryHandleInternal::Base( secondHandle ) );
+		if( noteLazy( note ) ) return;
+	}
+	check( launchProduct( batchSize, raw( firstHandle ), firstHeight, firstWidth, raw( secondHandle ), secondWidth,
+		raw( resultHandle ) ), "MultiplyMatrixByMatrix" );
+}
+
+int CB200MathEngine::launchProduct( int batchSize, const float* first, int firstHeight, int firstWidth, const float* second,
+	int secondWidth, float* result ) const
+{
+	CB200MathEngine* self = const_cast<CB200MathEngine*>( this );
 	// The second operand is [K x N]: the tensor-core kernel wants both operands K-major.  One transposing pass over it
 	// (into stack memory) costs a read and a write of the operand and lets the product run on the TMA-fed path, which
 	// is several times faster than gathering a column-major operand element by element.
 	const size_t floats = static_cast<size_t>( batchSize ) * firstWidth * secondWidth;
 	if( firstWidth >= 4 && secondWidth >= 4 && floats < ( static_cast<size_t>( 1 ) << 31 ) ) {
-		CMemoryHandle scratch = StackAlloc( floats * sizeof( float ) );
+		CMemoryHandle scratch = self->StackAlloc( floats * sizeof( float ) );
 		float* transposed = static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) );
-		int rc = nb200_transpose_matrix( stream, batchSize, raw( secondHandle ), firstWidth, 1, secondWidth, 1, transposed );
+		int rc = nb200_transpose_matrix( stream, batchSize, second, firstWidth, 1, secondWidth, 1, transposed );
 		if( rc == 0 ) {
-			rc = productWithScratch( batchSize, raw( firstHandle ), firstHeight, firstWidth, firstWidth, transposed, secondWidth,
-				firstWidth, raw( resultHandle ), secondWidth );
+			rc = productWithScratch( batchSize, first, firstHeight, firstWidth, firstWidth, transposed, secondWidth,
+				firstWidth, result, secondWidth );
 		}
-		StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
-		check( rc, "MultiplyMatrixByMatrix" );
-		return;
+		self->StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
+		return rc;
 	}
-	check( nb200_multiply_matrix_by_matrix( stream, batchSize, raw( firstHandle ), firstHeight, firstWidth, raw( secondHandle ),
-		secondWidth, raw( resultHandle ), nullptr, precision ), "MultiplyMatrixByMatrix" );
+	return nb200_multiply_matrix_by_matrix( stream, batchSize, first, firstHeight, firstWidth, second, secondWidth, result,
+		nullptr, precision );
 }
 
 void CB200MathEngine::MultiplyDiagMatrixByMatrix( const CConstFloatHandle& firstHandle, int firstSize,

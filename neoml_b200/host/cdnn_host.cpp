@@ -19,6 +19,8 @@
 #include <NeoML/NeoML.h>
 #include <NeoML/Dnn/DnnDistributed.h>
 
+#include <dlfcn.h>
+
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -767,6 +769,194 @@ CDNN_API int cdnn_selftest_free_while_pending( void* enginePtr, float* maxDiffer
 		float worst = 0.f;
 		for( size_t i = 0; i < kept.size(); ++i ) worst = std::max( worst, std::fabs( kept[i] - freed[i] ) );
 		*maxDifference = worst;
+	} );
+}
+
+// BlobResizeImage (constant border) followed by BlobMaxPooling, the pair behind a padded stem pool, in the orders in
+// which a caller may touch the buffers involved.  An engine may hold the padding back and pool the unpadded image in
+// one pass; whatever it does, every buffer must read as if each call had run when it was made:
+//   0  pad, pool, read the pooled image          1  pad, pool, then read the PADDED image
+//   2  pad, free the source, pool                2  (same number) ...
+//   3  pad, overwrite the source, read the padded image (it shows the old source)
+//   4  pad, free the padded image unread, pad again into a new blob, pool
+// Writes the number of values that differ from a host evaluation (0 is the only right answer) and, for case 0, how
+// many kernels the pad + pool pair launched (-1 where the engine does not count launches).
+CDNN_API int cdnn_selftest_padded_pool( void* enginePtr, int* mismatches, int* launchesOfCase0 )
+{
+	return guarded( [&] {
+		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
+		const int n = 2, h = 9, w = 11, c = 8, ph = h + 2, pw = w + 2, oh = ( ph - 3 ) / 2 + 1, ow = ( pw - 3 ) / 2 + 1;
+		const float border = 0.25f; // above part of the data: the border then decides some maxima
+		CSplitMix rng( 31337 );
+		std::vector<float> x( static_cast<size_t>( n ) * h * w * c );
+		for( float& v : x ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+		auto padded = [&]( const std::vector<float>& src ) {
+			std::vector<float> y( static_cast<size_t>( n ) * ph * pw * c, border );
+			for( int b = 0; b < n; ++b ) for( int i = 0; i < h; ++i ) for( int j = 0; j < w; ++j ) for( int k = 0; k < c; ++k ) {
+				y[( ( static_cast<size_t>( b ) * ph + i + 1 ) * pw + j + 1 ) * c + k] = src[( ( static_cast<size_t>( b ) * h + i ) * w + j ) * c + k];
+			}
+			return y;
+		};
+		auto pooled = [&]( const std::vector<float>& p ) {
+			std::vector<float> y( static_cast<size_t>( n ) * oh * ow * c );
+			for( int b = 0; b < n; ++b ) for( int i = 0; i < oh; ++i ) for( int j = 0; j < ow; ++j ) for( int k = 0; k < c; ++k ) {
+				float best = -1e30f;
+				for( int fy = 0; fy < 3; ++fy ) for( int fx = 0; fx < 3; ++fx ) {
+					best = std::max( best, p[( ( static_cast<size_t>( b ) * ph + 2 * i + fy ) * pw + 2 * j + fx ) * c + k] );
+				}
+				y[( ( static_cast<size_t>( b ) * oh + i ) * ow + j ) * c + k] = best;
+			}
+			return y;
+		};
+		const std::vector<float> wantPadded = padded( x ), wantPooled = pooled( wantPadded );
+		typedef long long ( *TCount )();
+		TCount launchCount = reinterpret_cast<TCount>( dlsym( RTLD_DEFAULT, "nb200_launch_count" ) );
+		int wrong = 0;
+		auto compare = [&]( const CDnnBlob& blob, const std::vector<float>& want ) {
+			std::vector<float> got( static_cast<size_t>( blob.GetDataSize() ) );
+			const_cast<CDnnBlob&>( blob ).CopyTo( got.data() );
+			if( got.size() != want.size() ) { wrong += 1000000; return; }
+			for( size_t i = 0; i < got.size(); ++i ) wrong += got[i] == want[i] ? 0 : 1;
+		};
+		*launchesOfCase0 = -1;
+		for( int scenario = 0; scenario < 5; ++scenario ) {
+			CPtr<CDnnBlob> src = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, n, h, w, c );
+			CPtr<CDnnBlob> pad = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, n, ph, pw, c );
+			CPtr<CDnnBlob> out = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, n, oh, ow, c );
+			src->CopyFrom( x.data() );
+			pad->Fill( -7.f );
+			out->Fill( -7.f );
+			std::unique_ptr<CMaxPoolingDesc> desc( e.InitMaxPooling( pad->GetDesc(), 3, 3, 2, 2, out->GetDesc() ) );
+			const long long before = launchCount != nullptr ? launchCount() : 0;
+			e.BlobResizeImage( src->GetDesc(), src->GetData(), 1, 1, 1, 1, border, pad->GetDesc(), pad->GetData() );
+			switch( scenario ) {
+				case 0:
+					e.BlobMaxPooling( *desc, pad->GetData(), nullptr, out->GetData() );
+					if( launchCount != nullptr ) *launchesOfCase0 = static_cast<int>( launchCount() - before );
+					compare( *out, wantPooled );
+					break;
+				case 1:
+					e.BlobMaxPooling( *desc, pad->GetData(), nullptr, out->GetData() );
+					compare( *pad, wantPadded );
+					compare( *out, wantPooled );
+					break;
+				case 2:
+					src = nullptr;
+					{ CPtr<CDnnBlob> other = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, n, h, w, c ); other->Fill( 3.f ); }
+					e.BlobMaxPooling( *desc, pad->GetData(), nullptr, out->GetData() );
+					compare( *out, wantPooled );
+					break;
+				case 3:
+					src->Fill( 9.f );
+					compare( *pad, wantPadded );
+					break;
+				case 4: {
+					pad = nullptr;
+					CPtr<CDnnBlob> again = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, n, ph, pw, c );
+					e.BlobResizeImage( src->GetDesc(), src->GetData(), 1, 1, 1, 1, border, again->GetDesc(), again->GetData() );
+					e.BlobMaxPooling( *desc, again->GetData(), nullptr, out->GetData() );
+					compare( *out, wantPooled );
+					compare( *again, wantPadded );
+					break;
+				}
+			}
+		}
+		*mismatches = wrong;
+	} );
+}
+
+// The score chain of CMultiheadAttentionLayer as the layers issue it -- batched MultiplyMatrixByMatrix( Q, Kt ),
+// VectorMultiply in place, AddVectorToMatrixRows of the mask into ANOTHER blob (CAddToObjectLayer is not an in-place
+// layer), MatrixSoftmaxByRows in place, MultiplyMatrixByMatrix( P, V ) -- in the orders in which a caller may touch the
+// buffers.  An engine may run the chain as one kernel and leave scores and probabilities unwritten; whatever it does,
+// every buffer must read as if each call had run when it was made:
+//   0  the chain, read the result                    1  the chain, then read the probabilities
+//   2  blobs released as early as NeoML's reuse mode releases them (Q, Kt after the product; scores after the mask)
+//   3  the keys overwritten after the softmax was issued: probabilities and result show the old keys
+//   4  no mask: scale and softmax in place
+// Writes the largest error of any value read, relative to the RMS of what it is compared with (against a
+// double-precision host evaluation), and how many kernels case 0 launched (-1 where launches are not counted).
+CDNN_API int cdnn_selftest_attention_chain( void* enginePtr, float* worstError, int* launchesOfCase0 )
+{
+	return guarded( [&] {
+		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
+		const int heads = 3, seq = 128, depth = 64;
+		const float scaleValue = 0.125f;
+		CSplitMix rng( 4242 );
+		std::vector<float> q( heads * seq * depth ), kt( heads * depth * seq ), v( heads * seq * depth ), mask( seq * seq );
+		for( float& x : q ) x = static_cast<float>( rng.uniform() * 2 - 1 );
+		for( float& x : kt ) x = static_cast<float>( rng.uniform() * 2 - 1 );
+		for( float& x : v ) x = static_cast<float>( rng.uniform() * 2 - 1 );
+		for( int i = 0; i < seq; ++i ) for( int j = 0; j < seq; ++j ) mask[i * seq + j] = j > i ? -1e9f : 0.f;
+		auto evaluate = [&]( const std::vector<float>& keys, bool withMask, std::vector<double>& probs, std::vector<double>& out ) {
+			probs.assign( static_cast<size_t>( heads ) * seq * seq, 0. );
+			out.assign( static_cast<size_t>( heads ) * seq * depth, 0. );
+			for( int h = 0; h < heads; ++h ) for( int i = 0; i < seq; ++i ) {
+				double* row = &probs[( static_cast<size_t>( h ) * seq + i ) * seq];
+				double top = -1e300;
+				for( int j = 0; j < seq; ++j ) {
+					double sum = 0;
+					for( int d = 0; d < depth; ++d ) sum += double( q[( h * seq + i ) * depth + d] ) * keys[( h * depth + d ) * seq + j];
+					row[j] = sum * scaleValue + ( withMask ? mask[i * seq + j] : 0.f );
+					top = std::max( top, row[j] );
+				}
+				double total = 0;
+				for( int j = 0; j < seq; ++j ) { row[j] = std::exp( row[j] - top ); total += row[j]; }
+				for( int j = 0; j < seq; ++j ) row[j] /= total;
+				for( int d = 0; d < depth; ++d ) {
+					double sum = 0;
+					for( int j = 0; j < seq; ++j ) sum += row[j] * v[( h * seq + j ) * depth + d];
+					out[( static_cast<size_t>( h ) * seq + i ) * depth + d] = sum;
+				}
+			}
+		};
+		std::vector<double> wantProbs, wantOut, wantProbsNoMask, wantOutNoMask;
+		evaluate( kt, true, wantProbs, wantOut );
+		evaluate( kt, false, wantProbsNoMask, wantOutNoMask );
+		typedef long long ( *TCount )();
+		TCount launchCount = reinterpret_cast<TCount>( dlsym( RTLD_DEFAULT, "nb200_launch_count" ) );
+		double worst = 0;
+		auto compare = [&]( const CDnnBlob& blob, const std::vector<double>& want ) {
+			std::vector<float> got( static_cast<size_t>( blob.GetDataSize() ) );
+			const_cast<CDnnBlob&>( blob ).CopyTo( got.data() );
+			if( got.size() != want.size() ) { worst = 1e30; return; }
+			double square = 0, gap = 0;
+			for( size_t i = 0; i < got.size(); ++i ) { square += want[i] * want[i]; gap = std::max( gap, std::fabs( got[i] - want[i] ) ); }
+			const double error = gap / std::sqrt( square / got.size() );
+			worst = std::max( worst, error == error ? error : 1e30 );
+		};
+		*launchesOfCase0 = -1;
+		for( int scenario = 0; scenario < 5; ++scenario ) {
+			const bool withMask = scenario != 4;
+			CPtr<CDnnBlob> bq = CDnnBlob::CreateTensor( e, CT_Float, { 1, heads, 1, seq, 1, 1, depth } );
+			CPtr<CDnnBlob> bk = CDnnBlob::CreateTensor( e, CT_Float, { 1, heads, 1, depth, 1, 1, seq } );
+			CPtr<CDnnBlob> bv = CDnnBlob::CreateTensor( e, CT_Float, { 1, heads, 1, seq, 1, 1, depth } );
+			CPtr<CDnnBlob> bm = CDnnBlob::CreateTensor( e, CT_Float, { 1, 1, 1, seq, 1, 1, seq } );
+			CPtr<CDnnBlob> scores = CDnnBlob::CreateTensor( e, CT_Float, { 1, heads, 1, seq, 1, 1, seq } );
+			CPtr<CDnnBlob> masked = scores;
+			if( withMask ) masked = CDnnBlob::CreateTensor( e, CT_Float, { 1, heads, 1, seq, 1, 1, seq } );
+			CPtr<CDnnBlob> out = CDnnBlob::CreateTensor( e, CT_Float, { 1, heads, 1, seq, 1, 1, depth } );
+			CPtr<CDnnBlob> factor = CDnnBlob::CreateVector( e, CT_Float, 1 );
+			bq->CopyFrom( q.data() ); bk->CopyFrom( kt.data() ); bv->CopyFrom( v.data() ); bm->CopyFrom( mask.data() );
+			factor->Fill( scaleValue );
+			scores->Fill( -7.f ); out->Fill( -7.f );
+			if( withMask ) masked->Fill( -7.f );
+			const long long before = launchCount != nullptr ? launchCount() : 0;
+			e.MultiplyMatrixByMatrix( heads, bq->GetData(), seq, depth, bk->GetData(), seq, scores->GetData(), scores->GetDataSize() );
+			if( scenario == 2 ) { bq = nullptr; bk = nullptr; }
+			e.VectorMultiply( scores->GetData(), scores->GetData(), scores->GetDataSize(), factor->GetData() );
+			if( withMask ) {
+				e.AddVectorToMatrixRows( 1, scores->GetData(), masked->GetData(), heads, seq * seq, bm->GetData() );
+				if( scenario == 2 ) scores = nullptr;
+			}
+			e.MatrixSoftmaxByRows( masked->GetData(), heads * seq, seq, masked->GetData() );
+			if( scenario == 3 ) bk->Fill( 0.5f );
+			e.MultiplyMatrixByMatrix( heads, masked->GetData(), seq, seq, bv->GetData(), depth, out->GetData(), out->GetDataSize() );
+			if( scenario == 0 && launchCount != nullptr ) *launchesOfCase0 = static_cast<int>( launchCount() - before );
+			compare( *out, withMask ? wantOut : wantOutNoMask );
+			if( scenario == 1 || scenario == 3 ) compare( *masked, wantProbs );
+		}
+		*worstError = static_cast<float>( worst );
 	} );
 }
 

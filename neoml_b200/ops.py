@@ -303,6 +303,31 @@ def BlobMaxPooling(source, filter_size, stride, result=None, with_indices=False)
     return (result, idx) if with_indices else result
 
 
+def AttentionScoresValues(q, kt, v, scale=None, mask=None, precision=PREC_3XTF32):
+    """softmax(scale * q @ kt + mask) @ v per batch entry; q [b, sq, d], kt [b, d, st], v [b, st, d]; scale: a 1-element
+    device tensor or None; mask [sq, st] or None."""
+    b, sq, d = q.shape
+    st = kt.shape[2]
+    out = torch.empty((b, sq, d), dtype=torch.float32, device=q.device)
+    capi.check("AttentionScoresValues", capi.load().nb200_attention_scores_values(
+        _stream(), b, _ptr(q), _ptr(kt), _ptr(v), sq, d, st, _ptr(scale), _ptr(mask), _ptr(out), precision))
+    return out
+
+
+def BlobMaxPoolingPadded(source, deltas, default_value, filter_size, stride, result=None):
+    """BlobResizeImage (constant padding; deltas = left, right, top, bottom) + BlobMaxPooling as one pass."""
+    n, h, w, c = source.shape
+    left, right, top, bottom = deltas
+    ho = (h + top + bottom - filter_size[0]) // stride[0] + 1
+    wo = (w + left + right - filter_size[1]) // stride[1] + 1
+    if result is None:
+        result = torch.empty((n, ho, wo, c), dtype=torch.float32, device=source.device)
+    capi.check("BlobMaxPoolingPadded", capi.load().nb200_blob_max_pooling_padded(
+        _stream(), n, h, w, c, left, right, top, bottom, float(default_value), filter_size[0], filter_size[1], stride[0],
+        stride[1], _ptr(source), _ptr(result)))
+    return result
+
+
 def BlobMeanPooling(source, filter_size, stride, result=None):
     n, h, w, c = source.shape
     ho, wo = (h - filter_size[0]) // stride[0] + 1, (w - filter_size[1]) // stride[1] + 1

@@ -17,11 +17,18 @@ _ip = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 _i, _f, _vp = C.c_int, C.c_float, C.c_void_p
 
 
+_HANDED_OVER = []
+
+
 def _opt(a):
     """ctypes argument for an optional array: numpy (host) or anything with data_ptr() (a torch device tensor)."""
     if a is None:
         return None
     if hasattr(a, "data_ptr"):
+        # Device memory handed to an engine that may hold a call back for fusion has to outlive that call.  Under NeoML
+        # it does (blobs are the engine's own allocations: it sees their release); a torch tensor is foreign memory,
+        # so it is kept until the engine has been drained (ShimmedB200Engine.sync / close).
+        _HANDED_OVER.append(a)
         return _vp(a.data_ptr())
     return a.ctypes.data_as(_vp)
 
@@ -455,6 +462,7 @@ class ShimmedB200Engine(Reference):
             self.torch.cuda.synchronize()
             self.engine_lib.nb200_destroy_math_engine(self.engine)
             self.engine = None
+            _HANDED_OVER.clear()
 
     def sync(self):
         """Results become visible the way NeoML reads them: through a data exchange on the engine (it launches
@@ -464,6 +472,7 @@ class ShimmedB200Engine(Reference):
             self.torch.cuda.synchronize()
         self._chk(self.lib.ref_engine_sync(self.engine, _vp(self._probe.data_ptr())))
         self.torch.cuda.synchronize()
+        _HANDED_OVER.clear()
 
     def _zeros(self, shape, dtype=np.float32):
         # torch fills on its own stream, the engine computes on another: finish the fill before handing the tensor over
@@ -473,9 +482,13 @@ class ShimmedB200Engine(Reference):
         return y
 
     def _scalar(self, value):
-        y = self.torch.tensor([value], dtype=self.torch.float32, device="cuda")
-        self.torch.cuda.synchronize()
-        return y
+        # kept for the life of the engine: a call may be held back for fusion, and this memory is not the engine's own
+        # (under NeoML such scalars live in blobs and stack variables whose release the engine sees)
+        cache = self.__dict__.setdefault("_scalars", {})
+        if value not in cache:
+            cache[value] = self.torch.tensor([value], dtype=self.torch.float32, device="cuda")
+            self.torch.cuda.synchronize()
+        return cache[value]
 
     def _copy(self, a):
         y = a.clone()

@@ -2,7 +2,7 @@
 that is built to run out -- nothing here faults, traps or hangs a GPU.  Runs in a process of its own (see
 tests/cdnn_parity.py) and prints one JSON line.
 
-    python tests/cdnn_failures.py wait_timeout | memory_limit | free_while_pending | abort_distributed
+    python tests/cdnn_failures.py wait_timeout | memory_limit | free_while_pending | abort_distributed | padded_pool | ...
 """
 from __future__ import annotations
 
@@ -129,6 +129,21 @@ def overlapped_input():
 def free_while_pending():
     engine = cdnn.Engine("gpu")
     return {"max_difference": cdnn.selftest_free_while_pending(engine)}
+
+
+def padded_pool():
+    """BlobResizeImage + BlobMaxPooling in every order of touching the buffers (see cdnn_selftest_padded_pool); the same
+    harness on the reference CPU engine is the control."""
+    engine = cdnn.Engine("gpu")
+    wrong, launches = cdnn.selftest_padded_pool(engine)
+    return {"mismatches": wrong, "launches_pad_plus_pool": launches}
+
+
+def attention_chain():
+    """The attention score chain in every order of touching its buffers (see cdnn_selftest_attention_chain)."""
+    engine = cdnn.Engine("gpu")
+    worst, launches = cdnn.selftest_attention_chain(engine)
+    return {"worst_error": worst, "launches_of_the_chain": launches}
 
 
 def abort_distributed():

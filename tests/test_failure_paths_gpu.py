@@ -53,3 +53,18 @@ def test_prepared_filters_follow_new_filter_values():
 
 def test_input_copies_that_overlap_the_previous_step_change_nothing():
     assert run_case("overlapped_input")["all_steps_bit_identical"]
+
+
+def test_padding_that_is_only_noted_is_never_observable():
+    """The engine pools the unpadded image in one pass and leaves the padded image unwritten until somebody looks."""
+    row = run_case("padded_pool")
+    assert row["mismatches"] == 0
+    assert row["launches_pad_plus_pool"] == 1
+
+
+def test_attention_scores_that_are_only_noted_are_never_observable():
+    """The engine runs the five calls of the chain as one kernel and writes scores and probabilities only for whoever
+    reads them; early releases and an overwritten input change nothing."""
+    row = run_case("attention_chain")
+    assert row["worst_error"] < 1e-4, row
+    assert row["launches_of_the_chain"] == 1

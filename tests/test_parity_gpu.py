@@ -180,6 +180,22 @@ def test_vector_ops(ops, oracle):
             assert gate_err(got, want) < 1e-5, (name, n)  # fused multiply-add vs two roundings, expf vs exp
 
 
+def test_sigmoid_gate_in_one_pass_equals_the_three_calls(ops, oracle):
+    """y = sigmoid(a * s) * a (CGELULayer's fast form) as one pass: the bits of VectorMultiply, VectorSigmoid,
+    VectorEltwiseMultiply run one after the other, and the oracle's chain to tolerance."""
+    for n in (5, 1001, 1 << 16):
+        a = cases.uniform(14, (n,), -6, 6)
+        sc = torch.tensor([1.702], dtype=torch.float32, device="cuda")
+        ad = dev(a)
+        t = ops.vector_op("MULTIPLY", ad, scalar=sc)
+        t = ops.vector_op("SIGMOID", t)
+        three = host(ops.vector_op("ELTWISE_MUL", ad, t))
+        one = host(ops.vector_op("SIGMOID_MUL", ad, scalar=sc))
+        assert np.array_equal(one, three)
+        want = oracle.vector_op(5, a, oracle.vector_op(10, oracle.vector_op(6, a, None, 1.702)))
+        assert gate_err(one, want) < 1e-5
+
+
 def test_vector_ops_unaligned_and_in_place(ops, oracle):
     a = cases.uniform(13, (1003,))
     buf = torch.zeros(1004, dtype=torch.float32, device="cuda")
@@ -500,6 +516,90 @@ def test_vectorised_helper_variants(ops, oracle):
     for shape in [(2, 23, 31, 8), (1, 7, 9, 64), (3, 3, 3, 4)]:          # odd sizes: partial strips at the right edge
         x = cases.uniform(74, shape)
         assert np.array_equal(host(ops.BlobMaxPooling(dev(x), (3, 3), (2, 2))), oracle.blob_max_pooling(x, (3, 3), (2, 2))[0])
+
+
+def _attention_reference(q, kt, v, scale, mask):
+    import torch
+    s = torch.matmul(q.double(), kt.double())
+    if scale is not None:
+        s = s * float(scale)
+    if mask is not None:
+        s = s + mask.double()
+    return torch.matmul(torch.softmax(s, dim=-1), v.double())
+
+
+@pytest.mark.parametrize("case", [
+    (3, 128, 128, False, 1.0), (2, 256, 384, True, 1.0), (2, 200, 260, True, 1.0), (5, 512, 512, True, 1.0),
+    (2, 128, 512, False, 40.0),      # later key blocks dominate: the running reference of the softmax has to move
+])
+def test_attention_chain_as_one_kernel(ops, case):
+    """softmax(scale * Q Kt + mask) V against a float64 evaluation: the same gate as the separate calls (1e-4 of the
+    result's RMS).  The mask is NeoML's: -1e9 where a key is hidden (here: the causal triangle)."""
+    import torch
+    b, sq, st, masked, growth = case
+    d = 64
+    q = dev(cases.uniform(81, (b, sq, d)))
+    kt = dev(cases.uniform(82, (b, d, st)))
+    v = dev(cases.uniform(83, (b, st, d)))
+    if growth != 1.0:
+        kt[:, :, st // 2:] *= growth                       # scores of the second half are up to 40 x larger
+    scale = torch.tensor([0.125], dtype=torch.float32, device="cuda")
+    mask = None
+    if masked:
+        mask = torch.triu(torch.full((sq, st), -1e9, dtype=torch.float32, device="cuda"), diagonal=1 + max(st - sq, 0))
+    got = ops.AttentionScoresValues(q, kt, v, scale=scale, mask=mask)
+    want = _attention_reference(q, kt, v, 0.125, mask)
+    torch.cuda.synchronize()
+    assert ops.capi.load().nb200_device_status(None, 0) == 0
+    err = (got.double() - want).abs().max() / want.pow(2).mean().sqrt()
+    assert float(err) < 1e-4, float(err)
+    # the engine's separate calls give the same to the same gate
+    s = ops.MultiplyMatrixByMatrix(q, kt)
+    s = s * 0.125 + (mask if mask is not None else 0.0)
+    chain = ops.MultiplyMatrixByMatrix(torch.softmax(s, dim=-1).contiguous(), v)
+    err_chain = (chain.double() - want).abs().max() / want.pow(2).mean().sqrt()
+    assert float(err) < max(4.0 * float(err_chain), 2e-5), (float(err), float(err_chain))
+
+
+def test_attention_chain_many_items_per_cta_is_exact_and_repeatable(ops):
+    """Configuration 4's size (768 heads x 512 x 512): every CTA walks some twenty items, buffers are handed from one
+    item to the next.  Three runs give the same bits, and every item meets the gate against float64."""
+    import torch
+    b, sq, st, d = 768, 512, 512, 64
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(b, sq, d, device="cuda", generator=gen)
+    kt = torch.randn(b, d, st, device="cuda", generator=gen) * 0.3
+    v = torch.randn(b, st, d, device="cuda", generator=gen)
+    scale = torch.full((1,), 0.125, device="cuda")
+    for mask in (None, torch.triu(torch.full((sq, st), -1e9, device="cuda"), diagonal=1)):
+        runs = [ops.AttentionScoresValues(q, kt, v, scale=scale, mask=mask) for _ in range(3)]
+        torch.cuda.synchronize()
+        assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+        worst = 0.0
+        for i0 in range(0, b, 64):
+            want = _attention_reference(q[i0:i0 + 64], kt[i0:i0 + 64], v[i0:i0 + 64], 0.125, mask)
+            err = (runs[0][i0:i0 + 64].double() - want).abs().reshape(64 * 4, -1).amax(-1) / want.pow(2).mean().sqrt()
+            worst = max(worst, float(err.max()))
+        assert worst < 1e-4, worst
+
+
+def test_attention_chain_refuses_what_it_does_not_cover(ops):
+    import torch
+    q = torch.zeros((1, 128, 32), device="cuda")
+    kt = torch.zeros((1, 32, 128), device="cuda")
+    with pytest.raises(Exception):
+        ops.AttentionScoresValues(q, kt, q)                # depth 32: the separate calls are the way
+
+
+def test_padded_max_pool_equals_resize_then_pool(ops, oracle):
+    """One pass over the unpadded image against BlobResizeImage followed by BlobMaxPooling on the oracle: bit-exact,
+    including a border value above the data (it then wins at the edges) and uneven borders."""
+    for shape, deltas, value in [((2, 23, 31, 8), (1, 1, 1, 1), 0.0), ((1, 8, 8, 64), (1, 1, 1, 1), 5.0),
+                                 ((3, 7, 9, 4), (2, 0, 1, 3), -1.0), ((1, 112, 112, 64), (1, 1, 1, 1), 0.0)]:
+        x = cases.uniform(75, shape)
+        padded = oracle.blob_resize_image(x, *deltas, 0, value)
+        want = oracle.blob_max_pooling(padded, (3, 3), (2, 2))[0]
+        assert np.array_equal(host(ops.BlobMaxPoolingPadded(dev(x), deltas, value, (3, 3), (2, 2))), want)
 
 
 def test_blob_convolution_random_shapes(ops, oracle):
