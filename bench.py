@@ -63,6 +63,7 @@ def parse_args():
                          "block, config 4 FC and attention products, config 5 matrix products) against the tensor roofline")
     ap.add_argument("--sweep", action="store_true",
                     help="per-GPU batch 1/32/256/1024 on 1/2/4/8 engines of one process (CreateDistributedCudaMathEngines)")
+    ap.add_argument("--only", default="", help="with --products: run only the cases whose name contains this text")
     ap.add_argument("--transformer", action="store_true", help="configuration 4 (12 encoder layers, 64 x 512 x 768) as a CDnn")
     ap.add_argument("--kernel-options", type=int, default=0,
                     help="diagnostic switches of the contraction launcher (16 gather kernel, 32 no split K, 64 no "
@@ -661,6 +662,8 @@ def run_products(args):
                       lambda a=a, b=b, c=c: ops.MultiplyMatrixByMatrix(a, b, result=c, precision=prec)))
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for name, flops, fn in cases:
+        if args.only and args.only not in name:
+            continue
         for _ in range(max(args.warmup, 3)):
             fn()
         torch.cuda.synchronize()

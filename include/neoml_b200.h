@@ -46,7 +46,9 @@ enum {
 enum {
 	NB200_ACT_NONE = 0,
 	NB200_ACT_RELU = 1,   /* param > 0: min(max(x,0),param); else max(x,0)  (VectorReLU, NME.h:143-145) */
-	NB200_ACT_HSWISH = 2  /* x * relu6(x+3) / 6 */
+	NB200_ACT_HSWISH = 2, /* x * relu6(x+3) / 6 */
+	NB200_ACT_SIGMOID_GATE = 3 /* x * sigmoid(x * param): CGELULayer's fast form (NeoML/src/Dnn/Layers/GELULayer.cpp:145-163,
+	                            * param = 1.702) with the roundings of its three calls (NB200_VEC_SIGMOID_MUL) */
 };
 
 /* Optional fused tail of a contraction: y = act(acc + bias[n] (+ residual[m,n])).
@@ -98,8 +100,8 @@ NB200_API int nb200_multiply_matrix_by_matrix(void* stream, int batch, const flo
 	const float* b, int n, float* c, const nb200_epilogue* epi, int precision);
 /* The score chain of CMultiheadAttentionLayer (NeoML/src/Dnn/Layers/MultiheadAttentionLayer.cpp:145-223) as one kernel:
  * batched MultiplyMatrixByMatrix (NME.h:580-582) of q [batch][seq_q x depth] by kt [batch][depth x seq_to],
- * VectorMultiply by *scale (NME.h:268; NULL = 1), AddVectorToMatrixRows of mask [seq_q x seq_to] (NME.h:456-458; the same
- * for every batch entry, NULL = none), MatrixSoftmaxByRows (NME.h:501-502), and the batched MultiplyMatrixByMatrix of the
+ * VectorMultiply by *scale (NME.h:268; NULL = 1), AddVectorToMatrixRows of mask [seq_q x seq_to] (NME.h:419-420; the same
+ * for every batch entry, NULL = none), MatrixSoftmaxByRows (NME.h:450), and the batched MultiplyMatrixByMatrix of the
  * probabilities by v [batch][seq_to x depth] -> out [batch][seq_q x depth].  The scores stay in tensor memory.
  * depth == 64, seq_q >= 128, seq_to >= 128 and a multiple of 4, 16-byte aligned operands, NB200_PREC_3XTF32;
  * NB200_EINVAL for anything else: issue the calls one by one then. */
@@ -232,6 +234,19 @@ NB200_API int nb200_sum_matrix_rows(void* stream, int batch, float* y, const flo
 	int add);
 /* SumMatrixColumns (NME.h:439-440): y[h] = sum_w x[h][w]. */
 NB200_API int nb200_sum_matrix_columns(void* stream, float* y, const float* x, int height, int width);
+/* AddVectorToMatrixColumns (NME.h:423-424) into a scratch matrix, optionally VectorEltwiseMultiply of it by itself
+ * (NME.h:279), then SumMatrixColumns (NME.h:439-440) -- the variance step of CObjectNormalizationLayer
+ * (NeoML/src/Dnn/Layers/ObjectNormalizationLayer.cpp:198-216) -- as one pass over x, the scratch matrix never written:
+ * y[h] = sum_w f(x[h][w] + row_add[h]), f = identity or the square; same roundings and order of additions. */
+NB200_API int nb200_sum_matrix_columns_shifted(void* stream, float* y, const float* x, int height, int width,
+	const float* row_add, int square);
+/* AddVectorToMatrixColumns (NME.h:423-424), MultiplyDiagMatrixByMatrix (NME.h:570-572), MultiplyMatrixByDiagMatrix
+ * (NME.h:588-596), AddVectorToMatrixRows (NME.h:419-420) -- the normalise / scale / bias steps of
+ * CObjectNormalizationLayer (ObjectNormalizationLayer.cpp:218-242) -- as one pass:
+ * y[h][w] = (((x[h][w] + row_add[h]) [squared]) * row_mul[h]) * col_mul[w] + col_add[w]; a NULL vector skips its step;
+ * each step is rounded by itself, so the result is the bits of the separate calls.  y may be x. */
+NB200_API int nb200_matrix_rows_cols_affine(void* stream, const float* x, int height, int width, const float* row_add,
+	int square, const float* row_mul, const float* col_mul, const float* col_add, float* y);
 /* MultiplyDiagMatrixByMatrix (NME.h:570-572): y[i][j] = d[i] * x[i][j]. */
 NB200_API int nb200_multiply_diag_matrix_by_matrix(void* stream, const float* d, int height, const float* x,
 	int width, float* y);
@@ -260,7 +275,7 @@ NB200_API int nb200_find_max_value_in_columns(void* stream, int batch, const flo
  * max_indices (optional) receives the flat in-image index of each maximum. */
 NB200_API int nb200_blob_max_pooling(void* stream, int batch, int h, int w, int c, int filter_h, int filter_w,
 	int stride_h, int stride_w, const float* x, float* y, int* max_indices);
-/* BlobResizeImage with constant padding (NME.h:1020-1023) followed by BlobMaxPooling (NME.h:817-822) as one pass: the
+/* BlobResizeImage with constant padding (NME.h:708-716) followed by BlobMaxPooling (NME.h:817-822) as one pass: the
  * windows slide over x [batch,h,w,c] surrounded by pad_* rows / columns of pad_value; y is what pooling the padded
  * image would give, the padded image is never written.  3x3 windows with stride 2 and c % 4 == 0 only (the padded stem
  * pool of the ResNets); NB200_EINVAL for any other form: pad and pool with the two calls then. */

@@ -88,6 +88,10 @@ def load():
         lib.cdnn_selftest_abort_distributed.argtypes = [_ip, C.c_char_p, C.c_int]
     if hasattr(lib, "cdnn_selftest_padded_pool"):
         lib.cdnn_selftest_padded_pool.argtypes = [C.c_void_p, _ip, _ip]
+    if hasattr(lib, "cdnn_selftest_product_chain"):
+        lib.cdnn_selftest_product_chain.argtypes = [C.c_void_p, _fp]
+    if hasattr(lib, "cdnn_selftest_normalization_chain"):
+        lib.cdnn_selftest_normalization_chain.argtypes = [C.c_void_p, _fp, _ip]
     if hasattr(lib, "cdnn_selftest_attention_chain"):
         lib.cdnn_selftest_attention_chain.argtypes = [C.c_void_p, _fp, _ip]
     _lib = lib
@@ -286,6 +290,23 @@ def selftest_attention_chain(engine: Engine) -> tuple[float, int]:
     worst, launches = C.c_float(-1), C.c_int(-1)
     if load().cdnn_selftest_attention_chain(engine.ptr, C.byref(worst), C.byref(launches)) != 0:
         _fail("selftest_attention_chain")
+    return worst.value, launches.value
+
+
+def selftest_product_chain(engine: Engine) -> float:
+    """See cdnn_selftest_product_chain: the largest error relative to the RMS of the expected values."""
+    worst = C.c_float(-1)
+    if load().cdnn_selftest_product_chain(engine.ptr, C.byref(worst)) != 0:
+        _fail("selftest_product_chain")
+    return worst.value
+
+
+def selftest_normalization_chain(engine: Engine) -> tuple[float, int]:
+    """See cdnn_selftest_normalization_chain: (largest relative difference from the host evaluation, kernels launched by
+    the output chain and its read)."""
+    worst, launches = C.c_float(-1), C.c_int(-1)
+    if load().cdnn_selftest_normalization_chain(engine.ptr, C.byref(worst), C.byref(launches)) != 0:
+        _fail("selftest_normalization_chain")
     return worst.value, launches.value
 
 

@@ -420,6 +420,8 @@ __device__ __forceinline__ float apply_act(float v, int act, float param)
 		if(param > 0.f) v = fminf(v, param);
 	} else if(act == NB200_ACT_HSWISH) {
 		v = v * fminf(fmaxf(v + 3.f, 0.f), 6.f) * (1.f / 6.f);
+	} else if(act == NB200_ACT_SIGMOID_GATE) {
+		v = __fmul_rn(1.f / (1.f + expf(-__fmul_rn(v, param))), v);
 	}
 	return v;
 }

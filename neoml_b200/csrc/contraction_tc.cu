@@ -628,6 +628,7 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		// uniform epilogue options, decided once: the fast store path has no branch per element
 		const bool fastStore = vec && p.accumulate == 0 && p.act != NB200_ACT_HSWISH;
 		const bool clampOn = p.act == NB200_ACT_RELU;
+		const bool gateOn = p.act == NB200_ACT_SIGMOID_GATE;
 		const float actParam = p.act_param_device != nullptr ? __ldg(p.act_param_device) : p.act_param;
 		const float clampHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
 		bool ok = true;
@@ -801,6 +802,10 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 							o.y = clampOn ? fminf(fmaxf(o.y, 0.f), clampHi) : o.y;
 							o.z = clampOn ? fminf(fmaxf(o.z, 0.f), clampHi) : o.z;
 							o.w = clampOn ? fminf(fmaxf(o.w, 0.f), clampHi) : o.w;
+							if(gateOn) {
+								o.x = apply_act(o.x, NB200_ACT_SIGMOID_GATE, actParam); o.y = apply_act(o.y, NB200_ACT_SIGMOID_GATE, actParam);
+								o.z = apply_act(o.z, NB200_ACT_SIGMOID_GATE, actParam); o.w = apply_act(o.w, NB200_ACT_SIGMOID_GATE, actParam);
+							}
 							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
 							if(m < mEnd) {
 								asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");

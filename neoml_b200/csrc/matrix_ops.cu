@@ -172,18 +172,84 @@ __global__ void __launch_bounds__(256) sum_rows_vec_kernel(float* __restrict__ y
 	}
 }
 
-// y[h] = sum_w x[h][w]: one warp per row
+// y[h] = sum_w x[h][w]: one warp per row.  SHIFTED: the element is first moved by the row's own addend and, if
+// `square`, multiplied by itself -- every step rounded like the separate calls it stands for -- and the sum runs in
+// the same order, so the result is that of AddVectorToMatrixColumns, VectorEltwiseMultiply and SumMatrixColumns.
+template<bool SHIFTED>
 __global__ void __launch_bounds__(256) sum_cols_kernel(float* __restrict__ y, const float* __restrict__ x,
-	int height, int width)
+	int height, int width, const float* __restrict__ rowAdd, int square)
 {
 	const int warpsPerBlock = blockDim.x >> 5;
 	const int lane = threadIdx.x & 31;
 	for(int h = blockIdx.x * warpsPerBlock + (threadIdx.x >> 5); h < height; h += gridDim.x * warpsPerBlock) {
 		const float* row = x + static_cast<size_t>(h) * width;
 		float acc = 0.f;
-		for(int w = lane; w < width; w += 32) acc += row[w];
+		if(SHIFTED) {
+			const float a = __ldg(rowAdd + h);
+			for(int w = lane; w < width; w += 32) {
+				float v = __fadd_rn(row[w], a);
+				if(square) v = __fmul_rn(v, v);
+				acc += v;
+			}
+		} else {
+			for(int w = lane; w < width; w += 32) acc += row[w];
+		}
 		acc = warp_sum(acc);
 		if(lane == 0) y[h] = acc;
+	}
+}
+
+// y[h][w] = (((x[h][w] + rowAdd[h]) [squared]) * rowMul[h]) * colMul[w] + colAdd[w]; every step optional and rounded
+// by itself, in this order: the chain AddVectorToMatrixColumns, [VectorEltwiseMultiply by itself,]
+// MultiplyDiagMatrixByMatrix, MultiplyMatrixByDiagMatrix, AddVectorToMatrixRows in one pass.
+struct Affine {
+	const float* rowAdd;
+	const float* rowMul;
+	const float* colMul;
+	const float* colAdd;
+	int square;
+};
+
+template<int V>
+__global__ void __launch_bounds__(256) affine_kernel(const float* __restrict__ x, float* __restrict__ y, long long total,
+	int width, const Affine f)
+{
+	const int wv = width / V;
+	const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+	for(long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+		const long long h = e / wv;
+		const int w = static_cast<int>(e - h * wv) * V;
+		float v[V];
+		if(V == 4) {
+			const float4 t = reinterpret_cast<const float4*>(x)[e];
+			v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+		} else {
+			v[0] = x[e];
+		}
+		if(f.rowAdd != nullptr) {
+			const float a = __ldg(f.rowAdd + h);
+#pragma unroll
+			for(int i = 0; i < V; ++i) v[i] = __fadd_rn(v[i], a);
+		}
+		if(f.square) {
+#pragma unroll
+			for(int i = 0; i < V; ++i) v[i] = __fmul_rn(v[i], v[i]);
+		}
+		if(f.rowMul != nullptr) {
+			const float m = __ldg(f.rowMul + h);
+#pragma unroll
+			for(int i = 0; i < V; ++i) v[i] = __fmul_rn(v[i], m);
+		}
+		if(f.colMul != nullptr) {
+#pragma unroll
+			for(int i = 0; i < V; ++i) v[i] = __fmul_rn(v[i], __ldg(f.colMul + w + i));
+		}
+		if(f.colAdd != nullptr) {
+#pragma unroll
+			for(int i = 0; i < V; ++i) v[i] = __fadd_rn(v[i], __ldg(f.colAdd + w + i));
+		}
+		if(V == 4) reinterpret_cast<float4*>(y)[e] = make_float4(v[0], v[1], v[2], v[3]);
+		else y[e] = v[0];
 	}
 }
 
@@ -544,7 +610,37 @@ int nb200_sum_matrix_columns(void* stream, float* y, const float* x, int height,
 	if(height == 0) return NB200_OK;
 	if(x == nullptr || y == nullptr) return NB200_EINVAL;
 	NB200_REQUIRE_DEVICE();
-	sum_cols_kernel<<<grid_for(height, 8, 16), 256, 0, as_stream(stream)>>>(y, x, height, width);
+	sum_cols_kernel<false><<<grid_for(height, 8, 16), 256, 0, as_stream(stream)>>>(y, x, height, width, nullptr, 0);
+	count_launch();
+	return check_launch();
+}
+
+int nb200_sum_matrix_columns_shifted(void* stream, float* y, const float* x, int height, int width, const float* row_add,
+	int square)
+{
+	if(height < 0 || width < 0) return NB200_EINVAL;
+	if(height == 0) return NB200_OK;
+	if(x == nullptr || y == nullptr || row_add == nullptr) return NB200_EINVAL;
+	NB200_REQUIRE_DEVICE();
+	sum_cols_kernel<true><<<grid_for(height, 8, 16), 256, 0, as_stream(stream)>>>(y, x, height, width, row_add, square);
+	count_launch();
+	return check_launch();
+}
+
+int nb200_matrix_rows_cols_affine(void* stream, const float* x, int height, int width, const float* row_add, int square,
+	const float* row_mul, const float* col_mul, const float* col_add, float* y)
+{
+	if(height < 0 || width < 0) return NB200_EINVAL;
+	const long long total = static_cast<long long>(height) * width;
+	if(total == 0) return NB200_OK;
+	if(x == nullptr || y == nullptr) return NB200_EINVAL;
+	NB200_REQUIRE_DEVICE();
+	const Affine f = { row_add, row_mul, col_mul, col_add, square };
+	if(width % 4 == 0 && aligned16(x) && aligned16(y)) {
+		affine_kernel<4><<<grid_for(total / 4, 256, 16), 256, 0, as_stream(stream)>>>(x, y, total / 4, width, f);
+	} else {
+		affine_kernel<1><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(x, y, total, width, f);
+	}
 	count_launch();
 	return check_launch();
 }

@@ -153,7 +153,10 @@ void CB200MathEngine::releaseDeferredFrees() const
 
 bool CB200MathEngine::noteLazy( const CLazyResult& note ) const
 {
-	if( note.resultBase == nullptr || memory.BlockBytes( note.resultBase ) == 0 ) return false;
+	if( note.resultBase == nullptr
+		|| ( memory.BlockBytes( note.resultBase ) == 0 && memory.StackBlockBytes( note.resultBase ) == 0 ) ) {
+		return false;
+	}
 	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 	lazy.push_back( note );
 	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
@@ -171,8 +174,8 @@ int CB200MathEngine::findLazy( const void* result, CLazyResult::TKind kind ) con
 bool CB200MathEngine::lazyReads( const void* allocationBase ) const
 {
 	for( const CLazyResult& note : lazy ) {
-		for( const void* base : note.inputBases ) {
-			if( base == allocationBase ) return true;
+		for( const CLazyResult::CInput& input : note.inputs ) {
+			if( input.base == allocationBase ) return true;
 		}
 	}
 	return false;
@@ -187,10 +190,26 @@ void CB200MathEngine::materializeLazy( size_t index ) const
 	cudaSetDevice( device );
 	// the kernels launched now read and write these allocations, whenever the calls were noted
 	noteUse( note.resultBase );
-	for( const void* base : note.inputBases ) noteUse( base );
+	for( const CLazyResult::CInput& input : note.inputs ) noteUse( input.base );
 	if( note.kind == CLazyResult::K_Resize ) {
 		check( nb200_blob_resize_image( stream, note.batch, note.h, note.w, note.c, note.left, note.right, note.top, note.bottom,
 			0, note.value, note.from, note.result ), "BlobResizeImage" );
+	} else if( note.kind == CLazyResult::K_Product ) {
+		// the epilogue carries bias, residual and the complete gate; a gate noted in part runs as the calls it was
+		check( productWithScratch( 1, note.first, note.rows, note.depth, note.firstRowSize, note.second, note.width,
+			note.secondRowSize, note.result, note.width, note.bias, note.residual, note.gate == 3 ? note.gateScale : nullptr ),
+			"MultiplyMatrixByTransposedMatrix" );
+		if( note.gate == 1 || note.gate == 2 ) {
+			check( nb200_vector_op( stream, NB200_VEC_MULTIPLY, note.result, nullptr, note.gateScale, 0.f, note.result,
+				static_cast<int>( note.resultFloats ) ), "VectorMultiply" );
+		}
+		if( note.gate == 2 ) {
+			check( nb200_vector_op( stream, NB200_VEC_SIGMOID, note.result, nullptr, nullptr, 0.f, note.result,
+				static_cast<int>( note.resultFloats ) ), "VectorSigmoid" );
+		}
+	} else if( note.kind == CLazyResult::K_Affine ) {
+		check( nb200_matrix_rows_cols_affine( stream, note.from, note.rows, note.width, note.rowAdd, note.square ? 1 : 0,
+			note.rowMul, note.colMul, note.colAdd, note.result ), "AddVectorToMatrixColumns" );
 	} else {
 		check( self->launchProduct( note.batch, note.first, note.seqQ, note.depth, note.second, note.seqTo, note.result ),
 			"MultiplyMatrixByMatrix" );
@@ -221,15 +240,19 @@ void CB200MathEngine::materializeAllLazy() const
 	while( !lazy.empty() ) materializeLazy( 0 );
 }
 
-void CB200MathEngine::touchLazy( const void* allocationBase, bool mayWrite ) const
+void CB200MathEngine::touchLazy( const void* allocationBase, const void* from, bool mayWrite ) const
 {
 	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	const char* const start = static_cast<const char*>( from );
 	for( ;; ) {
 		int hit = -1;
 		for( size_t i = 0; i < lazy.size() && hit < 0; ++i ) {
-			if( lazy[i].resultBase == allocationBase ) hit = static_cast<int>( i );
-			for( size_t k = 0; mayWrite && hit < 0 && k < lazy[i].inputBases.size(); ++k ) {
-				if( lazy[i].inputBases[k] == allocationBase ) hit = static_cast<int>( i );
+			if( lazy[i].resultBase == allocationBase
+				&& start < reinterpret_cast<const char*>( lazy[i].result + lazy[i].resultFloats ) ) {
+				hit = static_cast<int>( i );
+			}
+			for( size_t k = 0; mayWrite && hit < 0 && k < lazy[i].inputs.size(); ++k ) {
+				if( lazy[i].inputs[k].base == allocationBase && start < lazy[i].inputs[k].end ) hit = static_cast<int>( i );
 			}
 		}
 		if( hit < 0 ) return;
@@ -237,19 +260,19 @@ void CB200MathEngine::touchLazy( const void* allocationBase, bool mayWrite ) con
 	}
 }
 
-CB200MathEngine::CLazyResult* CB200MathEngine::deriveScores( int sourceNote, const CFloatHandle& resultHandle ) const
+CB200MathEngine::CLazyResult* CB200MathEngine::deriveNote( int sourceNote, const CFloatHandle& resultHandle ) const
 {
 	const float* const source = lazy[sourceNote].result;
 	if( peek( resultHandle ) == source ) return &lazy[sourceNote];
 	CLazyResult copy = lazy[sourceNote];
 	const void* base = CMemoryHandleInternal::Base( resultHandle );
-	if( base == copy.resultBase || memory.BlockBytes( base ) == 0 ) return nullptr;
-	for( const void* input : copy.inputBases ) {
-		if( input == base ) return nullptr;
+	if( base == copy.resultBase || ( memory.BlockBytes( base ) == 0 && memory.StackBlockBytes( base ) == 0 ) ) return nullptr;
+	for( const CLazyResult::CInput& input : copy.inputs ) {
+		if( input.base == base ) return nullptr;
 	}
 	copy.result = raw( resultHandle ); // whatever was noted for that buffer, or reads it, is carried out first
 	copy.resultBase = base;
-	if( findLazy( source, CLazyResult::K_Scores ) < 0 ) return nullptr; // that included the source
+	if( findLazy( source, copy.kind ) < 0 ) return nullptr; // that included the source
 	lazy.push_back( copy );
 	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
 	return &lazy.back();
@@ -553,7 +576,10 @@ void CB200MathEngine::StackFree( const CMemoryHandle& handle )
 		// the variable's memory can be handed out again; the stack is LIFO, so the free itself cannot be postponed
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 		if( anythingRecorded() ) enter();
-		if( !lazy.empty() ) touchLazy( CMemoryHandleInternal::Base( handle ), true );
+		if( !lazy.empty() ) {
+			forgetLazyResultIn( CMemoryHandleInternal::Base( handle ) ); // nobody can read a noted result in this variable any more
+			touchLazy( CMemoryHandleInternal::Base( handle ), CMemoryHandleInternal::Base( handle ), true ); // what reads the variable is carried out now
+		}
 	}
 	if( !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( handle ) );
 	memory.StackFree( CMemoryHandleInternal::GetRaw( handle ) );
@@ -586,7 +612,7 @@ void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* 
 	enter();
 	const void* base = CMemoryHandleInternal::Base( result );
 	if( !preparedFilters.empty() ) forgetPreparedFilter( base );
-	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( base, true );
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( base, CMemoryHandleInternal::GetRaw( result ), true );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	void* const destination = CMemoryHandleInternal::GetRaw( result );
 	// A large exchange into a heap block that nothing queued can touch overlaps the kernels in flight (see noteUse)
@@ -615,7 +641,7 @@ void CB200MathEngine::DataExchangeRaw( void* result, const CMemoryHandle& source
 	if( size == 0 ) return;
 	if( source.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
 	enter();
-	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( CMemoryHandleInternal::Base( source ), false );
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( CMemoryHandleInternal::Base( source ), CMemoryHandleInternal::GetRaw( source ), false );
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	if( cudaMemcpyAsync( result, CMemoryHandleInternal::GetRaw( source ), size, cudaMemcpyDeviceToHost, s ) != cudaSuccess
 		|| cudaStreamSynchronize( s ) != cudaSuccess ) {
@@ -712,7 +738,7 @@ CMemoryHandle CB200MathEngine::CopyFrom( const CMemoryHandle& handle, size_t siz
 	IMathEngine* other = handle.GetMathEngine();
 	if( other == this ) {
 		enter();
-		if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( CMemoryHandleInternal::Base( handle ), false );
+		if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( CMemoryHandleInternal::Base( handle ), CMemoryHandleInternal::GetRaw( handle ), false );
 		noteUse( CMemoryHandleInternal::Base( result ) );
 		noteUse( CMemoryHandleInternal::Base( handle ) );
 		cudaMemcpyAsync( CMemoryHandleInternal::GetRaw( result ), CMemoryHandleInternal::GetRaw( handle ), size,

@@ -57,6 +57,7 @@ public:
 	size_t InPools() const { return pooled; }
 	size_t FreeOnDevice() const;
 	size_t BlockBytes( const void* ptr ) const;  // size of the live heap block that starts at ptr, 0 when unknown
+	size_t StackBlockBytes( const void* ptr ) const; // the same for a live stack allocation of the calling thread
 
 private:
 	struct CStack {
@@ -131,7 +132,7 @@ private:
 		if( !std::is_const<T>::value && !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( h ) );
 		if( !h.IsNull() ) noteUse( CMemoryHandleInternal::Base( h ) );
 		if( lazyCount.load( std::memory_order_relaxed ) != 0 && !h.IsNull() ) {
-			touchLazy( CMemoryHandleInternal::Base( h ), !std::is_const<T>::value );
+			touchLazy( CMemoryHandleInternal::Base( h ), CMemoryHandleInternal::GetRaw( h ), !std::is_const<T>::value );
 		}
 		return CMemoryHandleInternal::GetRaw( h );
 	}
@@ -208,14 +209,24 @@ private:
 	// noted calls, and the noted result is never written.  Nobody can observe that: a handle into the result's
 	// allocation that reaches raw() has the noted calls launched first, so has a handle that may be written through
 	// into an allocation the noted calls read; freeing such an allocation is postponed; freeing the result's own
-	// allocation forgets the note.  Only results in heap blocks of this engine are noted (their end of life is seen).
+	// allocation forgets the note.  Only results in heap blocks and stack variables of this engine are noted (their end
+	// of life is seen).
 	struct CLazyResult {
-		enum TKind { K_Resize, K_Scores };
+		enum TKind { K_Resize, K_Scores, K_Affine, K_Product };
 		TKind kind = K_Resize;
 		const void* resultBase = nullptr;         // allocation the result lies in
 		float* result = nullptr;
 		long long resultFloats = 0;
-		std::vector<const void*> inputBases;      // allocations the noted calls read
+		// what the noted calls read: the allocation and where the operand ends in it.  A handle tells where an access
+		// starts, not how far it goes, so an access is taken to reach from the handle to the end of its allocation:
+		// it meets an operand (or the result) that ends above the handle.
+		struct CInput { const void* base; const char* end; };
+		std::vector<CInput> inputs;
+		template<class THandle> void Reads( const THandle& handle, long long floats )
+		{
+			inputs.push_back( { CMemoryHandleInternal::Base( handle ),
+				static_cast<const char*>( CMemoryHandleInternal::GetRaw( static_cast<const CMemoryHandle&>( handle ) ) ) + floats * sizeof( float ) } );
+		}
 		// K_Resize: result = from (batch x h x w x c) with a border of `value`
 		int batch = 0, h = 0, w = 0, c = 0, left = 0, right = 0, top = 0, bottom = 0;
 		float value = 0.f;
@@ -228,6 +239,24 @@ private:
 		const float* scale = nullptr;
 		const float* mask = nullptr;
 		bool softmax = false;
+		// K_Affine: result (rows x width) = (((from + rowAdd[row]) [squared]) * rowMul[row]) * colMul[column] + colAdd[column],
+		// the steps as noted so far and in this order (CObjectNormalizationLayer's chains)
+		int rows = 0, width = 0;
+		const float* rowAdd = nullptr;
+		bool square = false;
+		const float* rowMul = nullptr;
+		const float* colMul = nullptr;
+		const float* colAdd = nullptr;
+		// K_Product: result (rows x width, dense) = first (rows x depth, row size firstRowSize) * second^T (width x depth,
+		// row size secondRowSize) -- a fully connected layer's product -- then, as noted: + bias[column]; + residual
+		// (CEltwiseSumLayer); or the steps of CGELULayer's fast form: * *gateScale (gate 1), sigmoid (gate 2), * the
+		// biased product (gate 3 = complete: x * sigmoid( x * *gateScale ), the product's epilogue does it)
+		int firstRowSize = 0, secondRowSize = 0;
+		const float* bias = nullptr;
+		const float* residual = nullptr;
+		const float* gateScale = nullptr;
+		int gate = 0;
+		const float* gateSource = nullptr; // the buffer the biased product was noted for (the gate's other factor)
 	};
 	mutable std::vector<CLazyResult> lazy;   // under pendingMutex
 	mutable std::atomic<int> lazyCount{ 0 };
@@ -235,17 +264,17 @@ private:
 	int findLazy( const void* result, CLazyResult::TKind kind ) const;
 	void materializeLazy( size_t index ) const;                  // launches the noted calls, forgets the note
 	void materializeAllLazy() const;
-	void touchLazy( const void* allocationBase, bool mayWrite ) const;
+	void touchLazy( const void* allocationBase, const void* from, bool mayWrite ) const; // an access starting at `from`
 	bool lazyReads( const void* allocationBase ) const;
 	bool forgetLazyResultIn( const void* allocationBase ) const; // true if a note was forgotten
-	// `result = op( source )` over a noted score matrix: the note that describes `result` -- the source's own when the
+	// `result = op( source )` over a noted matrix: the note that describes `result` -- the source's own when the
 	// call is in place, a copy bound to the new buffer otherwise; nullptr when `result` cannot carry a note
-	CLazyResult* deriveScores( int sourceNote, const CFloatHandle& resultHandle ) const;
+	CLazyResult* deriveNote( int sourceNote, const CFloatHandle& resultHandle ) const;
 	int launchProduct( int batchSize, const float* first, int firstHeight, int firstWidth, const float* second,
 		int secondWidth, float* result ) const;
 	int productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
 		const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize,
-		const float* bias = nullptr ) const;
+		const float* bias = nullptr, const float* residual = nullptr, const float* gateScale = nullptr ) const;
 	mutable std::recursive_mutex pendingMutex;
 	// NeoML frees a layer's input blobs right after its RunOnce (reuse-memory mode), i.e. possibly while a recorded
 	// call still refers to them.  Such a heap block goes back to the pool only after the recorded call has been

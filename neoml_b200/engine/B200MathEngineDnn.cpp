@@ -135,7 +135,7 @@ void CB200MathEngine::BlobMaxPooling( const CMaxPoolingDesc& poolDesc, const CCo
 			if( note.batch == g.batch && note.h + note.top + note.bottom == g.h && note.w + note.left + note.right == g.w
 				&& note.c == g.c && nb200_blob_max_pooling_padded( stream, note.batch, note.h, note.w, note.c, note.left, note.right,
 					note.top, note.bottom, note.value, g.fh, g.fw, g.sh, g.sw, note.from, out ) == NB200_OK ) {
-				for( const void* base : note.inputBases ) noteUse( base );
+				for( const CLazyResult::CInput& input : note.inputs ) noteUse( input.base );
 				return;
 			}
 		}
@@ -180,7 +180,7 @@ void CB200MathEngine::BlobResizeImage( const CBlobDesc& from, const CFloatHandle
 		note.resultFloats = static_cast<long long>( note.batch ) * ( note.h + deltaTop + deltaBottom )
 			* ( note.w + deltaLeft + deltaRight ) * channels;
 		note.from = raw( CConstFloatHandle( fromData ) );
-		note.inputBases.push_back( CMemoryHandleInternal::Base( fromData ) );
+		note.Reads( fromData, static_cast<long long>( note.batch ) * note.h * note.w * channels );
 		if( noteLazy( note ) ) return;
 	}
 	check( nb200_blob_resize_image( stream, from.ObjectCount(), from.Height(), from.Width(), channels,

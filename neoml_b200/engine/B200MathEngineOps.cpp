@@ -82,6 +82,29 @@ void CB200MathEngine::VectorExp( const CConstFloatHandle& firstHandle, const CFl
 void CB200MathEngine::VectorAdd( const CConstFloatHandle& firstHandle, const CConstFloatHandle& secondHandle,
 	const CFloatHandle& resultHandle, int vectorSize )
 {
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( firstHandle ) != peek( secondHandle ) ) {
+		// a noted fully connected product plus another tensor (CEltwiseSumLayer): the other tensor becomes the residual
+		// of the product's epilogue, the sum is noted for the result buffer
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		for( int side = 0; side < 2; ++side ) {
+			const CConstFloatHandle& noted = side == 0 ? firstHandle : secondHandle;
+			const CConstFloatHandle& other = side == 0 ? secondHandle : firstHandle;
+			const int at = findLazy( peek( noted ), CLazyResult::K_Product );
+			if( at < 0 || lazy[at].resultFloats != vectorSize || lazy[at].gate != 0 || lazy[at].residual != nullptr
+				|| findLazy( peek( other ), CLazyResult::K_Product ) >= 0 ) {
+				continue;
+			}
+			const float* const addend = raw( other ); // whatever is noted for that tensor is carried out first
+			if( findLazy( peek( noted ), CLazyResult::K_Product ) != at ) break;
+			CLazyResult* note = deriveNote( at, resultHandle );
+			if( note == nullptr ) break;
+			note->residual = addend;
+			// the addend may be the result buffer itself (a sum in place of the other operand): then it is covered by
+			// the rule for the result, and reading it is what the epilogue does
+			if( peek( other ) != peek( resultHandle ) ) note->Reads( other, vectorSize );
+			return;
+		}
+	}
 	if( fuseAdd( raw( firstHandle ), raw( secondHandle ), raw( resultHandle ), vectorSize ) ) return;
 	vectorOp( NB200_VEC_ADD, raw( firstHandle ), raw( secondHandle ), nullptr, 0.f, raw( resultHandle ), vectorSize, "VectorAdd" );
 }
@@ -115,11 +138,11 @@ void CB200MathEngine::VectorMultiply( const CConstFloatHandle& firstHandle, cons
 		if( at >= 0 && lazy[at].resultFloats == vectorSize && lazy[at].scale == nullptr && lazy[at].mask == nullptr
 			&& !lazy[at].softmax ) {
 			lazy[at].scale = factor;
-			lazy[at].inputBases.push_back( CMemoryHandleInternal::Base( multiplierHandle ) );
+			lazy[at].Reads( multiplierHandle, 1 );
 			return;
 		}
 	}
-	if( raw( firstHandle ) == raw( resultHandle ) && vectorSize > 0 ) {
+	if( peek( firstHandle ) == peek( resultHandle ) && vectorSize > 0 ) {
 		// in place: held back, a softmax over the same buffer may absorb it (see CPendingRowOps)
 		enter();
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
@@ -129,6 +152,23 @@ void CB200MathEngine::VectorMultiply( const CConstFloatHandle& firstHandle, cons
 		pendingRows.scale = raw( multiplierHandle );
 		pendingRows.active = true;
 		return;
+	}
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( firstHandle ) != peek( resultHandle ) ) {
+		// a noted product times a device scalar into another buffer: the first step of CGELULayer's gate
+		const float* const factor = raw( multiplierHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( firstHandle ), CLazyResult::K_Product );
+		if( at >= 0 && lazy[at].resultFloats == vectorSize && lazy[at].gate == 0 && lazy[at].residual == nullptr ) {
+			const float* const source = lazy[at].result;
+			CLazyResult* note = deriveNote( at, resultHandle );
+			if( note != nullptr ) {
+				note->gate = 1;
+				note->gateScale = factor;
+				note->gateSource = source;
+				note->Reads( multiplierHandle, 1 );
+				return;
+			}
+		}
 	}
 	const std::ptrdiff_t apart = peek( resultHandle ) - peek( firstHandle );
 	if( vectorSize > 0 && ( apart >= vectorSize || -apart >= vectorSize ) ) {
@@ -155,6 +195,33 @@ void CB200MathEngine::VectorNegMultiply( const CConstFloatHandle& firstHandle, c
 void CB200MathEngine::VectorEltwiseMultiply( const CConstFloatHandle& firstHandle, const CConstFloatHandle& secondHandle,
 	const CFloatHandle& resultHandle, int vectorSize )
 {
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( firstHandle ) != peek( secondHandle )
+		&& ( peek( firstHandle ) == peek( resultHandle ) || peek( secondHandle ) == peek( resultHandle ) ) ) {
+		// the sigmoid of a scaled noted product times that product, in place of the sigmoid: CGELULayer's gate is complete
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( resultHandle ), CLazyResult::K_Product );
+		const float* const other = peek( firstHandle ) == peek( resultHandle ) ? peek( secondHandle ) : peek( firstHandle );
+		// the other factor has to be the biased product itself, still as it was noted: the buffer the gate started from,
+		// still described by a note of the same product
+		const int source = at >= 0 ? findLazy( other, CLazyResult::K_Product ) : -1;
+		if( source >= 0 && lazy[at].gate == 2 && lazy[at].resultFloats == vectorSize && lazy[at].gateSource == other
+			&& lazy[source].gate == 0 && lazy[source].residual == nullptr && lazy[source].first == lazy[at].first
+			&& lazy[source].second == lazy[at].second && lazy[source].bias == lazy[at].bias ) {
+			lazy[at].gate = 3;
+			return;
+		}
+	}
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( firstHandle ) == peek( secondHandle )
+		&& peek( firstHandle ) == peek( resultHandle ) ) {
+		// a noted matrix multiplied by itself in place: the square joins the note
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( firstHandle ), CLazyResult::K_Affine );
+		if( at >= 0 && lazy[at].resultFloats == vectorSize && !lazy[at].square && lazy[at].rowMul == nullptr
+			&& lazy[at].colMul == nullptr && lazy[at].colAdd == nullptr ) {
+			lazy[at].square = true;
+			return;
+		}
+	}
 	{
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 		const CPendingSigmoidGate g = pendingGate;
@@ -189,6 +256,14 @@ void CB200MathEngine::VectorInv( const CConstFloatHandle& firstHandle, const CFl
 
 void CB200MathEngine::VectorSigmoid( const CConstFloatHandle& firstHandle, const CFloatHandle& resultHandle, int vectorSize )
 {
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( firstHandle ) == peek( resultHandle ) ) {
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( firstHandle ), CLazyResult::K_Product );
+		if( at >= 0 && lazy[at].gate == 1 && lazy[at].resultFloats == vectorSize ) {
+			lazy[at].gate = 2;
+			return;
+		}
+	}
 	{
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
 		if( pendingGate.active && !pendingGate.sigmoid && raw( firstHandle ) == pendingGate.output
@@ -216,13 +291,33 @@ void CB200MathEngine::AddVectorToMatrixRows( int batchSize, const CConstFloatHan
 		// the mask of attention added to a noted score matrix (see CLazyResult), in place or into another buffer
 		const float* const mask = raw( vectorHandle );
 		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int product = findLazy( peek( matrixHandle ), CLazyResult::K_Product );
+		if( product >= 0 && peek( matrixHandle ) == peek( resultHandle ) && lazy[product].rows == matrixHeight
+			&& lazy[product].width == matrixWidth && lazy[product].bias == nullptr && lazy[product].residual == nullptr
+			&& lazy[product].gate == 0 ) {
+			// ... or the free terms of a fully connected layer added to its noted product
+			lazy[product].bias = mask;
+			lazy[product].Reads( vectorHandle, matrixWidth );
+			return;
+		}
+		const int affine = findLazy( peek( matrixHandle ), CLazyResult::K_Affine );
+		if( affine >= 0 && lazy[affine].rows == matrixHeight && lazy[affine].width == matrixWidth && !lazy[affine].square
+			&& lazy[affine].colAdd == nullptr ) {
+			// ... or the column addends of a noted matrix (the bias of an object normalisation)
+			CLazyResult* note = deriveNote( affine, resultHandle );
+			if( note != nullptr ) {
+				note->colAdd = mask;
+				note->Reads( vectorHandle, matrixWidth );
+				return;
+			}
+		}
 		const int at = findLazy( peek( matrixHandle ), CLazyResult::K_Scores );
 		if( at >= 0 && lazy[at].resultFloats == size && matrixHeight == lazy[at].batch
 			&& matrixWidth == lazy[at].seqQ * lazy[at].seqTo && lazy[at].mask == nullptr && !lazy[at].softmax ) {
-			CLazyResult* note = deriveScores( at, resultHandle );
+			CLazyResult* note = deriveNote( at, resultHandle );
 			if( note != nullptr ) {
 				note->mask = mask;
-				note->inputBases.push_back( CMemoryHandleInternal::Base( vectorHandle ) );
+				note->Reads( vectorHandle, matrixWidth );
 				return;
 			}
 		}
@@ -258,6 +353,25 @@ void CB200MathEngine::AddVectorToMatrixColumns( const CConstFloatHandle& matrixH
 	int matrixHeight, int matrixWidth, const CConstFloatHandle& vectorHandle )
 {
 	enter();
+	const long long size = static_cast<long long>( matrixHeight ) * matrixWidth;
+	const bool inPlace = peek( matrixHandle ) == peek( resultHandle );
+	if( size > 0 && ( inPlace || CMemoryHandleInternal::Base( matrixHandle ) != CMemoryHandleInternal::Base( resultHandle ) )
+		&& CMemoryHandleInternal::Base( vectorHandle ) != CMemoryHandleInternal::Base( resultHandle ) ) {
+		// noted, not written (see CLazyResult) -- CObjectNormalizationLayer squares and sums this matrix (into a
+		// scratch matrix), or scales and shifts it (in place when the layer runs in place); either chain then runs as
+		// one pass.  In place the note's source is the result buffer itself: whoever touches it finds it written.
+		CLazyResult note;
+		note.kind = CLazyResult::K_Affine;
+		note.rowAdd = raw( vectorHandle );
+		note.result = raw( resultHandle );
+		note.from = inPlace ? note.result : raw( matrixHandle );
+		note.resultBase = CMemoryHandleInternal::Base( resultHandle );
+		note.resultFloats = size;
+		note.rows = matrixHeight; note.width = matrixWidth;
+		if( !inPlace ) note.Reads( matrixHandle, size );
+		note.Reads( vectorHandle, matrixHeight );
+		if( noteLazy( note ) ) return;
+	}
 	check( nb200_add_vector_to_matrix_columns( stream, raw( matrixHandle ), raw( resultHandle ), matrixHeight, matrixWidth,
 		raw( vectorHandle ) ), "AddVectorToMatrixColumns" );
 }
@@ -280,6 +394,20 @@ void CB200MathEngine::SumMatrixColumns( const CFloatHandle& resultHandle, const 
 	int matrixWidth )
 {
 	enter();
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) {
+		// the row sums of a noted matrix (a shifted, maybe squared one): one pass over its source
+		float* const sums = raw( resultHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( matrixHandle ), CLazyResult::K_Affine );
+		if( at >= 0 && lazy[at].rows == matrixHeight && lazy[at].width == matrixWidth && lazy[at].rowMul == nullptr
+			&& lazy[at].colMul == nullptr && lazy[at].colAdd == nullptr ) {
+			const CLazyResult& note = lazy[at];
+			check( nb200_sum_matrix_columns_shifted( stream, sums, note.from, matrixHeight, matrixWidth, note.rowAdd,
+				note.square ? 1 : 0 ), "SumMatrixColumns" );
+			for( const CLazyResult::CInput& input : note.inputs ) noteUse( input.base );
+			return;
+		}
+	}
 	check( nb200_sum_matrix_columns( stream, raw( resultHandle ), raw( matrixHandle ), matrixHeight, matrixWidth ), "SumMatrixColumns" );
 }
 
@@ -291,7 +419,7 @@ void CB200MathEngine::MatrixSoftmaxByRows( const CConstFloatHandle& matrix, int 
 		const int at = findLazy( peek( matrix ), CLazyResult::K_Scores );
 		if( at >= 0 && !lazy[at].softmax && width == lazy[at].seqTo
 			&& static_cast<long long>( height ) == static_cast<long long>( lazy[at].batch ) * lazy[at].seqQ ) {
-			CLazyResult* note = deriveScores( at, result );
+			CLazyResult* note = deriveNote( at, result );
 			if( note != nullptr ) {
 				note->softmax = true;
 				return;
@@ -358,6 +486,25 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 	// recorded: the bias that a fully connected layer adds next rides in the epilogue (see CPendingProduct); any other
 	// call launches the product first
 	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	const long long size = static_cast<long long>( firstHeight ) * secondHeight;
+	if( resultRowSize == secondHeight && size > 0 && size < ( 1ll << 31 )
+		&& CMemoryHandleInternal::Base( resultHandle ) != CMemoryHandleInternal::Base( firstHandle )
+		&& CMemoryHandleInternal::Base( resultHandle ) != CMemoryHandleInternal::Base( secondHandle ) ) {
+		// noted, not launched (see CLazyResult): the bias, the residual sum or the GELU gate that the next layers
+		// apply ride in the product's epilogue; whoever else touches the result finds it written
+		CLazyResult note;
+		note.kind = CLazyResult::K_Product;
+		note.first = raw( firstHandle );
+		note.second = raw( secondHandle );
+		note.result = raw( resultHandle );
+		note.resultBase = CMemoryHandleInternal::Base( resultHandle );
+		note.resultFloats = size;
+		note.rows = firstHeight; note.depth = firstWidth; note.width = secondHeight;
+		note.firstRowSize = firstRowSize; note.secondRowSize = secondRowSize;
+		note.Reads( firstHandle, static_cast<long long>( firstHeight - 1 ) * firstRowSize + firstWidth );
+		note.Reads( secondHandle, static_cast<long long>( secondHeight - 1 ) * secondRowSize + firstWidth );
+		if( noteLazy( note ) ) return;
+	}
 	pendingProduct.first = raw( firstHandle );
 	pendingProduct.firstHeight = firstHeight; pendingProduct.firstWidth = firstWidth; pendingProduct.firstRowSize = firstRowSize;
 	pendingProduct.second = raw( secondHandle );
@@ -370,12 +517,19 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 // first * second^T with work space from the stack allocator: a prepared second operand for tall products, room for
 // split-K partial results for products with few output tiles
 int CB200MathEngine::productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
-	const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize, const float* bias ) const
+	const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize, const float* bias,
+	const float* residual, const float* gateScale ) const
 {
 	CB200MathEngine* self = const_cast<CB200MathEngine*>( this );
 	nb200_epilogue withBias = {};
 	withBias.bias = bias;
-	const nb200_epilogue* const epi = bias != nullptr ? &withBias : nullptr;
+	withBias.residual = residual;
+	withBias.ld_residual = resultRowSize;
+	if( gateScale != nullptr ) {
+		withBias.act = NB200_ACT_SIGMOID_GATE;
+		withBias.act_param_device = gateScale;
+	}
+	const nb200_epilogue* const epi = ( bias != nullptr || residual != nullptr || gateScale != nullptr ) ? &withBias : nullptr;
 	const size_t floats = nb200_matrix_product_scratch_floats( batchSize, firstHeight, secondHeight, firstWidth, secondRowSize );
 	if( floats == 0 ) {
 		return nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
@@ -413,7 +567,7 @@ void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHa
 			const CLazyResult& note = lazy[at];
 			if( nb200_attention_scores_values( stream, batchSize, note.first, note.second, values, note.seqQ, note.depth,
 					note.seqTo, note.scale, note.mask, out, precision ) == NB200_OK ) {
-				for( const void* base : note.inputBases ) noteUse( base );
+				for( const CLazyResult::CInput& input : note.inputs ) noteUse( input.base );
 				return;
 			}
 		}
@@ -434,8 +588,8 @@ void CB200MathEngine::MultiplyMatrixByMatrix( int batchSize, const CConstFloatHa
 		note.resultBase = CMemoryHandleInternal::Base( resultHandle );
 		note.resultFloats = scores;
 		note.batch = batchSize; note.seqQ = firstHeight; note.depth = firstWidth; note.seqTo = secondWidth;
-		note.inputBases.push_back( CMemoryHandleInternal::Base( firstHandle ) );
-		note.inputBases.push_back( CMemoryHandleInternal::Base( secondHandle ) );
+		note.Reads( firstHandle, static_cast<long long>( batchSize ) * firstHeight * firstWidth );
+		note.Reads( secondHandle, static_cast<long long>( batchSize ) * firstWidth * secondWidth );
 		if( noteLazy( note ) ) return;
 	}
 	check( launchProduct( batchSize, raw( firstHandle ), firstHeight, firstWidth, raw( secondHandle ), secondWidth,
@@ -469,6 +623,18 @@ void CB200MathEngine::MultiplyDiagMatrixByMatrix( const CConstFloatHandle& first
 	const CConstFloatHandle& secondHandle, int secondWidth, const CFloatHandle& resultHandle, int )
 {
 	enter();
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && peek( secondHandle ) == peek( resultHandle ) ) {
+		// in place on a noted matrix: the row factors join the note
+		const float* const factors = raw( firstHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( secondHandle ), CLazyResult::K_Affine );
+		if( at >= 0 && lazy[at].rows == firstSize && lazy[at].width == secondWidth && !lazy[at].square
+			&& lazy[at].rowMul == nullptr && lazy[at].colMul == nullptr && lazy[at].colAdd == nullptr ) {
+			lazy[at].rowMul = factors;
+			lazy[at].Reads( firstHandle, firstSize );
+			return;
+		}
+	}
 	check( nb200_multiply_diag_matrix_by_matrix( stream, raw( firstHandle ), firstSize, raw( secondHandle ), secondWidth,
 		raw( resultHandle ) ), "MultiplyDiagMatrixByMatrix" );
 }
@@ -480,6 +646,21 @@ void CB200MathEngine::BatchMultiplyMatrixByDiagMatrix( int batchSize, const CCon
 	if( batchSize > 1 && firstMatrixOffset != height * width ) { notImplemented( "BatchMultiplyMatrixByDiagMatrix (strided first operand)" ); return; }
 	if( secondMatrixOffset != 0 && secondMatrixOffset != width ) { notImplemented( "BatchMultiplyMatrixByDiagMatrix (strided diagonal)" ); return; }
 	enter();
+	if( lazyCount.load( std::memory_order_relaxed ) != 0 && batchSize == 1 ) {
+		// a noted matrix times column factors, in place or into another buffer: the factors join the note
+		const float* const factors = raw( secondHandle );
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		const int at = findLazy( peek( firstHandle ), CLazyResult::K_Affine );
+		if( at >= 0 && lazy[at].rows == height && lazy[at].width == width && !lazy[at].square && lazy[at].colMul == nullptr
+			&& lazy[at].colAdd == nullptr ) {
+			CLazyResult* note = deriveNote( at, resultHandle );
+			if( note != nullptr ) {
+				note->colMul = factors;
+				note->Reads( secondHandle, width );
+				return;
+			}
+		}
+	}
 	check( nb200_multiply_matrix_by_diag_matrix( stream, batchSize, raw( firstHandle ), height, width, raw( secondHandle ),
 		secondMatrixOffset, raw( resultHandle ) ), "BatchMultiplyMatrixByDiagMatrix" );
 }

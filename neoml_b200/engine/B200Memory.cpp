@@ -167,6 +167,18 @@ size_t CB200Memory::BlockBytes( const void* ptr ) const
 	return it == live.end() ? 0 : it->second;
 }
 
+size_t CB200Memory::StackBlockBytes( const void* ptr ) const
+{
+	std::lock_guard<std::mutex> lock( mutex );
+	auto it = stacks.find( std::this_thread::get_id() );
+	if( it == stacks.end() ) return 0;
+	const CStack& st = it->second;
+	for( size_t i = st.marks.size(); i-- > 0; ) {
+		if( st.slabs[st.marks[i].slab].first + st.marks[i].offset == ptr ) return st.marks[i].bytes;
+	}
+	return 0;
+}
+
 size_t CB200Memory::FreeOnDevice() const
 {
 	size_t freeBytes = 0, total = 0;

@@ -960,6 +960,200 @@ CDNN_API int cdnn_selftest_attention_chain( void* enginePtr, float* worstError, 
 	} );
 }
 
+// The chains of CObjectNormalizationLayer (ObjectNormalizationLayer.cpp:190-242) on raw engine calls, with its kinds of
+// memory (the row vectors in ONE stack variable, the squared differences in another), in the orders in which a caller
+// may touch the buffers.  An engine may hold the matrix-sized steps back and run each chain as one pass:
+//   0  variance chain: x - mean into a stack matrix, squared in place, row sums; then the stack matrix itself is read
+//   1  output chain: x - mean into the output, * 1/std by rows, * scale by columns, + bias by columns; output read
+//   2  the output chain, but the row vectors are overwritten before the output is read: it shows the old vectors
+//   3  the output chain, the stack variable with the row vectors released before the output is read
+//   4  the output chain in place on x (the layer is an in-place layer), output read
+// Writes the largest difference from a host evaluation with the same single-precision steps, relative to the
+// largest magnitude (0 is expected), and the kernels launched by case 1's four calls plus the read.
+CDNN_API int cdnn_selftest_normalization_chain( void* enginePtr, float* worstError, int* launchesOfCase1 )
+{
+	return guarded( [&] {
+		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
+		const int rows = 37, width = 96;
+		CSplitMix rng( 777 );
+		std::vector<float> x( rows * width ), negMean( rows ), invStd( rows ), scale( width ), bias( width );
+		for( float& v : x ) v = static_cast<float>( rng.uniform() * 4 - 2 );
+		for( float& v : negMean ) v = static_cast<float>( rng.uniform() - 0.5 );
+		for( float& v : invStd ) v = static_cast<float>( rng.uniform() + 0.5 );
+		for( float& v : scale ) v = static_cast<float>( rng.uniform() + 0.5 );
+		for( float& v : bias ) v = static_cast<float>( rng.uniform() - 0.5 );
+		typedef long long ( *TCount )();
+		TCount launchCount = reinterpret_cast<TCount>( dlsym( RTLD_DEFAULT, "nb200_launch_count" ) );
+		double worst = 0;
+		auto compare = [&]( const std::vector<float>& got, const std::vector<float>& want ) {
+			float top = 0;
+			for( float v : want ) top = std::max( top, std::fabs( v ) );
+			for( size_t i = 0; i < got.size(); ++i ) {
+				const double error = std::fabs( got[i] - want[i] ) / top;
+				worst = std::max( worst, error == error ? error : 1e30 );
+			}
+		};
+		std::vector<float> wantSquares( rows * width ), wantSums( rows ), wantOut( rows * width );
+		for( int r = 0; r < rows; ++r ) {
+			for( int c = 0; c < width; ++c ) {
+				volatile float d = x[r * width + c] + negMean[r];
+				volatile float q = d * d;
+				wantSquares[r * width + c] = q;
+				volatile float n = d * invStd[r];
+				volatile float m = n * scale[c];
+				volatile float o = m + bias[c];
+				wantOut[r * width + c] = o;
+			}
+			double sum = 0;
+			for( int c = 0; c < width; ++c ) sum += wantSquares[r * width + c];
+			wantSums[r] = static_cast<float>( sum );
+		}
+		*launchesOfCase1 = -1;
+		CPtr<CDnnBlob> bx = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+		CPtr<CDnnBlob> bscale = CDnnBlob::CreateVector( e, CT_Float, width );
+		CPtr<CDnnBlob> bbias = CDnnBlob::CreateVector( e, CT_Float, width );
+		bx->CopyFrom( x.data() ); bscale->CopyFrom( scale.data() ); bbias->CopyFrom( bias.data() );
+		for( int scenario = 0; scenario < 5; ++scenario ) {
+			CPtr<CDnnBlob> out = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+			out->Fill( -7.f );
+			if( scenario == 4 ) out->CopyFrom( x.data() );
+			std::vector<float> got( rows * width );
+			{
+				CFloatHandleStackVar vectors( e, 2 * rows );
+				const CFloatHandle mean = vectors.GetHandle(), inv = vectors.GetHandle() + rows;
+				e.DataExchangeTyped<float>( mean, negMean.data(), rows );
+				e.DataExchangeTyped<float>( inv, invStd.data(), rows );
+				if( scenario == 0 ) {
+					CFloatHandleStackVar temp( e, rows * width );
+					CFloatHandleStackVar sums( e, rows );
+					e.AddVectorToMatrixColumns( bx->GetData(), temp.GetHandle(), rows, width, mean );
+					e.VectorEltwiseMultiply( temp.GetHandle(), temp.GetHandle(), temp.GetHandle(), rows * width );
+					e.SumMatrixColumns( sums.GetHandle(), temp.GetHandle(), rows, width );
+					std::vector<float> gotSums( rows );
+					e.DataExchangeTyped<float>( gotSums.data(), sums.GetHandle(), rows );
+					// sums of 96 values in another order than the host's: compared to that accuracy
+					float top = 0;
+					for( float v : wantSums ) top = std::max( top, std::fabs( v ) );
+					for( int r = 0; r < rows; ++r ) {
+						const double error = std::fabs( gotSums[r] - wantSums[r] ) / top;
+						worst = std::max( worst, error < 1e-5 ? 0. : error );
+					}
+					e.DataExchangeTyped<float>( got.data(), temp.GetHandle(), rows * width );
+					compare( got, wantSquares );
+					continue;
+				}
+				const long long before = launchCount != nullptr ? launchCount() : 0;
+				e.AddVectorToMatrixColumns( scenario == 4 ? out->GetData() : bx->GetData(), out->GetData(), rows, width, mean );
+				e.MultiplyDiagMatrixByMatrix( inv, rows, out->GetData(), width, out->GetData(), rows * width );
+				e.MultiplyMatrixByDiagMatrix( out->GetData(), rows, width, bscale->GetData(), out->GetData(), rows * width );
+				e.AddVectorToMatrixRows( 1, out->GetData(), out->GetData(), rows, width, bbias->GetData() );
+				if( scenario == 4 ) {
+					out->CopyTo( got.data() );
+					compare( got, wantOut );
+				} else if( scenario == 1 ) {
+					out->CopyTo( got.data() );
+					if( launchCount != nullptr ) *launchesOfCase1 = static_cast<int>( launchCount() - before );
+					compare( got, wantOut );
+				} else if( scenario == 2 ) {
+					e.VectorFill( mean, 100.f, 2 * rows );
+					out->CopyTo( got.data() );
+					compare( got, wantOut );
+				}
+			}
+			if( scenario == 3 ) {
+				CFloatHandleStackVar other( e, 2 * rows ); // lands where the row vectors were
+				e.VectorFill( other.GetHandle(), 100.f, 2 * rows );
+				out->CopyTo( got.data() );
+				compare( got, wantOut );
+			}
+		}
+		*worstError = static_cast<float>( worst );
+	} );
+}
+
+// A fully connected layer's product with what the next layers do to it, on raw engine calls: the free terms added in
+// place (CFullyConnectedLayer), then one of
+//   0  nothing: the biased product is read            1  CGELULayer's fast form into another blob, that blob read
+//   2  the same, then the biased product read as well 3  CEltwiseSumLayer with another tensor into a third blob
+//   4  the sum written over the other tensor          5  only the first step of the gate (x * 1.702), then read
+//   6  the weights overwritten after the layer ran and before anything was read: the old weights count
+// An engine may hold the product back and run bias, sum or gate in its epilogue.  Writes the largest error relative
+// to the RMS of the expected values (double-precision host evaluation).
+CDNN_API int cdnn_selftest_product_chain( void* enginePtr, float* worstError )
+{
+	return guarded( [&] {
+		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
+		const int rows = 200, depth = 96, width = 160;
+		CSplitMix rng( 999 );
+		std::vector<float> x( rows * depth ), w( width * depth ), b( width ), other( rows * width );
+		for( float& v : x ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+		for( float& v : w ) v = static_cast<float>( rng.uniform() * 2 - 1 ) * 0.2f;
+		for( float& v : b ) v = static_cast<float>( rng.uniform() - 0.5 );
+		for( float& v : other ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+		std::vector<double> biased( rows * width ), gated( rows * width ), summed( rows * width ), scaled( rows * width );
+		for( int r = 0; r < rows; ++r ) for( int c = 0; c < width; ++c ) {
+			double sum = b[c];
+			for( int k = 0; k < depth; ++k ) sum += double( x[r * depth + k] ) * w[c * depth + k];
+			biased[r * width + c] = sum;
+			scaled[r * width + c] = sum * 1.702f;
+			gated[r * width + c] = sum / ( 1. + std::exp( -sum * 1.702f ) );
+			summed[r * width + c] = sum + other[r * width + c];
+		}
+		double worst = 0;
+		auto compare = [&]( const CDnnBlob& blob, const std::vector<double>& want ) {
+			std::vector<float> got( static_cast<size_t>( blob.GetDataSize() ) );
+			const_cast<CDnnBlob&>( blob ).CopyTo( got.data() );
+			double square = 0, gap = 0;
+			for( size_t i = 0; i < got.size(); ++i ) { square += want[i] * want[i]; gap = std::max( gap, std::fabs( got[i] - want[i] ) ); }
+			const double error = gap / std::sqrt( square / got.size() );
+			worst = std::max( worst, error == error ? error : 1e30 );
+		};
+		for( int scenario = 0; scenario < 7; ++scenario ) {
+			CPtr<CDnnBlob> bx = CDnnBlob::CreateMatrix( e, CT_Float, rows, depth );
+			CPtr<CDnnBlob> bw = CDnnBlob::CreateMatrix( e, CT_Float, width, depth );
+			CPtr<CDnnBlob> bb = CDnnBlob::CreateVector( e, CT_Float, width );
+			CPtr<CDnnBlob> bo = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+			CPtr<CDnnBlob> product = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+			CPtr<CDnnBlob> second = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+			CPtr<CDnnBlob> factor = CDnnBlob::CreateVector( e, CT_Float, 1 );
+			bx->CopyFrom( x.data() ); bw->CopyFrom( w.data() ); bb->CopyFrom( b.data() ); bo->CopyFrom( other.data() );
+			factor->Fill( 1.702f ); product->Fill( -7.f ); second->Fill( -7.f );
+			const int size = rows * width;
+			e.MultiplyMatrixByTransposedMatrix( bx->GetData(), rows, depth, depth, bw->GetData(), width, depth, product->GetData(), width, size );
+			e.AddVectorToMatrixRows( 1, product->GetData(), product->GetData(), rows, width, bb->GetData() );
+			switch( scenario ) {
+				case 0:
+					compare( *product, biased );
+					break;
+				case 1: case 2:
+					e.VectorMultiply( product->GetData(), second->GetData(), size, factor->GetData() );
+					e.VectorSigmoid( second->GetData(), second->GetData(), size );
+					e.VectorEltwiseMultiply( product->GetData(), second->GetData(), second->GetData(), size );
+					compare( *second, gated );
+					if( scenario == 2 ) compare( *product, biased );
+					break;
+				case 3:
+					e.VectorAdd( product->GetData(), bo->GetData(), second->GetData(), size );
+					compare( *second, summed );
+					break;
+				case 4:
+					e.VectorAdd( bo->GetData(), product->GetData(), bo->GetData(), size );
+					compare( *bo, summed );
+					break;
+				case 5:
+					e.VectorMultiply( product->GetData(), second->GetData(), size, factor->GetData() );
+					compare( *second, scaled );
+					break;
+				case 6:
+					bw->Fill( 3.f );
+					compare( *product, biased );
+					break;
+			}
+		}
+		*worstError = static_cast<float>( worst );
+	} );
+}
+
 // Two distributed engines (CreateDistributedCudaMathEngines on devices[0..1]).  First one AllReduce from two host
 // threads: every element must come out as the mean.  Then, between steps and with no collective in flight, engine 1
 // calls AbortDistributed; the next AllReduce on engine 0 has to end with NeoML's "Stopping due to error in another

@@ -146,6 +146,19 @@ def attention_chain():
     return {"worst_error": worst, "launches_of_the_chain": launches}
 
 
+def normalization_chain():
+    """The object-normalisation chains in every order of touching their buffers (cdnn_selftest_normalization_chain)."""
+    engine = cdnn.Engine("gpu")
+    worst, launches = cdnn.selftest_normalization_chain(engine)
+    return {"worst_error": worst, "launches_of_the_output_chain": launches}
+
+
+def product_chain():
+    """A fully connected product with bias, GELU gate or residual sum in every order of touching the buffers."""
+    engine = cdnn.Engine("gpu")
+    return {"worst_error": cdnn.selftest_product_chain(engine)}
+
+
 def abort_distributed():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     cdnn.load()

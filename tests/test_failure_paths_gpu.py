@@ -68,3 +68,17 @@ def test_attention_scores_that_are_only_noted_are_never_observable():
     row = run_case("attention_chain")
     assert row["worst_error"] < 1e-4, row
     assert row["launches_of_the_chain"] == 1
+
+
+def test_normalisation_steps_that_are_only_noted_are_never_observable():
+    """Shift, square, row sums as one pass; shift, row scale, column scale, column shift as one pass (same roundings as
+    the separate calls); an overwritten or released row vector changes nothing."""
+    row = run_case("normalization_chain")
+    assert row["worst_error"] == 0.0, row
+    assert row["launches_of_the_output_chain"] == 1
+
+
+def test_fully_connected_products_that_are_only_noted_are_never_observable():
+    """Bias, residual sum and the GELU gate ride in the product's epilogue; reading the plain product afterwards,
+    a gate noted in part and overwritten weights all give what the separate calls give."""
+    assert run_case("product_chain")["worst_error"] < 1e-5

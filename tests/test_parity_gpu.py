@@ -591,6 +591,30 @@ def test_attention_chain_refuses_what_it_does_not_cover(ops):
         ops.AttentionScoresValues(q, kt, q)                # depth 32: the separate calls are the way
 
 
+def test_normalisation_passes_equal_the_separate_calls(ops):
+    """nb200_sum_matrix_columns_shifted and nb200_matrix_rows_cols_affine against the calls they stand for, bit for bit."""
+    import ctypes as C
+    lib = ops.capi.load()
+    ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    for rows, width in [(5, 7), (64, 768), (33, 100)]:
+        x = dev(cases.uniform(91, (rows, width)))
+        a, b = dev(cases.uniform(92, (rows,))), dev(cases.uniform(93, (rows,), 0.5, 1.5))
+        c, d = dev(cases.uniform(94, (width,), 0.5, 1.5)), dev(cases.uniform(95, (width,)))
+        shifted = ops.AddVectorToMatrixColumns(x.reshape(-1), a, rows, width)
+        squared = ops.vector_op("ELTWISE_MUL", shifted.reshape(-1), shifted.reshape(-1))
+        for square, src in ((0, shifted), (1, squared)):
+            got = torch.empty(rows, device="cuda")
+            ops.capi.check("sum", lib.nb200_sum_matrix_columns_shifted(None, ptr(got), ptr(x), rows, width, ptr(a), square))
+            assert torch.equal(got, ops.SumMatrixColumns(src.reshape(-1), rows, width))
+        want = ops.MultiplyDiagMatrixByMatrix(b, shifted.reshape(-1), rows, width)
+        want = ops.BatchMultiplyMatrixByDiagMatrix(1, want, rows, width, c, 0)
+        want = ops.AddVectorToMatrixRows(1, want, d, rows, width)
+        got = torch.empty(rows * width, device="cuda")
+        ops.capi.check("affine", lib.nb200_matrix_rows_cols_affine(None, ptr(x), rows, width, ptr(a), 0, ptr(b), ptr(c), ptr(d), ptr(got)))
+        torch.cuda.synchronize()
+        assert torch.equal(got.reshape(-1), want.reshape(-1))
+
+
 def test_padded_max_pool_equals_resize_then_pool(ops, oracle):
     """One pass over the unpadded image against BlobResizeImage followed by BlobMaxPooling on the oracle: bit-exact,
     including a border value above the data (it then wins at the edges) and uneven borders."""
