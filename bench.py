@@ -627,44 +627,58 @@ def run_products(args):
     eff = peak / 2 / (3 if args.precision == 0 else 1)
     dev, prec = "cuda", args.precision
     rnd = lambda *shape: torch.rand(*shape, device=dev) - 0.5
-    cases = []
-    # config 1: one 3x3 convolution, 32x56x56x64 -> 64
-    x1, f1, b1 = rnd(32, 56, 56, 64), rnd(64, 3, 3, 64), rnd(64)
-    cases.append(("cfg1 BlobConvolution 32x56x56x64, 3x3 -> 64", 2.0 * 32 * 56 * 56 * 64 * 576,
-                  lambda: ops.BlobConvolution(x1, f1, b1, padding=(1, 1), precision=prec)))
-    # config 2: MobileNetV2 block 64x56x56x32, expand 192, ReLU6 twice, residual
-    x2, we, wd, wo = torch.rand(64, 56, 56, 32, device=dev), rnd(192, 32), rnd(3, 3, 192), rnd(32, 192) * 0.2
-    be, bd, bo = rnd(192) * 0.2, rnd(192) * 0.2, rnd(32) * 0.2
-    cases.append(("cfg2 MobileNetV2Block 64x56x56x32 (expand 192)", 5.63e9,
-                  lambda: ops.MobileNetV2Block(x2, we, be, wd, bd, wo, bo, stride=1, residual=True)))
+    cases = []   # (name, algorithmic flops, setup): setup() allocates the operands and returns the call to time
+
+    def cfg1():
+        x1, f1, b1 = rnd(32, 56, 56, 64), rnd(64, 3, 3, 64), rnd(64)
+        return lambda: ops.BlobConvolution(x1, f1, b1, padding=(1, 1), precision=prec)
+    cases.append(("cfg1 BlobConvolution 32x56x56x64, 3x3 -> 64", 2.0 * 32 * 56 * 56 * 64 * 576, cfg1))
+
+    def cfg2():
+        x2, we, wd, wo = torch.rand(64, 56, 56, 32, device=dev), rnd(192, 32), rnd(3, 3, 192), rnd(32, 192) * 0.2
+        be, bd, bo = rnd(192) * 0.2, rnd(192) * 0.2, rnd(32) * 0.2
+        return lambda: ops.MobileNetV2Block(x2, we, be, wd, bd, wo, bo, stride=1, residual=True)
+    cases.append(("cfg2 MobileNetV2Block 64x56x56x32 (expand 192)", 5.63e9, cfg2))
+
     # config 4: the FC products of an encoder layer (32768 tokens) and the per-head attention products
     for m, k, n in [(32768, 768, 768), (32768, 768, 3072), (32768, 3072, 768)]:
-        a, b = rnd(m, k), rnd(n, k)
-        cases.append((f"cfg4 MultiplyMatrixByTransposedMatrix {m}x{k} * ({n}x{k})^T", 2.0 * m * k * n,
-                      lambda a=a, b=b: ops.MultiplyMatrixByTransposedMatrix(a, b, precision=prec)))
-    q, kk, sc = rnd(768, 512, 64), rnd(768, 512, 64), torch.empty(768, 512, 512, device=dev)
-    cases.append(("cfg4 QK^T: batch 768, 512x64 * (512x64)^T", 2.0 * 768 * 512 * 512 * 64,
-                  lambda: ops.BatchMultiplyMatrixByTransposedMatrix(q, kk, result=sc, precision=prec)))
-    pr, v, ctx = torch.rand(768, 512, 512, device=dev), rnd(768, 512, 64), torch.empty(768, 512, 64, device=dev)
-    cases.append(("cfg4 PV: batch 768, MultiplyMatrixByMatrix 512x512 * 512x64", 2.0 * 768 * 512 * 512 * 64,
-                  lambda: ops.MultiplyMatrixByMatrix(pr, v, result=ctx, precision=prec)))
+        def fc(m=m, k=k, n=n):
+            a, b = rnd(m, k), rnd(n, k)
+            return lambda: ops.MultiplyMatrixByTransposedMatrix(a, b, precision=prec)
+        cases.append((f"cfg4 MultiplyMatrixByTransposedMatrix {m}x{k} * ({n}x{k})^T", 2.0 * m * k * n, fc))
+
+    def qk():
+        q, kk, sc = rnd(768, 512, 64), rnd(768, 512, 64), torch.empty(768, 512, 512, device=dev)
+        return lambda: ops.BatchMultiplyMatrixByTransposedMatrix(q, kk, result=sc, precision=prec)
+    cases.append(("cfg4 QK^T: batch 768, 512x64 * (512x64)^T", 2.0 * 768 * 512 * 512 * 64, qk))
+
+    def pv():
+        pr, v, ctx = torch.rand(768, 512, 512, device=dev), rnd(768, 512, 64), torch.empty(768, 512, 64, device=dev)
+        return lambda: ops.MultiplyMatrixByMatrix(pr, v, result=ctx, precision=prec)
+    cases.append(("cfg4 PV: batch 768, MultiplyMatrixByMatrix 512x512 * 512x64", 2.0 * 768 * 512 * 512 * 64, pv))
+
     if prec == 0:
-        kt4 = rnd(768, 64, 512)
-        scale4 = torch.full((1,), 0.125, device=dev)
-        mask4 = torch.triu(torch.full((512, 512), -1e9, device=dev), diagonal=1)
-        cases.append(("cfg4 attention chain as one kernel: softmax(scale QK^T + mask) V, batch 768, 512 x 512 x 64",
-                      4.0 * 768 * 512 * 512 * 64,
-                      lambda: ops.AttentionScoresValues(q, kt4, v, scale=scale4, mask=mask4)))
+        for masked in (False, True):
+            def chain(masked=masked):
+                q, kt4, v = rnd(768, 512, 64), rnd(768, 64, 512), rnd(768, 512, 64)
+                scale4 = torch.full((1,), 0.125, device=dev)
+                mask4 = torch.triu(torch.full((512, 512), -1e9, device=dev), diagonal=1) if masked else None
+                return lambda: ops.AttentionScoresValues(q, kt4, v, scale=scale4, mask=mask4)
+            cases.append(("cfg4 attention chain as one kernel: softmax(scale QK^T" + (" + mask" if masked else "")
+                          + ") V, batch 768, 512 x 512 x 64", 4.0 * 768 * 512 * 512 * 64, chain))
+
     # config 5: square MultiplyMatrixByMatrix
     for size in (1024, 4096, 8192):
-        a, b, c = rnd(1, size, size), rnd(1, size, size), torch.empty(1, size, size, device=dev)
-        cases.append((f"cfg5 MultiplyMatrixByMatrix {size}^3", 2.0 * size ** 3,
-                      lambda a=a, b=b, c=c: ops.MultiplyMatrixByMatrix(a, b, result=c, precision=prec)))
+        def square(size=size):
+            a, b, c = rnd(1, size, size), rnd(1, size, size), torch.empty(1, size, size, device=dev)
+            return lambda: ops.MultiplyMatrixByMatrix(a, b, result=c, precision=prec)
+        cases.append((f"cfg5 MultiplyMatrixByMatrix {size}^3", 2.0 * size ** 3, square))
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for name, flops, fn in cases:
+    for name, flops, setup in cases:
         if args.only and args.only not in name:
             continue
-        for _ in range(max(args.warmup, 3)):
+        fn = setup()
+        for _ in range(max(args.warmup, 3) if not args.only else max(args.warmup, 1)):
             fn()
         torch.cuda.synchronize()
         start.record()
@@ -678,6 +692,8 @@ def run_products(args):
                           "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s",
                                        "frac": round(tf / peak, 4), "effective_peak_for_this_arithmetic": round(eff, 1),
                                        "frac_of_effective_peak": round(tf / eff, 3)}}))
+        del fn
+        torch.cuda.empty_cache()
 
 
 def main():

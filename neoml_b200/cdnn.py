@@ -88,6 +88,8 @@ def load():
         lib.cdnn_selftest_abort_distributed.argtypes = [_ip, C.c_char_p, C.c_int]
     if hasattr(lib, "cdnn_selftest_padded_pool"):
         lib.cdnn_selftest_padded_pool.argtypes = [C.c_void_p, _ip, _ip]
+    if hasattr(lib, "cdnn_selftest_random_program"):
+        lib.cdnn_selftest_random_program.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int, _fp, C.c_int]
     if hasattr(lib, "cdnn_selftest_product_chain"):
         lib.cdnn_selftest_product_chain.argtypes = [C.c_void_p, _fp]
     if hasattr(lib, "cdnn_selftest_normalization_chain"):
@@ -291,6 +293,17 @@ def selftest_attention_chain(engine: Engine) -> tuple[float, int]:
     if load().cdnn_selftest_attention_chain(engine.ptr, C.byref(worst), C.byref(launches)) != 0:
         _fail("selftest_attention_chain")
     return worst.value, launches.value
+
+
+RANDOM_PROGRAM_STATE_FLOATS = 6 * 24 * 32 + 4 * 24 + 3 * 32 + 2
+
+
+def selftest_random_program(engine: Engine, seed: int, steps: int):
+    """See cdnn_selftest_random_program: the final contents of all its buffers after `steps` random calls."""
+    state = np.zeros(RANDOM_PROGRAM_STATE_FLOATS, np.float32)
+    if load().cdnn_selftest_random_program(engine.ptr, seed, steps, state.ctypes.data_as(_fp), state.size) != 0:
+        _fail("selftest_random_program")
+    return state
 
 
 def selftest_product_chain(engine: Engine) -> float:

@@ -1154,6 +1154,79 @@ CDNN_API int cdnn_selftest_product_chain( void* enginePtr, float* worstError )
 	} );
 }
 
+// A seeded random program over a handful of small buffers, made of the calls an engine may hold back, note or fuse
+// (the element-wise and row / column broadcast calls, row sums, the fully connected product, copies, fills, frees),
+// with operands chosen at random: in place or not, matrices that come back in later calls, row vectors that share
+// one allocation, buffers released and allocated again in the middle.  Whatever an engine does between the calls, the
+// final contents of every buffer must be those of carrying out each call when it is made; the caller compares the
+// state two engines end in.  `state` receives matrices, then vectors, then scalars (stateFloats in all).
+CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long seed, int steps, float* state, int stateFloats )
+{
+	return guarded( [&] {
+		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
+		const int rows = 24, width = 32, size = rows * width;
+		const int matrices = 6, rowVectors = 4, colVectors = 3, scalars = 2, weights = 2;
+		if( stateFloats != matrices * size + rowVectors * rows + colVectors * width + scalars ) throw std::logic_error( "state size" );
+		CSplitMix rng( seed );
+		auto fill = [&]( CDnnBlob& blob, float low, float high ) {
+			std::vector<float> v( static_cast<size_t>( blob.GetDataSize() ) );
+			for( float& x : v ) x = static_cast<float>( low + ( high - low ) * rng.uniform() );
+			blob.CopyFrom( v.data() );
+		};
+		std::vector<CPtr<CDnnBlob>> m( matrices ), w( weights ), col( colVectors );
+		for( auto& b : m ) { b = CDnnBlob::CreateMatrix( e, CT_Float, rows, width ); fill( *b, -1.f, 1.f ); }
+		for( auto& b : w ) { b = CDnnBlob::CreateMatrix( e, CT_Float, width, width ); fill( *b, -0.3f, 0.3f ); }
+		for( auto& b : col ) { b = CDnnBlob::CreateVector( e, CT_Float, width ); fill( *b, 0.5f, 1.5f ); }
+		// the row vectors live two to a blob (as a normalisation keeps its mean and its 1/sigma), the scalars in one blob
+		CPtr<CDnnBlob> rowPairs[2] = { CDnnBlob::CreateVector( e, CT_Float, 2 * rows ), CDnnBlob::CreateVector( e, CT_Float, 2 * rows ) };
+		fill( *rowPairs[0], 0.5f, 1.5f ); fill( *rowPairs[1], -0.5f, 0.5f );
+		CPtr<CDnnBlob> scalarBlob = CDnnBlob::CreateVector( e, CT_Float, scalars );
+		fill( *scalarBlob, 0.5f, 1.7f );
+		auto rowVec = [&]( int i ) { return rowPairs[i / 2]->GetData() + ( i % 2 ) * rows; };
+		auto scalar = [&]( int i ) { return scalarBlob->GetData() + i; };
+		auto pick = [&]( int n ) { return static_cast<int>( rng.next() % n ); };
+		for( int step = 0; step < steps; ++step ) {
+			const int a = pick( matrices ), b = pick( matrices ), c = pick( matrices );
+			const int r = pick( rowVectors ), k = pick( colVectors ), s = pick( scalars );
+			switch( pick( 15 ) ) {
+				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
+				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
+				case 2:
+					e.SumMatrixColumns( rowVec( r ), m[a]->GetData(), rows, width );
+					e.VectorTanh( rowVec( r ), rowVec( r ), rows );
+					break;
+				case 3: e.MultiplyDiagMatrixByMatrix( rowVec( r ), rows, m[a]->GetData(), width, m[b]->GetData(), size ); break;
+				case 4: e.MultiplyMatrixByDiagMatrix( m[a]->GetData(), rows, width, col[k]->GetData(), m[b]->GetData(), size ); break;
+				case 5: e.AddVectorToMatrixRows( 1, m[a]->GetData(), m[b]->GetData(), rows, width, col[k]->GetData() ); break;
+				case 6: e.VectorMultiply( m[a]->GetData(), m[b]->GetData(), size, scalar( s ) ); break;
+				case 7: e.VectorSigmoid( m[a]->GetData(), m[b]->GetData(), size ); break;
+				case 8: e.VectorAdd( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
+				case 9:
+					if( a != b ) {
+						e.MultiplyMatrixByTransposedMatrix( m[a]->GetData(), rows, width, width, w[pick( weights )]->GetData(), width, width,
+							m[b]->GetData(), width, size );
+					}
+					break;
+				case 10: if( a != b ) e.VectorCopy( m[b]->GetData(), m[a]->GetData(), size ); break;
+				case 11: // released and allocated again: whatever was held back for the old buffer must not land in the new one
+					m[a] = nullptr;
+					m[a] = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+					m[a]->Fill( static_cast<float>( rng.uniform() - 0.5 ) );
+					break;
+				case 12: e.VectorFill( rowVec( r ), static_cast<float>( rng.uniform() + 0.5 ), rows ); break;
+				case 13: e.VectorTanh( m[a]->GetData(), m[a]->GetData(), size ); break;
+				case 14: fill( *w[pick( weights )], -0.3f, 0.3f ); break; // new weights: a product held back must have used the old ones
+			}
+			if( step % 3 == 2 ) e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size ); // keeps magnitudes bounded
+		}
+		float* out = state;
+		for( auto& blob : m ) { blob->CopyTo( out ); out += size; }
+		for( int i = 0; i < 2; ++i ) { rowPairs[i]->CopyTo( out ); out += 2 * rows; }
+		for( auto& blob : col ) { blob->CopyTo( out ); out += width; }
+		scalarBlob->CopyTo( out );
+	} );
+}
+
 // Two distributed engines (CreateDistributedCudaMathEngines on devices[0..1]).  First one AllReduce from two host
 // threads: every element must come out as the mean.  Then, between steps and with no collective in flight, engine 1
 // calls AbortDistributed; the next AllReduce on engine 0 has to end with NeoML's "Stopping due to error in another

@@ -159,6 +159,23 @@ def product_chain():
     return {"worst_error": cdnn.selftest_product_chain(engine)}
 
 
+def random_program():
+    """Seeded random programs of the calls the engine holds back, notes or fuses, on the B200 engine and on the reference
+    CPU engine (the control): the buffers must end in the same state."""
+    gpu, cpu = cdnn.Engine("gpu"), cdnn.Engine("cpu")
+    worst, worst_seed = 0.0, -1
+    for seed in range(40):
+        steps = 20 + 7 * (seed % 9)
+        got = cdnn.selftest_random_program(gpu, 1000 + seed, steps)
+        want = cdnn.selftest_random_program(cpu, 1000 + seed, steps)
+        gap = float(np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want))))
+        if not np.isfinite(gap):
+            gap = 1e30
+        if gap > worst:
+            worst, worst_seed = gap, seed
+    return {"worst_gap": worst, "seed": worst_seed}
+
+
 def abort_distributed():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     cdnn.load()
