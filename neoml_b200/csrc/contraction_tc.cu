@@ -626,9 +626,9 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 		float* biasStrip = reinterpret_cast<float*>(staging + MAX_EPI_WARPS * STAGING_BYTES_PER_WARP) + ew * HALF_COLS;
 		int biasCol = -1;
 		// uniform epilogue options, decided once: the fast store path has no branch per element
-		const bool fastStore = vec && p.accumulate == 0 && p.act != NB200_ACT_HSWISH;
+		const bool fastStore = vec && p.accumulate == 0 && p.act != NB200_ACT_HSWISH && p.act != NB200_ACT_SIGMOID_GATE;
+		const bool gateStore = vec && p.accumulate == 0 && p.act == NB200_ACT_SIGMOID_GATE;
 		const bool clampOn = p.act == NB200_ACT_RELU;
-		const bool gateOn = p.act == NB200_ACT_SIGMOID_GATE;
 		const float actParam = p.act_param_device != nullptr ? __ldg(p.act_param_device) : p.act_param;
 		const float clampHi = actParam > 0.f ? actParam : __int_as_float(0x7f800000);
 		bool ok = true;
@@ -802,10 +802,22 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 							o.y = clampOn ? fminf(fmaxf(o.y, 0.f), clampHi) : o.y;
 							o.z = clampOn ? fminf(fmaxf(o.z, 0.f), clampHi) : o.z;
 							o.w = clampOn ? fminf(fmaxf(o.w, 0.f), clampHi) : o.w;
-							if(gateOn) {
-								o.x = apply_act(o.x, NB200_ACT_SIGMOID_GATE, actParam); o.y = apply_act(o.y, NB200_ACT_SIGMOID_GATE, actParam);
-								o.z = apply_act(o.z, NB200_ACT_SIGMOID_GATE, actParam); o.w = apply_act(o.w, NB200_ACT_SIGMOID_GATE, actParam);
+							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
+							if(m < mEnd) {
+								asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
 							}
+						}
+					} else if(gateStore && colsFull) {
+						// the same with the sigmoid gate as activation: a loop of its own, so that the common one above carries
+						// none of its code (the short-K layers are bound by that loop)
+#pragma unroll
+						for(int i = 0; i < 4; ++i) {
+							const int m = rowBase + 8 * i + rowInGroup;
+							float4 o = ov[i];
+							o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
+							if(useRes) { o.x += res[i].x; o.y += res[i].y; o.z += res[i].z; o.w += res[i].w; }
+							o.x = apply_act(o.x, NB200_ACT_SIGMOID_GATE, actParam); o.y = apply_act(o.y, NB200_ACT_SIGMOID_GATE, actParam);
+							o.z = apply_act(o.z, NB200_ACT_SIGMOID_GATE, actParam); o.w = apply_act(o.w, NB200_ACT_SIGMOID_GATE, actParam);
 							float* dst = C + static_cast<size_t>(m) * p.ldc + n;
 							if(m < mEnd) {
 								asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
