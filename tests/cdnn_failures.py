@@ -176,6 +176,33 @@ def random_program():
     return {"worst_gap": worst, "seed": worst_seed}
 
 
+def launch_counts():
+    """Kernel launches per CDnn::RunOnce: what the engine's run-time fusion leaves of the call sequences NeoML issues.
+    ResNet-50 makes 106 BlobConvolution + 130 element-wise / pooling / resize calls per pass, an encoder layer about 60
+    calls; the counts below are what is launched for them."""
+    from neoml_b200 import resnet50
+    lib = _capi.load()
+    engine = cdnn.Engine("gpu")
+    rng = np.random.default_rng(21)
+    out = {}
+    net = cdnn.Net(engine, cdnn.Model.resnet50(resnet50.make_weights()))
+    net.set_input("in", rng.uniform(0, 1, (32, 224, 224, 3)).astype(np.float32))
+    net.run()
+    before = lib.nb200_launch_count()
+    net.run()
+    out["resnet50_launches_per_pass"] = int(lib.nb200_launch_count() - before)
+    net.close()
+    layers, heads, seq = 2, 2, 128
+    net = cdnn.Net(engine, cdnn.Model.transformer(layers, 64 * heads, heads, 256, seed=3, sigma=0.05, mask=True))
+    net.set_input("in", rng.standard_normal((4, seq, 64 * heads)).astype(np.float32))
+    net.set_input("mask", np.triu(np.ones((seq, seq), np.float32), 1), (1, 1, 1, 1, seq, 1, seq))
+    net.run()
+    before = lib.nb200_launch_count()
+    net.run()
+    out["transformer_launches_per_layer"] = (lib.nb200_launch_count() - before) / layers
+    return out
+
+
 def abort_distributed():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     cdnn.load()

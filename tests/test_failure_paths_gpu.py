@@ -89,3 +89,13 @@ def test_random_programs_end_in_the_state_the_reference_engine_ends_in():
     replaced) leave every buffer as the reference CPU engine leaves it: nothing the engine holds back is observable."""
     row = run_case("random_program")
     assert row["worst_gap"] < 1e-3, row
+
+
+def test_the_fusions_hold_in_a_cdnn():
+    """A regression in the engine's run-time fusion would still give right results, only slower: pin the launch counts.
+    ResNet-50: 54 contractions + stem padding + ONE pooling pass + five small kernels (no separate add, ReLU, resize or
+    per-pass filter preparation).  Encoder layer: six products, one attention kernel, four transposes, and per
+    normalisation two row-sum passes, five vector-sized launches and one normalise-scale-shift pass."""
+    row = run_case("launch_counts")
+    assert row["resnet50_launches_per_pass"] <= 80, row     # 61 at batch 256; small batches add split-K finishing passes
+    assert row["transformer_launches_per_layer"] <= 42, row  # 34 at full size; about 60 calls arrive
