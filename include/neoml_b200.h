@@ -95,6 +95,17 @@ NB200_API size_t nb200_matrix_product_scratch_floats(int batch, int m, int n, in
 NB200_API int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int batch, const float* a, int m,
 	int k, int lda, const float* b, int n, int ldb, float* c, int ldc, float* scratch, const nb200_epilogue* epi,
 	int precision);
+/* The same product (NME.h:529-532, one problem) with the second operand prepared ahead of the call: a fully connected
+ * layer's weights do not change between passes, so their tensor-core form (the lo part of the 3xTF32 split, or the
+ * rounded copy for TF32) is made once -- nb200_matrix_product_prepared_floats(m, n, k, ldb) floats of device memory,
+ * 16-byte aligned, 0 when a product of m rows does not use a prepared operand -- and handed to every call until the
+ * weights change.  `scratch` then only serves split K (NULL allowed); prepared_b == NULL is the call above. */
+NB200_API size_t nb200_matrix_product_prepared_floats(int m, int n, int k, int ldb);
+NB200_API int nb200_matrix_product_prepare_second(void* stream, const float* b, int n, int k, int ldb, float* prepared,
+	int precision);
+NB200_API int nb200_multiply_matrix_by_transposed_matrix_prepared(void* stream, const float* a, int m, int k, int lda,
+	const float* b, int n, int ldb, float* c, int ldc, const float* prepared_b, float* scratch, const nb200_epilogue* epi,
+	int precision);
 /* IBlasEngine::MultiplyMatrixByMatrix (NME.h:580-582): C_b[M x N] = A_b[M x K] * B_b[K x N], dense row-major. */
 NB200_API int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int m, int k,
 	const float* b, int n, float* c, const nb200_epilogue* epi, int precision);

@@ -84,6 +84,9 @@ SIGNATURES = {
     "nb200_find_max_value_in_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "nb200_find_max_value_in_columns": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp]),
     "nb200_blob_max_pooling": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "nb200_matrix_product_prepared_floats": (C.c_size_t, [_i, _i, _i, _i]),
+    "nb200_matrix_product_prepare_second": (_i, [_vp, _vp, _i, _i, _i, _vp, _i]),
+    "nb200_multiply_matrix_by_transposed_matrix_prepared": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _EP, _i]),
     "nb200_sum_matrix_columns_shifted": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i]),
     "nb200_matrix_rows_cols_affine": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "nb200_attention_scores_values": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i]),

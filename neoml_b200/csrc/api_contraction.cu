@@ -275,8 +275,10 @@ size_t nb200_matrix_product_scratch_floats(int batch, int m, int n, int k, int l
 	return floats;
 }
 
-int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int batch, const float* a, int m, int k,
-	int lda, const float* b, int n, int ldb, float* c, int ldc, float* scratch, const nb200_epilogue* epi, int precision)
+// The product behind the three entry points below.  `prepared` (optional, batch 1): the second operand in the form
+// nb200_matrix_product_prepare_second makes, kept by the caller for as long as the operand does not change.
+static int matrix_product(void* stream, int batch, const float* a, int m, int k, int lda, const float* b, int n, int ldb,
+	float* c, int ldc, float* scratch, const float* prepared, const nb200_epilogue* epi, int precision)
 {
 	if(batch < 0 || m < 0 || n < 0 || k <= 0 || lda < k || ldb < k || ldc < n) return NB200_EINVAL;
 	set_call_flops(2.0 * batch * m * n * k);
@@ -290,13 +292,18 @@ int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int ba
 	fill_epilogue(p, epi);
 	if(p.residual == nullptr) p.ldr = ldc;
 	p.a_vec = vec_ok(a, lda, p.strideA); p.b_vec = vec_ok(b, ldb, p.strideB);
-	if(scratch == nullptr || precision == NB200_PREC_FP32_SIMT || batch == 0 || m == 0 || n == 0 || !p.a_vec || !p.b_vec
-		|| static_cast<long long>(batch) * n * ldb > 0x7fffffffLL) {
-		return run(p, batch, stream, precision);
-	}
-	float* rest = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15));
-	const bool prepare = m >= PREPARE_B_MIN_ROWS;
-	if(prepare) {
+	const bool plain = precision == NB200_PREC_FP32_SIMT || batch == 0 || m == 0 || n == 0 || !p.a_vec || !p.b_vec
+		|| static_cast<long long>(batch) * n * ldb > 0x7fffffffLL;
+	if(plain || (scratch == nullptr && prepared == nullptr)) return run(p, batch, stream, precision);
+	float* rest = scratch != nullptr
+		? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 15) & ~static_cast<uintptr_t>(15)) : nullptr;
+	const bool wanted = m >= PREPARE_B_MIN_ROWS;
+	const bool given = wanted && prepared != nullptr && batch == 1 && aligned16(prepared);
+	const bool prepare = wanted && !given && rest != nullptr;
+	if(given) {
+		if(precision == NB200_PREC_3XTF32) p.Blo = prepared; else p.B = prepared;
+		p.b_ready = 1;
+	} else if(prepare) {
 		// one pass over the second operand as it lies in memory (the floats between its rows, if any, are carried along)
 		if(device_status_word() == nullptr) return NB200_ENODEVICE;
 		const long long span = static_cast<long long>(batch - 1) * p.strideB + static_cast<long long>(n - 1) * ldb + k;
@@ -309,15 +316,45 @@ int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int ba
 		p.b_ready = 1;
 		rest += (static_cast<size_t>(batch) * n * ldb + 3) / 4 * 4;
 	}
-	if(batch == 1 && split_scratch_floats(m, n, k) > 0) {
+	if(batch == 1 && rest != nullptr && split_scratch_floats(m, n, k) > 0) {
 		p.splitScratch = rest;
 		p.splitScratchFloats = static_cast<long long>(SPLIT_SCRATCH_FLOATS);
 	}
 	const int rc = run(p, batch, stream, precision);
-	if(rc != NB200_EINVAL || !prepare) return rc;
+	if(rc != NB200_EINVAL || !(prepare || given)) return rc;
 	// the launcher could not describe an operand to TMA after all: in-kernel conversion, unsplit
 	p.B = b; p.Blo = nullptr; p.b_ready = 0; p.splitScratch = nullptr;
 	return run(p, batch, stream, precision);
+}
+
+int nb200_multiply_matrix_by_transposed_matrix_with_scratch(void* stream, int batch, const float* a, int m, int k,
+	int lda, const float* b, int n, int ldb, float* c, int ldc, float* scratch, const nb200_epilogue* epi, int precision)
+{
+	return matrix_product(stream, batch, a, m, k, lda, b, n, ldb, c, ldc, scratch, nullptr, epi, precision);
+}
+
+size_t nb200_matrix_product_prepared_floats(int m, int n, int k, int ldb)
+{
+	if(m < PREPARE_B_MIN_ROWS || n <= 0 || k <= 0 || ldb < k) return 0;
+	return (static_cast<size_t>(n - 1) * ldb + k + 3) / 4 * 4;
+}
+
+int nb200_matrix_product_prepare_second(void* stream, const float* b, int n, int k, int ldb, float* prepared, int precision)
+{
+	if(n <= 0 || k <= 0 || ldb < k || b == nullptr || prepared == nullptr || !aligned16(prepared)) return NB200_EINVAL;
+	if(precision != NB200_PREC_3XTF32 && precision != NB200_PREC_TF32) return NB200_EINVAL;
+	if(device_status_word() == nullptr) return NB200_ENODEVICE;
+	const long long span = static_cast<long long>(n - 1) * ldb + k;
+	prepare_filter_kernel<<<grid_for(span, 256, 8), 256, 0, as_stream(stream)>>>(b, prepared, span,
+		precision == NB200_PREC_3XTF32 ? 0 : 1);
+	count_launch(1);
+	return check_launch();
+}
+
+int nb200_multiply_matrix_by_transposed_matrix_prepared(void* stream, const float* a, int m, int k, int lda, const float* b,
+	int n, int ldb, float* c, int ldc, const float* prepared_b, float* scratch, const nb200_epilogue* epi, int precision)
+{
+	return matrix_product(stream, 1, a, m, k, lda, b, n, ldb, c, ldc, scratch, prepared_b, epi, precision);
 }
 
 int nb200_multiply_matrix_by_matrix(void* stream, int batch, const float* a, int m, int k,

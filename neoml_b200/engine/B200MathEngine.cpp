@@ -140,12 +140,17 @@ bool CB200MathEngine::pendingRefersTo( const void* begin, size_t bytes ) const
 void CB200MathEngine::releaseDeferredFrees() const
 {
 	if( deferredFrees.empty() ) return;
-	std::vector<void*> kept;
-	for( void* p : deferredFrees ) {
-		if( pendingRefersTo( p, memory.BlockBytes( p ) ) || lazyReads( p ) ) kept.push_back( p );
-		else freeBlock( p );
+	std::vector<void*> work;
+	work.swap( deferredFrees ); // what is called below may come back here
+	for( void* p : work ) {
+		if( pendingRefersTo( p, memory.BlockBytes( p ) ) || lazyReads( p ) ) {
+			deferredFrees.push_back( p );
+		} else {
+			// a noted call may have prepared an operand from this block after its owner released it
+			if( !preparedFilters.empty() ) forgetPreparedFilter( p );
+			freeBlock( p );
+		}
 	}
-	deferredFrees.swap( kept );
 }
 
 //---------------------------------------------------------------------------------------------------------------------
@@ -197,8 +202,8 @@ void CB200MathEngine::materializeLazy( size_t index ) const
 	} else if( note.kind == CLazyResult::K_Product ) {
 		// the epilogue carries bias, residual and the complete gate; a gate noted in part runs as the calls it was
 		check( productWithScratch( 1, note.first, note.rows, note.depth, note.firstRowSize, note.second, note.width,
-			note.secondRowSize, note.result, note.width, note.bias, note.residual, note.gate == 3 ? note.gateScale : nullptr ),
-			"MultiplyMatrixByTransposedMatrix" );
+			note.secondRowSize, note.result, note.width, note.bias, note.residual, note.gate == 3 ? note.gateScale : nullptr,
+			note.inputs.size() > 1 ? note.inputs[1].base : nullptr ), "MultiplyMatrixByTransposedMatrix" );
 		if( note.gate == 1 || note.gate == 2 ) {
 			check( nb200_vector_op( stream, NB200_VEC_MULTIPLY, note.result, nullptr, note.gateScale, 0.f, note.result,
 				static_cast<int>( note.resultFloats ) ), "VectorMultiply" );
@@ -434,8 +439,43 @@ const float* CB200MathEngine::preparedFilterFor( const CPendingConvolution& call
 	return f.data;
 }
 
+const float* CB200MathEngine::preparedSecondFor( const void* allocationBase, const float* second, int rows, int secondHeight,
+	int depth, int secondRowSize ) const
+{
+	if( allocationBase == nullptr || memory.BlockBytes( allocationBase ) == 0 ) return nullptr; // end of life not seen
+	const size_t floats = nb200_matrix_product_prepared_floats( rows, secondHeight, depth, secondRowSize );
+	if( floats == 0 ) return nullptr;
+	std::lock_guard<std::mutex> lock( preparedMutex );
+	auto it = preparedFilters.find( allocationBase );
+	if( it != preparedFilters.end() ) {
+		const CPreparedFilter& f = it->second;
+		if( f.filter == second && f.k == secondHeight && f.r == -1 && f.s == secondRowSize && f.c == depth ) return f.data;
+		freeBlock( f.data ); // the allocation now serves another operand
+		preparedFilters.erase( it );
+	}
+	CPreparedFilter f;
+	f.filter = second;
+	f.k = secondHeight; f.r = -1; f.s = secondRowSize; f.c = depth; // r = -1 marks a matrix operand
+	f.data = static_cast<float*>( memory.Alloc( floats * sizeof( float ) ) );
+	if( f.data == nullptr ) return nullptr; // no room: the call prepares into its scratch as before
+	if( nb200_matrix_product_prepare_second( stream, second, secondHeight, depth, secondRowSize, f.data, precision ) != NB200_OK ) {
+		memory.Free( f.data );
+		return nullptr;
+	}
+	preparedFilters.emplace( allocationBase, f );
+	return f.data;
+}
+
 void CB200MathEngine::forgetPreparedFilter( const void* allocationBase ) const
 {
+	{
+		// a recorded convolution that is about to use the prepared form is launched first, with the old contents
+		std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+		if( pending.active && pending.filterAllocation == allocationBase ) {
+			cudaSetDevice( device );
+			flushPending();
+		}
+	}
 	std::lock_guard<std::mutex> lock( preparedMutex );
 	auto it = preparedFilters.find( allocationBase );
 	if( it == preparedFilters.end() ) return;
@@ -611,8 +651,8 @@ void CB200MathEngine::DataExchangeRaw( const CMemoryHandle& result, const void* 
 	if( result.GetMathEngine() != this ) { raiseAssert( "DataExchangeRaw: the handle belongs to another math engine" ); return; }
 	enter();
 	const void* base = CMemoryHandleInternal::Base( result );
-	if( !preparedFilters.empty() ) forgetPreparedFilter( base );
 	if( lazyCount.load( std::memory_order_relaxed ) != 0 ) touchLazy( base, CMemoryHandleInternal::GetRaw( result ), true );
+	if( !preparedFilters.empty() ) forgetPreparedFilter( base ); // after whatever still needed the old contents has run
 	cudaStream_t s = static_cast<cudaStream_t>( stream );
 	void* const destination = CMemoryHandleInternal::GetRaw( result );
 	// A large exchange into a heap block that nothing queued can touch overlaps the kernels in flight (see noteUse)

@@ -129,11 +129,12 @@ private:
 	template<class T> T* raw( const CTypedMemoryHandle<T>& h ) const
 	{
 		if( !h.IsNull() && h.GetMathEngine() != this ) notImplemented( "use of a handle that belongs to another math engine" );
-		if( !std::is_const<T>::value && !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( h ) );
 		if( !h.IsNull() ) noteUse( CMemoryHandleInternal::Base( h ) );
 		if( lazyCount.load( std::memory_order_relaxed ) != 0 && !h.IsNull() ) {
 			touchLazy( CMemoryHandleInternal::Base( h ), CMemoryHandleInternal::GetRaw( h ), !std::is_const<T>::value );
 		}
+		// last: what was held back for this allocation has now been launched with the prepared form of the old contents
+		if( !std::is_const<T>::value && !preparedFilters.empty() ) forgetPreparedFilter( CMemoryHandleInternal::Base( h ) );
 		return CMemoryHandleInternal::GetRaw( h );
 	}
 	// the pointer alone: for a method that first looks whether its operand is a result noted below
@@ -274,7 +275,8 @@ private:
 		int secondWidth, float* result ) const;
 	int productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
 		const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize,
-		const float* bias = nullptr, const float* residual = nullptr, const float* gateScale = nullptr ) const;
+		const float* bias = nullptr, const float* residual = nullptr, const float* gateScale = nullptr,
+		const void* secondAllocation = nullptr ) const;
 	mutable std::recursive_mutex pendingMutex;
 	// NeoML frees a layer's input blobs right after its RunOnce (reuse-memory mode), i.e. possibly while a recorded
 	// call still refers to them.  Such a heap block goes back to the pool only after the recorded call has been
@@ -294,6 +296,9 @@ private:
 	mutable std::unordered_map<const void*, CPreparedFilter> preparedFilters;
 	mutable std::mutex preparedMutex;
 	const float* preparedFilterFor( const CPendingConvolution& call ) const;
+	// the same for the second operand (the weights) of a fully connected product of `rows` rows
+	const float* preparedSecondFor( const void* allocationBase, const float* second, int rows, int secondHeight, int depth,
+		int secondRowSize ) const;
 	void forgetPreparedFilter( const void* allocationBase ) const;
 	void forgetAllPreparedFilters() const;
 	// allocation base of every conv filter handle, noted at the call (raw pointers carry no allocation)

@@ -518,7 +518,7 @@ void CB200MathEngine::MultiplyMatrixByTransposedMatrix( const CConstFloatHandle&
 // split-K partial results for products with few output tiles
 int CB200MathEngine::productWithScratch( int batchSize, const float* first, int firstHeight, int firstWidth, int firstRowSize,
 	const float* second, int secondHeight, int secondRowSize, float* result, int resultRowSize, const float* bias,
-	const float* residual, const float* gateScale ) const
+	const float* residual, const float* gateScale, const void* secondAllocation ) const
 {
 	CB200MathEngine* self = const_cast<CB200MathEngine*>( this );
 	nb200_epilogue withBias = {};
@@ -530,15 +530,21 @@ int CB200MathEngine::productWithScratch( int batchSize, const float* first, int 
 		withBias.act_param_device = gateScale;
 	}
 	const nb200_epilogue* const epi = ( bias != nullptr || residual != nullptr || gateScale != nullptr ) ? &withBias : nullptr;
+	// a layer's weights are prepared for the tensor core once and kept for as long as nothing writes to them
+	const float* prepared = batchSize == 1 && secondAllocation != nullptr
+		? preparedSecondFor( secondAllocation, second, firstHeight, secondHeight, firstWidth, secondRowSize ) : nullptr;
 	const size_t floats = nb200_matrix_product_scratch_floats( batchSize, firstHeight, secondHeight, firstWidth, secondRowSize );
 	if( floats == 0 ) {
 		return nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
 			firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize, nullptr, epi, precision );
 	}
 	CMemoryHandle scratch = self->StackAlloc( floats * sizeof( float ) );
-	const int rc = nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
-		firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize,
-		static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) ), epi, precision );
+	float* const room = static_cast<float*>( CMemoryHandleInternal::GetRaw( scratch ) );
+	const int rc = prepared != nullptr
+		? nb200_multiply_matrix_by_transposed_matrix_prepared( stream, first, firstHeight, firstWidth, firstRowSize, second,
+			secondHeight, secondRowSize, result, resultRowSize, prepared, room, epi, precision )
+		: nb200_multiply_matrix_by_transposed_matrix_with_scratch( stream, batchSize, first, firstHeight, firstWidth,
+			firstRowSize, second, secondHeight, secondRowSize, result, resultRowSize, room, epi, precision );
 	self->StackFree( scratch ); // stream order keeps the kernels ahead of the next user of the stack
 	return rc;
 }

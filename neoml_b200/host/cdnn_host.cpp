@@ -1077,6 +1077,7 @@ CDNN_API int cdnn_selftest_normalization_chain( void* enginePtr, float* worstErr
 //   2  the same, then the biased product read as well 3  CEltwiseSumLayer with another tensor into a third blob
 //   4  the sum written over the other tensor          5  only the first step of the gate (x * 1.702), then read
 //   6  the weights overwritten after the layer ran and before anything was read: the old weights count
+// and a 1024-row layer run three times with its weights replaced in between (by a host copy, by a device-side fill).
 // An engine may hold the product back and run bias, sum or gate in its epilogue.  Writes the largest error relative
 // to the RMS of the expected values (double-precision host evaluation).
 CDNN_API int cdnn_selftest_product_chain( void* enginePtr, float* worstError )
@@ -1148,6 +1149,39 @@ CDNN_API int cdnn_selftest_product_chain( void* enginePtr, float* worstError )
 					bw->Fill( 3.f );
 					compare( *product, biased );
 					break;
+			}
+		}
+		// A layer of 1024 rows (an engine may keep a prepared form of the weights from pass to pass): three passes, the
+		// weights replaced by a host copy before the second and by a device-side fill before the third.
+		{
+			const int tall = 1024;
+			std::vector<float> xs( tall * depth );
+			for( float& v : xs ) v = static_cast<float>( rng.uniform() * 2 - 1 );
+			CPtr<CDnnBlob> bx = CDnnBlob::CreateMatrix( e, CT_Float, tall, depth );
+			CPtr<CDnnBlob> bw = CDnnBlob::CreateMatrix( e, CT_Float, width, depth );
+			CPtr<CDnnBlob> bb = CDnnBlob::CreateVector( e, CT_Float, width );
+			bx->CopyFrom( xs.data() ); bb->CopyFrom( b.data() );
+			std::vector<float> weightsOfPass = w;
+			for( int pass = 0; pass < 3; ++pass ) {
+				if( pass == 1 ) for( float& v : weightsOfPass ) v = -0.5f * v;
+				if( pass == 2 ) {
+					for( float& v : weightsOfPass ) v = 0.01f;
+					e.VectorFill( bw->GetData(), 0.01f, bw->GetDataSize() );
+				} else {
+					bw->CopyFrom( weightsOfPass.data() );
+				}
+				CPtr<CDnnBlob> product = CDnnBlob::CreateMatrix( e, CT_Float, tall, width );
+				product->Fill( -7.f );
+				e.MultiplyMatrixByTransposedMatrix( bx->GetData(), tall, depth, depth, bw->GetData(), width, depth, product->GetData(),
+					width, tall * width );
+				e.AddVectorToMatrixRows( 1, product->GetData(), product->GetData(), tall, width, bb->GetData() );
+				std::vector<double> want( static_cast<size_t>( tall ) * width );
+				for( int r = 0; r < tall; ++r ) for( int c = 0; c < width; ++c ) {
+					double sum = b[c];
+					for( int k = 0; k < depth; ++k ) sum += double( xs[r * depth + k] ) * weightsOfPass[c * depth + k];
+					want[static_cast<size_t>( r ) * width + c] = sum;
+				}
+				compare( *product, want );
 			}
 		}
 		*worstError = static_cast<float>( worst );

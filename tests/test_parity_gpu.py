@@ -591,6 +591,30 @@ def test_attention_chain_refuses_what_it_does_not_cover(ops):
         ops.AttentionScoresValues(q, kt, q)                # depth 32: the separate calls are the way
 
 
+def test_product_with_a_prepared_second_operand_equals_the_plain_call(ops):
+    """nb200_multiply_matrix_by_transposed_matrix_prepared against the call that prepares per call: the same bits, with
+    bias in the epilogue, for both precisions; short products report that they use no prepared operand."""
+    import ctypes as C
+    lib = ops.capi.load()
+    ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    assert lib.nb200_matrix_product_prepared_floats(512, 96, 64, 64) == 0
+    for m, k, n, prec in [(2048, 192, 160, ops.PREC_3XTF32), (1024, 64, 256, ops.PREC_TF32), (1500, 96, 100, ops.PREC_3XTF32)]:
+        a, b, bias = dev(cases.uniform(96, (m, k))), dev(cases.uniform(97, (n, k))), dev(cases.uniform(98, (n,)))
+        want = ops.MultiplyMatrixByTransposedMatrix(a, b, free_term=bias, precision=prec)
+        floats = lib.nb200_matrix_product_prepared_floats(m, n, k, k)
+        assert floats >= n * k
+        prepared = torch.empty(floats, device="cuda")
+        ops.capi.check("prepare", lib.nb200_matrix_product_prepare_second(None, ptr(b), n, k, k, ptr(prepared), prec))
+        scratch = torch.empty(lib.nb200_matrix_product_scratch_floats(1, m, n, k, k) + 16, device="cuda")
+        got = torch.full((m, n), float("nan"), device="cuda")
+        epi = ops.capi.Epilogue(bias.data_ptr(), None, 0, ops.ACT_NONE, 0.0, 0, None)
+        for _ in range(2):      # the prepared operand serves any number of calls
+            ops.capi.check("product", lib.nb200_multiply_matrix_by_transposed_matrix_prepared(
+                None, ptr(a), m, k, k, ptr(b), n, k, ptr(got), n, ptr(prepared), ptr(scratch), C.byref(epi), prec))
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), (m, k, n, prec)
+
+
 def test_normalisation_passes_equal_the_separate_calls(ops):
     """nb200_sum_matrix_columns_shifted and nb200_matrix_rows_cols_affine against the calls they stand for, bit for bit."""
     import ctypes as C
