@@ -18,7 +18,7 @@ same CDnn on the reference's own CPU math engine (oracle/_ref: NeoML and NeoMath
 per host thread on slices of the same 256-image batch.
 
 Other modes: --sweep (per-GPU batch 1/32/256/1024 on 1/2/4/8 engines of ONE process made by NeoML's
-CreateDistributedCudaMathEngines, one host thread per engine), --transformer (configuration 4 as a CDnn), --ops and
+CreateDistributedCudaMathEngines, one host thread per engine; plain and double-buffered input loop), --transformer (configuration 4 as a CDnn), --ops and
 --products (kernel-level figures at the configurations' sizes).
 """
 from __future__ import annotations
@@ -469,18 +469,27 @@ def run_sweep(args):
         for b in batches:
             for i in range(n):
                 reps.net(i).set_input_ptr("in", x.data_ptr(), (1, b, 1, IMAGE[0], IMAGE[1], 1, IMAGE[2]))
-            steps = {1: 200, 32: 60, 256: args.steps, 1024: max(4, args.steps // 4)}[b]
+            steps = {1: 200, 32: 60, 256: args.steps, 1024: max(4, args.steps // 2)}[b]
             per_out = b * (resnet50.CLASSES + 1) * 4
             secs = reps.time_steps(max(args.warmup, 3), steps, "in", x.data_ptr(), 0, "probs,argmax", out.data_ptr(), per_out)
+            secs2 = reps.time_steps(max(args.warmup, 3), steps, "in", x.data_ptr(), 0, "probs,argmax", out.data_ptr(), per_out,
+                                    double_buffered=True)
             row = {"mode": "sweep", "engines": n, "per_gpu_batch": b, "steps": steps,
                    "images_per_s": round(n * b * steps / secs, 1), "ms_per_step": round(1e3 * secs / steps, 3),
-                   "call": "CreateDistributedCudaMathEngines, one host thread per engine, host buffers in and out"}
+                   "double_buffered_images_per_s": round(n * b * steps / secs2, 1),
+                   "double_buffered_ms_per_step": round(1e3 * secs2 / steps, 3),
+                   "call": "CreateDistributedCudaMathEngines, one host thread per engine, host buffers in and out; "
+                           "double_buffered: the input copy of step i+1 is issued before the results of step i are read"}
             rows.append(row)
             print(json.dumps(row), flush=True)
         reps.close()
     base = {r["per_gpu_batch"]: r["images_per_s"] for r in rows if r["engines"] == 1}
+    base2 = {r["per_gpu_batch"]: r["double_buffered_images_per_s"] for r in rows if r["engines"] == 1}
     print(json.dumps({"mode": "sweep_summary", "scaling_vs_one_engine": {
-        f"b{r['per_gpu_batch']}_x{r['engines']}": round(r["images_per_s"] / base[r["per_gpu_batch"]], 3) for r in rows}}))
+        f"b{r['per_gpu_batch']}_x{r['engines']}": round(r["images_per_s"] / base[r["per_gpu_batch"]], 3) for r in rows},
+        "double_buffered_scaling_vs_one_engine": {
+        f"b{r['per_gpu_batch']}_x{r['engines']}": round(r["double_buffered_images_per_s"] / base2[r["per_gpu_batch"]], 3)
+        for r in rows}}))
 
 
 def run_transformer(args):

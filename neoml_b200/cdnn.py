@@ -80,9 +80,10 @@ def load():
     lib.cdnn_replicas_destroy.argtypes = [C.c_void_p]
     lib.cdnn_replicas_net.restype = C.c_void_p
     lib.cdnn_replicas_net.argtypes = [C.c_void_p, C.c_int]
-    lib.cdnn_replicas_time_steps.restype = C.c_double
-    lib.cdnn_replicas_time_steps.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_char_p, C.c_void_p, C.c_longlong,
-                                             C.c_char_p, C.c_void_p, C.c_longlong]
+    for fn in (lib.cdnn_replicas_time_steps, lib.cdnn_replicas_time_steps_double_buffered):
+        fn.restype = C.c_double
+        fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_char_p, C.c_void_p, C.c_longlong,
+                       C.c_char_p, C.c_void_p, C.c_longlong]
     if hasattr(lib, "cdnn_selftest_free_while_pending"):
         lib.cdnn_selftest_free_while_pending.argtypes = [C.c_void_p, _fp]
         lib.cdnn_selftest_abort_distributed.argtypes = [_ip, C.c_char_p, C.c_int]
@@ -348,11 +349,15 @@ class Replicas:
         return Net(None, None, _ptr_=load().cdnn_replicas_net(self.ptr, i))
 
     def time_steps(self, warmup: int, steps: int, source: str, inputs_ptr: int, input_floats_per_replica: int,
-                   sink: str, outputs_ptr: int, output_bytes_per_replica: int) -> float:
-        t = load().cdnn_replicas_time_steps(self.ptr, warmup, steps, source.encode(),
-                                            C.c_void_p(inputs_ptr) if inputs_ptr else None, input_floats_per_replica,
-                                            sink.encode(), C.c_void_p(outputs_ptr) if outputs_ptr else None,
-                                            output_bytes_per_replica)
+                   sink: str, outputs_ptr: int, output_bytes_per_replica: int, double_buffered: bool = False) -> float:
+        """Seconds until the last replica finished `steps` x (host -> source blob, RunOnce, sink -> host), all replicas
+        started together on one thread each.  double_buffered: every replica issues the input copy of step i+1
+        before it reads the results of step i."""
+        fn = load().cdnn_replicas_time_steps_double_buffered if double_buffered else load().cdnn_replicas_time_steps
+        t = fn(self.ptr, warmup, steps, source.encode(),
+               C.c_void_p(inputs_ptr) if inputs_ptr else None, input_floats_per_replica,
+               sink.encode(), C.c_void_p(outputs_ptr) if outputs_ptr else None,
+               output_bytes_per_replica)
         if t < 0:
             _fail("replicas time_steps")
         return t

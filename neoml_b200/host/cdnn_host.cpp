@@ -686,8 +686,27 @@ CDNN_API void* cdnn_replicas_net( void* replicas, int index )
 // Every replica, on its own host thread, runs `steps` x ( host -> source, RunOnce, sink -> host ) on its slice:
 // replica i reads inputs + i * inputFloatsPerReplica and writes outputs + i * outputBytesPerReplica.  All threads
 // start together; returns the wall-clock seconds until the last one finished (after `warmup` untimed steps each).
+static double replicasTimeSteps( void* replicas, int warmup, int steps, const char* sourceName, const float* inputs,
+	long long inputFloatsPerReplica, const char* sinkName, char* outputs, long long outputBytesPerReplica, bool doubleBuffered );
+
 CDNN_API double cdnn_replicas_time_steps( void* replicas, int warmup, int steps, const char* sourceName, const float* inputs,
 	long long inputFloatsPerReplica, const char* sinkName, char* outputs, long long outputBytesPerReplica )
+{
+	return replicasTimeSteps( replicas, warmup, steps, sourceName, inputs, inputFloatsPerReplica, sinkName, outputs,
+		outputBytesPerReplica, false );
+}
+
+// The same with every replica's input double-buffered (two blobs alternate as the source layer's blob; the copy of
+// step i + 1 is issued right after RunOnce of step i): the loop of a caller that hides its input copy.
+CDNN_API double cdnn_replicas_time_steps_double_buffered( void* replicas, int warmup, int steps, const char* sourceName,
+	const float* inputs, long long inputFloatsPerReplica, const char* sinkName, char* outputs, long long outputBytesPerReplica )
+{
+	return replicasTimeSteps( replicas, warmup, steps, sourceName, inputs, inputFloatsPerReplica, sinkName, outputs,
+		outputBytesPerReplica, true );
+}
+
+static double replicasTimeSteps( void* replicas, int warmup, int steps, const char* sourceName, const float* inputs,
+	long long inputFloatsPerReplica, const char* sinkName, char* outputs, long long outputBytesPerReplica, bool doubleBuffered )
 {
 	CReplicas* r = static_cast<CReplicas*>( replicas );
 	const int n = static_cast<int>( r->nets.size() );
@@ -701,14 +720,16 @@ CDNN_API double cdnn_replicas_time_steps( void* replicas, int warmup, int steps,
 			SetMathEngineExceptionHandler( GetExceptionHandler() );
 			const float* in = inputs != nullptr ? inputs + i * inputFloatsPerReplica : nullptr;
 			char* out = outputs != nullptr ? outputs + i * outputBytesPerReplica : nullptr;
-			if( warmup > 0 && cdnn_net_time_steps( r->nets[i].get(), warmup, sourceName, in, sinkName, out, outputBytesPerReplica ) < 0 ) {
-				errors[i] = lastError;
-			}
+			// the warm-up runs the loop that is timed, so that the engine's pools hold that loop's blocks
+			const auto run = [&]( int count ) {
+				return doubleBuffered ? cdnn_net_time_steps_double_buffered( r->nets[i].get(), count, sourceName, in, 0, sinkName, out, 0,
+					outputBytesPerReplica )
+					: cdnn_net_time_steps( r->nets[i].get(), count, sourceName, in, sinkName, out, outputBytesPerReplica );
+			};
+			if( warmup > 0 && run( warmup ) < 0 ) errors[i] = lastError;
 			ready.fetch_add( 1 );
 			while( !go.load() ) std::this_thread::yield();
-			if( errors[i].empty() && cdnn_net_time_steps( r->nets[i].get(), steps, sourceName, in, sinkName, out, outputBytesPerReplica ) < 0 ) {
-				errors[i] = lastError;
-			}
+			if( errors[i].empty() && run( steps ) < 0 ) errors[i] = lastError;
 			finished[i] = std::chrono::steady_clock::now();
 		} );
 	}
