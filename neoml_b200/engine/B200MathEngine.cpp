@@ -270,6 +270,9 @@ CB200MathEngine::CLazyResult* CB200MathEngine::deriveNote( int sourceNote, const
 	const float* const source = lazy[sourceNote].result;
 	if( peek( resultHandle ) == source ) return &lazy[sourceNote];
 	CLazyResult copy = lazy[sourceNote];
+	// A note made in place reads the buffer it will write, and that buffer is not among its inputs: a copy of it for
+	// another buffer would read the source before or after the in-place result lands, whichever is touched first.
+	if( copy.kind == CLazyResult::K_Affine && copy.from == copy.result ) return nullptr;
 	const void* base = CMemoryHandleInternal::Base( resultHandle );
 	if( base == copy.resultBase || ( memory.BlockBytes( base ) == 0 && memory.StackBlockBytes( base ) == 0 ) ) return nullptr;
 	for( const CLazyResult::CInput& input : copy.inputs ) {

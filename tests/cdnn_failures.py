@@ -164,10 +164,11 @@ def random_program():
     CPU engine (the control): the buffers must end in the same state."""
     gpu, cpu = cdnn.Engine("gpu"), cdnn.Engine("cpu")
     worst, worst_seed = 0.0, -1
-    for seed in range(40):
-        steps = 20 + 7 * (seed % 9)
-        got = cdnn.selftest_random_program(gpu, 1000 + seed, steps)
-        want = cdnn.selftest_random_program(cpu, 1000 + seed, steps)
+    # the second range holds the programs that once caught a copy of an in-place note reading its source too late
+    programs = [(1000 + i, 20 + 7 * (i % 9)) for i in range(40)] + [(5000 + i, 15 + 11 * (i % 13)) for i in range(600)]
+    for seed, steps in programs:
+        got = cdnn.selftest_random_program(gpu, seed, steps)
+        want = cdnn.selftest_random_program(cpu, seed, steps)
         gap = float(np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want))))
         if not np.isfinite(gap):
             gap = 1e30
