@@ -163,15 +163,31 @@ bool CB200MathEngine::noteLazy( const CLazyResult& note ) const
 		return false;
 	}
 	std::lock_guard<std::recursive_mutex> lock( pendingMutex );
+	flushRecorded();
 	lazy.push_back( note );
 	lazyCount.store( static_cast<int>( lazy.size() ), std::memory_order_relaxed );
 	return true;
 }
 
+void CB200MathEngine::flushRecorded() const
+{
+	if( !anythingRecorded() ) return;
+	cudaSetDevice( device );
+	flushPending();
+	flushProduct();
+	flushRowOps();
+	flushGate();
+}
+
+// Whoever finds a note is about to extend it, copy it or consume it: nothing stays recorded across that (see
+// flushRecorded; launching recorded calls leaves the notes as they are, so the index stays good).
 int CB200MathEngine::findLazy( const void* result, CLazyResult::TKind kind ) const
 {
 	for( size_t i = 0; i < lazy.size(); ++i ) {
-		if( lazy[i].result == result && lazy[i].kind == kind ) return static_cast<int>( i );
+		if( lazy[i].result == result && lazy[i].kind == kind ) {
+			flushRecorded();
+			return static_cast<int>( i );
+		}
 	}
 	return -1;
 }

@@ -203,6 +203,11 @@ private:
 	mutable CPendingSigmoidGate pendingGate;
 	void flushGate() const;
 	bool anythingRecorded() const { return pending.active || pendingRows.active || pendingProduct.active || pendingGate.active; }
+	// Launches every recorded call.  A note is made, copied or extended only with nothing recorded: a noted result is
+	// written when somebody touches it, which may be before the next call's enter(), and a call recorded BEFORE the
+	// note may still read what the note will write, or write what it will read.  (A call recorded AFTER a note has
+	// resolved its operands through raw(), so it has met the note already.)
+	void flushRecorded() const;
 	// Results that are noted, not computed.  BlobResizeImage with constant padding, and the score chain of attention
 	// (a batched MultiplyMatrixByMatrix, then in place VectorMultiply / AddVectorToMatrixRows / MatrixSoftmaxByRows)
 	// only note what they would write.  The consumer that usually follows -- BlobMaxPooling over the padded image,

@@ -1243,7 +1243,8 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 		for( int step = 0; step < steps; ++step ) {
 			const int a = pick( matrices ), b = pick( matrices ), c = pick( matrices );
 			const int r = pick( rowVectors ), k = pick( colVectors ), s = pick( scalars );
-			switch( pick( 15 ) ) {
+			// seeds from 1 000 000 on also draw the composite steps 15..19 (smaller seeds keep the programs they always made)
+			switch( pick( seed >= 1000000ull ? 20 : 15 ) ) {
 				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
 				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
 				case 2:
@@ -1271,6 +1272,51 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 				case 12: e.VectorFill( rowVec( r ), static_cast<float>( rng.uniform() + 0.5 ), rows ); break;
 				case 13: e.VectorTanh( m[a]->GetData(), m[a]->GetData(), size ); break;
 				case 14: fill( *w[pick( weights )], -0.3f, 0.3f ); break; // new weights: a product held back must have used the old ones
+				case 15: // a fully connected layer: product, free terms in place, maybe the sum with another tensor
+					if( a != b ) {
+						e.MultiplyMatrixByTransposedMatrix( m[a]->GetData(), rows, width, width, w[pick( weights )]->GetData(), width, width,
+							m[b]->GetData(), width, size );
+						e.AddVectorToMatrixRows( 1, m[b]->GetData(), m[b]->GetData(), rows, width, col[k]->GetData() );
+						if( pick( 2 ) == 0 ) e.VectorAdd( m[b]->GetData(), m[c]->GetData(), m[pick( matrices )]->GetData(), size );
+					}
+					break;
+				case 16: // the gate x * sigmoid( s * x ), all of it or only its first steps
+					if( a != b ) {
+						e.VectorMultiply( m[a]->GetData(), m[b]->GetData(), size, scalar( s ) );
+						if( pick( 4 ) != 0 ) {
+							e.VectorSigmoid( m[b]->GetData(), m[b]->GetData(), size );
+							if( pick( 4 ) != 0 ) e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[b]->GetData(), size );
+						}
+					}
+					break;
+				case 17: { // the steps of an object normalisation, in place or not, cut short at random
+					const int t = pick( 2 ) == 0 ? a : b;
+					e.AddVectorToMatrixColumns( m[a]->GetData(), m[t]->GetData(), rows, width, rowVec( r ) );
+					switch( pick( 3 ) ) {
+						case 0:
+							e.VectorEltwiseMultiply( m[t]->GetData(), m[t]->GetData(), m[t]->GetData(), size );
+							if( pick( 2 ) == 0 ) {
+								e.SumMatrixColumns( rowVec( ( r + 1 ) % rowVectors ), m[t]->GetData(), rows, width );
+								e.VectorTanh( rowVec( ( r + 1 ) % rowVectors ), rowVec( ( r + 1 ) % rowVectors ), rows );
+							}
+							break;
+						case 1: {
+							e.MultiplyDiagMatrixByMatrix( rowVec( ( r + 2 ) % rowVectors ), rows, m[t]->GetData(), width, m[t]->GetData(), size );
+							const int u = pick( 2 ) == 0 ? t : c;
+							if( pick( 3 ) != 0 ) e.MultiplyMatrixByDiagMatrix( m[t]->GetData(), rows, width, col[k]->GetData(), m[u]->GetData(), size );
+							if( pick( 3 ) != 0 ) e.AddVectorToMatrixRows( 1, m[u]->GetData(), m[u]->GetData(), rows, width, col[( k + 1 ) % colVectors]->GetData() );
+							break;
+						}
+						default: break;
+					}
+					break;
+				}
+				case 18: // scale in place, maybe shift by columns, softmax by rows: attention's row chain without the products
+					e.VectorMultiply( m[a]->GetData(), m[a]->GetData(), size, scalar( s ) );
+					if( pick( 2 ) == 0 ) e.AddVectorToMatrixRows( 1, m[a]->GetData(), m[a]->GetData(), rows, width, col[k]->GetData() );
+					if( pick( 4 ) != 0 ) e.MatrixSoftmaxByRows( m[a]->GetData(), rows, width, pick( 2 ) == 0 ? m[a]->GetData() : m[b]->GetData() );
+					break;
+				case 19: e.MultiplyDiagMatrixByMatrix( rowVec( r ), rows, m[a]->GetData(), width, m[a]->GetData(), size ); break;
 			}
 			if( step % 3 == 2 ) e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size ); // keeps magnitudes bounded
 		}

@@ -165,7 +165,10 @@ def random_program():
     gpu, cpu = cdnn.Engine("gpu"), cdnn.Engine("cpu")
     worst, worst_seed = 0.0, -1
     # the second range holds the programs that once caught a copy of an in-place note reading its source too late
-    programs = [(1000 + i, 20 + 7 * (i % 9)) for i in range(40)] + [(5000 + i, 15 + 11 * (i % 13)) for i in range(600)]
+    # and the third one (seeds from 1 000 000 on also draw whole layer chains, cut short at random) those that caught a
+    # note written, when touched, ahead of a call recorded before it
+    programs = ([(1000 + i, 20 + 7 * (i % 9)) for i in range(40)] + [(5000 + i, 15 + 11 * (i % 13)) for i in range(600)]
+                + [(1000000 + i, 15 + 11 * (i % 13)) for i in range(2000)])
     for seed, steps in programs:
         got = cdnn.selftest_random_program(gpu, seed, steps)
         want = cdnn.selftest_random_program(cpu, seed, steps)
