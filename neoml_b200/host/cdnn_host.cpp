@@ -1243,8 +1243,9 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 		for( int step = 0; step < steps; ++step ) {
 			const int a = pick( matrices ), b = pick( matrices ), c = pick( matrices );
 			const int r = pick( rowVectors ), k = pick( colVectors ), s = pick( scalars );
-			// seeds from 1 000 000 on also draw the composite steps 15..19 (smaller seeds keep the programs they always made)
-			switch( pick( seed >= 1000000ull ? 20 : 15 ) ) {
+			// seeds from 1 000 000 on also draw the composite steps 15..19, seeds from 2 000 000 on the steps 20 and 21 with
+			// temporaries that die early (smaller seeds keep the programs they always made)
+			switch( pick( seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 ) ) {
 				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
 				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
 				case 2:
@@ -1317,6 +1318,37 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 					if( pick( 4 ) != 0 ) e.MatrixSoftmaxByRows( m[a]->GetData(), rows, width, pick( 2 ) == 0 ? m[a]->GetData() : m[b]->GetData() );
 					break;
 				case 19: e.MultiplyDiagMatrixByMatrix( rowVec( r ), rows, m[a]->GetData(), width, m[a]->GetData(), size ); break;
+				case 20: { // a normalisation whose row statistics live in ONE stack variable that dies while the matrix is only noted
+					CFloatHandleStackVar stats( e, 2 * rows );
+					e.SumMatrixColumns( stats.GetHandle(), m[a]->GetData(), rows, width );
+					e.VectorTanh( stats.GetHandle(), stats.GetHandle(), rows );
+					e.VectorFill( stats.GetHandle() + rows, static_cast<float>( rng.uniform() + 0.5 ), rows );
+					const int t = pick( 2 ) == 0 ? a : b;
+					e.AddVectorToMatrixColumns( m[a]->GetData(), m[t]->GetData(), rows, width, stats.GetHandle() );
+					if( pick( 2 ) == 0 ) e.VectorAddValue( stats.GetHandle() + rows, stats.GetHandle() + rows, rows, scalar( s ) );
+					if( pick( 3 ) != 0 ) e.MultiplyDiagMatrixByMatrix( stats.GetHandle() + rows, rows, m[t]->GetData(), width, m[t]->GetData(), size );
+					if( pick( 2 ) == 0 ) {
+						const int u = pick( 2 ) == 0 ? t : c;
+						e.MultiplyMatrixByDiagMatrix( m[t]->GetData(), rows, width, col[k]->GetData(), m[u]->GetData(), size );
+					}
+					break;
+				}
+				case 21: // a fully connected layer whose input blob is released right after the call, as reuse-memory mode does
+					if( a != b ) {
+						CPtr<CDnnBlob> input = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+						e.VectorCopy( input->GetData(), m[a]->GetData(), size );
+						e.MultiplyMatrixByTransposedMatrix( input->GetData(), rows, width, width, w[pick( weights )]->GetData(), width, width,
+							m[b]->GetData(), width, size );
+						if( pick( 2 ) == 0 ) e.AddVectorToMatrixRows( 1, m[b]->GetData(), m[b]->GetData(), rows, width, col[k]->GetData() );
+						input = nullptr;
+						if( pick( 2 ) == 0 ) { // and the block may come back at once, for something else
+							CPtr<CDnnBlob> other = CDnnBlob::CreateMatrix( e, CT_Float, rows, width );
+							other->Fill( 3.f );
+							e.VectorAdd( m[c]->GetData(), other->GetData(), m[c]->GetData(), size );
+							e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
+						}
+					}
+					break;
 			}
 			if( step % 3 == 2 ) e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size ); // keeps magnitudes bounded
 		}

@@ -168,7 +168,9 @@ def random_program():
     # and the third one (seeds from 1 000 000 on also draw whole layer chains, cut short at random) those that caught a
     # note written, when touched, ahead of a call recorded before it
     programs = ([(1000 + i, 20 + 7 * (i % 9)) for i in range(40)] + [(5000 + i, 15 + 11 * (i % 13)) for i in range(600)]
-                + [(1000000 + i, 15 + 11 * (i % 13)) for i in range(2000)])
+                + [(1000000 + i, 15 + 11 * (i % 13)) for i in range(2000)]
+                # from 2 000 000 on: also statistics in a stack variable and blobs that die while a note still reads them
+                + [(2000000 + i, 15 + 11 * (i % 13)) for i in range(2000)])
     for seed, steps in programs:
         got = cdnn.selftest_random_program(gpu, seed, steps)
         want = cdnn.selftest_random_program(cpu, seed, steps)
