@@ -1240,12 +1240,25 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 		auto rowVec = [&]( int i ) { return rowPairs[i / 2]->GetData() + ( i % 2 ) * rows; };
 		auto scalar = [&]( int i ) { return scalarBlob->GetData() + i; };
 		auto pick = [&]( int n ) { return static_cast<int>( rng.next() % n ); };
+		// attention: 2 heads, 128 queries and keys of depth 64 (the smallest shape an engine may treat as a score chain);
+		// what these calls compute reaches the compared state through copies of 24 x 32 pieces into the matrices above
+		const int heads = 2, seq = 128, depth = 64, scoreSize = heads * seq * seq, headSize = heads * seq * depth;
+		CPtr<CDnnBlob> q, kt, v, mask, attended, scores[2];
+		if( seed >= 3000000ull ) {
+			q = CDnnBlob::CreateVector( e, CT_Float, headSize ); fill( *q, -1.f, 1.f );
+			kt = CDnnBlob::CreateVector( e, CT_Float, headSize ); fill( *kt, -1.f, 1.f );
+			v = CDnnBlob::CreateVector( e, CT_Float, headSize ); fill( *v, -1.f, 1.f );
+			mask = CDnnBlob::CreateVector( e, CT_Float, seq * seq ); fill( *mask, -0.5f, 0.5f );
+			attended = CDnnBlob::CreateVector( e, CT_Float, headSize ); fill( *attended, -1.f, 1.f );
+			for( auto& b : scores ) { b = CDnnBlob::CreateVector( e, CT_Float, scoreSize ); fill( *b, -1.f, 1.f ); }
+		}
 		for( int step = 0; step < steps; ++step ) {
 			const int a = pick( matrices ), b = pick( matrices ), c = pick( matrices );
 			const int r = pick( rowVectors ), k = pick( colVectors ), s = pick( scalars );
 			// seeds from 1 000 000 on also draw the composite steps 15..19, seeds from 2 000 000 on the steps 20 and 21 with
-			// temporaries that die early (smaller seeds keep the programs they always made)
-			switch( pick( seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 ) ) {
+			// temporaries that die early, seeds from 3 000 000 on the calls of attention on buffers of their own, 22..30
+			// (smaller seeds keep the programs they always made)
+			switch( pick( seed >= 3000000ull ? 31 : seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 ) ) {
 				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
 				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
 				case 2:
@@ -1348,6 +1361,48 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 							e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
 						}
 					}
+					break;
+				case 22: // scores = Q * Kt
+					e.MultiplyMatrixByMatrix( heads, q->GetData(), seq, depth, kt->GetData(), seq, scores[a % 2]->GetData(), scoreSize );
+					break;
+				case 23: e.VectorMultiply( scores[a % 2]->GetData(), scores[a % 2]->GetData(), scoreSize, scalar( s ) ); break;
+				case 24: // + mask, in place or into the other score buffer
+					e.AddVectorToMatrixRows( 1, scores[a % 2]->GetData(), scores[b % 2]->GetData(), heads, seq * seq, mask->GetData() );
+					break;
+				case 25: e.MatrixSoftmaxByRows( scores[a % 2]->GetData(), heads * seq, seq, scores[b % 2]->GetData() ); break;
+				case 26: // out = scores * V; a piece of it goes into the compared state
+					e.MultiplyMatrixByMatrix( heads, scores[a % 2]->GetData(), seq, seq, v->GetData(), depth, attended->GetData(), headSize );
+					e.VectorCopy( m[c]->GetData(), attended->GetData() + pick( headSize - size ), size );
+					e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
+					break;
+				case 27: // somebody reads a score buffer
+					e.VectorCopy( m[c]->GetData(), scores[a % 2]->GetData() + pick( scoreSize - size ), size );
+					e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
+					break;
+				case 28: { // an operand of the chain changes while scores may still be only noted
+					CDnnBlob* operands[4] = { q.Ptr(), kt.Ptr(), v.Ptr(), mask.Ptr() };
+					CDnnBlob* chosen = operands[pick( 4 )];
+					e.VectorTanh( chosen->GetData(), chosen->GetData(), chosen->GetDataSize() );
+					break;
+				}
+				case 29: { // the whole chain as CMultiheadAttentionLayer issues it, scale and mask at random
+					const int x = a % 2, y = pick( 2 ), z = pick( 2 );
+					e.MultiplyMatrixByMatrix( heads, q->GetData(), seq, depth, kt->GetData(), seq, scores[x]->GetData(), scoreSize );
+					if( pick( 4 ) != 0 ) e.VectorMultiply( scores[x]->GetData(), scores[x]->GetData(), scoreSize, scalar( s ) );
+					int at = x;
+					if( pick( 2 ) == 0 ) {
+						e.AddVectorToMatrixRows( 1, scores[x]->GetData(), scores[y]->GetData(), heads, seq * seq, mask->GetData() );
+						at = y;
+					}
+					e.MatrixSoftmaxByRows( scores[at]->GetData(), heads * seq, seq, scores[z]->GetData() );
+					e.MultiplyMatrixByMatrix( heads, scores[z]->GetData(), seq, seq, v->GetData(), depth, attended->GetData(), headSize );
+					e.VectorCopy( m[c]->GetData(), attended->GetData() + pick( headSize - size ), size );
+					break;
+				}
+				case 30: // a score buffer is released and allocated again
+					scores[a % 2] = nullptr;
+					scores[a % 2] = CDnnBlob::CreateVector( e, CT_Float, scoreSize );
+					scores[a % 2]->Fill( static_cast<float>( rng.uniform() - 0.5 ) );
 					break;
 			}
 			if( step % 3 == 2 ) e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size ); // keeps magnitudes bounded

@@ -170,7 +170,9 @@ def random_program():
     programs = ([(1000 + i, 20 + 7 * (i % 9)) for i in range(40)] + [(5000 + i, 15 + 11 * (i % 13)) for i in range(600)]
                 + [(1000000 + i, 15 + 11 * (i % 13)) for i in range(2000)]
                 # from 2 000 000 on: also statistics in a stack variable and blobs that die while a note still reads them
-                + [(2000000 + i, 15 + 11 * (i % 13)) for i in range(2000)])
+                + [(2000000 + i, 15 + 11 * (i % 13)) for i in range(2000)]
+                # from 3 000 000 on: also the calls of attention (scores, scale, mask, softmax, values) in any order
+                + [(3000000 + i, 15 + 11 * (i % 13)) for i in range(1200)])
     for seed, steps in programs:
         got = cdnn.selftest_random_program(gpu, seed, steps)
         want = cdnn.selftest_random_program(cpu, seed, steps)

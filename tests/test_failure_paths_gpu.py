@@ -85,8 +85,8 @@ def test_fully_connected_products_that_are_only_noted_are_never_observable():
 
 
 def test_random_programs_end_in_the_state_the_reference_engine_ends_in():
-    """4 640 random call sequences (in place or not, shared allocations, buffers released in the middle, weights
-    replaced, whole layer chains cut short, temporaries that die early) leave every buffer as the reference CPU engine leaves it: nothing the engine
+    """5 840 random call sequences (in place or not, shared allocations, buffers released in the middle, weights
+    replaced, whole layer chains cut short, temporaries that die early, the calls of attention in any order) leave every buffer as the reference CPU engine leaves it: nothing the engine
     holds back is observable.  Rounding alone separates the engines by 2e-5 to 1e-4 here (a long program amplifies it);
     one call carried out twice, too late or too early shows as 1e-3 or more."""
     row = run_case("random_program")
