@@ -1252,13 +1252,29 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 			attended = CDnnBlob::CreateVector( e, CT_Float, headSize ); fill( *attended, -1.f, 1.f );
 			for( auto& b : scores ) { b = CDnnBlob::CreateVector( e, CT_Float, scoreSize ); fill( *b, -1.f, 1.f ); }
 		}
+		// convolution: 3 x 3, padding 1, 32 -> 32 channels on 2 x 12 x 12 images, so that any image may follow any other
+		const int images = 3, imageSize = 2 * 12 * 12 * 32, filterSize = 32 * 9 * 32;
+		CPtr<CDnnBlob> image[3], filter[2], freeTerms[2], zero;
+		std::unique_ptr<CConvolutionDesc> convolution;
+		if( seed >= 4000000ull ) {
+			for( auto& b : image ) { b = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 12, 12, 32 ); fill( *b, -1.f, 1.f ); }
+			for( auto& b : filter ) { b = CDnnBlob::CreateTensor( e, CT_Float, { 1, 32, 1, 3, 3, 1, 32 } ); fill( *b, -0.08f, 0.08f ); }
+			for( auto& b : freeTerms ) { b = CDnnBlob::CreateVector( e, CT_Float, 32 ); fill( *b, -0.2f, 0.2f ); }
+			zero = CDnnBlob::CreateVector( e, CT_Float, 1 );
+			zero->Fill( 0.f );
+			convolution.reset( e.InitBlobConvolution( image[0]->GetDesc(), 1, 1, 1, 1, 1, 1, filter[0]->GetDesc(), image[1]->GetDesc() ) );
+		}
+		auto convolve = [&]( int from, int to, int which ) {
+			const CConstFloatHandle freeTerm = freeTerms[which]->GetData();
+			e.BlobConvolution( *convolution, image[from]->GetData(), filter[which]->GetData(), &freeTerm, image[to]->GetData() );
+		};
 		for( int step = 0; step < steps; ++step ) {
 			const int a = pick( matrices ), b = pick( matrices ), c = pick( matrices );
 			const int r = pick( rowVectors ), k = pick( colVectors ), s = pick( scalars );
 			// seeds from 1 000 000 on also draw the composite steps 15..19, seeds from 2 000 000 on the steps 20 and 21 with
-			// temporaries that die early, seeds from 3 000 000 on the calls of attention on buffers of their own, 22..30
-			// (smaller seeds keep the programs they always made)
-			switch( pick( seed >= 3000000ull ? 31 : seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 ) ) {
+			// temporaries that die early, seeds from 3 000 000 on the calls of attention on buffers of their own, 22..30,
+			// seeds from 4 000 000 on the calls around a convolution, 31..38 (smaller seeds keep the programs they always made)
+			switch( pick( seed >= 4000000ull ? 39 : seed >= 3000000ull ? 31 : seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 ) ) {
 				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
 				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
 				case 2:
@@ -1397,6 +1413,44 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 					e.MatrixSoftmaxByRows( scores[at]->GetData(), heads * seq, seq, scores[z]->GetData() );
 					e.MultiplyMatrixByMatrix( heads, scores[z]->GetData(), seq, seq, v->GetData(), depth, attended->GetData(), headSize );
 					e.VectorCopy( m[c]->GetData(), attended->GetData() + pick( headSize - size ), size );
+					break;
+				}
+				case 31: if( a % images != b % images ) convolve( a % images, b % images, k % 2 ); break;
+				case 32: // another image added in place: the residual sum of a block
+					if( a % images != b % images ) {
+						e.VectorAdd( image[a % images]->GetData(), image[b % images]->GetData(), image[a % images]->GetData(), imageSize );
+					}
+					break;
+				case 33: e.VectorReLU( image[a % images]->GetData(), image[a % images]->GetData(), imageSize, zero->GetData() ); break;
+				case 34: fill( *filter[k % 2], -0.08f, 0.08f ); break; // new weights from the host
+				case 35: // the filter written on the device
+					e.VectorMultiply( filter[k % 2]->GetData(), filter[k % 2]->GetData(), filterSize, scalar( s ) );
+					e.VectorTanh( filter[k % 2]->GetData(), filter[k % 2]->GetData(), filterSize );
+					break;
+				case 36: // an image is released and allocated again
+					image[a % images] = nullptr;
+					image[a % images] = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 12, 12, 32 );
+					image[a % images]->Fill( static_cast<float>( rng.uniform() - 0.5 ) );
+					break;
+				case 37: // somebody reads an image; it is also kept bounded
+					e.VectorTanh( image[a % images]->GetData(), image[a % images]->GetData(), imageSize );
+					e.VectorCopy( m[c]->GetData(), image[a % images]->GetData() + pick( imageSize - size ), size );
+					break;
+				case 38: { // a residual block's tail: convolution, + shortcut, ReLU; the source may be released at once
+					const int from = a % images, to = ( from + 1 + pick( 2 ) ) % images, shortcut = pick( images );
+					convolve( from, to, k % 2 );
+					const bool early = pick( 2 ) == 0;
+					if( early ) image[from] = nullptr;
+					if( shortcut != to && ( !early || shortcut != from ) && pick( 4 ) != 0 ) {
+						e.VectorAdd( image[to]->GetData(), image[shortcut]->GetData(), image[to]->GetData(), imageSize );
+					}
+					if( pick( 4 ) != 0 ) e.VectorReLU( image[to]->GetData(), image[to]->GetData(), imageSize, zero->GetData() );
+					if( early ) {
+						image[from] = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 12, 12, 32 );
+						image[from]->Fill( static_cast<float>( rng.uniform() - 0.5 ) );
+					}
+					e.VectorCopy( m[c]->GetData(), image[to]->GetData() + pick( imageSize - size ), size );
+					e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
 					break;
 				}
 				case 30: // a score buffer is released and allocated again

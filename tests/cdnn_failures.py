@@ -187,7 +187,9 @@ def random_program():
                 # from 2 000 000 on: also statistics in a stack variable and blobs that die while a note still reads them
                 + [(2000000 + i, 15 + 11 * (i % 13)) for i in range(2000)]
                 # from 3 000 000 on: also the calls of attention (scores, scale, mask, softmax, values) in any order
-                + [(3000000 + i, 15 + 11 * (i % 13)) for i in range(1200)])
+                + [(3000000 + i, 15 + 11 * (i % 13)) for i in range(1200)]
+                # from 4 000 000 on: also convolutions with their in-place sum and ReLU, filters rewritten, sources released
+                + [(4000000 + i, 15 + 11 * (i % 13)) for i in range(1500)])
     for seed, steps in programs:
         got = cdnn.selftest_random_program(gpu, seed, steps)
         want = cdnn.selftest_random_program(cpu, seed, steps)
