@@ -1219,9 +1219,12 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 {
 	return guarded( [&] {
 		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
-		const int rows = 24, width = 32, size = rows * width;
+		// seeds from 5 000 000 on run on 1024-row matrices (from there an engine may keep a prepared form of a product's
+		// weights) and draw the steps 0..21, 39 and 40; the state then holds the first 24 rows of everything
+		const bool tall = seed >= 5000000ull;
+		const int seenRows = 24, rows = tall ? 1024 : seenRows, width = 32, size = rows * width;
 		const int matrices = 6, rowVectors = 4, colVectors = 3, scalars = 2, weights = 2;
-		if( stateFloats != matrices * size + rowVectors * rows + colVectors * width + scalars ) throw std::logic_error( "state size" );
+		if( stateFloats != matrices * seenRows * width + rowVectors * seenRows + colVectors * width + scalars ) throw std::logic_error( "state size" );
 		CSplitMix rng( seed );
 		auto fill = [&]( CDnnBlob& blob, float low, float high ) {
 			std::vector<float> v( static_cast<size_t>( blob.GetDataSize() ) );
@@ -1274,7 +1277,9 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 			// seeds from 1 000 000 on also draw the composite steps 15..19, seeds from 2 000 000 on the steps 20 and 21 with
 			// temporaries that die early, seeds from 3 000 000 on the calls of attention on buffers of their own, 22..30,
 			// seeds from 4 000 000 on the calls around a convolution, 31..38 (smaller seeds keep the programs they always made)
-			switch( pick( seed >= 4000000ull ? 39 : seed >= 3000000ull ? 31 : seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 ) ) {
+			int op = pick( tall ? 24 : seed >= 4000000ull ? 39 : seed >= 3000000ull ? 31 : seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 );
+			if( tall && op >= 22 ) op += 17;
+			switch( op ) {
 				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
 				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
 				case 2:
@@ -1453,6 +1458,18 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 					e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
 					break;
 				}
+				case 39: { // the weights written on the device
+					const int which = pick( weights );
+					e.VectorTanh( w[which]->GetData(), w[which]->GetData(), width * width );
+					break;
+				}
+				case 40: { // the weights released and allocated again
+					const int which = pick( weights );
+					w[which] = nullptr;
+					w[which] = CDnnBlob::CreateMatrix( e, CT_Float, width, width );
+					fill( *w[which], -0.3f, 0.3f );
+					break;
+				}
 				case 30: // a score buffer is released and allocated again
 					scores[a % 2] = nullptr;
 					scores[a % 2] = CDnnBlob::CreateVector( e, CT_Float, scoreSize );
@@ -1462,8 +1479,19 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 			if( step % 3 == 2 ) e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size ); // keeps magnitudes bounded
 		}
 		float* out = state;
-		for( auto& blob : m ) { blob->CopyTo( out ); out += size; }
-		for( int i = 0; i < 2; ++i ) { rowPairs[i]->CopyTo( out ); out += 2 * rows; }
+		std::vector<float> whole( static_cast<size_t>( size ) );
+		for( auto& blob : m ) {
+			blob->CopyTo( whole.data() );
+			std::copy( whole.begin(), whole.begin() + seenRows * width, out );
+			out += seenRows * width;
+		}
+		for( int i = 0; i < 2; ++i ) {
+			rowPairs[i]->CopyTo( whole.data() );
+			for( int half = 0; half < 2; ++half ) {
+				std::copy( whole.begin() + half * rows, whole.begin() + half * rows + seenRows, out );
+				out += seenRows;
+			}
+		}
 		for( auto& blob : col ) { blob->CopyTo( out ); out += width; }
 		scalarBlob->CopyTo( out );
 	} );

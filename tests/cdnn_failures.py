@@ -189,7 +189,10 @@ def random_program():
                 # from 3 000 000 on: also the calls of attention (scores, scale, mask, softmax, values) in any order
                 + [(3000000 + i, 15 + 11 * (i % 13)) for i in range(1200)]
                 # from 4 000 000 on: also convolutions with their in-place sum and ReLU, filters rewritten, sources released
-                + [(4000000 + i, 15 + 11 * (i % 13)) for i in range(1500)])
+                + [(4000000 + i, 15 + 11 * (i % 13)) for i in range(1500)]
+                # from 5 000 000 on: 1024-row matrices (an engine may keep a prepared form of a product's weights), the
+                # weights also written on the device and reallocated
+                + [(5000000 + i, 15 + 11 * (i % 13)) for i in range(1000)])
     for seed, steps in programs:
         got = cdnn.selftest_random_program(gpu, seed, steps)
         want = cdnn.selftest_random_program(cpu, seed, steps)
