@@ -85,7 +85,8 @@ enum {
 	// indexed by tile
 	TR_EPI_ACC_FULL = 7, TR_EPI_TMEM_READ = 8, TR_EPI_TILE_DONE = 9, TR_MMA_TILE_COMMITTED = 10, TR_EPI_LD0 = 11, TR_EPI_STS0 = 12,
 	TR_EPI_STG0 = 13, TR_EPI_CH1 = 14,
-	TR_ROLES = 16
+	TR_MMA_TILE_BEGIN = 16, TR_MMA_ACC_EMPTY = 17,
+	TR_ROLES = 18
 };
 __device__ __forceinline__ void trace(const ContractionParams& p, int role, int step)
 {
@@ -551,7 +552,9 @@ __global__ void __maxnreg__(128) contraction_tc_kernel(const ContractionParams p
 			for(int local = 0; local < myTiles && ok; ++local) {
 				const int set = local & 1;
 				const uint32_t accParity = ((local >> 1) & 1) ^ 1;
+				if(lane == 0) trace(p, TR_MMA_TILE_BEGIN, local);
 				if(!mbar_wait_bounded_warp(&accEmptyBar[set], accParity, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
+				if(lane == 0) trace(p, TR_MMA_ACC_EMPTY, local);
 				if(FOLD && !mbar_wait_bounded_warp(crossEmptyBar, (local & 1) ^ 1, abortFlag, p.status, SITE_ACC_EMPTY)) { ok = false; break; }
 				tc_fence_after_sync();
 				const uint32_t accMain = tmemBase + set * ACC_COLS;
