@@ -1221,7 +1221,9 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 		IMathEngine& e = *static_cast<IMathEngine*>( enginePtr );
 		// seeds from 5 000 000 on run on 1024-row matrices (from there an engine may keep a prepared form of a product's
 		// weights) and draw the steps 0..21, 39 and 40; the state then holds the first 24 rows of everything
-		const bool tall = seed >= 5000000ull;
+		// seeds from 6 000 000 on: small matrices again, all of the above but 39 and 40, and the padded pooling of a
+		// network's stem, 41..45
+		const bool tall = seed >= 5000000ull && seed < 6000000ull;
 		const int seenRows = 24, rows = tall ? 1024 : seenRows, width = 32, size = rows * width;
 		const int matrices = 6, rowVectors = 4, colVectors = 3, scalars = 2, weights = 2;
 		if( stateFloats != matrices * seenRows * width + rowVectors * seenRows + colVectors * width + scalars ) throw std::logic_error( "state size" );
@@ -1267,6 +1269,20 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 			zero->Fill( 0.f );
 			convolution.reset( e.InitBlobConvolution( image[0]->GetDesc(), 1, 1, 1, 1, 1, 1, filter[0]->GetDesc(), image[1]->GetDesc() ) );
 		}
+		// padded pooling: an image with a border of one pixel, then 3 x 3 maxima with stride 2
+		const int paddedSize = 2 * 14 * 14 * 32, pooledSize = 2 * 6 * 6 * 32;
+		const float border = 0.25f; // above part of the data: the border decides some maxima
+		CPtr<CDnnBlob> padded[2], pooled;
+		std::unique_ptr<CMaxPoolingDesc> pooling;
+		if( seed >= 6000000ull ) {
+			for( auto& b : padded ) { b = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 14, 14, 32 ); fill( *b, -1.f, 1.f ); }
+			pooled = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 6, 6, 32 );
+			fill( *pooled, -1.f, 1.f );
+			pooling.reset( e.InitMaxPooling( padded[0]->GetDesc(), 3, 3, 2, 2, pooled->GetDesc() ) );
+		}
+		auto pad = [&]( int from, int to ) {
+			e.BlobResizeImage( image[from]->GetDesc(), image[from]->GetData(), 1, 1, 1, 1, border, padded[to]->GetDesc(), padded[to]->GetData() );
+		};
 		auto convolve = [&]( int from, int to, int which ) {
 			const CConstFloatHandle freeTerm = freeTerms[which]->GetData();
 			e.BlobConvolution( *convolution, image[from]->GetData(), filter[which]->GetData(), &freeTerm, image[to]->GetData() );
@@ -1277,8 +1293,10 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 			// seeds from 1 000 000 on also draw the composite steps 15..19, seeds from 2 000 000 on the steps 20 and 21 with
 			// temporaries that die early, seeds from 3 000 000 on the calls of attention on buffers of their own, 22..30,
 			// seeds from 4 000 000 on the calls around a convolution, 31..38 (smaller seeds keep the programs they always made)
-			int op = pick( tall ? 24 : seed >= 4000000ull ? 39 : seed >= 3000000ull ? 31 : seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 );
+			int op = pick( seed >= 6000000ull ? 44 : tall ? 24 : seed >= 4000000ull ? 39 : seed >= 3000000ull ? 31
+				: seed >= 2000000ull ? 22 : seed >= 1000000ull ? 20 : 15 );
 			if( tall && op >= 22 ) op += 17;
+			if( seed >= 6000000ull && op >= 39 ) op += 2; // 39..43 -> 41..45
 			switch( op ) {
 				case 0: e.AddVectorToMatrixColumns( m[a]->GetData(), m[b]->GetData(), rows, width, rowVec( r ) ); break;
 				case 1: e.VectorEltwiseMultiply( m[a]->GetData(), m[b]->GetData(), m[c]->GetData(), size ); break;
@@ -1458,6 +1476,36 @@ CDNN_API int cdnn_selftest_random_program( void* enginePtr, unsigned long long s
 					e.VectorTanh( m[c]->GetData(), m[c]->GetData(), size );
 					break;
 				}
+				case 41: pad( a % images, b % 2 ); break;
+				case 42: // pooled = maxima of a padded image; a piece of it goes into the compared state
+					e.BlobMaxPooling( *pooling, padded[a % 2]->GetData(), nullptr, pooled->GetData() );
+					e.VectorCopy( m[c]->GetData(), pooled->GetData() + pick( pooledSize - size ), size );
+					break;
+				case 43: // somebody reads a padded image
+					e.VectorCopy( m[c]->GetData(), padded[a % 2]->GetData() + pick( paddedSize - size ), size );
+					break;
+				case 44: { // a stem: convolution, ReLU, border, pooling; the convolution's result may be released at once
+					const int from = a % images, to = ( from + 1 + pick( 2 ) ) % images, x = pick( 2 );
+					convolve( from, to, k % 2 );
+					if( pick( 4 ) != 0 ) e.VectorReLU( image[to]->GetData(), image[to]->GetData(), imageSize, zero->GetData() );
+					pad( to, x );
+					const bool early = pick( 2 ) == 0;
+					if( early ) {
+						image[to] = nullptr;
+						image[to] = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 12, 12, 32 );
+						image[to]->Fill( static_cast<float>( rng.uniform() - 0.5 ) );
+					}
+					if( pick( 4 ) != 0 ) {
+						e.BlobMaxPooling( *pooling, padded[x]->GetData(), nullptr, pooled->GetData() );
+						e.VectorCopy( m[c]->GetData(), pooled->GetData() + pick( pooledSize - size ), size );
+					}
+					break;
+				}
+				case 45: // a padded image is released and allocated again
+					padded[a % 2] = nullptr;
+					padded[a % 2] = CDnnBlob::Create2DImageBlob( e, CT_Float, 1, 2, 14, 14, 32 );
+					padded[a % 2]->Fill( static_cast<float>( rng.uniform() - 0.5 ) );
+					break;
 				case 39: { // the weights written on the device
 					const int which = pick( weights );
 					e.VectorTanh( w[which]->GetData(), w[which]->GetData(), width * width );

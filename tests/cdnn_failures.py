@@ -192,7 +192,9 @@ def random_program():
                 + [(4000000 + i, 15 + 11 * (i % 13)) for i in range(1500)]
                 # from 5 000 000 on: 1024-row matrices (an engine may keep a prepared form of a product's weights), the
                 # weights also written on the device and reallocated
-                + [(5000000 + i, 15 + 11 * (i % 13)) for i in range(1000)])
+                + [(5000000 + i, 15 + 11 * (i % 13)) for i in range(1000)]
+                # from 6 000 000 on: small matrices, everything above, and a stem's border + pooling around the convolutions
+                + [(6000000 + i, 15 + 11 * (i % 13)) for i in range(1500)])
     for seed, steps in programs:
         got = cdnn.selftest_random_program(gpu, seed, steps)
         want = cdnn.selftest_random_program(cpu, seed, steps)

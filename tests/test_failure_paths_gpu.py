@@ -85,10 +85,10 @@ def test_fully_connected_products_that_are_only_noted_are_never_observable():
 
 
 def test_random_programs_end_in_the_state_the_reference_engine_ends_in():
-    """8 340 random call sequences (in place or not, shared allocations, buffers released in the middle, weights
+    """9 840 random call sequences (in place or not, shared allocations, buffers released in the middle, weights
     replaced, whole layer chains cut short, temporaries that die early, the calls of attention and those around a convolution in any order) leave every buffer as the reference CPU engine leaves it: nothing the engine
     holds back is observable.  The gap is the largest difference in a buffer over that buffer's largest value (at least 1).
-    Rounding alone separates the engines by up to 2.6e-4 (worst of 24 640 programs; a long program amplifies it); one call
+    Rounding alone separates the engines by up to 2.6e-4 (worst of 29 640 programs; a long program amplifies it); one call
     carried out twice, too late or too early shows as 1e-3 to 10."""
     row = run_case("random_program")
     assert row["worst_gap"] < 5e-4, row
