@@ -204,6 +204,24 @@ def random_program():
     return {"worst_gap": worst, "seed": worst_seed}
 
 
+def random_program_cpu():
+    """The random programs themselves, on the reference CPU engine alone (no GPU needed): every class of seeds runs,
+    gives finite values, and gives the same values when it runs again (a program must depend on its seed only)."""
+    cpu = cdnn.Engine("cpu")
+    classes, worst = {}, 0.0
+    for base in (1000, 5000, 1000000, 2000000, 3000000, 4000000, 5000000, 6000000):
+        for i in range(12):
+            steps = 15 + 11 * (i % 13)
+            first = cdnn.selftest_random_program(cpu, base + i, steps)
+            again = cdnn.selftest_random_program(cpu, base + i, steps)
+            ok = bool(np.isfinite(first).all() and np.array_equal(first, again))
+            classes[str(base)] = classes.get(str(base), True) and ok
+            worst = max(worst, float(np.max(np.abs(first))))
+        other = cdnn.selftest_random_program(cpu, base + 1, 15 + 11)
+        classes[str(base)] = classes[str(base)] and not np.array_equal(other, cdnn.selftest_random_program(cpu, base + 2, 15 + 11))
+    return {"classes": classes, "largest_value": worst}
+
+
 def launch_counts():
     """Kernel launches per CDnn::RunOnce: what the engine's run-time fusion leaves of the call sequences NeoML issues.
     ResNet-50 makes 106 BlobConvolution + 130 element-wise / pooling / resize calls per pass, an encoder layer about 60
